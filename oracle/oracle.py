@@ -1,0 +1,247 @@
+"""Python face of the CPU oracle for `gemm_fp4`.
+
+TEST INFRASTRUCTURE ONLY: imported by tests, by the smoke check and by the
+benchmark's CPU-baseline leg.  The product package never imports this module.
+
+Three independent statements of the same arithmetic live here so that they can be
+checked against one another:
+
+* the C library built from ``gemm_fp4_ref.c`` (follows the reference interpreter,
+  crates/lex-front/src/interp.rs:30-47, 76-82, 500-526, 643-657),
+* a numpy twin (``np_*``) that uses numpy's own float16/float32 casts, and
+* the f64 restatement the reference's own test uses as its expected value
+  (crates/lex-front/tests/syntax.rs:509-523, 559-571).
+
+Parity status: pinned against the reference's known-answer recipes; the f16 bit
+patterns of staged weights are "parity unpinned" by any reference fixture (they
+follow from IEEE round-to-nearest-even alone).
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+import subprocess
+from pathlib import Path
+
+import numpy as np
+
+HERE = Path(__file__).resolve().parent
+_LIB = None
+
+# Decode tables written out as literals: the values of interp.rs:31 and the OCP
+# e4m3fn format, stated a second time (as scripts/qwen_nvfp4.py:27-42 does).
+E2M1 = np.array([0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0,
+                 -0.0, -0.5, -1.0, -1.5, -2.0, -3.0, -4.0, -6.0], dtype=np.float32)
+
+
+def e4m3_table() -> np.ndarray:
+    b = np.arange(256, dtype=np.uint32)
+    e = (b >> 3) & 0xF
+    m = (b & 7).astype(np.float64)
+    v = np.where(e == 0, m * 2.0 ** -9, (1.0 + m / 8.0) * 2.0 ** (e.astype(np.float64) - 7.0))
+    v = np.where((e == 15) & ((b & 7) == 7), np.nan, v)
+    v = np.where(b >> 7 == 1, -v, v)
+    return v.astype(np.float32)
+
+
+E4M3 = e4m3_table()
+
+
+def build(force: bool = False) -> Path:
+    """Compile the C oracle beside its source (make; gcc with OpenMP)."""
+    so = HERE / "liblexoracle.so"
+    src = HERE / "gemm_fp4_ref.c"
+    if force or not so.exists() or so.stat().st_mtime < src.stat().st_mtime:
+        subprocess.run(["make", "-C", str(HERE)], check=True, capture_output=True)
+    return so
+
+
+def lib() -> ctypes.CDLL:
+    global _LIB
+    if _LIB is None:
+        L = ctypes.CDLL(str(build()))
+        u32, vp, ci = ctypes.c_uint32, ctypes.c_void_p, ctypes.c_int
+        L.lexo_e2m1.restype = ctypes.c_float
+        L.lexo_e2m1.argtypes = [ctypes.c_uint8]
+        L.lexo_e4m3.restype = ctypes.c_float
+        L.lexo_e4m3.argtypes = [ctypes.c_uint8]
+        L.lexo_f32_to_f16.restype = ctypes.c_uint16
+        L.lexo_f32_to_f16.argtypes = [ctypes.c_float]
+        L.lexo_f16_to_f32.restype = ctypes.c_float
+        L.lexo_f16_to_f32.argtypes = [ctypes.c_uint16]
+        L.lexo_dequant_fp4_f16.restype = None
+        L.lexo_dequant_fp4_f16.argtypes = [u32, u32, vp, vp, vp, vp]
+        L.lexo_gemm_fp4_rows.restype = ci
+        L.lexo_gemm_fp4_rows.argtypes = [u32, u32, u32, u32, vp, vp, vp, vp, vp, vp, u32, u32, ci]
+        L.lexo_max_rel_err.restype = ctypes.c_float
+        L.lexo_max_rel_err.argtypes = [vp, vp, ctypes.c_size_t]
+        L.lexo_err_of_scale.restype = None
+        L.lexo_err_of_scale.argtypes = [vp, vp, ctypes.c_size_t, vp]
+        L.lexo_max_threads.restype = ci
+        _LIB = L
+    return _LIB
+
+
+def _p(a: np.ndarray) -> int:
+    return a.ctypes.data
+
+
+def _check_shapes(x16, wq, ws, wg):
+    m, k = x16.shape
+    n = wq.shape[0]
+    if x16.dtype != np.float16 and x16.dtype != np.uint16:
+        raise TypeError("x must be float16 (or its uint16 bit patterns)")
+    if wq.shape != (n, k // 2) or ws.shape != (n, k // 16) or wg.shape != (n,):
+        # the rank-1 row-scale rule of crates/lex-front/tests/tensor_shapes.rs:65-67
+        raise ValueError(f"shapes do not fit gemm_fp4: x{x16.shape} wq{wq.shape} ws{ws.shape} wg{wg.shape}")
+    return m, n, k
+
+
+def gemm_fp4(x16, wq, ws, wg, r=None, bk: int = 64, rows=None, threads: int = 0) -> np.ndarray:
+    """The oracle: y f32[m,n].  `rows=(n0,n1)` computes only those W rows (others stay 0)."""
+    m, n, k = _check_shapes(x16, wq, ws, wg)
+    x16 = np.ascontiguousarray(x16).view(np.uint16)
+    wq = np.ascontiguousarray(wq).view(np.uint8)
+    ws = np.ascontiguousarray(ws).view(np.uint8)
+    wg = np.ascontiguousarray(wg, dtype=np.float32)
+    y = np.zeros((m, n), dtype=np.float32)
+    rp = None
+    if r is not None:
+        r = np.ascontiguousarray(r, dtype=np.float32)
+        assert r.shape == (m, n)
+        rp = _p(r)
+    n0, n1 = rows if rows is not None else (0, n)
+    rc = lib().lexo_gemm_fp4_rows(m, n, k, bk, _p(x16), _p(wq), _p(ws), _p(wg), rp, _p(y), n0, n1, threads)
+    if rc != 0:
+        raise ValueError(f"gemm_fp4 oracle rejected the shape (rc={rc}): k={k} does not divide by bk={bk}")
+    return y
+
+
+def dequant_fp4_f16(wq, ws, wg) -> np.ndarray:
+    """uint16 [n,k]: the f16 bit pattern of every staged weight."""
+    n, kh = wq.shape
+    k = 2 * kh
+    wq = np.ascontiguousarray(wq).view(np.uint8)
+    ws = np.ascontiguousarray(ws).view(np.uint8)
+    wg = np.ascontiguousarray(wg, dtype=np.float32)
+    out = np.empty((n, k), dtype=np.uint16)
+    lib().lexo_dequant_fp4_f16(n, k, _p(wq), _p(ws), _p(wg), _p(out))
+    return out
+
+
+def max_rel_err(got, want) -> float:
+    got = np.ascontiguousarray(got, dtype=np.float32)
+    want = np.ascontiguousarray(want, dtype=np.float32)
+    return float(lib().lexo_max_rel_err(_p(got), _p(want), got.size))
+
+
+def err_of_scale(got, want):
+    """(error of scale, scale, floored per-element relative error)."""
+    got = np.ascontiguousarray(got, dtype=np.float32)
+    want = np.ascontiguousarray(want, dtype=np.float32)
+    out = np.zeros(3, dtype=np.float64)
+    lib().lexo_err_of_scale(_p(got), _p(want), got.size, _p(out))
+    return float(out[0]), float(out[1]), float(out[2])
+
+
+def max_threads() -> int:
+    return int(lib().lexo_max_threads())
+
+
+# ---------------------------------------------------------------- numpy twin
+
+def np_codes(wq: np.ndarray) -> np.ndarray:
+    """uint8 [n,k]: the 4-bit code of every column; even column = low nibble (interp.rs:650)."""
+    b = wq.view(np.uint8)
+    out = np.empty((b.shape[0], b.shape[1] * 2), dtype=np.uint8)
+    out[:, 0::2] = b & 0xF
+    out[:, 1::2] = b >> 4
+    return out
+
+
+def np_dequant_f32(wq, ws, wg) -> np.ndarray:
+    """f32 [n,k] before staging: (e2m1 * e4m3) * wg, each product rounded to f32."""
+    with np.errstate(invalid="ignore", over="ignore"):
+        v = E2M1[np_codes(wq)] * np.repeat(E4M3[ws.view(np.uint8)], 16, axis=1)
+        return (v * wg.astype(np.float32)[:, None]).astype(np.float32)
+
+
+def np_dequant_f16(wq, ws, wg) -> np.ndarray:
+    with np.errstate(over="ignore", invalid="ignore"):
+        return np_dequant_f32(wq, ws, wg).astype(np.float16)
+
+
+def np_gemm_fp4(x16, wq, ws, wg, r=None, bk: int = 64) -> np.ndarray:
+    """Small cases only: the interpreter's order, vectorised across (i, j)."""
+    m, n, k = _check_shapes(x16, wq, ws, wg)
+    if k % bk:
+        raise ValueError("k does not divide by bk")
+    a = x16.view(np.float16).astype(np.float32)
+    b = np_dequant_f16(wq, ws, wg).astype(np.float32)
+    acc = np.zeros((m, n), dtype=np.float32)
+    with np.errstate(invalid="ignore", over="ignore"):
+        for t in range(0, k, bk):
+            s = np.zeros((m, n), dtype=np.float32)
+            for p in range(t, t + bk):
+                s = s + a[:, p, None] * b[None, :, p]
+            acc = acc + s
+        if r is not None:
+            acc = acc + r.astype(np.float32)
+    return acc
+
+
+# ------------------------------------------- the reference's own test recipes
+
+def lcg_fill(length: int, seed: int) -> np.ndarray:
+    """crates/lex-front/tests/syntax.rs:387-395: floats in [-0.5, 0.5)."""
+    out = np.empty(length, dtype=np.float32)
+    x = seed & 0xFFFFFFFF
+    for i in range(length):
+        x = (x * 1664525 + 1013904223) & 0xFFFFFFFF
+        out[i] = np.float32(np.float32(x >> 9) / np.float32(1 << 23)) - np.float32(0.5)
+    return out
+
+
+def kat_inputs(m: int, n: int, k: int, residual: bool = False):
+    """Inputs of `the_fp4_gemm_decodes_stages_and_multiplies` (syntax.rs:543-551) or, with
+    `residual`, of `the_residual_epilogue_adds_the_stream_to_the_product` (syntax.rs:652-658)."""
+    if not residual:
+        x = lcg_fill(m * k, 31)
+        i = np.arange(n * k // 2, dtype=np.int64)
+        q = ((i * 97 + 13) % 256).astype(np.uint8)
+        j = np.arange(n * k // 16, dtype=np.int64)
+        sc = (0x30 + j % 7).astype(np.uint8)
+        g = (0.5 + (np.arange(n) % 5).astype(np.float32) * np.float32(0.25)).astype(np.float32)
+        r = None
+    else:
+        x = lcg_fill(m * k, 51)
+        i = np.arange(n * k // 2, dtype=np.int64)
+        q = ((i * 31 + 7) % 256).astype(np.uint8)
+        j = np.arange(n * k // 16, dtype=np.int64)
+        sc = (0x30 + j % 5).astype(np.uint8)
+        g = (0.5 + (np.arange(n) % 3).astype(np.float32) * np.float32(0.5)).astype(np.float32)
+        r = lcg_fill(m * n, 52).reshape(m, n)
+    # Tensor::new rounds x to f16 on creation (interp.rs:61-69).
+    x16 = x.reshape(m, k).astype(np.float16)
+    return x16, q.reshape(n, k // 2), sc.reshape(n, k // 16), g, r
+
+
+def f64_restatement(x16, wq, ws, wg) -> np.ndarray:
+    """The expected value of syntax.rs:559-575: decode in f64 with the test's own tables,
+    round the weight to f16 from f64, multiply and sum in f64."""
+    mag = np.array([0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0], dtype=np.float64)
+    c = np_codes(wq)
+    e2 = np.where(c & 8, -mag[c & 7], mag[c & 7])
+    b = ws.view(np.uint8).astype(np.int64)
+    e, mm = (b >> 3) & 15, (b & 7).astype(np.float64)
+    v = np.where(e == 0, mm / 8.0 * 2.0 ** -6, (1.0 + mm / 8.0) * 2.0 ** (e.astype(np.float64) - 7.0))
+    v = np.where(b & 0x80, -v, v)
+    w = e2 * np.repeat(v, 16, axis=1) * wg.astype(np.float64)[:, None]
+    w = w.astype(np.float16).astype(np.float64)          # half::f16::from_f64
+    return x16.view(np.float16).astype(np.float64) @ w.T
+
+
+def ensure_built() -> None:
+    build()
+    if not os.path.exists(HERE / "liblexoracle.so"):
+        raise RuntimeError("oracle library missing after build")

@@ -1,0 +1,155 @@
+"""The CPU oracle against the reference's own known-answer recipes and against two
+independent restatements (numpy float16 casts; the reference test's f64 arithmetic)."""
+import numpy as np
+import pytest
+
+from lex_gpu_b200 import inputs
+from oracle import oracle as O
+
+
+def test_e2m1_table_matches_the_literal_values():
+    # crates/lex-front/src/interp.rs:30-34 ; crates/lex-front/tests/syntax.rs:509-513
+    want = [0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0]
+    L = O.lib()
+    for c in range(16):
+        got = L.lexo_e2m1(c)
+        assert got == (-want[c & 7] if c & 8 else want[c & 7])
+    assert np.signbit(np.float32(L.lexo_e2m1(8)))          # code 8 is -0.0
+
+
+def test_e4m3_all_256_bytes():
+    # crates/lex-front/src/interp.rs:37-47 ; scripts/qwen_nvfp4.py:32-40
+    L = O.lib()
+    for b in range(256):
+        got = np.float32(L.lexo_e4m3(b))
+        want = O.E4M3[b]
+        if b & 0x7F == 0x7F:
+            assert np.isnan(got) and np.isnan(want)
+        else:
+            assert got == want and np.signbit(got) == np.signbit(want), hex(b)
+    assert O.E4M3[0x7E] == 448.0 and O.E4M3[0x01] == 2.0 ** -9 and O.E4M3[0x38] == 1.0
+
+
+def test_f16_rounding_agrees_with_numpy_on_every_boundary():
+    """Every f16 value, the midpoint to its neighbour and one f32 ulp either side of it."""
+    L = O.lib()
+    h = np.arange(0x0000, 0x7C00, dtype=np.uint16)
+    v = h.view(np.float16).astype(np.float32)
+    nxt = (h + 1).astype(np.uint16).view(np.float16).astype(np.float64)
+    mid = ((v.astype(np.float64) + nxt) / 2).astype(np.float32)       # exact in f32
+    cases = np.concatenate([v, mid, np.nextafter(mid, np.float32(0)), np.nextafter(mid, np.float32(np.inf)),
+                            np.array([65504.0, 65519.99, 65520.0, 65536.0, 1e9, 2.0 ** -25, 2.0 ** -24,
+                                      np.nextafter(np.float32(2.0 ** -25), np.float32(1)), 0.0, 1e-30],
+                                     dtype=np.float32)])
+    cases = np.concatenate([cases, -cases])
+    with np.errstate(over="ignore"):
+        want = cases.astype(np.float16).view(np.uint16)
+    got = np.array([L.lexo_f32_to_f16(float(c)) for c in cases], dtype=np.uint16)
+    assert np.array_equal(got, want)
+    back = np.array([L.lexo_f16_to_f32(int(x)) for x in h], dtype=np.float32)
+    assert np.array_equal(back, v)
+    assert L.lexo_f32_to_f16(float("nan")) & 0x7C00 == 0x7C00 and L.lexo_f32_to_f16(float("nan")) & 0x3FF
+    assert L.lexo_f32_to_f16(float("inf")) == 0x7C00 and L.lexo_f32_to_f16(float("-inf")) == 0xFC00
+
+
+def test_f16_rounding_agrees_with_numpy_on_random_f32():
+    rng = np.random.Generator(np.random.PCG64(5))
+    bits = rng.integers(0, 2 ** 32, size=200_000, dtype=np.uint64).astype(np.uint32)
+    f = bits.view(np.float32)
+    f = f[np.isfinite(f)]
+    small = (rng.standard_normal(200_000) * np.exp2(rng.uniform(-26, 17, 200_000))).astype(np.float32)
+    L = O.lib()
+    for arr in (f[:60_000], small[:120_000]):
+        with np.errstate(over="ignore"):
+            want = arr.astype(np.float16).view(np.uint16)
+        got = np.array([L.lexo_f32_to_f16(float(c)) for c in arr], dtype=np.uint16)
+        assert np.array_equal(got, want)
+
+
+@pytest.mark.parametrize("bm,bn,bk", [(128, 128, 64), (64, 128, 32)])   # nvidia-ada, apple-m-series
+def test_known_answer_recipe_of_the_reference_test(bm, bn, bk):
+    """crates/lex-front/tests/syntax.rs:525-585: (m,n,k) = (bm, 2bn, 2bk); y[i,j] for i step 9,
+    j step 7 within 1e-3 * max(|want|, 1) of the f64 restatement."""
+    m, n, k = bm, 2 * bn, 2 * bk
+    x16, q, sc, g, _ = O.kat_inputs(m, n, k)
+    got = O.gemm_fp4(x16, q, sc, g, bk=bk)
+    want = O.f64_restatement(x16, q, sc, g)
+    sub_g, sub_w = got[::9, ::7].astype(np.float64), want[::9, ::7]
+    assert np.all(np.abs(sub_g - sub_w) < 1e-3 * np.maximum(np.abs(sub_w), 1.0))
+    # stronger than the reference asks: every element, and the numpy twin bit for bit
+    assert np.all(np.abs(got - want) < 1e-3 * np.maximum(np.abs(want), 1.0))
+    assert np.array_equal(got, O.np_gemm_fp4(x16, q, sc, g, bk=bk))
+    assert np.abs(want).max() > 1e-3
+
+
+@pytest.mark.parametrize("bm,bn,bk", [(128, 128, 64), (64, 128, 32)])
+def test_residual_recipe_of_the_reference_test(bm, bn, bk):
+    """crates/lex-front/tests/syntax.rs:634-683: with r minus with a zero r is r to 1e-5."""
+    m, n, k = bm, 2 * bn, bk
+    x16, q, sc, g, r = O.kat_inputs(m, n, k, residual=True)
+    with_r = O.gemm_fp4(x16, q, sc, g, r=r, bk=bk)
+    without = O.gemm_fp4(x16, q, sc, g, r=np.zeros_like(r), bk=bk)
+    assert np.all(np.abs((with_r - without).astype(np.float64) - r) < 1e-5)
+    assert np.array_equal(without, O.gemm_fp4(x16, q, sc, g, bk=bk))
+
+
+def test_dequant_bits_c_vs_numpy_on_adversarial_scales():
+    wq, ws, wg = inputs.adversarial_dequant_case()
+    got = O.dequant_fp4_f16(wq, ws, wg)
+    want = O.np_dequant_f16(wq, ws, wg).view(np.uint16)
+    nan_g = (got & 0x7C00 == 0x7C00) & (got & 0x3FF != 0)
+    nan_w = (want & 0x7C00 == 0x7C00) & (want & 0x3FF != 0)
+    assert np.array_equal(nan_g, nan_w)
+    assert np.array_equal(got[~nan_g], want[~nan_w])
+    # -0 codes give f16 -0 when the scales are positive (row 0: wg = 1, scale byte 0x38 = 1.0)
+    codes = O.np_codes(wq)
+    col = 0x38 * 16 + int(np.where(codes[0, 0x38 * 16:0x38 * 16 + 16] == 8)[0][0])
+    assert got[0, col] == 0x8000
+    # the NaN scale bytes decode to NaN, not to +-480
+    assert np.all(nan_g[0, 0x7F * 16:0x7F * 16 + 16]) and np.all(nan_g[0, 0xFF * 16:0xFF * 16 + 16])
+
+
+def test_c_oracle_equals_numpy_twin_on_config0():
+    x, wq, ws, wg = inputs.make_case(128, 128, 64)
+    y = O.gemm_fp4(x, wq, ws, wg)
+    assert np.array_equal(y, O.np_gemm_fp4(x, wq, ws, wg))
+    assert np.abs(y).max() > 1e-3
+    # thread count does not change a single bit (rows are independent)
+    assert np.array_equal(y, O.gemm_fp4(x, wq, ws, wg, threads=1))
+
+
+def test_row_slices_and_ragged_m():
+    x, wq, ws, wg = inputs.make_case(5, 48, 128, seed_base=10)
+    full = O.gemm_fp4(x, wq, ws, wg)
+    part = O.gemm_fp4(x, wq, ws, wg, rows=(16, 35))
+    assert np.array_equal(part[:, 16:35], full[:, 16:35]) and not part[:, :16].any() and not part[:, 35:].any()
+    assert np.array_equal(full, O.np_gemm_fp4(x, wq, ws, wg))
+
+
+def test_shapes_the_operator_rejects():
+    x, wq, ws, wg = inputs.make_case(4, 16, 96)
+    with pytest.raises(ValueError):          # k = 96 does not divide by bk = 64 (syntax.rs:1513-1516)
+        O.gemm_fp4(x, wq, ws, wg, bk=64)
+    with pytest.raises(ValueError):          # a rank-2 row scale is refused (tensor_shapes.rs:65-67)
+        O.gemm_fp4(x, wq, ws, wg.reshape(-1, 1), bk=32)
+    assert O.gemm_fp4(x, wq, ws, wg, bk=32).shape == (4, 16)
+
+
+def test_metrics():
+    want = np.array([1.0, -2.0, 0.0, 4.0], dtype=np.float32)
+    got = np.array([1.001, -2.0, 0.0005, 4.0], dtype=np.float32)
+    assert abs(O.max_rel_err(got, want) - 0.5) < 1e-6          # 0.0005 / max(0, 1e-3)
+    e, scale, rel = O.err_of_scale(got, want)
+    assert scale == 4.0 and abs(e - 0.001 / 4.0) < 1e-7
+    assert abs(rel - 0.0005 / 4e-3) < 1e-6
+    assert O.max_rel_err(np.array([np.inf], dtype=np.float32), np.array([1.0], dtype=np.float32)) == np.inf
+
+
+def test_scale_generator_stays_in_the_normal_range():
+    _, ws, wg = inputs.make_weights(64, 1024, seed_base=3)
+    assert ws.min() >= 0x08 and ws.max() <= 0x48
+    v = O.E4M3[ws]
+    assert v.min() >= 2.0 ** -6 and v.max() <= 4.0
+    assert wg.min() >= 0.5 and wg.max() < 2.0
+    # nearest-even rounding of the generator: exact values map to themselves
+    assert np.array_equal(inputs.nearest_e4m3(O.E4M3[1:0x7F].astype(np.float64)), np.arange(1, 0x7F, dtype=np.uint8))
