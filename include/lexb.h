@@ -1,0 +1,175 @@
+/* liblexb - the C ABI of the sm_100a (B200) backend for lex's `gemm_fp4` operator.
+ *
+ *   y[m,n] (f32) = x[m,k] (f16) . dequant(wq, ws, wg)^T (+ r[m,n])
+ *     wq u8[n,k/2]  two E2M1 codes per byte, even column in the low nibble
+ *     ws u8[n,k/16] one E4M3 (OCP e4m3fn) scale per 16 weights
+ *     wg f32[n]     one scale per row
+ *
+ * This is the boundary a Rust `lex-cuda` backend would bind with `extern "C"` in place of
+ * its NVRTC + driver path: each entry point names the reference interface it stands in
+ * for (paths are relative to the lex-gpu tree).  Every function returns 0 on success and a
+ * non-zero lexb_status otherwise, with a message in lexb_last_error(); nothing aborts or
+ * panics.  All pointers in signatures are plain C; device memory is referred to through
+ * opaque lexb_buffer handles (which can wrap a device pointer the caller already owns).
+ * There is no CPU fallback: without a compute-capability-10.x device lexb_open fails.
+ */
+#ifndef LEXB_H
+#define LEXB_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(_WIN32)
+#define LEXB_API
+#else
+#define LEXB_API __attribute__((visibility("default")))
+#endif
+
+typedef enum lexb_status {
+    LEXB_OK = 0,
+    LEXB_ERR_ARG = 1,          /* null handle, short buffer, misaligned pointer, wrong binding */
+    LEXB_ERR_SHAPE = 2,        /* a shape the operator rejects ("does not divide") */
+    LEXB_ERR_CUDA = 3,         /* a CUDA call failed; the message carries its error string */
+    LEXB_ERR_UNSUPPORTED = 4,  /* no sm_100 device, or a schedule the device cannot hold */
+    LEXB_ERR_DEVICE = 5        /* a kernel reported a failure through the status word */
+} lexb_status;
+
+typedef struct lexb_gpu lexb_gpu;           /* lex_cuda::Gpu        crates/lex-cuda/src/device.rs:316-325 */
+typedef struct lexb_buffer lexb_buffer;     /* lex_cuda::Buffer     crates/lex-cuda/src/device.rs:257-278 */
+typedef struct lexb_pipeline lexb_pipeline; /* lex_cuda::Pipeline   crates/lex-cuda/src/device.rs:281-301 */
+
+/* lex_cuda::DeviceInfo, crates/lex-cuda/src/device.rs:303-310 (+ what a B200 plan needs) */
+typedef struct lexb_device_info {
+    char name[128];
+    int cc_major, cc_minor;
+    int sm_count;
+    int unified_memory;                     /* always 0: weights are staged across PCIe */
+    size_t max_threadgroup_bytes;           /* opt-in dynamic shared memory per block */
+    uint64_t recommended_working_set_bytes; /* total device memory, as the reference reports */
+    size_t l2_bytes;
+} lexb_device_info;
+
+/* Optional schedule override, the counterpart of a `.lx` schedule line
+ * (crates/lex-front/lx/gemm_fp4.lx:38-39) and of the LEX_GEMM_CU_* variables
+ * (crates/lex-msl/src/gemm.rs:90-135).  Zero fields mean "choose". */
+typedef struct lexb_sched {
+    uint32_t kernel;  /* 0 auto, 1 split-K matvec (m <= 16), 2 tcgen05 GEMM */
+    uint32_t tm;      /* tokens per CTA tile of the GEMM: multiple of 16, <= 256 */
+    uint32_t stages;  /* pipeline depth of the GEMM */
+    uint32_t kc;      /* K columns of x staged per chunk in the matvec: multiple of 1024 */
+} lexb_sched;
+
+/* lex_msl::program::Lowered, crates/lex-msl/src/program.rs:44-63: the launch descriptor.
+ * `writes` is per binding in the order [x, wq, ws, wg, (r), y] (crates/lex-msl/src/gemm.rs:78-82). */
+typedef struct lexb_lowered {
+    char entry[96];              /* gemm_fp4[_res]_{m}_{n}_{k}_{bm}_{bn}_{bk}, crates/lex-front/src/syntax.rs:933-939 */
+    uint32_t grid, grid2;
+    uint32_t threads;
+    uint32_t threadgroup_bytes;  /* dynamic shared memory */
+    uint32_t nbind;
+    uint8_t writes[6];
+    uint32_t kernel;             /* 1 matvec, 2 tcgen05 */
+    uint32_t m, n, k, residual;
+    uint32_t bm, bn, bk, stages;
+} lexb_lowered;
+
+/* lex_cuda::Step, crates/lex-cuda/src/device.rs:314: a pipeline and its buffers in binding
+ * order [x, wq, ws, wg, (r), y] (QBuf::bind, crates/lex-rt/src/qwen_run.rs:375-387). */
+typedef struct lexb_step {
+    const lexb_pipeline* pipeline;
+    lexb_buffer* const* buffers;
+    uint32_t nbuffers;           /* 5 without residual, 6 with */
+} lexb_step;
+
+LEXB_API const char* lexb_last_error(void);   /* message of this thread's last failing call */
+LEXB_API const char* lexb_version(void);
+
+/* Gpu::open, crates/lex-cuda/src/device.rs:350-404.  Takes a device ordinal (the reference
+ * always opens device 0) and uses the device's primary context, so that memory allocated by
+ * another runtime in the same process (a collective library's buffers) can be wrapped. */
+LEXB_API int lexb_open(int device, lexb_gpu** out);
+LEXB_API void lexb_close(lexb_gpu* gpu);
+/* Gpu::info, crates/lex-cuda/src/device.rs:424-458 */
+LEXB_API int lexb_info(lexb_gpu* gpu, lexb_device_info* out);
+/* Launches go to the gpu's own stream unless a caller-owned CUDA stream is set (null = own). */
+LEXB_API int lexb_set_stream(lexb_gpu* gpu, void* cuda_stream);
+LEXB_API void* lexb_get_stream(lexb_gpu* gpu);
+/* cuCtxSynchronize in Gpu::run_launches, crates/lex-cuda/src/device.rs:668-671 */
+LEXB_API int lexb_sync(lexb_gpu* gpu);
+
+/* Gpu::zeroed / upload / write / download / download_at, crates/lex-cuda/src/device.rs:527-627 */
+LEXB_API int lexb_alloc(lexb_gpu* gpu, size_t bytes, lexb_buffer** out);          /* contents undefined */
+LEXB_API int lexb_zeroed(lexb_gpu* gpu, size_t bytes, lexb_buffer** out);
+LEXB_API int lexb_wrap(lexb_gpu* gpu, void* device_ptr, size_t bytes, lexb_buffer** out); /* not owned */
+LEXB_API int lexb_free(lexb_buffer* buf);                                          /* Buffer::drop */
+LEXB_API void* lexb_buffer_ptr(const lexb_buffer* buf);
+LEXB_API size_t lexb_buffer_bytes(const lexb_buffer* buf);                         /* Buffer::len_bytes */
+LEXB_API int lexb_upload(lexb_gpu* gpu, lexb_buffer* dst, size_t byte_off, const void* src, size_t bytes);
+LEXB_API int lexb_download(lexb_gpu* gpu, const lexb_buffer* src, size_t byte_off, void* dst, size_t bytes);
+LEXB_API int lexb_memset(lexb_gpu* gpu, lexb_buffer* dst, int byte, size_t bytes);
+/* Page-locked host memory for the per-step activations and results. */
+LEXB_API int lexb_host_alloc(size_t bytes, void** out);
+LEXB_API int lexb_host_free(void* p);
+
+/* lx_kernels::gemm + Gpu::build_lowered, crates/lex-rt/src/lx_kernels.rs:43-107 and
+ * crates/lex-cuda/src/device.rs:475-483: choose the kernel and tiles for a shape.  Nothing is
+ * compiled at run time; the kernels are built for sm_100a ahead of time.  Shapes must
+ * satisfy n % 128 == 0 and k % 64 == 0 (m > 16) or n % 16 == 0 and k % 32 == 0 (m <= 16);
+ * others are refused with LEXB_ERR_SHAPE, as the `.lx` program refuses extents that do not
+ * divide (crates/lex-front/src/syntax.rs:1513-1516). */
+LEXB_API int lexb_gemm_fp4_plan(lexb_gpu* gpu, uint32_t m, uint32_t n, uint32_t k, int residual,
+                                const lexb_sched* sched_or_null, lexb_pipeline** out);
+LEXB_API void lexb_pipeline_free(lexb_pipeline* p);                                /* Pipeline::drop */
+LEXB_API int lexb_pipeline_describe(const lexb_pipeline* p, lexb_lowered* out);
+
+/* One Step, asynchronous on the gpu's stream: Gpu::run, crates/lex-cuda/src/device.rs:629-648.
+ * Buffers in the order [x, wq, ws, wg, (r), y]; r must be null exactly when the pipeline
+ * was planned without a residual. */
+LEXB_API int lexb_gemm_fp4_launch(lexb_gpu* gpu, const lexb_pipeline* p, const lexb_buffer* x,
+                                  const lexb_buffer* wq, const lexb_buffer* ws, const lexb_buffer* wg,
+                                  const lexb_buffer* r_or_null, lexb_buffer* y);
+/* The call a runtime makes per prefill chunk with host activations: copy x from host memory
+ * into x_dev, launch, copy y_dev back into y_host, wait.  The weights stay resident, as
+ * lex-rt keeps them (Runner::forward_with writes only per-step inputs,
+ * crates/lex-rt/src/qwen_run.rs:2348-2373, and downloads the result, :2401-2404). */
+LEXB_API int lexb_gemm_fp4_run_host(lexb_gpu* gpu, const lexb_pipeline* p, const void* x_host, lexb_buffer* x_dev,
+                                    const lexb_buffer* wq, const lexb_buffer* ws, const lexb_buffer* wg,
+                                    const lexb_buffer* r_or_null, lexb_buffer* y_dev, void* y_host);
+/* Gpu::run_launches, crates/lex-cuda/src/device.rs:650-672: all steps, one synchronise;
+ * cpu_s = host time to enqueue, wall_s = host time until the device is idle. */
+LEXB_API int lexb_run_launches(lexb_gpu* gpu, const lexb_step* steps, size_t nsteps, double* cpu_s, double* wall_s);
+/* Gpu::run_each_timed, crates/lex-cuda/src/device.rs:684-739: device seconds per step,
+ * from events recorded between launches, no synchronise in between. */
+LEXB_API int lexb_run_each_timed(lexb_gpu* gpu, const lexb_step* steps, size_t nsteps, double* seconds_out);
+/* Device seconds for `reps` back-to-back passes over the steps (events on the launch stream). */
+LEXB_API int lexb_time_launches(lexb_gpu* gpu, const lexb_step* steps, size_t nsteps, uint32_t reps, double* seconds_out);
+
+/* Kernels never spin without a limit: a wait that gives up ORs a code into a device status
+ * word and the kernel leaves in order.  This reads the word (after a synchronise) and clears it. */
+LEXB_API int lexb_status_word(lexb_gpu* gpu, uint32_t* out);
+/* Runs a one-block kernel whose only wait is on a barrier nothing will ever complete, with a
+ * limit of `limit_us` microseconds, to show that the bounded wait reports and returns.  Sets
+ * the status word to LEXB_STATUS_WAIT_NEVER. */
+LEXB_API int lexb_selftest_bounded_wait(lexb_gpu* gpu, uint32_t limit_us);
+#define LEXB_STATUS_WAIT_NEVER (1u << 16)
+
+/* Test hook for the bit-exact claim: the f16 every kernel multiplies by, for all n*k weights,
+ * written row-major as u16 bit patterns (the value Op::Stage produces,
+ * crates/lex-front/src/interp.rs:500-507, from Op::DequantFp4, :643-657). */
+LEXB_API int lexb_dequant_fp4_f16(lexb_gpu* gpu, uint32_t n, uint32_t k, const lexb_buffer* wq,
+                                  const lexb_buffer* ws, const lexb_buffer* wg, lexb_buffer* w_f16);
+
+/* Column-parallel sharding over `world` devices (new: the reference is single-GPU,
+ * crates/lex-cuda/src/device.rs:358-359).  Rank `rank` owns weight rows [*n0, *n1) - whole
+ * 128-row tiles, the remainder spread over the first ranks - of wq, ws and wg, and writes the
+ * same columns of y. */
+LEXB_API int lexb_shard_rows(uint32_t n, uint32_t world, uint32_t rank, uint32_t* n0, uint32_t* n1);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* LEXB_H */

@@ -1,0 +1,643 @@
+// Host side of liblexb: the C ABI declared in include/lexb.h over the CUDA runtime.
+// It mirrors lex_cuda::device (crates/lex-cuda/src/device.rs): a Gpu that owns a stream,
+// Buffers, Pipelines (a planned kernel + launch shape) and Steps, with string errors
+// instead of panics.  Kernels are compiled ahead of time for sm_100a and live in this
+// library; there is no NVRTC step and no CPU path.
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <chrono>
+#include <cstdarg>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <mutex>
+#include <new>
+#include <string>
+#include <vector>
+
+#include "../../include/lexb.h"
+#include "gemm_fp4_sm100.cuh"
+#include "matvec_fp4_sm100.cuh"
+
+namespace {
+
+thread_local std::string g_last_error;
+
+int fail(int code, const char* fmt, ...) {
+    char buf[512];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof buf, fmt, ap);
+    va_end(ap);
+    g_last_error = buf;
+    return code;
+}
+
+#define CUDA_TRY(expr)                                                                          \
+    do {                                                                                        \
+        cudaError_t e_ = (expr);                                                                \
+        if (e_ != cudaSuccess)                                                                  \
+            return fail(LEXB_ERR_CUDA, "%s: %s (%s)", #expr, cudaGetErrorString(e_), cudaGetErrorName(e_)); \
+    } while (0)
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+enum { KERNEL_MATVEC = 1, KERNEL_TCGEN05 = 2 };
+
+}  // namespace
+
+struct lexb_gpu {
+    int device = 0;
+    cudaStream_t own_stream = nullptr;
+    cudaStream_t stream = nullptr;       // own_stream or the caller's
+    uint32_t* d_status = nullptr;
+    cudaDeviceProp prop{};
+    EncodeTiledFn encode_tiled = nullptr;
+    size_t smem_optin = 0;
+};
+
+struct lexb_buffer {
+    lexb_gpu* gpu;
+    void* ptr;
+    size_t bytes;
+    bool owned;
+};
+
+struct lexb_pipeline {
+    lexb_gpu* gpu;
+    uint32_t kernel;
+    uint32_t m, n, k;
+    bool residual;
+    // tcgen05 GEMM
+    uint32_t tm, stages, tmem_cols, m_tiles;
+    // matvec
+    uint32_t kc;
+    uint32_t grid, threads, smem;
+    char entry[96];
+    // tensor maps of x, keyed by the device pointer they were encoded for
+    struct MapEntry {
+        const void* x;
+        CUtensorMap map;
+    };
+    mutable std::vector<MapEntry> maps;
+    mutable std::mutex maps_lock;
+};
+
+namespace {
+
+int use(lexb_gpu* g) {
+    if (!g) return fail(LEXB_ERR_ARG, "null gpu handle");
+    CUDA_TRY(cudaSetDevice(g->device));
+    return LEXB_OK;
+}
+
+int check_buf(const lexb_buffer* b, const lexb_gpu* g, size_t need, const char* what) {
+    if (!b) return fail(LEXB_ERR_ARG, "%s: null buffer", what);
+    if (b->gpu != g) return fail(LEXB_ERR_ARG, "%s: buffer belongs to another gpu handle", what);
+    if (b->bytes < need) return fail(LEXB_ERR_ARG, "%s: buffer holds %zu bytes, the shape needs %zu", what, b->bytes, need);
+    if ((reinterpret_cast<uintptr_t>(b->ptr) & 15u) != 0) return fail(LEXB_ERR_ARG, "%s: device pointer is not 16-byte aligned", what);
+    return LEXB_OK;
+}
+
+uint32_t round_up(uint32_t v, uint32_t to) { return (v + to - 1) / to * to; }
+
+uint32_t env_u32(const char* name, uint32_t dflt) {
+    const char* s = getenv(name);
+    if (!s || !*s) return dflt;
+    return static_cast<uint32_t>(strtoul(s, nullptr, 10));
+}
+
+// one-block kernel for lexb_selftest_bounded_wait: a barrier with one expected arrival that
+// never comes; the wait gives up after limit_cycles and reports.
+__global__ void bounded_wait_selftest_kernel(uint32_t* status, long long limit_cycles) {
+    __shared__ __align__(8) uint64_t bar;
+    const uint32_t b = lexb::smem_u32(&bar);
+    if (threadIdx.x == 0) {
+        lexb::mbar_init(b, 1);
+        lexb::fence_mbar_init();
+        const long long t0 = clock64();
+        bool done = false;
+        while (!(done = lexb::mbar_try_wait(b, 0))) {
+            if (clock64() - t0 > limit_cycles) break;
+        }
+        if (!done) atomicOr(status, lexb::ST_WAIT_NEVER);
+    }
+}
+
+// every staged weight as f16 bits: one thread per group of 16
+__global__ void dequant_fp4_f16_kernel(uint32_t n, uint32_t k, const uint8_t* __restrict__ wq,
+                                       const uint8_t* __restrict__ ws, const float* __restrict__ wg,
+                                       uint16_t* __restrict__ out) {
+    const uint32_t groups_per_row = k / 16u;
+    const size_t total = static_cast<size_t>(n) * groups_per_row;
+    for (size_t gi = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; gi < total;
+         gi += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        const uint32_t row = static_cast<uint32_t>(gi / groups_per_row);
+        const uint2 q = *reinterpret_cast<const uint2*>(wq + gi * 8u);
+        uint4 lo, hi;
+        lexb::decode_group16(q, ws[gi], wg[row], lo, hi);
+        uint4* o = reinterpret_cast<uint4*>(out + gi * 16u);
+        o[0] = lo;
+        o[1] = hi;
+    }
+}
+
+int get_x_map(const lexb_pipeline* p, const void* x, CUtensorMap* out) {
+    std::lock_guard<std::mutex> lk(p->maps_lock);
+    for (const auto& e : p->maps)
+        if (e.x == x) {
+            *out = e.map;
+            return LEXB_OK;
+        }
+    CUtensorMap map;
+    // x f16[m, k] row-major; box = 64 columns (128 bytes, the swizzle span) x tm rows.
+    // Rows past m are filled with zeros by the copy engine.
+    const cuuint64_t dims[2] = {p->k, p->m};
+    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(p->k) * 2u};
+    const cuuint32_t box[2] = {lexb::GEMM_BK, p->tm};
+    const cuuint32_t estr[2] = {1, 1};
+    CUresult r = p->gpu->encode_tiled(&map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(x), dims, strides, box,
+                                      estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                      CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(LEXB_ERR_CUDA, "cuTensorMapEncodeTiled(x) failed with CUresult %d", (int)r);
+    if (p->maps.size() >= 64) p->maps.erase(p->maps.begin());
+    p->maps.push_back({x, map});
+    *out = map;
+    return LEXB_OK;
+}
+
+int launch_one(lexb_gpu* g, const lexb_pipeline* p, const lexb_buffer* x, const lexb_buffer* wq, const lexb_buffer* ws,
+               const lexb_buffer* wg, const lexb_buffer* r, lexb_buffer* y) {
+    if (!p) return fail(LEXB_ERR_ARG, "null pipeline");
+    if (p->gpu != g) return fail(LEXB_ERR_ARG, "pipeline was planned on another gpu handle");
+    const size_t m = p->m, n = p->n, k = p->k;
+    int rc;
+    if ((rc = check_buf(x, g, m * k * 2, "x"))) return rc;
+    if ((rc = check_buf(wq, g, n * k / 2, "wq"))) return rc;
+    if ((rc = check_buf(ws, g, n * k / 16, "ws"))) return rc;
+    if ((rc = check_buf(wg, g, n * 4, "wg"))) return rc;
+    if ((rc = check_buf(y, g, m * n * 4, "y"))) return rc;
+    if (p->residual) {
+        if ((rc = check_buf(r, g, m * n * 4, "r"))) return rc;
+    } else if (r) {
+        return fail(LEXB_ERR_ARG, "a residual buffer was bound to a pipeline planned without one");
+    }
+    if (p->kernel == KERNEL_TCGEN05) {
+        CUtensorMap map;
+        if ((rc = get_x_map(p, x->ptr, &map))) return rc;
+        lexb::GemmArgs a{};
+        a.wq = static_cast<const uint8_t*>(wq->ptr);
+        a.ws = static_cast<const uint8_t*>(ws->ptr);
+        a.wg = static_cast<const float*>(wg->ptr);
+        a.r = r ? static_cast<const float*>(r->ptr) : nullptr;
+        a.y = static_cast<float*>(y->ptr);
+        a.status = g->d_status;
+        a.m = p->m; a.n = p->n; a.k = p->k;
+        a.tm = p->tm; a.stages = p->stages; a.tmem_cols = p->tmem_cols; a.m_tiles = p->m_tiles;
+        lexb::gemm_fp4_tcgen05_kernel<<<p->grid, p->threads, p->smem, g->stream>>>(map, a);
+    } else {
+        lexb::MatvecArgs a{};
+        a.x = static_cast<const __half*>(x->ptr);
+        a.wq = static_cast<const uint8_t*>(wq->ptr);
+        a.ws = static_cast<const uint8_t*>(ws->ptr);
+        a.wg = static_cast<const float*>(wg->ptr);
+        a.r = r ? static_cast<const float*>(r->ptr) : nullptr;
+        a.y = static_cast<float*>(y->ptr);
+        a.m = p->m; a.n = p->n; a.k = p->k; a.kc = p->kc;
+        if (p->m > 8)
+            lexb::matvec_fp4_kernel<true><<<p->grid, p->threads, p->smem, g->stream>>>(a);
+        else
+            lexb::matvec_fp4_kernel<false><<<p->grid, p->threads, p->smem, g->stream>>>(a);
+    }
+    CUDA_TRY(cudaGetLastError());
+    return LEXB_OK;
+}
+
+int launch_step(lexb_gpu* g, const lexb_step& s) {
+    if (!s.pipeline || !s.buffers) return fail(LEXB_ERR_ARG, "step without pipeline or buffers");
+    const bool res = s.pipeline->residual;
+    if (s.nbuffers != (res ? 6u : 5u))
+        return fail(LEXB_ERR_ARG, "step binds %u buffers, the pipeline takes %u: [x, wq, ws, wg, %sy]", s.nbuffers,
+                    res ? 6u : 5u, res ? "r, " : "");
+    lexb_buffer* const* b = s.buffers;
+    return launch_one(g, s.pipeline, b[0], b[1], b[2], b[3], res ? b[4] : nullptr, res ? b[5] : b[4]);
+}
+
+}  // namespace
+
+extern "C" {
+
+const char* lexb_last_error(void) { return g_last_error.c_str(); }
+const char* lexb_version(void) { return "lexb 0.1 (sm_100a; gemm_fp4: tcgen05 GEMM + split-K matvec)"; }
+
+int lexb_open(int device, lexb_gpu** out) {
+    if (!out) return fail(LEXB_ERR_ARG, "lexb_open: null out");
+    *out = nullptr;
+    int count = 0;
+    cudaError_t e = cudaGetDeviceCount(&count);
+    if (e != cudaSuccess || count == 0)
+        return fail(LEXB_ERR_UNSUPPORTED, "no CUDA device (%s); this library has no CPU path", cudaGetErrorString(e));
+    if (device < 0 || device >= count) return fail(LEXB_ERR_ARG, "device %d out of range (%d devices)", device, count);
+    lexb_gpu* g = new (std::nothrow) lexb_gpu();
+    if (!g) return fail(LEXB_ERR_ARG, "out of host memory");
+    g->device = device;
+    auto bail = [&](int code) { lexb_close(g); return code; };
+    if (cudaSetDevice(device) != cudaSuccess) return bail(fail(LEXB_ERR_CUDA, "cudaSetDevice(%d) failed", device));
+    if (cudaGetDeviceProperties(&g->prop, device) != cudaSuccess) return bail(fail(LEXB_ERR_CUDA, "cudaGetDeviceProperties failed"));
+    if (g->prop.major != 10)
+        return bail(fail(LEXB_ERR_UNSUPPORTED, "device %d is %s (compute %d.%d); the kernels are built for sm_100a only",
+                         device, g->prop.name, g->prop.major, g->prop.minor));
+    g->smem_optin = g->prop.sharedMemPerBlockOptin;
+    if (cudaStreamCreateWithFlags(&g->own_stream, cudaStreamNonBlocking) != cudaSuccess)
+        return bail(fail(LEXB_ERR_CUDA, "cudaStreamCreate failed"));
+    g->stream = g->own_stream;
+    if (cudaMalloc(&g->d_status, sizeof(uint32_t)) != cudaSuccess || cudaMemset(g->d_status, 0, sizeof(uint32_t)) != cudaSuccess)
+        return bail(fail(LEXB_ERR_CUDA, "allocating the status word failed"));
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres) != cudaSuccess || !fn ||
+        qres != cudaDriverEntryPointSuccess)
+        return bail(fail(LEXB_ERR_CUDA, "the driver does not export cuTensorMapEncodeTiled"));
+    g->encode_tiled = reinterpret_cast<EncodeTiledFn>(fn);
+    const int max_smem = static_cast<int>(g->smem_optin);
+    if (cudaFuncSetAttribute(lexb::gemm_fp4_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem) != cudaSuccess ||
+        cudaFuncSetAttribute(lexb::matvec_fp4_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem) != cudaSuccess ||
+        cudaFuncSetAttribute(lexb::matvec_fp4_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem) != cudaSuccess)
+        return bail(fail(LEXB_ERR_CUDA, "cudaFuncSetAttribute(max dynamic shared memory) failed: %s", cudaGetErrorString(cudaGetLastError())));
+    *out = g;
+    return LEXB_OK;
+}
+
+void lexb_close(lexb_gpu* g) {
+    if (!g) return;
+    cudaSetDevice(g->device);
+    if (g->own_stream) {
+        cudaStreamSynchronize(g->own_stream);
+        cudaStreamDestroy(g->own_stream);
+    }
+    if (g->d_status) cudaFree(g->d_status);
+    delete g;
+}
+
+int lexb_info(lexb_gpu* g, lexb_device_info* out) {
+    int rc = use(g);
+    if (rc) return rc;
+    if (!out) return fail(LEXB_ERR_ARG, "lexb_info: null out");
+    memset(out, 0, sizeof *out);
+    snprintf(out->name, sizeof out->name, "%s", g->prop.name);
+    out->cc_major = g->prop.major;
+    out->cc_minor = g->prop.minor;
+    out->sm_count = g->prop.multiProcessorCount;
+    out->unified_memory = 0;
+    out->max_threadgroup_bytes = g->smem_optin;
+    out->recommended_working_set_bytes = g->prop.totalGlobalMem;
+    out->l2_bytes = static_cast<size_t>(g->prop.l2CacheSize);
+    return LEXB_OK;
+}
+
+int lexb_set_stream(lexb_gpu* g, void* cuda_stream) {
+    int rc = use(g);
+    if (rc) return rc;
+    g->stream = cuda_stream ? static_cast<cudaStream_t>(cuda_stream) : g->own_stream;
+    return LEXB_OK;
+}
+void* lexb_get_stream(lexb_gpu* g) { return g ? static_cast<void*>(g->stream) : nullptr; }
+
+int lexb_sync(lexb_gpu* g) {
+    int rc = use(g);
+    if (rc) return rc;
+    CUDA_TRY(cudaStreamSynchronize(g->stream));
+    return LEXB_OK;
+}
+
+int lexb_alloc(lexb_gpu* g, size_t bytes, lexb_buffer** out) {
+    int rc = use(g);
+    if (rc) return rc;
+    if (!out) return fail(LEXB_ERR_ARG, "lexb_alloc: null out");
+    *out = nullptr;
+    void* p = nullptr;
+    CUDA_TRY(cudaMalloc(&p, bytes ? bytes : 1));
+    lexb_buffer* b = new (std::nothrow) lexb_buffer{g, p, bytes, true};
+    if (!b) {
+        cudaFree(p);
+        return fail(LEXB_ERR_ARG, "out of host memory");
+    }
+    *out = b;
+    return LEXB_OK;
+}
+
+int lexb_zeroed(lexb_gpu* g, size_t bytes, lexb_buffer** out) {
+    int rc = lexb_alloc(g, bytes, out);
+    if (rc) return rc;
+    if (bytes) {
+        cudaError_t e = cudaMemsetAsync((*out)->ptr, 0, bytes, g->stream);
+        if (e == cudaSuccess) e = cudaStreamSynchronize(g->stream);
+        if (e != cudaSuccess) {
+            lexb_free(*out);
+            *out = nullptr;
+            return fail(LEXB_ERR_CUDA, "zeroing %zu bytes failed: %s", bytes, cudaGetErrorString(e));
+        }
+    }
+    return LEXB_OK;
+}
+
+int lexb_wrap(lexb_gpu* g, void* device_ptr, size_t bytes, lexb_buffer** out) {
+    if (!g || !out) return fail(LEXB_ERR_ARG, "lexb_wrap: null argument");
+    if (!device_ptr && bytes) return fail(LEXB_ERR_ARG, "lexb_wrap: null device pointer");
+    lexb_buffer* b = new (std::nothrow) lexb_buffer{g, device_ptr, bytes, false};
+    if (!b) return fail(LEXB_ERR_ARG, "out of host memory");
+    *out = b;
+    return LEXB_OK;
+}
+
+int lexb_free(lexb_buffer* b) {
+    if (!b) return LEXB_OK;
+    int rc = LEXB_OK;
+    if (b->owned && b->ptr) {
+        cudaSetDevice(b->gpu->device);
+        cudaError_t e = cudaFree(b->ptr);
+        if (e != cudaSuccess) rc = fail(LEXB_ERR_CUDA, "cudaFree: %s", cudaGetErrorString(e));
+    }
+    delete b;
+    return rc;
+}
+
+void* lexb_buffer_ptr(const lexb_buffer* b) { return b ? b->ptr : nullptr; }
+size_t lexb_buffer_bytes(const lexb_buffer* b) { return b ? b->bytes : 0; }
+
+int lexb_upload(lexb_gpu* g, lexb_buffer* dst, size_t off, const void* src, size_t bytes) {
+    int rc = use(g);
+    if (rc) return rc;
+    if (!dst || (!src && bytes)) return fail(LEXB_ERR_ARG, "lexb_upload: null argument");
+    if (off > dst->bytes || bytes > dst->bytes - off)
+        return fail(LEXB_ERR_ARG, "lexb_upload: %zu bytes at offset %zu overrun a buffer of %zu", bytes, off, dst->bytes);
+    CUDA_TRY(cudaMemcpyAsync(static_cast<char*>(dst->ptr) + off, src, bytes, cudaMemcpyHostToDevice, g->stream));
+    CUDA_TRY(cudaStreamSynchronize(g->stream));
+    return LEXB_OK;
+}
+
+int lexb_download(lexb_gpu* g, const lexb_buffer* src, size_t off, void* dst, size_t bytes) {
+    int rc = use(g);
+    if (rc) return rc;
+    if (!src || (!dst && bytes)) return fail(LEXB_ERR_ARG, "lexb_download: null argument");
+    if (off > src->bytes || bytes > src->bytes - off)
+        return fail(LEXB_ERR_ARG, "lexb_download: %zu bytes at offset %zu overrun a buffer of %zu", bytes, off, src->bytes);
+    CUDA_TRY(cudaMemcpyAsync(dst, static_cast<const char*>(src->ptr) + off, bytes, cudaMemcpyDeviceToHost, g->stream));
+    CUDA_TRY(cudaStreamSynchronize(g->stream));
+    return LEXB_OK;
+}
+
+int lexb_memset(lexb_gpu* g, lexb_buffer* dst, int byte, size_t bytes) {
+    int rc = use(g);
+    if (rc) return rc;
+    if (!dst) return fail(LEXB_ERR_ARG, "lexb_memset: null buffer");
+    if (bytes > dst->bytes) return fail(LEXB_ERR_ARG, "lexb_memset: %zu bytes overrun a buffer of %zu", bytes, dst->bytes);
+    CUDA_TRY(cudaMemsetAsync(dst->ptr, byte, bytes, g->stream));
+    return LEXB_OK;
+}
+
+int lexb_host_alloc(size_t bytes, void** out) {
+    if (!out) return fail(LEXB_ERR_ARG, "lexb_host_alloc: null out");
+    CUDA_TRY(cudaHostAlloc(out, bytes ? bytes : 1, cudaHostAllocDefault));
+    return LEXB_OK;
+}
+int lexb_host_free(void* p) {
+    if (p) CUDA_TRY(cudaFreeHost(p));
+    return LEXB_OK;
+}
+
+int lexb_gemm_fp4_plan(lexb_gpu* g, uint32_t m, uint32_t n, uint32_t k, int residual, const lexb_sched* sched,
+                       lexb_pipeline** out) {
+    int rc = use(g);
+    if (rc) return rc;
+    if (!out) return fail(LEXB_ERR_ARG, "lexb_gemm_fp4_plan: null out");
+    *out = nullptr;
+    if (m == 0 || n == 0 || k == 0) return fail(LEXB_ERR_SHAPE, "gemm_fp4: empty extent (m=%u n=%u k=%u)", m, n, k);
+    lexb_sched s{};
+    if (sched) s = *sched;
+    if (!s.kernel) s.kernel = env_u32("LEXB_KERNEL", 0);
+    if (!s.tm) s.tm = env_u32("LEXB_TM", 0);
+    if (!s.stages) s.stages = env_u32("LEXB_STAGES", 0);
+    if (!s.kc) s.kc = env_u32("LEXB_KC", 0);
+    uint32_t kernel = s.kernel ? s.kernel : (m <= 16 ? KERNEL_MATVEC : KERNEL_TCGEN05);
+    if (kernel == KERNEL_MATVEC && m > 16) return fail(LEXB_ERR_SHAPE, "the matvec kernel takes m <= 16, not %u", m);
+    if (kernel != KERNEL_MATVEC && kernel != KERNEL_TCGEN05) return fail(LEXB_ERR_ARG, "unknown kernel selector %u", kernel);
+
+    lexb_pipeline* p = new (std::nothrow) lexb_pipeline();
+    if (!p) return fail(LEXB_ERR_ARG, "out of host memory");
+    p->gpu = g;
+    p->kernel = kernel;
+    p->m = m; p->n = n; p->k = k;
+    p->residual = residual != 0;
+    auto bail = [&](int code) { delete p; return code; };
+    const char* stem = residual ? "gemm_fp4_res" : "gemm_fp4";
+
+    if (kernel == KERNEL_TCGEN05) {
+        if (n % lexb::GEMM_TN) return bail(fail(LEXB_ERR_SHAPE, "gemm_fp4: bn = %u does not divide n = %u", lexb::GEMM_TN, n));
+        if (k % lexb::GEMM_BK) return bail(fail(LEXB_ERR_SHAPE, "gemm_fp4: bk = %u does not divide k = %u", lexb::GEMM_BK, k));
+        uint32_t tm = s.tm;
+        if (!tm) {
+            const uint32_t tiles = (m + 255u) / 256u;
+            tm = round_up((m + tiles - 1u) / tiles, 16u);
+        }
+        if (tm < 16 || tm > 256 || tm % 16) return bail(fail(LEXB_ERR_ARG, "tm = %u is not a multiple of 16 in [16, 256]", tm));
+        const uint32_t stage_bytes = lexb::gemm_stage_bytes(tm);
+        uint32_t max_stages = 0;
+        while (max_stages < 12 && lexb::gemm_smem_bytes(tm, max_stages + 1) <= g->smem_optin) max_stages++;
+        if (max_stages < 2) return bail(fail(LEXB_ERR_UNSUPPORTED, "tm = %u leaves room for %u stages (%u bytes each)", tm, max_stages, stage_bytes));
+        uint32_t stages = s.stages ? s.stages : max_stages;
+        if (stages < 2 || stages > max_stages) return bail(fail(LEXB_ERR_ARG, "stages = %u outside [2, %u] for tm = %u", stages, max_stages, tm));
+        uint32_t cols = 32;
+        while (cols < tm) cols *= 2;
+        p->tm = tm; p->stages = stages; p->tmem_cols = cols; p->m_tiles = (m + tm - 1) / tm;
+        p->grid = p->m_tiles * (n / lexb::GEMM_TN);
+        p->threads = lexb::GEMM_THREADS;
+        p->smem = lexb::gemm_smem_bytes(tm, stages);
+        snprintf(p->entry, sizeof p->entry, "%s_%u_%u_%u_%u_%u_%u", stem, m, n, k, tm, lexb::GEMM_TN, lexb::GEMM_BK);
+    } else {
+        if (n % lexb::MV_ROWS) return bail(fail(LEXB_ERR_SHAPE, "gemm_fp4 (matvec): %u rows per block do not divide n = %u", lexb::MV_ROWS, n));
+        if (k % 32u) return bail(fail(LEXB_ERR_SHAPE, "gemm_fp4 (matvec): 32 does not divide k = %u", k));
+        uint32_t kc = s.kc;
+        if (!kc) {
+            // the whole of K if x fits in 64 KiB of shared memory, else the largest multiple
+            // of one CTA round (1024 columns) that does
+            const uint32_t budget = 65536u;
+            kc = round_up(k, lexb::MV_ROUND);
+            while (kc > lexb::MV_ROUND && m * (2u * kc + 8u) > budget) kc -= lexb::MV_ROUND;
+        }
+        if (kc % lexb::MV_ROUND || kc == 0) return bail(fail(LEXB_ERR_ARG, "kc = %u is not a multiple of %u", kc, lexb::MV_ROUND));
+        p->kc = kc;
+        p->grid = n / lexb::MV_ROWS;
+        p->threads = lexb::MV_THREADS;
+        p->smem = lexb::matvec_smem_bytes(m, kc);
+        if (p->smem > g->smem_optin) return bail(fail(LEXB_ERR_UNSUPPORTED, "kc = %u needs %u bytes of shared memory", kc, p->smem));
+        snprintf(p->entry, sizeof p->entry, "%s_%u_%u_%u_%u_%u_%u", stem, m, n, k, m, lexb::MV_ROWS, lexb::MV_SLICE);
+    }
+    *out = p;
+    return LEXB_OK;
+}
+
+void lexb_pipeline_free(lexb_pipeline* p) { delete p; }
+
+int lexb_pipeline_describe(const lexb_pipeline* p, lexb_lowered* out) {
+    if (!p || !out) return fail(LEXB_ERR_ARG, "lexb_pipeline_describe: null argument");
+    memset(out, 0, sizeof *out);
+    snprintf(out->entry, sizeof out->entry, "%s", p->entry);
+    out->grid = p->grid;
+    out->grid2 = 1;
+    out->threads = p->threads;
+    out->threadgroup_bytes = p->smem;
+    out->nbind = p->residual ? 6 : 5;
+    out->writes[out->nbind - 1] = 1;
+    out->kernel = p->kernel;
+    out->m = p->m; out->n = p->n; out->k = p->k; out->residual = p->residual;
+    if (p->kernel == KERNEL_TCGEN05) {
+        out->bm = p->tm; out->bn = lexb::GEMM_TN; out->bk = lexb::GEMM_BK; out->stages = p->stages;
+    } else {
+        out->bm = p->m; out->bn = lexb::MV_ROWS; out->bk = lexb::MV_SLICE; out->stages = 1;
+    }
+    return LEXB_OK;
+}
+
+int lexb_gemm_fp4_launch(lexb_gpu* g, const lexb_pipeline* p, const lexb_buffer* x, const lexb_buffer* wq,
+                         const lexb_buffer* ws, const lexb_buffer* wg, const lexb_buffer* r, lexb_buffer* y) {
+    int rc = use(g);
+    if (rc) return rc;
+    return launch_one(g, p, x, wq, ws, wg, r, y);
+}
+
+int lexb_gemm_fp4_run_host(lexb_gpu* g, const lexb_pipeline* p, const void* x_host, lexb_buffer* x_dev,
+                           const lexb_buffer* wq, const lexb_buffer* ws, const lexb_buffer* wg, const lexb_buffer* r,
+                           lexb_buffer* y_dev, void* y_host) {
+    int rc = use(g);
+    if (rc) return rc;
+    if (!p || !x_host || !y_host || !x_dev || !y_dev) return fail(LEXB_ERR_ARG, "lexb_gemm_fp4_run_host: null argument");
+    const size_t xb = static_cast<size_t>(p->m) * p->k * 2, yb = static_cast<size_t>(p->m) * p->n * 4;
+    if (x_dev->bytes < xb || y_dev->bytes < yb) return fail(LEXB_ERR_ARG, "lexb_gemm_fp4_run_host: staging buffers too small");
+    CUDA_TRY(cudaMemcpyAsync(x_dev->ptr, x_host, xb, cudaMemcpyHostToDevice, g->stream));
+    if ((rc = launch_one(g, p, x_dev, wq, ws, wg, r, y_dev))) return rc;
+    CUDA_TRY(cudaMemcpyAsync(y_host, y_dev->ptr, yb, cudaMemcpyDeviceToHost, g->stream));
+    CUDA_TRY(cudaStreamSynchronize(g->stream));
+    return LEXB_OK;
+}
+
+int lexb_run_launches(lexb_gpu* g, const lexb_step* steps, size_t nsteps, double* cpu_s, double* wall_s) {
+    int rc = use(g);
+    if (rc) return rc;
+    if (!steps && nsteps) return fail(LEXB_ERR_ARG, "lexb_run_launches: null steps");
+    const auto t0 = std::chrono::steady_clock::now();
+    for (size_t i = 0; i < nsteps; i++)
+        if ((rc = launch_step(g, steps[i]))) return rc;
+    const auto t1 = std::chrono::steady_clock::now();
+    CUDA_TRY(cudaStreamSynchronize(g->stream));
+    const auto t2 = std::chrono::steady_clock::now();
+    if (cpu_s) *cpu_s = std::chrono::duration<double>(t1 - t0).count();
+    if (wall_s) *wall_s = std::chrono::duration<double>(t2 - t0).count();
+    return LEXB_OK;
+}
+
+int lexb_run_each_timed(lexb_gpu* g, const lexb_step* steps, size_t nsteps, double* seconds_out) {
+    int rc = use(g);
+    if (rc) return rc;
+    if ((!steps || !seconds_out) && nsteps) return fail(LEXB_ERR_ARG, "lexb_run_each_timed: null argument");
+    std::vector<cudaEvent_t> ev(nsteps + 1, nullptr);
+    auto cleanup = [&]() { for (auto e : ev) if (e) cudaEventDestroy(e); };
+    for (auto& e : ev)
+        if (cudaEventCreate(&e) != cudaSuccess) { cleanup(); return fail(LEXB_ERR_CUDA, "cudaEventCreate failed"); }
+    cudaEventRecord(ev[0], g->stream);
+    for (size_t i = 0; i < nsteps; i++) {
+        if ((rc = launch_step(g, steps[i]))) { cleanup(); return rc; }
+        cudaEventRecord(ev[i + 1], g->stream);
+    }
+    cudaError_t e = cudaStreamSynchronize(g->stream);
+    if (e != cudaSuccess) { cleanup(); return fail(LEXB_ERR_CUDA, "synchronise: %s", cudaGetErrorString(e)); }
+    for (size_t i = 0; i < nsteps; i++) {
+        float ms = 0.f;
+        cudaEventElapsedTime(&ms, ev[i], ev[i + 1]);
+        seconds_out[i] = ms * 1e-3;
+    }
+    cleanup();
+    return LEXB_OK;
+}
+
+int lexb_time_launches(lexb_gpu* g, const lexb_step* steps, size_t nsteps, uint32_t reps, double* seconds_out) {
+    int rc = use(g);
+    if (rc) return rc;
+    if ((!steps && nsteps) || !seconds_out) return fail(LEXB_ERR_ARG, "lexb_time_launches: null argument");
+    cudaEvent_t a, b;
+    CUDA_TRY(cudaEventCreate(&a));
+    CUDA_TRY(cudaEventCreate(&b));
+    CUDA_TRY(cudaStreamSynchronize(g->stream));
+    cudaEventRecord(a, g->stream);
+    for (uint32_t r = 0; r < reps; r++)
+        for (size_t i = 0; i < nsteps; i++)
+            if ((rc = launch_step(g, steps[i]))) { cudaEventDestroy(a); cudaEventDestroy(b); return rc; }
+    cudaEventRecord(b, g->stream);
+    cudaError_t e = cudaStreamSynchronize(g->stream);
+    float ms = 0.f;
+    if (e == cudaSuccess) e = cudaEventElapsedTime(&ms, a, b);
+    cudaEventDestroy(a);
+    cudaEventDestroy(b);
+    if (e != cudaSuccess) return fail(LEXB_ERR_CUDA, "timing: %s", cudaGetErrorString(e));
+    *seconds_out = ms * 1e-3;
+    return LEXB_OK;
+}
+
+int lexb_status_word(lexb_gpu* g, uint32_t* out) {
+    int rc = use(g);
+    if (rc) return rc;
+    if (!out) return fail(LEXB_ERR_ARG, "lexb_status_word: null out");
+    CUDA_TRY(cudaStreamSynchronize(g->stream));
+    CUDA_TRY(cudaMemcpy(out, g->d_status, sizeof(uint32_t), cudaMemcpyDeviceToHost));
+    CUDA_TRY(cudaMemset(g->d_status, 0, sizeof(uint32_t)));
+    return LEXB_OK;
+}
+
+int lexb_selftest_bounded_wait(lexb_gpu* g, uint32_t limit_us) {
+    int rc = use(g);
+    if (rc) return rc;
+    if (limit_us == 0 || limit_us > 1000000u) return fail(LEXB_ERR_ARG, "limit_us must be in [1, 1000000]");
+    const long long cycles = static_cast<long long>(limit_us) * (g->prop.clockRate / 1000);   // clockRate is kHz
+    bounded_wait_selftest_kernel<<<1, 32, 0, g->stream>>>(g->d_status, cycles);
+    CUDA_TRY(cudaGetLastError());
+    CUDA_TRY(cudaStreamSynchronize(g->stream));
+    return LEXB_OK;
+}
+
+int lexb_dequant_fp4_f16(lexb_gpu* g, uint32_t n, uint32_t k, const lexb_buffer* wq, const lexb_buffer* ws,
+                         const lexb_buffer* wg, lexb_buffer* w_f16) {
+    int rc = use(g);
+    if (rc) return rc;
+    if (n == 0 || k == 0 || k % 16u) return fail(LEXB_ERR_SHAPE, "dequant_fp4: group 16 does not divide k = %u", k);
+    const size_t nn = n, kk = k;
+    if ((rc = check_buf(wq, g, nn * kk / 2, "wq"))) return rc;
+    if ((rc = check_buf(ws, g, nn * kk / 16, "ws"))) return rc;
+    if ((rc = check_buf(wg, g, nn * 4, "wg"))) return rc;
+    if ((rc = check_buf(w_f16, g, nn * kk * 2, "w_f16"))) return rc;
+    const size_t groups = nn * kk / 16;
+    const uint32_t threads = 256;
+    const uint32_t blocks = static_cast<uint32_t>(std::min<size_t>((groups + threads - 1) / threads, 148u * 32u));
+    dequant_fp4_f16_kernel<<<blocks, threads, 0, g->stream>>>(n, k, static_cast<const uint8_t*>(wq->ptr),
+                                                              static_cast<const uint8_t*>(ws->ptr),
+                                                              static_cast<const float*>(wg->ptr),
+                                                              static_cast<uint16_t*>(w_f16->ptr));
+    CUDA_TRY(cudaGetLastError());
+    return LEXB_OK;
+}
+
+int lexb_shard_rows(uint32_t n, uint32_t world, uint32_t rank, uint32_t* n0, uint32_t* n1) {
+    if (!n0 || !n1) return fail(LEXB_ERR_ARG, "lexb_shard_rows: null out");
+    if (world == 0 || rank >= world) return fail(LEXB_ERR_ARG, "rank %u outside world %u", rank, world);
+    if (n % 128u) return fail(LEXB_ERR_SHAPE, "sharding splits whole 128-row tiles; 128 does not divide n = %u", n);
+    const uint32_t tiles = n / 128u, base = tiles / world, extra = tiles % world;
+    const uint32_t first = rank * base + (rank < extra ? rank : extra);
+    const uint32_t count = base + (rank < extra ? 1u : 0u);
+    *n0 = first * 128u;
+    *n1 = (first + count) * 128u;
+    return LEXB_OK;
+}
+
+}  // extern "C"

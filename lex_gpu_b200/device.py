@@ -1,0 +1,363 @@
+"""ctypes binding of liblexb's C ABI, shaped like lex_cuda::device
+(crates/lex-cuda/src/device.rs): Gpu, Buffer, Pipeline, Step, run_launches, run_each_timed.
+
+This module is only a binding.  Every operation goes through the shared library built from
+csrc/; there is no Python or CPU implementation behind it, and loading fails with an error
+when the library is missing.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import POINTER, byref, c_char, c_double, c_int, c_size_t, c_uint8, c_uint32, c_uint64, c_void_p
+from pathlib import Path
+from typing import Optional, Sequence
+
+import numpy as np
+
+PKG = Path(__file__).resolve().parent
+LIB_PATH = PKG / "liblexb.so"
+
+KERNEL_AUTO, KERNEL_MATVEC, KERNEL_TCGEN05 = 0, 1, 2
+STATUS_WAIT_NEVER = 1 << 16
+
+# Every symbol include/lexb.h declares.
+SYMBOLS = [
+    "lexb_last_error", "lexb_version", "lexb_open", "lexb_close", "lexb_info", "lexb_set_stream", "lexb_get_stream",
+    "lexb_sync", "lexb_alloc", "lexb_zeroed", "lexb_wrap", "lexb_free", "lexb_buffer_ptr", "lexb_buffer_bytes",
+    "lexb_upload", "lexb_download", "lexb_memset", "lexb_host_alloc", "lexb_host_free", "lexb_gemm_fp4_plan",
+    "lexb_pipeline_free", "lexb_pipeline_describe", "lexb_gemm_fp4_launch", "lexb_gemm_fp4_run_host",
+    "lexb_run_launches", "lexb_run_each_timed", "lexb_time_launches", "lexb_status_word",
+    "lexb_selftest_bounded_wait", "lexb_dequant_fp4_f16", "lexb_shard_rows",
+]
+
+
+class LexbError(RuntimeError):
+    def __init__(self, code: int, message: str):
+        super().__init__(f"lexb error {code}: {message}")
+        self.code = code
+        self.message = message
+
+
+class DeviceInfo(ctypes.Structure):
+    _fields_ = [("name", c_char * 128), ("cc_major", c_int), ("cc_minor", c_int), ("sm_count", c_int),
+                ("unified_memory", c_int), ("max_threadgroup_bytes", c_size_t),
+                ("recommended_working_set_bytes", c_uint64), ("l2_bytes", c_size_t)]
+
+
+class Sched(ctypes.Structure):
+    _fields_ = [("kernel", c_uint32), ("tm", c_uint32), ("stages", c_uint32), ("kc", c_uint32)]
+
+
+class Lowered(ctypes.Structure):
+    _fields_ = [("entry", c_char * 96), ("grid", c_uint32), ("grid2", c_uint32), ("threads", c_uint32),
+                ("threadgroup_bytes", c_uint32), ("nbind", c_uint32), ("writes", c_uint8 * 6), ("kernel", c_uint32),
+                ("m", c_uint32), ("n", c_uint32), ("k", c_uint32), ("residual", c_uint32),
+                ("bm", c_uint32), ("bn", c_uint32), ("bk", c_uint32), ("stages", c_uint32)]
+
+
+class StepStruct(ctypes.Structure):
+    _fields_ = [("pipeline", c_void_p), ("buffers", POINTER(c_void_p)), ("nbuffers", c_uint32)]
+
+
+_lib = None
+
+
+def load_library() -> ctypes.CDLL:
+    """Load liblexb.so from the package directory.  Raises if it has not been built."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not LIB_PATH.exists():
+        raise RuntimeError(f"{LIB_PATH} is missing: build it with `python -m lex_gpu_b200.build` "
+                           "(there is no CPU or Python implementation to fall back to)")
+    L = ctypes.CDLL(str(LIB_PATH))
+    vp, u32, sz = c_void_p, c_uint32, c_size_t
+    L.lexb_last_error.restype = ctypes.c_char_p
+    L.lexb_version.restype = ctypes.c_char_p
+    L.lexb_open.argtypes = [c_int, POINTER(vp)]
+    L.lexb_close.argtypes = [vp]
+    L.lexb_close.restype = None
+    L.lexb_info.argtypes = [vp, POINTER(DeviceInfo)]
+    L.lexb_set_stream.argtypes = [vp, vp]
+    L.lexb_get_stream.argtypes = [vp]
+    L.lexb_get_stream.restype = vp
+    L.lexb_sync.argtypes = [vp]
+    L.lexb_alloc.argtypes = [vp, sz, POINTER(vp)]
+    L.lexb_zeroed.argtypes = [vp, sz, POINTER(vp)]
+    L.lexb_wrap.argtypes = [vp, vp, sz, POINTER(vp)]
+    L.lexb_free.argtypes = [vp]
+    L.lexb_buffer_ptr.argtypes = [vp]
+    L.lexb_buffer_ptr.restype = vp
+    L.lexb_buffer_bytes.argtypes = [vp]
+    L.lexb_buffer_bytes.restype = sz
+    L.lexb_upload.argtypes = [vp, vp, sz, vp, sz]
+    L.lexb_download.argtypes = [vp, vp, sz, vp, sz]
+    L.lexb_memset.argtypes = [vp, vp, c_int, sz]
+    L.lexb_host_alloc.argtypes = [sz, POINTER(vp)]
+    L.lexb_host_free.argtypes = [vp]
+    L.lexb_gemm_fp4_plan.argtypes = [vp, u32, u32, u32, c_int, POINTER(Sched), POINTER(vp)]
+    L.lexb_pipeline_free.argtypes = [vp]
+    L.lexb_pipeline_free.restype = None
+    L.lexb_pipeline_describe.argtypes = [vp, POINTER(Lowered)]
+    L.lexb_gemm_fp4_launch.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp]
+    L.lexb_gemm_fp4_run_host.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp]
+    L.lexb_run_launches.argtypes = [vp, POINTER(StepStruct), sz, POINTER(c_double), POINTER(c_double)]
+    L.lexb_run_each_timed.argtypes = [vp, POINTER(StepStruct), sz, POINTER(c_double)]
+    L.lexb_time_launches.argtypes = [vp, POINTER(StepStruct), sz, u32, POINTER(c_double)]
+    L.lexb_status_word.argtypes = [vp, POINTER(u32)]
+    L.lexb_selftest_bounded_wait.argtypes = [vp, u32]
+    L.lexb_dequant_fp4_f16.argtypes = [vp, u32, u32, vp, vp, vp, vp]
+    L.lexb_shard_rows.argtypes = [u32, u32, u32, POINTER(u32), POINTER(u32)]
+    _lib = L
+    return L
+
+
+def _check(rc: int) -> None:
+    if rc != 0:
+        raise LexbError(rc, load_library().lexb_last_error().decode(errors="replace"))
+
+
+def shard_rows(n: int, world: int, rank: int) -> tuple[int, int]:
+    """Rows [n0, n1) of W that `rank` of `world` owns (host arithmetic only; needs no GPU)."""
+    n0, n1 = c_uint32(), c_uint32()
+    _check(load_library().lexb_shard_rows(n, world, rank, byref(n0), byref(n1)))
+    return n0.value, n1.value
+
+
+class Buffer:
+    """A device buffer (lex_cuda::Buffer, device.rs:257-278); freed on close() or collection."""
+
+    def __init__(self, gpu: "Gpu", handle: int, keepalive=None):
+        self.gpu, self._h, self._keep = gpu, handle, keepalive
+
+    @property
+    def handle(self) -> int:
+        if self._h is None:
+            raise LexbError(1, "buffer already freed")
+        return self._h
+
+    def len_bytes(self) -> int:
+        return int(load_library().lexb_buffer_bytes(self.handle))
+
+    @property
+    def ptr(self) -> int:
+        return int(load_library().lexb_buffer_ptr(self.handle) or 0)
+
+    def close(self) -> None:
+        if self._h is not None:
+            load_library().lexb_free(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+class Pipeline:
+    """A planned kernel and its launch shape (lex_cuda::Pipeline, device.rs:281-301)."""
+
+    def __init__(self, gpu: "Gpu", handle: int):
+        self.gpu, self._h = gpu, handle
+
+    @property
+    def handle(self) -> int:
+        if self._h is None:
+            raise LexbError(1, "pipeline already freed")
+        return self._h
+
+    def describe(self) -> Lowered:
+        out = Lowered()
+        _check(load_library().lexb_pipeline_describe(self.handle, byref(out)))
+        return out
+
+    def close(self) -> None:
+        if self._h is not None:
+            load_library().lexb_pipeline_free(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+Step = tuple  # (Pipeline, [Buffer, ...]) in the order [x, wq, ws, wg, (r), y]; device.rs:314
+
+
+class _Steps:
+    def __init__(self, steps: Sequence[Step]):
+        self.n = len(steps)
+        self.arr = (StepStruct * max(self.n, 1))()
+        self._keep = []
+        for i, (pipe, bufs) in enumerate(steps):
+            ptrs = (c_void_p * len(bufs))(*[b.handle for b in bufs])
+            self._keep.append(ptrs)
+            self.arr[i].pipeline = pipe.handle
+            self.arr[i].buffers = ctypes.cast(ptrs, POINTER(c_void_p))
+            self.arr[i].nbuffers = len(bufs)
+
+
+class Gpu:
+    """lex_cuda::Gpu (device.rs:316-810) for the one operator this backend provides."""
+
+    def __init__(self, device: int = 0):
+        self._L = load_library()
+        h = c_void_p()
+        _check(self._L.lexb_open(device, byref(h)))
+        self._h = h.value
+        self.device = device
+
+    @classmethod
+    def open(cls, device: int = 0) -> "Gpu":
+        return cls(device)
+
+    @property
+    def handle(self) -> int:
+        if self._h is None:
+            raise LexbError(1, "gpu already closed")
+        return self._h
+
+    def close(self) -> None:
+        if self._h is not None:
+            self._L.lexb_close(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def info(self) -> DeviceInfo:
+        out = DeviceInfo()
+        _check(self._L.lexb_info(self.handle, byref(out)))
+        return out
+
+    def name(self) -> str:
+        return self.info().name.decode()
+
+    def set_stream(self, cuda_stream: Optional[int]) -> None:
+        _check(self._L.lexb_set_stream(self.handle, c_void_p(cuda_stream or 0)))
+
+    def sync(self) -> None:
+        _check(self._L.lexb_sync(self.handle))
+
+    # ---- memory
+    def alloc(self, nbytes: int) -> Buffer:
+        h = c_void_p()
+        _check(self._L.lexb_alloc(self.handle, nbytes, byref(h)))
+        return Buffer(self, h.value)
+
+    def zeroed(self, nbytes: int) -> Buffer:
+        h = c_void_p()
+        _check(self._L.lexb_zeroed(self.handle, nbytes, byref(h)))
+        return Buffer(self, h.value)
+
+    def upload(self, array: np.ndarray) -> Buffer:
+        a = np.ascontiguousarray(array)
+        b = self.alloc(a.nbytes)
+        self.write(b, 0, a)
+        return b
+
+    def wrap(self, device_ptr: int, nbytes: int, keepalive=None) -> Buffer:
+        """A non-owning view of device memory allocated elsewhere (e.g. a torch tensor)."""
+        h = c_void_p()
+        _check(self._L.lexb_wrap(self.handle, c_void_p(device_ptr), nbytes, byref(h)))
+        return Buffer(self, h.value, keepalive)
+
+    def wrap_tensor(self, t) -> Buffer:
+        if not t.is_cuda or not t.is_contiguous():
+            raise ValueError("wrap_tensor needs a contiguous CUDA tensor")
+        return self.wrap(t.data_ptr(), t.numel() * t.element_size(), keepalive=t)
+
+    def write(self, buf: Buffer, byte_offset: int, array: np.ndarray) -> None:
+        a = np.ascontiguousarray(array)
+        _check(self._L.lexb_upload(self.handle, buf.handle, byte_offset, c_void_p(a.ctypes.data), a.nbytes))
+
+    def download(self, buf: Buffer, dtype, shape, byte_offset: int = 0) -> np.ndarray:
+        out = np.empty(shape, dtype=dtype)
+        _check(self._L.lexb_download(self.handle, buf.handle, byte_offset, c_void_p(out.ctypes.data), out.nbytes))
+        return out
+
+    def memset(self, buf: Buffer, byte: int, nbytes: Optional[int] = None) -> None:
+        _check(self._L.lexb_memset(self.handle, buf.handle, byte, buf.len_bytes() if nbytes is None else nbytes))
+
+    # ---- the operator
+    def plan_gemm_fp4(self, m: int, n: int, k: int, residual: bool = False, kernel: int = 0, tm: int = 0,
+                      stages: int = 0, kc: int = 0) -> Pipeline:
+        s = Sched(kernel, tm, stages, kc)
+        h = c_void_p()
+        _check(self._L.lexb_gemm_fp4_plan(self.handle, m, n, k, int(residual), byref(s), byref(h)))
+        return Pipeline(self, h.value)
+
+    def run(self, pipe: Pipeline, bufs: Sequence[Buffer]) -> None:
+        """One launch, asynchronous; bufs = [x, wq, ws, wg, (r), y] (Gpu::run, device.rs:629-648)."""
+        res = len(bufs) == 6
+        if len(bufs) not in (5, 6):
+            raise LexbError(1, f"gemm_fp4 binds 5 or 6 buffers, not {len(bufs)}")
+        x, wq, ws, wg = bufs[:4]
+        r, y = (bufs[4], bufs[5]) if res else (None, bufs[4])
+        _check(self._L.lexb_gemm_fp4_launch(self.handle, pipe.handle, x.handle, wq.handle, ws.handle, wg.handle,
+                                            r.handle if r is not None else None, y.handle))
+
+    def run_host(self, pipe: Pipeline, x_host_ptr: int, x_dev: Buffer, wq: Buffer, ws: Buffer, wg: Buffer,
+                 r: Optional[Buffer], y_dev: Buffer, y_host_ptr: int) -> None:
+        _check(self._L.lexb_gemm_fp4_run_host(self.handle, pipe.handle, c_void_p(x_host_ptr), x_dev.handle, wq.handle,
+                                              ws.handle, wg.handle, r.handle if r is not None else None,
+                                              y_dev.handle, c_void_p(y_host_ptr)))
+
+    def run_launches(self, steps: Sequence[Step]) -> tuple[float, float]:
+        s = _Steps(steps)
+        cpu, wall = c_double(), c_double()
+        _check(self._L.lexb_run_launches(self.handle, s.arr, s.n, byref(cpu), byref(wall)))
+        return cpu.value, wall.value
+
+    def run_each_timed(self, steps: Sequence[Step]) -> list[float]:
+        s = _Steps(steps)
+        out = (c_double * max(s.n, 1))()
+        _check(self._L.lexb_run_each_timed(self.handle, s.arr, s.n, out))
+        return [out[i] for i in range(s.n)]
+
+    def time_launches(self, steps: Sequence[Step], reps: int = 1) -> float:
+        s = _Steps(steps)
+        out = c_double()
+        _check(self._L.lexb_time_launches(self.handle, s.arr, s.n, reps, byref(out)))
+        return out.value
+
+    def status_word(self) -> int:
+        out = c_uint32()
+        _check(self._L.lexb_status_word(self.handle, byref(out)))
+        return out.value
+
+    def selftest_bounded_wait(self, limit_us: int = 1000) -> None:
+        _check(self._L.lexb_selftest_bounded_wait(self.handle, limit_us))
+
+    def dequant_fp4_f16(self, n: int, k: int, wq: Buffer, ws: Buffer, wg: Buffer, out: Buffer) -> None:
+        _check(self._L.lexb_dequant_fp4_f16(self.handle, n, k, wq.handle, ws.handle, wg.handle, out.handle))
+
+
+class HostBuffer:
+    """Page-locked host memory viewed as a numpy array."""
+
+    def __init__(self, nbytes: int):
+        p = c_void_p()
+        _check(load_library().lexb_host_alloc(nbytes, byref(p)))
+        self.ptr, self.nbytes = p.value, nbytes
+
+    def array(self, dtype, shape) -> np.ndarray:
+        buf = (ctypes.c_uint8 * self.nbytes).from_address(self.ptr)
+        return np.frombuffer(buf, dtype=dtype, count=int(np.prod(shape))).reshape(shape)
+
+    def close(self) -> None:
+        if self.ptr:
+            load_library().lexb_host_free(c_void_p(self.ptr))
+            self.ptr = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass

@@ -1,0 +1,316 @@
+"""Parity of the CUDA kernels with the CPU oracle, through the C ABI.
+
+Gates (the reference's GEMM convention, crates/lex-cuda/tests/device_gpu.rs:294-303):
+  * of scale:  max|got - want| / max|want| <= 2e-3, after asserting max|want| > 1e-3;
+  * per element with a floor tied to the output scale: |d| / max(|want|, 1e-3 max|want|) <= 2e-3;
+  * dequantised weights: every f16 bit pattern equal (-0 != +0; NaN matches NaN).
+"""
+import numpy as np
+import pytest
+
+import lex_gpu_b200 as L
+from lex_gpu_b200 import inputs
+from oracle import oracle as O
+
+pytestmark = pytest.mark.gpu
+
+TOL = 2e-3
+
+
+@pytest.fixture(scope="module")
+def gpu():
+    from lex_gpu_b200 import build
+    build.build()
+    g = L.Gpu(0)
+    yield g
+    g.close()
+
+
+def check(got, want, tol=TOL):
+    assert np.isfinite(got).all(), "non-finite output (an element was not written?)"
+    err, scale, rel = O.err_of_scale(got, want)
+    assert scale > 1e-3, "the reference output is all but zero"
+    assert err <= tol, f"{err:e} of scale"
+    assert rel <= tol, f"per-element relative error {rel:e}"
+    return err
+
+
+def same_f16_bits(got, want):
+    nan_g = (got & 0x7C00 == 0x7C00) & (got & 0x3FF != 0)
+    nan_w = (want & 0x7C00 == 0x7C00) & (want & 0x3FF != 0)
+    return np.array_equal(nan_g, nan_w) and np.array_equal(got[~nan_g], want[~nan_w])
+
+
+# ---------------------------------------------------------------- dequant: bit-exact
+
+def test_dequant_bit_exact_adversarial(gpu):
+    wq, ws, wg = inputs.adversarial_dequant_case()
+    got = L.dequant_fp4_f16(gpu, wq, ws, wg)
+    want = O.dequant_fp4_f16(wq, ws, wg)
+    assert same_f16_bits(got, want)
+    assert (want == 0x8000).any() and (want == 0x0000).any()      # both zeros occur
+
+
+def test_dequant_bit_exact_benchmark_distribution(gpu):
+    wq, ws, wg = inputs.make_weights(2048, 5120, seed_base=0)
+    got = L.dequant_fp4_f16(gpu, wq, ws, wg)
+    assert np.array_equal(got, O.dequant_fp4_f16(wq, ws, wg))
+
+
+def test_dequant_rejects_k_not_multiple_of_16(gpu):
+    with pytest.raises(L.LexbError):
+        b = gpu.alloc(1024)
+        gpu.dequant_fp4_f16(4, 24, b, b, b, b)
+
+
+# ---------------------------------------------------------------- matvec path (m <= 16)
+
+@pytest.mark.parametrize("m", [1, 2, 3, 4, 8, 9, 16])
+def test_matvec_small_shapes(gpu, m):
+    x, wq, ws, wg = inputs.make_case(m, 256, 1024, seed_base=20 + m)
+    got = L.gemm_fp4(gpu, x, wq, ws, wg)
+    check(got, O.gemm_fp4(x, wq, ws, wg))
+
+
+@pytest.mark.parametrize("m,n,k", [(1, 16, 32), (4, 48, 64), (2, 32, 96), (5, 64, 160), (16, 16, 2080), (3, 128, 3072)])
+def test_matvec_ragged_k(gpu, m, n, k):
+    """k a multiple of 32 only: slices that end inside a warp's 128 columns; bk = 32 in the oracle."""
+    x, wq, ws, wg = inputs.make_case(m, n, k, seed_base=31)
+    check(L.gemm_fp4(gpu, x, wq, ws, wg), O.gemm_fp4(x, wq, ws, wg, bk=32))
+
+
+@pytest.mark.parametrize("m,kc", [(4, 1024), (16, 1024), (16, 2048), (1, 4096)])
+def test_matvec_chunked_x(gpu, m, kc):
+    x, wq, ws, wg = inputs.make_case(m, 64, 5120, seed_base=41)
+    check(L.gemm_fp4(gpu, x, wq, ws, wg, kc=kc), O.gemm_fp4(x, wq, ws, wg))
+
+
+def test_matvec_residual(gpu):
+    x, wq, ws, wg = inputs.make_case(4, 128, 512, seed_base=51)
+    r = inputs.make_residual(4, 128, seed_base=51)
+    got = L.gemm_fp4(gpu, x, wq, ws, wg, r=r)
+    want = O.gemm_fp4(x, wq, ws, wg, r=r)
+    check(got, want)
+    base = L.gemm_fp4(gpu, x, wq, ws, wg)
+    assert np.allclose(got - base, r, atol=1e-4)
+
+
+@pytest.mark.parametrize("m", [1, 4])
+@pytest.mark.parametrize("n,k", [(17408, 5120), (5120, 17408)])
+def test_matvec_benchmark_shapes(gpu, m, n, k):
+    """BASELINE config 1 at full size, against the full oracle."""
+    x, wq, ws, wg = inputs.make_case(m, n, k)
+    got = L.gemm_fp4(gpu, x, wq, ws, wg)
+    check(got, O.gemm_fp4(x, wq, ws, wg))
+
+
+def test_a_token_does_not_depend_on_its_batch(gpu):
+    """The int8 test idea of crates/lex-cuda/tests/device_gpu.rs:314-: a row's result is the same
+    whatever else is in the batch - bit for bit within the matvec path."""
+    x, wq, ws, wg = inputs.make_case(8, 256, 2048, seed_base=61)
+    y8 = L.gemm_fp4(gpu, x, wq, ws, wg)
+    y1 = L.gemm_fp4(gpu, x[:1].copy(), wq, ws, wg)
+    y4 = L.gemm_fp4(gpu, x[:4].copy(), wq, ws, wg)
+    assert np.array_equal(y1, y8[:1]) and np.array_equal(y4, y8[:4])
+
+
+# ---------------------------------------------------------------- tcgen05 path (m > 16)
+
+def test_gemm_config0_readme_example(gpu):
+    """m = n = 128, k = 64: one tile, one K step (BASELINE config 0)."""
+    x, wq, ws, wg = inputs.make_case(128, 128, 64)
+    check(L.gemm_fp4(gpu, x, wq, ws, wg), O.gemm_fp4(x, wq, ws, wg))
+
+
+@pytest.mark.parametrize("bm,bn,bk", [(128, 128, 64)])
+def test_gemm_known_answer_recipe(gpu, bm, bn, bk):
+    """Inputs of crates/lex-front/tests/syntax.rs:525-585 with its own tolerance against the f64 restatement."""
+    m, n, k = bm, 2 * bn, 2 * bk
+    x16, q, sc, g, _ = O.kat_inputs(m, n, k)
+    got = L.gemm_fp4(gpu, x16, q, sc, g)
+    want = O.f64_restatement(x16, q, sc, g)
+    assert np.all(np.abs(got - want) < 1e-3 * np.maximum(np.abs(want), 1.0))
+    check(got, O.gemm_fp4(x16, q, sc, g))
+
+
+def test_gemm_residual_recipe(gpu):
+    """crates/lex-front/tests/syntax.rs:634-683: the residual is added exactly once."""
+    m, n, k = 128, 256, 64
+    x16, q, sc, g, r = O.kat_inputs(m, n, k, residual=True)
+    with_r = L.gemm_fp4(gpu, x16, q, sc, g, r=r)
+    without = L.gemm_fp4(gpu, x16, q, sc, g, r=np.zeros_like(r))
+    assert np.all(np.abs((with_r - without).astype(np.float64) - r) < 1e-5)
+    check(with_r, O.gemm_fp4(x16, q, sc, g, r=r))
+
+
+@pytest.mark.parametrize("m,n,k", [(256, 512, 1024), (17, 128, 256), (40, 128, 512), (96, 256, 1024),
+                                   (300, 384, 2048), (512, 1024, 5120), (1000, 256, 320)])
+def test_gemm_shapes(gpu, m, n, k):
+    """Multi-tile, multi-K-step and ragged m (the reference's ragged cases,
+    crates/lex-cuda/tests/device_gpu.rs:210-305, restricted to n % 128 == 0, k % 64 == 0)."""
+    x, wq, ws, wg = inputs.make_case(m, n, k, seed_base=m + n)
+    check(L.gemm_fp4(gpu, x, wq, ws, wg), O.gemm_fp4(x, wq, ws, wg))
+
+
+@pytest.mark.parametrize("tm,stages", [(16, 2), (32, 3), (64, 0), (128, 4), (256, 2), (256, 0), (112, 0)])
+def test_gemm_schedules(gpu, tm, stages):
+    x, wq, ws, wg = inputs.make_case(200, 256, 1536, seed_base=71)
+    check(L.gemm_fp4(gpu, x, wq, ws, wg, kernel=2, tm=tm, stages=stages), O.gemm_fp4(x, wq, ws, wg))
+
+
+def test_gemm_small_m_through_the_tensor_path(gpu):
+    """m <= 16 forced onto the tcgen05 kernel agrees with the matvec kernel to tolerance."""
+    x, wq, ws, wg = inputs.make_case(16, 256, 1024, seed_base=81)
+    want = O.gemm_fp4(x, wq, ws, wg)
+    check(L.gemm_fp4(gpu, x, wq, ws, wg, kernel=2), want)
+    check(L.gemm_fp4(gpu, x, wq, ws, wg, kernel=1), want)
+
+
+def test_gemm_multiplies_exactly_the_oracles_f16_weights(gpu):
+    """x = one-hot rows: y[i, j] is then the staged weight W[j, k_i] itself, so the tensor-core
+    path reproduces the oracle's f16 weights exactly (only the sign of zero is lost in a sum)."""
+    n, k = 256, 512
+    wq, ws, wg = inputs.make_weights(n, k, seed_base=91)
+    x = np.zeros((k, k), dtype=np.float16)
+    x[np.arange(k), np.arange(k)] = 1.0
+    got = L.gemm_fp4(gpu, x, wq, ws, wg)                        # [k, n] = W^T
+    want = O.dequant_fp4_f16(wq, ws, wg).view(np.float16).astype(np.float32).T
+    assert np.array_equal(got, want)
+
+
+def test_gemm_wide_scale_range(gpu):
+    """Every finite scale byte (E4M3 subnormals and negative scales included) and row scales of
+    both signs over three decades, through the MMA path: f16-subnormal and large weights mix."""
+    n, k, m = 256, 2048, 64
+    rng = np.random.Generator(np.random.PCG64(95))
+    finite = np.array([b for b in range(256) if b & 0x7F != 0x7F], dtype=np.uint8)
+    ws = rng.choice(finite, size=(n, k // 16))
+    wq = rng.integers(0, 256, size=(n, k // 2), dtype=np.uint8)
+    wg = (np.exp(rng.uniform(np.log(1e-3), 0.0, n)) * rng.choice([-1.0, 1.0], n)).astype(np.float32)
+    x = inputs.make_x(m, k, seed_base=95)
+    assert np.array_equal(L.dequant_fp4_f16(gpu, wq, ws, wg), O.dequant_fp4_f16(wq, ws, wg))
+    check(L.gemm_fp4(gpu, x, wq, ws, wg), O.gemm_fp4(x, wq, ws, wg))
+    check(L.gemm_fp4(gpu, x[:8].copy(), wq, ws, wg), O.gemm_fp4(x[:8].copy(), wq, ws, wg))
+
+
+@pytest.mark.parametrize("n,k", [(17408, 5120), (5120, 17408)])
+def test_gemm_27b_mlp_prefill_m512(gpu, n, k):
+    """BASELINE config 3 (m = 512) at full size against the full oracle."""
+    x, wq, ws, wg = inputs.make_case(512, n, k)
+    err = check(L.gemm_fp4(gpu, x, wq, ws, wg), O.gemm_fp4(x, wq, ws, wg))
+    print(f"m=512 n={n} k={k}: {err:.3e} of scale")
+
+
+@pytest.mark.parametrize("n,k", [(6144, 4096), (28672, 4096), (4096, 14336)])
+def test_gemm_llama8b_prefill_projections(gpu, n, k):
+    """BASELINE config 2: oracle on a slice of rows (full n on the GPU)."""
+    x, wq, ws, wg = inputs.make_case(512, n, k, seed_base=2)
+    got = L.gemm_fp4(gpu, x, wq, ws, wg)
+    lo, hi = n // 2 - 256, n // 2 + 256
+    want = O.gemm_fp4(x, wq, ws, wg, rows=(lo, hi))
+    check(got[:, lo:hi], want[:, lo:hi])
+    first = O.gemm_fp4(x, wq, ws, wg, rows=(0, 128))
+    check(got[:, :128], first[:, :128])
+    last = O.gemm_fp4(x, wq, ws, wg, rows=(n - 128, n))
+    check(got[:, n - 128:], last[:, n - 128:])
+
+
+def test_gemm_m2048_linearity_and_slices(gpu):
+    """m = 2048 (config 3's larger batch): oracle on row slices, and the size-independent
+    property that the result for a sub-batch equals the same rows of the full batch."""
+    n, k = 5120, 17408
+    x, wq, ws, wg = inputs.make_case(2048, n, k, seed_base=3)
+    got = L.gemm_fp4(gpu, x, wq, ws, wg)
+    want = O.gemm_fp4(x, wq, ws, wg, rows=(1024, 1280))
+    check(got[:, 1024:1280], want[:, 1024:1280])
+    sub = L.gemm_fp4(gpu, x[512:1024].copy(), wq, ws, wg)
+    assert np.array_equal(sub, got[512:1024])
+
+
+# ---------------------------------------------------------------- boundary behaviour
+
+def test_shapes_the_operator_rejects(gpu):
+    for m, n, k in [(64, 100, 128), (64, 128, 96), (4, 40, 64), (4, 32, 48), (0, 128, 64)]:
+        with pytest.raises(L.LexbError) as e:
+            gpu.plan_gemm_fp4(m, n, k)
+        assert e.value.code == 2, (m, n, k)
+    with pytest.raises(L.LexbError):
+        gpu.plan_gemm_fp4(64, 128, 64, kernel=1)        # matvec kernel takes m <= 16
+    with pytest.raises(L.LexbError):
+        gpu.plan_gemm_fp4(64, 128, 64, tm=24)
+
+
+def test_launch_validates_bindings(gpu):
+    pipe = gpu.plan_gemm_fp4(32, 128, 64)
+    small = gpu.alloc(64)
+    ok = gpu.alloc(32 * 128 * 4)
+    with pytest.raises(L.LexbError) as e:
+        gpu.run(pipe, [small, ok, ok, ok, ok])
+    assert "x" in e.value.message and e.value.code == 1
+    with pytest.raises(L.LexbError):
+        gpu.run(pipe, [ok, ok, ok, ok, ok, ok])          # a residual bound to a pipeline without one
+    with pytest.raises(L.LexbError):
+        gpu.run(pipe, [ok, ok, ok])
+
+
+def test_describe_mirrors_the_lowered_descriptor(gpu):
+    d = gpu.plan_gemm_fp4(512, 17408, 5120).describe()
+    assert d.entry.decode() == "gemm_fp4_512_17408_5120_256_128_64"
+    assert (d.grid, d.grid2, d.threads, d.nbind) == (272, 1, 320, 5)
+    assert list(d.writes)[:5] == [0, 0, 0, 0, 1] and d.kernel == 2
+    d = gpu.plan_gemm_fp4(4, 17408, 5120, residual=True).describe()
+    assert d.entry.decode().startswith("gemm_fp4_res_4_17408_5120") and d.kernel == 1
+    assert d.nbind == 6 and list(d.writes) == [0, 0, 0, 0, 0, 1] and d.grid == 1088
+
+
+def test_run_launches_and_timing_entry_points(gpu):
+    x, wq, ws, wg = inputs.make_case(64, 256, 512, seed_base=7)
+    q = L.QBuf(gpu, wq, ws, wg)
+    xb, yb = gpu.upload(x), gpu.zeroed(64 * 256 * 4)
+    pipe = gpu.plan_gemm_fp4(64, 256, 512)
+    steps = [(pipe, q.bind(xb, None, yb))] * 3
+    cpu_s, wall_s = gpu.run_launches(steps)
+    assert 0 <= cpu_s <= wall_s
+    each = gpu.run_each_timed(steps)
+    assert len(each) == 3 and all(t > 0 for t in each)
+    assert gpu.time_launches(steps, reps=2) > 0
+    check(gpu.download(yb, np.float32, (64, 256)), O.gemm_fp4(x, wq, ws, wg))
+    assert gpu.status_word() == 0
+
+
+def test_run_host_copies_in_and_out(gpu):
+    m, n, k = 64, 256, 512
+    x, wq, ws, wg = inputs.make_case(m, n, k, seed_base=8)
+    q = L.QBuf(gpu, wq, ws, wg)
+    pipe = gpu.plan_gemm_fp4(m, n, k)
+    hx, hy = L.HostBuffer(x.nbytes), L.HostBuffer(m * n * 4)
+    hx.array(np.float16, (m, k))[:] = x
+    xd, yd = gpu.alloc(x.nbytes), gpu.alloc(m * n * 4)
+    gpu.run_host(pipe, hx.ptr, xd, q.wq, q.ws, q.wg, None, yd, hy.ptr)
+    check(hy.array(np.float32, (m, n)).copy(), O.gemm_fp4(x, wq, ws, wg))
+
+
+def test_wrapping_a_torch_tensor(gpu):
+    import torch
+    m, n, k = 32, 128, 256
+    x, wq, ws, wg = inputs.make_case(m, n, k, seed_base=9)
+    dev = torch.device("cuda:0")
+    tx = torch.from_numpy(x.view(np.int16)).to(dev)
+    tq, ts, tg = (torch.from_numpy(a).to(dev) for a in (wq, ws, wg))
+    ty = torch.full((m, n), float("nan"), device=dev)
+    torch.cuda.synchronize()
+    pipe = gpu.plan_gemm_fp4(m, n, k)
+    gpu.run(pipe, [gpu.wrap_tensor(t) for t in (tx, tq, ts, tg, ty)])
+    gpu.sync()
+    check(ty.cpu().numpy(), O.gemm_fp4(x, wq, ws, wg))
+
+
+def test_bounded_wait_reports_and_returns(gpu):
+    """A wait on a barrier nothing completes gives up after its limit and sets the status word;
+    the context stays usable."""
+    assert gpu.status_word() == 0
+    gpu.selftest_bounded_wait(limit_us=2000)
+    assert gpu.status_word() == L.device.STATUS_WAIT_NEVER
+    assert gpu.status_word() == 0                                # reading clears it
+    x, wq, ws, wg = inputs.make_case(32, 128, 64, seed_base=5)
+    check(L.gemm_fp4(gpu, x, wq, ws, wg), O.gemm_fp4(x, wq, ws, wg))
