@@ -235,8 +235,12 @@ def run_ours(args):
         gpu.run(pipe, [xb, bufs[0], bufs[1], bufs[2], yb])
 
     # long enough for the clock sampler to see the load: repeat the measured block
-    secs, clocks = timed(pipe, gemm_step, args.steps, args.warmup, sample_clocks=True)
-    if (clocks or {}).get("samples", 0) < 3:
+    full = args.only == "all"
+    if args.only == "matvec":
+        secs, clocks = timed(pipe, gemm_step, 1, 3)
+    else:
+        secs, clocks = timed(pipe, gemm_step, args.steps, args.warmup, sample_clocks=full)
+    if full and (clocks or {}).get("samples", 0) < 3:
         # the timed region is shorter than the sampler's period: sample clocks over a longer
         # run of the same steps (not the reported time)
         _, clocks2 = timed(pipe, gemm_step, max(args.steps, 3000), 0, sample_clocks=True)
@@ -254,35 +258,37 @@ def run_ours(args):
                 "frac_of_nominal_2250": local_flops / per_launch / 1e12 / 2250.0}
 
     # ---- e2e: host x -> device, launch, y -> host, every step, through the C ABI call
-    hx = L.HostBuffer(x_np.nbytes)
-    hx.array(np.float16, (M, K))[:] = x_np
-    hy = L.HostBuffer(M * n_local * 4)
-    xd, yd = gpu.alloc(x_np.nbytes), gpu.alloc(M * n_local * 4)
-    e2e_steps = max(5, min(args.steps, 50))
-    for i in range(3):
-        b = weights[i % COPIES][1]
-        gpu.run_host(pipe, hx.ptr, xd, b[0], b[1], b[2], None, yd, hy.ptr)
-    barrier()
-    t = time.perf_counter()
-    for i in range(e2e_steps):
-        b = weights[i % COPIES][1]
-        gpu.run_host(pipe, hx.ptr, xd, b[0], b[1], b[2], None, yd, hy.ptr)
-    torch.cuda.synchronize(dev)
-    e2e_secs = time.perf_counter() - t
-    if dist is not None:
-        tt = torch.tensor([e2e_secs], device=dev, dtype=torch.float64)
-        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
-        e2e_secs = float(tt.item())
-    checksum = float(hy.array(np.float32, (M, n_local))[0, :8].sum())
-    e2e = {"value": flops_step * e2e_steps / e2e_secs / 1e12, "unit": "TFLOP/s",
-           "h2d_bytes_per_step": int(x_np.nbytes), "d2h_bytes_per_step": int(M * n_local * 4), "steps": e2e_steps,
-           "ms_per_step": 1e3 * e2e_secs / e2e_steps,
-           "note": "lexb_gemm_fp4_run_host: pinned x in, y out, weights resident"}
+    e2e, checksum = None, None
+    if full:
+        hx = L.HostBuffer(x_np.nbytes)
+        hx.array(np.float16, (M, K))[:] = x_np
+        hy = L.HostBuffer(M * n_local * 4)
+        xd, yd = gpu.alloc(x_np.nbytes), gpu.alloc(M * n_local * 4)
+        e2e_steps = max(5, min(args.steps, 50))
+        for i in range(3):
+            b = weights[i % COPIES][1]
+            gpu.run_host(pipe, hx.ptr, xd, b[0], b[1], b[2], None, yd, hy.ptr)
+        barrier()
+        t = time.perf_counter()
+        for i in range(e2e_steps):
+            b = weights[i % COPIES][1]
+            gpu.run_host(pipe, hx.ptr, xd, b[0], b[1], b[2], None, yd, hy.ptr)
+        torch.cuda.synchronize(dev)
+        e2e_secs = time.perf_counter() - t
+        if dist is not None:
+            tt = torch.tensor([e2e_secs], device=dev, dtype=torch.float64)
+            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+            e2e_secs = float(tt.item())
+        checksum = float(hy.array(np.float32, (M, n_local))[0, :8].sum())
+        e2e = {"value": flops_step * e2e_steps / e2e_secs / 1e12, "unit": "TFLOP/s",
+               "h2d_bytes_per_step": int(x_np.nbytes), "d2h_bytes_per_step": int(M * n_local * 4), "steps": e2e_steps,
+               "ms_per_step": 1e3 * e2e_secs / e2e_steps,
+               "note": "lexb_gemm_fp4_run_host: pinned x in, y out, weights resident"}
 
     # ---- matvec (m = 1, 4): GB/s of weight bytes
     matvec = {}
     wbytes_local = n_local * K // 2 + n_local * K // 16 + 4 * n_local
-    for mm in (1, 4):
+    for mm in ((1, 4) if args.only != "gemm" else ()):
         p_mv = gpu.plan_gemm_fp4(mm, n_local, K)
         xs = gpu.wrap_tensor(x_t[:mm].contiguous())
         ys_t = torch.empty((mm, n_local), dtype=torch.float32, device=dev)
@@ -292,8 +298,9 @@ def run_ours(args):
             b = weights[i % COPIES][1]
             gpu.run(p_mv, [xs, b[0], b[1], b[2], ys])
 
-        s_mv, _ = timed(p_mv, mv_step, max(args.steps, 200), max(args.warmup, 20))
-        per = s_mv / max(args.steps, 200)
+        mv_steps = max(args.steps, 200) if full else args.steps
+        s_mv, _ = timed(p_mv, mv_step, mv_steps, max(args.warmup, 20) if full else args.warmup)
+        per = s_mv / mv_steps
         gbs = wbytes_local / per / 1e9
         matvec[f"m{mm}"] = {"gbs_weight_bytes": gbs * world, "us_per_launch": per * 1e6,
                             "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
@@ -302,7 +309,7 @@ def run_ours(args):
 
     # ---- all-gather variant (N > 1): y shards -> [N][m][n/N] on every rank
     allgather = None
-    if dist is not None:
+    if dist is not None and full:
         sizes = [L.shard_rows(N_ROWS, world, r) for r in range(world)]
         if len({b - a for a, b in sizes}) == 1:
             full = torch.empty((world, M, n_local), dtype=torch.float32, device=dev)
@@ -319,7 +326,7 @@ def run_ours(args):
                          "layout": "[N][m][n/N]"}
 
     if rank == 0:
-        info = cpu_leg() if world == 1 else None
+        info = cpu_leg() if (world == 1 and full) else None
         line = {"metric": METRIC, "value": tflops, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
                 "warmup": args.warmup, "ms_per_step": 1e3 * per_launch, "higher_is_better": True,
                 "scaling": "strong", "vs_baseline": None, "dtype": "f16*fp4->f32", "data": "synthetic",
@@ -330,7 +337,7 @@ def run_ours(args):
                                         "grid": desc.grid, "threads": desc.threads, "smem": desc.threadgroup_bytes}},
                 "roofline": roofline, "cpu_baseline": info, "e2e": e2e, "gpu_launches": args.steps,
                 "clocks": clocks, "matvec": matvec, "allgather": allgather, "device_status": status,
-                "checksum": checksum}
+                "checksum": checksum, "only": args.only}
         print(json.dumps(line))
     if dist is not None:
         dist.barrier()
@@ -343,6 +350,8 @@ def main():
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--only", default="all", choices=["all", "gemm", "matvec"],
+                    help="time one kernel only (short runs for profilers); the JSON line then omits the other legs")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.impl == "reference":

@@ -41,8 +41,10 @@ struct GemmArgs {
     uint32_t m, n, k;
     uint32_t tm;          // tokens per CTA tile: multiple of 16, 16..256
     uint32_t stages;      // pipeline depth
-    uint32_t tmem_cols;   // power of two >= max(32, tm)
+    uint32_t tmem_cols;   // power of two >= max(32, n_acc * tm)
+    uint32_t n_acc;       // 1 or 2 accumulators; with 2, even and odd K steps alternate
     uint32_t m_tiles;     // ceil(m / tm)
+    uint32_t x_tx_bytes;  // bytes one TMA x tile delivers: min(tm, m) rows of 128 bytes
 };
 
 __host__ __device__ constexpr uint32_t gemm_stage_bytes(uint32_t tm) { return tm * 128u + GEMM_W_TILE_BYTES; }
@@ -107,7 +109,7 @@ gemm_fp4_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmAr
                     ok = false;
                     break;
                 }
-                mbar_arrive_expect_tx(x_full(s), x_bytes);
+                mbar_arrive_expect_tx(x_full(s), a.x_tx_bytes);
                 tma_load_2d(base + s * stage_bytes, &tmap_x, (int)(kb * GEMM_BK), (int)m0, x_full(s));
                 issued = kb + 1;
             }
@@ -152,7 +154,9 @@ gemm_fp4_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmAr
                 for (uint32_t kk = 0; kk < GEMM_BK / 16; kk++) {
                     const uint64_t a_desc = umma_desc_k_sw128(w_addr + kk * 32u);
                     const uint64_t b_desc = umma_desc_k_sw128(x_addr + kk * 32u);
-                    umma_f16_ss(tmem_base, a_desc, b_desc, idesc, (kb | kk) != 0u);
+                    // Two accumulators halve the run of truncating f32 additions each one
+                    // sees (the tensor core does not round to nearest when it accumulates).
+                    umma_f16_ss(tmem_base + (kb % a.n_acc) * a.tm, a_desc, b_desc, idesc, (kb >= a.n_acc) || kk != 0u);
                 }
                 umma_commit(empty(s));      // frees the stage once these MMAs have read it
             }
@@ -216,7 +220,16 @@ gemm_fp4_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmAr
             for (uint32_t c = half; c < chunks; c += 2u) {
                 uint32_t v[16];
                 tmem_ld_32x32b_x16(tmem_base + ((32u * quarter) << 16) + c * 16u, v);
-                tmem_ld_wait();
+                if (a.n_acc > 1 && KB > 1) {
+                    uint32_t v2[16];
+                    tmem_ld_32x32b_x16(tmem_base + ((32u * quarter) << 16) + a.tm + c * 16u, v2);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (uint32_t j = 0; j < 16; j++)
+                        v[j] = __float_as_uint(__uint_as_float(v[j]) + __uint_as_float(v2[j]));
+                } else {
+                    tmem_ld_wait();
+                }
                 const uint32_t t0 = m0 + c * 16u;
 #pragma unroll
                 for (uint32_t j = 0; j < 16; j++) {

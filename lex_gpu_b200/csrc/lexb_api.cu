@@ -72,7 +72,7 @@ struct lexb_pipeline {
     uint32_t m, n, k;
     bool residual;
     // tcgen05 GEMM
-    uint32_t tm, stages, tmem_cols, m_tiles;
+    uint32_t tm, stages, tmem_cols, m_tiles, n_acc;
     // matvec
     uint32_t kc;
     uint32_t grid, threads, smem;
@@ -157,7 +157,7 @@ int get_x_map(const lexb_pipeline* p, const void* x, CUtensorMap* out) {
     // Rows past m are filled with zeros by the copy engine.
     const cuuint64_t dims[2] = {p->k, p->m};
     const cuuint64_t strides[1] = {static_cast<cuuint64_t>(p->k) * 2u};
-    const cuuint32_t box[2] = {lexb::GEMM_BK, p->tm};
+    const cuuint32_t box[2] = {lexb::GEMM_BK, p->tm < p->m ? p->tm : p->m};   // never taller than the tensor
     const cuuint32_t estr[2] = {1, 1};
     CUresult r = p->gpu->encode_tiled(&map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(x), dims, strides, box,
                                       estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
@@ -196,7 +196,8 @@ int launch_one(lexb_gpu* g, const lexb_pipeline* p, const lexb_buffer* x, const 
         a.y = static_cast<float*>(y->ptr);
         a.status = g->d_status;
         a.m = p->m; a.n = p->n; a.k = p->k;
-        a.tm = p->tm; a.stages = p->stages; a.tmem_cols = p->tmem_cols; a.m_tiles = p->m_tiles;
+        a.tm = p->tm; a.stages = p->stages; a.tmem_cols = p->tmem_cols; a.m_tiles = p->m_tiles; a.n_acc = p->n_acc;
+        a.x_tx_bytes = (p->tm < p->m ? p->tm : p->m) * 128u;
         lexb::gemm_fp4_tcgen05_kernel<<<p->grid, p->threads, p->smem, g->stream>>>(map, a);
     } else {
         lexb::MatvecArgs a{};
@@ -450,9 +451,11 @@ int lexb_gemm_fp4_plan(lexb_gpu* g, uint32_t m, uint32_t n, uint32_t k, int resi
         if (max_stages < 2) return bail(fail(LEXB_ERR_UNSUPPORTED, "tm = %u leaves room for %u stages (%u bytes each)", tm, max_stages, stage_bytes));
         uint32_t stages = s.stages ? s.stages : max_stages;
         if (stages < 2 || stages > max_stages) return bail(fail(LEXB_ERR_ARG, "stages = %u outside [2, %u] for tm = %u", stages, max_stages, tm));
+        // two alternating accumulators whenever they fit the 512 columns of TMEM
+        const uint32_t n_acc = 2;
         uint32_t cols = 32;
-        while (cols < tm) cols *= 2;
-        p->tm = tm; p->stages = stages; p->tmem_cols = cols; p->m_tiles = (m + tm - 1) / tm;
+        while (cols < n_acc * tm) cols *= 2;
+        p->tm = tm; p->stages = stages; p->tmem_cols = cols; p->n_acc = n_acc; p->m_tiles = (m + tm - 1) / tm;
         p->grid = p->m_tiles * (n / lexb::GEMM_TN);
         p->threads = lexb::GEMM_THREADS;
         p->smem = lexb::gemm_smem_bytes(tm, stages);
