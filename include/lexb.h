@@ -57,7 +57,7 @@ typedef struct lexb_device_info {
  * (crates/lex-front/lx/gemm_fp4.lx:38-39) and of the LEX_GEMM_CU_* variables
  * (crates/lex-msl/src/gemm.rs:90-135).  Zero fields mean "choose". */
 typedef struct lexb_sched {
-    uint32_t kernel;  /* 0 auto, 1 split-K matvec (m <= 16), 2 tcgen05 GEMM */
+    uint32_t kernel;  /* 0 auto, 1 split-K matvec (m <= 16), 2 tcgen05 GEMM, 3 two-CTA tcgen05 GEMM (m > 256) */
     uint32_t tm;      /* tokens per CTA tile of the GEMM: multiple of 16, <= 256 */
     uint32_t stages;  /* pipeline depth of the GEMM */
     uint32_t kc;      /* K columns of x staged per chunk in the matvec: multiple of 1024 */
@@ -72,7 +72,7 @@ typedef struct lexb_lowered {
     uint32_t threadgroup_bytes;  /* dynamic shared memory */
     uint32_t nbind;
     uint8_t writes[6];
-    uint32_t kernel;             /* 1 matvec, 2 tcgen05 */
+    uint32_t kernel;             /* 1 matvec, 2 tcgen05, 3 two-CTA tcgen05 */
     uint32_t m, n, k, residual;
     uint32_t bm, bn, bk, stages;
 } lexb_lowered;

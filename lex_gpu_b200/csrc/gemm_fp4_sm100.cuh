@@ -165,23 +165,28 @@ gemm_fp4_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmAr
         __syncwarp();
     } else {
         // ---------------------------------------------------------------- dequant warps 0-7
-        const uint32_t r = tid >> 1, h = tid & 1u;
+        // Thread (row r, half h): a warp covers 32 consecutive rows and one half, so the eight
+        // 16-byte chunks any 8 consecutive lanes store fall into eight different bank groups.
+        const uint32_t r = tid & 127u, h = tid >> 7;
         const uint32_t row = n0 + r;
         const float g = __ldg(a.wg + row);
         const uint4* qrow = reinterpret_cast<const uint4*>(a.wq + (size_t)row * (a.k / 2)) + h;
         const uint32_t* srow = reinterpret_cast<const uint32_t*>(a.ws + (size_t)row * (a.k / 16));
         const uint32_t w_off = r * 128u;
         const uint32_t sw_xor = r & 7u;
-        uint4 q_next = __ldg(qrow);
-        uint32_t s_next = __ldg(srow);
+        // two K steps of codes and scales in flight
+        uint4 q0 = __ldg(qrow), q1 = KB > 1 ? __ldg(qrow + 2) : make_uint4(0, 0, 0, 0);
+        uint32_t s0 = __ldg(srow), s1 = KB > 1 ? __ldg(srow + 1) : 0u;
         bool ok = true;
         for (uint32_t kb = 0; kb < KB; kb++) {
             const uint32_t s = kb % S, ph = (kb / S) & 1u;
-            const uint4 q = q_next;
-            const uint32_t sw = s_next >> (16u * h);
-            if (kb + 1 < KB) {
-                q_next = __ldg(qrow + 2u * (kb + 1));
-                s_next = __ldg(srow + kb + 1);
+            const uint4 q = q0;
+            const uint32_t sw = s0 >> (16u * h);
+            q0 = q1;
+            s0 = s1;
+            if (kb + 2 < KB) {
+                q1 = __ldg(qrow + 2u * (kb + 2));
+                s1 = __ldg(srow + kb + 2);
             }
             uint4 o0, o1, o2, o3;
             decode_group16(make_uint2(q.x, q.y), sw & 0xFFu, g, o0, o1);

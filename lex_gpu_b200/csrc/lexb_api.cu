@@ -18,6 +18,7 @@
 
 #include "../../include/lexb.h"
 #include "gemm_fp4_sm100.cuh"
+#include "gemm_fp4_sm100_pair.cuh"
 #include "matvec_fp4_sm100.cuh"
 
 namespace {
@@ -45,7 +46,7 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
-enum { KERNEL_MATVEC = 1, KERNEL_TCGEN05 = 2 };
+enum { KERNEL_MATVEC = 1, KERNEL_TCGEN05 = 2, KERNEL_TCGEN05_PAIR = 3 };
 
 }  // namespace
 
@@ -157,7 +158,8 @@ int get_x_map(const lexb_pipeline* p, const void* x, CUtensorMap* out) {
     // Rows past m are filled with zeros by the copy engine.
     const cuuint64_t dims[2] = {p->k, p->m};
     const cuuint64_t strides[1] = {static_cast<cuuint64_t>(p->k) * 2u};
-    const cuuint32_t box[2] = {lexb::GEMM_BK, p->tm < p->m ? p->tm : p->m};   // never taller than the tensor
+    const uint32_t box_rows = p->kernel == KERNEL_TCGEN05_PAIR ? lexb::PAIR_XBLK_ROWS : (p->tm < p->m ? p->tm : p->m);
+    const cuuint32_t box[2] = {lexb::GEMM_BK, box_rows};   // never taller than the tensor
     const cuuint32_t estr[2] = {1, 1};
     CUresult r = p->gpu->encode_tiled(&map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(x), dims, strides, box,
                                       estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
@@ -185,7 +187,7 @@ int launch_one(lexb_gpu* g, const lexb_pipeline* p, const lexb_buffer* x, const 
     } else if (r) {
         return fail(LEXB_ERR_ARG, "a residual buffer was bound to a pipeline planned without one");
     }
-    if (p->kernel == KERNEL_TCGEN05) {
+    if (p->kernel == KERNEL_TCGEN05 || p->kernel == KERNEL_TCGEN05_PAIR) {
         CUtensorMap map;
         if ((rc = get_x_map(p, x->ptr, &map))) return rc;
         lexb::GemmArgs a{};
@@ -198,7 +200,10 @@ int launch_one(lexb_gpu* g, const lexb_pipeline* p, const lexb_buffer* x, const 
         a.m = p->m; a.n = p->n; a.k = p->k;
         a.tm = p->tm; a.stages = p->stages; a.tmem_cols = p->tmem_cols; a.m_tiles = p->m_tiles; a.n_acc = p->n_acc;
         a.x_tx_bytes = (p->tm < p->m ? p->tm : p->m) * 128u;
-        lexb::gemm_fp4_tcgen05_kernel<<<p->grid, p->threads, p->smem, g->stream>>>(map, a);
+        if (p->kernel == KERNEL_TCGEN05_PAIR)
+            lexb::gemm_fp4_tcgen05_pair_kernel<<<p->grid, p->threads, p->smem, g->stream>>>(map, a);
+        else
+            lexb::gemm_fp4_tcgen05_kernel<<<p->grid, p->threads, p->smem, g->stream>>>(map, a);
     } else {
         lexb::MatvecArgs a{};
         a.x = static_cast<const __half*>(x->ptr);
@@ -265,6 +270,7 @@ int lexb_open(int device, lexb_gpu** out) {
     g->encode_tiled = reinterpret_cast<EncodeTiledFn>(fn);
     const int max_smem = static_cast<int>(g->smem_optin);
     if (cudaFuncSetAttribute(lexb::gemm_fp4_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem) != cudaSuccess ||
+        cudaFuncSetAttribute(lexb::gemm_fp4_tcgen05_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem) != cudaSuccess ||
         cudaFuncSetAttribute(lexb::matvec_fp4_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem) != cudaSuccess ||
         cudaFuncSetAttribute(lexb::matvec_fp4_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem) != cudaSuccess)
         return bail(fail(LEXB_ERR_CUDA, "cudaFuncSetAttribute(max dynamic shared memory) failed: %s", cudaGetErrorString(cudaGetLastError())));
@@ -423,9 +429,12 @@ int lexb_gemm_fp4_plan(lexb_gpu* g, uint32_t m, uint32_t n, uint32_t k, int resi
     if (!s.tm) s.tm = env_u32("LEXB_TM", 0);
     if (!s.stages) s.stages = env_u32("LEXB_STAGES", 0);
     if (!s.kc) s.kc = env_u32("LEXB_KC", 0);
-    uint32_t kernel = s.kernel ? s.kernel : (m <= 16 ? KERNEL_MATVEC : KERNEL_TCGEN05);
+    // m <= 16: matvec.  m > 256 and whole 256-row pairs: the two-CTA GEMM.  Otherwise the one-CTA GEMM.
+    uint32_t kernel = s.kernel ? s.kernel
+                               : (m <= 16 ? KERNEL_MATVEC
+                                          : ((m > 256 && n % 256u == 0 && k % lexb::GEMM_BK == 0) ? KERNEL_TCGEN05_PAIR : KERNEL_TCGEN05));
     if (kernel == KERNEL_MATVEC && m > 16) return fail(LEXB_ERR_SHAPE, "the matvec kernel takes m <= 16, not %u", m);
-    if (kernel != KERNEL_MATVEC && kernel != KERNEL_TCGEN05) return fail(LEXB_ERR_ARG, "unknown kernel selector %u", kernel);
+    if (kernel < KERNEL_MATVEC || kernel > KERNEL_TCGEN05_PAIR) return fail(LEXB_ERR_ARG, "unknown kernel selector %u", kernel);
 
     lexb_pipeline* p = new (std::nothrow) lexb_pipeline();
     if (!p) return fail(LEXB_ERR_ARG, "out of host memory");
@@ -460,6 +469,20 @@ int lexb_gemm_fp4_plan(lexb_gpu* g, uint32_t m, uint32_t n, uint32_t k, int resi
         p->threads = lexb::GEMM_THREADS;
         p->smem = lexb::gemm_smem_bytes(tm, stages);
         snprintf(p->entry, sizeof p->entry, "%s_%u_%u_%u_%u_%u_%u", stem, m, n, k, tm, lexb::GEMM_TN, lexb::GEMM_BK);
+    } else if (kernel == KERNEL_TCGEN05_PAIR) {
+        if (n % (2u * lexb::GEMM_TN)) return bail(fail(LEXB_ERR_SHAPE, "gemm_fp4 (pair): bn = %u does not divide n = %u", 2u * lexb::GEMM_TN, n));
+        if (k % lexb::GEMM_BK) return bail(fail(LEXB_ERR_SHAPE, "gemm_fp4: bk = %u does not divide k = %u", lexb::GEMM_BK, k));
+        if (m < lexb::PAIR_XBLK_ROWS) return bail(fail(LEXB_ERR_SHAPE, "the two-CTA kernel takes m >= %u, not %u", lexb::PAIR_XBLK_ROWS, m));
+        uint32_t max_stages = 0;
+        while (max_stages < 12 && lexb::pair_smem_bytes(max_stages + 1) <= g->smem_optin) max_stages++;
+        uint32_t stages = s.stages ? s.stages : max_stages;
+        if (stages < 2 || stages > max_stages) return bail(fail(LEXB_ERR_ARG, "stages = %u outside [2, %u]", stages, max_stages));
+        p->tm = lexb::PAIR_TOKENS; p->stages = stages; p->tmem_cols = lexb::PAIR_TMEM_COLS; p->n_acc = 1;
+        p->m_tiles = (m + lexb::PAIR_TOKENS - 1) / lexb::PAIR_TOKENS;
+        p->grid = 2u * p->m_tiles * (n / (2u * lexb::GEMM_TN));
+        p->threads = lexb::GEMM_THREADS;
+        p->smem = lexb::pair_smem_bytes(stages);
+        snprintf(p->entry, sizeof p->entry, "%s_%u_%u_%u_%u_%u_%u", stem, m, n, k, lexb::PAIR_TOKENS, 2u * lexb::GEMM_TN, lexb::GEMM_BK);
     } else {
         if (n % lexb::MV_ROWS) return bail(fail(LEXB_ERR_SHAPE, "gemm_fp4 (matvec): %u rows per block do not divide n = %u", lexb::MV_ROWS, n));
         if (k % 32u) return bail(fail(LEXB_ERR_SHAPE, "gemm_fp4 (matvec): 32 does not divide k = %u", k));
@@ -497,8 +520,9 @@ int lexb_pipeline_describe(const lexb_pipeline* p, lexb_lowered* out) {
     out->writes[out->nbind - 1] = 1;
     out->kernel = p->kernel;
     out->m = p->m; out->n = p->n; out->k = p->k; out->residual = p->residual;
-    if (p->kernel == KERNEL_TCGEN05) {
-        out->bm = p->tm; out->bn = lexb::GEMM_TN; out->bk = lexb::GEMM_BK; out->stages = p->stages;
+    if (p->kernel == KERNEL_TCGEN05 || p->kernel == KERNEL_TCGEN05_PAIR) {
+        out->bm = p->tm; out->bn = p->kernel == KERNEL_TCGEN05_PAIR ? 2u * lexb::GEMM_TN : lexb::GEMM_TN;
+        out->bk = lexb::GEMM_BK; out->stages = p->stages;
     } else {
         out->bm = p->m; out->bn = lexb::MV_ROWS; out->bk = lexb::MV_SLICE; out->stages = 1;
     }

@@ -17,7 +17,7 @@ import numpy as np
 PKG = Path(__file__).resolve().parent
 LIB_PATH = PKG / "liblexb.so"
 
-KERNEL_AUTO, KERNEL_MATVEC, KERNEL_TCGEN05 = 0, 1, 2
+KERNEL_AUTO, KERNEL_MATVEC, KERNEL_TCGEN05, KERNEL_TCGEN05_PAIR = 0, 1, 2, 3
 STATUS_WAIT_NEVER = 1 << 16
 
 # Every symbol include/lexb.h declares.
