@@ -61,6 +61,7 @@ typedef struct lexb_sched {
     uint32_t tm;      /* tokens per CTA tile of the GEMM: multiple of 16, <= 256 */
     uint32_t stages;  /* pipeline depth of the GEMM */
     uint32_t kc;      /* K columns of x staged per chunk in the matvec: multiple of 1024 */
+    uint32_t w_stages; /* two-CTA GEMM: depth of the ring of decoded W tiles (stages = depth of the x ring) */
 } lexb_sched;
 
 /* lex_msl::program::Lowered, crates/lex-msl/src/program.rs:44-63: the launch descriptor.
@@ -156,6 +157,17 @@ LEXB_API int lexb_status_word(lexb_gpu* gpu, uint32_t* out);
  * the status word to LEXB_STATUS_WAIT_NEVER. */
 LEXB_API int lexb_selftest_bounded_wait(lexb_gpu* gpu, uint32_t limit_us);
 #define LEXB_STATUS_WAIT_NEVER (1u << 16)
+
+/* In-kernel phase timers of the two-CTA GEMM (the counterpart of LEX_SYNC's per-call-site
+ * attribution, crates/lex-rt/src/qwen_run.rs:2926-2960, one level down): with tracing enabled
+ * for up to max_ctas blocks, each block of the next launch records 16 SM-clock values:
+ * [0] start, [1] first K step ready, [2] all MMAs issued, [3] cycles the MMA thread waited for
+ * x tiles, [4] for its own W tile, [5] for the partner's W tile, [6] accumulator complete,
+ * [7] epilogue done ([1]-[5] only in the leader block of a pair); [8..10] and [12..14]: for the
+ * first and the last dequant thread, cycles in the decode loop, of which waiting for packed
+ * weights, of which waiting for a free W stage.  max_ctas = 0 turns it off. */
+LEXB_API int lexb_trace_enable(lexb_gpu* gpu, uint32_t max_ctas);
+LEXB_API int lexb_trace_read(lexb_gpu* gpu, uint64_t* out, uint32_t ctas);
 
 /* Test hook for the bit-exact claim: the f16 every kernel multiplies by, for all n*k weights,
  * written row-major as u16 bit patterns (the value Op::Stage produces,

@@ -38,13 +38,16 @@ struct GemmArgs {
     const float* r;       // [m, n] or null
     float* y;             // [m, n]
     uint32_t* status;     // device status word (ORed)
+    unsigned long long* trace;   // null, or 8 counters per CTA written by the two-CTA kernel (phase timers)
     uint32_t m, n, k;
     uint32_t tm;          // tokens per CTA tile: multiple of 16, 16..256
-    uint32_t stages;      // pipeline depth
+    uint32_t stages;      // pipeline depth (of the x ring in the two-CTA kernel)
+    uint32_t w_stages;    // two-CTA kernel: depth of the ring of decoded W tiles
     uint32_t tmem_cols;   // power of two >= max(32, n_acc * tm)
     uint32_t n_acc;       // 1 or 2 accumulators; with 2, even and odd K steps alternate
     uint32_t m_tiles;     // ceil(m / tm)
     uint32_t x_tx_bytes;  // bytes one TMA x tile delivers: min(tm, m) rows of 128 bytes
+    uint32_t flags;       // bit 0 (two-CTA kernel): reuse the W tile from the MMA's A collector buffer
 };
 
 __host__ __device__ constexpr uint32_t gemm_stage_bytes(uint32_t tm) { return tm * 128u + GEMM_W_TILE_BYTES; }
@@ -132,6 +135,7 @@ gemm_fp4_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmAr
         // ---------------------------------------------------------------- MMA issuer
         if (lane == 0) {
             const uint32_t idesc = umma_idesc_f16_f32(GEMM_TN, a.tm);
+            const uint32_t x_lo0 = umma_desc_lo(base), stage16 = stage_bytes >> 4, w_off16 = x_bytes >> 4;
             bool ok = true;
             for (uint32_t kb = 0; kb < KB && ok; kb++) {
                 const uint32_t s = kb % S, ph = (kb / S) & 1u;
@@ -148,16 +152,13 @@ gemm_fp4_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmAr
                     break;
                 }
                 tc_fence_after_sync();
-                const uint32_t x_addr = base + s * stage_bytes;
-                const uint32_t w_addr = x_addr + x_bytes;
+                const uint32_t b_lo = x_lo0 + s * stage16, a_lo = b_lo + w_off16;
+                // Two accumulators halve the run of truncating f32 additions each one sees (the
+                // tensor core does not round to nearest when it accumulates).
+                const uint32_t d = tmem_base + (kb % a.n_acc) * a.tm;
+                umma1_flag(d, a_lo, b_lo, idesc, kb >= a.n_acc);
 #pragma unroll
-                for (uint32_t kk = 0; kk < GEMM_BK / 16; kk++) {
-                    const uint64_t a_desc = umma_desc_k_sw128(w_addr + kk * 32u);
-                    const uint64_t b_desc = umma_desc_k_sw128(x_addr + kk * 32u);
-                    // Two accumulators halve the run of truncating f32 additions each one
-                    // sees (the tensor core does not round to nearest when it accumulates).
-                    umma_f16_ss(tmem_base + (kb % a.n_acc) * a.tm, a_desc, b_desc, idesc, (kb >= a.n_acc) || kk != 0u);
-                }
+                for (uint32_t kk = 1; kk < GEMM_BK / 16; kk++) umma1_acc(d, a_lo + 2u * kk, b_lo + 2u * kk, idesc);
                 umma_commit(empty(s));      // frees the stage once these MMAs have read it
             }
             if (ok) umma_commit(acc_full);  // accumulator complete

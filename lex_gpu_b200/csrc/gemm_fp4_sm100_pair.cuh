@@ -11,6 +11,11 @@
 // decoded weights: twice the decode budget of the one-CTA kernel, and half its shared-memory
 // traffic for x.
 //
+// The packed weights never pass through a dequant thread's global loads: a third single-thread
+// role brings them in by TMA, 256 columns of K at a time (a [128 rows x 128 bytes] tile of codes,
+// 128-byte swizzled, and a [128 x 16 bytes] tile of scales), two such blocks in flight, and the
+// dequant threads read their 8 bytes of codes and 1 scale byte per K step from shared memory.
+//
 // Barriers: the leader CTA's `x_full` and `w_full` collect arrivals from both CTAs (the partner
 // arrives through shared::cluster addresses; its TMA reports bytes to the leader's barrier);
 // `empty` and `acc_full` exist in both CTAs and are signalled together by tcgen05.commit.
@@ -25,27 +30,49 @@ namespace lexb {
 constexpr uint32_t PAIR_TOKENS = 512;                 // tokens per pair tile
 constexpr uint32_t PAIR_XBLK_ROWS = 128;              // tokens per TMA box (one CTA's half of a block)
 constexpr uint32_t PAIR_XBLK_BYTES = PAIR_XBLK_ROWS * 128u;                  // 16 KiB
-constexpr uint32_t PAIR_STAGE_BYTES = 2u * PAIR_XBLK_BYTES + GEMM_W_TILE_BYTES;   // 48 KiB
+constexpr uint32_t PAIR_X_STAGE_BYTES = 2u * PAIR_XBLK_BYTES;                // 32 KiB: two token blocks
 constexpr uint32_t PAIR_TMEM_COLS = 512;
+constexpr uint32_t PAIR_DEQ_THREADS = 512;            // 16 warps: one group of 16 weights per thread and K step
+constexpr uint32_t PAIR_WARP_TMA = 16;
+constexpr uint32_t PAIR_WARP_MMA = 17;                // leader: issues the MMAs; partner: relays its w_full
+constexpr uint32_t PAIR_WARP_RAW = 18;                // TMA of the packed codes and scales
+constexpr uint32_t PAIR_THREADS = 608;
+constexpr uint32_t PAIR_RAW_K = 256;                  // K columns per block of packed weights
+constexpr uint32_t PAIR_RAW_WQ_BYTES = GEMM_TN * (PAIR_RAW_K / 2);          // 16 KiB
+constexpr uint32_t PAIR_RAW_WS_BYTES = GEMM_TN * (PAIR_RAW_K / 16);         // 2 KiB
+constexpr uint32_t PAIR_RAW_BYTES = PAIR_RAW_WQ_BYTES + PAIR_RAW_WS_BYTES;
+constexpr uint32_t PAIR_RAW_STAGES = 2;
 
-__host__ __device__ constexpr uint32_t pair_smem_bytes(uint32_t stages) {
-    return stages * PAIR_STAGE_BYTES + (3u * stages + 1u) * 8u + 16u + 1024u;
+// x ring, W ring (their depths are independent: the decoded W tiles may run further ahead of the
+// MMA than the x tiles), packed-weight blocks, barriers, TMEM slot + abort flag, alignment slack
+__host__ __device__ constexpr uint32_t pair_smem_bytes(uint32_t sx, uint32_t sw) {
+    return sx * PAIR_X_STAGE_BYTES + sw * GEMM_W_TILE_BYTES + PAIR_RAW_STAGES * PAIR_RAW_BYTES +
+           (2u * sx + 3u * sw + 1u + 2u * PAIR_RAW_STAGES) * 8u + 16u + 1024u;
 }
 
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
-gemm_fp4_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmArgs a) {
+template <bool TRACE>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1)
+gemm_fp4_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_wq,
+                             const __grid_constant__ CUtensorMap tmap_ws, const GemmArgs a) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw_addr = smem_u32(smem_raw);
     const uint32_t base = (raw_addr + 1023u) & ~1023u;
     uint8_t* const smem = smem_raw + (base - raw_addr);
 
-    const uint32_t S = a.stages;
-    const uint32_t bars = base + S * PAIR_STAGE_BYTES;
-    auto x_full = [&](uint32_t s) { return bars + 8u * s; };            // used in the leader only
-    auto w_full = [&](uint32_t s) { return bars + 8u * (S + s); };      // used in the leader only
-    auto empty = [&](uint32_t s) { return bars + 8u * (2u * S + s); };  // both CTAs
-    const uint32_t acc_full = bars + 8u * 3u * S;                       // both CTAs
-    uint32_t* const tmem_slot = reinterpret_cast<uint32_t*>(smem + S * PAIR_STAGE_BYTES + (3u * S + 1u) * 8u);
+    const uint32_t SX = a.stages, SW = a.w_stages;
+    const uint32_t w_base = base + SX * PAIR_X_STAGE_BYTES;                // decoded W tiles
+    const uint32_t raw_base = w_base + SW * GEMM_W_TILE_BYTES;             // packed weight blocks
+    const uint32_t bars = raw_base + PAIR_RAW_STAGES * PAIR_RAW_BYTES;
+    auto x_full = [&](uint32_t s) { return bars + 8u * s; };                      // leader only: bytes of both CTAs
+    auto x_empty = [&](uint32_t s) { return bars + 8u * (SX + s); };              // both CTAs, signalled together
+    auto w_full = [&](uint32_t s) { return bars + 8u * (2u * SX + s); };          // each CTA: its own dequant threads
+    auto w_peer = [&](uint32_t s) { return bars + 8u * (2u * SX + SW + s); };     // leader only: the partner's W tile
+    auto w_empty = [&](uint32_t s) { return bars + 8u * (2u * SX + 2u * SW + s); };   // both CTAs
+    const uint32_t nb = 2u * SX + 3u * SW;
+    const uint32_t acc_full = bars + 8u * nb;                                     // both CTAs
+    auto raw_full = [&](uint32_t rs) { return bars + 8u * (nb + 1u + rs); };
+    auto raw_empty = [&](uint32_t rs) { return bars + 8u * (nb + 1u + PAIR_RAW_STAGES + rs); };
+    uint32_t* const tmem_slot = reinterpret_cast<uint32_t*>(smem + (bars - base) + (nb + 1u + 2u * PAIR_RAW_STAGES) * 8u);
     volatile uint32_t* const abort_flag = tmem_slot + 1;
 
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
@@ -55,19 +82,32 @@ gemm_fp4_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const G
     const uint32_t m0 = m_tile * PAIR_TOKENS;
     const uint32_t n0 = n_pair * 2u * GEMM_TN + rank * GEMM_TN;
     const uint32_t KB = a.k / GEMM_BK;
+    const long long t_start = clock64();
 
     if (tid == 0) {
         *abort_flag = 0;
-        for (uint32_t s = 0; s < S; s++) {
+        for (uint32_t s = 0; s < SX; s++) {
             mbar_init(x_full(s), 2);                         // one arrive.expect_tx per CTA
-            mbar_init(w_full(s), 16);                        // one arrive per dequant warp of either CTA
-            mbar_init(empty(s), 1);
+            mbar_init(x_empty(s), 1);
+        }
+        for (uint32_t s = 0; s < SW; s++) {
+            mbar_init(w_full(s), PAIR_DEQ_THREADS);          // every dequant thread of this CTA
+            mbar_init(w_peer(s), 1);                         // the partner's relay thread
+            mbar_init(w_empty(s), 1);
+        }
+        for (uint32_t rs = 0; rs < PAIR_RAW_STAGES; rs++) {
+            mbar_init(raw_full(rs), 1);
+            mbar_init(raw_empty(rs), PAIR_DEQ_THREADS);
         }
         mbar_init(acc_full, 1);
         fence_mbar_init();
     }
-    if (warp == GEMM_WARP_TMA && lane == 0) prefetch_tensormap(&tmap_x);
-    if (warp == GEMM_WARP_MMA) {
+    if (warp == PAIR_WARP_TMA && lane == 0) prefetch_tensormap(&tmap_x);
+    if (warp == PAIR_WARP_RAW && lane == 0) {
+        prefetch_tensormap(&tmap_wq);
+        prefetch_tensormap(&tmap_ws);
+    }
+    if (warp == PAIR_WARP_MMA) {
         tmem_alloc_pair(smem_u32(tmem_slot), PAIR_TMEM_COLS);
         tmem_relinquish_pair();
     }
@@ -77,19 +117,19 @@ gemm_fp4_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const G
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
 
-    if (warp == GEMM_WARP_TMA) {
+    if (warp == PAIR_WARP_TMA) {
         // ---------------------------------------------------------------- TMA producer (both CTAs)
         if (lane == 0) {
             for (uint32_t kb = 0; kb < KB; kb++) {
-                const uint32_t s = kb % S, ph = (kb / S) & 1u;
-                if (!mbar_wait(empty(s), ph ^ 1u, abort_flag)) {
+                const uint32_t s = kb % SX, ph = (kb / SX) & 1u;
+                if (!mbar_wait(x_empty(s), ph ^ 1u, abort_flag)) {
                     atomicOr(a.status, ST_WAIT_EMPTY_TMA);
                     *abort_flag = 1;
                     break;
                 }
                 const uint32_t lead_bar = map_to_cta(x_full(s), 0);
                 mbar_arrive_expect_tx_cluster(lead_bar, 2u * PAIR_XBLK_BYTES);
-                const uint32_t dst = base + s * PAIR_STAGE_BYTES;
+                const uint32_t dst = base + s * PAIR_X_STAGE_BYTES;
                 // token block tb covers tokens m0 + 256 tb .. +255; this CTA holds 128 of them
                 tma_load_2d_pair(dst, &tmap_x, (int)(kb * GEMM_BK), (int)(m0 + rank * PAIR_XBLK_ROWS), lead_bar);
                 tma_load_2d_pair(dst + PAIR_XBLK_BYTES, &tmap_x, (int)(kb * GEMM_BK),
@@ -104,84 +144,177 @@ gemm_fp4_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const G
             }
         }
         __syncwarp();
-    } else if (warp == GEMM_WARP_MMA) {
+    } else if (warp == PAIR_WARP_RAW) {
+        // ---------------------------------------------------------------- TMA of packed weights (both CTAs)
+        if (lane == 0) {
+            const uint32_t RB = (a.k + PAIR_RAW_K - 1u) / PAIR_RAW_K;
+            for (uint32_t rb = 0; rb < RB; rb++) {
+                const uint32_t rs = rb % PAIR_RAW_STAGES, ph = (rb / PAIR_RAW_STAGES) & 1u;
+                if (!mbar_wait(raw_empty(rs), ph ^ 1u, abort_flag)) {
+                    atomicOr(a.status, ST_WAIT_EMPTY_TMA);
+                    *abort_flag = 1;
+                    break;
+                }
+                mbar_arrive_expect_tx(raw_full(rs), PAIR_RAW_BYTES);
+                const uint32_t dst = raw_base + rs * PAIR_RAW_BYTES;
+                tma_load_2d(dst, &tmap_wq, (int)(rb * (PAIR_RAW_K / 2)), (int)n0, raw_full(rs));
+                tma_load_2d(dst + PAIR_RAW_WQ_BYTES, &tmap_ws, (int)(rb * (PAIR_RAW_K / 16)), (int)n0, raw_full(rs));
+            }
+            if (*abort_flag) {
+                const long long t0 = clock64();
+                while (clock64() - t0 < 400000) {
+                }
+            }
+        }
+        __syncwarp();
+    } else if (warp == PAIR_WARP_MMA) {
+        if (rank != 0 && lane == 0) {
+            // ------------------------------------------------------------ partner: relay of w_full
+            // One cluster-scope arrive per K step from this otherwise idle thread, so that the
+            // dequant threads only ever touch barriers of their own CTA.
+            for (uint32_t kb = 0; kb < KB; kb++) {
+                const uint32_t s = kb % SW, ph = (kb / SW) & 1u;
+                if (!mbar_wait(w_full(s), ph, abort_flag)) {
+                    atomicOr(a.status, ST_WAIT_W_FULL);
+                    *abort_flag = 1;
+                    break;
+                }
+                mbar_arrive_cluster(map_to_cta(w_peer(s), 0));
+            }
+        }
         // ---------------------------------------------------------------- MMA issuer (leader only)
         if (rank == 0 && lane == 0) {
             const uint32_t idesc = umma_idesc_f16_f32(256u, 256u);
+            const uint32_t x_lo0 = umma_desc_lo(base), w_lo0 = umma_desc_lo(w_base);
+            const uint32_t d0 = tmem_base, d1 = tmem_base + 256u;
+            const bool reuse_a = (a.flags & 1u) != 0u;
             bool ok = true;
+            long long wait_x = 0, wait_w = 0, wait_p = 0, t_first = 0;
             for (uint32_t kb = 0; kb < KB; kb++) {
-                const uint32_t s = kb % S, ph = (kb / S) & 1u;
+                const uint32_t s = kb % SX, ph = (kb / SX) & 1u;
+                const uint32_t sw = kb % SW, phw = (kb / SW) & 1u;
+                long long tw0 = 0, tw1 = 0, tw2 = 0;
+                if (TRACE) tw0 = clock64();
                 if (!mbar_wait_cluster(x_full(s), ph, abort_flag)) {
                     atomicOr(a.status, ST_WAIT_X_FULL);
                     *abort_flag = 1;
                     ok = false;
                     break;
                 }
-                if (!mbar_wait_cluster(w_full(s), ph, abort_flag)) {
+                if (TRACE) tw1 = clock64();
+                if (!mbar_wait(w_full(sw), phw, abort_flag)) {
                     atomicOr(a.status, ST_WAIT_W_FULL);
                     *abort_flag = 1;
                     ok = false;
                     break;
                 }
-                tc_fence_after_sync();
-                const uint32_t x_addr = base + s * PAIR_STAGE_BYTES;
-                const uint32_t w_addr = x_addr + 2u * PAIR_XBLK_BYTES;
-#pragma unroll
-                for (uint32_t kk = 0; kk < GEMM_BK / 16; kk++) {
-                    const uint64_t a_desc = umma_desc_k_sw128(w_addr + kk * 32u);
-                    const uint32_t acc = (kb | kk) != 0u;
-                    umma_f16_ss_pair(tmem_base, a_desc, umma_desc_k_sw128(x_addr + kk * 32u), idesc, acc);
-                    umma_f16_ss_pair(tmem_base + 256u, a_desc, umma_desc_k_sw128(x_addr + PAIR_XBLK_BYTES + kk * 32u),
-                                     idesc, acc);
+                if (TRACE) tw2 = clock64();
+                if (!mbar_wait_cluster(w_peer(sw), phw, abort_flag)) {
+                    atomicOr(a.status, ST_WAIT_W_FULL);
+                    *abort_flag = 1;
+                    ok = false;
+                    break;
                 }
-                umma_commit_pair(empty(s), 3);               // frees the stage in both CTAs
+                if (TRACE) {
+                    const long long tw3 = clock64();
+                    wait_x += tw1 - tw0;
+                    wait_w += tw2 - tw1;
+                    wait_p += tw3 - tw2;
+                    if (kb == 0) t_first = tw3;
+                }
+                tc_fence_after_sync();
+                // low descriptor halves of this K step's tiles; +2 per 16 columns of K
+                const uint32_t b0 = x_lo0 + s * (PAIR_X_STAGE_BYTES >> 4);
+                const uint32_t b1 = b0 + (PAIR_XBLK_BYTES >> 4);
+                const uint32_t aw = w_lo0 + sw * (GEMM_W_TILE_BYTES >> 4);
+                const uint32_t first = kb != 0u;          // the very first MMA of each block overwrites
+                if (reuse_a) {
+                    // both token blocks multiply the same W tile: read it from shared memory once
+                    umma2_flag_fill(d0, aw, b0, idesc, first);
+                    umma2_flag_lastuse(d1, aw, b1, idesc, first);
+#pragma unroll
+                    for (uint32_t kk = 1; kk < GEMM_BK / 16; kk++) {
+                        umma2_acc_fill(d0, aw + 2u * kk, b0 + 2u * kk, idesc);
+                        umma2_acc_lastuse(d1, aw + 2u * kk, b1 + 2u * kk, idesc);
+                    }
+                } else {
+                    umma2_flag(d0, aw, b0, idesc, first);
+                    umma2_flag(d1, aw, b1, idesc, first);
+#pragma unroll
+                    for (uint32_t kk = 1; kk < GEMM_BK / 16; kk++) {
+                        umma2_acc(d0, aw + 2u * kk, b0 + 2u * kk, idesc);
+                        umma2_acc(d1, aw + 2u * kk, b1 + 2u * kk, idesc);
+                    }
+                }
+                umma_commit_pair(x_empty(s), 3);             // frees the x stage in both CTAs
+                umma_commit_pair(w_empty(sw), 3);            // and the W stage
             }
             if (ok) umma_commit_pair(acc_full, 3);
+            if (TRACE && a.trace) {
+                unsigned long long* tr = a.trace + 16ull * blockIdx.x;
+                tr[1] = (unsigned long long)t_first;      // first stage ready
+                tr[2] = (unsigned long long)clock64();    // all MMAs issued
+                tr[3] = (unsigned long long)wait_x;
+                tr[4] = (unsigned long long)wait_w;
+                tr[5] = (unsigned long long)wait_p;
+            }
         }
         __syncwarp();
     } else {
-        // ---------------------------------------------------------------- dequant warps 0-7 (both CTAs)
-        // Thread (row r, half h): a warp covers 32 consecutive rows and one half, so the eight
-        // 16-byte chunks any 8 consecutive lanes store fall into eight different bank groups.
-        const uint32_t r = tid & 127u, h = tid >> 7;
+        // ---------------------------------------------------------------- dequant warps 0-15 (both CTAs)
+        // Thread (row r, group q): a warp covers 32 consecutive rows and one group of 16 columns,
+        // so the 16-byte chunks any 8 consecutive lanes store fall into different bank groups.
+        const uint32_t r = tid & 127u, qtr = tid >> 7;
         const uint32_t row = n0 + r;
         const float g = __ldg(a.wg + row);
-        const uint4* qrow = reinterpret_cast<const uint4*>(a.wq + (size_t)row * (a.k / 2)) + h;
-        const uint32_t* srow = reinterpret_cast<const uint32_t*>(a.ws + (size_t)row * (a.k / 16));
-        const uint32_t w_off = 2u * PAIR_XBLK_BYTES + r * 128u;
+        const uint32_t w_off = (w_base - base) + r * 128u;
         const uint32_t sw_xor = r & 7u;
-        const uint32_t c = 4u * h;
-        // two K steps of codes and scales in flight
-        uint4 q0 = __ldg(qrow), q1 = KB > 1 ? __ldg(qrow + 2) : make_uint4(0, 0, 0, 0);
-        uint32_t s0 = __ldg(srow), s1 = KB > 1 ? __ldg(srow + 1) : 0u;
+        const uint32_t c = 2u * qtr;
+        const uint8_t* raw0 = smem + (raw_base - base);
         bool ok = true;
+        long long dq_wait_raw = 0, dq_wait_empty = 0, dq_t0 = 0;
+        if (TRACE) dq_t0 = clock64();
         for (uint32_t kb = 0; kb < KB; kb++) {
-            const uint32_t s = kb % S, ph = (kb / S) & 1u;
-            const uint4 q = q0;
-            const uint32_t sw = s0 >> (16u * h);
-            q0 = q1;
-            s0 = s1;
-            if (kb + 2 < KB) {
-                q1 = __ldg(qrow + 2u * (kb + 2));
-                s1 = __ldg(srow + kb + 2);
+            const uint32_t s = kb % SW, ph = (kb / SW) & 1u;
+            const uint32_t jj = kb & 3u, rb = kb >> 2;
+            const uint32_t rs = rb % PAIR_RAW_STAGES, rph = (rb / PAIR_RAW_STAGES) & 1u;
+            long long tq0 = 0;
+            if (TRACE) tq0 = clock64();
+            if (jj == 0 && !mbar_wait(raw_full(rs), rph, abort_flag)) {
+                atomicOr(a.status, ST_WAIT_X_FULL);
+                *abort_flag = 1;
+                ok = false;
+                break;
             }
-            uint4 o0, o1, o2, o3;
-            decode_group16(make_uint2(q.x, q.y), sw & 0xFFu, g, o0, o1);
-            decode_group16(make_uint2(q.z, q.w), (sw >> 8) & 0xFFu, g, o2, o3);
-            if (!mbar_wait(empty(s), ph ^ 1u, abort_flag)) {
+            if (TRACE) dq_wait_raw += clock64() - tq0;
+            // codes of K step jj of this block: bytes 32 jj + 8 qtr of row r, in the swizzled tile
+            const uint8_t* raw = raw0 + rs * PAIR_RAW_BYTES;
+            const uint32_t ch = 2u * jj + (qtr >> 1);
+            const uint2 q = *reinterpret_cast<const uint2*>(raw + r * 128u + ((ch ^ sw_xor) << 4) + 8u * (qtr & 1u));
+            const uint32_t sb = raw[PAIR_RAW_WQ_BYTES + r * 16u + 4u * jj + qtr];
+            if (jj == 3u || kb + 1 == KB) mbar_arrive(raw_empty(rs));   // this thread is done with the block
+            uint4 o0, o1;
+            decode_group16(q, sb, g, o0, o1);
+            long long tq1 = 0;
+            if (TRACE) tq1 = clock64();
+            if (!mbar_wait(w_empty(s), ph ^ 1u, abort_flag)) {
                 atomicOr(a.status, ST_WAIT_EMPTY_DEQ);
                 *abort_flag = 1;
                 ok = false;
                 break;
             }
-            uint8_t* wt = smem + s * PAIR_STAGE_BYTES + w_off;
+            if (TRACE) dq_wait_empty += clock64() - tq1;
+            uint8_t* wt = smem + s * GEMM_W_TILE_BYTES + w_off;
             *reinterpret_cast<uint4*>(wt + (((c + 0u) ^ sw_xor) << 4)) = o0;
             *reinterpret_cast<uint4*>(wt + (((c + 1u) ^ sw_xor) << 4)) = o1;
-            *reinterpret_cast<uint4*>(wt + (((c + 2u) ^ sw_xor) << 4)) = o2;
-            *reinterpret_cast<uint4*>(wt + (((c + 3u) ^ sw_xor) << 4)) = o3;
-            fence_proxy_async_smem();
-            __syncwarp();
-            if (lane == 0) mbar_arrive_cluster(map_to_cta(w_full(s), 0));
+            fence_proxy_async_smem();       // generic-proxy stores -> visible to the MMA's reads
+            mbar_arrive(w_full(s));
+        }
+        if (TRACE && a.trace && (tid == 0 || tid == 511)) {
+            unsigned long long* tr = a.trace + 16ull * blockIdx.x + (tid == 0 ? 8 : 12);
+            tr[0] = (unsigned long long)(clock64() - dq_t0);     // dequant loop, total
+            tr[1] = (unsigned long long)dq_wait_raw;            // ... of which waiting for packed weights
+            tr[2] = (unsigned long long)dq_wait_empty;          // ... and for a free W stage
         }
         __syncwarp();
         // ---------------------------------------------------------------- epilogue (both CTAs)
@@ -194,11 +327,15 @@ gemm_fp4_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const G
             }
         }
         go = __shfl_sync(0xFFFFFFFFu, go, 0);
+        if (TRACE && a.trace && tid == 0) {
+            a.trace[16ull * blockIdx.x + 0] = (unsigned long long)t_start;
+            a.trace[16ull * blockIdx.x + 6] = (unsigned long long)clock64();   // accumulator complete
+        }
         if (go) {
             tc_fence_after_sync();
-            const uint32_t quarter = warp & 3u, half = warp >> 2;
+            const uint32_t quarter = warp & 3u, slice = warp >> 2;      // 4 lane quarters x 4 column slices
             const uint32_t out_row = n0 + 32u * quarter + lane;
-            for (uint32_t cc = half; cc < PAIR_TOKENS / 16u; cc += 2u) {
+            for (uint32_t cc = slice; cc < PAIR_TOKENS / 16u; cc += 4u) {
                 const uint32_t t0 = m0 + cc * 16u;
                 if (t0 >= a.m) break;                        // warp-uniform
                 uint32_t v[16];
@@ -220,8 +357,9 @@ gemm_fp4_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const G
 
     tc_fence_before_sync();
     __syncthreads();
+    if (TRACE && a.trace && tid == 0) a.trace[16ull * blockIdx.x + 7] = (unsigned long long)clock64();   // epilogue done
     cluster_sync_all();          // the partner's shared memory and barriers stay alive until both are done
-    if (warp == GEMM_WARP_MMA) {
+    if (warp == PAIR_WARP_MMA) {
         tc_fence_after_sync();
         tmem_dealloc_pair(tmem_base, PAIR_TMEM_COLS);
     }

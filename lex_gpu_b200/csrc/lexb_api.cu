@@ -55,6 +55,8 @@ struct lexb_gpu {
     cudaStream_t own_stream = nullptr;
     cudaStream_t stream = nullptr;       // own_stream or the caller's
     uint32_t* d_status = nullptr;
+    unsigned long long* d_trace = nullptr;   // phase timers of the last two-CTA launch, when tracing is on
+    size_t trace_ctas = 0;
     cudaDeviceProp prop{};
     EncodeTiledFn encode_tiled = nullptr;
     size_t smem_optin = 0;
@@ -73,15 +75,15 @@ struct lexb_pipeline {
     uint32_t m, n, k;
     bool residual;
     // tcgen05 GEMM
-    uint32_t tm, stages, tmem_cols, m_tiles, n_acc;
+    uint32_t tm, stages, w_stages, tmem_cols, m_tiles, n_acc, flags;
     // matvec
     uint32_t kc;
     uint32_t grid, threads, smem;
     char entry[96];
     // tensor maps of x, keyed by the device pointer they were encoded for
     struct MapEntry {
-        const void* x;
-        CUtensorMap map;
+        const void *x, *wq, *ws;
+        CUtensorMap map, map_wq, map_ws;
     };
     mutable std::vector<MapEntry> maps;
     mutable std::mutex maps_lock;
@@ -146,28 +148,50 @@ __global__ void dequant_fp4_f16_kernel(uint32_t n, uint32_t k, const uint8_t* __
     }
 }
 
-int get_x_map(const lexb_pipeline* p, const void* x, CUtensorMap* out) {
+int encode_2d(const lexb_pipeline* p, CUtensorMap* map, CUtensorMapDataType dt, uint32_t esize, const void* ptr,
+              uint64_t inner, uint64_t outer, uint32_t box_inner, uint32_t box_outer, CUtensorMapSwizzle swz,
+              const char* what) {
+    const cuuint64_t dims[2] = {inner, outer};
+    const cuuint64_t strides[1] = {inner * esize};
+    const cuuint32_t box[2] = {box_inner, box_outer};
+    const cuuint32_t estr[2] = {1, 1};
+    CUresult r = p->gpu->encode_tiled(map, dt, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                                      CU_TENSOR_MAP_INTERLEAVE_NONE, swz, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(LEXB_ERR_CUDA, "cuTensorMapEncodeTiled(%s) failed with CUresult %d", what, (int)r);
+    return LEXB_OK;
+}
+
+// Tensor maps for one binding, cached by the device pointers they were encoded for.
+int get_maps(const lexb_pipeline* p, const void* x, const void* wq, const void* ws, lexb_pipeline::MapEntry* out) {
     std::lock_guard<std::mutex> lk(p->maps_lock);
+    const bool pair = p->kernel == KERNEL_TCGEN05_PAIR;
     for (const auto& e : p->maps)
-        if (e.x == x) {
-            *out = e.map;
+        if (e.x == x && (!pair || (e.wq == wq && e.ws == ws))) {
+            *out = e;
             return LEXB_OK;
         }
-    CUtensorMap map;
-    // x f16[m, k] row-major; box = 64 columns (128 bytes, the swizzle span) x tm rows.
-    // Rows past m are filled with zeros by the copy engine.
-    const cuuint64_t dims[2] = {p->k, p->m};
-    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(p->k) * 2u};
-    const uint32_t box_rows = p->kernel == KERNEL_TCGEN05_PAIR ? lexb::PAIR_XBLK_ROWS : (p->tm < p->m ? p->tm : p->m);
-    const cuuint32_t box[2] = {lexb::GEMM_BK, box_rows};   // never taller than the tensor
-    const cuuint32_t estr[2] = {1, 1};
-    CUresult r = p->gpu->encode_tiled(&map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(x), dims, strides, box,
-                                      estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                                      CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) return fail(LEXB_ERR_CUDA, "cuTensorMapEncodeTiled(x) failed with CUresult %d", (int)r);
+    lexb_pipeline::MapEntry e{};
+    e.x = x; e.wq = wq; e.ws = ws;
+    int rc;
+    // x f16[m, k] row-major; box = 64 columns (128 bytes, the swizzle span) x the tile's tokens, never
+    // taller than the tensor.  Rows past m are filled with zeros by the copy engine.
+    const uint32_t box_rows = pair ? lexb::PAIR_XBLK_ROWS : (p->tm < p->m ? p->tm : p->m);
+    if ((rc = encode_2d(p, &e.map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, x, p->k, p->m, lexb::GEMM_BK, box_rows,
+                        CU_TENSOR_MAP_SWIZZLE_128B, "x")))
+        return rc;
+    if (pair) {
+        // wq u8[n, k/2]: 128 rows x 128 bytes (256 columns of K), swizzled; ws u8[n, k/16]: 128 rows x 16 bytes
+        if ((rc = encode_2d(p, &e.map_wq, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, wq, p->k / 2, p->n, lexb::PAIR_RAW_K / 2,
+                            lexb::GEMM_TN, CU_TENSOR_MAP_SWIZZLE_128B, "wq")))
+            return rc;
+        if ((rc = encode_2d(p, &e.map_ws, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, ws, p->k / 16, p->n, lexb::PAIR_RAW_K / 16,
+                            lexb::GEMM_TN, CU_TENSOR_MAP_SWIZZLE_NONE, "ws")))
+            return rc;
+    }
     if (p->maps.size() >= 64) p->maps.erase(p->maps.begin());
-    p->maps.push_back({x, map});
-    *out = map;
+    p->maps.push_back(e);
+    *out = e;
     return LEXB_OK;
 }
 
@@ -188,8 +212,8 @@ int launch_one(lexb_gpu* g, const lexb_pipeline* p, const lexb_buffer* x, const 
         return fail(LEXB_ERR_ARG, "a residual buffer was bound to a pipeline planned without one");
     }
     if (p->kernel == KERNEL_TCGEN05 || p->kernel == KERNEL_TCGEN05_PAIR) {
-        CUtensorMap map;
-        if ((rc = get_x_map(p, x->ptr, &map))) return rc;
+        lexb_pipeline::MapEntry maps;
+        if ((rc = get_maps(p, x->ptr, wq->ptr, ws->ptr, &maps))) return rc;
         lexb::GemmArgs a{};
         a.wq = static_cast<const uint8_t*>(wq->ptr);
         a.ws = static_cast<const uint8_t*>(ws->ptr);
@@ -197,13 +221,17 @@ int launch_one(lexb_gpu* g, const lexb_pipeline* p, const lexb_buffer* x, const 
         a.r = r ? static_cast<const float*>(r->ptr) : nullptr;
         a.y = static_cast<float*>(y->ptr);
         a.status = g->d_status;
+        a.trace = (g->d_trace && p->kernel == KERNEL_TCGEN05_PAIR && p->grid <= g->trace_ctas) ? g->d_trace : nullptr;
         a.m = p->m; a.n = p->n; a.k = p->k;
-        a.tm = p->tm; a.stages = p->stages; a.tmem_cols = p->tmem_cols; a.m_tiles = p->m_tiles; a.n_acc = p->n_acc;
+        a.tm = p->tm; a.stages = p->stages; a.w_stages = p->w_stages; a.flags = p->flags; a.tmem_cols = p->tmem_cols; a.m_tiles = p->m_tiles; a.n_acc = p->n_acc;
         a.x_tx_bytes = (p->tm < p->m ? p->tm : p->m) * 128u;
         if (p->kernel == KERNEL_TCGEN05_PAIR)
-            lexb::gemm_fp4_tcgen05_pair_kernel<<<p->grid, p->threads, p->smem, g->stream>>>(map, a);
+            if (a.trace)
+                lexb::gemm_fp4_tcgen05_pair_kernel<true><<<p->grid, p->threads, p->smem, g->stream>>>(maps.map, maps.map_wq, maps.map_ws, a);
+            else
+                lexb::gemm_fp4_tcgen05_pair_kernel<false><<<p->grid, p->threads, p->smem, g->stream>>>(maps.map, maps.map_wq, maps.map_ws, a);
         else
-            lexb::gemm_fp4_tcgen05_kernel<<<p->grid, p->threads, p->smem, g->stream>>>(map, a);
+            lexb::gemm_fp4_tcgen05_kernel<<<p->grid, p->threads, p->smem, g->stream>>>(maps.map, a);
     } else {
         lexb::MatvecArgs a{};
         a.x = static_cast<const __half*>(x->ptr);
@@ -270,7 +298,8 @@ int lexb_open(int device, lexb_gpu** out) {
     g->encode_tiled = reinterpret_cast<EncodeTiledFn>(fn);
     const int max_smem = static_cast<int>(g->smem_optin);
     if (cudaFuncSetAttribute(lexb::gemm_fp4_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem) != cudaSuccess ||
-        cudaFuncSetAttribute(lexb::gemm_fp4_tcgen05_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem) != cudaSuccess ||
+        cudaFuncSetAttribute(lexb::gemm_fp4_tcgen05_pair_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem) != cudaSuccess ||
+        cudaFuncSetAttribute(lexb::gemm_fp4_tcgen05_pair_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem) != cudaSuccess ||
         cudaFuncSetAttribute(lexb::matvec_fp4_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem) != cudaSuccess ||
         cudaFuncSetAttribute(lexb::matvec_fp4_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem) != cudaSuccess)
         return bail(fail(LEXB_ERR_CUDA, "cudaFuncSetAttribute(max dynamic shared memory) failed: %s", cudaGetErrorString(cudaGetLastError())));
@@ -286,6 +315,7 @@ void lexb_close(lexb_gpu* g) {
         cudaStreamDestroy(g->own_stream);
     }
     if (g->d_status) cudaFree(g->d_status);
+    if (g->d_trace) cudaFree(g->d_trace);
     delete g;
 }
 
@@ -429,10 +459,11 @@ int lexb_gemm_fp4_plan(lexb_gpu* g, uint32_t m, uint32_t n, uint32_t k, int resi
     if (!s.tm) s.tm = env_u32("LEXB_TM", 0);
     if (!s.stages) s.stages = env_u32("LEXB_STAGES", 0);
     if (!s.kc) s.kc = env_u32("LEXB_KC", 0);
+    if (!s.w_stages) s.w_stages = env_u32("LEXB_WSTAGES", 0);
     // m <= 16: matvec.  m > 256 and whole 256-row pairs: the two-CTA GEMM.  Otherwise the one-CTA GEMM.
     uint32_t kernel = s.kernel ? s.kernel
                                : (m <= 16 ? KERNEL_MATVEC
-                                          : ((m > 256 && n % 256u == 0 && k % lexb::GEMM_BK == 0) ? KERNEL_TCGEN05_PAIR : KERNEL_TCGEN05));
+                                          : ((m > 256 && n % 256u == 0 && k % lexb::PAIR_RAW_K == 0) ? KERNEL_TCGEN05_PAIR : KERNEL_TCGEN05));
     if (kernel == KERNEL_MATVEC && m > 16) return fail(LEXB_ERR_SHAPE, "the matvec kernel takes m <= 16, not %u", m);
     if (kernel < KERNEL_MATVEC || kernel > KERNEL_TCGEN05_PAIR) return fail(LEXB_ERR_ARG, "unknown kernel selector %u", kernel);
 
@@ -471,17 +502,20 @@ int lexb_gemm_fp4_plan(lexb_gpu* g, uint32_t m, uint32_t n, uint32_t k, int resi
         snprintf(p->entry, sizeof p->entry, "%s_%u_%u_%u_%u_%u_%u", stem, m, n, k, tm, lexb::GEMM_TN, lexb::GEMM_BK);
     } else if (kernel == KERNEL_TCGEN05_PAIR) {
         if (n % (2u * lexb::GEMM_TN)) return bail(fail(LEXB_ERR_SHAPE, "gemm_fp4 (pair): bn = %u does not divide n = %u", 2u * lexb::GEMM_TN, n));
-        if (k % lexb::GEMM_BK) return bail(fail(LEXB_ERR_SHAPE, "gemm_fp4: bk = %u does not divide k = %u", lexb::GEMM_BK, k));
+        if (k % lexb::PAIR_RAW_K) return bail(fail(LEXB_ERR_SHAPE, "gemm_fp4 (pair): the packed-weight block of %u columns does not divide k = %u", lexb::PAIR_RAW_K, k));
         if (m < lexb::PAIR_XBLK_ROWS) return bail(fail(LEXB_ERR_SHAPE, "the two-CTA kernel takes m >= %u, not %u", lexb::PAIR_XBLK_ROWS, m));
-        uint32_t max_stages = 0;
-        while (max_stages < 12 && lexb::pair_smem_bytes(max_stages + 1) <= g->smem_optin) max_stages++;
-        uint32_t stages = s.stages ? s.stages : max_stages;
-        if (stages < 2 || stages > max_stages) return bail(fail(LEXB_ERR_ARG, "stages = %u outside [2, %u]", stages, max_stages));
-        p->tm = lexb::PAIR_TOKENS; p->stages = stages; p->tmem_cols = lexb::PAIR_TMEM_COLS; p->n_acc = 1;
+        // x ring of 4 stages and W ring of 3 by default (212 KiB with the packed-weight blocks)
+        uint32_t stages = s.stages ? s.stages : 4u;
+        uint32_t w_stages = s.w_stages ? s.w_stages : 3u;
+        if (stages < 2 || w_stages < 2 || lexb::pair_smem_bytes(stages, w_stages) > g->smem_optin)
+            return bail(fail(LEXB_ERR_ARG, "stages = %u with w_stages = %u need %u bytes of shared memory (limit %zu)", stages,
+                             w_stages, lexb::pair_smem_bytes(stages, w_stages), g->smem_optin));
+        p->tm = lexb::PAIR_TOKENS; p->stages = stages; p->w_stages = w_stages;
+        p->flags = env_u32("LEXB_COLLECTOR", 0) ? 1u : 0u; p->tmem_cols = lexb::PAIR_TMEM_COLS; p->n_acc = 1;
         p->m_tiles = (m + lexb::PAIR_TOKENS - 1) / lexb::PAIR_TOKENS;
         p->grid = 2u * p->m_tiles * (n / (2u * lexb::GEMM_TN));
-        p->threads = lexb::GEMM_THREADS;
-        p->smem = lexb::pair_smem_bytes(stages);
+        p->threads = lexb::PAIR_THREADS;
+        p->smem = lexb::pair_smem_bytes(stages, w_stages);
         snprintf(p->entry, sizeof p->entry, "%s_%u_%u_%u_%u_%u_%u", stem, m, n, k, lexb::PAIR_TOKENS, 2u * lexb::GEMM_TN, lexb::GEMM_BK);
     } else {
         if (n % lexb::MV_ROWS) return bail(fail(LEXB_ERR_SHAPE, "gemm_fp4 (matvec): %u rows per block do not divide n = %u", lexb::MV_ROWS, n));
@@ -620,6 +654,31 @@ int lexb_status_word(lexb_gpu* g, uint32_t* out) {
     CUDA_TRY(cudaStreamSynchronize(g->stream));
     CUDA_TRY(cudaMemcpy(out, g->d_status, sizeof(uint32_t), cudaMemcpyDeviceToHost));
     CUDA_TRY(cudaMemset(g->d_status, 0, sizeof(uint32_t)));
+    return LEXB_OK;
+}
+
+int lexb_trace_enable(lexb_gpu* g, uint32_t max_ctas) {
+    int rc = use(g);
+    if (rc) return rc;
+    if (g->d_trace) {
+        CUDA_TRY(cudaFree(g->d_trace));
+        g->d_trace = nullptr;
+        g->trace_ctas = 0;
+    }
+    if (max_ctas) {
+        CUDA_TRY(cudaMalloc(&g->d_trace, sizeof(unsigned long long) * 16u * max_ctas));
+        CUDA_TRY(cudaMemset(g->d_trace, 0, sizeof(unsigned long long) * 16u * max_ctas));
+        g->trace_ctas = max_ctas;
+    }
+    return LEXB_OK;
+}
+
+int lexb_trace_read(lexb_gpu* g, uint64_t* out, uint32_t ctas) {
+    int rc = use(g);
+    if (rc) return rc;
+    if (!out || !g->d_trace || ctas > g->trace_ctas) return fail(LEXB_ERR_ARG, "lexb_trace_read: tracing is off or the request is too large");
+    CUDA_TRY(cudaStreamSynchronize(g->stream));
+    CUDA_TRY(cudaMemcpy(out, g->d_trace, sizeof(uint64_t) * 16u * ctas, cudaMemcpyDeviceToHost));
     return LEXB_OK;
 }
 

@@ -137,6 +137,51 @@ __device__ __forceinline__ uint64_t umma_desc_k_sw128(uint32_t smem_addr) {
     return d;
 }
 
+// The single thread that issues the MMAs shares its scheduler with decode warps, so every
+// instruction it spends between two MMAs delays the tensor pipe.  These helpers keep that count
+// small: the high half of a descriptor is constant, the low half is (address >> 4) | LBO, and
+// stepping K by 16 is +2 on the low half.
+constexpr uint32_t UMMA_DESC_HI_SW128 = (1024u >> 4) | (1u << 14) | (2u << 29);
+__device__ __forceinline__ uint32_t umma_desc_lo(uint32_t smem_addr) {
+    return ((smem_addr & 0x3FFFFu) >> 4) | (1u << 16);
+}
+#define LEXB_UMMA_ASM(GROUP, COLLECTOR, PRED_SETUP)                                                          \
+    asm volatile("{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t" PRED_SETUP                                  \
+                 "mov.b64 da, {%1, %4};\n\tmov.b64 db, {%2, %4};\n\t"                                        \
+                 "tcgen05.mma.cta_group::" GROUP ".kind::f16" COLLECTOR " [%0], da, db, %3, p;\n\t}"          \
+                 ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(idesc), "r"(UMMA_DESC_HI_SW128), "r"(accumulate)   \
+                 : "memory")
+// accumulate is a run-time flag
+__device__ __forceinline__ void umma1_flag(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t idesc, uint32_t accumulate) {
+    LEXB_UMMA_ASM("1", "", "setp.ne.b32 p, %5, 0;\n\t");
+}
+__device__ __forceinline__ void umma2_flag(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t idesc, uint32_t accumulate) {
+    LEXB_UMMA_ASM("2", "", "setp.ne.b32 p, %5, 0;\n\t");
+}
+__device__ __forceinline__ void umma2_flag_fill(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t idesc, uint32_t accumulate) {
+    LEXB_UMMA_ASM("2", ".collector::a::fill", "setp.ne.b32 p, %5, 0;\n\t");
+}
+__device__ __forceinline__ void umma2_flag_lastuse(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t idesc, uint32_t accumulate) {
+    LEXB_UMMA_ASM("2", ".collector::a::lastuse", "setp.ne.b32 p, %5, 0;\n\t");
+}
+// accumulate always
+__device__ __forceinline__ void umma1_acc(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t idesc) {
+    const uint32_t accumulate = 1;
+    LEXB_UMMA_ASM("1", "", "setp.eq.b32 p, 0, 0;\n\t");
+}
+__device__ __forceinline__ void umma2_acc(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t idesc) {
+    const uint32_t accumulate = 1;
+    LEXB_UMMA_ASM("2", "", "setp.eq.b32 p, 0, 0;\n\t");
+}
+__device__ __forceinline__ void umma2_acc_fill(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t idesc) {
+    const uint32_t accumulate = 1;
+    LEXB_UMMA_ASM("2", ".collector::a::fill", "setp.eq.b32 p, 0, 0;\n\t");
+}
+__device__ __forceinline__ void umma2_acc_lastuse(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t idesc) {
+    const uint32_t accumulate = 1;
+    LEXB_UMMA_ASM("2", ".collector::a::lastuse", "setp.eq.b32 p, 0, 0;\n\t");
+}
+
 // Instruction descriptor, kind::f16: f16 x f16 -> f32, both operands K-major, M x N tile.
 __host__ __device__ constexpr uint32_t umma_idesc_f16_f32(uint32_t M, uint32_t N) {
     return (1u << 4)              // D format f32

@@ -27,7 +27,7 @@ SYMBOLS = [
     "lexb_upload", "lexb_download", "lexb_memset", "lexb_host_alloc", "lexb_host_free", "lexb_gemm_fp4_plan",
     "lexb_pipeline_free", "lexb_pipeline_describe", "lexb_gemm_fp4_launch", "lexb_gemm_fp4_run_host",
     "lexb_run_launches", "lexb_run_each_timed", "lexb_time_launches", "lexb_status_word",
-    "lexb_selftest_bounded_wait", "lexb_dequant_fp4_f16", "lexb_shard_rows",
+    "lexb_selftest_bounded_wait", "lexb_dequant_fp4_f16", "lexb_shard_rows", "lexb_trace_enable", "lexb_trace_read",
 ]
 
 
@@ -45,7 +45,7 @@ class DeviceInfo(ctypes.Structure):
 
 
 class Sched(ctypes.Structure):
-    _fields_ = [("kernel", c_uint32), ("tm", c_uint32), ("stages", c_uint32), ("kc", c_uint32)]
+    _fields_ = [("kernel", c_uint32), ("tm", c_uint32), ("stages", c_uint32), ("kc", c_uint32), ("w_stages", c_uint32)]
 
 
 class Lowered(ctypes.Structure):
@@ -108,6 +108,8 @@ def load_library() -> ctypes.CDLL:
     L.lexb_selftest_bounded_wait.argtypes = [vp, u32]
     L.lexb_dequant_fp4_f16.argtypes = [vp, u32, u32, vp, vp, vp, vp]
     L.lexb_shard_rows.argtypes = [u32, u32, u32, POINTER(u32), POINTER(u32)]
+    L.lexb_trace_enable.argtypes = [vp, u32]
+    L.lexb_trace_read.argtypes = [vp, vp, u32]
     _lib = L
     return L
 
@@ -287,8 +289,8 @@ class Gpu:
 
     # ---- the operator
     def plan_gemm_fp4(self, m: int, n: int, k: int, residual: bool = False, kernel: int = 0, tm: int = 0,
-                      stages: int = 0, kc: int = 0) -> Pipeline:
-        s = Sched(kernel, tm, stages, kc)
+                      stages: int = 0, kc: int = 0, w_stages: int = 0) -> Pipeline:
+        s = Sched(kernel, tm, stages, kc, w_stages)
         h = c_void_p()
         _check(self._L.lexb_gemm_fp4_plan(self.handle, m, n, k, int(residual), byref(s), byref(h)))
         return Pipeline(self, h.value)
@@ -331,6 +333,15 @@ class Gpu:
         out = c_uint32()
         _check(self._L.lexb_status_word(self.handle, byref(out)))
         return out.value
+
+    def trace_enable(self, max_ctas: int) -> None:
+        _check(self._L.lexb_trace_enable(self.handle, max_ctas))
+
+    def trace_read(self, ctas: int) -> np.ndarray:
+        """uint64 [ctas, 16] phase timers of the last traced launch (see lexb_trace_enable)."""
+        out = np.zeros((ctas, 16), dtype=np.uint64)
+        _check(self._L.lexb_trace_read(self.handle, c_void_p(out.ctypes.data), ctas))
+        return out
 
     def selftest_bounded_wait(self, limit_us: int = 1000) -> None:
         _check(self._L.lexb_selftest_bounded_wait(self.handle, limit_us))

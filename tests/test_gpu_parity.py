@@ -158,7 +158,7 @@ def test_gemm_shapes(gpu, m, n, k):
     check(L.gemm_fp4(gpu, x, wq, ws, wg), O.gemm_fp4(x, wq, ws, wg), rel_tol=TOL if k < 4096 else LONG_K_REL)
 
 
-@pytest.mark.parametrize("m,n,k", [(512, 256, 64), (512, 256, 512), (300, 256, 1024), (257, 512, 320),
+@pytest.mark.parametrize("m,n,k", [(512, 256, 256), (512, 256, 512), (300, 256, 1024), (257, 512, 768),
                                    (1000, 512, 2048), (1024, 768, 1280), (128, 256, 256)])
 def test_gemm_two_cta_kernel(gpu, m, n, k):
     """The cta_group::2 kernel (pairs of CTAs, 512 tokens per tile), forced; partial token tiles,
@@ -170,12 +170,12 @@ def test_gemm_two_cta_kernel(gpu, m, n, k):
 
 
 def test_gemm_two_cta_kernel_residual_and_stages(gpu):
-    m, n, k = 640, 512, 768
+    m, n, k = 640, 512, 1792
     x, wq, ws, wg = inputs.make_case(m, n, k, seed_base=77)
     r = inputs.make_residual(m, n, seed_base=77)
     want = O.gemm_fp4(x, wq, ws, wg, r=r)
-    for stages in (2, 3, 0):
-        check(L.gemm_fp4(gpu, x, wq, ws, wg, r=r, kernel=3, stages=stages), want)
+    for stages, w_stages in ((2, 2), (3, 5), (4, 2), (0, 0)):
+        check(L.gemm_fp4(gpu, x, wq, ws, wg, r=r, kernel=3, stages=stages, w_stages=w_stages), want)
 
 
 def test_two_cta_kernel_multiplies_exactly_the_oracles_f16_weights(gpu):
@@ -274,6 +274,8 @@ def test_shapes_the_operator_rejects(gpu):
         gpu.plan_gemm_fp4(64, 128, 64, kernel=1)        # matvec kernel takes m <= 16
     with pytest.raises(L.LexbError):
         gpu.plan_gemm_fp4(64, 128, 64, tm=24)
+    with pytest.raises(L.LexbError):
+        gpu.plan_gemm_fp4(512, 256, 320, kernel=3)      # the two-CTA kernel takes k in blocks of 256
 
 
 def test_launch_validates_bindings(gpu):
@@ -292,7 +294,7 @@ def test_launch_validates_bindings(gpu):
 def test_describe_mirrors_the_lowered_descriptor(gpu):
     d = gpu.plan_gemm_fp4(512, 17408, 5120).describe()
     assert d.entry.decode() == "gemm_fp4_512_17408_5120_512_256_64"
-    assert (d.grid, d.grid2, d.threads, d.nbind) == (136, 1, 320, 5)
+    assert (d.grid, d.grid2, d.threads, d.nbind) == (136, 1, 608, 5)
     assert list(d.writes)[:5] == [0, 0, 0, 0, 1] and d.kernel == 3
     d = gpu.plan_gemm_fp4(256, 17408, 5120).describe()
     assert d.entry.decode() == "gemm_fp4_256_17408_5120_256_128_64" and d.kernel == 2 and d.grid == 136
