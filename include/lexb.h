@@ -62,6 +62,7 @@ typedef struct lexb_sched {
     uint32_t stages;  /* pipeline depth of the GEMM */
     uint32_t kc;      /* K columns of x staged per chunk in the matvec: multiple of 1024 */
     uint32_t w_stages; /* two-CTA GEMM: depth of the ring of decoded W tiles (stages = depth of the x ring) */
+    uint32_t k_splits; /* two-CTA GEMM: split K this many ways (partials in a workspace the pipeline owns, then summed) */
 } lexb_sched;
 
 /* lex_msl::program::Lowered, crates/lex-msl/src/program.rs:44-63: the launch descriptor.
@@ -76,6 +77,8 @@ typedef struct lexb_lowered {
     uint32_t kernel;             /* 1 matvec, 2 tcgen05, 3 two-CTA tcgen05 */
     uint32_t m, n, k, residual;
     uint32_t bm, bn, bk, stages;
+    uint32_t k_splits;           /* > 1: a second launch sums the partial products */
+    uint64_t scratch_bytes;      /* Lowered::scratch_bytes: the split-K workspace */
 } lexb_lowered;
 
 /* lex_cuda::Step, crates/lex-cuda/src/device.rs:314: a pipeline and its buffers in binding

@@ -48,6 +48,10 @@ struct GemmArgs {
     uint32_t m_tiles;     // ceil(m / tm)
     uint32_t x_tx_bytes;  // bytes one TMA x tile delivers: min(tm, m) rows of 128 bytes
     uint32_t flags;       // bit 0 (two-CTA kernel): reuse the W tile from the MMA's A collector buffer
+    // split-K (two-CTA kernel): split s of k_splits takes K steps [s * kb_per_split, ...) and writes its
+    // partial product to partial[s][m][n]; a reduction kernel then forms y.  k_splits = 1: y is written.
+    uint32_t k_splits, kb_per_split;
+    float* partial;
 };
 
 __host__ __device__ constexpr uint32_t gemm_stage_bytes(uint32_t tm) { return tm * 128u + GEMM_W_TILE_BYTES; }

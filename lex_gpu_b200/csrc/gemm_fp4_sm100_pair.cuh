@@ -78,10 +78,13 @@ gemm_fp4_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const _
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
     const uint32_t rank = cluster_ctarank();                 // 0 = leader
     const uint32_t pair = blockIdx.x >> 1;
-    const uint32_t m_tile = pair % a.m_tiles, n_pair = pair / a.m_tiles;
+    const uint32_t split = pair % a.k_splits, tile = pair / a.k_splits;
+    const uint32_t m_tile = tile % a.m_tiles, n_pair = tile / a.m_tiles;
     const uint32_t m0 = m_tile * PAIR_TOKENS;
-    const uint32_t n0 = n_pair * 2u * GEMM_TN + rank * GEMM_TN;
-    const uint32_t KB = a.k / GEMM_BK;
+    const uint32_t n0 = n_pair * 2u * GEMM_TN + rank * GEMM_TN;     // may be == n in the last pair: nothing to store
+    const uint32_t kb0 = split * a.kb_per_split;                    // first K step of this split (a multiple of 4)
+    const uint32_t kb_all = a.k / GEMM_BK;
+    const uint32_t KB = (kb_all - kb0 < a.kb_per_split) ? (kb_all - kb0) : a.kb_per_split;
     const long long t_start = clock64();
 
     if (tid == 0) {
@@ -131,8 +134,8 @@ gemm_fp4_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const _
                 mbar_arrive_expect_tx_cluster(lead_bar, 2u * PAIR_XBLK_BYTES);
                 const uint32_t dst = base + s * PAIR_X_STAGE_BYTES;
                 // token block tb covers tokens m0 + 256 tb .. +255; this CTA holds 128 of them
-                tma_load_2d_pair(dst, &tmap_x, (int)(kb * GEMM_BK), (int)(m0 + rank * PAIR_XBLK_ROWS), lead_bar);
-                tma_load_2d_pair(dst + PAIR_XBLK_BYTES, &tmap_x, (int)(kb * GEMM_BK),
+                tma_load_2d_pair(dst, &tmap_x, (int)((kb0 + kb) * GEMM_BK), (int)(m0 + rank * PAIR_XBLK_ROWS), lead_bar);
+                tma_load_2d_pair(dst + PAIR_XBLK_BYTES, &tmap_x, (int)((kb0 + kb) * GEMM_BK),
                                  (int)(m0 + 256u + rank * PAIR_XBLK_ROWS), lead_bar);
             }
             if (*abort_flag) {
@@ -147,7 +150,7 @@ gemm_fp4_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const _
     } else if (warp == PAIR_WARP_RAW) {
         // ---------------------------------------------------------------- TMA of packed weights (both CTAs)
         if (lane == 0) {
-            const uint32_t RB = (a.k + PAIR_RAW_K - 1u) / PAIR_RAW_K;
+            const uint32_t RB = (KB + 3u) / 4u, rb0 = kb0 / 4u;
             for (uint32_t rb = 0; rb < RB; rb++) {
                 const uint32_t rs = rb % PAIR_RAW_STAGES, ph = (rb / PAIR_RAW_STAGES) & 1u;
                 if (!mbar_wait(raw_empty(rs), ph ^ 1u, abort_flag)) {
@@ -157,8 +160,8 @@ gemm_fp4_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const _
                 }
                 mbar_arrive_expect_tx(raw_full(rs), PAIR_RAW_BYTES);
                 const uint32_t dst = raw_base + rs * PAIR_RAW_BYTES;
-                tma_load_2d(dst, &tmap_wq, (int)(rb * (PAIR_RAW_K / 2)), (int)n0, raw_full(rs));
-                tma_load_2d(dst + PAIR_RAW_WQ_BYTES, &tmap_ws, (int)(rb * (PAIR_RAW_K / 16)), (int)n0, raw_full(rs));
+                tma_load_2d(dst, &tmap_wq, (int)((rb0 + rb) * (PAIR_RAW_K / 2)), (int)n0, raw_full(rs));
+                tma_load_2d(dst + PAIR_RAW_WQ_BYTES, &tmap_ws, (int)((rb0 + rb) * (PAIR_RAW_K / 16)), (int)n0, raw_full(rs));
             }
             if (*abort_flag) {
                 const long long t0 = clock64();
@@ -266,7 +269,8 @@ gemm_fp4_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const _
         // so the 16-byte chunks any 8 consecutive lanes store fall into different bank groups.
         const uint32_t r = tid & 127u, qtr = tid >> 7;
         const uint32_t row = n0 + r;
-        const float g = __ldg(a.wg + row);
+        // rows past n (second half of an odd last pair): the copy engine fills their codes with zeros
+        const float g = row < a.n ? __ldg(a.wg + row) : 0.0f;
         const uint32_t w_off = (w_base - base) + r * 128u;
         const uint32_t sw_xor = r & 7u;
         const uint32_t c = 2u * qtr;
@@ -331,10 +335,13 @@ gemm_fp4_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const _
             a.trace[16ull * blockIdx.x + 0] = (unsigned long long)t_start;
             a.trace[16ull * blockIdx.x + 6] = (unsigned long long)clock64();   // accumulator complete
         }
-        if (go) {
+        if (go && n0 < a.n) {
             tc_fence_after_sync();
             const uint32_t quarter = warp & 3u, slice = warp >> 2;      // 4 lane quarters x 4 column slices
             const uint32_t out_row = n0 + 32u * quarter + lane;
+            const bool to_partial = a.k_splits > 1u;
+            float* const out = to_partial ? a.partial + (size_t)split * a.m * a.n : a.y;
+            const float* const res = to_partial ? nullptr : a.r;
             for (uint32_t cc = slice; cc < PAIR_TOKENS / 16u; cc += 4u) {
                 const uint32_t t0 = m0 + cc * 16u;
                 if (t0 >= a.m) break;                        // warp-uniform
@@ -347,8 +354,8 @@ gemm_fp4_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const _
                     if (t < a.m) {
                         const size_t o = (size_t)t * a.n + out_row;
                         float val = __uint_as_float(v[j]);
-                        if (a.r) val = val + __ldg(a.r + o);
-                        a.y[o] = val;
+                        if (res) val = val + __ldg(res + o);
+                        out[o] = val;
                     }
                 }
             }
@@ -362,6 +369,24 @@ gemm_fp4_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const _
     if (warp == PAIR_WARP_MMA) {
         tc_fence_after_sync();
         tmem_dealloc_pair(tmem_base, PAIR_TMEM_COLS);
+    }
+}
+
+// y = sum over splits of partial[s] (+ r), four floats per thread step; the order of the sum is fixed.
+__global__ void splitk_reduce_kernel(const float* __restrict__ partial, uint32_t splits, size_t elems,
+                                     const float* __restrict__ r, float* __restrict__ y) {
+    const size_t n4 = elems / 4;
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n4; i += (size_t)gridDim.x * blockDim.x) {
+        float4 acc = reinterpret_cast<const float4*>(partial)[i];
+        for (uint32_t s = 1; s < splits; s++) {
+            const float4 p = reinterpret_cast<const float4*>(partial + (size_t)s * elems)[i];
+            acc.x += p.x; acc.y += p.y; acc.z += p.z; acc.w += p.w;
+        }
+        if (r) {
+            const float4 q = reinterpret_cast<const float4*>(r)[i];
+            acc.x += q.x; acc.y += q.y; acc.z += q.z; acc.w += q.w;
+        }
+        reinterpret_cast<float4*>(y)[i] = acc;
     }
 }
 

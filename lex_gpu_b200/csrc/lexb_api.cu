@@ -76,6 +76,8 @@ struct lexb_pipeline {
     bool residual;
     // tcgen05 GEMM
     uint32_t tm, stages, w_stages, tmem_cols, m_tiles, n_acc, flags;
+    uint32_t k_splits = 1, kb_per_split = 0;
+    float* partial = nullptr;   // split-K workspace [k_splits][m][n], owned by the pipeline
     // matvec
     uint32_t kc;
     uint32_t grid, threads, smem;
@@ -223,15 +225,24 @@ int launch_one(lexb_gpu* g, const lexb_pipeline* p, const lexb_buffer* x, const 
         a.status = g->d_status;
         a.trace = (g->d_trace && p->kernel == KERNEL_TCGEN05_PAIR && p->grid <= g->trace_ctas) ? g->d_trace : nullptr;
         a.m = p->m; a.n = p->n; a.k = p->k;
-        a.tm = p->tm; a.stages = p->stages; a.w_stages = p->w_stages; a.flags = p->flags; a.tmem_cols = p->tmem_cols; a.m_tiles = p->m_tiles; a.n_acc = p->n_acc;
+        a.tm = p->tm; a.stages = p->stages; a.w_stages = p->w_stages; a.flags = p->flags;
+        a.k_splits = p->k_splits; a.kb_per_split = p->kb_per_split; a.partial = p->partial;
+        a.tmem_cols = p->tmem_cols; a.m_tiles = p->m_tiles; a.n_acc = p->n_acc;
         a.x_tx_bytes = (p->tm < p->m ? p->tm : p->m) * 128u;
-        if (p->kernel == KERNEL_TCGEN05_PAIR)
+        if (p->kernel == KERNEL_TCGEN05_PAIR) {
             if (a.trace)
                 lexb::gemm_fp4_tcgen05_pair_kernel<true><<<p->grid, p->threads, p->smem, g->stream>>>(maps.map, maps.map_wq, maps.map_ws, a);
             else
                 lexb::gemm_fp4_tcgen05_pair_kernel<false><<<p->grid, p->threads, p->smem, g->stream>>>(maps.map, maps.map_wq, maps.map_ws, a);
-        else
+            if (p->k_splits > 1) {
+                CUDA_TRY(cudaGetLastError());
+                const size_t elems = static_cast<size_t>(p->m) * p->n;       // n % 128 == 0: a multiple of 4
+                const uint32_t blocks = static_cast<uint32_t>(std::min<size_t>((elems / 4 + 255) / 256, 148u * 8u));
+                lexb::splitk_reduce_kernel<<<blocks, 256, 0, g->stream>>>(p->partial, p->k_splits, elems, a.r, a.y);
+            }
+        } else {
             lexb::gemm_fp4_tcgen05_kernel<<<p->grid, p->threads, p->smem, g->stream>>>(maps.map, a);
+        }
     } else {
         lexb::MatvecArgs a{};
         a.x = static_cast<const __half*>(x->ptr);
@@ -460,10 +471,11 @@ int lexb_gemm_fp4_plan(lexb_gpu* g, uint32_t m, uint32_t n, uint32_t k, int resi
     if (!s.stages) s.stages = env_u32("LEXB_STAGES", 0);
     if (!s.kc) s.kc = env_u32("LEXB_KC", 0);
     if (!s.w_stages) s.w_stages = env_u32("LEXB_WSTAGES", 0);
+    if (!s.k_splits) s.k_splits = env_u32("LEXB_KSPLITS", 0);
     // m <= 16: matvec.  m > 256 and whole 256-row pairs: the two-CTA GEMM.  Otherwise the one-CTA GEMM.
     uint32_t kernel = s.kernel ? s.kernel
                                : (m <= 16 ? KERNEL_MATVEC
-                                          : ((m > 256 && n % 256u == 0 && k % lexb::PAIR_RAW_K == 0) ? KERNEL_TCGEN05_PAIR : KERNEL_TCGEN05));
+                                          : ((m > 256 && n % lexb::GEMM_TN == 0 && k % lexb::PAIR_RAW_K == 0) ? KERNEL_TCGEN05_PAIR : KERNEL_TCGEN05));
     if (kernel == KERNEL_MATVEC && m > 16) return fail(LEXB_ERR_SHAPE, "the matvec kernel takes m <= 16, not %u", m);
     if (kernel < KERNEL_MATVEC || kernel > KERNEL_TCGEN05_PAIR) return fail(LEXB_ERR_ARG, "unknown kernel selector %u", kernel);
 
@@ -473,7 +485,7 @@ int lexb_gemm_fp4_plan(lexb_gpu* g, uint32_t m, uint32_t n, uint32_t k, int resi
     p->kernel = kernel;
     p->m = m; p->n = n; p->k = k;
     p->residual = residual != 0;
-    auto bail = [&](int code) { delete p; return code; };
+    auto bail = [&](int code) { lexb_pipeline_free(p); return code; };
     const char* stem = residual ? "gemm_fp4_res" : "gemm_fp4";
 
     if (kernel == KERNEL_TCGEN05) {
@@ -501,7 +513,7 @@ int lexb_gemm_fp4_plan(lexb_gpu* g, uint32_t m, uint32_t n, uint32_t k, int resi
         p->smem = lexb::gemm_smem_bytes(tm, stages);
         snprintf(p->entry, sizeof p->entry, "%s_%u_%u_%u_%u_%u_%u", stem, m, n, k, tm, lexb::GEMM_TN, lexb::GEMM_BK);
     } else if (kernel == KERNEL_TCGEN05_PAIR) {
-        if (n % (2u * lexb::GEMM_TN)) return bail(fail(LEXB_ERR_SHAPE, "gemm_fp4 (pair): bn = %u does not divide n = %u", 2u * lexb::GEMM_TN, n));
+        if (n % lexb::GEMM_TN) return bail(fail(LEXB_ERR_SHAPE, "gemm_fp4 (pair): %u rows per CTA do not divide n = %u", lexb::GEMM_TN, n));
         if (k % lexb::PAIR_RAW_K) return bail(fail(LEXB_ERR_SHAPE, "gemm_fp4 (pair): the packed-weight block of %u columns does not divide k = %u", lexb::PAIR_RAW_K, k));
         if (m < lexb::PAIR_XBLK_ROWS) return bail(fail(LEXB_ERR_SHAPE, "the two-CTA kernel takes m >= %u, not %u", lexb::PAIR_XBLK_ROWS, m));
         // x ring of 4 stages and W ring of 3 by default (212 KiB with the packed-weight blocks)
@@ -513,7 +525,38 @@ int lexb_gemm_fp4_plan(lexb_gpu* g, uint32_t m, uint32_t n, uint32_t k, int resi
         p->tm = lexb::PAIR_TOKENS; p->stages = stages; p->w_stages = w_stages;
         p->flags = env_u32("LEXB_COLLECTOR", 0) ? 1u : 0u; p->tmem_cols = lexb::PAIR_TMEM_COLS; p->n_acc = 1;
         p->m_tiles = (m + lexb::PAIR_TOKENS - 1) / lexb::PAIR_TOKENS;
-        p->grid = 2u * p->m_tiles * (n / (2u * lexb::GEMM_TN));
+        const uint32_t n_pairs = (n + 2u * lexb::GEMM_TN - 1) / (2u * lexb::GEMM_TN);
+        const uint32_t tiles = p->m_tiles * n_pairs;
+        // Split K when whole tiles fill the SM pairs badly (few tiles, or a short last wave).  Each
+        // split takes whole blocks of 256 columns (at least 4) and writes a partial product that a
+        // second launch sums.  Model: a K step costs about 0.9 us on a pair; the partials cost their
+        // write and read at about 4 TB/s.
+        const uint32_t sm_pairs = static_cast<uint32_t>(g->prop.multiProcessorCount) / 2u;
+        const uint32_t raw_blocks = k / lexb::PAIR_RAW_K;
+        uint32_t splits = s.k_splits ? s.k_splits : 1u;
+        if (!s.k_splits) {
+            double best = 1e30;
+            for (uint32_t c = 1; c <= 8u && raw_blocks / c >= 4u; c++) {
+                const uint32_t rbs = (raw_blocks + c - 1u) / c, eff = (raw_blocks + rbs - 1u) / rbs;
+                const double waves = static_cast<double>((tiles * eff + sm_pairs - 1u) / sm_pairs);
+                double us = waves * rbs * 4.0 * 0.9 + 12.0;
+                if (eff > 1u) us += 2.0 * eff * static_cast<double>(m) * n * 4.0 / 4e6 + 4.0;
+                if (us < best * 0.97) {      // a larger split must win clearly
+                    best = us;
+                    splits = eff;
+                }
+            }
+        }
+        if (splits < 1u || splits > raw_blocks) return bail(fail(LEXB_ERR_ARG, "k_splits = %u outside [1, %u]", splits, raw_blocks));
+        const uint32_t rb_per_split = (raw_blocks + splits - 1u) / splits;
+        splits = (raw_blocks + rb_per_split - 1u) / rb_per_split;          // no empty split
+        p->k_splits = splits;
+        p->kb_per_split = rb_per_split * (lexb::PAIR_RAW_K / lexb::GEMM_BK);
+        if (splits > 1u) {
+            cudaError_t e = cudaMalloc(&p->partial, sizeof(float) * splits * static_cast<size_t>(m) * n);
+            if (e != cudaSuccess) return bail(fail(LEXB_ERR_CUDA, "allocating the split-K workspace: %s", cudaGetErrorString(e)));
+        }
+        p->grid = 2u * tiles * splits;
         p->threads = lexb::PAIR_THREADS;
         p->smem = lexb::pair_smem_bytes(stages, w_stages);
         snprintf(p->entry, sizeof p->entry, "%s_%u_%u_%u_%u_%u_%u", stem, m, n, k, lexb::PAIR_TOKENS, 2u * lexb::GEMM_TN, lexb::GEMM_BK);
@@ -540,7 +583,14 @@ int lexb_gemm_fp4_plan(lexb_gpu* g, uint32_t m, uint32_t n, uint32_t k, int resi
     return LEXB_OK;
 }
 
-void lexb_pipeline_free(lexb_pipeline* p) { delete p; }
+void lexb_pipeline_free(lexb_pipeline* p) {
+    if (!p) return;
+    if (p->partial) {
+        cudaSetDevice(p->gpu->device);
+        cudaFree(p->partial);
+    }
+    delete p;
+}
 
 int lexb_pipeline_describe(const lexb_pipeline* p, lexb_lowered* out) {
     if (!p || !out) return fail(LEXB_ERR_ARG, "lexb_pipeline_describe: null argument");
@@ -557,6 +607,8 @@ int lexb_pipeline_describe(const lexb_pipeline* p, lexb_lowered* out) {
     if (p->kernel == KERNEL_TCGEN05 || p->kernel == KERNEL_TCGEN05_PAIR) {
         out->bm = p->tm; out->bn = p->kernel == KERNEL_TCGEN05_PAIR ? 2u * lexb::GEMM_TN : lexb::GEMM_TN;
         out->bk = lexb::GEMM_BK; out->stages = p->stages;
+        out->k_splits = p->k_splits;
+        out->scratch_bytes = p->partial ? sizeof(float) * p->k_splits * static_cast<uint64_t>(p->m) * p->n : 0;
     } else {
         out->bm = p->m; out->bn = lexb::MV_ROWS; out->bk = lexb::MV_SLICE; out->stages = 1;
     }

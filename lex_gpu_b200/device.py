@@ -45,14 +45,15 @@ class DeviceInfo(ctypes.Structure):
 
 
 class Sched(ctypes.Structure):
-    _fields_ = [("kernel", c_uint32), ("tm", c_uint32), ("stages", c_uint32), ("kc", c_uint32), ("w_stages", c_uint32)]
+    _fields_ = [("kernel", c_uint32), ("tm", c_uint32), ("stages", c_uint32), ("kc", c_uint32), ("w_stages", c_uint32), ("k_splits", c_uint32)]
 
 
 class Lowered(ctypes.Structure):
     _fields_ = [("entry", c_char * 96), ("grid", c_uint32), ("grid2", c_uint32), ("threads", c_uint32),
                 ("threadgroup_bytes", c_uint32), ("nbind", c_uint32), ("writes", c_uint8 * 6), ("kernel", c_uint32),
                 ("m", c_uint32), ("n", c_uint32), ("k", c_uint32), ("residual", c_uint32),
-                ("bm", c_uint32), ("bn", c_uint32), ("bk", c_uint32), ("stages", c_uint32)]
+                ("bm", c_uint32), ("bn", c_uint32), ("bk", c_uint32), ("stages", c_uint32),
+                ("k_splits", c_uint32), ("scratch_bytes", c_uint64)]
 
 
 class StepStruct(ctypes.Structure):
@@ -289,8 +290,8 @@ class Gpu:
 
     # ---- the operator
     def plan_gemm_fp4(self, m: int, n: int, k: int, residual: bool = False, kernel: int = 0, tm: int = 0,
-                      stages: int = 0, kc: int = 0, w_stages: int = 0) -> Pipeline:
-        s = Sched(kernel, tm, stages, kc, w_stages)
+                      stages: int = 0, kc: int = 0, w_stages: int = 0, k_splits: int = 0) -> Pipeline:
+        s = Sched(kernel, tm, stages, kc, w_stages, k_splits)
         h = c_void_p()
         _check(self._L.lexb_gemm_fp4_plan(self.handle, m, n, k, int(residual), byref(s), byref(h)))
         return Pipeline(self, h.value)

@@ -178,6 +178,25 @@ def test_gemm_two_cta_kernel_residual_and_stages(gpu):
         check(L.gemm_fp4(gpu, x, wq, ws, wg, r=r, kernel=3, stages=stages, w_stages=w_stages), want)
 
 
+@pytest.mark.parametrize("m,n,k,splits", [(512, 256, 2048, 2), (600, 384, 4096, 4), (512, 384, 512, 1),
+                                          (300, 128, 1024, 3), (512, 640, 2304, 5)])
+def test_gemm_two_cta_split_k_and_odd_last_pair(gpu, m, n, k, splits):
+    """K split across CTA pairs (partials in the pipeline's workspace, summed by a second launch),
+    n an odd number of 128-row tiles (the last pair has one idle half), with and without r."""
+    x, wq, ws, wg = inputs.make_case(m, n, k, seed_base=n + k)
+    r = inputs.make_residual(m, n, seed_base=5)
+    rel = TOL if k < 4096 else LONG_K_REL
+    check(L.gemm_fp4(gpu, x, wq, ws, wg, kernel=3, k_splits=splits), O.gemm_fp4(x, wq, ws, wg), rel_tol=rel)
+    check(L.gemm_fp4(gpu, x, wq, ws, wg, r=r, kernel=3, k_splits=splits), O.gemm_fp4(x, wq, ws, wg, r=r), rel_tol=rel)
+
+
+def test_split_k_is_chosen_for_few_tiles(gpu):
+    d = gpu.plan_gemm_fp4(512, 5120, 17408).describe()          # 20 pairs on 74 SM pairs
+    assert d.kernel == 3 and d.k_splits == 3 and d.scratch_bytes == 3 * 512 * 5120 * 4 and d.grid == 120
+    d = gpu.plan_gemm_fp4(512, 17408, 5120).describe()
+    assert d.k_splits == 1 and d.scratch_bytes == 0
+
+
 def test_two_cta_kernel_multiplies_exactly_the_oracles_f16_weights(gpu):
     n, k = 512, 512
     wq, ws, wg = inputs.make_weights(n, k, seed_base=92)
@@ -256,10 +275,10 @@ def test_gemm_m2048_linearity_and_slices(gpu):
     property that the result for a sub-batch equals the same rows of the full batch."""
     n, k = 5120, 17408
     x, wq, ws, wg = inputs.make_case(2048, n, k, seed_base=3)
-    got = L.gemm_fp4(gpu, x, wq, ws, wg)
+    got = L.gemm_fp4(gpu, x, wq, ws, wg, k_splits=1)
     want = O.gemm_fp4(x, wq, ws, wg, rows=(1024, 1280))
     check(got[:, 1024:1280], want[:, 1024:1280], rel_tol=LONG_K_REL)
-    sub = L.gemm_fp4(gpu, x[512:1024].copy(), wq, ws, wg)
+    sub = L.gemm_fp4(gpu, x[512:1024].copy(), wq, ws, wg, k_splits=1)      # same K order as the full batch
     assert np.array_equal(sub, got[512:1024])
 
 
