@@ -178,6 +178,27 @@ LEXB_API int lexb_trace_read(lexb_gpu* gpu, uint64_t* out, uint32_t ctas);
 LEXB_API int lexb_dequant_fp4_f16(lexb_gpu* gpu, uint32_t n, uint32_t k, const lexb_buffer* wq,
                                   const lexb_buffer* ws, const lexb_buffer* wg, lexb_buffer* w_f16);
 
+/* No counterpart in the reference.  The split-K form of the two-CTA GEMM for callers that must not
+ * allocate device memory once they are running: a runtime that handed the whole device to its own
+ * pool at start-up (lex-rt sizes its caches off total device memory, crates/lex-cuda/src/device.rs:449-456),
+ * so that a later cudaMalloc for a workspace can fail, or a decode loop that cannot afford the
+ * device-wide synchronisation an allocation implies.  lexb_gemm_fp4_plan allocates the split-K
+ * workspace; this call instead keeps the partial products in a 32 MiB array that is part of the
+ * library image (LEXB_STATIC_SCRATCH_BYTES; every GPU that loads the library holds it until exit), and
+ * calls no cudaMalloc / cudaFree or other allocating routine.  It plans and launches in one call:
+ * y = x . W^T (+ r) with K split `k_splits` ways (2..8, whole blocks of 256 columns), m >= 128,
+ * n % 128 == 0, k % 256 == 0.  Shapes whose partials (splits * m * n * 4 bytes) exceed the array are
+ * refused with LEXB_ERR_UNSUPPORTED and a message that says so.
+ * The first call on a device resolves the array's device address (cudaGetSymbolAddress); make that
+ * first call before any stream capture.  All calls on a device share the array, which keeps the last
+ * call's partials: nothing needs clearing (every partial is written before it is read), but two
+ * calls that overlap on the GPU - different streams, or different gpu handles of one device - race.
+ * Results are bit-identical to a pipeline planned with the same k_splits. */
+#define LEXB_STATIC_SCRATCH_BYTES (32ull << 20)
+LEXB_API int lexb_gemm_fp4_splitk_static(lexb_gpu* gpu, uint32_t m, uint32_t n, uint32_t k, uint32_t k_splits,
+                                         const lexb_buffer* x, const lexb_buffer* wq, const lexb_buffer* ws,
+                                         const lexb_buffer* wg, const lexb_buffer* r_or_null, lexb_buffer* y);
+
 /* Column-parallel sharding over `world` devices (new: the reference is single-GPU,
  * crates/lex-cuda/src/device.rs:358-359).  Rank `rank` owns weight rows [*n0, *n1) - whole
  * 128-row tiles, the remainder spread over the first ranks - of wq, ws and wg, and writes the

@@ -21,6 +21,10 @@
 #include "gemm_fp4_sm100_pair.cuh"
 #include "matvec_fp4_sm100.cuh"
 
+// Scratch of lexb_gemm_fp4_splitk_static: split-K partial products [splits][m][n] f32.  Part of
+// the library image, so every GPU that loads the library holds these 32 MiB until the process exits.
+static __device__ __align__(256) float g_splitk_static_scratch[LEXB_STATIC_SCRATCH_BYTES / sizeof(float)];
+
 namespace {
 
 thread_local std::string g_last_error;
@@ -55,6 +59,7 @@ struct lexb_gpu {
     cudaStream_t own_stream = nullptr;
     cudaStream_t stream = nullptr;       // own_stream or the caller's
     uint32_t* d_status = nullptr;
+    float* static_scratch = nullptr;         // device address of g_splitk_static_scratch on this device, once resolved
     unsigned long long* d_trace = nullptr;   // phase timers of the last two-CTA launch, when tracing is on
     size_t trace_ctas = 0;
     cudaDeviceProp prop{};
@@ -762,6 +767,87 @@ int lexb_dequant_fp4_f16(lexb_gpu* g, uint32_t n, uint32_t k, const lexb_buffer*
                                                               static_cast<const uint8_t*>(ws->ptr),
                                                               static_cast<const float*>(wg->ptr),
                                                               static_cast<uint16_t*>(w_f16->ptr));
+    CUDA_TRY(cudaGetLastError());
+    return LEXB_OK;
+}
+
+int lexb_gemm_fp4_splitk_static(lexb_gpu* g, uint32_t m, uint32_t n, uint32_t k, uint32_t k_splits, const lexb_buffer* x,
+                                const lexb_buffer* wq, const lexb_buffer* ws, const lexb_buffer* wg, const lexb_buffer* r,
+                                lexb_buffer* y) {
+    int rc = use(g);
+    if (rc) return rc;
+    if (m < lexb::PAIR_XBLK_ROWS || n == 0 || n % lexb::GEMM_TN || k == 0 || k % lexb::PAIR_RAW_K)
+        return fail(LEXB_ERR_SHAPE, "gemm_fp4 (static scratch): needs m >= %u, n %% %u == 0, k %% %u == 0; got m=%u n=%u k=%u",
+                    lexb::PAIR_XBLK_ROWS, lexb::GEMM_TN, lexb::PAIR_RAW_K, m, n, k);
+    const uint32_t raw_blocks = k / lexb::PAIR_RAW_K;
+    if (k_splits < 2u || k_splits > 8u || k_splits > raw_blocks)
+        return fail(LEXB_ERR_ARG, "k_splits = %u outside [2, %u]", k_splits, raw_blocks < 8u ? raw_blocks : 8u);
+    const uint32_t rb_per_split = (raw_blocks + k_splits - 1u) / k_splits;
+    const uint32_t splits = (raw_blocks + rb_per_split - 1u) / rb_per_split;
+    const uint64_t need = sizeof(float) * static_cast<uint64_t>(splits) * m * n;
+    if (need > LEXB_STATIC_SCRATCH_BYTES)
+        return fail(LEXB_ERR_UNSUPPORTED,
+                    "gemm_fp4 (static scratch): %u splits of m=%u n=%u need %llu bytes of scratch, the built-in array holds %llu; "
+                    "use fewer splits or a planned pipeline",
+                    splits, m, n, (unsigned long long)need, (unsigned long long)LEXB_STATIC_SCRATCH_BYTES);
+    if (!g->static_scratch) {
+        // Once per device, with that device current (use() above): the symbol's name is a host-side
+        // stand-in, the kernels need its device address.
+        void* p = nullptr;
+        CUDA_TRY(cudaGetSymbolAddress(&p, g_splitk_static_scratch));
+        g->static_scratch = static_cast<float*>(p);
+    }
+    // The same launch shape lexb_gemm_fp4_plan builds for the two-CTA kernel, held on the stack.
+    lexb_pipeline p;
+    p.gpu = g;
+    p.kernel = KERNEL_TCGEN05_PAIR;
+    p.m = m; p.n = n; p.k = k;
+    p.residual = r != nullptr;
+    p.tm = lexb::PAIR_TOKENS; p.stages = 4; p.w_stages = 3; p.tmem_cols = lexb::PAIR_TMEM_COLS; p.n_acc = 1; p.flags = 0;
+    p.kc = 0;
+    p.m_tiles = (m + lexb::PAIR_TOKENS - 1) / lexb::PAIR_TOKENS;
+    p.k_splits = splits;
+    p.kb_per_split = rb_per_split * (lexb::PAIR_RAW_K / lexb::GEMM_BK);
+    p.grid = 2u * p.m_tiles * ((n + 2u * lexb::GEMM_TN - 1) / (2u * lexb::GEMM_TN)) * splits;
+    p.threads = lexb::PAIR_THREADS;
+    p.smem = lexb::pair_smem_bytes(p.stages, p.w_stages);
+    if (p.smem > g->smem_optin) return fail(LEXB_ERR_UNSUPPORTED, "the device offers %zu bytes of shared memory, the kernel needs %u", g->smem_optin, p.smem);
+    const size_t mm = m, nn = n, kk = k;
+    if ((rc = check_buf(x, g, mm * kk * 2, "x"))) return rc;
+    if ((rc = check_buf(wq, g, nn * kk / 2, "wq"))) return rc;
+    if ((rc = check_buf(ws, g, nn * kk / 16, "ws"))) return rc;
+    if ((rc = check_buf(wg, g, nn * 4, "wg"))) return rc;
+    if ((rc = check_buf(y, g, mm * nn * 4, "y"))) return rc;
+    if (r && (rc = check_buf(r, g, mm * nn * 4, "r"))) return rc;
+    CUtensorMap map_x, map_wq, map_ws;      // encoded on the host for this call, not cached
+    if ((rc = encode_2d(&p, &map_x, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, x->ptr, k, m, lexb::GEMM_BK, lexb::PAIR_XBLK_ROWS,
+                        CU_TENSOR_MAP_SWIZZLE_128B, "x")))
+        return rc;
+    if ((rc = encode_2d(&p, &map_wq, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, wq->ptr, k / 2, n, lexb::PAIR_RAW_K / 2, lexb::GEMM_TN,
+                        CU_TENSOR_MAP_SWIZZLE_128B, "wq")))
+        return rc;
+    if ((rc = encode_2d(&p, &map_ws, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, ws->ptr, k / 16, n, lexb::PAIR_RAW_K / 16, lexb::GEMM_TN,
+                        CU_TENSOR_MAP_SWIZZLE_NONE, "ws")))
+        return rc;
+    lexb::GemmArgs a{};
+    a.wq = static_cast<const uint8_t*>(wq->ptr);
+    a.ws = static_cast<const uint8_t*>(ws->ptr);
+    a.wg = static_cast<const float*>(wg->ptr);
+    a.r = r ? static_cast<const float*>(r->ptr) : nullptr;
+    a.y = static_cast<float*>(y->ptr);
+    a.status = g->d_status;
+    a.trace = nullptr;
+    a.m = m; a.n = n; a.k = k;
+    a.tm = p.tm; a.stages = p.stages; a.w_stages = p.w_stages; a.flags = 0;
+    a.k_splits = splits; a.kb_per_split = p.kb_per_split;
+    a.partial = g->static_scratch;          // every element of the partials is written before it is read: nothing to clear
+    a.tmem_cols = p.tmem_cols; a.m_tiles = p.m_tiles; a.n_acc = 1;
+    a.x_tx_bytes = 0;
+    lexb::gemm_fp4_tcgen05_pair_kernel<false><<<p.grid, p.threads, p.smem, g->stream>>>(map_x, map_wq, map_ws, a);
+    CUDA_TRY(cudaGetLastError());
+    const size_t elems = mm * nn;
+    const uint32_t blocks = static_cast<uint32_t>(std::min<size_t>((elems / 4 + 255) / 256, 148u * 8u));
+    lexb::splitk_reduce_kernel<<<blocks, 256, 0, g->stream>>>(g->static_scratch, splits, elems, a.r, a.y);
     CUDA_TRY(cudaGetLastError());
     return LEXB_OK;
 }

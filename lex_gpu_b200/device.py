@@ -28,6 +28,7 @@ SYMBOLS = [
     "lexb_pipeline_free", "lexb_pipeline_describe", "lexb_gemm_fp4_launch", "lexb_gemm_fp4_run_host",
     "lexb_run_launches", "lexb_run_each_timed", "lexb_time_launches", "lexb_status_word",
     "lexb_selftest_bounded_wait", "lexb_dequant_fp4_f16", "lexb_shard_rows", "lexb_trace_enable", "lexb_trace_read",
+    "lexb_gemm_fp4_splitk_static",
 ]
 
 
@@ -110,6 +111,7 @@ def load_library() -> ctypes.CDLL:
     L.lexb_dequant_fp4_f16.argtypes = [vp, u32, u32, vp, vp, vp, vp]
     L.lexb_shard_rows.argtypes = [u32, u32, u32, POINTER(u32), POINTER(u32)]
     L.lexb_trace_enable.argtypes = [vp, u32]
+    L.lexb_gemm_fp4_splitk_static.argtypes = [vp, u32, u32, u32, u32, vp, vp, vp, vp, vp, vp]
     L.lexb_trace_read.argtypes = [vp, vp, u32]
     _lib = L
     return L
@@ -334,6 +336,16 @@ class Gpu:
         out = c_uint32()
         _check(self._L.lexb_status_word(self.handle, byref(out)))
         return out.value
+
+    def gemm_fp4_splitk_static(self, m: int, n: int, k: int, k_splits: int, bufs: Sequence[Buffer]) -> None:
+        """Split-K GEMM whose workspace is the library's built-in array: allocates nothing.
+        bufs = [x, wq, ws, wg, (r), y]; asynchronous on the gpu's stream."""
+        if len(bufs) not in (5, 6):
+            raise LexbError(1, f"gemm_fp4 binds 5 or 6 buffers, not {len(bufs)}")
+        x, wq, ws, wg = bufs[:4]
+        r, y = (bufs[4], bufs[5]) if len(bufs) == 6 else (None, bufs[4])
+        _check(self._L.lexb_gemm_fp4_splitk_static(self.handle, m, n, k, k_splits, x.handle, wq.handle, ws.handle,
+                                                   wg.handle, r.handle if r is not None else None, y.handle))
 
     def trace_enable(self, max_ctas: int) -> None:
         _check(self._L.lexb_trace_enable(self.handle, max_ctas))
