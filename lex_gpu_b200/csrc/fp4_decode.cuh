@@ -24,16 +24,15 @@
 
 namespace lexb {
 
-// OCP e4m3fn byte -> f32, exact for all 256 bytes (subnormals included); the two
-// bytes with exponent 15 and mantissa 7 are NaN (interp.rs:41-42).
-__device__ __forceinline__ float e4m3_to_f32(uint32_t b) {
-    // (b & 0x7f) << 20 is an f32 whose exponent field is the E4M3 exponent and whose top
-    // mantissa bits are the E4M3 mantissa; 2^120 rebiases it (127 - 7).  An E4M3
-    // subnormal becomes an f32 subnormal here and the multiply normalises it exactly.
-    float v = __uint_as_float((b & 0x7Fu) << 20) * __uint_as_float(0x7B800000u);   // 2^120
-    if ((b & 0x7Fu) == 0x7Fu) v = __uint_as_float(0x7FC00000u);
-    return (b & 0x80u) ? -v : v;
+// Two OCP e4m3fn bytes -> two f32, exact for all 256 byte values: the hardware conversion to f16 is
+// exact (every E4M3 value, subnormals included, is an f16 value) and maps the two NaN bytes
+// (exponent 15, mantissa 7; interp.rs:41-42) to NaN; f16 -> f32 is exact as well.
+__device__ __forceinline__ float2 e4m3x2_to_f32(uint32_t two_bytes) {
+    uint32_t h2;
+    asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(h2) : "h"(static_cast<unsigned short>(two_bytes)));
+    return __half22float2(*reinterpret_cast<const __half2*>(&h2));
 }
+__device__ __forceinline__ float e4m3_to_f32(uint32_t b) { return e4m3x2_to_f32(b & 0xFFu).x; }
 
 __device__ __forceinline__ uint32_t pack_f16x2_rn(float lo, float hi) {
     uint32_t r;
@@ -53,8 +52,7 @@ struct GroupTable {
     uint32_t lo0, lo1, hi0, hi1;
 };
 
-__device__ __forceinline__ GroupTable make_group_table(uint32_t scale_byte, float wg) {
-    const float s = e4m3_to_f32(scale_byte);
+__device__ __forceinline__ GroupTable make_group_table_f32(float s, float wg) {
     // (e2m1 * s) is exact; __fmul_rn keeps the compiler from reassociating or contracting.
     const float p0 = __fmul_rn(__fmul_rn(0.0f, s), wg);
     const float p1 = __fmul_rn(__fmul_rn(0.5f, s), wg);
@@ -74,6 +72,10 @@ __device__ __forceinline__ GroupTable make_group_table(uint32_t scale_byte, floa
     t.hi0 = prmt(h01, h23, 0x7531u);
     t.hi1 = prmt(h45, h67, 0x7531u);
     return t;
+}
+
+__device__ __forceinline__ GroupTable make_group_table(uint32_t scale_byte, float wg) {
+    return make_group_table_f32(e4m3_to_f32(scale_byte), wg);
 }
 
 // Eight codes (one 32-bit word of wq: code j in bits 4j..4j+3, i.e. column order) ->

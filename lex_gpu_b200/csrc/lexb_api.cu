@@ -570,18 +570,30 @@ int lexb_gemm_fp4_plan(lexb_gpu* g, uint32_t m, uint32_t n, uint32_t k, int resi
         if (k % 32u) return bail(fail(LEXB_ERR_SHAPE, "gemm_fp4 (matvec): 32 does not divide k = %u", k));
         uint32_t kc = s.kc;
         if (!kc) {
-            // the whole of K if x fits in 64 KiB of shared memory, else the largest multiple
-            // of one CTA round (1024 columns) that does
-            const uint32_t budget = 65536u;
+            // the whole of K if x fits in 96 KiB of shared memory (blocks are then persistent and
+            // stage x once), else the largest multiple of one block round (1024 columns) that does
+            const uint32_t budget = 98304u;
             kc = round_up(k, lexb::MV_ROUND);
-            while (kc > lexb::MV_ROUND && m * (2u * kc + 8u) > budget) kc -= lexb::MV_ROUND;
+            while (kc > lexb::MV_ROUND && m * lexb::matvec_x_pitch(kc) > budget) kc -= lexb::MV_ROUND;
         }
         if (kc % lexb::MV_ROUND || kc == 0) return bail(fail(LEXB_ERR_ARG, "kc = %u is not a multiple of %u", kc, lexb::MV_ROUND));
         p->kc = kc;
-        p->grid = n / lexb::MV_ROWS;
         p->threads = lexb::MV_THREADS;
         p->smem = lexb::matvec_smem_bytes(m, kc);
         if (p->smem > g->smem_optin) return bail(fail(LEXB_ERR_UNSUPPORTED, "kc = %u needs %u bytes of shared memory", kc, p->smem));
+        const uint32_t row_blocks = n / lexb::MV_ROWS;
+        if (kc >= k) {
+            // persistent: as many blocks as stay resident (4 per SM by registers), each with the same
+            // number of row blocks
+            uint32_t per_sm = static_cast<uint32_t>(g->smem_optin / (p->smem + 1024u));
+            if (per_sm > 4u) per_sm = 4u;
+            if (per_sm < 1u) per_sm = 1u;
+            const uint32_t max_blocks = per_sm * static_cast<uint32_t>(g->prop.multiProcessorCount);
+            const uint32_t per_block = (row_blocks + max_blocks - 1u) / max_blocks;
+            p->grid = (row_blocks + per_block - 1u) / per_block;
+        } else {
+            p->grid = row_blocks;
+        }
         snprintf(p->entry, sizeof p->entry, "%s_%u_%u_%u_%u_%u_%u", stem, m, n, k, m, lexb::MV_ROWS, lexb::MV_SLICE);
     }
     *out = p;
