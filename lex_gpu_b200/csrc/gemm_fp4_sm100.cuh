@@ -51,6 +51,8 @@ struct GemmArgs {
     // split-K (two-CTA kernel): split s of k_splits takes K steps [s * kb_per_split, ...) and writes its
     // partial product to partial[s][m][n]; a reduction kernel then forms y.  k_splits = 1: y is written.
     uint32_t k_splits, kb_per_split;
+    uint32_t tok_blocks;  // two-CTA kernel: 256-token blocks per tile, 2 (m > 256) or 1; with 1, TMEM holds two
+                          // accumulators that take even and odd K steps
     float* partial;
 };
 
@@ -87,7 +89,7 @@ gemm_fp4_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmAr
         *abort_flag = 0;
         for (uint32_t s = 0; s < S; s++) {
             mbar_init(x_full(s), 1);
-            mbar_init(w_full(s), GEMM_DEQ_THREADS);
+            mbar_init(w_full(s), GEMM_DEQ_THREADS / 32u);   // one arrival per dequant warp
             mbar_init(empty(s), 1);
         }
         mbar_init(acc_full, 1);
@@ -137,19 +139,20 @@ gemm_fp4_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmAr
         __syncwarp();
     } else if (warp == GEMM_WARP_MMA) {
         // ---------------------------------------------------------------- MMA issuer
-        if (lane == 0) {
+        // The whole warp runs the loop with warp-uniform values; one elected lane issues.
+        {
             const uint32_t idesc = umma_idesc_f16_f32(GEMM_TN, a.tm);
             const uint32_t x_lo0 = umma_desc_lo(base), stage16 = stage_bytes >> 4, w_off16 = x_bytes >> 4;
             bool ok = true;
-            for (uint32_t kb = 0; kb < KB && ok; kb++) {
+            for (uint32_t kb = 0; kb < KB; kb++) {
                 const uint32_t s = kb % S, ph = (kb / S) & 1u;
-                if (!mbar_wait(x_full(s), ph, abort_flag)) {
+                if (!__all_sync(0xFFFFFFFFu, mbar_wait(x_full(s), ph, abort_flag))) {
                     atomicOr(a.status, ST_WAIT_X_FULL);
                     *abort_flag = 1;
                     ok = false;
                     break;
                 }
-                if (!mbar_wait(w_full(s), ph, abort_flag)) {
+                if (!__all_sync(0xFFFFFFFFu, mbar_wait(w_full(s), ph, abort_flag))) {
                     atomicOr(a.status, ST_WAIT_W_FULL);
                     *abort_flag = 1;
                     ok = false;
@@ -160,12 +163,15 @@ gemm_fp4_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmAr
                 // Two accumulators halve the run of truncating f32 additions each one sees (the
                 // tensor core does not round to nearest when it accumulates).
                 const uint32_t d = tmem_base + (kb % a.n_acc) * a.tm;
-                umma1_flag(d, a_lo, b_lo, idesc, kb >= a.n_acc);
+                if (elect_one()) {
+                    umma1_flag(d, a_lo, b_lo, idesc, kb >= a.n_acc);
 #pragma unroll
-                for (uint32_t kk = 1; kk < GEMM_BK / 16; kk++) umma1_acc(d, a_lo + 2u * kk, b_lo + 2u * kk, idesc);
-                umma_commit(empty(s));      // frees the stage once these MMAs have read it
+                    for (uint32_t kk = 1; kk < GEMM_BK / 16; kk++) umma1_acc(d, a_lo + 2u * kk, b_lo + 2u * kk, idesc);
+                    umma_commit(empty(s));      // frees the stage once these MMAs have read it
+                }
+                __syncwarp();
             }
-            if (ok) umma_commit(acc_full);  // accumulator complete
+            if (ok && elect_one()) umma_commit(acc_full);  // accumulator complete
         }
         __syncwarp();
     } else {
@@ -196,7 +202,7 @@ gemm_fp4_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmAr
             uint4 o0, o1, o2, o3;
             decode_group16(make_uint2(q.x, q.y), sw & 0xFFu, g, o0, o1);
             decode_group16(make_uint2(q.z, q.w), (sw >> 8) & 0xFFu, g, o2, o3);
-            if (!mbar_wait(empty(s), ph ^ 1u, abort_flag)) {
+            if (!__all_sync(0xFFFFFFFFu, mbar_wait(empty(s), ph ^ 1u, abort_flag))) {   // warp-uniform give-up
                 atomicOr(a.status, ST_WAIT_EMPTY_DEQ);
                 *abort_flag = 1;
                 ok = false;
@@ -209,7 +215,8 @@ gemm_fp4_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmAr
             *reinterpret_cast<uint4*>(wt + (((c + 2u) ^ sw_xor) << 4)) = o2;
             *reinterpret_cast<uint4*>(wt + (((c + 3u) ^ sw_xor) << 4)) = o3;
             fence_proxy_async_smem();       // make the generic-proxy stores visible to the MMA
-            mbar_arrive(w_full(s));
+            __syncwarp();                   // one arrival per warp: arrivals on one barrier serialise
+            if (lane == 0) mbar_arrive(w_full(s));
         }
         __syncwarp();
         // ---------------------------------------------------------------- epilogue

@@ -80,7 +80,8 @@ gemm_fp4_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const _
     const uint32_t pair = blockIdx.x >> 1;
     const uint32_t split = pair % a.k_splits, tile = pair / a.k_splits;
     const uint32_t m_tile = tile % a.m_tiles, n_pair = tile / a.m_tiles;
-    const uint32_t m0 = m_tile * PAIR_TOKENS;
+    const uint32_t TB = a.tok_blocks;                              // 1 or 2 blocks of 256 tokens per tile
+    const uint32_t m0 = m_tile * TB * 256u;
     const uint32_t n0 = n_pair * 2u * GEMM_TN + rank * GEMM_TN;     // may be == n in the last pair: nothing to store
     const uint32_t kb0 = split * a.kb_per_split;                    // first K step of this split (a multiple of 4)
     const uint32_t kb_all = a.k / GEMM_BK;
@@ -94,13 +95,13 @@ gemm_fp4_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const _
             mbar_init(x_empty(s), 1);
         }
         for (uint32_t s = 0; s < SW; s++) {
-            mbar_init(w_full(s), PAIR_DEQ_THREADS);          // every dequant thread of this CTA
+            mbar_init(w_full(s), PAIR_DEQ_THREADS / 32u);    // one arrival per dequant warp of this CTA
             mbar_init(w_peer(s), 1);                         // the partner's relay thread
             mbar_init(w_empty(s), 1);
         }
         for (uint32_t rs = 0; rs < PAIR_RAW_STAGES; rs++) {
             mbar_init(raw_full(rs), 1);
-            mbar_init(raw_empty(rs), PAIR_DEQ_THREADS);
+            mbar_init(raw_empty(rs), PAIR_DEQ_THREADS / 32u);
         }
         mbar_init(acc_full, 1);
         fence_mbar_init();
@@ -131,12 +132,13 @@ gemm_fp4_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const _
                     break;
                 }
                 const uint32_t lead_bar = map_to_cta(x_full(s), 0);
-                mbar_arrive_expect_tx_cluster(lead_bar, 2u * PAIR_XBLK_BYTES);
+                mbar_arrive_expect_tx_cluster(lead_bar, TB * a.x_tx_bytes);
                 const uint32_t dst = base + s * PAIR_X_STAGE_BYTES;
                 // token block tb covers tokens m0 + 256 tb .. +255; this CTA holds 128 of them
                 tma_load_2d_pair(dst, &tmap_x, (int)((kb0 + kb) * GEMM_BK), (int)(m0 + rank * PAIR_XBLK_ROWS), lead_bar);
-                tma_load_2d_pair(dst + PAIR_XBLK_BYTES, &tmap_x, (int)((kb0 + kb) * GEMM_BK),
-                                 (int)(m0 + 256u + rank * PAIR_XBLK_ROWS), lead_bar);
+                if (TB > 1u)
+                    tma_load_2d_pair(dst + PAIR_XBLK_BYTES, &tmap_x, (int)((kb0 + kb) * GEMM_BK),
+                                     (int)(m0 + 256u + rank * PAIR_XBLK_ROWS), lead_bar);
             }
             if (*abort_flag) {
                 // The byte counts of this CTA's copies are kept by the leader's barriers, which
@@ -186,33 +188,34 @@ gemm_fp4_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const _
             }
         }
         // ---------------------------------------------------------------- MMA issuer (leader only)
-        if (rank == 0 && lane == 0) {
+        // The whole warp runs the loop with warp-uniform values; one elected lane issues.
+        if (rank == 0) {
             const uint32_t idesc = umma_idesc_f16_f32(256u, 256u);
             const uint32_t x_lo0 = umma_desc_lo(base), w_lo0 = umma_desc_lo(w_base);
             const uint32_t d0 = tmem_base, d1 = tmem_base + 256u;
             const bool reuse_a = (a.flags & 1u) != 0u;
             bool ok = true;
-            long long wait_x = 0, wait_w = 0, wait_p = 0, t_first = 0;
+            long long wait_x = 0, wait_w = 0, wait_p = 0, t_first = 0, t_issue = 0, t_commit = 0;
             for (uint32_t kb = 0; kb < KB; kb++) {
                 const uint32_t s = kb % SX, ph = (kb / SX) & 1u;
                 const uint32_t sw = kb % SW, phw = (kb / SW) & 1u;
                 long long tw0 = 0, tw1 = 0, tw2 = 0;
                 if (TRACE) tw0 = clock64();
-                if (!mbar_wait_cluster(x_full(s), ph, abort_flag)) {
+                if (!__all_sync(0xFFFFFFFFu, mbar_wait_cluster(x_full(s), ph, abort_flag))) {
                     atomicOr(a.status, ST_WAIT_X_FULL);
                     *abort_flag = 1;
                     ok = false;
                     break;
                 }
                 if (TRACE) tw1 = clock64();
-                if (!mbar_wait(w_full(sw), phw, abort_flag)) {
+                if (!__all_sync(0xFFFFFFFFu, mbar_wait(w_full(sw), phw, abort_flag))) {
                     atomicOr(a.status, ST_WAIT_W_FULL);
                     *abort_flag = 1;
                     ok = false;
                     break;
                 }
                 if (TRACE) tw2 = clock64();
-                if (!mbar_wait_cluster(w_peer(sw), phw, abort_flag)) {
+                if (!__all_sync(0xFFFFFFFFu, mbar_wait_cluster(w_peer(sw), phw, abort_flag))) {
                     atomicOr(a.status, ST_WAIT_W_FULL);
                     *abort_flag = 1;
                     ok = false;
@@ -226,40 +229,58 @@ gemm_fp4_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const _
                     if (kb == 0) t_first = tw3;
                 }
                 tc_fence_after_sync();
+                long long ti0 = 0;
+                if (TRACE) ti0 = clock64();
                 // low descriptor halves of this K step's tiles; +2 per 16 columns of K
                 const uint32_t b0 = x_lo0 + s * (PAIR_X_STAGE_BYTES >> 4);
                 const uint32_t b1 = b0 + (PAIR_XBLK_BYTES >> 4);
                 const uint32_t aw = w_lo0 + sw * (GEMM_W_TILE_BYTES >> 4);
-                const uint32_t first = kb != 0u;          // the very first MMA of each block overwrites
-                if (reuse_a) {
-                    // both token blocks multiply the same W tile: read it from shared memory once
-                    umma2_flag_fill(d0, aw, b0, idesc, first);
-                    umma2_flag_lastuse(d1, aw, b1, idesc, first);
+                if (elect_one()) {
+                if (TB > 1u) {
+                    const uint32_t first = kb != 0u;      // the very first MMA of each block overwrites
+                    if (reuse_a) {
+                        // both token blocks multiply the same W tile: read it from shared memory once
+                        umma2_flag_fill(d0, aw, b0, idesc, first);
+                        umma2_flag_lastuse(d1, aw, b1, idesc, first);
 #pragma unroll
-                    for (uint32_t kk = 1; kk < GEMM_BK / 16; kk++) {
-                        umma2_acc_fill(d0, aw + 2u * kk, b0 + 2u * kk, idesc);
-                        umma2_acc_lastuse(d1, aw + 2u * kk, b1 + 2u * kk, idesc);
+                        for (uint32_t kk = 1; kk < GEMM_BK / 16; kk++) {
+                            umma2_acc_fill(d0, aw + 2u * kk, b0 + 2u * kk, idesc);
+                            umma2_acc_lastuse(d1, aw + 2u * kk, b1 + 2u * kk, idesc);
+                        }
+                    } else {
+                        umma2_flag(d0, aw, b0, idesc, first);
+                        umma2_flag(d1, aw, b1, idesc, first);
+#pragma unroll
+                        for (uint32_t kk = 1; kk < GEMM_BK / 16; kk++) {
+                            umma2_acc(d0, aw + 2u * kk, b0 + 2u * kk, idesc);
+                            umma2_acc(d1, aw + 2u * kk, b1 + 2u * kk, idesc);
+                        }
                     }
                 } else {
-                    umma2_flag(d0, aw, b0, idesc, first);
-                    umma2_flag(d1, aw, b1, idesc, first);
+                    // one token block: even and odd K steps go to two accumulators, which halves the
+                    // run of truncating f32 additions each one sees
+                    const uint32_t d = (kb & 1u) ? d1 : d0;
+                    umma2_flag(d, aw, b0, idesc, kb >= 2u);
 #pragma unroll
-                    for (uint32_t kk = 1; kk < GEMM_BK / 16; kk++) {
-                        umma2_acc(d0, aw + 2u * kk, b0 + 2u * kk, idesc);
-                        umma2_acc(d1, aw + 2u * kk, b1 + 2u * kk, idesc);
-                    }
+                    for (uint32_t kk = 1; kk < GEMM_BK / 16; kk++) umma2_acc(d, aw + 2u * kk, b0 + 2u * kk, idesc);
                 }
                 umma_commit_pair(x_empty(s), 3);             // frees the x stage in both CTAs
                 umma_commit_pair(w_empty(sw), 3);            // and the W stage
+                }
+                __syncwarp();
+                if (TRACE) t_issue += clock64() - ti0;
             }
-            if (ok) umma_commit_pair(acc_full, 3);
-            if (TRACE && a.trace) {
+            if (ok && elect_one()) umma_commit_pair(acc_full, 3);
+            __syncwarp();
+            if (TRACE && a.trace && lane == 0) {
                 unsigned long long* tr = a.trace + 16ull * blockIdx.x;
                 tr[1] = (unsigned long long)t_first;      // first stage ready
                 tr[2] = (unsigned long long)clock64();    // all MMAs issued
                 tr[3] = (unsigned long long)wait_x;
                 tr[4] = (unsigned long long)wait_w;
                 tr[5] = (unsigned long long)wait_p;
+                tr[11] = (unsigned long long)t_issue;     // cycles spent issuing MMAs (queue back-pressure included)
+                tr[15] = (unsigned long long)t_commit;    // cycles spent issuing the two commits
             }
         }
         __syncwarp();
@@ -284,7 +305,8 @@ gemm_fp4_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const _
             const uint32_t rs = rb % PAIR_RAW_STAGES, rph = (rb / PAIR_RAW_STAGES) & 1u;
             long long tq0 = 0;
             if (TRACE) tq0 = clock64();
-            if (jj == 0 && !mbar_wait(raw_full(rs), rph, abort_flag)) {
+            // waits are made warp-uniform (a vote) so that a give-up leaves no lane behind at a __syncwarp
+            if (jj == 0 && !__all_sync(0xFFFFFFFFu, mbar_wait(raw_full(rs), rph, abort_flag))) {
                 atomicOr(a.status, ST_WAIT_X_FULL);
                 *abort_flag = 1;
                 ok = false;
@@ -296,12 +318,15 @@ gemm_fp4_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const _
             const uint32_t ch = 2u * jj + (qtr >> 1);
             const uint2 q = *reinterpret_cast<const uint2*>(raw + r * 128u + ((ch ^ sw_xor) << 4) + 8u * (qtr & 1u));
             const uint32_t sb = raw[PAIR_RAW_WQ_BYTES + r * 16u + 4u * jj + qtr];
-            if (jj == 3u || kb + 1 == KB) mbar_arrive(raw_empty(rs));   // this thread is done with the block
+            if (jj == 3u || kb + 1 == KB) {                              // this warp is done with the block
+                __syncwarp();
+                if (lane == 0) mbar_arrive(raw_empty(rs));
+            }
             uint4 o0, o1;
             decode_group16(q, sb, g, o0, o1);
             long long tq1 = 0;
             if (TRACE) tq1 = clock64();
-            if (!mbar_wait(w_empty(s), ph ^ 1u, abort_flag)) {
+            if (!__all_sync(0xFFFFFFFFu, mbar_wait(w_empty(s), ph ^ 1u, abort_flag))) {
                 atomicOr(a.status, ST_WAIT_EMPTY_DEQ);
                 *abort_flag = 1;
                 ok = false;
@@ -312,7 +337,10 @@ gemm_fp4_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const _
             *reinterpret_cast<uint4*>(wt + (((c + 0u) ^ sw_xor) << 4)) = o0;
             *reinterpret_cast<uint4*>(wt + (((c + 1u) ^ sw_xor) << 4)) = o1;
             fence_proxy_async_smem();       // generic-proxy stores -> visible to the MMA's reads
-            mbar_arrive(w_full(s));
+            // One arrival per warp: hundreds of arrivals on one barrier serialise in shared memory
+            // and were the longest item of a K step.
+            __syncwarp();
+            if (lane == 0) mbar_arrive(w_full(s));
         }
         if (TRACE && a.trace && (tid == 0 || tid == 511)) {
             unsigned long long* tr = a.trace + 16ull * blockIdx.x + (tid == 0 ? 8 : 12);
@@ -342,12 +370,22 @@ gemm_fp4_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const _
             const bool to_partial = a.k_splits > 1u;
             float* const out = to_partial ? a.partial + (size_t)split * a.m * a.n : a.y;
             const float* const res = to_partial ? nullptr : a.r;
-            for (uint32_t cc = slice; cc < PAIR_TOKENS / 16u; cc += 4u) {
+            const bool two_acc = TB == 1u && KB > 1u;
+            for (uint32_t cc = slice; cc < TB * 16u; cc += 4u) {
                 const uint32_t t0 = m0 + cc * 16u;
                 if (t0 >= a.m) break;                        // warp-uniform
                 uint32_t v[16];
                 tmem_ld_32x32b_x16(tmem_base + ((32u * quarter) << 16) + cc * 16u, v);
-                tmem_ld_wait();
+                if (two_acc) {
+                    uint32_t v2[16];
+                    tmem_ld_32x32b_x16(tmem_base + ((32u * quarter) << 16) + 256u + cc * 16u, v2);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (uint32_t j = 0; j < 16; j++)
+                        v[j] = __float_as_uint(__uint_as_float(v[j]) + __uint_as_float(v2[j]));
+                } else {
+                    tmem_ld_wait();
+                }
 #pragma unroll
                 for (uint32_t j = 0; j < 16; j++) {
                     const uint32_t t = t0 + j;

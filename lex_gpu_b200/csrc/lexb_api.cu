@@ -81,7 +81,7 @@ struct lexb_pipeline {
     bool residual;
     // tcgen05 GEMM
     uint32_t tm, stages, w_stages, tmem_cols, m_tiles, n_acc, flags;
-    uint32_t k_splits = 1, kb_per_split = 0;
+    uint32_t k_splits = 1, kb_per_split = 0, tok_blocks = 2;
     float* partial = nullptr;   // split-K workspace [k_splits][m][n], owned by the pipeline
     // matvec
     uint32_t kc;
@@ -183,7 +183,7 @@ int get_maps(const lexb_pipeline* p, const void* x, const void* wq, const void* 
     int rc;
     // x f16[m, k] row-major; box = 64 columns (128 bytes, the swizzle span) x the tile's tokens, never
     // taller than the tensor.  Rows past m are filled with zeros by the copy engine.
-    const uint32_t box_rows = pair ? lexb::PAIR_XBLK_ROWS : (p->tm < p->m ? p->tm : p->m);
+    const uint32_t box_rows = pair ? (p->m < lexb::PAIR_XBLK_ROWS ? p->m : lexb::PAIR_XBLK_ROWS) : (p->tm < p->m ? p->tm : p->m);
     if ((rc = encode_2d(p, &e.map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, x, p->k, p->m, lexb::GEMM_BK, box_rows,
                         CU_TENSOR_MAP_SWIZZLE_128B, "x")))
         return rc;
@@ -231,9 +231,10 @@ int launch_one(lexb_gpu* g, const lexb_pipeline* p, const lexb_buffer* x, const 
         a.trace = (g->d_trace && p->kernel == KERNEL_TCGEN05_PAIR && p->grid <= g->trace_ctas) ? g->d_trace : nullptr;
         a.m = p->m; a.n = p->n; a.k = p->k;
         a.tm = p->tm; a.stages = p->stages; a.w_stages = p->w_stages; a.flags = p->flags;
-        a.k_splits = p->k_splits; a.kb_per_split = p->kb_per_split; a.partial = p->partial;
+        a.k_splits = p->k_splits; a.kb_per_split = p->kb_per_split; a.partial = p->partial; a.tok_blocks = p->tok_blocks;
         a.tmem_cols = p->tmem_cols; a.m_tiles = p->m_tiles; a.n_acc = p->n_acc;
-        a.x_tx_bytes = (p->tm < p->m ? p->tm : p->m) * 128u;
+        a.x_tx_bytes = p->kernel == KERNEL_TCGEN05_PAIR ? (p->m < lexb::PAIR_XBLK_ROWS ? p->m : lexb::PAIR_XBLK_ROWS) * 128u
+                                                        : (p->tm < p->m ? p->tm : p->m) * 128u;
         if (p->kernel == KERNEL_TCGEN05_PAIR) {
             if (a.trace)
                 lexb::gemm_fp4_tcgen05_pair_kernel<true><<<p->grid, p->threads, p->smem, g->stream>>>(maps.map, maps.map_wq, maps.map_ws, a);
@@ -477,10 +478,16 @@ int lexb_gemm_fp4_plan(lexb_gpu* g, uint32_t m, uint32_t n, uint32_t k, int resi
     if (!s.kc) s.kc = env_u32("LEXB_KC", 0);
     if (!s.w_stages) s.w_stages = env_u32("LEXB_WSTAGES", 0);
     if (!s.k_splits) s.k_splits = env_u32("LEXB_KSPLITS", 0);
-    // m <= 16: matvec.  m > 256 and whole 256-row pairs: the two-CTA GEMM.  Otherwise the one-CTA GEMM.
-    uint32_t kernel = s.kernel ? s.kernel
-                               : (m <= 16 ? KERNEL_MATVEC
-                                          : ((m > 256 && n % lexb::GEMM_TN == 0 && k % lexb::PAIR_RAW_K == 0) ? KERNEL_TCGEN05_PAIR : KERNEL_TCGEN05));
+    // m <= 16: matvec.  Otherwise the two-CTA GEMM when the shape allows it (k in blocks of 256), except
+    // for few tokens with enough 128-row tiles to fill the SMs, where the one-CTA kernel is a little faster;
+    // the one-CTA kernel also takes the shapes the two-CTA kernel cannot (k % 256 != 0).
+    uint32_t kernel = s.kernel;
+    if (!kernel) {
+        if (m <= 16) kernel = KERNEL_MATVEC;
+        else if (n % lexb::GEMM_TN == 0 && k % lexb::PAIR_RAW_K == 0 && !(m <= 128 && n / lexb::GEMM_TN >= 120))
+            kernel = KERNEL_TCGEN05_PAIR;
+        else kernel = KERNEL_TCGEN05;
+    }
     if (kernel == KERNEL_MATVEC && m > 16) return fail(LEXB_ERR_SHAPE, "the matvec kernel takes m <= 16, not %u", m);
     if (kernel < KERNEL_MATVEC || kernel > KERNEL_TCGEN05_PAIR) return fail(LEXB_ERR_ARG, "unknown kernel selector %u", kernel);
 
@@ -520,16 +527,16 @@ int lexb_gemm_fp4_plan(lexb_gpu* g, uint32_t m, uint32_t n, uint32_t k, int resi
     } else if (kernel == KERNEL_TCGEN05_PAIR) {
         if (n % lexb::GEMM_TN) return bail(fail(LEXB_ERR_SHAPE, "gemm_fp4 (pair): %u rows per CTA do not divide n = %u", lexb::GEMM_TN, n));
         if (k % lexb::PAIR_RAW_K) return bail(fail(LEXB_ERR_SHAPE, "gemm_fp4 (pair): the packed-weight block of %u columns does not divide k = %u", lexb::PAIR_RAW_K, k));
-        if (m < lexb::PAIR_XBLK_ROWS) return bail(fail(LEXB_ERR_SHAPE, "the two-CTA kernel takes m >= %u, not %u", lexb::PAIR_XBLK_ROWS, m));
         // x ring of 4 stages and W ring of 3 by default (212 KiB with the packed-weight blocks)
         uint32_t stages = s.stages ? s.stages : 4u;
         uint32_t w_stages = s.w_stages ? s.w_stages : 3u;
         if (stages < 2 || w_stages < 2 || lexb::pair_smem_bytes(stages, w_stages) > g->smem_optin)
             return bail(fail(LEXB_ERR_ARG, "stages = %u with w_stages = %u need %u bytes of shared memory (limit %zu)", stages,
                              w_stages, lexb::pair_smem_bytes(stages, w_stages), g->smem_optin));
-        p->tm = lexb::PAIR_TOKENS; p->stages = stages; p->w_stages = w_stages;
+        p->tok_blocks = m > 256u ? 2u : 1u;
+        p->tm = p->tok_blocks * 256u; p->stages = stages; p->w_stages = w_stages;
         p->flags = env_u32("LEXB_COLLECTOR", 0) ? 1u : 0u; p->tmem_cols = lexb::PAIR_TMEM_COLS; p->n_acc = 1;
-        p->m_tiles = (m + lexb::PAIR_TOKENS - 1) / lexb::PAIR_TOKENS;
+        p->m_tiles = (m + p->tm - 1) / p->tm;
         const uint32_t n_pairs = (n + 2u * lexb::GEMM_TN - 1) / (2u * lexb::GEMM_TN);
         const uint32_t tiles = p->m_tiles * n_pairs;
         // Split K when whole tiles fill the SM pairs badly (few tiles, or a short last wave).  Each
@@ -564,7 +571,7 @@ int lexb_gemm_fp4_plan(lexb_gpu* g, uint32_t m, uint32_t n, uint32_t k, int resi
         p->grid = 2u * tiles * splits;
         p->threads = lexb::PAIR_THREADS;
         p->smem = lexb::pair_smem_bytes(stages, w_stages);
-        snprintf(p->entry, sizeof p->entry, "%s_%u_%u_%u_%u_%u_%u", stem, m, n, k, lexb::PAIR_TOKENS, 2u * lexb::GEMM_TN, lexb::GEMM_BK);
+        snprintf(p->entry, sizeof p->entry, "%s_%u_%u_%u_%u_%u_%u", stem, m, n, k, p->tm, 2u * lexb::GEMM_TN, lexb::GEMM_BK);
     } else {
         if (n % lexb::MV_ROWS) return bail(fail(LEXB_ERR_SHAPE, "gemm_fp4 (matvec): %u rows per block do not divide n = %u", lexb::MV_ROWS, n));
         if (k % 32u) return bail(fail(LEXB_ERR_SHAPE, "gemm_fp4 (matvec): 32 does not divide k = %u", k));
@@ -815,7 +822,7 @@ int lexb_gemm_fp4_splitk_static(lexb_gpu* g, uint32_t m, uint32_t n, uint32_t k,
     p.kernel = KERNEL_TCGEN05_PAIR;
     p.m = m; p.n = n; p.k = k;
     p.residual = r != nullptr;
-    p.tm = lexb::PAIR_TOKENS; p.stages = 4; p.w_stages = 3; p.tmem_cols = lexb::PAIR_TMEM_COLS; p.n_acc = 1; p.flags = 0;
+    p.tok_blocks = 2; p.tm = lexb::PAIR_TOKENS; p.stages = 4; p.w_stages = 3; p.tmem_cols = lexb::PAIR_TMEM_COLS; p.n_acc = 1; p.flags = 0;
     p.kc = 0;
     p.m_tiles = (m + lexb::PAIR_TOKENS - 1) / lexb::PAIR_TOKENS;
     p.k_splits = splits;
@@ -851,10 +858,10 @@ int lexb_gemm_fp4_splitk_static(lexb_gpu* g, uint32_t m, uint32_t n, uint32_t k,
     a.trace = nullptr;
     a.m = m; a.n = n; a.k = k;
     a.tm = p.tm; a.stages = p.stages; a.w_stages = p.w_stages; a.flags = 0;
-    a.k_splits = splits; a.kb_per_split = p.kb_per_split;
+    a.k_splits = splits; a.kb_per_split = p.kb_per_split; a.tok_blocks = 2;
     a.partial = g->static_scratch;          // every element of the partials is written before it is read: nothing to clear
     a.tmem_cols = p.tmem_cols; a.m_tiles = p.m_tiles; a.n_acc = 1;
-    a.x_tx_bytes = 0;
+    a.x_tx_bytes = lexb::PAIR_XBLK_BYTES;
     lexb::gemm_fp4_tcgen05_pair_kernel<false><<<p.grid, p.threads, p.smem, g->stream>>>(map_x, map_wq, map_ws, a);
     CUDA_TRY(cudaGetLastError());
     const size_t elems = mm * nn;
