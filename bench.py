@@ -192,8 +192,13 @@ def run_ours(args):
     xb = gpu.wrap_tensor(x_t)
     weights = []
     for c in range(COPIES):
-        wq, ws, wg = inputs.make_weights(N_ROWS, K, copy=c)
-        t = [torch.from_numpy(np.ascontiguousarray(a[n0:n1])).to(dev) for a in (wq, ws, wg)]
+        if world == 1:
+            wq, ws, wg = inputs.make_weights(N_ROWS, K, copy=c)
+        else:
+            # a rank generates only its own slab (same distributions, its own seed): generating and
+            # slicing the whole matrix on every rank would cost minutes of host time
+            wq, ws, wg = inputs.make_weights(n_local, K, seed_base=10_000 * (rank + 1), copy=c)
+        t = [torch.from_numpy(np.ascontiguousarray(a)).to(dev) for a in (wq, ws, wg)]
         weights.append((t, [gpu.wrap_tensor(v) for v in t]))
     y_t = torch.empty((M, n_local), dtype=torch.float32, device=dev)
     yb = gpu.wrap_tensor(y_t)
@@ -313,20 +318,17 @@ def run_ours(args):
     # ---- all-gather variant (N > 1): y shards -> [N][m][n/N] on every rank
     allgather = None
     if dist is not None and full:
-        sizes = [L.shard_rows(N_ROWS, world, r) for r in range(world)]
-        if len({b - a for a, b in sizes}) == 1:
-            full = torch.empty((world, M, n_local), dtype=torch.float32, device=dev)
+        from lex_gpu_b200.shard import RowShard, all_gather_y
+        shard = RowShard.of(N_ROWS, world, rank)
 
-            def ag_step(i):
-                gemm_step(i)
-                dist.all_gather_into_tensor(full, y_t)
+        def ag_step(i):
+            gemm_step(i)
+            all_gather_y(y_t, shard)        # NCCL, ordered after the launch on the same stream
 
-            # the collective runs on torch's stream machinery: make it wait on our stream
-            with torch.cuda.stream(stream):
-                s_ag, _ = timed(pipe, ag_step, args.steps, args.warmup)
-            allgather = {"value": flops_step * args.steps / s_ag / 1e12, "unit": "TFLOP/s",
-                         "ms_per_step": 1e3 * s_ag / args.steps, "bytes_per_rank": int(M * n_local * 4),
-                         "layout": "[N][m][n/N]"}
+        s_ag, _ = timed(pipe, ag_step, args.steps, args.warmup)
+        allgather = {"value": flops_step * args.steps / s_ag / 1e12, "unit": "TFLOP/s",
+                     "ms_per_step": 1e3 * s_ag / args.steps, "bytes_per_rank": int(M * shard.max_rows() * 4),
+                     "layout": "[N][m][max rows per rank]"}
 
     if rank == 0:
         info = cpu_leg() if (world == 1 and full) else None
@@ -334,7 +336,8 @@ def run_ours(args):
                 "warmup": args.warmup, "ms_per_step": 1e3 * per_launch, "higher_is_better": True,
                 "scaling": "strong", "vs_baseline": None, "dtype": "f16*fp4->f32", "data": "synthetic",
                 "config": {"workload": f"gemm_fp4 m={M} n={N_ROWS} k={K} (27B MLP gate/up prefill)",
-                           "parallelism": f"n-sharded x{world}, {n_local} rows per GPU, no gather in the step",
+                           "parallelism": f"n-sharded x{world}, {n_local} rows on rank 0, no gather in the step",
+                           "k_splits": desc.k_splits,
                            "l2": f"{COPIES} weight copies rotated per step ({COPIES * wbytes_local / 1e6:.0f} MB per GPU > L2)",
                            "schedule": {"bm": desc.bm, "bn": desc.bn, "bk": desc.bk, "stages": desc.stages,
                                         "grid": desc.grid, "threads": desc.threads, "smem": desc.threadgroup_bytes}},
