@@ -34,7 +34,6 @@ ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
 
 M, N_ROWS, K = 512, 17408, 5120
-COPIES = 8
 METRIC = "gemm_fp4 TFLOP/s at m=512 (27B MLP gate/up: n=17408 k=5120)"
 
 
@@ -191,6 +190,9 @@ def run_ours(args):
     x_t = torch.from_numpy(x_np.view(np.int16)).to(dev)
     xb = gpu.wrap_tensor(x_t)
     weights = []
+    # enough copies of this rank's slab to exceed the L2 (126 MB) several times over
+    wbytes_one = n_local * K // 2 + n_local * K // 16 + 4 * n_local
+    COPIES = max(8, -(-400_000_000 // wbytes_one))
     for c in range(COPIES):
         if world == 1:
             wq, ws, wg = inputs.make_weights(N_ROWS, K, copy=c)
@@ -330,6 +332,42 @@ def run_ours(args):
                      "ms_per_step": 1e3 * s_ag / args.steps, "bytes_per_rank": int(M * shard.max_rows() * 4),
                      "layout": "[N][m][max rows per rank]"}
 
+    # ---- one layer of the 27B MLP stack at m = 4096 (BASELINE config 4), n-sharded: gate, up (n=17408,
+    # k=5120) and down (n=5120, k=17408), independent calls, y not chained.  Reported, not the headline.
+    stack = None
+    if full and args.stack:
+        m4 = 4096
+        shapes = [("gate", N_ROWS, K), ("up", N_ROWS, K), ("down", K, N_ROWS)]
+        steps4, flops4 = [], 0.0
+        keep = []
+        for name, nn, kk in shapes:
+            a0, a1 = L.shard_rows(nn, world, rank)
+            nl = a1 - a0
+            xx = torch.from_numpy(inputs.make_x(m4, kk, seed_base=5).view(np.int16)).to(dev)
+            yy = torch.empty((m4, nl), dtype=torch.float32, device=dev)
+            sets = []
+            slab = nl * kk // 2 + nl * kk // 16 + 4 * nl
+            for c in range(max(3, -(-400_000_000 // (3 * slab)))):      # rotate through more than the L2 holds
+                w = inputs.make_weights(nl, kk, seed_base=20_000 * (rank + 1) + (0 if name != "up" else 7), copy=c)
+                tt = [torch.from_numpy(np.ascontiguousarray(v)).to(dev) for v in w]
+                sets.append(tt)
+            pp = gpu.plan_gemm_fp4(m4, nl, kk)
+            keep.append((xx, yy, sets, pp))
+            steps4.append((pp, gpu.wrap_tensor(xx), [[gpu.wrap_tensor(v) for v in tt] for tt in sets], gpu.wrap_tensor(yy)))
+            flops4 += 2.0 * m4 * nn * kk
+
+        def layer_step(i):
+            for pp, xbuf, wsets, ybuf in steps4:
+                b = wsets[i % len(wsets)]
+                gpu.run(pp, [xbuf, b[0], b[1], b[2], ybuf])
+
+        n_layers = 16
+        s4, _ = timed(None, layer_step, n_layers, 3)
+        stack = {"value": flops4 * n_layers / s4 / 1e12, "unit": "TFLOP/s", "ms_per_layer": 1e3 * s4 / n_layers,
+                 "config": f"m=4096, gate+up (n=17408,k=5120) + down (n=5120,k=17408) per layer, n-sharded x{world}, no gather",
+                 "layers_timed": n_layers}
+        del keep
+
     if rank == 0:
         info = cpu_leg() if (world == 1 and full) else None
         line = {"metric": METRIC, "value": tflops, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
@@ -343,7 +381,7 @@ def run_ours(args):
                                         "grid": desc.grid, "threads": desc.threads, "smem": desc.threadgroup_bytes}},
                 "roofline": roofline, "cpu_baseline": info, "e2e": e2e, "gpu_launches": args.steps,
                 "clocks": clocks, "matvec": matvec, "allgather": allgather, "device_status": status,
-                "checksum": checksum, "only": args.only}
+                "checksum": checksum, "only": args.only, "stack_m4096": stack}
         print(json.dumps(line))
     if dist is not None:
         dist.barrier()
@@ -356,6 +394,8 @@ def main():
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-stack", dest="stack", action="store_false",
+                    help="skip the m=4096 stack-layer leg (reported under stack_m4096)")
     ap.add_argument("--only", default="all", choices=["all", "gemm", "matvec"],
                     help="time one kernel only (short runs for profilers); the JSON line then omits the other legs")
     args = ap.parse_args()
