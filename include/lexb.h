@@ -136,6 +136,16 @@ LEXB_API int lexb_pipeline_describe(const lexb_pipeline* p, lexb_lowered* out);
 LEXB_API int lexb_gemm_fp4_launch(lexb_gpu* gpu, const lexb_pipeline* p, const lexb_buffer* x,
                                   const lexb_buffer* wq, const lexb_buffer* ws, const lexb_buffer* wg,
                                   const lexb_buffer* r_or_null, lexb_buffer* y);
+/* New (the reference is single-GPU): the n-sharded launch with the all-gather of y fused into the
+ * kernel's epilogue.  This rank owns columns [n0, n0 + n) of a gathered y[m, n_total]; y_of_rank[d]
+ * is the address, in this GPU's address space, of rank d's gathered y (its own included) - e.g. the
+ * peer pointers of a symmetric-memory allocation.  Every finished 128-byte row segment is stored to
+ * all `world` buffers with plain peer stores over NVLink (with split-K, by the reduction launch).
+ * The caller synchronises the ranks before anyone reads a gathered y.  Two-CTA GEMM shapes only. */
+LEXB_API int lexb_gemm_fp4_launch_gather(lexb_gpu* gpu, const lexb_pipeline* p, const lexb_buffer* x,
+                                         const lexb_buffer* wq, const lexb_buffer* ws, const lexb_buffer* wg,
+                                         const lexb_buffer* r_or_null, void* const* y_of_rank, uint32_t world,
+                                         uint32_t n_total, uint32_t n0);
 /* The call a runtime makes per prefill chunk with host activations: copy x from host memory
  * into x_dev, launch, copy y_dev back into y_host, wait.  The weights stay resident, as
  * lex-rt keeps them (Runner::forward_with writes only per-step inputs,

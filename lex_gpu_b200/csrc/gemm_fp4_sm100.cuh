@@ -31,6 +31,8 @@ constexpr uint32_t GEMM_WARP_MMA = 9;
 constexpr uint32_t GEMM_THREADS = 320;
 constexpr uint32_t GEMM_W_TILE_BYTES = GEMM_TN * GEMM_BK * 2;   // 16 KiB
 
+constexpr uint32_t GATHER_MAX = 8;
+
 struct GemmArgs {
     const uint8_t* wq;    // [n, k/2]
     const uint8_t* ws;    // [n, k/16]
@@ -51,6 +53,11 @@ struct GemmArgs {
     // split-K (two-CTA kernel): split s of k_splits takes K steps [s * kb_per_split, ...) and writes its
     // partial product to partial[s][m][n]; a reduction kernel then forms y.  k_splits = 1: y is written.
     uint32_t k_splits, kb_per_split;
+    // Fused all-gather (two-CTA kernel): with gather_world > 0 the result is not written to y but to
+    // column gather_n0 + j of every gather_y[d], d < gather_world - y buffers of row length gather_n, one
+    // per GPU, mapped into this GPU's address space (plain peer stores over NVLink; no copy-engine loads).
+    float* gather_y[GATHER_MAX];
+    uint32_t gather_world, gather_n, gather_n0;
     uint32_t tok_blocks;  // two-CTA kernel: 256-token blocks per tile, 2 (m > 256) or 1; with 1, TMEM holds two
                           // accumulators that take even and odd K steps
     float* partial;

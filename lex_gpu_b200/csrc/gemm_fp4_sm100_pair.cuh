@@ -386,14 +386,30 @@ gemm_fp4_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const _
                 } else {
                     tmem_ld_wait();
                 }
+                if (a.gather_world == 0u || to_partial) {
 #pragma unroll
-                for (uint32_t j = 0; j < 16; j++) {
-                    const uint32_t t = t0 + j;
-                    if (t < a.m) {
-                        const size_t o = (size_t)t * a.n + out_row;
-                        float val = __uint_as_float(v[j]);
-                        if (res) val = val + __ldg(res + o);
-                        out[o] = val;
+                    for (uint32_t j = 0; j < 16; j++) {
+                        const uint32_t t = t0 + j;
+                        if (t < a.m) {
+                            const size_t o = (size_t)t * a.n + out_row;
+                            float val = __uint_as_float(v[j]);
+                            if (res) val = val + __ldg(res + o);
+                            out[o] = val;
+                        }
+                    }
+                } else {
+                    // fused all-gather: the same 128-byte row segment goes to every GPU's y
+#pragma unroll
+                    for (uint32_t j = 0; j < 16; j++) {
+                        const uint32_t t = t0 + j;
+                        if (t < a.m) {
+                            float val = __uint_as_float(v[j]);
+                            if (res) val = val + __ldg(res + (size_t)t * a.n + out_row);
+                            const size_t o = (size_t)t * a.gather_n + a.gather_n0 + out_row;
+#pragma unroll
+                            for (uint32_t d = 0; d < GATHER_MAX; d++)
+                                if (d < a.gather_world) a.gather_y[d][o] = val;
+                        }
                     }
                 }
             }
@@ -411,8 +427,13 @@ gemm_fp4_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const _
 }
 
 // y = sum over splits of partial[s] (+ r), four floats per thread step; the order of the sum is fixed.
+struct GatherDst {
+    float* y[GATHER_MAX];
+    uint32_t world, n_total, n0, n_local;   // world = 0: plain y
+};
+
 __global__ void splitk_reduce_kernel(const float* __restrict__ partial, uint32_t splits, size_t elems,
-                                     const float* __restrict__ r, float* __restrict__ y) {
+                                     const float* __restrict__ r, float* __restrict__ y, const GatherDst g) {
     const size_t n4 = elems / 4;
     for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n4; i += (size_t)gridDim.x * blockDim.x) {
         float4 acc = reinterpret_cast<const float4*>(partial)[i];
@@ -424,7 +445,16 @@ __global__ void splitk_reduce_kernel(const float* __restrict__ partial, uint32_t
             const float4 q = reinterpret_cast<const float4*>(r)[i];
             acc.x += q.x; acc.y += q.y; acc.z += q.z; acc.w += q.w;
         }
-        reinterpret_cast<float4*>(y)[i] = acc;
+        if (g.world == 0u) {
+            reinterpret_cast<float4*>(y)[i] = acc;
+        } else {
+            // fused all-gather: element (t, c) of the local [m, n_local] goes to column n0 + c of every y
+            const size_t e = i * 4, t = e / g.n_local, c = e - t * g.n_local;
+            const size_t o = t * g.n_total + g.n0 + c;
+#pragma unroll
+            for (uint32_t d = 0; d < GATHER_MAX; d++)
+                if (d < g.world) *reinterpret_cast<float4*>(g.y[d] + o) = acc;
+        }
     }
 }
 

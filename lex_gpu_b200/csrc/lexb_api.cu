@@ -203,7 +203,7 @@ int get_maps(const lexb_pipeline* p, const void* x, const void* wq, const void* 
 }
 
 int launch_one(lexb_gpu* g, const lexb_pipeline* p, const lexb_buffer* x, const lexb_buffer* wq, const lexb_buffer* ws,
-               const lexb_buffer* wg, const lexb_buffer* r, lexb_buffer* y) {
+               const lexb_buffer* wg, const lexb_buffer* r, lexb_buffer* y, const lexb::GatherDst* gather = nullptr) {
     if (!p) return fail(LEXB_ERR_ARG, "null pipeline");
     if (p->gpu != g) return fail(LEXB_ERR_ARG, "pipeline was planned on another gpu handle");
     const size_t m = p->m, n = p->n, k = p->k;
@@ -212,7 +212,9 @@ int launch_one(lexb_gpu* g, const lexb_pipeline* p, const lexb_buffer* x, const 
     if ((rc = check_buf(wq, g, n * k / 2, "wq"))) return rc;
     if ((rc = check_buf(ws, g, n * k / 16, "ws"))) return rc;
     if ((rc = check_buf(wg, g, n * 4, "wg"))) return rc;
-    if ((rc = check_buf(y, g, m * n * 4, "y"))) return rc;
+    if (!gather && (rc = check_buf(y, g, m * n * 4, "y"))) return rc;
+    if (gather && p->kernel != KERNEL_TCGEN05_PAIR)
+        return fail(LEXB_ERR_UNSUPPORTED, "the fused all-gather exists in the two-CTA GEMM only (m > 16, n %% 128 == 0, k %% 256 == 0)");
     if (p->residual) {
         if ((rc = check_buf(r, g, m * n * 4, "r"))) return rc;
     } else if (r) {
@@ -226,7 +228,13 @@ int launch_one(lexb_gpu* g, const lexb_pipeline* p, const lexb_buffer* x, const 
         a.ws = static_cast<const uint8_t*>(ws->ptr);
         a.wg = static_cast<const float*>(wg->ptr);
         a.r = r ? static_cast<const float*>(r->ptr) : nullptr;
-        a.y = static_cast<float*>(y->ptr);
+        a.y = y ? static_cast<float*>(y->ptr) : nullptr;
+        lexb::GatherDst gd{};
+        if (gather) {
+            gd = *gather;
+            for (uint32_t d = 0; d < gd.world; d++) a.gather_y[d] = gd.y[d];
+            a.gather_world = gd.world; a.gather_n = gd.n_total; a.gather_n0 = gd.n0;
+        }
         a.status = g->d_status;
         a.trace = (g->d_trace && p->kernel == KERNEL_TCGEN05_PAIR && p->grid <= g->trace_ctas) ? g->d_trace : nullptr;
         a.m = p->m; a.n = p->n; a.k = p->k;
@@ -244,7 +252,7 @@ int launch_one(lexb_gpu* g, const lexb_pipeline* p, const lexb_buffer* x, const 
                 CUDA_TRY(cudaGetLastError());
                 const size_t elems = static_cast<size_t>(p->m) * p->n;       // n % 128 == 0: a multiple of 4
                 const uint32_t blocks = static_cast<uint32_t>(std::min<size_t>((elems / 4 + 255) / 256, 148u * 8u));
-                lexb::splitk_reduce_kernel<<<blocks, 256, 0, g->stream>>>(p->partial, p->k_splits, elems, a.r, a.y);
+                lexb::splitk_reduce_kernel<<<blocks, 256, 0, g->stream>>>(p->partial, p->k_splits, elems, a.r, a.y, gd);
             }
         } else {
             lexb::gemm_fp4_tcgen05_kernel<<<p->grid, p->threads, p->smem, g->stream>>>(maps.map, a);
@@ -646,6 +654,25 @@ int lexb_gemm_fp4_launch(lexb_gpu* g, const lexb_pipeline* p, const lexb_buffer*
     return launch_one(g, p, x, wq, ws, wg, r, y);
 }
 
+int lexb_gemm_fp4_launch_gather(lexb_gpu* g, const lexb_pipeline* p, const lexb_buffer* x, const lexb_buffer* wq,
+                                const lexb_buffer* ws, const lexb_buffer* wg, const lexb_buffer* r, void* const* y_of_rank,
+                                uint32_t world, uint32_t n_total, uint32_t n0) {
+    int rc = use(g);
+    if (rc) return rc;
+    if (!p || !y_of_rank) return fail(LEXB_ERR_ARG, "lexb_gemm_fp4_launch_gather: null argument");
+    if (world == 0 || world > lexb::GATHER_MAX) return fail(LEXB_ERR_ARG, "world = %u outside [1, %u]", world, lexb::GATHER_MAX);
+    if (n_total % 4u || n0 % 4u || static_cast<uint64_t>(n0) + p->n > n_total)
+        return fail(LEXB_ERR_ARG, "columns [%u, %u) do not fit a gathered row of %u", n0, n0 + p->n, n_total);
+    lexb::GatherDst gd{};
+    gd.world = world; gd.n_total = n_total; gd.n0 = n0; gd.n_local = p->n;
+    for (uint32_t d = 0; d < world; d++) {
+        if (!y_of_rank[d] || (reinterpret_cast<uintptr_t>(y_of_rank[d]) & 15u))
+            return fail(LEXB_ERR_ARG, "y of rank %u is null or not 16-byte aligned", d);
+        gd.y[d] = static_cast<float*>(y_of_rank[d]);
+    }
+    return launch_one(g, p, x, wq, ws, wg, r, nullptr, &gd);
+}
+
 int lexb_gemm_fp4_run_host(lexb_gpu* g, const lexb_pipeline* p, const void* x_host, lexb_buffer* x_dev,
                            const lexb_buffer* wq, const lexb_buffer* ws, const lexb_buffer* wg, const lexb_buffer* r,
                            lexb_buffer* y_dev, void* y_host) {
@@ -866,7 +893,7 @@ int lexb_gemm_fp4_splitk_static(lexb_gpu* g, uint32_t m, uint32_t n, uint32_t k,
     CUDA_TRY(cudaGetLastError());
     const size_t elems = mm * nn;
     const uint32_t blocks = static_cast<uint32_t>(std::min<size_t>((elems / 4 + 255) / 256, 148u * 8u));
-    lexb::splitk_reduce_kernel<<<blocks, 256, 0, g->stream>>>(g->static_scratch, splits, elems, a.r, a.y);
+    lexb::splitk_reduce_kernel<<<blocks, 256, 0, g->stream>>>(g->static_scratch, splits, elems, a.r, a.y, lexb::GatherDst{});
     CUDA_TRY(cudaGetLastError());
     return LEXB_OK;
 }

@@ -28,7 +28,7 @@ SYMBOLS = [
     "lexb_pipeline_free", "lexb_pipeline_describe", "lexb_gemm_fp4_launch", "lexb_gemm_fp4_run_host",
     "lexb_run_launches", "lexb_run_each_timed", "lexb_time_launches", "lexb_status_word",
     "lexb_selftest_bounded_wait", "lexb_dequant_fp4_f16", "lexb_shard_rows", "lexb_trace_enable", "lexb_trace_read",
-    "lexb_gemm_fp4_splitk_static",
+    "lexb_gemm_fp4_splitk_static", "lexb_gemm_fp4_launch_gather",
 ]
 
 
@@ -111,6 +111,7 @@ def load_library() -> ctypes.CDLL:
     L.lexb_dequant_fp4_f16.argtypes = [vp, u32, u32, vp, vp, vp, vp]
     L.lexb_shard_rows.argtypes = [u32, u32, u32, POINTER(u32), POINTER(u32)]
     L.lexb_trace_enable.argtypes = [vp, u32]
+    L.lexb_gemm_fp4_launch_gather.argtypes = [vp, vp, vp, vp, vp, vp, vp, POINTER(vp), u32, u32, u32]
     L.lexb_gemm_fp4_splitk_static.argtypes = [vp, u32, u32, u32, u32, vp, vp, vp, vp, vp, vp]
     L.lexb_trace_read.argtypes = [vp, vp, u32]
     _lib = L
@@ -307,6 +308,15 @@ class Gpu:
         r, y = (bufs[4], bufs[5]) if res else (None, bufs[4])
         _check(self._L.lexb_gemm_fp4_launch(self.handle, pipe.handle, x.handle, wq.handle, ws.handle, wg.handle,
                                             r.handle if r is not None else None, y.handle))
+
+    def run_gather(self, pipe: Pipeline, x: Buffer, wq: Buffer, ws: Buffer, wg: Buffer, r: Optional[Buffer],
+                   y_ptr_of_rank: Sequence[int], n_total: int, n0: int) -> None:
+        """One launch whose epilogue stores this rank's columns [n0, n0+n) into every rank's gathered y
+        (device addresses valid on this GPU, e.g. symmetric-memory peer pointers).  Asynchronous."""
+        arr = (c_void_p * len(y_ptr_of_rank))(*[c_void_p(p) for p in y_ptr_of_rank])
+        _check(self._L.lexb_gemm_fp4_launch_gather(self.handle, pipe.handle, x.handle, wq.handle, ws.handle, wg.handle,
+                                                   r.handle if r is not None else None, arr, len(y_ptr_of_rank),
+                                                   n_total, n0))
 
     def run_host(self, pipe: Pipeline, x_host_ptr: int, x_dev: Buffer, wq: Buffer, ws: Buffer, wg: Buffer,
                  r: Optional[Buffer], y_dev: Buffer, y_host_ptr: int) -> None:

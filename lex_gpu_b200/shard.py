@@ -67,3 +67,19 @@ def assemble(gathered, shard: RowShard):
     for r, (a, b) in enumerate(shard.spans()):
         y[:, a:b] = gathered[r, :, :b - a]
     return y
+
+
+class SymmetricY:
+    """A gathered y[m, n] f32 on every rank, allocated as symmetric memory so that each rank holds the
+    device addresses of all ranks' buffers (`ptrs`), which is what lexb_gemm_fp4_launch_gather stores to."""
+
+    def __init__(self, m: int, n: int, group):
+        import torch
+        import torch.distributed._symmetric_memory as symm
+        self.tensor = symm.empty((m, n), dtype=torch.float32, device=torch.device("cuda", torch.cuda.current_device()))
+        self.handle = symm.rendezvous(self.tensor, group)
+        self.ptrs = [int(p) for p in self.handle.buffer_ptrs]
+
+    def barrier(self) -> None:
+        """All ranks' work queued so far on the current stream is done before any rank continues."""
+        self.handle.barrier()

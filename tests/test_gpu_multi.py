@@ -1,0 +1,76 @@
+"""Two or more GPUs: the fused all-gather epilogue over symmetric memory against the NCCL all-gather.
+Skipped on a single-GPU machine (the store logic itself is covered there with several buffers on one GPU)."""
+import os
+import socket
+import sys
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+ROOT = Path(__file__).resolve().parent.parent
+
+
+def _free_port() -> int:
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, m, n, k, out_dir):
+    sys.path.insert(0, str(ROOT))
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    import torch
+    import torch.distributed as dist
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    import lex_gpu_b200 as L
+    from lex_gpu_b200 import inputs
+    from lex_gpu_b200.shard import RowShard, SymmetricY, all_gather_y, assemble
+    x, wq, ws, wg = inputs.make_case(m, n, k, seed_base=9)
+    sh = RowShard.of(n, world, rank)
+    q_, s_, g_ = sh.slice_weights(wq, ws, wg)
+    gpu = L.Gpu(rank)
+    stream = torch.cuda.current_stream()
+    gpu.set_stream(stream.cuda_stream)
+    q = L.QBuf(gpu, np.ascontiguousarray(q_), np.ascontiguousarray(s_), np.ascontiguousarray(g_))
+    xb = gpu.upload(x)
+    pipe = gpu.plan_gemm_fp4(m, sh.rows, k, kernel=3)
+    # NCCL path
+    y_local = torch.empty((m, sh.rows), dtype=torch.float32, device="cuda")
+    gpu.run(pipe, q.bind(xb, None, gpu.wrap_tensor(y_local)))
+    y_nccl = assemble(all_gather_y(y_local, sh), sh)
+    # fused path
+    sy = SymmetricY(m, n, dist.group.WORLD)
+    sy.tensor.fill_(float("nan"))
+    sy.barrier()
+    gpu.run_gather(pipe, xb, q.wq, q.ws, q.wg, None, sy.ptrs, n, sh.n0)
+    sy.barrier()
+    torch.cuda.synchronize()
+    same = torch.equal(sy.tensor, y_nccl)
+    if rank == 0:
+        np.save(os.path.join(out_dir, "y.npy"), sy.tensor.cpu().numpy())
+    flag = torch.tensor([1 if same else 0], device="cuda")
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+    if rank == 0:
+        np.save(os.path.join(out_dir, "same.npy"), flag.cpu().numpy())
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_fused_gather_equals_nccl_all_gather(tmp_path):
+    import torch
+    import torch.multiprocessing as mp
+    world = min(torch.cuda.device_count(), 4)
+    if world < 2:
+        pytest.skip("needs at least two GPUs")
+    m, n, k = 512, 256 * world * 2, 1024
+    mp.spawn(_worker, args=(world, _free_port(), m, n, k, str(tmp_path)), nprocs=world, join=True)
+    sys.path.insert(0, str(ROOT))
+    from lex_gpu_b200 import inputs
+    from oracle import oracle as O
+    assert int(np.load(tmp_path / "same.npy")[0]) == 1
+    x, wq, ws, wg = inputs.make_case(m, n, k, seed_base=9)
+    err, scale, rel = O.err_of_scale(np.load(tmp_path / "y.npy"), O.gemm_fp4(x, wq, ws, wg))
+    assert scale > 1e-3 and err <= 2e-3 and rel <= 2e-3

@@ -377,3 +377,29 @@ def test_bounded_wait_reports_and_returns(gpu):
     assert gpu.status_word() == 0                                # reading clears it
     x, wq, ws, wg = inputs.make_case(32, 128, 64, seed_base=5)
     check(L.gemm_fp4(gpu, x, wq, ws, wg), O.gemm_fp4(x, wq, ws, wg))
+
+
+# ---------------------------------------------------------------- fused all-gather epilogue
+
+@pytest.mark.parametrize("m,n,k,splits", [(512, 256, 512, 1), (300, 384, 2048, 3), (64, 256, 1024, 2)])
+def test_gather_epilogue_writes_every_ranks_y(gpu, m, n, k, splits):
+    """The n-sharded launch with the all-gather fused in: this 'rank' owns columns [n0, n0+n) of a wider
+    y and stores them into every rank's buffer.  Here the 'ranks' are three buffers on one GPU."""
+    n_total, n0 = 1024, 384
+    x, wq, ws, wg = inputs.make_case(m, n, k, seed_base=n + k)
+    r = inputs.make_residual(m, n, seed_base=3)
+    want = O.gemm_fp4(x, wq, ws, wg, r=r)
+    q = L.QBuf(gpu, wq, ws, wg)
+    xb, rb = gpu.upload(x), gpu.upload(r)
+    ys = [gpu.alloc(4 * m * n_total) for _ in range(3)]
+    for y in ys:
+        gpu.memset(y, 0xFF)
+    pipe = gpu.plan_gemm_fp4(m, n, k, residual=True, kernel=3, k_splits=splits)
+    gpu.run_gather(pipe, xb, q.wq, q.ws, q.wg, rb, [y.ptr for y in ys], n_total, n0)
+    assert gpu.status_word() == 0
+    for y in ys:
+        full = gpu.download(y, np.float32, (m, n_total))
+        check(full[:, n0:n0 + n], want)
+        assert np.isnan(full[:, :n0]).all() and np.isnan(full[:, n0 + n:]).all()      # nothing else touched
+    with pytest.raises(L.LexbError):
+        gpu.run_gather(pipe, xb, q.wq, q.ws, q.wg, rb, [y.ptr for y in ys], n_total, n_total - 128)
