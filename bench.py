@@ -331,6 +331,24 @@ def run_ours(args):
         allgather = {"value": flops_step * args.steps / s_ag / 1e12, "unit": "TFLOP/s",
                      "ms_per_step": 1e3 * s_ag / args.steps, "bytes_per_rank": int(M * shard.max_rows() * 4),
                      "layout": "[N][m][max rows per rank]"}
+        # the same gather fused into the kernel: peer stores into every rank's y[m, n] (symmetric memory),
+        # one cross-rank barrier per step
+        try:
+            from lex_gpu_b200.shard import SymmetricY
+            with torch.cuda.stream(stream):
+                sy = SymmetricY(M, N_ROWS, dist.group.WORLD)
+
+                def fused_step(i):
+                    b = weights[i % COPIES][1]
+                    gpu.run_gather(pipe, xb, b[0], b[1], b[2], None, sy.ptrs, N_ROWS, n0)
+                    sy.barrier()
+
+                s_fu, _ = timed(pipe, fused_step, args.steps, args.warmup)
+            allgather["fused_peer_stores"] = {"value": flops_step * args.steps / s_fu / 1e12, "unit": "TFLOP/s",
+                                              "ms_per_step": 1e3 * s_fu / args.steps, "layout": "[m][n] on every rank",
+                                              "note": "epilogue stores to all ranks over NVLink + one barrier per step"}
+        except Exception as e:      # symmetric memory unavailable on this machine
+            allgather["fused_peer_stores"] = {"unavailable": repr(e)[:200]}
 
     # ---- one layer of the 27B MLP stack at m = 4096 (BASELINE config 4), n-sharded: gate, up (n=17408,
     # k=5120) and down (n=5120, k=17408), independent calls, y not chained.  Reported, not the headline.
