@@ -122,7 +122,8 @@ LEXB_API int lexb_host_free(void* p);
 /* lx_kernels::gemm + Gpu::build_lowered, crates/lex-rt/src/lx_kernels.rs:43-107 and
  * crates/lex-cuda/src/device.rs:475-483: choose the kernel and tiles for a shape.  Nothing is
  * compiled at run time; the kernels are built for sm_100a ahead of time.  Shapes must
- * satisfy n % 128 == 0 and k % 64 == 0 (m > 16) or n % 16 == 0 and k % 32 == 0 (m <= 16);
+ * satisfy n % 128 == 0 and k % 64 == 0 (the tcgen05 GEMMs, chosen for m > 8) or n % 16 == 0 and
+ * k % 32 == 0 (the matvec, chosen for m <= 8 and for m <= 16 when the GEMMs cannot take the shape);
  * others are refused with LEXB_ERR_SHAPE, as the `.lx` program refuses extents that do not
  * divide (crates/lex-front/src/syntax.rs:1513-1516). */
 LEXB_API int lexb_gemm_fp4_plan(lexb_gpu* gpu, uint32_t m, uint32_t n, uint32_t k, int residual,

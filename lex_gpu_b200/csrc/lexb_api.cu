@@ -266,10 +266,14 @@ int launch_one(lexb_gpu* g, const lexb_pipeline* p, const lexb_buffer* x, const 
         a.r = r ? static_cast<const float*>(r->ptr) : nullptr;
         a.y = static_cast<float*>(y->ptr);
         a.m = p->m; a.n = p->n; a.k = p->k; a.kc = p->kc;
-        if (p->m > 8)
-            lexb::matvec_fp4_kernel<true><<<p->grid, p->threads, p->smem, g->stream>>>(a);
-        else
-            lexb::matvec_fp4_kernel<false><<<p->grid, p->threads, p->smem, g->stream>>>(a);
+        const bool ragged = (p->k % lexb::MV_SLICE) != 0u;
+        if (p->m > 8) {
+            if (ragged) lexb::matvec_fp4_kernel<true, true><<<p->grid, p->threads, p->smem, g->stream>>>(a);
+            else lexb::matvec_fp4_kernel<true, false><<<p->grid, p->threads, p->smem, g->stream>>>(a);
+        } else {
+            if (ragged) lexb::matvec_fp4_kernel<false, true><<<p->grid, p->threads, p->smem, g->stream>>>(a);
+            else lexb::matvec_fp4_kernel<false, false><<<p->grid, p->threads, p->smem, g->stream>>>(a);
+        }
     }
     CUDA_TRY(cudaGetLastError());
     return LEXB_OK;
@@ -325,8 +329,10 @@ int lexb_open(int device, lexb_gpu** out) {
     if (cudaFuncSetAttribute(lexb::gemm_fp4_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem) != cudaSuccess ||
         cudaFuncSetAttribute(lexb::gemm_fp4_tcgen05_pair_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem) != cudaSuccess ||
         cudaFuncSetAttribute(lexb::gemm_fp4_tcgen05_pair_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem) != cudaSuccess ||
-        cudaFuncSetAttribute(lexb::matvec_fp4_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem) != cudaSuccess ||
-        cudaFuncSetAttribute(lexb::matvec_fp4_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem) != cudaSuccess)
+        cudaFuncSetAttribute(lexb::matvec_fp4_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem) != cudaSuccess ||
+        cudaFuncSetAttribute(lexb::matvec_fp4_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem) != cudaSuccess ||
+        cudaFuncSetAttribute(lexb::matvec_fp4_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem) != cudaSuccess ||
+        cudaFuncSetAttribute(lexb::matvec_fp4_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem) != cudaSuccess)
         return bail(fail(LEXB_ERR_CUDA, "cudaFuncSetAttribute(max dynamic shared memory) failed: %s", cudaGetErrorString(cudaGetLastError())));
     *out = g;
     return LEXB_OK;
@@ -486,12 +492,12 @@ int lexb_gemm_fp4_plan(lexb_gpu* g, uint32_t m, uint32_t n, uint32_t k, int resi
     if (!s.kc) s.kc = env_u32("LEXB_KC", 0);
     if (!s.w_stages) s.w_stages = env_u32("LEXB_WSTAGES", 0);
     if (!s.k_splits) s.k_splits = env_u32("LEXB_KSPLITS", 0);
-    // m <= 16: matvec.  Otherwise the two-CTA GEMM when the shape allows it (k in blocks of 256), except
+    // m <= 8: matvec (it also takes 9..16 when asked, but the GEMMs are faster there).  Otherwise the two-CTA GEMM when the shape allows it (k in blocks of 256), except
     // for few tokens with enough 128-row tiles to fill the SMs, where the one-CTA kernel is a little faster;
     // the one-CTA kernel also takes the shapes the two-CTA kernel cannot (k % 256 != 0).
     uint32_t kernel = s.kernel;
     if (!kernel) {
-        if (m <= 16) kernel = KERNEL_MATVEC;
+        if (m <= 8 || ((n % lexb::GEMM_TN || k % lexb::GEMM_BK) && m <= 16)) kernel = KERNEL_MATVEC;
         else if (n % lexb::GEMM_TN == 0 && k % lexb::PAIR_RAW_K == 0 && !(m <= 128 && n / lexb::GEMM_TN >= 120))
             kernel = KERNEL_TCGEN05_PAIR;
         else kernel = KERNEL_TCGEN05;

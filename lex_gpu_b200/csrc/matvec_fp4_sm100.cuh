@@ -52,7 +52,7 @@ __host__ __device__ constexpr uint32_t matvec_x_pitch(uint32_t kc) {
 }
 // two reduction buffers (alternating per row block), then the x chunk
 __host__ __device__ constexpr uint32_t matvec_smem_bytes(uint32_t m, uint32_t kc) {
-    return 2u * MV_RED_BYTES + m * matvec_x_pitch(kc) + 16u;
+    return 2u * MV_RED_BYTES + 128u + m * matvec_x_pitch(kc) + 16u;   // 128 bytes of zeros before x
 }
 
 __device__ __forceinline__ void mma_m16n8k16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
@@ -68,11 +68,12 @@ struct MvLoad {
     uint32_t sa, sb;     // their two scale bytes (low 16 bits)
 };
 
-template <bool HI>   // HI: m > 8, a second group of 8 tokens
+template <bool HI, bool RAGGED>   // HI: m > 8, a second group of 8 tokens; RAGGED: k % 128 != 0
 __global__ void __launch_bounds__(MV_THREADS) matvec_fp4_kernel(const MatvecArgs a) {
     extern __shared__ __align__(16) uint8_t mv_smem[];
     float* const red = reinterpret_cast<float*>(mv_smem);               // [2][warp][row 16][token 16]
-    uint8_t* const xs = mv_smem + 2u * MV_RED_BYTES;
+    uint8_t* const zeros = mv_smem + 2u * MV_RED_BYTES;                 // 128 bytes: x of a token that does not exist
+    uint8_t* const xs = zeros + 128u;
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
     const uint32_t g = lane >> 2, t = lane & 3u;
     const uint32_t k = a.k, kc = a.kc;
@@ -80,10 +81,10 @@ __global__ void __launch_bounds__(MV_THREADS) matvec_fp4_kernel(const MatvecArgs
     const uint32_t slices = (k + MV_SLICE - 1u) / MV_SLICE;             // per row block
     const uint32_t row_blocks = a.n / MV_ROWS;
     const bool resident = kc >= k;                                      // all of x staged once
-    const bool lane_in_k_always = (k % MV_SLICE) == 0u;
+    constexpr bool lane_in_k_always = !RAGGED;
 
-    const uint32_t tok_lo = g, tok_hi = g + 8u;
-    const bool have_lo = tok_lo < a.m, have_hi = HI && tok_hi < a.m;
+    // lanes whose token does not exist (and lanes past the end of K) read the zero block instead
+    const bool have_lo = g < a.m, have_hi = HI && (g + 8u) < a.m;
 
     // x[:, k0:k1] -> shared memory, 8 bytes at a time (coalesced in, conflict-free out)
     auto stage_x = [&](uint32_t k0, uint32_t k1) {
@@ -93,18 +94,21 @@ __global__ void __launch_bounds__(MV_THREADS) matvec_fp4_kernel(const MatvecArgs
             const uint2 v = __ldg(reinterpret_cast<const uint2*>(a.x + (size_t)tok * k + k0) + u);
             *reinterpret_cast<uint2*>(xs + tok * pitch + (u >> 3) * 72u + (u & 7u) * 8u) = v;
         }
+        if (tid < 16u) *reinterpret_cast<uint2*>(zeros + tid * 8u) = make_uint2(0u, 0u);
     };
 
     // this lane's loads for slice `it` of row block `rb`
+    const size_t q_pitch8 = (size_t)8u * (k / 2), s_pitch8 = (size_t)8u * (k / 16);
     auto load = [&](uint32_t rb, uint32_t it) {
         MvLoad L;
         const uint32_t col = it * MV_SLICE + 32u * t;                   // first of this lane's 32 columns
         if (lane_in_k_always || col < k) {                              // k % 32 == 0: all 32 or none
-            const size_t ra = (size_t)(rb * MV_ROWS + g), rbw = ra + 8u;
-            L.qa = __ldg(reinterpret_cast<const uint4*>(a.wq + ra * (k / 2) + col / 2u));
-            L.qb = __ldg(reinterpret_cast<const uint4*>(a.wq + rbw * (k / 2) + col / 2u));
-            L.sa = __ldg(reinterpret_cast<const unsigned short*>(a.ws + ra * (k / 16) + col / 16u));
-            L.sb = __ldg(reinterpret_cast<const unsigned short*>(a.ws + rbw * (k / 16) + col / 16u));
+            const uint8_t* qa_p = a.wq + (size_t)(rb * MV_ROWS + g) * (k / 2) + col / 2u;
+            const uint8_t* sa_p = a.ws + (size_t)(rb * MV_ROWS + g) * (k / 16) + col / 16u;
+            L.qa = __ldg(reinterpret_cast<const uint4*>(qa_p));
+            L.qb = __ldg(reinterpret_cast<const uint4*>(qa_p + q_pitch8));
+            L.sa = __ldg(reinterpret_cast<const unsigned short*>(sa_p));
+            L.sb = __ldg(reinterpret_cast<const unsigned short*>(sa_p + s_pitch8));
         } else {                                                        // past the end: zero codes, unit scale
             L.qa = make_uint4(0, 0, 0, 0);
             L.qb = make_uint4(0, 0, 0, 0);
@@ -153,8 +157,8 @@ __global__ void __launch_bounds__(MV_THREADS) matvec_fp4_kernel(const MatvecArgs
                 const float ga_e = in_range ? ga : 1.0f, gb_e = in_range ? gb : 1.0f;
                 // this lane's 64 bytes of x per token: run (slice offset / 32 + t), 72 bytes apart
                 const uint32_t xoff = (((it * MV_SLICE - k0) >> 5) + t) * 72u;
-                const uint8_t* x_lo = xs + tok_lo * pitch + xoff;
-                const uint8_t* x_hi = xs + tok_hi * pitch + xoff;
+                const uint8_t* x_lo = (have_lo && in_range) ? xs + g * pitch + xoff : zeros;
+                const uint8_t* x_hi = (have_hi && in_range) ? xs + (g + 8u) * pitch + xoff : zeros;
                 const float2 sca = e4m3x2_to_f32(cur.sa), scb = e4m3x2_to_f32(cur.sb);
 
 #pragma unroll
@@ -171,12 +175,10 @@ __global__ void __launch_bounds__(MV_THREADS) matvec_fp4_kernel(const MatvecArgs
 #pragma unroll
                         for (uint32_t hf = 0; hf < 2; hf++) {
                             const uint32_t unit = 4u * grp + 2u * wd + hf;   // 8-byte unit of the lane's 64 bytes
-                            uint2 bl = make_uint2(0u, 0u);
-                            if (have_lo && in_range) bl = *reinterpret_cast<const uint2*>(x_lo + 8u * unit);
+                            const uint2 bl = *reinterpret_cast<const uint2*>(x_lo + 8u * unit);
                             mma_m16n8k16(c_lo, oa[2 * hf], ob[2 * hf], oa[2 * hf + 1], ob[2 * hf + 1], bl.x, bl.y);
                             if (HI) {
-                                uint2 bh = make_uint2(0u, 0u);
-                                if (have_hi && in_range) bh = *reinterpret_cast<const uint2*>(x_hi + 8u * unit);
+                                const uint2 bh = *reinterpret_cast<const uint2*>(x_hi + 8u * unit);
                                 mma_m16n8k16(c_hi, oa[2 * hf], ob[2 * hf], oa[2 * hf + 1], ob[2 * hf + 1], bh.x, bh.y);
                             }
                         }
