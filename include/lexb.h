@@ -210,6 +210,23 @@ LEXB_API int lexb_gemm_fp4_splitk_static(lexb_gpu* gpu, uint32_t m, uint32_t n, 
                                          const lexb_buffer* x, const lexb_buffer* wq, const lexb_buffer* ws,
                                          const lexb_buffer* wg, const lexb_buffer* r_or_null, lexb_buffer* y);
 
+/* The step after gate/up in the MLP: out = silu(gate) * up, elementwise in f32, written as f16 (what
+ * `down` reads, X_DTYPE in crates/lex-rt/src/qwen_run.rs:317-327) or f32.  The operator is
+ * crates/lex-front/lx/silu_mul.lx / lex_front::llama::silu_mul (crates/lex-front/src/llama.rs:858-891).
+ * gate and up are f32 [rows, cols] views given by a buffer, an offset and a row pitch in elements, so
+ * that one gemm_fp4 launch over gate's and up's rows concatenated ([m, 2n] output) feeds it directly:
+ * gate = (y, 0, 2n), up = (y, n, 2n). */
+LEXB_API int lexb_silu_mul(lexb_gpu* gpu, uint32_t rows, uint32_t cols, const lexb_buffer* gate, size_t gate_offset,
+                           size_t gate_pitch, const lexb_buffer* up, size_t up_offset, size_t up_pitch,
+                           lexb_buffer* out, int out_f16);
+
+/* Runner::chunk / prefill_limit, crates/lex-rt/src/qwen_run.rs:2478-2501 with GEMM_SIZES and MAX_BATCH of
+ * :730-746: how a prompt of `tokens` is cut into prefill chunks - the largest of 512, 256, 128, 64, 32, 16
+ * that fits under `limit` (0 = 512) and the tokens left, then at most 8 at a time for the batched
+ * matvec.  gemm_ok = 0 reproduces the no-GEMM fallback (chunks of 8).  chunks may be null to count. */
+LEXB_API int lexb_prefill_chunks(uint32_t tokens, uint32_t limit, int gemm_ok, uint32_t* chunks, uint32_t max_chunks,
+                                 uint32_t* count);
+
 /* Column-parallel sharding over `world` devices (new: the reference is single-GPU,
  * crates/lex-cuda/src/device.rs:358-359).  Rank `rank` owns weight rows [*n0, *n1) - whole
  * 128-row tiles, the remainder spread over the first ranks - of wq, ws and wg, and writes the

@@ -155,6 +155,36 @@ __global__ void dequant_fp4_f16_kernel(uint32_t n, uint32_t k, const uint8_t* __
     }
 }
 
+// a = silu(g) * u = g * (1 / (1 + exp(-g))) * u, evaluated in f32 in that order
+// (crates/lex-front/src/llama.rs:879-888, sigmoid as crates/lex-front/src/ir.rs:244), four columns per thread.
+template <typename OutT>
+__global__ void silu_mul_kernel(uint32_t rows, uint32_t cols, const float* __restrict__ g, size_t g_pitch,
+                                const float* __restrict__ u, size_t u_pitch, OutT* __restrict__ out) {
+    const uint32_t c4 = cols / 4u;
+    const size_t total = static_cast<size_t>(rows) * c4;
+    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total;
+         i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        const size_t r = i / c4, c = (i - r * c4) * 4u;
+        const float4 gv = *reinterpret_cast<const float4*>(g + r * g_pitch + c);
+        const float4 uv = *reinterpret_cast<const float4*>(u + r * u_pitch + c);
+        const float gg[4] = {gv.x, gv.y, gv.z, gv.w}, uu[4] = {uv.x, uv.y, uv.z, uv.w};
+        float y[4];
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const float sg = __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-gg[j])));
+            y[j] = __fmul_rn(__fmul_rn(gg[j], sg), uu[j]);
+        }
+        if constexpr (sizeof(OutT) == 4) {
+            *reinterpret_cast<float4*>(reinterpret_cast<float*>(out) + r * cols + c) = make_float4(y[0], y[1], y[2], y[3]);
+        } else {
+            uint2 packed;
+            packed.x = lexb::pack_f16x2_rn(y[0], y[1]);
+            packed.y = lexb::pack_f16x2_rn(y[2], y[3]);
+            *reinterpret_cast<uint2*>(reinterpret_cast<uint16_t*>(out) + r * cols + c) = packed;
+        }
+    }
+}
+
 int encode_2d(const lexb_pipeline* p, CUtensorMap* map, CUtensorMapDataType dt, uint32_t esize, const void* ptr,
               uint64_t inner, uint64_t outer, uint32_t box_inner, uint32_t box_outer, CUtensorMapSwizzle swz,
               const char* what) {
@@ -901,6 +931,59 @@ int lexb_gemm_fp4_splitk_static(lexb_gpu* g, uint32_t m, uint32_t n, uint32_t k,
     const uint32_t blocks = static_cast<uint32_t>(std::min<size_t>((elems / 4 + 255) / 256, 148u * 8u));
     lexb::splitk_reduce_kernel<<<blocks, 256, 0, g->stream>>>(g->static_scratch, splits, elems, a.r, a.y, lexb::GatherDst{});
     CUDA_TRY(cudaGetLastError());
+    return LEXB_OK;
+}
+
+int lexb_silu_mul(lexb_gpu* g, uint32_t rows, uint32_t cols, const lexb_buffer* gate, size_t gate_offset, size_t gate_pitch,
+                  const lexb_buffer* up, size_t up_offset, size_t up_pitch, lexb_buffer* out, int out_f16) {
+    int rc = use(g);
+    if (rc) return rc;
+    if (!gate || !up || !out) return fail(LEXB_ERR_ARG, "lexb_silu_mul: null buffer");
+    if (rows == 0 || cols == 0 || cols % 4u) return fail(LEXB_ERR_SHAPE, "silu_mul: 4 must divide cols = %u", cols);
+    if (gate_pitch < cols || up_pitch < cols || (gate_pitch | up_pitch | gate_offset | up_offset) % 4u)
+        return fail(LEXB_ERR_ARG, "silu_mul: pitches and offsets are in f32 elements, multiples of 4, pitch >= cols");
+    const size_t need_g = (gate_offset + static_cast<size_t>(rows - 1) * gate_pitch + cols) * 4;
+    const size_t need_u = (up_offset + static_cast<size_t>(rows - 1) * up_pitch + cols) * 4;
+    if ((rc = check_buf(gate, g, need_g, "gate"))) return rc;
+    if ((rc = check_buf(up, g, need_u, "up"))) return rc;
+    if ((rc = check_buf(out, g, static_cast<size_t>(rows) * cols * (out_f16 ? 2 : 4), "out"))) return rc;
+    const size_t total = static_cast<size_t>(rows) * (cols / 4u);
+    const uint32_t blocks = static_cast<uint32_t>(std::min<size_t>((total + 255) / 256, 148u * 16u));
+    const float* gp = static_cast<const float*>(gate->ptr) + gate_offset;
+    const float* up_ = static_cast<const float*>(up->ptr) + up_offset;
+    if (out_f16)
+        silu_mul_kernel<uint16_t><<<blocks, 256, 0, g->stream>>>(rows, cols, gp, gate_pitch, up_, up_pitch, static_cast<uint16_t*>(out->ptr));
+    else
+        silu_mul_kernel<float><<<blocks, 256, 0, g->stream>>>(rows, cols, gp, gate_pitch, up_, up_pitch, static_cast<float*>(out->ptr));
+    CUDA_TRY(cudaGetLastError());
+    return LEXB_OK;
+}
+
+int lexb_prefill_chunks(uint32_t tokens, uint32_t limit, int gemm_ok, uint32_t* chunks, uint32_t max_chunks, uint32_t* count) {
+    static const uint32_t GEMM_SIZES[6] = {512, 256, 128, 64, 32, 16};
+    const uint32_t MAX_BATCH = 8;
+    if (!count) return fail(LEXB_ERR_ARG, "lexb_prefill_chunks: null count");
+    // prefill_limit: the largest GEMM size that is <= the wanted chunk (512 when 0), else MAX_BATCH
+    uint32_t lim = MAX_BATCH;
+    if (gemm_ok) {
+        const uint32_t want = limit ? limit : 512u;
+        for (uint32_t s : GEMM_SIZES)
+            if (s <= want) { lim = s; break; }
+    }
+    uint32_t left = tokens, n = 0;
+    while (left > 0) {
+        uint32_t take = left < MAX_BATCH ? left : MAX_BATCH;
+        if (gemm_ok)
+            for (uint32_t s : GEMM_SIZES)
+                if (s <= lim && s <= left) { take = s; break; }
+        if (chunks) {
+            if (n >= max_chunks) return fail(LEXB_ERR_ARG, "lexb_prefill_chunks: more than %u chunks", max_chunks);
+            chunks[n] = take;
+        }
+        n++;
+        left -= take;
+    }
+    *count = n;
     return LEXB_OK;
 }
 

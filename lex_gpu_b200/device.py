@@ -28,7 +28,7 @@ SYMBOLS = [
     "lexb_pipeline_free", "lexb_pipeline_describe", "lexb_gemm_fp4_launch", "lexb_gemm_fp4_run_host",
     "lexb_run_launches", "lexb_run_each_timed", "lexb_time_launches", "lexb_status_word",
     "lexb_selftest_bounded_wait", "lexb_dequant_fp4_f16", "lexb_shard_rows", "lexb_trace_enable", "lexb_trace_read",
-    "lexb_gemm_fp4_splitk_static", "lexb_gemm_fp4_launch_gather",
+    "lexb_gemm_fp4_splitk_static", "lexb_gemm_fp4_launch_gather", "lexb_silu_mul", "lexb_prefill_chunks",
 ]
 
 
@@ -111,6 +111,8 @@ def load_library() -> ctypes.CDLL:
     L.lexb_dequant_fp4_f16.argtypes = [vp, u32, u32, vp, vp, vp, vp]
     L.lexb_shard_rows.argtypes = [u32, u32, u32, POINTER(u32), POINTER(u32)]
     L.lexb_trace_enable.argtypes = [vp, u32]
+    L.lexb_silu_mul.argtypes = [vp, u32, u32, vp, sz, sz, vp, sz, sz, vp, c_int]
+    L.lexb_prefill_chunks.argtypes = [u32, u32, c_int, POINTER(u32), u32, POINTER(u32)]
     L.lexb_gemm_fp4_launch_gather.argtypes = [vp, vp, vp, vp, vp, vp, vp, POINTER(vp), u32, u32, u32]
     L.lexb_gemm_fp4_splitk_static.argtypes = [vp, u32, u32, u32, u32, vp, vp, vp, vp, vp, vp]
     L.lexb_trace_read.argtypes = [vp, vp, u32]
@@ -121,6 +123,16 @@ def load_library() -> ctypes.CDLL:
 def _check(rc: int) -> None:
     if rc != 0:
         raise LexbError(rc, load_library().lexb_last_error().decode(errors="replace"))
+
+
+def prefill_chunks(tokens: int, limit: int = 0, gemm_ok: bool = True) -> list[int]:
+    """How lex-rt cuts a prompt into prefill chunks (host arithmetic only; needs no GPU)."""
+    L = load_library()
+    count = c_uint32()
+    _check(L.lexb_prefill_chunks(tokens, limit, int(gemm_ok), None, 0, byref(count)))
+    arr = (c_uint32 * max(count.value, 1))()
+    _check(L.lexb_prefill_chunks(tokens, limit, int(gemm_ok), arr, count.value, byref(count)))
+    return [arr[i] for i in range(count.value)]
 
 
 def shard_rows(n: int, world: int, rank: int) -> tuple[int, int]:
@@ -356,6 +368,12 @@ class Gpu:
         r, y = (bufs[4], bufs[5]) if len(bufs) == 6 else (None, bufs[4])
         _check(self._L.lexb_gemm_fp4_splitk_static(self.handle, m, n, k, k_splits, x.handle, wq.handle, ws.handle,
                                                    wg.handle, r.handle if r is not None else None, y.handle))
+
+    def silu_mul(self, rows: int, cols: int, gate: Buffer, up: Buffer, out: Buffer, out_f16: bool = True,
+                 gate_offset: int = 0, gate_pitch: int = 0, up_offset: int = 0, up_pitch: int = 0) -> None:
+        """out = silu(gate) * up; offsets and pitches in f32 elements (pitch 0 = cols)."""
+        _check(self._L.lexb_silu_mul(self.handle, rows, cols, gate.handle, gate_offset, gate_pitch or cols, up.handle,
+                                     up_offset, up_pitch or cols, out.handle, int(out_f16)))
 
     def trace_enable(self, max_ctas: int) -> None:
         _check(self._L.lexb_trace_enable(self.handle, max_ctas))

@@ -241,6 +241,19 @@ def f64_restatement(x16, wq, ws, wg) -> np.ndarray:
     return x16.view(np.float16).astype(np.float64) @ w.T
 
 
+def np_silu_mul(g: np.ndarray, u: np.ndarray, out_f16: bool = False) -> np.ndarray:
+    """silu(g) * u as the interpreter evaluates lex_front::llama::silu_mul (crates/lex-front/src/llama.rs:879-888,
+    sigmoid = 1 / (1 + exp(-x)), crates/lex-front/src/ir.rs:244): f32 throughout, one rounding per operation,
+    then the optional conversion to f16."""
+    g = g.astype(np.float32)
+    u = u.astype(np.float32)
+    one = np.float32(1.0)
+    with np.errstate(over="ignore"):
+        sg = one / (one + np.exp(-g, dtype=np.float32))
+        y = (g * sg) * u
+    return y.astype(np.float16) if out_f16 else y
+
+
 def ensure_built() -> None:
     build()
     if not os.path.exists(HERE / "liblexoracle.so"):

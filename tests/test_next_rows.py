@@ -1,0 +1,135 @@
+"""The rows either side of the hot path: the prefill chunk policy, the on-disk NVFP4 triple, and
+silu_mul between gate/up and down (CPU parts here; the GPU parts are marked gpu)."""
+import numpy as np
+import pytest
+
+import lex_gpu_b200 as L
+from lex_gpu_b200 import checkpoint, inputs
+from oracle import oracle as O
+
+
+def _chunks_restated(tokens, limit=0, gemm_ok=True):
+    """Runner::chunk + prefill_limit (crates/lex-rt/src/qwen_run.rs:2478-2501), restated."""
+    sizes, max_batch = [512, 256, 128, 64, 32, 16], 8
+    lim = next((g for g in sizes if g <= (limit or 512)), max_batch) if gemm_ok else max_batch
+    out, left = [], tokens
+    while left:
+        take = next((g for g in sizes if gemm_ok and g <= lim and g <= left), min(left, max_batch))
+        out.append(take)
+        left -= take
+    return out
+
+
+def test_prefill_chunk_policy_matches_the_runner():
+    for tokens in list(range(0, 70)) + [127, 128, 129, 511, 512, 513, 1000, 2048, 4095, 8191]:
+        for limit in (0, 512, 300, 128, 16, 9):
+            assert L.prefill_chunks(tokens, limit) == _chunks_restated(tokens, limit), (tokens, limit)
+        assert L.prefill_chunks(tokens, gemm_ok=False) == _chunks_restated(tokens, gemm_ok=False)
+    assert L.prefill_chunks(1000) == [512, 256, 128, 64, 32, 8]
+    assert sum(L.prefill_chunks(8191)) == 8191
+
+
+def test_nvfp4_blob_round_trip_and_nibble_order(tmp_path):
+    wq, ws, wg = inputs.make_weights(48, 256, seed_base=4)
+    path = tmp_path / "blob.safetensors"
+    checkpoint.write_nvfp4(path, {"blk.0.ffn_gate.weight": (wq, ws, 0.75), "blk.0.ffn_up.weight": (wq[::-1].copy(), ws, 1.5)})
+    assert set(checkpoint.tensor_names(path)) >= {"blk.0.ffn_gate.weight", "blk.0.ffn_gate.weight.scale"}
+    q2, s2, g2 = checkpoint.read_nvfp4(path, "blk.0.ffn_gate.weight")
+    assert np.array_equal(q2, wq) and np.array_equal(s2, ws) and np.array_equal(g2, np.full(48, 0.75, np.float32))
+    # the file's own statement of the order: value k of a little-endian u32 word is bits 4k..4k+3
+    # (scripts/qwen_nvfp4.py:75-82) - the same codes the operator's nibble rule gives (interp.rs:650)
+    words = q2.view("<u4")
+    nib = np.empty((48, 256), dtype=np.uint8)
+    for kk in range(8):
+        nib[:, kk::8] = (words >> (4 * kk)) & 0xF
+    assert np.array_equal(nib, O.np_codes(q2))
+    with pytest.raises(KeyError):
+        checkpoint.read_nvfp4(path, "blk.0.ffn_down.weight")
+
+
+def test_silu_mul_oracle_matches_the_formula():
+    """lex_front::llama tests::silu_mul_matches_the_formula (crates/lex-front/src/llama.rs:1412-1429)."""
+    rng = np.random.Generator(np.random.PCG64(1))
+    g, u = rng.standard_normal(4096).astype(np.float32) * 4, rng.standard_normal(4096).astype(np.float32)
+    want = (g.astype(np.float64) / (1.0 + np.exp(-g.astype(np.float64))) * u).astype(np.float32)
+    assert O.max_rel_err(O.np_silu_mul(g, u), want) < 1e-6
+
+
+@pytest.fixture(scope="module")
+def gpu():
+    from lex_gpu_b200 import build
+    build.build()
+    g = L.Gpu(0)
+    yield g
+    g.close()
+
+
+@pytest.mark.gpu
+def test_silu_mul_on_device(gpu):
+    rng = np.random.Generator(np.random.PCG64(2))
+    rows, cols = 37, 1024
+    g = (rng.standard_normal((rows, cols)) * 6).astype(np.float32)
+    u = rng.standard_normal((rows, cols)).astype(np.float32) * 3
+    g[0, :4] = [0.0, -0.0, 88.0, -104.0]
+    gb, ub = gpu.upload(g), gpu.upload(u)
+    o32, o16 = gpu.alloc(rows * cols * 4), gpu.alloc(rows * cols * 2)
+    gpu.silu_mul(rows, cols, gb, ub, o32, out_f16=False)
+    gpu.silu_mul(rows, cols, gb, ub, o16, out_f16=True)
+    got32 = gpu.download(o32, np.float32, (rows, cols))
+    got16 = gpu.download(o16, np.float16, (rows, cols))
+    want = O.np_silu_mul(g, u)
+    assert O.max_rel_err(got32, want) < 1e-6                       # the reference's own tolerance
+    # f16 output: the same value rounded once; at most one f16 step where the f32 values differ by an ulp
+    d = np.abs(got16.astype(np.float32) - want.astype(np.float16).astype(np.float32))
+    assert np.all(d <= np.abs(want) * 2.0 ** -10 + 1e-7)
+    with pytest.raises(L.LexbError):
+        gpu.silu_mul(rows, 1022, gb, ub, o32, out_f16=False)
+
+
+@pytest.mark.gpu
+def test_mlp_block_gate_up_fused_silu_down(gpu, tmp_path):
+    """One MLP block as lex-rt runs it (crates/lex-rt/src/qwen_run.rs:3165-3189), from a synthetic blob:
+    gate and up in ONE gemm_fp4 launch over their rows concatenated, silu_mul to f16, down with the
+    residual - every stage against the oracle."""
+    m, hidden, ffn = 96, 512, 1024
+    rng = np.random.Generator(np.random.PCG64(3))
+    mats = {}
+    for i, (name, n, k) in enumerate([("gate", ffn, hidden), ("up", ffn, hidden), ("down", hidden, ffn)]):
+        wq, ws, _ = inputs.make_weights(n, k, seed_base=30 + i)
+        mats[name] = (wq, ws, [0.02, 0.03, 0.01][i])
+    path = tmp_path / "mlp.safetensors"
+    checkpoint.write_nvfp4(path, {f"blk.0.ffn_{k}.weight": v for k, v in mats.items()})
+    W = {k: checkpoint.read_nvfp4(path, f"blk.0.ffn_{k}.weight") for k in mats}
+    x = inputs.make_x(m, hidden, seed_base=3)
+    resid = rng.standard_normal((m, hidden)).astype(np.float32)
+
+    # oracle
+    yg = O.gemm_fp4(x, *W["gate"])
+    yu = O.gemm_fp4(x, *W["up"])
+    a16 = O.np_silu_mul(yg, yu, out_f16=True)
+    want = O.gemm_fp4(a16, *W["down"], r=resid)
+
+    # device: concatenated gate|up weights, one launch; silu_mul reads the two halves of its output
+    cat = [np.concatenate([W["gate"][i], W["up"][i]], axis=0) for i in range(3)]
+    qgu, qd = L.QBuf(gpu, *cat), L.QBuf(gpu, *W["down"])
+    xb, rb = gpu.upload(x), gpu.upload(resid)
+    ygu, act, yout = gpu.alloc(m * 2 * ffn * 4), gpu.alloc(m * ffn * 2), gpu.alloc(m * hidden * 4)
+    p1, p2 = gpu.plan_gemm_fp4(m, 2 * ffn, hidden), gpu.plan_gemm_fp4(m, hidden, ffn, residual=True)
+    gpu.run(p1, qgu.bind(xb, None, ygu))
+    gpu.silu_mul(m, ffn, ygu, ygu, act, out_f16=True, gate_pitch=2 * ffn, up_offset=ffn, up_pitch=2 * ffn)
+    gpu.run(p2, qd.bind(act, rb, yout))
+    got_gu = gpu.download(ygu, np.float32, (m, 2 * ffn))
+    got_act = gpu.download(act, np.float16, (m, ffn))
+    got = gpu.download(yout, np.float32, (m, hidden))
+    assert gpu.status_word() == 0
+    e1, s1, r1 = O.err_of_scale(got_gu, np.concatenate([yg, yu], axis=1))
+    assert s1 > 1e-3 and e1 <= 2e-3 and r1 <= 2e-3
+    # silu_mul on the device's own gate/up: equal to the oracle's evaluation of the same inputs up to one f16 step
+    a_dev_in = O.np_silu_mul(got_gu[:, :ffn], got_gu[:, ffn:], out_f16=True).astype(np.float32)
+    assert np.all(np.abs(got_act.astype(np.float32) - a_dev_in) <= np.abs(a_dev_in) * 2.0 ** -10 + 1e-7)
+    # down on the device's own activation, against the oracle on that same activation
+    e2, s2, r2 = O.err_of_scale(got, O.gemm_fp4(got_act, *W["down"], r=resid))
+    assert s2 > 1e-3 and e2 <= 2e-3 and r2 <= 2e-3
+    # and the whole block against the oracle's chain, of scale (inputs of the last stage differ by f16 steps)
+    e3, s3, _ = O.err_of_scale(got, want)
+    assert s3 > 1e-3 and e3 <= 2e-3
