@@ -123,9 +123,14 @@ def test_a_token_does_not_depend_on_its_batch(gpu):
 # ---------------------------------------------------------------- tcgen05 path (m > 16)
 
 def test_gemm_config0_readme_example(gpu):
-    """m = n = 128, k = 64: one tile, one K step (BASELINE config 0)."""
+    """m = n = 128, k = 64: one tile, one K step (BASELINE config 0); also against the committed fixture."""
+    from pathlib import Path
     x, wq, ws, wg = inputs.make_case(128, 128, 64)
-    check(L.gemm_fp4(gpu, x, wq, ws, wg), O.gemm_fp4(x, wq, ws, wg))
+    got = L.gemm_fp4(gpu, x, wq, ws, wg)
+    check(got, O.gemm_fp4(x, wq, ws, wg))
+    gold = np.load(Path(__file__).resolve().parent / "golden" / "config0.npz")
+    check(got, gold["y"])
+    assert np.array_equal(L.dequant_fp4_f16(gpu, wq, ws, wg), gold["w16"])
 
 
 @pytest.mark.parametrize("bm,bn,bk", [(128, 128, 64)])

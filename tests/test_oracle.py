@@ -153,3 +153,29 @@ def test_scale_generator_stays_in_the_normal_range():
     assert wg.min() >= 0.5 and wg.max() < 2.0
     # nearest-even rounding of the generator: exact values map to themselves
     assert np.array_equal(inputs.nearest_e4m3(O.E4M3[1:0x7F].astype(np.float64)), np.arange(1, 0x7F, dtype=np.uint8))
+
+
+GOLDEN = __import__("pathlib").Path(__file__).resolve().parent / "golden"
+
+
+def test_decode_tables_equal_the_references_python_tables():
+    """tests/golden/decode_tables.npz was written by importing the reference's scripts/qwen_nvfp4.py
+    (tests/golden/make_golden.py): its E2M1 and E4M3 tables, and a small matrix dequantised with them."""
+    gold = np.load(GOLDEN / "decode_tables.npz")
+    L = O.lib()
+    assert np.array_equal(np.array([L.lexo_e2m1(c) for c in range(16)], dtype=np.float32), gold["e2m1"])
+    assert np.array_equal(np.signbit(gold["e2m1"]), np.array([c >= 8 for c in range(16)]))
+    ours = np.array([L.lexo_e4m3(b) for b in range(256)], dtype=np.float32)
+    nan = np.isnan(gold["e4m3"])
+    assert np.array_equal(np.isnan(ours), nan) and np.array_equal(ours[~nan], gold["e4m3"][~nan])
+    wg = np.full(gold["wq"].shape[0], gold["gs"], dtype=np.float32)
+    assert np.array_equal(O.np_dequant_f32(gold["wq"], gold["ws"], wg), gold["w_f32"])
+    with np.errstate(over="ignore"):
+        assert np.array_equal(O.dequant_fp4_f16(gold["wq"], gold["ws"], wg), gold["w_f32"].astype(np.float16).view(np.uint16))
+
+
+def test_config0_regression_pin():
+    gold = np.load(GOLDEN / "config0.npz")
+    x, wq, ws, wg = inputs.make_case(128, 128, 64)
+    assert np.array_equal(O.gemm_fp4(x, wq, ws, wg), gold["y"])
+    assert np.array_equal(O.dequant_fp4_f16(wq, ws, wg), gold["w16"])
