@@ -115,11 +115,15 @@ gemm_fp4_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const _
         tmem_alloc_pair(smem_u32(tmem_slot), PAIR_TMEM_COLS);
         tmem_relinquish_pair();
     }
+    allow_dependents();                                      // the next launch may be scheduled as SMs free up
     tc_fence_before_sync();
     __syncthreads();
     cluster_sync_all();                                      // both CTAs' barriers exist before any remote arrive
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
+    // Everything above touched only this block's shared memory and TMEM.  From here on the kernel
+    // reads x, the weights and r and writes y: wait for the launch ahead of this one in the stream.
+    grid_dependency_wait();
 
     if (warp == PAIR_WARP_TMA) {
         // ---------------------------------------------------------------- TMA producer (both CTAs)

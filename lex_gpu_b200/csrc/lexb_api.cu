@@ -59,6 +59,7 @@ struct lexb_gpu {
     cudaStream_t own_stream = nullptr;
     cudaStream_t stream = nullptr;       // own_stream or the caller's
     uint32_t* d_status = nullptr;
+    bool pdl = true;                         // programmatic dependent launch of the two-CTA GEMM
     float* static_scratch = nullptr;         // device address of g_splitk_static_scratch on this device, once resolved
     unsigned long long* d_trace = nullptr;   // phase timers of the last two-CTA launch, when tracing is on
     size_t trace_ctas = 0;
@@ -274,10 +275,23 @@ int launch_one(lexb_gpu* g, const lexb_pipeline* p, const lexb_buffer* x, const 
         a.x_tx_bytes = p->kernel == KERNEL_TCGEN05_PAIR ? (p->m < lexb::PAIR_XBLK_ROWS ? p->m : lexb::PAIR_XBLK_ROWS) * 128u
                                                         : (p->tm < p->m ? p->tm : p->m) * 128u;
         if (p->kernel == KERNEL_TCGEN05_PAIR) {
+            // Programmatic dependent launch: this kernel's blocks may be scheduled while the previous
+            // launch of the stream drains (they wait for it before touching global memory), which
+            // hides most of the gap between two launches.  LEXB_PDL=0 turns it off.
+            cudaLaunchConfig_t cfg{};
+            cfg.gridDim = dim3(p->grid);
+            cfg.blockDim = dim3(p->threads);
+            cfg.dynamicSmemBytes = p->smem;
+            cfg.stream = g->stream;
+            cudaLaunchAttribute attr[1];
+            attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+            attr[0].val.programmaticStreamSerializationAllowed = 1;
+            cfg.attrs = attr;
+            cfg.numAttrs = g->pdl ? 1 : 0;
             if (a.trace)
-                lexb::gemm_fp4_tcgen05_pair_kernel<true><<<p->grid, p->threads, p->smem, g->stream>>>(maps.map, maps.map_wq, maps.map_ws, a);
+                CUDA_TRY(cudaLaunchKernelEx(&cfg, lexb::gemm_fp4_tcgen05_pair_kernel<true>, maps.map, maps.map_wq, maps.map_ws, a));
             else
-                lexb::gemm_fp4_tcgen05_pair_kernel<false><<<p->grid, p->threads, p->smem, g->stream>>>(maps.map, maps.map_wq, maps.map_ws, a);
+                CUDA_TRY(cudaLaunchKernelEx(&cfg, lexb::gemm_fp4_tcgen05_pair_kernel<false>, maps.map, maps.map_wq, maps.map_ws, a));
             if (p->k_splits > 1) {
                 CUDA_TRY(cudaGetLastError());
                 const size_t elems = static_cast<size_t>(p->m) * p->n;       // n % 128 == 0: a multiple of 4
@@ -344,6 +358,7 @@ int lexb_open(int device, lexb_gpu** out) {
         return bail(fail(LEXB_ERR_UNSUPPORTED, "device %d is %s (compute %d.%d); the kernels are built for sm_100a only",
                          device, g->prop.name, g->prop.major, g->prop.minor));
     g->smem_optin = g->prop.sharedMemPerBlockOptin;
+    g->pdl = env_u32("LEXB_PDL", 1) != 0;
     if (cudaStreamCreateWithFlags(&g->own_stream, cudaStreamNonBlocking) != cudaSuccess)
         return bail(fail(LEXB_ERR_CUDA, "cudaStreamCreate failed"));
     g->stream = g->own_stream;

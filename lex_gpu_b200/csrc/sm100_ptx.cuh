@@ -76,6 +76,14 @@ __device__ __forceinline__ bool elect_one() {
     return pred != 0;
 }
 
+// Programmatic dependent launch: a kernel launched with the programmatic-stream-serialization
+// attribute may start before the kernel ahead of it in the stream has finished; it must not touch
+// global memory that kernel may still write (or that it still reads and this one overwrites) before
+// grid_dependency_wait() returns.  allow_dependents() lets the next such kernel be scheduled as soon as
+// resources free up.  Both are no-ops in a launch without the attribute.
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void allow_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 __device__ __forceinline__ void fence_proxy_async_smem() {
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
