@@ -117,8 +117,9 @@ gemm_fp4_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmAr
         if (lane == 0) {
             uint32_t issued = 0;
             bool ok = true;
-            for (uint32_t kb = 0; kb < KB && ok; kb++) {
-                const uint32_t s = kb % S, ph = (kb / S) & 1u;
+            RingPos pp;
+            for (uint32_t kb = 0; kb < KB && ok; kb++, pp.advance(S)) {
+                const uint32_t s = pp.s, ph = pp.ph;
                 if (!mbar_wait(empty(s), ph ^ 1u, abort_flag)) {
                     atomicOr(a.status, ST_WAIT_EMPTY_TMA);
                     *abort_flag = 1;
@@ -151,8 +152,10 @@ gemm_fp4_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmAr
             const uint32_t idesc = umma_idesc_f16_f32(GEMM_TN, a.tm);
             const uint32_t x_lo0 = umma_desc_lo(base), stage16 = stage_bytes >> 4, w_off16 = x_bytes >> 4;
             bool ok = true;
-            for (uint32_t kb = 0; kb < KB; kb++) {
-                const uint32_t s = kb % S, ph = (kb / S) & 1u;
+            RingPos pp;
+            uint32_t acc_sel = 0;                        // which accumulator takes this K step
+            for (uint32_t kb = 0; kb < KB; kb++, pp.advance(S)) {
+                const uint32_t s = pp.s, ph = pp.ph;
                 if (!__all_sync(0xFFFFFFFFu, mbar_wait(x_full(s), ph, abort_flag))) {
                     atomicOr(a.status, ST_WAIT_X_FULL);
                     *abort_flag = 1;
@@ -169,7 +172,8 @@ gemm_fp4_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmAr
                 const uint32_t b_lo = x_lo0 + s * stage16, a_lo = b_lo + w_off16;
                 // Two accumulators halve the run of truncating f32 additions each one sees (the
                 // tensor core does not round to nearest when it accumulates).
-                const uint32_t d = tmem_base + (kb % a.n_acc) * a.tm;
+                const uint32_t d = tmem_base + acc_sel * a.tm;
+                if (++acc_sel == a.n_acc) acc_sel = 0;
                 if (elect_one()) {
                     umma1_flag(d, a_lo, b_lo, idesc, kb >= a.n_acc);
 #pragma unroll
@@ -196,8 +200,9 @@ gemm_fp4_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmAr
         uint4 q0 = __ldg(qrow), q1 = KB > 1 ? __ldg(qrow + 2) : make_uint4(0, 0, 0, 0);
         uint32_t s0 = __ldg(srow), s1 = KB > 1 ? __ldg(srow + 1) : 0u;
         bool ok = true;
-        for (uint32_t kb = 0; kb < KB; kb++) {
-            const uint32_t s = kb % S, ph = (kb / S) & 1u;
+        RingPos pp;
+        for (uint32_t kb = 0; kb < KB; kb++, pp.advance(S)) {
+            const uint32_t s = pp.s, ph = pp.ph;
             const uint4 q = q0;
             const uint32_t sw = s0 >> (16u * h);
             q0 = q1;

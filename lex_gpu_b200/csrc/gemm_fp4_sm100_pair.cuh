@@ -128,8 +128,9 @@ gemm_fp4_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const _
     if (warp == PAIR_WARP_TMA) {
         // ---------------------------------------------------------------- TMA producer (both CTAs)
         if (lane == 0) {
-            for (uint32_t kb = 0; kb < KB; kb++) {
-                const uint32_t s = kb % SX, ph = (kb / SX) & 1u;
+            RingPos px;
+            for (uint32_t kb = 0; kb < KB; kb++, px.advance(SX)) {
+                const uint32_t s = px.s, ph = px.ph;
                 if (!mbar_wait(x_empty(s), ph ^ 1u, abort_flag)) {
                     atomicOr(a.status, ST_WAIT_EMPTY_TMA);
                     *abort_flag = 1;
@@ -157,8 +158,9 @@ gemm_fp4_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const _
         // ---------------------------------------------------------------- TMA of packed weights (both CTAs)
         if (lane == 0) {
             const uint32_t RB = (KB + 3u) / 4u, rb0 = kb0 / 4u;
-            for (uint32_t rb = 0; rb < RB; rb++) {
-                const uint32_t rs = rb % PAIR_RAW_STAGES, ph = (rb / PAIR_RAW_STAGES) & 1u;
+            RingPos pr;
+            for (uint32_t rb = 0; rb < RB; rb++, pr.advance(PAIR_RAW_STAGES)) {
+                const uint32_t rs = pr.s, ph = pr.ph;
                 if (!mbar_wait(raw_empty(rs), ph ^ 1u, abort_flag)) {
                     atomicOr(a.status, ST_WAIT_EMPTY_TMA);
                     *abort_flag = 1;
@@ -181,8 +183,9 @@ gemm_fp4_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const _
             // ------------------------------------------------------------ partner: relay of w_full
             // One cluster-scope arrive per K step from this otherwise idle thread, so that the
             // dequant threads only ever touch barriers of their own CTA.
-            for (uint32_t kb = 0; kb < KB; kb++) {
-                const uint32_t s = kb % SW, ph = (kb / SW) & 1u;
+            RingPos pw;
+            for (uint32_t kb = 0; kb < KB; kb++, pw.advance(SW)) {
+                const uint32_t s = pw.s, ph = pw.ph;
                 if (!mbar_wait(w_full(s), ph, abort_flag)) {
                     atomicOr(a.status, ST_WAIT_W_FULL);
                     *abort_flag = 1;
@@ -200,9 +203,10 @@ gemm_fp4_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const _
             const bool reuse_a = (a.flags & 1u) != 0u;
             bool ok = true;
             long long wait_x = 0, wait_w = 0, wait_p = 0, t_first = 0, t_issue = 0, t_commit = 0;
-            for (uint32_t kb = 0; kb < KB; kb++) {
-                const uint32_t s = kb % SX, ph = (kb / SX) & 1u;
-                const uint32_t sw = kb % SW, phw = (kb / SW) & 1u;
+            RingPos px, pw;
+            for (uint32_t kb = 0; kb < KB; kb++, px.advance(SX), pw.advance(SW)) {
+                const uint32_t s = px.s, ph = px.ph;
+                const uint32_t sw = pw.s, phw = pw.ph;
                 long long tw0 = 0, tw1 = 0, tw2 = 0;
                 if (TRACE) tw0 = clock64();
                 if (!__all_sync(0xFFFFFFFFu, mbar_wait_cluster(x_full(s), ph, abort_flag))) {
@@ -303,10 +307,12 @@ gemm_fp4_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const _
         bool ok = true;
         long long dq_wait_raw = 0, dq_wait_empty = 0, dq_t0 = 0;
         if (TRACE) dq_t0 = clock64();
-        for (uint32_t kb = 0; kb < KB; kb++) {
-            const uint32_t s = kb % SW, ph = (kb / SW) & 1u;
-            const uint32_t jj = kb & 3u, rb = kb >> 2;
-            const uint32_t rs = rb % PAIR_RAW_STAGES, rph = (rb / PAIR_RAW_STAGES) & 1u;
+        RingPos pw, pr;
+        for (uint32_t kb = 0; kb < KB; kb++, pw.advance(SW)) {
+            const uint32_t s = pw.s, ph = pw.ph;
+            const uint32_t jj = kb & 3u;
+            if (jj == 0u && kb != 0u) pr.advance(PAIR_RAW_STAGES);
+            const uint32_t rs = pr.s, rph = pr.ph;
             long long tq0 = 0;
             if (TRACE) tq0 = clock64();
             // waits are made warp-uniform (a vote) so that a give-up leaves no lane behind at a __syncwarp

@@ -537,13 +537,12 @@ int lexb_gemm_fp4_plan(lexb_gpu* g, uint32_t m, uint32_t n, uint32_t k, int resi
     if (!s.kc) s.kc = env_u32("LEXB_KC", 0);
     if (!s.w_stages) s.w_stages = env_u32("LEXB_WSTAGES", 0);
     if (!s.k_splits) s.k_splits = env_u32("LEXB_KSPLITS", 0);
-    // m <= 8: matvec (it also takes 9..16 when asked, but the GEMMs are faster there).  Otherwise the two-CTA GEMM when the shape allows it (k in blocks of 256), except
-    // for few tokens with enough 128-row tiles to fill the SMs, where the one-CTA kernel is a little faster;
-    // the one-CTA kernel also takes the shapes the two-CTA kernel cannot (k % 256 != 0).
+    // m <= 8: matvec (it also takes 9..16 when asked, but the GEMMs are faster there).  Otherwise the
+    // two-CTA GEMM when the shape allows it (k in blocks of 256); the one-CTA kernel takes the rest.
     uint32_t kernel = s.kernel;
     if (!kernel) {
         if (m <= 8 || ((n % lexb::GEMM_TN || k % lexb::GEMM_BK) && m <= 16)) kernel = KERNEL_MATVEC;
-        else if (n % lexb::GEMM_TN == 0 && k % lexb::PAIR_RAW_K == 0 && !(m <= 128 && n / lexb::GEMM_TN >= 120))
+        else if (n % lexb::GEMM_TN == 0 && k % lexb::PAIR_RAW_K == 0)
             kernel = KERNEL_TCGEN05_PAIR;
         else kernel = KERNEL_TCGEN05;
     }

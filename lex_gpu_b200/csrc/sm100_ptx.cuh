@@ -8,6 +8,18 @@
 
 namespace lexb {
 
+// Position in a ring of `depth` stages: stage index and phase bit, advanced without the integer
+// division that `k % depth`, `(k / depth) & 1` would cost on every K step of a single-warp role.
+struct RingPos {
+    uint32_t s = 0, ph = 0;
+    __device__ __forceinline__ void advance(uint32_t depth) {
+        if (++s == depth) {
+            s = 0;
+            ph ^= 1u;
+        }
+    }
+};
+
 // Status codes a kernel may OR into the status word (0 = clean run).
 enum : uint32_t {
     ST_WAIT_X_FULL = 1u << 0,      // MMA thread gave up waiting for a TMA x tile

@@ -323,7 +323,7 @@ def test_describe_mirrors_the_lowered_descriptor(gpu):
     d = gpu.plan_gemm_fp4(256, 17408, 5120).describe()
     assert d.entry.decode() == "gemm_fp4_256_17408_5120_256_256_64" and d.kernel == 3 and d.grid == 136
     d = gpu.plan_gemm_fp4(64, 17408, 5120).describe()
-    assert d.entry.decode() == "gemm_fp4_64_17408_5120_64_128_64" and d.kernel == 2 and d.grid == 136
+    assert d.entry.decode() == "gemm_fp4_64_17408_5120_256_256_64" and d.kernel == 3 and d.grid == 136
     assert gpu.plan_gemm_fp4(64, 2176, 5120).describe().kernel == 3         # few tiles: split K on CTA pairs
     assert gpu.plan_gemm_fp4(64, 256, 320).describe().kernel == 2           # k not in blocks of 256
     d = gpu.plan_gemm_fp4(4, 17408, 5120, residual=True).describe()
