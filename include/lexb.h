@@ -57,13 +57,20 @@ typedef struct lexb_device_info {
  * (crates/lex-front/lx/gemm_fp4.lx:38-39) and of the LEX_GEMM_CU_* variables
  * (crates/lex-msl/src/gemm.rs:90-135).  Zero fields mean "choose". */
 typedef struct lexb_sched {
-    uint32_t kernel;  /* 0 auto, 1 split-K matvec (m <= 16), 2 tcgen05 GEMM, 3 two-CTA tcgen05 GEMM (m > 256) */
+    uint32_t kernel;  /* 0 auto, 1 split-K matvec (m <= 16), 2 tcgen05 GEMM, 3 two-CTA tcgen05 GEMM,
+                       * 4 block-scaled FP4 tensor-core kernel (m <= 4; matmul_q_x arithmetic, never chosen by auto) */
     uint32_t tm;      /* tokens per CTA tile of the GEMM: multiple of 16, <= 256 */
     uint32_t stages;  /* pipeline depth of the GEMM */
     uint32_t kc;      /* K columns of x staged per chunk in the matvec: multiple of 1024 */
     uint32_t w_stages; /* two-CTA GEMM: depth of the ring of decoded W tiles (stages = depth of the x ring) */
     uint32_t k_splits; /* two-CTA GEMM: split K this many ways (partials in a workspace the pipeline owns, then summed) */
+    uint32_t flags;    /* LEXB_SCHED_* bits */
 } lexb_sched;
+/* Block-scaled kernel only.  By default it treats wq and ws as constants of the stream: launched with
+ * programmatic stream serialization, it starts loading them while the kernel ahead of it in the stream
+ * is still running (x, r and y wait for that kernel as usual).  Set this bit when a kernel launched
+ * just before on the same stream writes the weights; copies and other streams' work are ordered anyway. */
+#define LEXB_SCHED_WEIGHTS_MAY_CHANGE 1u
 
 /* lex_msl::program::Lowered, crates/lex-msl/src/program.rs:44-63: the launch descriptor.
  * `writes` is per binding in the order [x, wq, ws, wg, (r), y] (crates/lex-msl/src/gemm.rs:78-82). */
@@ -74,7 +81,7 @@ typedef struct lexb_lowered {
     uint32_t threadgroup_bytes;  /* dynamic shared memory */
     uint32_t nbind;
     uint8_t writes[6];
-    uint32_t kernel;             /* 1 matvec, 2 tcgen05, 3 two-CTA tcgen05 */
+    uint32_t kernel;             /* 1 matvec, 2 tcgen05, 3 two-CTA tcgen05, 4 block-scaled FP4 */
     uint32_t m, n, k, residual;
     uint32_t bm, bn, bk, stages;
     uint32_t k_splits;           /* > 1: a second launch sums the partial products */
@@ -209,6 +216,20 @@ LEXB_API int lexb_dequant_fp4_f16(lexb_gpu* gpu, uint32_t n, uint32_t k, const l
 LEXB_API int lexb_gemm_fp4_splitk_static(lexb_gpu* gpu, uint32_t m, uint32_t n, uint32_t k, uint32_t k_splits,
                                          const lexb_buffer* x, const lexb_buffer* wq, const lexb_buffer* ws,
                                          const lexb_buffer* wg, const lexb_buffer* r_or_null, lexb_buffer* y);
+
+/* lex_front::llama::matmul_q_x with the NVFP4 layout (crates/lex-front/src/llama.rs:444-499): the
+ * operator the model runs for decode and speculative verification (t <= 8,
+ * crates/lex-rt/src/qwen_run.rs:2605-2606), same bindings [x, wq, ws, wg, (r), y] as gemm_fp4 but with
+ * the weights used as dequantised f32 values (e2m1 * e4m3 * wg, crates/lex-front/src/interp.rs:643-657),
+ * not rounded to f16.  The pipeline is launched like any other (lexb_gemm_fp4_launch, lexb_step).
+ * Here: t <= 4 tokens of f16 activations (x_half != 0; f32 x is refused), n_out % 128 == 0,
+ * n_in % 256 == 0.  The decode runs on the tensor cores' block-scaled FP4 path, which takes wq and ws
+ * as stored; each token is split exactly into eight rows of 2-bit E2M1 digits (16 significant bits
+ * below the largest value of every group of 16).  Results agree with the interpreter to about 1e-5 of
+ * scale (gate 2e-3, crates/lex-cuda/tests/device_gpu.rs:294-303); the entry name is the reference's
+ * (matvec_nvfp4_{n_out}x{n_in}[_res]_xh, matmul{t}_... for t > 1). */
+LEXB_API int lexb_matmul_fp4_plan(lexb_gpu* gpu, uint32_t t, uint32_t n_out, uint32_t n_in, int residual, int x_half,
+                                  const lexb_sched* sched_or_null, lexb_pipeline** out);
 
 /* The step after gate/up in the MLP: out = silu(gate) * up, elementwise in f32, written as f16 (what
  * `down` reads, X_DTYPE in crates/lex-rt/src/qwen_run.rs:317-327) or f32.  The operator is

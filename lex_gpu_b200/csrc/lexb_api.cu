@@ -20,6 +20,7 @@
 #include "gemm_fp4_sm100.cuh"
 #include "gemm_fp4_sm100_pair.cuh"
 #include "matvec_fp4_sm100.cuh"
+#include "matmul_q_fp4_sm100.cuh"
 
 // Scratch of lexb_gemm_fp4_splitk_static: split-K partial products [splits][m][n] f32.  Part of
 // the library image, so every GPU that loads the library holds these 32 MiB until the process exits.
@@ -50,7 +51,7 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
-enum { KERNEL_MATVEC = 1, KERNEL_TCGEN05 = 2, KERNEL_TCGEN05_PAIR = 3 };
+enum { KERNEL_MATVEC = 1, KERNEL_TCGEN05 = 2, KERNEL_TCGEN05_PAIR = 3, KERNEL_MATMUL_Q = 4 };
 
 }  // namespace
 
@@ -83,6 +84,7 @@ struct lexb_pipeline {
     // tcgen05 GEMM
     uint32_t tm, stages, w_stages, tmem_cols, m_tiles, n_acc, flags;
     uint32_t k_splits = 1, kb_per_split = 0, tok_blocks = 2;
+    uint32_t ws_pitch = 0;      // block-scaled kernel: bytes per row of one scale load
     float* partial = nullptr;   // split-K workspace [k_splits][m][n], owned by the pipeline
     // matvec
     uint32_t kc;
@@ -203,7 +205,7 @@ int encode_2d(const lexb_pipeline* p, CUtensorMap* map, CUtensorMapDataType dt, 
 // Tensor maps for one binding, cached by the device pointers they were encoded for.
 int get_maps(const lexb_pipeline* p, const void* x, const void* wq, const void* ws, lexb_pipeline::MapEntry* out) {
     std::lock_guard<std::mutex> lk(p->maps_lock);
-    const bool pair = p->kernel == KERNEL_TCGEN05_PAIR;
+    const bool pair = p->kernel == KERNEL_TCGEN05_PAIR || p->kernel == KERNEL_MATMUL_Q;
     for (const auto& e : p->maps)
         if (e.x == x && (!pair || (e.wq == wq && e.ws == ws))) {
             *out = e;
@@ -215,7 +217,8 @@ int get_maps(const lexb_pipeline* p, const void* x, const void* wq, const void* 
     // x f16[m, k] row-major; box = 64 columns (128 bytes, the swizzle span) x the tile's tokens, never
     // taller than the tensor.  Rows past m are filled with zeros by the copy engine.
     const uint32_t box_rows = pair ? (p->m < lexb::PAIR_XBLK_ROWS ? p->m : lexb::PAIR_XBLK_ROWS) : (p->tm < p->m ? p->tm : p->m);
-    if ((rc = encode_2d(p, &e.map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, x, p->k, p->m, lexb::GEMM_BK, box_rows,
+    if (p->kernel != KERNEL_MATMUL_Q &&      // that kernel reads x with plain loads
+        (rc = encode_2d(p, &e.map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, x, p->k, p->m, lexb::GEMM_BK, box_rows,
                         CU_TENSOR_MAP_SWIZZLE_128B, "x")))
         return rc;
     if (pair) {
@@ -223,7 +226,8 @@ int get_maps(const lexb_pipeline* p, const void* x, const void* wq, const void* 
         if ((rc = encode_2d(p, &e.map_wq, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, wq, p->k / 2, p->n, lexb::PAIR_RAW_K / 2,
                             lexb::GEMM_TN, CU_TENSOR_MAP_SWIZZLE_128B, "wq")))
             return rc;
-        if ((rc = encode_2d(p, &e.map_ws, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, ws, p->k / 16, p->n, lexb::PAIR_RAW_K / 16,
+        const uint32_t ws_box = p->kernel == KERNEL_MATMUL_Q ? p->ws_pitch : lexb::PAIR_RAW_K / 16;
+        if ((rc = encode_2d(p, &e.map_ws, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, ws, p->k / 16, p->n, ws_box,
                             lexb::GEMM_TN, CU_TENSOR_MAP_SWIZZLE_NONE, "ws")))
             return rc;
     }
@@ -301,6 +305,38 @@ int launch_one(lexb_gpu* g, const lexb_pipeline* p, const lexb_buffer* x, const 
         } else {
             lexb::gemm_fp4_tcgen05_kernel<<<p->grid, p->threads, p->smem, g->stream>>>(maps.map, a);
         }
+    } else if (p->kernel == KERNEL_MATMUL_Q) {
+        lexb_pipeline::MapEntry maps;
+        if ((rc = get_maps(p, x->ptr, wq->ptr, ws->ptr, &maps))) return rc;
+        lexb::MatmulQArgs a{};
+        a.x = static_cast<const __half*>(x->ptr);
+        a.wg = static_cast<const float*>(wg->ptr);
+        a.r = r ? static_cast<const float*>(r->ptr) : nullptr;
+        a.y = static_cast<float*>(y->ptr);
+        a.partial = p->partial;
+        a.status = g->d_status;
+        a.m = p->m; a.n = p->n; a.k = p->k; a.stages = p->stages;
+        a.k_splits = p->k_splits; a.kb_per_split = p->kb_per_split;
+        a.ws_pitch = p->ws_pitch; a.flags = p->flags;
+        cudaLaunchConfig_t cfg{};
+        cfg.gridDim = dim3(p->grid);
+        cfg.blockDim = dim3(p->threads);
+        cfg.dynamicSmemBytes = p->smem;
+        cfg.stream = g->stream;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = g->pdl ? 1 : 0;
+        a.trace = (g->d_trace && p->grid <= g->trace_ctas) ? g->d_trace : nullptr;
+        if (a.trace) CUDA_TRY(cudaLaunchKernelEx(&cfg, lexb::matmul_q_fp4_kernel<true>, maps.map_wq, maps.map_ws, a));
+        else CUDA_TRY(cudaLaunchKernelEx(&cfg, lexb::matmul_q_fp4_kernel<false>, maps.map_wq, maps.map_ws, a));
+        if (p->k_splits > 1) {
+            CUDA_TRY(cudaGetLastError());
+            const size_t elems = static_cast<size_t>(p->m) * p->n;
+            const uint32_t blocks = static_cast<uint32_t>(std::min<size_t>((elems / 4 + 255) / 256, 148u * 8u));
+            lexb::splitk_reduce_kernel<<<blocks, 256, 0, g->stream>>>(p->partial, p->k_splits, elems, a.r, a.y, lexb::GatherDst{});
+        }
     } else {
         lexb::MatvecArgs a{};
         a.x = static_cast<const __half*>(x->ptr);
@@ -377,7 +413,9 @@ int lexb_open(int device, lexb_gpu** out) {
         cudaFuncSetAttribute(lexb::matvec_fp4_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem) != cudaSuccess ||
         cudaFuncSetAttribute(lexb::matvec_fp4_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem) != cudaSuccess ||
         cudaFuncSetAttribute(lexb::matvec_fp4_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem) != cudaSuccess ||
-        cudaFuncSetAttribute(lexb::matvec_fp4_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem) != cudaSuccess)
+        cudaFuncSetAttribute(lexb::matvec_fp4_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem) != cudaSuccess ||
+        cudaFuncSetAttribute(lexb::matmul_q_fp4_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem) != cudaSuccess ||
+        cudaFuncSetAttribute(lexb::matmul_q_fp4_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem) != cudaSuccess)
         return bail(fail(LEXB_ERR_CUDA, "cudaFuncSetAttribute(max dynamic shared memory) failed: %s", cudaGetErrorString(cudaGetLastError())));
     *out = g;
     return LEXB_OK;
@@ -547,7 +585,7 @@ int lexb_gemm_fp4_plan(lexb_gpu* g, uint32_t m, uint32_t n, uint32_t k, int resi
         else kernel = KERNEL_TCGEN05;
     }
     if (kernel == KERNEL_MATVEC && m > 16) return fail(LEXB_ERR_SHAPE, "the matvec kernel takes m <= 16, not %u", m);
-    if (kernel < KERNEL_MATVEC || kernel > KERNEL_TCGEN05_PAIR) return fail(LEXB_ERR_ARG, "unknown kernel selector %u", kernel);
+    if (kernel < KERNEL_MATVEC || kernel > KERNEL_MATMUL_Q) return fail(LEXB_ERR_ARG, "unknown kernel selector %u", kernel);
 
     lexb_pipeline* p = new (std::nothrow) lexb_pipeline();
     if (!p) return fail(LEXB_ERR_ARG, "out of host memory");
@@ -558,7 +596,39 @@ int lexb_gemm_fp4_plan(lexb_gpu* g, uint32_t m, uint32_t n, uint32_t k, int resi
     auto bail = [&](int code) { lexb_pipeline_free(p); return code; };
     const char* stem = residual ? "gemm_fp4_res" : "gemm_fp4";
 
-    if (kernel == KERNEL_TCGEN05) {
+    if (kernel == KERNEL_MATMUL_Q) {
+        // Only through lexb_matmul_fp4_plan or an explicit selector: its arithmetic is matmul_q_x's
+        // (weights not rounded to f16), within gemm_fp4's tolerance but not its rounding.
+        if (m > lexb::MQ_MAX_TOKENS) return bail(fail(LEXB_ERR_SHAPE, "the block-scaled kernel takes at most %u tokens, not %u", lexb::MQ_MAX_TOKENS, m));
+        if (n % lexb::MQ_ROWS) return bail(fail(LEXB_ERR_SHAPE, "matmul_q (nvfp4): %u rows per block do not divide n = %u", lexb::MQ_ROWS, n));
+        if (k % lexb::MQ_STAGE_K) return bail(fail(LEXB_ERR_SHAPE, "matmul_q (nvfp4): blocks of %u columns do not divide k = %u", lexb::MQ_STAGE_K, k));
+        uint32_t stages = s.stages ? s.stages : lexb::MQ_MAX_STAGES;
+        if (stages < 2 || stages > lexb::MQ_MAX_STAGES || lexb::matmul_q_smem_bytes(stages) > g->smem_optin)
+            return bail(fail(LEXB_ERR_ARG, "stages = %u outside [2, %u] or over the shared-memory limit", stages, lexb::MQ_MAX_STAGES));
+        const uint32_t tiles = n / lexb::MQ_ROWS, kb_all = k / lexb::MQ_STAGE_K;
+        const uint32_t sms = static_cast<uint32_t>(g->prop.multiProcessorCount);
+        // one K range per block; split K when the row tiles alone leave most SMs idle
+        uint32_t splits = s.k_splits ? s.k_splits : (tiles * 2u <= sms ? sms / tiles : 1u);
+        if (splits > 8u) splits = 8u;
+        while (splits > 1u && kb_all / splits < 4u) splits--;
+        if (splits < 1u) splits = 1u;
+        const uint32_t per = (kb_all + splits - 1u) / splits;
+        splits = (kb_all + per - 1u) / per;
+        p->k_splits = splits; p->kb_per_split = per; p->stages = stages;
+        p->ws_pitch = k / 16u < 16u * lexb::MQ_WS_GROUP ? k / 16u : 16u * lexb::MQ_WS_GROUP;
+        // the weights are taken as constant (loaded ahead of the stream's order) unless the caller says otherwise
+        p->flags = (s.flags & LEXB_SCHED_WEIGHTS_MAY_CHANGE) ? 0u : 1u;
+        if (splits > 1u) {
+            cudaError_t e = cudaMalloc(&p->partial, sizeof(float) * splits * static_cast<size_t>(m) * n);
+            if (e != cudaSuccess) return bail(fail(LEXB_ERR_CUDA, "allocating the split-K workspace: %s", cudaGetErrorString(e)));
+        }
+        p->grid = tiles * splits;
+        p->threads = lexb::MQ_THREADS;
+        p->smem = lexb::matmul_q_smem_bytes(stages);
+        p->tm = m;
+        if (p->entry[0] == 0)
+            snprintf(p->entry, sizeof p->entry, "%s_%u_%u_%u_%u_%u_%u", stem, m, n, k, m, lexb::MQ_ROWS, lexb::MQ_STAGE_K);
+    } else if (kernel == KERNEL_TCGEN05) {
         if (n % lexb::GEMM_TN) return bail(fail(LEXB_ERR_SHAPE, "gemm_fp4: bn = %u does not divide n = %u", lexb::GEMM_TN, n));
         if (k % lexb::GEMM_BK) return bail(fail(LEXB_ERR_SHAPE, "gemm_fp4: bk = %u does not divide k = %u", lexb::GEMM_BK, k));
         uint32_t tm = s.tm;
@@ -665,6 +735,25 @@ int lexb_gemm_fp4_plan(lexb_gpu* g, uint32_t m, uint32_t n, uint32_t k, int resi
     return LEXB_OK;
 }
 
+int lexb_matmul_fp4_plan(lexb_gpu* g, uint32_t t, uint32_t n_out, uint32_t n_in, int residual, int x_half,
+                         const lexb_sched* sched, lexb_pipeline** out) {
+    if (!out) return fail(LEXB_ERR_ARG, "lexb_matmul_fp4_plan: null out");
+    *out = nullptr;
+    if (!x_half) return fail(LEXB_ERR_UNSUPPORTED, "matmul_q (nvfp4): f32 activations are not implemented; narrow x to f16 (x_half)");
+    lexb_sched s{};
+    if (sched) s = *sched;
+    s.kernel = KERNEL_MATMUL_Q;
+    int rc = lexb_gemm_fp4_plan(g, t, n_out, n_in, residual, &s, out);
+    if (rc) return rc;
+    // the reference's name for the program: matvec / matmul{t}, layout tag, rows x columns, _res, _xh
+    // (crates/lex-front/src/llama.rs:416-422, :459-465)
+    char tag[16];
+    if (t == 1) snprintf(tag, sizeof tag, "matvec");
+    else snprintf(tag, sizeof tag, "matmul%u", t);
+    snprintf((*out)->entry, sizeof (*out)->entry, "%s_nvfp4_%ux%u%s_xh", tag, n_out, n_in, residual ? "_res" : "");
+    return LEXB_OK;
+}
+
 void lexb_pipeline_free(lexb_pipeline* p) {
     if (!p) return;
     if (p->partial) {
@@ -686,7 +775,11 @@ int lexb_pipeline_describe(const lexb_pipeline* p, lexb_lowered* out) {
     out->writes[out->nbind - 1] = 1;
     out->kernel = p->kernel;
     out->m = p->m; out->n = p->n; out->k = p->k; out->residual = p->residual;
-    if (p->kernel == KERNEL_TCGEN05 || p->kernel == KERNEL_TCGEN05_PAIR) {
+    if (p->kernel == KERNEL_MATMUL_Q) {
+        out->bm = p->m; out->bn = lexb::MQ_ROWS; out->bk = lexb::MQ_STAGE_K; out->stages = p->stages;
+        out->k_splits = p->k_splits;
+        out->scratch_bytes = p->partial ? sizeof(float) * p->k_splits * static_cast<uint64_t>(p->m) * p->n : 0;
+    } else if (p->kernel == KERNEL_TCGEN05 || p->kernel == KERNEL_TCGEN05_PAIR) {
         out->bm = p->tm; out->bn = p->kernel == KERNEL_TCGEN05_PAIR ? 2u * lexb::GEMM_TN : lexb::GEMM_TN;
         out->bk = lexb::GEMM_BK; out->stages = p->stages;
         out->k_splits = p->k_splits;

@@ -1,0 +1,537 @@
+// matmul_q (NVFP4 layout) for a few tokens on the block-scaled FP4 tensor-core path of sm_100a.
+//
+//     y[t, j] = wg[j] * sum_g e4m3(ws[j, g]) * sum_{p in group g} e2m1(wq[j, p]) * x[t, p]   (+ r[t, j])
+//
+// which is lex's `matmul_q_x` with the NVFP4 layout (crates/lex-front/src/llama.rs:444-499, weights
+// dequantised by `Op::DequantFp4`, crates/lex-front/src/interp.rs:643-657) with the row scale
+// factored out of the sum: the weights are NOT rounded to f16 here, unlike in `gemm_fp4`.  This is
+// the operator the model runs for decode and for speculative verification (t <= 8,
+// crates/lex-rt/src/qwen_run.rs:2605-2606).
+//
+// The tensor core does the whole decode: `tcgen05.mma.kind::mxf4nvf4.block_scale` multiplies packed
+// E2M1 codes by a UE4M3 scale per 16 values of K, which is exactly how wq and ws are stored.  The
+// packed codes go from global memory to shared memory by TMA and are never touched by a thread; the
+// integer pipe, which bounds the table-lookup decode of `matvec_fp4_kernel`, is idle here and the
+// kernel streams at memory speed.
+//
+// The activations have to be E2M1 as well.  Each token is split exactly into MQ_PIECES = 8 rows of
+// 2-bit digits: inside a group of 16 values with largest exponent E, a value is sign * I * 2^(E-15)
+// with a 16-bit integer I (the 11-bit significand of the largest value fits with 5 bits to spare;
+// smaller values are rounded to that grid, which is finer than f16's own for anything within 2^5 of
+// the group's maximum), and I = sum_p digit_p * 4^(7-p).  Piece p holds the E2M1 codes of
+// digit_p / 2 (0, 0.5, 1, 1.5 are codes 0..3) and the group scale 2^(E - 2p - G), G a per-token
+// offset that keeps the scales inside UE4M3's range; the epilogue adds the 8 accumulator columns of a
+// token and multiplies by 2^G * wg[j].  So a token costs 8 columns of N, the minimum N of the
+// instruction for one token.
+//
+// Scale bytes with the sign bit set are legal E4M3 (the reference decodes them as negative scales):
+// the hardware scale is unsigned, so the sign is moved into the 16 codes of the group in shared
+// memory.  The two NaN bytes (0x7f, 0xff) make the whole output row NaN, as in the reference.
+//
+// Block = 128 weight rows (one row tile) x one K range; 6 warps: warp 0 issues the TMA loads of codes
+// and scale bytes, warp 1 the scale copies into tensor memory and the MMAs, warps 2-5 write the
+// activations' pieces and re-lay the weight scales for each stage, then run the epilogue.
+#pragma once
+#include <cuda_fp16.h>
+#include <stdint.h>
+
+#include "sm100_ptx.cuh"
+
+namespace lexb {
+
+constexpr uint32_t MQ_ROWS = 128;                         // weight rows per block
+constexpr uint32_t MQ_STAGE_K = 256;                      // values of K per stage: one 128-byte row of codes
+constexpr uint32_t MQ_PIECES = 8;                         // E2M1 digit rows per token
+constexpr uint32_t MQ_MAX_TOKENS = 4;
+constexpr uint32_t MQ_CODE_BYTES = MQ_ROWS * 128u;        // packed codes of a stage
+constexpr uint32_t MQ_B_BYTES = MQ_MAX_TOKENS * MQ_PIECES * 128u;   // the tokens' pieces of a stage
+constexpr uint32_t MQ_SF_BYTES = 4u * 512u;               // one 512-byte scale block per MMA of the stage
+constexpr uint32_t MQ_STAGE_BYTES = MQ_CODE_BYTES + MQ_B_BYTES + 2u * MQ_SF_BYTES;
+// The scale bytes as stored come in their own, coarser ring: one load covers MQ_WS_GROUP stages, so
+// that a row's piece of it is 64 bytes (16 bytes per stage would fetch half-used 32-byte sectors).
+constexpr uint32_t MQ_WS_GROUP = 4;
+constexpr uint32_t MQ_WS_SLOTS = 3;
+constexpr uint32_t MQ_WS_SLOT_BYTES = MQ_ROWS * 16u * MQ_WS_GROUP;
+constexpr uint32_t MQ_SCALE_WARPS = 8;                    // warps 2-5: weight scales of even stages, then the epilogue;
+                                                          // warps 6-9: weight scales of odd stages
+constexpr uint32_t MQ_PIECE_WARPS = 8;                    // warps 10-17: the tokens' digit rows
+constexpr uint32_t MQ_THREADS = 32u * (2u + MQ_SCALE_WARPS + MQ_PIECE_WARPS);
+constexpr uint32_t MQ_TMEM_COLS = 512;
+constexpr uint32_t MQ_MAX_STAGES = 8;
+constexpr uint32_t MQ_TMEM_D1 = 32;                       // second accumulator
+constexpr uint32_t MQ_TMEM_SFA = 64;                      // ring of 16 columns per stage
+constexpr uint32_t MQ_TMEM_SFB = MQ_TMEM_SFA + 16u * MQ_MAX_STAGES;
+
+static_assert(MQ_STAGE_BYTES % 1024u == 0, "every stage starts on a swizzle-pattern boundary");
+
+struct MatmulQArgs {
+    const __half* x;         // [m, k]
+    const float* wg;         // [n]
+    const float* r;          // [m, n] or null
+    float* y;                // [m, n]
+    float* partial;          // [k_splits][m][n] when k_splits > 1
+    uint32_t* status;
+    unsigned long long* trace;   // 16 phase timers per block, or null
+    uint32_t m, n, k, stages;
+    uint32_t k_splits, kb_per_split;   // in stages of 256
+    uint32_t ws_pitch;                 // bytes per row of a scale load: min(64, k / 16)
+    uint32_t flags;                    // bit 0: the weights are constant, load them before the launch ahead has finished
+};
+
+__host__ __device__ constexpr uint32_t matmul_q_smem_bytes(uint32_t stages) {
+    return stages * MQ_STAGE_BYTES + MQ_WS_SLOTS * MQ_WS_SLOT_BYTES + (3u * stages + 1u + 2u * MQ_WS_SLOTS) * 8u + 64u + MQ_ROWS + 1024u;
+}
+
+// bits [2i+1 : 2i] of an 8-bit value -> byte i
+__device__ __forceinline__ uint32_t mq_spread8(uint32_t t) {
+    uint32_t u = (t | (t << 12)) & 0x000F000Fu;
+    return (u | (u << 6)) & 0x03030303u;
+}
+
+// One f16 value -> its 16-bit integer on the grid of a group whose largest biased exponent is e_eff.
+__device__ __forceinline__ uint32_t mq_fixed16(uint32_t h, uint32_t e_eff) {
+    const uint32_t ex = (h >> 10) & 31u, frac = h & 1023u;
+    const uint32_t mant = ex ? (frac | 1024u) : frac;
+    const uint32_t d = e_eff - (ex ? ex : 1u);
+    return ((mant << 5) + ((1u << d) >> 1)) >> d;
+}
+
+// UE4M3 byte of 2^q (0 when it is below the smallest subnormal)
+__device__ __forceinline__ uint32_t mq_ue4m3_pow2(int q) {
+    if (q >= -6) return static_cast<uint32_t>(q + 7) << 3;
+    if (q >= -9) return 1u << (q + 9);
+    return 0u;
+}
+
+template <bool TRACE>
+__global__ void __launch_bounds__(MQ_THREADS, 1)
+matmul_q_fp4_kernel(const __grid_constant__ CUtensorMap tmap_wq, const __grid_constant__ CUtensorMap tmap_ws, MatmulQArgs a) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw_addr = smem_u32(smem_raw);
+    const uint32_t base = (raw_addr + 1023u) & ~1023u;
+    uint8_t* const smem = smem_raw + (base - raw_addr);
+
+    const uint32_t S = a.stages;
+    auto codes_of = [&](uint32_t s) { return base + s * MQ_STAGE_BYTES; };
+    auto b_of = [&](uint32_t s) { return codes_of(s) + MQ_CODE_BYTES; };
+    auto sfa_of = [&](uint32_t s) { return b_of(s) + MQ_B_BYTES; };
+    auto sfb_of = [&](uint32_t s) { return sfa_of(s) + MQ_SF_BYTES; };
+    const uint32_t ws_base = base + S * MQ_STAGE_BYTES;                   // MQ_WS_SLOTS slots of scale bytes as stored
+    const uint32_t bars = ws_base + MQ_WS_SLOTS * MQ_WS_SLOT_BYTES;
+    auto raw_full = [&](uint32_t s) { return bars + 8u * s; };            // TMA bytes of the stage landed
+    auto prep_full = [&](uint32_t s) { return bars + 8u * (S + s); };     // pieces and scale blocks written
+    auto empty = [&](uint32_t s) { return bars + 8u * (2u * S + s); };    // the stage's MMAs are done
+    const uint32_t acc_full = bars + 8u * 3u * S;
+    auto ws_full = [&](uint32_t r) { return bars + 8u * (3u * S + 1u + r); };
+    auto ws_empty = [&](uint32_t r) { return bars + 8u * (3u * S + 1u + MQ_WS_SLOTS + r); };    // all eight scale warps
+    uint32_t* const misc = reinterpret_cast<uint32_t*>(smem + (bars - base) + (3u * S + 1u + 2u * MQ_WS_SLOTS) * 8u);
+    uint32_t* const tmem_slot = misc;
+    volatile uint32_t* const abort_flag = misc + 1;
+    uint32_t* const tok_amax = misc + 2;                                   // [MQ_MAX_TOKENS]
+    volatile uint8_t* const nan_rows = reinterpret_cast<volatile uint8_t*>(misc + 16);   // [MQ_ROWS]: a NaN scale byte seen
+
+    const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
+    const uint32_t split = blockIdx.x % a.k_splits, tile = blockIdx.x / a.k_splits;
+    const uint32_t n0 = tile * MQ_ROWS;
+    const uint32_t kb_all = a.k / MQ_STAGE_K;
+    const uint32_t kb0 = split * a.kb_per_split;
+    const uint32_t KB = (kb_all - kb0 < a.kb_per_split) ? (kb_all - kb0) : a.kb_per_split;
+    const uint32_t N = a.m * MQ_PIECES;
+    const long long t_start = clock64();
+
+    if (warp == 0) {
+        // one barrier per lane: the whole set is ready after a few instructions
+        if (lane == 0) {
+            prefetch_tensormap(&tmap_wq);
+            prefetch_tensormap(&tmap_ws);
+            *abort_flag = 0;
+        }
+        if (lane < MQ_MAX_TOKENS) tok_amax[lane] = 0;
+        const uint32_t nbar = 3u * S + 1u + 2u * MQ_WS_SLOTS;
+        for (uint32_t b = lane; b < nbar; b += 32u) {
+            uint32_t count = 1;                                                  // raw_full, empty, acc_full, ws_full
+            if (b >= S && b < 2u * S) count = MQ_SCALE_WARPS / 2u + a.m;         // prep_full: four scale warps, one piece warp per token
+            if (b >= 3u * S + 1u + MQ_WS_SLOTS) count = MQ_SCALE_WARPS;          // ws_empty: every scale warp
+            mbar_init(bars + 8u * b, count);
+        }
+        __syncwarp();
+        long long ta = 0;
+        if (TRACE) ta = clock64();
+        fence_mbar_init();
+        if (TRACE && a.trace && lane == 0)
+            a.trace[16ull * blockIdx.x + 9] = ((unsigned long long)(uint32_t)(clock64() - t_start) << 32) | (uint32_t)(ta - t_start);
+    }
+    if (tid >= 64u && tid < 64u + MQ_ROWS) nan_rows[tid - 64u] = 0;
+    if (warp == 1) {
+        tmem_alloc(smem_u32(tmem_slot), MQ_TMEM_COLS);
+        tmem_relinquish();
+    }
+    if (warp != 0) allow_dependents();
+    // Warp 0 has set up every barrier itself and needs nothing from the others: it announces that and
+    // goes on to its loads, the other warps meet here (named barrier 2).
+    uint32_t tmem_base = 0;
+    if (warp == 0) {
+        asm volatile("bar.arrive 2, %0;" ::"r"(MQ_THREADS) : "memory");
+    } else {
+        tc_fence_before_sync();
+        asm volatile("bar.sync 2, %0;" ::"r"(MQ_THREADS) : "memory");
+        tc_fence_after_sync();
+        tmem_base = *tmem_slot;
+    }
+    // x, r and y belong to the stream's order; the weights may be declared constant, and the warp
+    // that loads them then starts while the launch ahead of this one is still running.
+    if (!((a.flags & 1u) && warp == 0)) grid_dependency_wait();
+
+    if (warp == 0) {
+        // ---------------------------------------------------------------- TMA producer
+        if (lane == 0) {
+            RingPos ps;
+            for (uint32_t kb = 0; kb < KB; kb++, ps.advance(S)) {
+                const uint32_t s = ps.s;
+                if (!mbar_wait(empty(s), ps.ph ^ 1u, abort_flag)) {
+                    atomicOr(a.status, ST_WAIT_EMPTY_TMA);
+                    *abort_flag = 1;
+                    break;
+                }
+                if (TRACE && a.trace && kb == 0) a.trace[16ull * blockIdx.x + 13] = (unsigned long long)clock64();
+                if ((kb & (MQ_WS_GROUP - 1u)) == 0u) {
+                    // scale bytes of this and the next three stages
+                    const uint32_t wsi = kb / MQ_WS_GROUP, r = wsi % MQ_WS_SLOTS, wph = (wsi / MQ_WS_SLOTS) & 1u;
+                    if (!mbar_wait(ws_empty(r), wph ^ 1u, abort_flag)) {
+                        atomicOr(a.status, ST_WAIT_EMPTY_TMA);
+                        *abort_flag = 1;
+                        break;
+                    }
+                    mbar_arrive_expect_tx(ws_full(r), a.ws_pitch * MQ_ROWS);
+                    tma_load_2d(ws_base + r * MQ_WS_SLOT_BYTES, &tmap_ws, (int)((kb0 + kb) * (MQ_STAGE_K / 16)), (int)n0, ws_full(r));
+                }
+                mbar_arrive_expect_tx(raw_full(s), MQ_CODE_BYTES);
+                tma_load_2d(codes_of(s), &tmap_wq, (int)((kb0 + kb) * (MQ_STAGE_K / 2)), (int)n0, raw_full(s));
+                if (kb + 1u == S || kb + 1u == KB) allow_dependents();       // the ring is filled (once is enough; twice is harmless)
+            }
+            if (*abort_flag) {
+                // copies still in flight land in this block's shared memory: give them a bounded time
+                const long long t0 = clock64();
+                while (clock64() - t0 < 400000) {
+                }
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        // ---------------------------------------------------------------- scale copies + MMA issue
+        const uint32_t idesc = umma_idesc_mxf4nvf4(128u, N);
+        if (TRACE && a.trace && lane == 0) a.trace[16ull * blockIdx.x + 15] = (unsigned long long)clock64();
+        bool ok = true;
+        long long w_raw = 0, w_prep = 0, t_issue = 0, t_first = 0;
+        RingPos ps;
+        for (uint32_t kb = 0; kb < KB; kb++, ps.advance(S)) {
+            const uint32_t s = ps.s, ph = ps.ph;
+            long long c0 = 0, c1 = 0, c2 = 0;
+            if (TRACE) c0 = clock64();
+            if (!__all_sync(0xFFFFFFFFu, mbar_wait(raw_full(s), ph, abort_flag))) {
+                atomicOr(a.status, ST_WAIT_X_FULL);
+                *abort_flag = 1;
+                ok = false;
+                break;
+            }
+            if (TRACE) c1 = clock64();
+            if (TRACE && a.trace && kb == 0 && lane == 0) a.trace[16ull * blockIdx.x + 14] = (unsigned long long)c1;
+            if (!__all_sync(0xFFFFFFFFu, mbar_wait(prep_full(s), ph, abort_flag))) {
+                atomicOr(a.status, ST_WAIT_W_FULL);
+                *abort_flag = 1;
+                ok = false;
+                break;
+            }
+            if (TRACE) {
+                c2 = clock64();
+                w_raw += c1 - c0;
+                w_prep += c2 - c1;
+                if (kb == 0) t_first = c2;
+            }
+            tc_fence_after_sync();
+            const uint32_t a_lo = umma_desc_lo(codes_of(s)), b_lo = umma_desc_lo(b_of(s));
+            const uint32_t sfa_t = tmem_base + MQ_TMEM_SFA + 16u * s, sfb_t = tmem_base + MQ_TMEM_SFB + 16u * s;
+            const uint32_t d = tmem_base + ((kb & 1u) ? MQ_TMEM_D1 : 0u);   // two accumulators, alternating
+            if (elect_one()) {
+#pragma unroll
+                for (uint32_t j = 0; j < 4; j++) {
+                    tmem_cp_32x128b_warpx4(sfa_t + 4u * j, umma_desc_scale_block(sfa_of(s) + 512u * j));
+                    tmem_cp_32x128b_warpx4(sfb_t + 4u * j, umma_desc_scale_block(sfb_of(s) + 512u * j));
+                }
+#pragma unroll
+                for (uint32_t j = 0; j < 4; j++)
+                    umma1_mxf4nvf4(d, a_lo + 2u * j, b_lo + 2u * j, idesc, sfa_t + 4u * j, sfb_t + 4u * j,
+                                   (kb >= 2u || j > 0u) ? 1u : 0u);
+                umma_commit(empty(s));
+            }
+            __syncwarp();
+            if (TRACE) t_issue += clock64() - c2;
+        }
+        if (ok && elect_one()) umma_commit(acc_full);
+        __syncwarp();
+        if (TRACE && a.trace && lane == 0) {
+            unsigned long long* tr = a.trace + 16ull * blockIdx.x;
+            tr[0] = (unsigned long long)t_start;
+            tr[1] = (unsigned long long)t_first;     // first stage ready
+            tr[2] = (unsigned long long)clock64();   // all MMAs issued
+            tr[3] = (unsigned long long)w_raw;       // MMA warp: waiting for the copy engine
+            tr[4] = (unsigned long long)w_prep;      // ... for the prep warps
+            tr[5] = (unsigned long long)t_issue;     // ... issuing copies and MMAs
+        }
+    } else if (warp >= 2u + MQ_SCALE_WARPS) {
+        // ---------------------------------------------------------------- piece warps: x -> E2M1 digit rows
+        const uint32_t xw = warp - (2u + MQ_SCALE_WARPS);
+        const uint32_t xt = tid - 32u * (2u + MQ_SCALE_WARPS);
+        const uint32_t items = KB * a.m;                      // item = (stage kb, token t), kb-major
+        // A warp takes every PW-th item.  Its consecutive items must be at most S stages apart: a wait
+        // on a stage's barrier can only tell "this turn of the ring" from the one before it.
+        const uint32_t PW = (S * a.m < MQ_PIECE_WARPS) ? S * a.m : MQ_PIECE_WARPS;
+        // the first item's values are on their way while the token maxima are found
+        uint4 xv = make_uint4(0, 0, 0, 0);
+        if (xw < PW && xw < items) {
+            const uint32_t kb = xw / a.m, t = xw - kb * a.m;
+            xv = __ldg(reinterpret_cast<const uint4*>(a.x + (size_t)t * a.k) + (size_t)(kb0 + kb) * (MQ_STAGE_K / 8u) + lane);
+        }
+        // largest exponent of each token (its scale offset G); the tokens' loads go out together
+        {
+            uint32_t mx[MQ_MAX_TOKENS] = {0, 0, 0, 0};
+            const uint4* xr = reinterpret_cast<const uint4*>(a.x);
+            const uint32_t row_chunks = a.k / 8u;
+            for (uint32_t i = xt; i < row_chunks; i += 32u * MQ_PIECE_WARPS) {
+                uint4 v[MQ_MAX_TOKENS];
+#pragma unroll
+                for (uint32_t t = 0; t < MQ_MAX_TOKENS; t++)
+                    v[t] = t < a.m ? __ldg(xr + (size_t)t * row_chunks + i) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+                for (uint32_t t = 0; t < MQ_MAX_TOKENS; t++) {
+                    mx[t] = __vmaxu2(mx[t], v[t].x & 0x7FFF7FFFu);
+                    mx[t] = __vmaxu2(mx[t], v[t].y & 0x7FFF7FFFu);
+                    mx[t] = __vmaxu2(mx[t], v[t].z & 0x7FFF7FFFu);
+                    mx[t] = __vmaxu2(mx[t], v[t].w & 0x7FFF7FFFu);
+                }
+            }
+#pragma unroll
+            for (uint32_t t = 0; t < MQ_MAX_TOKENS; t++) {
+                if (t < a.m) {
+                    uint32_t r = max(mx[t] & 0xFFFFu, mx[t] >> 16);
+                    r = __reduce_max_sync(0xFFFFFFFFu, r);
+                    if (lane == 0) atomicMax(tok_amax + t, r);
+                }
+            }
+        }
+        // B's scale blocks start as zeros: rows nobody writes must not hold stray NaN patterns
+        for (uint32_t i = xt; i < S * (MQ_SF_BYTES / 16u); i += 32u * MQ_PIECE_WARPS) {
+            const uint32_t s = i / (MQ_SF_BYTES / 16u), o = i % (MQ_SF_BYTES / 16u);
+            *reinterpret_cast<uint4*>(smem + (sfb_of(s) - base) + 16u * o) = make_uint4(0, 0, 0, 0);
+        }
+        asm volatile("bar.sync 1, %0;" ::"r"(32u * MQ_PIECE_WARPS) : "memory");
+        long long p_empty = 0, p_t0 = 0;
+        if (TRACE) p_t0 = clock64();
+        for (uint32_t it = (xw < PW ? xw : items); it < items; it += PW) {
+            const uint32_t kb = it / a.m, tok = it - kb * a.m;
+            const uint32_t s = kb % S, ph = (kb / S) & 1u;
+            const uint4 xc = xv;
+            if (it + PW < items) {
+                const uint32_t kn = (it + PW) / a.m, tn = (it + PW) - kn * a.m;
+                xv = __ldg(reinterpret_cast<const uint4*>(a.x + (size_t)tn * a.k) + (size_t)(kb0 + kn) * (MQ_STAGE_K / 8u) + lane);
+            }
+            const uint32_t tmax_e = tok_amax[tok] >> 10, tmax_eff = tmax_e ? tmax_e : 1u;
+            // ---- 8 values of the token: K offsets 8 lane .. 8 lane + 7 of the stage
+            const uint32_t hw[4] = {xc.x, xc.y, xc.z, xc.w};
+            uint32_t am = 0;
+#pragma unroll
+            for (uint32_t i = 0; i < 4; i++) am = __vmaxu2(am, hw[i] & 0x7FFF7FFFu);
+            am = max(am & 0xFFFFu, am >> 16);
+            am = max(am, __shfl_xor_sync(0xFFFFFFFFu, am, 1));        // a group of 16 is two lanes
+            const uint32_t e = am >> 10, e_eff = e ? e : 1u;
+            uint32_t blo[4], bhi[4];
+#pragma unroll
+            for (uint32_t i = 0; i < 4; i++) {
+                const uint32_t h0 = hw[i] & 0xFFFFu, h1 = hw[i] >> 16;
+                const uint32_t i0 = mq_fixed16(h0, e_eff), i1 = mq_fixed16(h1, e_eff);
+                const uint32_t sg = ((0u - (h0 >> 15)) & 0x08080808u) | ((0u - (h1 >> 15)) & 0x80808080u);
+                blo[i] = mq_spread8(i0 & 0xFFu) | (mq_spread8(i1 & 0xFFu) << 4) | sg;
+                bhi[i] = mq_spread8(i0 >> 8) | (mq_spread8(i1 >> 8) << 4) | sg;
+            }
+            // byte b of blo[i] / bhi[i] is the code pair of piece 7-b / 3-b: transpose 4x4 bytes
+            uint32_t w[8];
+            {
+                const uint32_t t0 = __byte_perm(blo[0], blo[1], 0x5140), t1 = __byte_perm(blo[2], blo[3], 0x5140);
+                const uint32_t t2 = __byte_perm(blo[0], blo[1], 0x7362), t3 = __byte_perm(blo[2], blo[3], 0x7362);
+                w[7] = __byte_perm(t0, t1, 0x5410);
+                w[6] = __byte_perm(t0, t1, 0x7632);
+                w[5] = __byte_perm(t2, t3, 0x5410);
+                w[4] = __byte_perm(t2, t3, 0x7632);
+                const uint32_t u0 = __byte_perm(bhi[0], bhi[1], 0x5140), u1 = __byte_perm(bhi[2], bhi[3], 0x5140);
+                const uint32_t u2 = __byte_perm(bhi[0], bhi[1], 0x7362), u3 = __byte_perm(bhi[2], bhi[3], 0x7362);
+                w[3] = __byte_perm(u0, u1, 0x5410);
+                w[2] = __byte_perm(u0, u1, 0x7632);
+                w[1] = __byte_perm(u2, u3, 0x5410);
+                w[0] = __byte_perm(u2, u3, 0x7632);
+            }
+            long long q0c = 0;
+            if (TRACE) q0c = clock64();
+            if (!__all_sync(0xFFFFFFFFu, mbar_wait(empty(s), ph ^ 1u, abort_flag))) {
+                atomicOr(a.status, ST_WAIT_EMPTY_DEQ);
+                *abort_flag = 1;
+                break;
+            }
+            if (TRACE) p_empty += clock64() - q0c;
+            uint8_t* const bt = smem + (b_of(s) - base) + (tok * MQ_PIECES) * 128u + 4u * (lane & 3u);
+#pragma unroll
+            for (uint32_t pc = 0; pc < MQ_PIECES; pc++)      // row 8 tok + pc: its chunk XOR is pc
+                *reinterpret_cast<uint32_t*>(bt + pc * 128u + (((lane >> 2) ^ pc) << 4)) = w[pc];
+            // scales of this group's pieces: 2^(8 - (token max - group max) - 2 piece)
+            const int q0 = 8 - (int)(tmax_eff - e_eff);
+            const uint32_t grp = lane >> 1;                  // group of 16 within the stage
+            uint8_t* const sb = smem + (sfb_of(s) - base) + (grp >> 2) * 512u + (tok * MQ_PIECES) * 16u + (grp & 3u);
+#pragma unroll
+            for (uint32_t i = 0; i < 4; i++) {
+                const uint32_t pc = 4u * (lane & 1u) + i;
+                sb[pc * 16u] = (uint8_t)mq_ue4m3_pow2(q0 - 2 * (int)pc);
+            }
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(prep_full(s));
+        }
+        if (TRACE && a.trace && xt == 0) {
+            unsigned long long* tr = a.trace + 16ull * blockIdx.x + 11;
+            tr[0] = (unsigned long long)(clock64() - p_t0);   // piece loop of warp 0, total
+            tr[1] = (unsigned long long)p_empty;              // ... waiting for a free stage
+        }
+        __syncwarp();
+    } else {
+        // ---------------------------------------------------------------- scale warps (2-5 also run the epilogue)
+        // Two sets of four warps take the even and the odd stages: one warp's pass over a stage is a
+        // short chain of dependent instructions that a single warp cannot overlap with itself.
+        const uint32_t set = (warp - 2u) >> 2;
+        const uint32_t row = 32u * (warp & 3u) + lane;        // the lanes of tensor memory this warp may read
+        const float g = __ldg(a.wg + n0 + row);
+        bool ok = true;
+        long long p_empty = 0, p_raw = 0, p_t0 = 0;
+        if (TRACE) p_t0 = clock64();
+        RingPos ps;
+        if (set) ps.advance(S);
+        for (uint32_t kb = set; kb < KB; kb += 2u, ps.advance(S), ps.advance(S)) {
+            const uint32_t s = ps.s, ph = ps.ph;
+            long long q0c = 0, q1c = 0;
+            if (TRACE) q0c = clock64();
+            if (!__all_sync(0xFFFFFFFFu, mbar_wait(empty(s), ph ^ 1u, abort_flag))) {
+                atomicOr(a.status, ST_WAIT_EMPTY_DEQ);
+                *abort_flag = 1;
+                ok = false;
+                break;
+            }
+            if (TRACE) q1c = clock64();
+            // ---- this row's 16 scale bytes of the stage -> four scale blocks
+            const uint32_t wsi = kb / MQ_WS_GROUP, wr = wsi % MQ_WS_SLOTS, wph = (wsi / MQ_WS_SLOTS) & 1u;
+            if (!__all_sync(0xFFFFFFFFu, mbar_wait(ws_full(wr), wph, abort_flag))) {
+                atomicOr(a.status, ST_WAIT_X_FULL);
+                *abort_flag = 1;
+                ok = false;
+                break;
+            }
+            if (TRACE) {
+                p_empty += q1c - q0c;
+                p_raw += clock64() - q1c;
+            }
+            const uint4 sc = *reinterpret_cast<const uint4*>(smem + (ws_base - base) + wr * MQ_WS_SLOT_BYTES + row * a.ws_pitch +
+                                                             16u * (kb & (MQ_WS_GROUP - 1u)));
+            if ((kb & (MQ_WS_GROUP - 1u)) >= MQ_WS_GROUP - 2u || kb + 2u >= KB) {   // this warp's last stage of the group
+                __syncwarp();
+                if (lane == 0) mbar_arrive(ws_empty(wr));
+            }
+            uint32_t sv[4] = {sc.x, sc.y, sc.z, sc.w};
+#pragma unroll
+            for (uint32_t j = 0; j < 4; j++) {
+                uint32_t v = sv[j];
+                if (v & 0x80808080u) {
+                    // negative scales: move the sign into the 16 codes of the group (once they are here)
+                    if (!mbar_wait(raw_full(s), ph, abort_flag)) {
+                        atomicOr(a.status, ST_WAIT_X_FULL);
+                        *abort_flag = 1;
+                    }
+                    for (uint32_t i = 0; i < 4; i++) {
+                        if ((v >> (8u * i + 7u)) & 1u) {
+                            const uint32_t bi = 4u * j + i;
+                            uint32_t* cw = reinterpret_cast<uint32_t*>(smem + (codes_of(s) - base) + row * 128u +
+                                                                       (((bi >> 1) ^ (row & 7u)) << 4) + 8u * (bi & 1u));
+                            cw[0] ^= 0x88888888u;
+                            cw[1] ^= 0x88888888u;
+                        }
+                    }
+                    v &= 0x7F7F7F7Fu;
+                }
+                const uint32_t z = v ^ 0x7F7F7F7Fu;
+                if ((z - 0x01010101u) & ~z & 0x80808080u) {      // some byte may be 0x7f: look at each
+                    for (uint32_t i = 0; i < 4; i++) {
+                        if (((v >> (8u * i)) & 0xFFu) == 0x7Fu) {
+                            nan_rows[row] = 1;
+                            v &= ~(0xFFu << (8u * i));
+                        }
+                    }
+                }
+                *reinterpret_cast<uint32_t*>(smem + (sfa_of(s) - base) + 512u * j + (row & 31u) * 16u + (row >> 5) * 4u) = v;
+            }
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(prep_full(s));
+        }
+        if (TRACE && a.trace && tid == 64) {
+            unsigned long long* tr = a.trace + 16ull * blockIdx.x + 6;
+            tr[0] = (unsigned long long)(clock64() - p_t0);   // scale loop of warp 2, total
+            tr[1] = (unsigned long long)p_empty;              // ... waiting for a free stage
+            tr[2] = (unsigned long long)p_raw;                // ... waiting for the scale bytes
+        }
+        // ---------------------------------------------------------------- epilogue (warps 2-5)
+        if (set == 0u) {
+        uint32_t go = 0;
+        if (lane == 0) {
+            go = ok && mbar_wait(acc_full, 0, abort_flag);
+            if (!go) {
+                atomicOr(a.status, ST_WAIT_ACC);
+                *abort_flag = 1;
+            }
+        }
+        go = __shfl_sync(0xFFFFFFFFu, go, 0);
+        if (go) {
+            tc_fence_after_sync();
+            const bool row_nan = nan_rows[row] != 0;
+            const uint32_t lane_base = tmem_base + ((32u * (warp & 3u)) << 16);
+            const bool to_partial = a.k_splits > 1u;
+            float* const out = to_partial ? a.partial + (size_t)split * a.m * a.n : a.y;
+            for (uint32_t t = 0; t < a.m; t++) {
+                uint32_t d0[8], d1[8];
+                tmem_ld_32x32b_x8(lane_base + 8u * t, d0);
+                if (KB > 1u) tmem_ld_32x32b_x8(lane_base + MQ_TMEM_D1 + 8u * t, d1);
+                tmem_ld_wait();
+                float v = 0.0f;
+#pragma unroll
+                for (int pc = 7; pc >= 0; pc--) {                // small pieces first
+                    float c = __uint_as_float(d0[pc]);
+                    if (KB > 1u) c += __uint_as_float(d1[pc]);
+                    v += c;
+                }
+                const uint32_t te = tok_amax[t] >> 10;
+                const uint32_t te_eff = te ? te : 1u;
+                const float tscale = __uint_as_float((te_eff - 23u + 127u) << 23);     // 2^G
+                v = v * tscale * g;
+                if (row_nan || te == 31u) v = __uint_as_float(0x7FC00000u);
+                const size_t o = (size_t)t * a.n + n0 + row;
+                if (!to_partial && a.r) v += __ldg(a.r + o);
+                out[o] = v;
+            }
+        }
+        }
+    }
+
+    tc_fence_before_sync();
+    __syncthreads();
+    if (TRACE && a.trace && tid == 0) a.trace[16ull * blockIdx.x + 10] = (unsigned long long)clock64();   // block done
+    if (warp == 1) {
+        tc_fence_after_sync();
+        tmem_dealloc(tmem_base, MQ_TMEM_COLS);
+    }
+}
+
+}  // namespace lexb

@@ -224,6 +224,55 @@ __host__ __device__ constexpr uint32_t umma_idesc_f16_f32(uint32_t M, uint32_t N
            | ((N >> 3) << 17) | ((M >> 4) << 24);
 }
 
+
+// ---- block-scaled FP4 MMA (kind::mxf4nvf4): E2M1 operands, one UE4M3 scale per 16 values of K ----
+// Both operands are packed E2M1 (two per byte, even K in the low nibble), K-major in the same
+// 128-byte-swizzled layout as above (a 128-byte row is 256 values of K); one instruction covers
+// K = 64 (32 bytes: +2 on the low descriptor half).  The scales of the 128 rows of A (and of the N
+// rows of B) for one instruction sit in tensor memory: lane (row % 32) of every 32-lane quarter,
+// byte 4 * (row / 32) + (group of 16 within the 64), i.e. four 32-bit columns per instruction.
+__host__ __device__ constexpr uint32_t umma_idesc_mxf4nvf4(uint32_t M, uint32_t N) {
+    return (1u << 7)              // A format E2M1
+           | (1u << 10)           // B format E2M1
+           | (0u << 15) | (0u << 16)   // A, B K-major
+           | ((N >> 3) << 17)
+           | (0u << 23)           // scale format UE4M3
+           | ((M >> 4) << 24);    // scale-factor ids (bits 4-5, 29-30) 0: all four bytes of a column are used
+}
+__device__ __forceinline__ void umma1_mxf4nvf4(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t idesc,
+                                               uint32_t sfa_tmem, uint32_t sfb_tmem, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+        "setp.ne.b32 p, %7, 0;\n\t"
+        "mov.b64 da, {%1, %4};\n\tmov.b64 db, {%2, %4};\n\t"
+        "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.block16 [%0], da, db, %3, [%5], [%6], p;\n\t}"
+        ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(idesc), "r"(UMMA_DESC_HI_SW128), "r"(sfa_tmem), "r"(sfb_tmem),
+          "r"(accumulate)
+        : "memory");
+}
+// Descriptor of a 512-byte scale block in shared memory: 32 rows of 16 bytes, contiguous (no swizzle;
+// 8-row core matrices 128 bytes apart).
+__device__ __forceinline__ uint64_t umma_desc_scale_block(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4);
+    d |= 1ull << 16;                                  // leading byte offset: one 16-byte column only
+    d |= static_cast<uint64_t>(128u >> 4) << 32;      // stride byte offset between 8-row groups
+    d |= 1ull << 46;
+    return d;
+}
+// Shared memory -> tensor memory: 32 rows x 16 bytes into lanes 0-31, columns [c, c + 4), repeated in
+// all four 32-lane quarters.  Asynchronous; ordered with the MMAs the same thread issues after it, and
+// tracked by that thread's next commit.
+__device__ __forceinline__ void tmem_cp_32x128b_warpx4(uint32_t taddr, uint64_t sdesc) {
+    asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
+}
+__device__ __forceinline__ void tmem_ld_32x32b_x8(uint32_t taddr, uint32_t (&v)[8]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                 : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7])
+                 : "r"(taddr)
+                 : "memory");
+}
+
 }  // namespace lexb
 
 // ---- two-CTA (cta_group::2) variants: a pair of CTAs in one cluster shares each MMA ------

@@ -29,6 +29,7 @@ SYMBOLS = [
     "lexb_run_launches", "lexb_run_each_timed", "lexb_time_launches", "lexb_status_word",
     "lexb_selftest_bounded_wait", "lexb_dequant_fp4_f16", "lexb_shard_rows", "lexb_trace_enable", "lexb_trace_read",
     "lexb_gemm_fp4_splitk_static", "lexb_gemm_fp4_launch_gather", "lexb_silu_mul", "lexb_prefill_chunks",
+    "lexb_matmul_fp4_plan",
 ]
 
 
@@ -46,7 +47,11 @@ class DeviceInfo(ctypes.Structure):
 
 
 class Sched(ctypes.Structure):
-    _fields_ = [("kernel", c_uint32), ("tm", c_uint32), ("stages", c_uint32), ("kc", c_uint32), ("w_stages", c_uint32), ("k_splits", c_uint32)]
+    _fields_ = [("kernel", c_uint32), ("tm", c_uint32), ("stages", c_uint32), ("kc", c_uint32), ("w_stages", c_uint32), ("k_splits", c_uint32),
+                ("flags", c_uint32)]
+
+
+SCHED_WEIGHTS_MAY_CHANGE = 1
 
 
 class Lowered(ctypes.Structure):
@@ -98,6 +103,7 @@ def load_library() -> ctypes.CDLL:
     L.lexb_host_alloc.argtypes = [sz, POINTER(vp)]
     L.lexb_host_free.argtypes = [vp]
     L.lexb_gemm_fp4_plan.argtypes = [vp, u32, u32, u32, c_int, POINTER(Sched), POINTER(vp)]
+    L.lexb_matmul_fp4_plan.argtypes = [vp, u32, u32, u32, c_int, c_int, POINTER(Sched), POINTER(vp)]
     L.lexb_pipeline_free.argtypes = [vp]
     L.lexb_pipeline_free.restype = None
     L.lexb_pipeline_describe.argtypes = [vp, POINTER(Lowered)]
@@ -309,6 +315,15 @@ class Gpu:
         s = Sched(kernel, tm, stages, kc, w_stages, k_splits)
         h = c_void_p()
         _check(self._L.lexb_gemm_fp4_plan(self.handle, m, n, k, int(residual), byref(s), byref(h)))
+        return Pipeline(self, h.value)
+
+    def plan_matmul_fp4(self, t: int, n_out: int, n_in: int, residual: bool = False, x_half: bool = True,
+                        stages: int = 0, k_splits: int = 0, weights_may_change: bool = False) -> Pipeline:
+        """matmul_q_x with the NVFP4 layout for t <= 4 tokens (llama.rs:444-499): weights as f32, not
+        rounded to f16; runs on the block-scaled FP4 tensor-core path."""
+        s = Sched(0, 0, stages, 0, 0, k_splits, SCHED_WEIGHTS_MAY_CHANGE if weights_may_change else 0)
+        h = c_void_p()
+        _check(self._L.lexb_matmul_fp4_plan(self.handle, t, n_out, n_in, int(residual), int(x_half), byref(s), byref(h)))
         return Pipeline(self, h.value)
 
     def run(self, pipe: Pipeline, bufs: Sequence[Buffer]) -> None:

@@ -96,6 +96,35 @@ def gemm_fp4(gpu: Gpu, x: np.ndarray, wq: np.ndarray, ws: np.ndarray, wg: np.nda
         pipe.close()
 
 
+def matmul_fp4(gpu: Gpu, x: np.ndarray, wq: np.ndarray, ws: np.ndarray, wg: np.ndarray,
+               r: Optional[np.ndarray] = None, **sched) -> np.ndarray:
+    """matmul_q_x with the NVFP4 layout, host arrays in and out (llama.rs:444-499): t <= 4 tokens of f16
+    activations against weights used as f32 (not rounded to f16).  For tests and examples."""
+    m, k = x.shape
+    n = wq.shape[0]
+    if x.dtype != np.float16:
+        raise TypeError("x must be float16 (x_half)")
+    pipe = gpu.plan_matmul_fp4(m, n, k, r is not None, True, **sched)
+    q = QBuf(gpu, wq, ws, wg)
+    xb = gpu.upload(x)
+    rb = gpu.upload(np.ascontiguousarray(r, dtype=np.float32)) if r is not None else None
+    yb = gpu.alloc(4 * m * n)
+    gpu.memset(yb, 0xEE)                      # a finite, absurd pattern (NaN is a legal result here)
+    try:
+        gpu.run(pipe, q.bind(xb, rb, yb))
+        y = gpu.download(yb, np.float32, (m, n))
+        st = gpu.status_word()
+        if st:
+            raise RuntimeError(f"matmul_fp4 kernel reported status 0x{st:x}")
+        return y
+    finally:
+        for b in (xb, yb, rb):
+            if b is not None:
+                b.close()
+        q.close()
+        pipe.close()
+
+
 def dequant_fp4_f16(gpu: Gpu, wq: np.ndarray, ws: np.ndarray, wg: np.ndarray) -> np.ndarray:
     """uint16 [n,k]: the f16 bit patterns the kernels multiply by."""
     n, kh = wq.shape

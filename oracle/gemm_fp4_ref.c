@@ -220,6 +220,55 @@ LEXO_API int lexo_gemm_fp4(uint32_t m, uint32_t n, uint32_t k, uint32_t bk, cons
     return lexo_gemm_fp4_rows(m, n, k, bk, x16, wq, ws, wg, r, y, 0, n, threads);
 }
 
+/* ---- matmul_q_x with the NVFP4 layout ------------------------------------ */
+
+/* crates/lex-front/src/llama.rs:444-499: per chunk of kc columns, part = MatMulNT(x, w) with
+ * w = DequantFp4 (f32, NOT rounded to f16: interp.rs:643-657) and a sequential f32 sum
+ * (interp.rs:527-548); acc += part; y = acc (+ r).  The runtime calls it with kc = n_in
+ * (crates/lex-rt/src/qwen_run.rs:2605).  x is given as f32 values (an f16 x is widened by
+ * the caller, which is exact).  Returns 0, or -1 when kc does not divide k or is not whole
+ * groups of 16 (llama.rs:407-413). */
+LEXO_API int lexo_matmul_q_x(uint32_t m, uint32_t n, uint32_t k, uint32_t kc, const float* x,
+                             const uint8_t* wq, const uint8_t* ws, const float* wg, const float* r,
+                             float* y, int threads) {
+    if (kc == 0 || k % kc != 0 || kc % 16 != 0) return -1;
+#ifdef _OPENMP
+    if (threads > 0) omp_set_num_threads(threads);
+#else
+    (void)threads;
+#endif
+    int rc = 0;
+#pragma omp parallel
+    {
+        float* w = (float*)__builtin_malloc((size_t)k * sizeof(float));
+        if (!w) {
+#pragma omp atomic write
+            rc = -2;
+        } else {
+#pragma omp for schedule(static)
+            for (int64_t j = 0; j < (int64_t)n; j++) {
+                const uint8_t* q = wq + (size_t)j * (k / 2);
+                const uint8_t* s = ws + (size_t)j * (k / 16);
+                for (uint32_t p = 0; p < k; p++) w[p] = dequant_one(q[p / 2], (int)p, s[p / 16], wg[j]);
+                for (uint32_t i = 0; i < m; i++) {
+                    const float* xi = x + (size_t)i * k;
+                    float acc = 0.0f;
+                    for (uint32_t c = 0; c < k; c += kc) {
+                        float part = 0.0f;
+                        for (uint32_t p = c; p < c + kc; p++) part += xi[p] * w[p];
+                        acc += part;
+                    }
+                    size_t o = (size_t)i * n + (size_t)j;
+                    if (r) acc = acc + r[o];
+                    y[o] = acc;
+                }
+            }
+        }
+        __builtin_free(w);
+    }
+    return rc;
+}
+
 /* ---- metrics ----------------------------------------------------------- */
 
 /* crates/lex-ir/src/reference.rs:69-82 */

@@ -73,6 +73,8 @@ def lib() -> ctypes.CDLL:
         L.lexo_dequant_fp4_f16.argtypes = [u32, u32, vp, vp, vp, vp]
         L.lexo_gemm_fp4_rows.restype = ci
         L.lexo_gemm_fp4_rows.argtypes = [u32, u32, u32, u32, vp, vp, vp, vp, vp, vp, u32, u32, ci]
+        L.lexo_matmul_q_x.restype = ci
+        L.lexo_matmul_q_x.argtypes = [u32, u32, u32, u32, vp, vp, vp, vp, vp, vp, ci]
         L.lexo_max_rel_err.restype = ctypes.c_float
         L.lexo_max_rel_err.argtypes = [vp, vp, ctypes.c_size_t]
         L.lexo_err_of_scale.restype = None
@@ -114,6 +116,33 @@ def gemm_fp4(x16, wq, ws, wg, r=None, bk: int = 64, rows=None, threads: int = 0)
     rc = lib().lexo_gemm_fp4_rows(m, n, k, bk, _p(x16), _p(wq), _p(ws), _p(wg), rp, _p(y), n0, n1, threads)
     if rc != 0:
         raise ValueError(f"gemm_fp4 oracle rejected the shape (rc={rc}): k={k} does not divide by bk={bk}")
+    return y
+
+
+def matmul_q_x(x, wq, ws, wg, r=None, kc: int = 0, threads: int = 0) -> np.ndarray:
+    """matmul_q_x with the NVFP4 layout (crates/lex-front/src/llama.rs:444-499): y f32[t, n_out] with the
+    weights as f32 (not rounded to f16) and a sequential f32 sum per chunk of kc columns (kc = 0: the
+    whole row, as the runtime calls it).  x is float16 or float32 [t, n_in]."""
+    x = np.asarray(x)
+    if x.dtype not in (np.float16, np.float32):
+        raise TypeError("x must be float16 or float32")
+    m, k = x.shape
+    n = wq.shape[0]
+    if wq.shape != (n, k // 2) or ws.shape != (n, k // 16) or wg.shape != (n,):
+        raise ValueError(f"shapes do not fit matmul_q_x: x{x.shape} wq{wq.shape} ws{ws.shape} wg{wg.shape}")
+    xf = np.ascontiguousarray(x.astype(np.float32))
+    wq = np.ascontiguousarray(wq).view(np.uint8)
+    ws = np.ascontiguousarray(ws).view(np.uint8)
+    wg = np.ascontiguousarray(wg, dtype=np.float32)
+    y = np.zeros((m, n), dtype=np.float32)
+    rp = None
+    if r is not None:
+        r = np.ascontiguousarray(r, dtype=np.float32)
+        assert r.shape == (m, n)
+        rp = _p(r)
+    rc = lib().lexo_matmul_q_x(m, n, k, kc or k, _p(xf), _p(wq), _p(ws), _p(wg), rp, _p(y), threads)
+    if rc != 0:
+        raise ValueError(f"matmul_q_x oracle rejected the shape (rc={rc}): kc={kc or k} must divide k={k} in groups of 16")
     return y
 
 

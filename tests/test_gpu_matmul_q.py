@@ -1,0 +1,210 @@
+"""matmul_q_x with the NVFP4 layout on the block-scaled FP4 tensor-core kernel, against the CPU oracle.
+
+The reference gate for its GPU matmuls is 2e-3 of scale against the interpreter
+(crates/lex-cuda/tests/device_gpu.rs:294-303).  This kernel does not round anything but the
+activations' split (16 bits below the largest value of each group of 16) and the f32 sums, so the
+tests hold it to 1e-4 of scale and print what they measure (about 4e-6).
+"""
+import numpy as np
+import pytest
+
+import lex_gpu_b200 as L
+from lex_gpu_b200 import inputs
+from oracle import oracle as O
+
+pytestmark = pytest.mark.gpu
+
+TOL = 1e-4          # of scale; the reference's own gate is 2e-3
+REF_TOL = 2e-3
+
+
+@pytest.fixture(scope="module")
+def gpu():
+    from lex_gpu_b200 import build
+    build.build()
+    g = L.Gpu(0)
+    yield g
+    g.close()
+
+
+def check(got, want, tol=TOL):
+    assert np.isfinite(got).all()
+    err, scale, rel = O.err_of_scale(got, want)
+    print(f"  {err:.3e} of scale, {rel:.3e} per element (floor 1e-3 of scale)")
+    assert scale > 1e-3
+    assert err <= tol, f"{err:e} of scale"
+    assert rel <= 5e-3, f"per-element relative error {rel:e}"
+
+
+@pytest.mark.parametrize("m,n,k", [(1, 128, 256), (1, 128, 512), (1, 256, 768), (2, 128, 1024), (3, 256, 4096),
+                                   (4, 384, 2048), (4, 128, 256), (1, 640, 5120)])
+def test_small_shapes(gpu, m, n, k):
+    x, wq, ws, wg = inputs.make_case(m, n, k, seed_base=300 + m + n)
+    check(L.matmul_fp4(gpu, x, wq, ws, wg), O.matmul_q_x(x, wq, ws, wg))
+
+
+@pytest.mark.parametrize("stages", [2, 3, 4, 5, 6, 8])
+@pytest.mark.parametrize("m", [1, 3, 4])
+def test_every_ring_depth(gpu, m, stages):
+    # more stages of K (20) than any ring: every slot is reused, by different piece warps
+    x, wq, ws, wg = inputs.make_case(m, 256, 5120, seed_base=330 + m)
+    check(L.matmul_fp4(gpu, x, wq, ws, wg, stages=stages, k_splits=1), O.matmul_q_x(x, wq, ws, wg))
+
+
+@pytest.mark.parametrize("splits", [1, 2, 3, 5, 8])
+def test_split_k(gpu, splits):
+    x, wq, ws, wg = inputs.make_case(2, 256, 7168, seed_base=340)
+    check(L.matmul_fp4(gpu, x, wq, ws, wg, k_splits=splits), O.matmul_q_x(x, wq, ws, wg))
+
+
+def test_residual(gpu):
+    x, wq, ws, wg = inputs.make_case(3, 256, 2048, seed_base=350)
+    r = np.random.Generator(np.random.PCG64(351)).standard_normal((3, 256)).astype(np.float32) * 100
+    check(L.matmul_fp4(gpu, x, wq, ws, wg, r=r), O.matmul_q_x(x, wq, ws, wg, r=r))
+    check(L.matmul_fp4(gpu, x, wq, ws, wg, r=r, k_splits=4), O.matmul_q_x(x, wq, ws, wg, r=r))
+
+
+def test_agrees_with_gemm_fp4_within_the_reference_gate(gpu):
+    # the same bindings through gemm_fp4 (weights rounded to f16): the two operators differ by that rounding only
+    x, wq, ws, wg = inputs.make_case(4, 512, 5120, seed_base=360)
+    a = L.matmul_fp4(gpu, x, wq, ws, wg)
+    b = L.gemm_fp4(gpu, x, wq, ws, wg)
+    err, _, _ = O.err_of_scale(a, b)
+    print(f"  matmul_q vs gemm_fp4: {err:.3e} of scale")
+    assert err <= REF_TOL
+    # and the explicit selector on the gemm_fp4 plan reaches the same kernel
+    c = L.gemm_fp4(gpu, x, wq, ws, wg, kernel=4)
+    assert np.array_equal(a, c)
+
+
+def test_every_scale_byte_and_code(gpu):
+    """All 256 scale bytes (subnormals, negative scales, the two NaN bytes) against all 16 codes."""
+    wq, ws, wg = inputs.adversarial_dequant_case()
+    keep = np.isfinite(wg) & (np.abs(wg) < 1e30) & (np.abs(wg) > 1e-30)      # row scales the f32 sum survives
+    wq, ws, wg = wq[keep][:896], ws[keep][:896], wg[keep][:896]
+    x = inputs.make_x(2, wq.shape[1] * 2, seed_base=370)
+    want = O.matmul_q_x(x, wq, ws, wg)
+    got = L.matmul_fp4(gpu, x, wq, ws, wg)
+    assert np.isnan(want).all() and np.isnan(got).all()          # every row holds the NaN bytes
+    # without the NaN bytes: exact E4M3 semantics of the other 254, signs included
+    ws2 = ws.copy()
+    ws2[ws2 == 0x7F] = 0x7E
+    ws2[ws2 == 0xFF] = 0x81
+    want = O.matmul_q_x(x, wq, ws2, wg)
+    got = L.matmul_fp4(gpu, x, wq, ws2, wg)
+    assert np.isfinite(got).all()
+    # rows differ in scale by 60 binades and share one pattern of scales and codes: a row's scale is
+    # |wg| times the largest |y / wg| over all rows
+    unit = (np.abs(want) / np.abs(wg)[None, :]).max()
+    err = (np.abs(got - want) / (np.abs(wg)[None, :] * unit)).max()
+    print(f"  worst element: {err:.3e} of its row's scale")
+    assert err <= TOL
+
+
+def test_nan_scale_poisons_its_row_only(gpu):
+    x, wq, ws, wg = inputs.make_case(2, 256, 1024, seed_base=380)
+    ws = ws.copy()
+    ws[5, 17] = 0x7F
+    ws[200, 0] = 0xFF
+    got = L.matmul_fp4(gpu, x, wq, ws, wg)
+    want = O.matmul_q_x(x, wq, ws, wg)
+    assert np.array_equal(np.isnan(got), np.isnan(want))
+    assert np.isnan(got[:, 5]).all() and np.isnan(got[:, 200]).all() and np.isnan(got).sum() == 4
+    ok = ~np.isnan(want)
+    assert O.err_of_scale(got[ok], want[ok])[0] <= TOL
+
+
+@pytest.mark.parametrize("kind", ["zeros", "tiny", "subnormal", "huge", "outliers", "one_hot"])
+def test_activation_ranges(gpu, kind):
+    m, n, k = 2, 256, 2048
+    _, wq, ws, wg = inputs.make_case(m, n, k, seed_base=390)
+    rng = np.random.Generator(np.random.PCG64(391))
+    x = rng.standard_normal((m, k)).astype(np.float32)
+    if kind == "zeros":
+        x[:] = 0
+    elif kind == "tiny":
+        x *= 1e-4
+    elif kind == "subnormal":
+        x *= 2e-6                                    # around f16's smallest normal and below
+    elif kind == "huge":
+        x *= 12000
+    elif kind == "outliers":
+        x[rng.random((m, k)) < 0.004] *= 500
+    elif kind == "one_hot":
+        x[:] = 0
+        x[0, 777] = 3.0
+        x[1, 5] = -2.0 ** -24                        # the smallest subnormal
+    x = np.clip(x, -65504, 65504).astype(np.float16)
+    want = O.matmul_q_x(x, wq, ws, wg)
+    got = L.matmul_fp4(gpu, x, wq, ws, wg)
+    assert np.isfinite(got).all()
+    if kind == "zeros":
+        assert not got.any()
+        return
+    for t in range(m):                               # the two tokens may differ in scale by far
+        err = np.abs(got[t] - want[t]).max() / np.abs(want[t]).max()
+        print(f"  token {t}: {err:.3e} of scale")
+        assert err <= TOL
+
+
+def test_non_finite_activation_gives_nan_for_that_token(gpu):
+    x, wq, ws, wg = inputs.make_case(3, 128, 512, seed_base=400)
+    x = x.copy()
+    x[1, 100] = np.float16(np.inf)
+    got = L.matmul_fp4(gpu, x, wq, ws, wg)
+    want = O.matmul_q_x(np.delete(x, 1, axis=0), wq, ws, wg)
+    assert np.isnan(got[1]).all()
+    assert O.err_of_scale(got[[0, 2]], want)[0] <= TOL
+
+
+def test_a_token_alone_and_in_a_batch_is_bit_identical(gpu):
+    """What speculative verification depends on (crates/lex-msl/src/int8.rs:28-32): a token's output
+    does not depend on the batch it is in."""
+    x, wq, ws, wg = inputs.make_case(4, 1024, 5120, seed_base=410)
+    full = L.matmul_fp4(gpu, x, wq, ws, wg)
+    for t in (0, 3):
+        alone = L.matmul_fp4(gpu, x[t:t + 1], wq, ws, wg)
+        assert np.array_equal(alone[0], full[t])
+
+
+def test_full_size_rows_against_the_oracle(gpu):
+    # the decode shapes of the 27B model; the oracle takes well under a second per call at m <= 4
+    for (m, n, k) in [(1, 17408, 5120), (4, 17408, 5120), (1, 5120, 17408)]:
+        x, wq, ws, wg = inputs.make_case(m, n, k, seed_base=420)
+        check(L.matmul_fp4(gpu, x, wq, ws, wg), O.matmul_q_x(x, wq, ws, wg))
+
+
+def test_names_and_refusals(gpu):
+    p = gpu.plan_matmul_fp4(1, 17408, 5120)
+    d = p.describe()
+    assert d.entry == b"matvec_nvfp4_17408x5120_xh" and d.kernel == 4 and d.grid == 136 and d.threads == 576
+    p.close()
+    p = gpu.plan_matmul_fp4(3, 5120, 17408, residual=True)
+    d = p.describe()
+    assert d.entry == b"matmul3_nvfp4_5120x17408_res_xh" and d.nbind == 6 and d.k_splits == 3
+    p.close()
+    for bad in [dict(t=5, n_out=128, n_in=256), dict(t=1, n_out=64, n_in=256), dict(t=1, n_out=128, n_in=128),
+                dict(t=0, n_out=128, n_in=256)]:
+        with pytest.raises(L.LexbError):
+            gpu.plan_matmul_fp4(bad["t"], bad["n_out"], bad["n_in"])
+    with pytest.raises(L.LexbError, match="f32 activations"):
+        gpu.plan_matmul_fp4(1, 128, 256, x_half=False)
+
+
+def test_back_to_back_launches_with_early_weight_loads(gpu):
+    """Launches in a row on one stream, each with its own weights and the same x and y buffers: the
+    next launch loads its weights while this one runs, and must still see this one's y order."""
+    m, n, k = 2, 1024, 2048
+    x = inputs.make_x(m, k, seed_base=430)
+    sets = [inputs.make_weights(n, k, seed_base=431, copy=c) for c in range(4)]
+    qs = [L.QBuf(gpu, *w) for w in sets]
+    xb = gpu.upload(x)
+    ys = [gpu.alloc(4 * m * n) for _ in sets]
+    pipe = gpu.plan_matmul_fp4(m, n, k)
+    for rep in range(3):
+        for q, yb in zip(qs, ys):
+            gpu.run(pipe, q.bind(xb, None, yb))
+    gpu.sync()
+    for w, yb in zip(sets, ys):
+        check(gpu.download(yb, np.float32, (m, n)), O.matmul_q_x(x, *w))
+    assert gpu.status_word() == 0

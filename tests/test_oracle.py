@@ -179,3 +179,36 @@ def test_config0_regression_pin():
     x, wq, ws, wg = inputs.make_case(128, 128, 64)
     assert np.array_equal(O.gemm_fp4(x, wq, ws, wg), gold["y"])
     assert np.array_equal(O.dequant_fp4_f16(wq, ws, wg), gold["w16"])
+
+
+# ---------------------------------------------------------------- matmul_q_x (NVFP4 layout)
+
+def test_matmul_q_x_matches_f64_and_keeps_f32_weights():
+    from lex_gpu_b200 import inputs
+    x, wq, ws, wg = inputs.make_case(3, 64, 1024, seed_base=900)
+    y = O.matmul_q_x(x, wq, ws, wg)
+    w = O.np_dequant_f32(wq, ws, wg).astype(np.float64)
+    ref = x.astype(np.float64) @ w.T
+    assert np.abs(y - ref).max() / np.abs(ref).max() < 2e-6       # only the f32 sums round
+    # gemm_fp4 rounds the weights to f16 on top of that: visibly further from exact arithmetic
+    y16 = O.gemm_fp4(x, wq, ws, wg)
+    assert np.abs(y16 - ref).max() / np.abs(ref).max() > 2e-5
+    assert O.err_of_scale(y16, y)[0] < 2e-3                        # and still inside the reference gate
+
+
+def test_matmul_q_x_chunks_residual_and_f32_x():
+    from lex_gpu_b200 import inputs
+    x, wq, ws, wg = inputs.make_case(2, 32, 512, seed_base=901)
+    r = np.arange(64, dtype=np.float32).reshape(2, 32)
+    whole = O.matmul_q_x(x, wq, ws, wg, r=r)
+    chunked = O.matmul_q_x(x, wq, ws, wg, r=r, kc=128)             # same value up to the order of the f32 sums
+    assert np.abs(whole - chunked).max() / np.abs(whole).max() < 1e-5
+    assert np.array_equal(O.matmul_q_x(x.astype(np.float32), wq, ws, wg, r=r), whole)   # widening f16 is exact
+    # the sequential sum of one chunk, restated in numpy
+    w = O.np_dequant_f32(wq, ws, wg)
+    acc = np.float32(0)
+    for p in range(512):
+        acc = np.float32(acc + np.float32(np.float32(x[1, p]) * w[7, p]))
+    assert np.float32(acc + r[1, 7]) == whole[1, 7]
+    with pytest.raises(ValueError):
+        O.matmul_q_x(x, wq, ws, wg, kc=100)                        # must divide k in groups of 16 (llama.rs:407-413)
