@@ -34,6 +34,9 @@ ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
 
 M, N_ROWS, K = 512, 17408, 5120
+# DRAM bytes per launch of the block-scaled matmul_q_x kernel at (17408, 5120), from the ncu capture under
+# profiles/ (None until one has been taken for the kernel as it stands)
+MQ_TRAFFIC = None
 METRIC = "gemm_fp4 TFLOP/s at m=512 (27B MLP gate/up: n=17408 k=5120)"
 
 
@@ -316,6 +319,22 @@ def run_ours(args):
                             "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                                          "frac": gbs / peaks["hbm_gbs"], "traffic": 50.24e6 if world == 1 else None,
                                          "frac_of_nominal_8000": gbs / 8000.0}}
+        # the same bindings through matmul_q_x (the operator the model decodes with: weights not rounded
+        # to f16), on the block-scaled FP4 tensor-core kernel
+        p_mq = gpu.plan_matmul_fp4(mm, n_local, K)
+
+        def mq_step(i, p_mq=p_mq, xs=xs, ys=ys):
+            b = weights[i % COPIES][1]
+            gpu.run(p_mq, [xs, b[0], b[1], b[2], ys])
+
+        s_mq, _ = timed(p_mq, mq_step, mv_steps, max(args.warmup, 20) if full else args.warmup)
+        per_q = s_mq / mv_steps
+        gbs_q = wbytes_local / per_q / 1e9
+        matvec[f"m{mm}"]["matmul_q_x"] = {
+            "kernel": p_mq.describe().entry.decode(), "gbs_weight_bytes": gbs_q * world, "us_per_launch": per_q * 1e6,
+            "roofline": {"bound": "hbm", "achieved": gbs_q, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                         "frac": gbs_q / peaks["hbm_gbs"], "traffic": MQ_TRAFFIC if world == 1 else None,
+                         "frac_of_nominal_8000": gbs_q / 8000.0}}
 
     # ---- all-gather variant (N > 1): y shards -> [N][m][n/N] on every rank
     allgather = None
