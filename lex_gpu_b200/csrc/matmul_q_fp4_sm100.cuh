@@ -186,8 +186,16 @@ matmul_q_fp4_kernel(const __grid_constant__ CUtensorMap tmap_wq, const __grid_co
         // ---------------------------------------------------------------- TMA producer
         if (lane == 0) {
             RingPos ps;
+            // Until its rings are full this warp waits for nothing.  Before its first wait for a slot to
+            // come free it joins the stream's order itself: the other warps cannot free anything before
+            // the launch ahead has finished, and a bounded wait must not run against that launch's time.
+            bool in_order = !(a.flags & 1u);
             for (uint32_t kb = 0; kb < KB; kb++, ps.advance(S)) {
                 const uint32_t s = ps.s;
+                if (!in_order && (kb >= S || kb / MQ_WS_GROUP + 1u >= MQ_WS_SLOTS)) {
+                    grid_dependency_wait();
+                    in_order = true;
+                }
                 if (!mbar_wait(empty(s), ps.ph ^ 1u, abort_flag)) {
                     atomicOr(a.status, ST_WAIT_EMPTY_TMA);
                     *abort_flag = 1;
@@ -195,15 +203,26 @@ matmul_q_fp4_kernel(const __grid_constant__ CUtensorMap tmap_wq, const __grid_co
                 }
                 if (TRACE && a.trace && kb == 0) a.trace[16ull * blockIdx.x + 13] = (unsigned long long)clock64();
                 if ((kb & (MQ_WS_GROUP - 1u)) == 0u) {
-                    // scale bytes of this and the next three stages
-                    const uint32_t wsi = kb / MQ_WS_GROUP, r = wsi % MQ_WS_SLOTS, wph = (wsi / MQ_WS_SLOTS) & 1u;
-                    if (!mbar_wait(ws_empty(r), wph ^ 1u, abort_flag)) {
+                    // Scale bytes, one group of four stages AHEAD of the codes (both groups at the start):
+                    // re-laying them does not need the codes, so the scale warps work ahead of the copy
+                    // engine's stream instead of starting when a stage lands.
+                    const uint32_t g_first = kb == 0u ? 0u : kb / MQ_WS_GROUP + 1u, g_last = kb / MQ_WS_GROUP + 1u;
+                    bool gave_up = false;
+                    for (uint32_t wsi = g_first; wsi <= g_last && wsi * MQ_WS_GROUP < KB; wsi++) {
+                        const uint32_t r = wsi % MQ_WS_SLOTS, wph = (wsi / MQ_WS_SLOTS) & 1u;
+                        if (!mbar_wait(ws_empty(r), wph ^ 1u, abort_flag)) {
+                            gave_up = true;
+                            break;
+                        }
+                        mbar_arrive_expect_tx(ws_full(r), a.ws_pitch * MQ_ROWS);
+                        tma_load_2d(ws_base + r * MQ_WS_SLOT_BYTES, &tmap_ws, (int)((kb0 + wsi * MQ_WS_GROUP) * (MQ_STAGE_K / 16)), (int)n0,
+                                    ws_full(r));
+                    }
+                    if (gave_up) {
                         atomicOr(a.status, ST_WAIT_EMPTY_TMA);
                         *abort_flag = 1;
                         break;
                     }
-                    mbar_arrive_expect_tx(ws_full(r), a.ws_pitch * MQ_ROWS);
-                    tma_load_2d(ws_base + r * MQ_WS_SLOT_BYTES, &tmap_ws, (int)((kb0 + kb) * (MQ_STAGE_K / 16)), (int)n0, ws_full(r));
                 }
                 mbar_arrive_expect_tx(raw_full(s), MQ_CODE_BYTES);
                 tma_load_2d(codes_of(s), &tmap_wq, (int)((kb0 + kb) * (MQ_STAGE_K / 2)), (int)n0, raw_full(s));
@@ -297,6 +316,7 @@ matmul_q_fp4_kernel(const __grid_constant__ CUtensorMap tmap_wq, const __grid_co
             uint32_t mx[MQ_MAX_TOKENS] = {0, 0, 0, 0};
             const uint4* xr = reinterpret_cast<const uint4*>(a.x);
             const uint32_t row_chunks = a.k / 8u;
+#pragma unroll 4
             for (uint32_t i = xt; i < row_chunks; i += 32u * MQ_PIECE_WARPS) {
                 uint4 v[MQ_MAX_TOKENS];
 #pragma unroll
