@@ -314,6 +314,8 @@ int launch_one(lexb_gpu* g, const lexb_pipeline* p, const lexb_buffer* x, const 
         a.r = r ? static_cast<const float*>(r->ptr) : nullptr;
         a.y = static_cast<float*>(y->ptr);
         a.partial = p->partial;
+        // the row tiles' arrival counters sit behind the partial products in the same allocation
+        a.counters = p->partial ? reinterpret_cast<uint32_t*>(p->partial + static_cast<size_t>(p->k_splits) * p->m * p->n) : nullptr;
         a.status = g->d_status;
         a.m = p->m; a.n = p->n; a.k = p->k; a.stages = p->stages;
         a.k_splits = p->k_splits; a.kb_per_split = p->kb_per_split;
@@ -331,12 +333,6 @@ int launch_one(lexb_gpu* g, const lexb_pipeline* p, const lexb_buffer* x, const 
         a.trace = (g->d_trace && p->grid <= g->trace_ctas) ? g->d_trace : nullptr;
         if (a.trace) CUDA_TRY(cudaLaunchKernelEx(&cfg, lexb::matmul_q_fp4_kernel<true>, maps.map_wq, maps.map_ws, a));
         else CUDA_TRY(cudaLaunchKernelEx(&cfg, lexb::matmul_q_fp4_kernel<false>, maps.map_wq, maps.map_ws, a));
-        if (p->k_splits > 1) {
-            CUDA_TRY(cudaGetLastError());
-            const size_t elems = static_cast<size_t>(p->m) * p->n;
-            const uint32_t blocks = static_cast<uint32_t>(std::min<size_t>((elems / 4 + 255) / 256, 148u * 8u));
-            lexb::splitk_reduce_kernel<<<blocks, 256, 0, g->stream>>>(p->partial, p->k_splits, elems, a.r, a.y, lexb::GatherDst{});
-        }
     } else {
         lexb::MatvecArgs a{};
         a.x = static_cast<const __half*>(x->ptr);
@@ -619,7 +615,10 @@ int lexb_gemm_fp4_plan(lexb_gpu* g, uint32_t m, uint32_t n, uint32_t k, int resi
         // the weights are taken as constant (loaded ahead of the stream's order) unless the caller says otherwise
         p->flags = (s.flags & LEXB_SCHED_WEIGHTS_MAY_CHANGE) ? 0u : 1u;
         if (splits > 1u) {
-            cudaError_t e = cudaMalloc(&p->partial, sizeof(float) * splits * static_cast<size_t>(m) * n);
+            // partial products [splits][m][n], then one arrival counter per row tile (zero between launches)
+            const size_t pbytes = sizeof(float) * splits * static_cast<size_t>(m) * n;
+            cudaError_t e = cudaMalloc(&p->partial, pbytes + sizeof(uint32_t) * tiles);
+            if (e == cudaSuccess) e = cudaMemset(reinterpret_cast<char*>(p->partial) + pbytes, 0, sizeof(uint32_t) * tiles);
             if (e != cudaSuccess) return bail(fail(LEXB_ERR_CUDA, "allocating the split-K workspace: %s", cudaGetErrorString(e)));
         }
         p->grid = tiles * splits;

@@ -70,6 +70,7 @@ struct MatmulQArgs {
     const float* r;          // [m, n] or null
     float* y;                // [m, n]
     float* partial;          // [k_splits][m][n] when k_splits > 1
+    uint32_t* counters;      // [n / 128], zero between launches: how many splits of a row tile have stored their partial
     uint32_t* status;
     unsigned long long* trace;   // 16 phase timers per block, or null
     uint32_t m, n, k, stages;
@@ -128,6 +129,7 @@ matmul_q_fp4_kernel(const __grid_constant__ CUtensorMap tmap_wq, const __grid_co
     uint32_t* const tmem_slot = misc;
     volatile uint32_t* const abort_flag = misc + 1;
     uint32_t* const tok_amax = misc + 2;                                   // [MQ_MAX_TOKENS]
+    volatile uint32_t* const fix_flag = misc + 6;
     volatile uint8_t* const nan_rows = reinterpret_cast<volatile uint8_t*>(misc + 16);   // [MQ_ROWS]: a NaN scale byte seen
 
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
@@ -540,6 +542,26 @@ matmul_q_fp4_kernel(const __grid_constant__ CUtensorMap tmap_wq, const __grid_co
                 const size_t o = (size_t)t * a.n + n0 + row;
                 if (!to_partial && a.r) v += __ldg(a.r + o);
                 out[o] = v;
+            }
+        }
+        if (a.k_splits > 1u) {
+            // The last block of a row tile to get here adds up the splits, always in the order of the
+            // splits, so the result does not depend on which block that is.  (A block that gave up
+            // above still counts itself: the counter must be back at zero for the next launch.)
+            __threadfence();
+            asm volatile("bar.sync 3, 128;" ::: "memory");
+            if (warp == 2u && lane == 0) *fix_flag = atomicAdd(a.counters + tile, 1u);
+            asm volatile("bar.sync 3, 128;" ::: "memory");
+            if (*fix_flag == a.k_splits - 1u) {
+                __threadfence();
+                for (uint32_t t = 0; t < a.m; t++) {
+                    const size_t o = (size_t)t * a.n + n0 + row;
+                    float sum = 0.0f;
+                    for (uint32_t sp = 0; sp < a.k_splits; sp++) sum += __ldcg(a.partial + (size_t)sp * a.m * a.n + o);
+                    if (a.r) sum += __ldg(a.r + o);
+                    a.y[o] = sum;
+                }
+                if (warp == 2u && lane == 0) a.counters[tile] = 0;
             }
         }
         }
