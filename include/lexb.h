@@ -57,7 +57,7 @@ typedef struct lexb_device_info {
  * (crates/lex-front/lx/gemm_fp4.lx:38-39) and of the LEX_GEMM_CU_* variables
  * (crates/lex-msl/src/gemm.rs:90-135).  Zero fields mean "choose". */
 typedef struct lexb_sched {
-    uint32_t kernel;  /* 0 auto, 1 split-K matvec (m <= 16), 2 tcgen05 GEMM, 3 two-CTA tcgen05 GEMM,
+    uint32_t kernel;  /* 0 auto, 1 matvec (m <= 16), 2 tcgen05 GEMM, 3 two-CTA tcgen05 GEMM,
                        * 4 block-scaled FP4 tensor-core kernel (m <= 4; matmul_q_x arithmetic, never chosen by auto) */
     uint32_t tm;      /* tokens per CTA tile of the GEMM: multiple of 16, <= 256 */
     uint32_t stages;  /* pipeline depth of the GEMM */
