@@ -222,12 +222,15 @@ LEXB_API int lexb_gemm_fp4_splitk_static(lexb_gpu* gpu, uint32_t m, uint32_t n, 
  * crates/lex-rt/src/qwen_run.rs:2605-2606), same bindings [x, wq, ws, wg, (r), y] as gemm_fp4 but with
  * the weights used as dequantised f32 values (e2m1 * e4m3 * wg, crates/lex-front/src/interp.rs:643-657),
  * not rounded to f16.  The pipeline is launched like any other (lexb_gemm_fp4_launch, lexb_step).
- * Here: t <= 4 tokens of f16 activations (x_half != 0; f32 x is refused), n_out % 128 == 0,
+ * Here: t <= 4 tokens, activations f16 (x_half != 0) or f32 (x_half == 0), n_out % 128 == 0,
  * n_in % 256 == 0.  The decode runs on the tensor cores' block-scaled FP4 path, which takes wq and ws
- * as stored; each token is split exactly into eight rows of 2-bit E2M1 digits (16 significant bits
- * below the largest value of every group of 16).  Results agree with the interpreter to about 1e-5 of
- * scale (gate 2e-3, crates/lex-cuda/tests/device_gpu.rs:294-303); the entry name is the reference's
- * (matvec_nvfp4_{n_out}x{n_in}[_res]_xh, matmul{t}_... for t > 1). */
+ * as stored; each token is split into eight rows of 2-bit E2M1 digits: 16 significant bits below the
+ * largest value of every group of 16, exact for f16 values within 2^5 of that maximum, and for f32
+ * input the precision the reference's integer path keeps (quant16, crates/lex-msl/src/int8.rs:44-99).
+ * Results agree with the interpreter to about 1e-5 of scale (gate 2e-3,
+ * crates/lex-cuda/tests/device_gpu.rs:294-303); the entry name is the reference's
+ * (matvec_nvfp4_{n_out}x{n_in}[_res][_xh], matmul{t}_... for t > 1).  A token holding an infinity or a
+ * NaN gives NaN for the whole token; magnitudes below 2^-111 count as zero. */
 LEXB_API int lexb_matmul_fp4_plan(lexb_gpu* gpu, uint32_t t, uint32_t n_out, uint32_t n_in, int residual, int x_half,
                                   const lexb_sched* sched_or_null, lexb_pipeline** out);
 

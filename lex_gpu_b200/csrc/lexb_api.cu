@@ -85,6 +85,7 @@ struct lexb_pipeline {
     uint32_t tm, stages, w_stages, tmem_cols, m_tiles, n_acc, flags;
     uint32_t k_splits = 1, kb_per_split = 0, tok_blocks = 2;
     uint32_t ws_pitch = 0;      // block-scaled kernel: bytes per row of one scale load
+    bool x_f32 = false;         // ... with f32 activations
     float* partial = nullptr;   // split-K workspace [k_splits][m][n], owned by the pipeline
     // matvec
     uint32_t kc;
@@ -243,7 +244,7 @@ int launch_one(lexb_gpu* g, const lexb_pipeline* p, const lexb_buffer* x, const 
     if (p->gpu != g) return fail(LEXB_ERR_ARG, "pipeline was planned on another gpu handle");
     const size_t m = p->m, n = p->n, k = p->k;
     int rc;
-    if ((rc = check_buf(x, g, m * k * 2, "x"))) return rc;
+    if ((rc = check_buf(x, g, m * k * (p->x_f32 ? 4 : 2), "x"))) return rc;
     if ((rc = check_buf(wq, g, n * k / 2, "wq"))) return rc;
     if ((rc = check_buf(ws, g, n * k / 16, "ws"))) return rc;
     if ((rc = check_buf(wg, g, n * 4, "wg"))) return rc;
@@ -309,7 +310,7 @@ int launch_one(lexb_gpu* g, const lexb_pipeline* p, const lexb_buffer* x, const 
         lexb_pipeline::MapEntry maps;
         if ((rc = get_maps(p, x->ptr, wq->ptr, ws->ptr, &maps))) return rc;
         lexb::MatmulQArgs a{};
-        a.x = static_cast<const __half*>(x->ptr);
+        a.x = x->ptr;
         a.wg = static_cast<const float*>(wg->ptr);
         a.r = r ? static_cast<const float*>(r->ptr) : nullptr;
         a.y = static_cast<float*>(y->ptr);
@@ -331,8 +332,13 @@ int launch_one(lexb_gpu* g, const lexb_pipeline* p, const lexb_buffer* x, const 
         cfg.attrs = attr;
         cfg.numAttrs = g->pdl ? 1 : 0;
         a.trace = (g->d_trace && p->grid <= g->trace_ctas) ? g->d_trace : nullptr;
-        if (a.trace) CUDA_TRY(cudaLaunchKernelEx(&cfg, lexb::matmul_q_fp4_kernel<true>, maps.map_wq, maps.map_ws, a));
-        else CUDA_TRY(cudaLaunchKernelEx(&cfg, lexb::matmul_q_fp4_kernel<false>, maps.map_wq, maps.map_ws, a));
+        if (p->x_f32) {
+            if (a.trace) CUDA_TRY(cudaLaunchKernelEx(&cfg, lexb::matmul_q_fp4_kernel<true, true>, maps.map_wq, maps.map_ws, a));
+            else CUDA_TRY(cudaLaunchKernelEx(&cfg, lexb::matmul_q_fp4_kernel<false, true>, maps.map_wq, maps.map_ws, a));
+        } else {
+            if (a.trace) CUDA_TRY(cudaLaunchKernelEx(&cfg, lexb::matmul_q_fp4_kernel<true, false>, maps.map_wq, maps.map_ws, a));
+            else CUDA_TRY(cudaLaunchKernelEx(&cfg, lexb::matmul_q_fp4_kernel<false, false>, maps.map_wq, maps.map_ws, a));
+        }
     } else {
         lexb::MatvecArgs a{};
         a.x = static_cast<const __half*>(x->ptr);
@@ -410,8 +416,10 @@ int lexb_open(int device, lexb_gpu** out) {
         cudaFuncSetAttribute(lexb::matvec_fp4_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem) != cudaSuccess ||
         cudaFuncSetAttribute(lexb::matvec_fp4_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem) != cudaSuccess ||
         cudaFuncSetAttribute(lexb::matvec_fp4_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem) != cudaSuccess ||
-        cudaFuncSetAttribute(lexb::matmul_q_fp4_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem) != cudaSuccess ||
-        cudaFuncSetAttribute(lexb::matmul_q_fp4_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem) != cudaSuccess)
+        cudaFuncSetAttribute(lexb::matmul_q_fp4_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem) != cudaSuccess ||
+        cudaFuncSetAttribute(lexb::matmul_q_fp4_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem) != cudaSuccess ||
+        cudaFuncSetAttribute(lexb::matmul_q_fp4_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem) != cudaSuccess ||
+        cudaFuncSetAttribute(lexb::matmul_q_fp4_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem) != cudaSuccess)
         return bail(fail(LEXB_ERR_CUDA, "cudaFuncSetAttribute(max dynamic shared memory) failed: %s", cudaGetErrorString(cudaGetLastError())));
     *out = g;
     return LEXB_OK;
@@ -738,7 +746,6 @@ int lexb_matmul_fp4_plan(lexb_gpu* g, uint32_t t, uint32_t n_out, uint32_t n_in,
                          const lexb_sched* sched, lexb_pipeline** out) {
     if (!out) return fail(LEXB_ERR_ARG, "lexb_matmul_fp4_plan: null out");
     *out = nullptr;
-    if (!x_half) return fail(LEXB_ERR_UNSUPPORTED, "matmul_q (nvfp4): f32 activations are not implemented; narrow x to f16 (x_half)");
     lexb_sched s{};
     if (sched) s = *sched;
     s.kernel = KERNEL_MATMUL_Q;
@@ -749,7 +756,8 @@ int lexb_matmul_fp4_plan(lexb_gpu* g, uint32_t t, uint32_t n_out, uint32_t n_in,
     char tag[16];
     if (t == 1) snprintf(tag, sizeof tag, "matvec");
     else snprintf(tag, sizeof tag, "matmul%u", t);
-    snprintf((*out)->entry, sizeof (*out)->entry, "%s_nvfp4_%ux%u%s_xh", tag, n_out, n_in, residual ? "_res" : "");
+    (*out)->x_f32 = !x_half;
+    snprintf((*out)->entry, sizeof (*out)->entry, "%s_nvfp4_%ux%u%s%s", tag, n_out, n_in, residual ? "_res" : "", x_half ? "_xh" : "");
     return LEXB_OK;
 }
 
@@ -821,7 +829,7 @@ int lexb_gemm_fp4_run_host(lexb_gpu* g, const lexb_pipeline* p, const void* x_ho
     int rc = use(g);
     if (rc) return rc;
     if (!p || !x_host || !y_host || !x_dev || !y_dev) return fail(LEXB_ERR_ARG, "lexb_gemm_fp4_run_host: null argument");
-    const size_t xb = static_cast<size_t>(p->m) * p->k * 2, yb = static_cast<size_t>(p->m) * p->n * 4;
+    const size_t xb = static_cast<size_t>(p->m) * p->k * (p->x_f32 ? 4 : 2), yb = static_cast<size_t>(p->m) * p->n * 4;
     if (x_dev->bytes < xb || y_dev->bytes < yb) return fail(LEXB_ERR_ARG, "lexb_gemm_fp4_run_host: staging buffers too small");
     CUDA_TRY(cudaMemcpyAsync(x_dev->ptr, x_host, xb, cudaMemcpyHostToDevice, g->stream));
     if ((rc = launch_one(g, p, x_dev, wq, ws, wg, r, y_dev))) return rc;

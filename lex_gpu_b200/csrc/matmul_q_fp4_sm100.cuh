@@ -14,15 +14,16 @@
 // integer pipe, which bounds the table-lookup decode of `matvec_fp4_kernel`, is idle here and the
 // kernel streams at memory speed.
 //
-// The activations have to be E2M1 as well.  Each token is split exactly into MQ_PIECES = 8 rows of
-// 2-bit digits: inside a group of 16 values with largest exponent E, a value is sign * I * 2^(E-15)
-// with a 16-bit integer I (the 11-bit significand of the largest value fits with 5 bits to spare;
-// smaller values are rounded to that grid, which is finer than f16's own for anything within 2^5 of
-// the group's maximum), and I = sum_p digit_p * 4^(7-p).  Piece p holds the E2M1 codes of
-// digit_p / 2 (0, 0.5, 1, 1.5 are codes 0..3) and the group scale 2^(E - 2p - G), G a per-token
-// offset that keeps the scales inside UE4M3's range; the epilogue adds the 8 accumulator columns of a
-// token and multiplies by 2^G * wg[j].  So a token costs 8 columns of N, the minimum N of the
-// instruction for one token.
+// The activations have to be E2M1 as well.  Each token (f16, or f32) is split into MQ_PIECES = 8 rows of
+// 2-bit digits: inside a group of 16 values with largest exponent E, a value is sign * I * 2^(E-15) with a
+// 16-bit integer I = round(|x| * 2^(15-E)).  For f16 input that is exact for every value within 2^5 of the
+// group's maximum (11 significant bits fit with 5 to spare) and finer than f16's own grid there; f32 input
+// keeps 16 bits below the group's maximum, which is what the reference's own integer path keeps
+// (`quant16`, crates/lex-msl/src/int8.rs:44-99).  I = sum_p digit_p * 4^(7-p); piece p holds the E2M1 codes
+// of digit_p / 2 (0, 0.5, 1, 1.5 are codes 0..3) and the group scale 2^(E - 2p - G), G a per-token offset
+// that keeps the scales inside UE4M3's range; the epilogue adds the 8 accumulator columns of a token and
+// multiplies by 2^G * wg[j].  So a token costs 8 columns of N, the minimum N of the instruction anyway.
+// Groups (and tokens) whose largest magnitude is below 2^-111 count as zero.
 //
 // Scale bytes with the sign bit set are legal E4M3 (the reference decodes them as negative scales):
 // the hardware scale is unsigned, so the sign is moved into the 16 codes of the group in shared
@@ -65,7 +66,7 @@ constexpr uint32_t MQ_TMEM_SFB = MQ_TMEM_SFA + 16u * MQ_MAX_STAGES;
 static_assert(MQ_STAGE_BYTES % 1024u == 0, "every stage starts on a swizzle-pattern boundary");
 
 struct MatmulQArgs {
-    const __half* x;         // [m, k]
+    const void* x;           // [m, k], f16 or f32
     const float* wg;         // [n]
     const float* r;          // [m, n] or null
     float* y;                // [m, n]
@@ -89,14 +90,6 @@ __device__ __forceinline__ uint32_t mq_spread8(uint32_t t) {
     return (u | (u << 6)) & 0x03030303u;
 }
 
-// One f16 value -> its 16-bit integer on the grid of a group whose largest biased exponent is e_eff.
-__device__ __forceinline__ uint32_t mq_fixed16(uint32_t h, uint32_t e_eff) {
-    const uint32_t ex = (h >> 10) & 31u, frac = h & 1023u;
-    const uint32_t mant = ex ? (frac | 1024u) : frac;
-    const uint32_t d = e_eff - (ex ? ex : 1u);
-    return ((mant << 5) + ((1u << d) >> 1)) >> d;
-}
-
 // UE4M3 byte of 2^q (0 when it is below the smallest subnormal)
 __device__ __forceinline__ uint32_t mq_ue4m3_pow2(int q) {
     if (q >= -6) return static_cast<uint32_t>(q + 7) << 3;
@@ -104,7 +97,7 @@ __device__ __forceinline__ uint32_t mq_ue4m3_pow2(int q) {
     return 0u;
 }
 
-template <bool TRACE>
+template <bool TRACE, bool XF32>
 __global__ void __launch_bounds__(MQ_THREADS, 1)
 matmul_q_fp4_kernel(const __grid_constant__ CUtensorMap tmap_wq, const __grid_constant__ CUtensorMap tmap_ws, MatmulQArgs a) {
     extern __shared__ uint8_t smem_raw[];
@@ -307,17 +300,34 @@ matmul_q_fp4_kernel(const __grid_constant__ CUtensorMap tmap_wq, const __grid_co
         // A warp takes every PW-th item.  Its consecutive items must be at most S stages apart: a wait
         // on a stage's barrier can only tell "this turn of the ring" from the one before it.
         const uint32_t PW = (S * a.m < MQ_PIECE_WARPS) ? S * a.m : MQ_PIECE_WARPS;
+        // one item's values for this lane: 8 consecutive values of K, as 8 halves or 8 floats
+        struct Chunk {
+            uint4 lo, hi;     // f16: lo only
+        };
+        auto load_chunk = [&](uint32_t kb, uint32_t t) {
+            Chunk c;
+            c.hi = make_uint4(0, 0, 0, 0);
+            if (XF32) {
+                const uint4* p4 = reinterpret_cast<const uint4*>(static_cast<const float*>(a.x) + (size_t)t * a.k) +
+                                  (size_t)(kb0 + kb) * (MQ_STAGE_K / 4u) + 2u * lane;
+                c.lo = __ldg(p4);
+                c.hi = __ldg(p4 + 1);
+            } else {
+                c.lo = __ldg(reinterpret_cast<const uint4*>(static_cast<const __half*>(a.x) + (size_t)t * a.k) +
+                             (size_t)(kb0 + kb) * (MQ_STAGE_K / 8u) + lane);
+            }
+            return c;
+        };
         // the first item's values are on their way while the token maxima are found
-        uint4 xv = make_uint4(0, 0, 0, 0);
-        if (xw < PW && xw < items) {
-            const uint32_t kb = xw / a.m, t = xw - kb * a.m;
-            xv = __ldg(reinterpret_cast<const uint4*>(a.x + (size_t)t * a.k) + (size_t)(kb0 + kb) * (MQ_STAGE_K / 8u) + lane);
-        }
-        // largest exponent of each token (its scale offset G); the tokens' loads go out together
+        Chunk xv;
+        xv.lo = xv.hi = make_uint4(0, 0, 0, 0);
+        if (xw < PW && xw < items) xv = load_chunk(xw / a.m, xw % a.m);
+        // largest magnitude of each token as f32 bits (its exponent gives the scale offset G); the
+        // tokens' loads go out together
         {
             uint32_t mx[MQ_MAX_TOKENS] = {0, 0, 0, 0};
             const uint4* xr = reinterpret_cast<const uint4*>(a.x);
-            const uint32_t row_chunks = a.k / 8u;
+            const uint32_t row_chunks = XF32 ? a.k / 4u : a.k / 8u;
 #pragma unroll 4
             for (uint32_t i = xt; i < row_chunks; i += 32u * MQ_PIECE_WARPS) {
                 uint4 v[MQ_MAX_TOKENS];
@@ -326,16 +336,25 @@ matmul_q_fp4_kernel(const __grid_constant__ CUtensorMap tmap_wq, const __grid_co
                     v[t] = t < a.m ? __ldg(xr + (size_t)t * row_chunks + i) : make_uint4(0, 0, 0, 0);
 #pragma unroll
                 for (uint32_t t = 0; t < MQ_MAX_TOKENS; t++) {
-                    mx[t] = __vmaxu2(mx[t], v[t].x & 0x7FFF7FFFu);
-                    mx[t] = __vmaxu2(mx[t], v[t].y & 0x7FFF7FFFu);
-                    mx[t] = __vmaxu2(mx[t], v[t].z & 0x7FFF7FFFu);
-                    mx[t] = __vmaxu2(mx[t], v[t].w & 0x7FFF7FFFu);
+                    if (XF32) {
+                        mx[t] = max(max(mx[t], v[t].x & 0x7FFFFFFFu), v[t].y & 0x7FFFFFFFu);
+                        mx[t] = max(max(mx[t], v[t].z & 0x7FFFFFFFu), v[t].w & 0x7FFFFFFFu);
+                    } else {
+                        mx[t] = __vmaxu2(mx[t], v[t].x & 0x7FFF7FFFu);
+                        mx[t] = __vmaxu2(mx[t], v[t].y & 0x7FFF7FFFu);
+                        mx[t] = __vmaxu2(mx[t], v[t].z & 0x7FFF7FFFu);
+                        mx[t] = __vmaxu2(mx[t], v[t].w & 0x7FFF7FFFu);
+                    }
                 }
             }
 #pragma unroll
             for (uint32_t t = 0; t < MQ_MAX_TOKENS; t++) {
                 if (t < a.m) {
-                    uint32_t r = max(mx[t] & 0xFFFFu, mx[t] >> 16);
+                    uint32_t r = mx[t];
+                    if (!XF32) {
+                        r = max(r & 0xFFFFu, r >> 16);
+                        r = __float_as_uint(__half2float(__ushort_as_half((unsigned short)r)));   // exact; inf and NaN stay so
+                    }
                     r = __reduce_max_sync(0xFFFFFFFFu, r);
                     if (lane == 0) atomicMax(tok_amax + t, r);
                 }
@@ -352,26 +371,38 @@ matmul_q_fp4_kernel(const __grid_constant__ CUtensorMap tmap_wq, const __grid_co
         for (uint32_t it = (xw < PW ? xw : items); it < items; it += PW) {
             const uint32_t kb = it / a.m, tok = it - kb * a.m;
             const uint32_t s = kb % S, ph = (kb / S) & 1u;
-            const uint4 xc = xv;
-            if (it + PW < items) {
-                const uint32_t kn = (it + PW) / a.m, tn = (it + PW) - kn * a.m;
-                xv = __ldg(reinterpret_cast<const uint4*>(a.x + (size_t)tn * a.k) + (size_t)(kb0 + kn) * (MQ_STAGE_K / 8u) + lane);
+            const Chunk xc = xv;
+            if (it + PW < items) xv = load_chunk((it + PW) / a.m, (it + PW) % a.m);
+            const uint32_t te8 = tok_amax[tok] >> 23;                 // the token's largest f32 exponent field
+            // ---- 8 values of the token: K offsets 8 lane .. 8 lane + 7 of the stage, as f32 bits
+            uint32_t fb[8];
+            if (XF32) {
+                fb[0] = xc.lo.x; fb[1] = xc.lo.y; fb[2] = xc.lo.z; fb[3] = xc.lo.w;
+                fb[4] = xc.hi.x; fb[5] = xc.hi.y; fb[6] = xc.hi.z; fb[7] = xc.hi.w;
+            } else {
+                const uint32_t hw[4] = {xc.lo.x, xc.lo.y, xc.lo.z, xc.lo.w};
+#pragma unroll
+                for (uint32_t i = 0; i < 4; i++) {
+                    const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&hw[i]));
+                    fb[2 * i] = __float_as_uint(f.x);
+                    fb[2 * i + 1] = __float_as_uint(f.y);
+                }
             }
-            const uint32_t tmax_e = tok_amax[tok] >> 10, tmax_eff = tmax_e ? tmax_e : 1u;
-            // ---- 8 values of the token: K offsets 8 lane .. 8 lane + 7 of the stage
-            const uint32_t hw[4] = {xc.x, xc.y, xc.z, xc.w};
             uint32_t am = 0;
 #pragma unroll
-            for (uint32_t i = 0; i < 4; i++) am = __vmaxu2(am, hw[i] & 0x7FFF7FFFu);
-            am = max(am & 0xFFFFu, am >> 16);
+            for (uint32_t i = 0; i < 8; i++) am = max(am, fb[i] & 0x7FFFFFFFu);
             am = max(am, __shfl_xor_sync(0xFFFFFFFFu, am, 1));        // a group of 16 is two lanes
-            const uint32_t e = am >> 10, e_eff = e ? e : 1u;
+            // |x| = I * 2^(E - 15), E the group's largest exponent: I = |x| * 2^(142 - e8), 16 bits.  Groups
+            // below 2^-111 count as zero (their scale factor would leave f32's range).
+            const uint32_t e8 = am >> 23;
+            const float to_fixed = e8 >= 16u ? __uint_as_float((269u - e8) << 23) : 0.0f;
             uint32_t blo[4], bhi[4];
 #pragma unroll
             for (uint32_t i = 0; i < 4; i++) {
-                const uint32_t h0 = hw[i] & 0xFFFFu, h1 = hw[i] >> 16;
-                const uint32_t i0 = mq_fixed16(h0, e_eff), i1 = mq_fixed16(h1, e_eff);
-                const uint32_t sg = ((0u - (h0 >> 15)) & 0x08080808u) | ((0u - (h1 >> 15)) & 0x80808080u);
+                const uint32_t b0 = fb[2 * i], b1 = fb[2 * i + 1];
+                const uint32_t i0 = min(__float2uint_rn(__uint_as_float(b0 & 0x7FFFFFFFu) * to_fixed), 65535u);
+                const uint32_t i1 = min(__float2uint_rn(__uint_as_float(b1 & 0x7FFFFFFFu) * to_fixed), 65535u);
+                const uint32_t sg = ((0u - (b0 >> 31)) & 0x08080808u) | ((0u - (b1 >> 31)) & 0x80808080u);
                 blo[i] = mq_spread8(i0 & 0xFFu) | (mq_spread8(i1 & 0xFFu) << 4) | sg;
                 bhi[i] = mq_spread8(i0 >> 8) | (mq_spread8(i1 >> 8) << 4) | sg;
             }
@@ -404,7 +435,7 @@ matmul_q_fp4_kernel(const __grid_constant__ CUtensorMap tmap_wq, const __grid_co
             for (uint32_t pc = 0; pc < MQ_PIECES; pc++)      // row 8 tok + pc: its chunk XOR is pc
                 *reinterpret_cast<uint32_t*>(bt + pc * 128u + (((lane >> 2) ^ pc) << 4)) = w[pc];
             // scales of this group's pieces: 2^(8 - (token max - group max) - 2 piece)
-            const int q0 = 8 - (int)(tmax_eff - e_eff);
+            const int q0 = 8 - (int)(te8 - e8);
             const uint32_t grp = lane >> 1;                  // group of 16 within the stage
             uint8_t* const sb = smem + (sfb_of(s) - base) + (grp >> 2) * 512u + (tok * MQ_PIECES) * 16u + (grp & 3u);
 #pragma unroll
@@ -534,11 +565,10 @@ matmul_q_fp4_kernel(const __grid_constant__ CUtensorMap tmap_wq, const __grid_co
                     if (KB > 1u) c += __uint_as_float(d1[pc]);
                     v += c;
                 }
-                const uint32_t te = tok_amax[t] >> 10;
-                const uint32_t te_eff = te ? te : 1u;
-                const float tscale = __uint_as_float((te_eff - 23u + 127u) << 23);     // 2^G
+                const uint32_t te = tok_amax[t] >> 23;
+                const float tscale = te >= 16u ? __uint_as_float((te - 8u) << 23) : 0.0f;   // 2^G, G = E_token - 8
                 v = v * tscale * g;
-                if (row_nan || te == 31u) v = __uint_as_float(0x7FC00000u);
+                if (row_nan || te == 255u) v = __uint_as_float(0x7FC00000u);
                 const size_t o = (size_t)t * a.n + n0 + row;
                 if (!to_partial && a.r) v += __ldg(a.r + o);
                 out[o] = v;

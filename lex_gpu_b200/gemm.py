@@ -98,13 +98,13 @@ def gemm_fp4(gpu: Gpu, x: np.ndarray, wq: np.ndarray, ws: np.ndarray, wg: np.nda
 
 def matmul_fp4(gpu: Gpu, x: np.ndarray, wq: np.ndarray, ws: np.ndarray, wg: np.ndarray,
                r: Optional[np.ndarray] = None, **sched) -> np.ndarray:
-    """matmul_q_x with the NVFP4 layout, host arrays in and out (llama.rs:444-499): t <= 4 tokens of f16
-    activations against weights used as f32 (not rounded to f16).  For tests and examples."""
+    """matmul_q_x with the NVFP4 layout, host arrays in and out (llama.rs:444-499): t <= 4 tokens of f16 or
+    f32 activations against weights used as f32 (not rounded to f16).  For tests and examples."""
     m, k = x.shape
     n = wq.shape[0]
-    if x.dtype != np.float16:
-        raise TypeError("x must be float16 (x_half)")
-    pipe = gpu.plan_matmul_fp4(m, n, k, r is not None, True, **sched)
+    if x.dtype not in (np.float16, np.float32):
+        raise TypeError("x must be float16 (x_half) or float32")
+    pipe = gpu.plan_matmul_fp4(m, n, k, r is not None, x.dtype == np.float16, **sched)
     q = QBuf(gpu, wq, ws, wg)
     xb = gpu.upload(x)
     rb = gpu.upload(np.ascontiguousarray(r, dtype=np.float32)) if r is not None else None

@@ -187,8 +187,44 @@ def test_names_and_refusals(gpu):
                 dict(t=0, n_out=128, n_in=256)]:
         with pytest.raises(L.LexbError):
             gpu.plan_matmul_fp4(bad["t"], bad["n_out"], bad["n_in"])
-    with pytest.raises(L.LexbError, match="f32 activations"):
-        gpu.plan_matmul_fp4(1, 128, 256, x_half=False)
+    p = gpu.plan_matmul_fp4(2, 256, 512, x_half=False)
+    assert p.describe().entry == b"matmul2_nvfp4_256x512"            # f32 activations: no _xh
+    p.close()
+
+
+@pytest.mark.parametrize("m,n,k", [(1, 128, 256), (2, 256, 1024), (4, 384, 2048), (1, 640, 5120), (3, 256, 7168)])
+def test_f32_activations(gpu, m, n, k):
+    _, wq, ws, wg = inputs.make_case(m, n, k, seed_base=440 + m)
+    x = np.random.Generator(np.random.PCG64(441 + m)).standard_normal((m, k)).astype(np.float32)
+    check(L.matmul_fp4(gpu, x, wq, ws, wg), O.matmul_q_x(x, wq, ws, wg))
+
+
+@pytest.mark.parametrize("kind", ["tiny", "huge", "outliers", "mantissa_all_ones", "zeros"])
+def test_f32_activation_ranges(gpu, kind):
+    m, n, k = 2, 256, 2048
+    _, wq, ws, wg = inputs.make_case(m, n, k, seed_base=450)
+    rng = np.random.Generator(np.random.PCG64(451))
+    x = rng.standard_normal((m, k)).astype(np.float32)
+    if kind == "tiny":
+        x *= np.float32(1e-30)
+    elif kind == "huge":
+        x *= np.float32(1e30)
+    elif kind == "outliers":
+        x[rng.random((m, k)) < 0.004] *= 3000
+    elif kind == "mantissa_all_ones":
+        x = (np.sign(x) * np.float32(1.9999999)).astype(np.float32)     # rounds up to the next power of two at 16 bits
+    elif kind == "zeros":
+        x[:] = 0
+    want = O.matmul_q_x(x, wq, ws, wg)
+    got = L.matmul_fp4(gpu, x, wq, ws, wg)
+    assert np.isfinite(got).all()
+    if kind == "zeros":
+        assert not got.any()
+        return
+    for t in range(m):
+        err = np.abs(got[t] - want[t]).max() / np.abs(want[t]).max()
+        print(f"  token {t}: {err:.3e} of scale")
+        assert err <= TOL
 
 
 def test_back_to_back_launches_with_early_weight_loads(gpu):
