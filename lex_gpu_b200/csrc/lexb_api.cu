@@ -606,8 +606,8 @@ int lexb_gemm_fp4_plan(lexb_gpu* g, uint32_t m, uint32_t n, uint32_t k, int resi
         if (m > lexb::MQ_MAX_TOKENS) return bail(fail(LEXB_ERR_SHAPE, "the block-scaled kernel takes at most %u tokens, not %u", lexb::MQ_MAX_TOKENS, m));
         if (n % lexb::MQ_ROWS) return bail(fail(LEXB_ERR_SHAPE, "matmul_q (nvfp4): %u rows per block do not divide n = %u", lexb::MQ_ROWS, n));
         if (k % lexb::MQ_STAGE_K) return bail(fail(LEXB_ERR_SHAPE, "matmul_q (nvfp4): blocks of %u columns do not divide k = %u", lexb::MQ_STAGE_K, k));
-        uint32_t stages = s.stages ? s.stages : lexb::MQ_MAX_STAGES;
-        if (stages < 2 || stages > lexb::MQ_MAX_STAGES || lexb::matmul_q_smem_bytes(stages) > g->smem_optin)
+        uint32_t stages = s.stages ? s.stages : (m <= 4u ? lexb::MQ_MAX_STAGES : 7u);     // what fits shared memory
+        if (stages < 2 || stages > lexb::MQ_MAX_STAGES || lexb::matmul_q_smem_bytes(m, stages) > g->smem_optin)
             return bail(fail(LEXB_ERR_ARG, "stages = %u outside [2, %u] or over the shared-memory limit", stages, lexb::MQ_MAX_STAGES));
         const uint32_t tiles = n / lexb::MQ_ROWS, kb_all = k / lexb::MQ_STAGE_K;
         const uint32_t sms = static_cast<uint32_t>(g->prop.multiProcessorCount);
@@ -631,7 +631,7 @@ int lexb_gemm_fp4_plan(lexb_gpu* g, uint32_t m, uint32_t n, uint32_t k, int resi
         }
         p->grid = tiles * splits;
         p->threads = lexb::MQ_THREADS;
-        p->smem = lexb::matmul_q_smem_bytes(stages);
+        p->smem = lexb::matmul_q_smem_bytes(m, stages);
         p->tm = m;
         if (p->entry[0] == 0)
             snprintf(p->entry, sizeof p->entry, "%s_%u_%u_%u_%u_%u_%u", stem, m, n, k, m, lexb::MQ_ROWS, lexb::MQ_STAGE_K);

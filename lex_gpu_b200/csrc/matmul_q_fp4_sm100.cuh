@@ -43,11 +43,14 @@ namespace lexb {
 constexpr uint32_t MQ_ROWS = 128;                         // weight rows per block
 constexpr uint32_t MQ_STAGE_K = 256;                      // values of K per stage: one 128-byte row of codes
 constexpr uint32_t MQ_PIECES = 8;                         // E2M1 digit rows per token
-constexpr uint32_t MQ_MAX_TOKENS = 4;
+constexpr uint32_t MQ_MAX_TOKENS = 8;
 constexpr uint32_t MQ_CODE_BYTES = MQ_ROWS * 128u;        // packed codes of a stage
-constexpr uint32_t MQ_B_BYTES = MQ_MAX_TOKENS * MQ_PIECES * 128u;   // the tokens' pieces of a stage
+// the tokens' pieces of a stage: 128 bytes x 8 rows per token, room for 4 or for 8 tokens
+__host__ __device__ constexpr uint32_t matmul_q_b_bytes(uint32_t m) { return m <= 4u ? 4096u : 8192u; }
 constexpr uint32_t MQ_SF_BYTES = 4u * 512u;               // one 512-byte scale block per MMA of the stage
-constexpr uint32_t MQ_STAGE_BYTES = MQ_CODE_BYTES + MQ_B_BYTES + 2u * MQ_SF_BYTES;
+__host__ __device__ constexpr uint32_t matmul_q_stage_bytes(uint32_t m) {
+    return MQ_CODE_BYTES + matmul_q_b_bytes(m) + 2u * MQ_SF_BYTES;      // a multiple of 1024: stages start on a swizzle-pattern boundary
+}
 // The scale bytes as stored come in their own, coarser ring: one load covers MQ_WS_GROUP stages, so
 // that a row's piece of it is 64 bytes (16 bytes per stage would fetch half-used 32-byte sectors).
 constexpr uint32_t MQ_WS_GROUP = 4;
@@ -59,11 +62,10 @@ constexpr uint32_t MQ_PIECE_WARPS = 8;                    // warps 10-17: the to
 constexpr uint32_t MQ_THREADS = 32u * (2u + MQ_SCALE_WARPS + MQ_PIECE_WARPS);
 constexpr uint32_t MQ_TMEM_COLS = 512;
 constexpr uint32_t MQ_MAX_STAGES = 8;
-constexpr uint32_t MQ_TMEM_D1 = 32;                       // second accumulator
-constexpr uint32_t MQ_TMEM_SFA = 64;                      // ring of 16 columns per stage
+constexpr uint32_t MQ_TMEM_D1 = 64;                       // second accumulator (N = 8 columns per token, at most 64)
+constexpr uint32_t MQ_TMEM_SFA = 128;                     // ring of 16 columns per stage
 constexpr uint32_t MQ_TMEM_SFB = MQ_TMEM_SFA + 16u * MQ_MAX_STAGES;
 
-static_assert(MQ_STAGE_BYTES % 1024u == 0, "every stage starts on a swizzle-pattern boundary");
 
 struct MatmulQArgs {
     const void* x;           // [m, k], f16 or f32
@@ -80,8 +82,8 @@ struct MatmulQArgs {
     uint32_t flags;                    // bit 0: the weights are constant, load them before the launch ahead has finished
 };
 
-__host__ __device__ constexpr uint32_t matmul_q_smem_bytes(uint32_t stages) {
-    return stages * MQ_STAGE_BYTES + MQ_WS_SLOTS * MQ_WS_SLOT_BYTES + (3u * stages + 1u + 2u * MQ_WS_SLOTS) * 8u + 64u + MQ_ROWS + 1024u;
+__host__ __device__ constexpr uint32_t matmul_q_smem_bytes(uint32_t m, uint32_t stages) {
+    return stages * matmul_q_stage_bytes(m) + MQ_WS_SLOTS * MQ_WS_SLOT_BYTES + (3u * stages + 1u + 2u * MQ_WS_SLOTS) * 8u + 64u + MQ_ROWS + 1024u;
 }
 
 // bits [2i+1 : 2i] of an 8-bit value -> byte i
@@ -106,9 +108,10 @@ matmul_q_fp4_kernel(const __grid_constant__ CUtensorMap tmap_wq, const __grid_co
     uint8_t* const smem = smem_raw + (base - raw_addr);
 
     const uint32_t S = a.stages;
+    const uint32_t MQ_STAGE_BYTES = matmul_q_stage_bytes(a.m);
     auto codes_of = [&](uint32_t s) { return base + s * MQ_STAGE_BYTES; };
     auto b_of = [&](uint32_t s) { return codes_of(s) + MQ_CODE_BYTES; };
-    auto sfa_of = [&](uint32_t s) { return b_of(s) + MQ_B_BYTES; };
+    auto sfa_of = [&](uint32_t s) { return b_of(s) + matmul_q_b_bytes(a.m); };
     auto sfb_of = [&](uint32_t s) { return sfa_of(s) + MQ_SF_BYTES; };
     const uint32_t ws_base = base + S * MQ_STAGE_BYTES;                   // MQ_WS_SLOTS slots of scale bytes as stored
     const uint32_t bars = ws_base + MQ_WS_SLOTS * MQ_WS_SLOT_BYTES;
@@ -122,7 +125,7 @@ matmul_q_fp4_kernel(const __grid_constant__ CUtensorMap tmap_wq, const __grid_co
     uint32_t* const tmem_slot = misc;
     volatile uint32_t* const abort_flag = misc + 1;
     uint32_t* const tok_amax = misc + 2;                                   // [MQ_MAX_TOKENS]
-    volatile uint32_t* const fix_flag = misc + 6;
+    volatile uint32_t* const fix_flag = misc + 2 + MQ_MAX_TOKENS;
     volatile uint8_t* const nan_rows = reinterpret_cast<volatile uint8_t*>(misc + 16);   // [MQ_ROWS]: a NaN scale byte seen
 
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
@@ -324,18 +327,18 @@ matmul_q_fp4_kernel(const __grid_constant__ CUtensorMap tmap_wq, const __grid_co
         if (xw < PW && xw < items) xv = load_chunk(xw / a.m, xw % a.m);
         // largest magnitude of each token as f32 bits (its exponent gives the scale offset G); the
         // tokens' loads go out together
-        {
-            uint32_t mx[MQ_MAX_TOKENS] = {0, 0, 0, 0};
+        for (uint32_t t0 = 0; t0 < a.m; t0 += 4u) {               // four tokens at a time (registers)
+            uint32_t mx[4] = {0, 0, 0, 0};
             const uint4* xr = reinterpret_cast<const uint4*>(a.x);
             const uint32_t row_chunks = XF32 ? a.k / 4u : a.k / 8u;
 #pragma unroll 4
             for (uint32_t i = xt; i < row_chunks; i += 32u * MQ_PIECE_WARPS) {
-                uint4 v[MQ_MAX_TOKENS];
+                uint4 v[4];
 #pragma unroll
-                for (uint32_t t = 0; t < MQ_MAX_TOKENS; t++)
-                    v[t] = t < a.m ? __ldg(xr + (size_t)t * row_chunks + i) : make_uint4(0, 0, 0, 0);
+                for (uint32_t t = 0; t < 4; t++)
+                    v[t] = t0 + t < a.m ? __ldg(xr + (size_t)(t0 + t) * row_chunks + i) : make_uint4(0, 0, 0, 0);
 #pragma unroll
-                for (uint32_t t = 0; t < MQ_MAX_TOKENS; t++) {
+                for (uint32_t t = 0; t < 4; t++) {
                     if (XF32) {
                         mx[t] = max(max(mx[t], v[t].x & 0x7FFFFFFFu), v[t].y & 0x7FFFFFFFu);
                         mx[t] = max(max(mx[t], v[t].z & 0x7FFFFFFFu), v[t].w & 0x7FFFFFFFu);
@@ -348,15 +351,15 @@ matmul_q_fp4_kernel(const __grid_constant__ CUtensorMap tmap_wq, const __grid_co
                 }
             }
 #pragma unroll
-            for (uint32_t t = 0; t < MQ_MAX_TOKENS; t++) {
-                if (t < a.m) {
+            for (uint32_t t = 0; t < 4; t++) {
+                if (t0 + t < a.m) {
                     uint32_t r = mx[t];
                     if (!XF32) {
                         r = max(r & 0xFFFFu, r >> 16);
                         r = __float_as_uint(__half2float(__ushort_as_half((unsigned short)r)));   // exact; inf and NaN stay so
                     }
                     r = __reduce_max_sync(0xFFFFFFFFu, r);
-                    if (lane == 0) atomicMax(tok_amax + t, r);
+                    if (lane == 0) atomicMax(tok_amax + t0 + t, r);
                 }
             }
         }
@@ -437,7 +440,8 @@ matmul_q_fp4_kernel(const __grid_constant__ CUtensorMap tmap_wq, const __grid_co
             // scales of this group's pieces: 2^(8 - (token max - group max) - 2 piece)
             const int q0 = 8 - (int)(te8 - e8);
             const uint32_t grp = lane >> 1;                  // group of 16 within the stage
-            uint8_t* const sb = smem + (sfb_of(s) - base) + (grp >> 2) * 512u + (tok * MQ_PIECES) * 16u + (grp & 3u);
+            // row n = 8 tok + piece of the block: 16 bytes per (n % 32), 4 bytes per (n / 32), one per group
+            uint8_t* const sb = smem + (sfb_of(s) - base) + (grp >> 2) * 512u + ((tok & 3u) * MQ_PIECES) * 16u + (tok >> 2) * 4u + (grp & 3u);
 #pragma unroll
             for (uint32_t i = 0; i < 4; i++) {
                 const uint32_t pc = 4u * (lane & 1u) + i;
