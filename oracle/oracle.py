@@ -255,6 +255,26 @@ def kat_inputs(m: int, n: int, k: int, residual: bool = False):
     return x16, q.reshape(n, k // 2), sc.reshape(n, k // 16), g, r
 
 
+def ref_fill(length: int, seed: int) -> np.ndarray:
+    """The input recipe of the reference's GPU tests (crates/lex-cuda/tests/device_gpu.rs:29-36):
+    x_i = ((i * 2654435761 + seed) mod 2^32 >> 9) / 2^22 - 1, in [-1, 1)."""
+    i = np.arange(length, dtype=np.uint64)
+    x = (i * np.uint64(2654435761) + np.uint64(seed)) & np.uint64(0xFFFFFFFF)
+    return ((x >> np.uint64(9)).astype(np.float32) / np.float32(4194304.0)) - np.float32(1.0)
+
+
+def ref_nvfp4_bytes(n_out: int, n_in: int, mul: int, add: int, scale_base: int, scale_mod: int):
+    """Codes and scale bytes as those tests build them (device_gpu.rs:138-143, 163-168, 189-194, 255-260):
+    code byte i = (i * mul + add) & 0xFF and scale byte i = scale_base + i % scale_mod, each minus 128 as an
+    i8 VALUE - so the byte the kernels see has bit 7 flipped (scale bytes come out with the sign bit set:
+    negative scales)."""
+    i = np.arange(n_out * n_in // 2, dtype=np.uint64)
+    codes = ((((i * np.uint64(mul) + np.uint64(add)) & np.uint64(0xFF)).astype(np.int64) - 128) & 0xFF).astype(np.uint8)
+    j = np.arange(n_out * n_in // 16, dtype=np.int64)
+    scales = ((scale_base + j % scale_mod - 128) & 0xFF).astype(np.uint8)
+    return codes.reshape(n_out, n_in // 2), scales.reshape(n_out, n_in // 16)
+
+
 def f64_restatement(x16, wq, ws, wg) -> np.ndarray:
     """The expected value of syntax.rs:559-575: decode in f64 with the test's own tables,
     round the weight to f16 from f64, multiply and sum in f64."""

@@ -249,3 +249,30 @@ def test_back_to_back_launches_with_early_weight_loads(gpu):
     for w, yb in zip(sets, ys):
         check(gpu.download(yb, np.float32, (m, n)), O.matmul_q_x(x, *w))
     assert gpu.status_word() == 0
+
+
+# ---------------------------------------------------------------- the reference's own GPU test recipes
+
+@pytest.mark.parametrize("m,n_in,mul,add,sbase,smod,rows,seed,x_half", [
+    (1, 512, 31, 7, 0x38, 5, "ones", 5, False),          # nvfp4_matvec_matches_the_interpreter (device_gpu.rs:131-152)
+    (1, 5120, 131, 17, 0x30, 11, "mod3", 9, False),      # nvfp4_matvec_loaded_wide_... (:159-179)
+    (3, 5120, 97, 3, 0x34, 7, "const", 13, False),       # nvfp4_matmul_loaded_wide_... (:184-204), m = 3 and 8
+    (8, 5120, 97, 3, 0x34, 7, "const", 13, False),
+    (8, 1024, 97, 3, 0x34, 7, "mod5", 3, True),          # the gemm-vs-matmul_q_x recipe (:244-262), half activations
+])
+def test_reference_gpu_test_recipes(gpu, m, n_in, mul, add, sbase, smod, rows, seed, x_half):
+    """Same inputs as the reference's CUDA tests, with 128 output rows (its 32 and 64 are below this kernel's
+    row tile); its bar for these kernels is 1e-4 of scale."""
+    n_out = 128
+    wq, ws = O.ref_nvfp4_bytes(n_out, n_in, mul, add, sbase, smod)
+    i = np.arange(n_out)
+    wg = {"ones": np.ones(n_out), "mod3": 0.5 + (i % 3) * 0.25, "const": np.full(n_out, 0.75),
+          "mod5": 0.5 + (i % 5) * 0.125}[rows].astype(np.float32)
+    x = O.ref_fill(m * n_in, seed).reshape(m, n_in)
+    if x_half:
+        x = x.astype(np.float16)
+    want = O.matmul_q_x(x, wq, ws, wg)
+    got = L.matmul_fp4(gpu, x, wq, ws, wg)
+    err, scale, _ = O.err_of_scale(got, want)
+    print(f"  {err:.3e} of scale {scale:.3e}")
+    assert scale > 1e-3 and err <= 1e-4

@@ -212,3 +212,18 @@ def test_matmul_q_x_chunks_residual_and_f32_x():
     assert np.float32(acc + r[1, 7]) == whole[1, 7]
     with pytest.raises(ValueError):
         O.matmul_q_x(x, wq, ws, wg, kc=100)                        # must divide k in groups of 16 (llama.rs:407-413)
+
+
+def test_matmul_q_x_on_the_reference_gpu_test_recipes():
+    """crates/lex-cuda/tests/device_gpu.rs:131-209: the recipes feed scale bytes with the sign bit set."""
+    x = O.ref_fill(512, 5).reshape(1, 512)
+    assert x.min() >= -1 and x.max() < 1 and x[0, 0] == np.float32(5 >> 9) / np.float32(4194304.0) - 1
+    wq, ws = O.ref_nvfp4_bytes(64, 512, 31, 7, 0x38, 5)
+    assert wq[0, 0] == ((7 - 128) & 0xFF) and set(np.unique(ws)) == {0xB8, 0xB9, 0xBA, 0xBB, 0xBC}
+    wg = np.ones(64, dtype=np.float32)
+    y = O.matmul_q_x(x, wq, ws, wg)
+    w = O.np_dequant_f32(wq, ws, wg).astype(np.float64)
+    assert w[0, 0] == -6.0 and w[0, 1] == 0.0                        # code 7 (6.0), then code 8 (-0), times the scale byte 0xb8 = -1
+    ref = x.astype(np.float64) @ w.T
+    assert np.abs(y - ref).max() / np.abs(ref).max() < 1e-6
+    assert np.abs(ref).max() > 1.0
