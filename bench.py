@@ -369,7 +369,7 @@ def run_ours(args):
         except Exception as e:      # symmetric memory unavailable on this machine
             allgather["fused_peer_stores"] = {"unavailable": repr(e)[:200]}
 
-    # ---- one layer of the 27B MLP stack at m = 4096 (BASELINE config 4), n-sharded: gate, up (n=17408,
+    # ---- one layer of the 27B MLP stack at m = 4096 (benchmark configuration 4 of BASELINE.json), n-sharded: gate, up (n=17408,
     # k=5120) and down (n=5120, k=17408), independent calls, y not chained.  Reported, not the headline.
     stack = None
     if full and args.stack:

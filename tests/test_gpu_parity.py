@@ -104,7 +104,7 @@ def test_matvec_residual(gpu):
 @pytest.mark.parametrize("m", [1, 4])
 @pytest.mark.parametrize("n,k", [(17408, 5120), (5120, 17408)])
 def test_matvec_benchmark_shapes(gpu, m, n, k):
-    """BASELINE config 1 at full size, against the full oracle."""
+    """Benchmark configuration 1 of BASELINE.json at full size, against the full oracle."""
     x, wq, ws, wg = inputs.make_case(m, n, k)
     got = L.gemm_fp4(gpu, x, wq, ws, wg)
     check(got, O.gemm_fp4(x, wq, ws, wg))
@@ -123,7 +123,7 @@ def test_a_token_does_not_depend_on_its_batch(gpu):
 # ---------------------------------------------------------------- tcgen05 path (m > 16)
 
 def test_gemm_config0_readme_example(gpu):
-    """m = n = 128, k = 64: one tile, one K step (BASELINE config 0); also against the committed fixture."""
+    """m = n = 128, k = 64: one tile, one K step (configuration 0 of BASELINE.json); also against the committed fixture."""
     from pathlib import Path
     x, wq, ws, wg = inputs.make_case(128, 128, 64)
     got = L.gemm_fp4(gpu, x, wq, ws, wg)
@@ -255,14 +255,14 @@ def test_gemm_wide_scale_range(gpu):
 
 @pytest.mark.parametrize("n,k", [(17408, 5120), (5120, 17408)])
 def test_gemm_27b_mlp_prefill_m512(gpu, n, k):
-    """BASELINE config 3 (m = 512) at full size against the full oracle."""
+    """Configuration 3 of BASELINE.json (m = 512) at full size against the full oracle."""
     x, wq, ws, wg = inputs.make_case(512, n, k)
     check(L.gemm_fp4(gpu, x, wq, ws, wg), O.gemm_fp4(x, wq, ws, wg), rel_tol=LONG_K_REL)
 
 
 @pytest.mark.parametrize("n,k", [(6144, 4096), (28672, 4096), (4096, 14336)])
 def test_gemm_llama8b_prefill_projections(gpu, n, k):
-    """BASELINE config 2: oracle on a slice of rows (full n on the GPU)."""
+    """Configuration 2 of BASELINE.json: oracle on a slice of rows (full n on the GPU)."""
     x, wq, ws, wg = inputs.make_case(512, n, k, seed_base=2)
     got = L.gemm_fp4(gpu, x, wq, ws, wg)
     lo, hi = n // 2 - 256, n // 2 + 256
