@@ -293,10 +293,44 @@ def run_ours(args):
             dist.all_reduce(tt, op=dist.ReduceOp.MAX)
             e2e_secs = float(tt.item())
         checksum = float(hy.array(np.float32, (M, n_local))[0, :8].sum())
+        serial_secs = e2e_secs
+        # The same steps double-buffered: two streams, two sets of staging buffers, lexb_gemm_fp4_enqueue_host.
+        # Every step still copies its x in and its y out inside the timed region; step i's copy back overlaps
+        # step i+1's copy in and launch.
+        stream2 = torch.cuda.Stream(device=dev)
+        lanes = [(stream, hx, hy, xd, yd)]
+        hx2 = L.HostBuffer(x_np.nbytes)
+        hx2.array(np.float16, (M, K))[:] = x_np
+        hy2 = L.HostBuffer(M * n_local * 4)
+        lanes.append((stream2, hx2, hy2, gpu.alloc(x_np.nbytes), gpu.alloc(M * n_local * 4)))
+
+        def piped(nsteps, first):
+            for i in range(nsteps):
+                st, h_x, h_y, d_x, d_y = lanes[i % 2]
+                gpu.set_stream(st.cuda_stream)
+                b = weights[(first + i) % COPIES][1]
+                gpu.enqueue_host(pipe, h_x.ptr, d_x, b[0], b[1], b[2], None, d_y, h_y.ptr)
+            torch.cuda.synchronize(dev)
+
+        piped(4, 0)
+        barrier()
+        t = time.perf_counter()
+        piped(e2e_steps, 4)
+        e2e_secs = time.perf_counter() - t
+        gpu.set_stream(stream.cuda_stream)
+        if dist is not None:
+            tt = torch.tensor([e2e_secs], device=dev, dtype=torch.float64)
+            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+            e2e_secs = float(tt.item())
+        checksum2 = float(hy2.array(np.float32, (M, n_local))[0, :8].sum())
         e2e = {"value": flops_step * e2e_steps / e2e_secs / 1e12, "unit": "TFLOP/s",
                "h2d_bytes_per_step": int(x_np.nbytes), "d2h_bytes_per_step": int(M * n_local * 4), "steps": e2e_steps,
                "ms_per_step": 1e3 * e2e_secs / e2e_steps,
-               "note": "lexb_gemm_fp4_run_host: pinned x in, y out, weights resident"}
+               "note": "lexb_gemm_fp4_enqueue_host on two streams: every step copies pinned x in and y out, weights "
+                       "resident; one step's copy back overlaps the next step's copy in and launch",
+               "one_stream": {"value": flops_step * e2e_steps / serial_secs / 1e12, "ms_per_step": 1e3 * serial_secs / e2e_steps,
+                              "note": "lexb_gemm_fp4_run_host, one step at a time"},
+               "checksum_second_lane": checksum2}
 
     # ---- matvec (m = 1, 4): GB/s of weight bytes
     matvec = {}

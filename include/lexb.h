@@ -161,6 +161,13 @@ LEXB_API int lexb_gemm_fp4_launch_gather(lexb_gpu* gpu, const lexb_pipeline* p, 
 LEXB_API int lexb_gemm_fp4_run_host(lexb_gpu* gpu, const lexb_pipeline* p, const void* x_host, lexb_buffer* x_dev,
                                     const lexb_buffer* wq, const lexb_buffer* ws, const lexb_buffer* wg,
                                     const lexb_buffer* r_or_null, lexb_buffer* y_dev, void* y_host);
+/* The same three steps enqueued on the gpu's current stream without the wait: the caller calls lexb_sync
+ * (on that stream) before it reads y_host or rewrites x_host.  With two streams (lexb_set_stream) and two
+ * sets of staging buffers a caller overlaps one chunk's copy back with the next chunk's copy in and launch;
+ * the reference has no counterpart (its runtime is synchronous per batch, crates/lex-cuda/src/device.rs:650-672). */
+LEXB_API int lexb_gemm_fp4_enqueue_host(lexb_gpu* gpu, const lexb_pipeline* p, const void* x_host, lexb_buffer* x_dev,
+                                        const lexb_buffer* wq, const lexb_buffer* ws, const lexb_buffer* wg,
+                                        const lexb_buffer* r_or_null, lexb_buffer* y_dev, void* y_host);
 /* Gpu::run_launches, crates/lex-cuda/src/device.rs:650-672: all steps, one synchronise;
  * cpu_s = host time to enqueue, wall_s = host time until the device is idle. */
 LEXB_API int lexb_run_launches(lexb_gpu* gpu, const lexb_step* steps, size_t nsteps, double* cpu_s, double* wall_s);

@@ -823,6 +823,20 @@ int lexb_gemm_fp4_launch_gather(lexb_gpu* g, const lexb_pipeline* p, const lexb_
     return launch_one(g, p, x, wq, ws, wg, r, nullptr, &gd);
 }
 
+int lexb_gemm_fp4_enqueue_host(lexb_gpu* g, const lexb_pipeline* p, const void* x_host, lexb_buffer* x_dev,
+                               const lexb_buffer* wq, const lexb_buffer* ws, const lexb_buffer* wg, const lexb_buffer* r,
+                               lexb_buffer* y_dev, void* y_host) {
+    int rc = use(g);
+    if (rc) return rc;
+    if (!p || !x_host || !y_host || !x_dev || !y_dev) return fail(LEXB_ERR_ARG, "lexb_gemm_fp4_enqueue_host: null argument");
+    const size_t xb = static_cast<size_t>(p->m) * p->k * (p->x_f32 ? 4 : 2), yb = static_cast<size_t>(p->m) * p->n * 4;
+    if (x_dev->bytes < xb || y_dev->bytes < yb) return fail(LEXB_ERR_ARG, "lexb_gemm_fp4_enqueue_host: staging buffers too small");
+    CUDA_TRY(cudaMemcpyAsync(x_dev->ptr, x_host, xb, cudaMemcpyHostToDevice, g->stream));
+    if ((rc = launch_one(g, p, x_dev, wq, ws, wg, r, y_dev))) return rc;
+    CUDA_TRY(cudaMemcpyAsync(y_host, y_dev->ptr, yb, cudaMemcpyDeviceToHost, g->stream));
+    return LEXB_OK;
+}
+
 int lexb_gemm_fp4_run_host(lexb_gpu* g, const lexb_pipeline* p, const void* x_host, lexb_buffer* x_dev,
                            const lexb_buffer* wq, const lexb_buffer* ws, const lexb_buffer* wg, const lexb_buffer* r,
                            lexb_buffer* y_dev, void* y_host) {

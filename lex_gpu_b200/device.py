@@ -26,6 +26,7 @@ SYMBOLS = [
     "lexb_sync", "lexb_alloc", "lexb_zeroed", "lexb_wrap", "lexb_free", "lexb_buffer_ptr", "lexb_buffer_bytes",
     "lexb_upload", "lexb_download", "lexb_memset", "lexb_host_alloc", "lexb_host_free", "lexb_gemm_fp4_plan",
     "lexb_pipeline_free", "lexb_pipeline_describe", "lexb_gemm_fp4_launch", "lexb_gemm_fp4_run_host",
+    "lexb_gemm_fp4_enqueue_host",
     "lexb_run_launches", "lexb_run_each_timed", "lexb_time_launches", "lexb_status_word",
     "lexb_selftest_bounded_wait", "lexb_dequant_fp4_f16", "lexb_shard_rows", "lexb_trace_enable", "lexb_trace_read",
     "lexb_gemm_fp4_splitk_static", "lexb_gemm_fp4_launch_gather", "lexb_silu_mul", "lexb_prefill_chunks",
@@ -109,6 +110,7 @@ def load_library() -> ctypes.CDLL:
     L.lexb_pipeline_describe.argtypes = [vp, POINTER(Lowered)]
     L.lexb_gemm_fp4_launch.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp]
     L.lexb_gemm_fp4_run_host.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp]
+    L.lexb_gemm_fp4_enqueue_host.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp]
     L.lexb_run_launches.argtypes = [vp, POINTER(StepStruct), sz, POINTER(c_double), POINTER(c_double)]
     L.lexb_run_each_timed.argtypes = [vp, POINTER(StepStruct), sz, POINTER(c_double)]
     L.lexb_time_launches.argtypes = [vp, POINTER(StepStruct), sz, u32, POINTER(c_double)]
@@ -344,6 +346,13 @@ class Gpu:
         _check(self._L.lexb_gemm_fp4_launch_gather(self.handle, pipe.handle, x.handle, wq.handle, ws.handle, wg.handle,
                                                    r.handle if r is not None else None, arr, len(y_ptr_of_rank),
                                                    n_total, n0))
+
+    def enqueue_host(self, pipe: Pipeline, x_host_ptr: int, x_dev: Buffer, wq: Buffer, ws: Buffer, wg: Buffer,
+                     r: Optional[Buffer], y_dev: Buffer, y_host_ptr: int) -> None:
+        """run_host without the wait: copy in, launch, copy out on the current stream; sync() before using y."""
+        _check(self._L.lexb_gemm_fp4_enqueue_host(self.handle, pipe.handle, c_void_p(x_host_ptr), x_dev.handle, wq.handle,
+                                                  ws.handle, wg.handle, r.handle if r is not None else None,
+                                                  y_dev.handle, c_void_p(y_host_ptr)))
 
     def run_host(self, pipe: Pipeline, x_host_ptr: int, x_dev: Buffer, wq: Buffer, ws: Buffer, wg: Buffer,
                  r: Optional[Buffer], y_dev: Buffer, y_host_ptr: int) -> None:

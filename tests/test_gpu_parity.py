@@ -358,6 +358,36 @@ def test_run_host_copies_in_and_out(gpu):
     check(hy.array(np.float32, (m, n)).copy(), O.gemm_fp4(x, wq, ws, wg))
 
 
+def test_enqueue_host_on_two_streams(gpu):
+    """Double-buffered chunks: two streams, two sets of staging buffers, no wait between the chunks."""
+    import torch
+    m, n, k = 96, 512, 1024
+    wq, ws, wg = inputs.make_weights(n, k, seed_base=12)
+    q = L.QBuf(gpu, wq, ws, wg)
+    pipe = gpu.plan_gemm_fp4(m, n, k)
+    xs = [inputs.make_x(m, k, seed_base=20 + i) for i in range(5)]
+    streams = [torch.cuda.Stream(), torch.cuda.Stream()]
+    lanes = [(L.HostBuffer(m * k * 2), L.HostBuffer(m * n * 4), gpu.alloc(m * k * 2), gpu.alloc(m * n * 4)) for _ in range(2)]
+    got = []
+    try:
+        for i, x in enumerate(xs):
+            hx, hy, xd, yd = lanes[i % 2]
+            if i >= 2:                                  # the lane's previous chunk must be out before its buffers are reused
+                streams[i % 2].synchronize()
+                got.append(hy.array(np.float32, (m, n)).copy())
+            hx.array(np.float16, (m, k))[:] = x
+            gpu.set_stream(streams[i % 2].cuda_stream)
+            gpu.enqueue_host(pipe, hx.ptr, xd, q.wq, q.ws, q.wg, None, yd, hy.ptr)
+        for i in range(len(xs) - 2, len(xs)):
+            streams[i % 2].synchronize()
+            got.append(lanes[i % 2][1].array(np.float32, (m, n)).copy())
+    finally:
+        gpu.set_stream(None)
+    for x, y in zip(xs, got):
+        check(y, O.gemm_fp4(x, wq, ws, wg))
+    assert gpu.status_word() == 0
+
+
 def test_wrapping_a_torch_tensor(gpu):
     import torch
     m, n, k = 32, 128, 256
