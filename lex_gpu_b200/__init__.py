@@ -4,8 +4,8 @@ The compute lives in liblexb.so (CUDA, built from csrc/ by `python -m lex_gpu_b2
 this package is its ctypes binding plus the synthetic-input generator and the n-sharded
 multi-GPU wrapper.  Importing the package does not load the library; opening a Gpu does.
 """
-from .device import Gpu, Buffer, Pipeline, HostBuffer, LexbError, load_library, shard_rows, prefill_chunks  # noqa: F401
+from .device import Gpu, Buffer, Pipeline, HostBuffer, StepList, LexbError, load_library, shard_rows, prefill_chunks  # noqa: F401
 from .gemm import Gemm, QBuf, GemmKernels, gemm_fp4, matmul_fp4, dequant_fp4_f16  # noqa: F401
 
-__all__ = ["Gpu", "Buffer", "Pipeline", "HostBuffer", "LexbError", "load_library", "shard_rows", "prefill_chunks",
+__all__ = ["Gpu", "Buffer", "Pipeline", "HostBuffer", "StepList", "LexbError", "load_library", "shard_rows", "prefill_chunks",
            "Gemm", "QBuf", "GemmKernels", "gemm_fp4", "matmul_fp4", "dequant_fp4_f16"]

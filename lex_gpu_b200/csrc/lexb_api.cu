@@ -238,8 +238,16 @@ int get_maps(const lexb_pipeline* p, const void* x, const void* wq, const void* 
     return LEXB_OK;
 }
 
+// The weights of the launch that follows in a step list: a hint for the block-scaled kernel, which pulls
+// their first stages into L2 before it ends.
+struct NextWeights {
+    const lexb_pipeline* pipe;
+    const lexb_buffer *x, *wq, *ws;
+};
+
 int launch_one(lexb_gpu* g, const lexb_pipeline* p, const lexb_buffer* x, const lexb_buffer* wq, const lexb_buffer* ws,
-               const lexb_buffer* wg, const lexb_buffer* r, lexb_buffer* y, const lexb::GatherDst* gather = nullptr) {
+               const lexb_buffer* wg, const lexb_buffer* r, lexb_buffer* y, const lexb::GatherDst* gather = nullptr,
+               const NextWeights* next = nullptr) {
     if (!p) return fail(LEXB_ERR_ARG, "null pipeline");
     if (p->gpu != g) return fail(LEXB_ERR_ARG, "pipeline was planned on another gpu handle");
     const size_t m = p->m, n = p->n, k = p->k;
@@ -321,6 +329,13 @@ int launch_one(lexb_gpu* g, const lexb_pipeline* p, const lexb_buffer* x, const 
         a.m = p->m; a.n = p->n; a.k = p->k; a.stages = p->stages;
         a.k_splits = p->k_splits; a.kb_per_split = p->kb_per_split;
         a.ws_pitch = p->ws_pitch; a.flags = p->flags;
+        lexb_pipeline::MapEntry nmaps = maps;         // placeholders when there is no hint (next_grid = 0)
+        if (next && next->pipe && next->pipe->kernel == KERNEL_MATMUL_Q && next->pipe->gpu == g && next->wq && next->ws &&
+            next->x && (p->flags & 1u) && get_maps(next->pipe, next->x->ptr, next->wq->ptr, next->ws->ptr, &nmaps) == LEXB_OK) {
+            const lexb_pipeline* q = next->pipe;
+            a.next_grid = q->grid; a.next_k_splits = q->k_splits; a.next_kb_per_split = q->kb_per_split;
+            a.next_kb_all = q->k / lexb::MQ_STAGE_K; a.next_stages = q->stages; a.next_ws_pitch = q->ws_pitch;
+        }
         cudaLaunchConfig_t cfg{};
         cfg.gridDim = dim3(p->grid);
         cfg.blockDim = dim3(p->threads);
@@ -333,11 +348,11 @@ int launch_one(lexb_gpu* g, const lexb_pipeline* p, const lexb_buffer* x, const 
         cfg.numAttrs = g->pdl ? 1 : 0;
         a.trace = (g->d_trace && p->grid <= g->trace_ctas) ? g->d_trace : nullptr;
         if (p->x_f32) {
-            if (a.trace) CUDA_TRY(cudaLaunchKernelEx(&cfg, lexb::matmul_q_fp4_kernel<true, true>, maps.map_wq, maps.map_ws, a));
-            else CUDA_TRY(cudaLaunchKernelEx(&cfg, lexb::matmul_q_fp4_kernel<false, true>, maps.map_wq, maps.map_ws, a));
+            if (a.trace) CUDA_TRY(cudaLaunchKernelEx(&cfg, lexb::matmul_q_fp4_kernel<true, true>, maps.map_wq, maps.map_ws, nmaps.map_wq, nmaps.map_ws, a));
+            else CUDA_TRY(cudaLaunchKernelEx(&cfg, lexb::matmul_q_fp4_kernel<false, true>, maps.map_wq, maps.map_ws, nmaps.map_wq, nmaps.map_ws, a));
         } else {
-            if (a.trace) CUDA_TRY(cudaLaunchKernelEx(&cfg, lexb::matmul_q_fp4_kernel<true, false>, maps.map_wq, maps.map_ws, a));
-            else CUDA_TRY(cudaLaunchKernelEx(&cfg, lexb::matmul_q_fp4_kernel<false, false>, maps.map_wq, maps.map_ws, a));
+            if (a.trace) CUDA_TRY(cudaLaunchKernelEx(&cfg, lexb::matmul_q_fp4_kernel<true, false>, maps.map_wq, maps.map_ws, nmaps.map_wq, nmaps.map_ws, a));
+            else CUDA_TRY(cudaLaunchKernelEx(&cfg, lexb::matmul_q_fp4_kernel<false, false>, maps.map_wq, maps.map_ws, nmaps.map_wq, nmaps.map_ws, a));
         }
     } else {
         lexb::MatvecArgs a{};
@@ -361,14 +376,19 @@ int launch_one(lexb_gpu* g, const lexb_pipeline* p, const lexb_buffer* x, const 
     return LEXB_OK;
 }
 
-int launch_step(lexb_gpu* g, const lexb_step& s) {
+int launch_step(lexb_gpu* g, const lexb_step& s, const lexb_step* following = nullptr) {
     if (!s.pipeline || !s.buffers) return fail(LEXB_ERR_ARG, "step without pipeline or buffers");
     const bool res = s.pipeline->residual;
     if (s.nbuffers != (res ? 6u : 5u))
         return fail(LEXB_ERR_ARG, "step binds %u buffers, the pipeline takes %u: [x, wq, ws, wg, %sy]", s.nbuffers,
                     res ? 6u : 5u, res ? "r, " : "");
     lexb_buffer* const* b = s.buffers;
-    return launch_one(g, s.pipeline, b[0], b[1], b[2], b[3], res ? b[4] : nullptr, res ? b[5] : b[4]);
+    NextWeights nw{};
+    static const bool hints = env_u32("LEXB_NEXT_HINT", 1) != 0;     // LEXB_NEXT_HINT=0: no prefetch of the next step's weights
+    if (hints && following && following->pipeline && following->buffers && following->nbuffers >= 5u)
+        nw = NextWeights{following->pipeline, following->buffers[0], following->buffers[1], following->buffers[2]};
+    return launch_one(g, s.pipeline, b[0], b[1], b[2], b[3], res ? b[4] : nullptr, res ? b[5] : b[4], nullptr,
+                      nw.pipe ? &nw : nullptr);
 }
 
 }  // namespace
@@ -858,7 +878,7 @@ int lexb_run_launches(lexb_gpu* g, const lexb_step* steps, size_t nsteps, double
     if (!steps && nsteps) return fail(LEXB_ERR_ARG, "lexb_run_launches: null steps");
     const auto t0 = std::chrono::steady_clock::now();
     for (size_t i = 0; i < nsteps; i++)
-        if ((rc = launch_step(g, steps[i]))) return rc;
+        if ((rc = launch_step(g, steps[i], i + 1 < nsteps ? &steps[i + 1] : nullptr))) return rc;
     const auto t1 = std::chrono::steady_clock::now();
     CUDA_TRY(cudaStreamSynchronize(g->stream));
     const auto t2 = std::chrono::steady_clock::now();
@@ -877,7 +897,7 @@ int lexb_run_each_timed(lexb_gpu* g, const lexb_step* steps, size_t nsteps, doub
         if (cudaEventCreate(&e) != cudaSuccess) { cleanup(); return fail(LEXB_ERR_CUDA, "cudaEventCreate failed"); }
     cudaEventRecord(ev[0], g->stream);
     for (size_t i = 0; i < nsteps; i++) {
-        if ((rc = launch_step(g, steps[i]))) { cleanup(); return rc; }
+        if ((rc = launch_step(g, steps[i], i + 1 < nsteps ? &steps[i + 1] : nullptr))) { cleanup(); return rc; }
         cudaEventRecord(ev[i + 1], g->stream);
     }
     cudaError_t e = cudaStreamSynchronize(g->stream);
@@ -901,8 +921,11 @@ int lexb_time_launches(lexb_gpu* g, const lexb_step* steps, size_t nsteps, uint3
     CUDA_TRY(cudaStreamSynchronize(g->stream));
     cudaEventRecord(a, g->stream);
     for (uint32_t r = 0; r < reps; r++)
-        for (size_t i = 0; i < nsteps; i++)
-            if ((rc = launch_step(g, steps[i]))) { cudaEventDestroy(a); cudaEventDestroy(b); return rc; }
+        for (size_t i = 0; i < nsteps; i++) {
+            // the list repeats: the step after the last one is the first one again
+            const lexb_step* following = i + 1 < nsteps ? &steps[i + 1] : (r + 1 < reps ? &steps[0] : nullptr);
+            if ((rc = launch_step(g, steps[i], following))) { cudaEventDestroy(a); cudaEventDestroy(b); return rc; }
+        }
     cudaEventRecord(b, g->stream);
     cudaError_t e = cudaStreamSynchronize(g->stream);
     float ms = 0.f;

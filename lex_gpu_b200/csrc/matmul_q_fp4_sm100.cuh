@@ -80,6 +80,11 @@ struct MatmulQArgs {
     uint32_t k_splits, kb_per_split;   // in stages of 256
     uint32_t ws_pitch;                 // bytes per row of a scale load: min(64, k / 16)
     uint32_t flags;                    // bit 0: the weights are constant, load them before the launch ahead has finished
+    // The launch that follows this one in the step list, when it is of this kernel too (grid 0: none): its
+    // blocks' first `next_stages` stages of weights are prefetched into L2 by this launch's blocks once
+    // they have requested all of their own, so that DRAM keeps streaming through this launch's tail and the
+    // next one's set-up instead of idling.
+    uint32_t next_grid, next_k_splits, next_kb_per_split, next_kb_all, next_stages, next_ws_pitch;
 };
 
 __host__ __device__ constexpr uint32_t matmul_q_smem_bytes(uint32_t m, uint32_t stages) {
@@ -101,7 +106,8 @@ __device__ __forceinline__ uint32_t mq_ue4m3_pow2(int q) {
 
 template <bool TRACE, bool XF32>
 __global__ void __launch_bounds__(MQ_THREADS, 1)
-matmul_q_fp4_kernel(const __grid_constant__ CUtensorMap tmap_wq, const __grid_constant__ CUtensorMap tmap_ws, MatmulQArgs a) {
+matmul_q_fp4_kernel(const __grid_constant__ CUtensorMap tmap_wq, const __grid_constant__ CUtensorMap tmap_ws,
+                    const __grid_constant__ CUtensorMap next_wq, const __grid_constant__ CUtensorMap next_ws, MatmulQArgs a) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw_addr = smem_u32(smem_raw);
     const uint32_t base = (raw_addr + 1023u) & ~1023u;
@@ -230,6 +236,20 @@ matmul_q_fp4_kernel(const __grid_constant__ CUtensorMap tmap_wq, const __grid_co
                 // copies still in flight land in this block's shared memory: give them a bounded time
                 const long long t0 = clock64();
                 while (clock64() - t0 < 400000) {
+                }
+            } else {
+                // what the next launch's blocks will ask for first, into L2 (block c for block c; the
+                // blocks beyond this launch's grid are shared out in turns)
+                for (uint32_t c = blockIdx.x; c < a.next_grid; c += gridDim.x) {
+                    const uint32_t nsplit = c % a.next_k_splits, ntile = c / a.next_k_splits;
+                    const uint32_t nkb0 = nsplit * a.next_kb_per_split;
+                    uint32_t nkb = a.next_kb_all - nkb0 < a.next_kb_per_split ? a.next_kb_all - nkb0 : a.next_kb_per_split;
+                    if (nkb > a.next_stages) nkb = a.next_stages;
+                    for (uint32_t kb = 0; kb < nkb; kb++) {
+                        if ((kb & (MQ_WS_GROUP - 1u)) == 0u)
+                            tma_prefetch_l2_2d(&next_ws, (int)((nkb0 + kb) * (MQ_STAGE_K / 16)), (int)(ntile * MQ_ROWS));
+                        tma_prefetch_l2_2d(&next_wq, (int)((nkb0 + kb) * (MQ_STAGE_K / 2)), (int)(ntile * MQ_ROWS));
+                    }
                 }
             }
         }

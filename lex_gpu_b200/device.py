@@ -213,7 +213,10 @@ class Pipeline:
 Step = tuple  # (Pipeline, [Buffer, ...]) in the order [x, wq, ws, wg, (r), y]; device.rs:314
 
 
-class _Steps:
+class StepList:
+    """A step list marshalled once (the C array of lexb_step): pass it to run_launches / run_each_timed /
+    time_launches instead of the Python list when the same list is issued repeatedly or is being timed."""
+
     def __init__(self, steps: Sequence[Step]):
         self.n = len(steps)
         self.arr = (StepStruct * max(self.n, 1))()
@@ -361,19 +364,19 @@ class Gpu:
                                               y_dev.handle, c_void_p(y_host_ptr)))
 
     def run_launches(self, steps: Sequence[Step]) -> tuple[float, float]:
-        s = _Steps(steps)
+        s = steps if isinstance(steps, StepList) else StepList(steps)
         cpu, wall = c_double(), c_double()
         _check(self._L.lexb_run_launches(self.handle, s.arr, s.n, byref(cpu), byref(wall)))
         return cpu.value, wall.value
 
     def run_each_timed(self, steps: Sequence[Step]) -> list[float]:
-        s = _Steps(steps)
+        s = steps if isinstance(steps, StepList) else StepList(steps)
         out = (c_double * max(s.n, 1))()
         _check(self._L.lexb_run_each_timed(self.handle, s.arr, s.n, out))
         return [out[i] for i in range(s.n)]
 
     def time_launches(self, steps: Sequence[Step], reps: int = 1) -> float:
-        s = _Steps(steps)
+        s = steps if isinstance(steps, StepList) else StepList(steps)
         out = c_double()
         _check(self._L.lexb_time_launches(self.handle, s.arr, s.n, reps, byref(out)))
         return out.value

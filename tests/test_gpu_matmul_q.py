@@ -276,3 +276,27 @@ def test_reference_gpu_test_recipes(gpu, m, n_in, mul, add, sbase, smod, rows, s
     err, scale, _ = O.err_of_scale(got, want)
     print(f"  {err:.3e} of scale {scale:.3e}")
     assert scale > 1e-3 and err <= 1e-4
+
+
+def test_step_list_with_the_next_steps_weights_prefetched(gpu):
+    """lexb_run_launches tells each launch which weights follow; the kernel pulls their first stages into
+    L2 before it ends.  A hint only: shapes, K splits and pipelines change from step to step here."""
+    m = 2
+    shapes = [(256, 1024), (128, 5120), (384, 2048), (256, 1024)]
+    x_of_k = {k: inputs.make_x(m, k, seed_base=460 + k) for _, k in shapes}
+    xb = {k: gpu.upload(v) for k, v in x_of_k.items()}
+    pipes, qs, ys, ws_host = [], [], [], []
+    for i, (n, k) in enumerate(shapes):
+        w = inputs.make_weights(n, k, seed_base=470 + i)
+        ws_host.append(w)
+        qs.append(L.QBuf(gpu, *w))
+        pipes.append(gpu.plan_matmul_fp4(m, n, k))
+        ys.append(gpu.alloc(4 * m * n))
+    steps = L.StepList([(p, q.bind(xb[k], None, y)) for p, q, y, (_, k) in zip(pipes, qs, ys, shapes)])
+    for _ in range(3):
+        gpu.run_launches(steps)
+    each = gpu.run_each_timed(steps)
+    assert len(each) == len(shapes) and all(t > 0 for t in each)
+    for (n, k), w, y in zip(shapes, ws_host, ys):
+        check(gpu.download(y, np.float32, (m, n)), O.matmul_q_x(x_of_k[k], *w))
+    assert gpu.status_word() == 0
