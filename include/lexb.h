@@ -193,7 +193,13 @@ LEXB_API int lexb_selftest_bounded_wait(lexb_gpu* gpu, uint32_t limit_us);
  * x tiles, [4] for its own W tile, [5] for the partner's W tile, [6] accumulator complete,
  * [7] epilogue done ([1]-[5] only in the leader block of a pair); [8..10] and [12..14]: for the
  * first and the last dequant thread, cycles in the decode loop, of which waiting for packed
- * weights, of which waiting for a free W stage.  max_ctas = 0 turns it off. */
+ * weights, of which waiting for a free W stage.  max_ctas = 0 turns it off.
+ * The block-scaled kernel records, per block: [0] start, [1] first stage ready to multiply, [2] all
+ * MMAs issued, [3] cycles its MMA warp waited for codes, [4] for scale blocks and pieces, [5] spent
+ * issuing; [6..8] the first scale warp's loop, of which waiting for a free stage, for scale bytes;
+ * [9] when its barriers were initialised (low half) and fenced (high half), relative to the start;
+ * [10] block done; [11..12] the first piece warp's loop, of which waiting for a free stage;
+ * [13] first copy issued, [14] first codes landed, [15] set-up done. */
 LEXB_API int lexb_trace_enable(lexb_gpu* gpu, uint32_t max_ctas);
 LEXB_API int lexb_trace_read(lexb_gpu* gpu, uint64_t* out, uint32_t ctas);
 
