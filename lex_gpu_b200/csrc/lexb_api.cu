@@ -696,8 +696,9 @@ int lexb_gemm_fp4_plan(lexb_gpu* g, uint32_t m, uint32_t n, uint32_t k, int resi
         const uint32_t tiles = p->m_tiles * n_pairs;
         // Split K when whole tiles fill the SM pairs badly (few tiles, or a short last wave).  Each
         // split takes whole blocks of 256 columns (at least 4) and writes a partial product that a
-        // second launch sums.  Model: a K step costs about 0.9 us on a pair; the partials cost their
-        // write and read at about 4 TB/s.
+        // second launch sums.  Model: a K step costs about 0.9 us on a pair with 512 tokens and 0.55 us
+        // with 256 (the decode is the same, the MMAs half); the partials cost their write and read, at
+        // about 8 TB/s while they fit in L2 and 4 TB/s when they do not.
         const uint32_t sm_pairs = static_cast<uint32_t>(g->prop.multiProcessorCount) / 2u;
         const uint32_t raw_blocks = k / lexb::PAIR_RAW_K;
         uint32_t splits = s.k_splits ? s.k_splits : 1u;
@@ -706,8 +707,9 @@ int lexb_gemm_fp4_plan(lexb_gpu* g, uint32_t m, uint32_t n, uint32_t k, int resi
             for (uint32_t c = 1; c <= 8u && raw_blocks / c >= 4u; c++) {
                 const uint32_t rbs = (raw_blocks + c - 1u) / c, eff = (raw_blocks + rbs - 1u) / rbs;
                 const double waves = static_cast<double>((tiles * eff + sm_pairs - 1u) / sm_pairs);
-                double us = waves * rbs * 4.0 * 0.9 + 12.0;
-                if (eff > 1u) us += 2.0 * eff * static_cast<double>(m) * n * 4.0 / 4e6 + 4.0;
+                double us = waves * rbs * 4.0 * (p->tok_blocks == 2u ? 0.9 : 0.55) + 12.0;
+                const double pbytes = static_cast<double>(eff) * m * n * 4.0;
+                if (eff > 1u) us += 2.0 * pbytes / (pbytes <= 64e6 ? 8e6 : 4e6) + 4.0;
                 if (us < best * 0.97) {      // a larger split must win clearly
                     best = us;
                     splits = eff;
