@@ -86,6 +86,9 @@ struct lexb_pipeline {
     uint32_t k_splits = 1, kb_per_split = 0, tok_blocks = 2;
     uint32_t ws_pitch = 0;      // block-scaled kernel: bytes per row of one scale load
     bool x_f32 = false;         // ... with f32 activations
+    bool mq_pre = false;        // ... with the tokens' digit rows from the pieces kernel: buffers and their tensor map
+    uint8_t* pre_buf = nullptr; // [8 m][k / 2] digit rows, then [k / 256][2048] scale blocks, then [m] magnitudes
+    CUtensorMap pre_map{};
     float* partial = nullptr;   // split-K workspace [k_splits][m][n], owned by the pipeline
     // matvec
     uint32_t kc;
@@ -347,13 +350,30 @@ int launch_one(lexb_gpu* g, const lexb_pipeline* p, const lexb_buffer* x, const 
         cfg.attrs = attr;
         cfg.numAttrs = g->pdl ? 1 : 0;
         a.trace = (g->d_trace && p->grid <= g->trace_ctas) ? g->d_trace : nullptr;
-        if (p->x_f32) {
-            if (a.trace) CUDA_TRY(cudaLaunchKernelEx(&cfg, lexb::matmul_q_fp4_kernel<true, true>, maps.map_wq, maps.map_ws, nmaps.map_wq, nmaps.map_ws, a));
-            else CUDA_TRY(cudaLaunchKernelEx(&cfg, lexb::matmul_q_fp4_kernel<false, true>, maps.map_wq, maps.map_ws, nmaps.map_wq, nmaps.map_ws, a));
-        } else {
-            if (a.trace) CUDA_TRY(cudaLaunchKernelEx(&cfg, lexb::matmul_q_fp4_kernel<true, false>, maps.map_wq, maps.map_ws, nmaps.map_wq, nmaps.map_ws, a));
-            else CUDA_TRY(cudaLaunchKernelEx(&cfg, lexb::matmul_q_fp4_kernel<false, false>, maps.map_wq, maps.map_ws, nmaps.map_wq, nmaps.map_ws, a));
+        const size_t pieces_bytes = static_cast<size_t>(p->m) * 8u * (p->k / 2u), sfb_bytes = static_cast<size_t>(p->k / lexb::MQ_STAGE_K) * lexb::MQ_SF_BYTES;
+        if (p->mq_pre) {
+            a.pre_sfb = p->pre_buf + pieces_bytes;
+            a.pre_amax = reinterpret_cast<const uint32_t*>(p->pre_buf + pieces_bytes + sfb_bytes);
+            cudaLaunchConfig_t pc{};
+            pc.gridDim = dim3(p->m);
+            pc.blockDim = dim3(1024);
+            pc.stream = g->stream;
+            pc.attrs = attr;
+            pc.numAttrs = cfg.numAttrs;
+            uint32_t* amax_w = reinterpret_cast<uint32_t*>(p->pre_buf + pieces_bytes + sfb_bytes);
+            if (p->x_f32) CUDA_TRY(cudaLaunchKernelEx(&pc, lexb::matmul_q_pieces_kernel<true>, static_cast<const void*>(x->ptr), p->k, p->pre_buf, p->pre_buf + pieces_bytes, amax_w));
+            else CUDA_TRY(cudaLaunchKernelEx(&pc, lexb::matmul_q_pieces_kernel<false>, static_cast<const void*>(x->ptr), p->k, p->pre_buf, p->pre_buf + pieces_bytes, amax_w));
         }
+        const CUtensorMap& bmap = p->mq_pre ? p->pre_map : maps.map_wq;      // a placeholder without the pieces kernel
+#define LEXB_MQ_LAUNCH(TR, XF, PR) CUDA_TRY(cudaLaunchKernelEx(&cfg, lexb::matmul_q_fp4_kernel<TR, XF, PR>, maps.map_wq, maps.map_ws, nmaps.map_wq, nmaps.map_ws, bmap, a))
+        if (p->mq_pre) {
+            if (p->x_f32) { if (a.trace) LEXB_MQ_LAUNCH(true, true, true); else LEXB_MQ_LAUNCH(false, true, true); }
+            else { if (a.trace) LEXB_MQ_LAUNCH(true, false, true); else LEXB_MQ_LAUNCH(false, false, true); }
+        } else {
+            if (p->x_f32) { if (a.trace) LEXB_MQ_LAUNCH(true, true, false); else LEXB_MQ_LAUNCH(false, true, false); }
+            else { if (a.trace) LEXB_MQ_LAUNCH(true, false, false); else LEXB_MQ_LAUNCH(false, false, false); }
+        }
+#undef LEXB_MQ_LAUNCH
     } else {
         lexb::MatvecArgs a{};
         a.x = static_cast<const __half*>(x->ptr);
@@ -436,10 +456,14 @@ int lexb_open(int device, lexb_gpu** out) {
         cudaFuncSetAttribute(lexb::matvec_fp4_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem) != cudaSuccess ||
         cudaFuncSetAttribute(lexb::matvec_fp4_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem) != cudaSuccess ||
         cudaFuncSetAttribute(lexb::matvec_fp4_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem) != cudaSuccess ||
-        cudaFuncSetAttribute(lexb::matmul_q_fp4_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem) != cudaSuccess ||
-        cudaFuncSetAttribute(lexb::matmul_q_fp4_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem) != cudaSuccess ||
-        cudaFuncSetAttribute(lexb::matmul_q_fp4_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem) != cudaSuccess ||
-        cudaFuncSetAttribute(lexb::matmul_q_fp4_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem) != cudaSuccess)
+        cudaFuncSetAttribute(lexb::matmul_q_fp4_kernel<true, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem) != cudaSuccess ||
+        cudaFuncSetAttribute(lexb::matmul_q_fp4_kernel<false, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem) != cudaSuccess ||
+        cudaFuncSetAttribute(lexb::matmul_q_fp4_kernel<true, true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem) != cudaSuccess ||
+        cudaFuncSetAttribute(lexb::matmul_q_fp4_kernel<false, true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem) != cudaSuccess ||
+        cudaFuncSetAttribute(lexb::matmul_q_fp4_kernel<true, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem) != cudaSuccess ||
+        cudaFuncSetAttribute(lexb::matmul_q_fp4_kernel<false, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem) != cudaSuccess ||
+        cudaFuncSetAttribute(lexb::matmul_q_fp4_kernel<true, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem) != cudaSuccess ||
+        cudaFuncSetAttribute(lexb::matmul_q_fp4_kernel<false, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem) != cudaSuccess)
         return bail(fail(LEXB_ERR_CUDA, "cudaFuncSetAttribute(max dynamic shared memory) failed: %s", cudaGetErrorString(cudaGetLastError())));
     *out = g;
     return LEXB_OK;
@@ -649,8 +673,21 @@ int lexb_gemm_fp4_plan(lexb_gpu* g, uint32_t m, uint32_t n, uint32_t k, int resi
             if (e == cudaSuccess) e = cudaMemset(reinterpret_cast<char*>(p->partial) + pbytes, 0, sizeof(uint32_t) * tiles);
             if (e != cudaSuccess) return bail(fail(LEXB_ERR_CUDA, "allocating the split-K workspace: %s", cudaGetErrorString(e)));
         }
+        // From 5 tokens on the digit rows are derived once per launch by a small kernel ahead of this one
+        // (each block deriving them itself is what bounds the kernel there); LEXB_MQ_PRE=0/1 forces either way.
+        p->mq_pre = env_u32("LEXB_MQ_PRE", m > 4u ? 1u : 0u) != 0;
+        if (p->mq_pre) {
+            const size_t pieces_bytes = static_cast<size_t>(m) * 8u * (k / 2u), sfb_bytes = static_cast<size_t>(kb_all) * lexb::MQ_SF_BYTES;
+            const size_t total = pieces_bytes + sfb_bytes + 64u;
+            cudaError_t e = cudaMalloc(&p->pre_buf, total);
+            if (e == cudaSuccess) e = cudaMemset(p->pre_buf, 0, total);          // scale rows nobody writes stay zero
+            if (e != cudaSuccess) return bail(fail(LEXB_ERR_CUDA, "allocating the digit-row buffers: %s", cudaGetErrorString(e)));
+            int erc = encode_2d(p, &p->pre_map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, p->pre_buf, k / 2u, 8u * m, 128u, 8u * m,
+                                CU_TENSOR_MAP_SWIZZLE_128B, "digit rows");
+            if (erc) return bail(erc);
+        }
         p->grid = tiles * splits;
-        p->threads = lexb::MQ_THREADS;
+        p->threads = p->mq_pre ? 32u * (2u + lexb::MQ_SCALE_WARPS) : lexb::MQ_THREADS;
         p->smem = lexb::matmul_q_smem_bytes(m, stages);
         p->tm = m;
         if (p->entry[0] == 0)
@@ -785,9 +822,10 @@ int lexb_matmul_fp4_plan(lexb_gpu* g, uint32_t t, uint32_t n_out, uint32_t n_in,
 
 void lexb_pipeline_free(lexb_pipeline* p) {
     if (!p) return;
-    if (p->partial) {
+    if (p->partial || p->pre_buf) {
         cudaSetDevice(p->gpu->device);
         cudaFree(p->partial);
+        cudaFree(p->pre_buf);
     }
     delete p;
 }

@@ -85,6 +85,11 @@ struct MatmulQArgs {
     // they have requested all of their own, so that DRAM keeps streaming through this launch's tail and the
     // next one's set-up instead of idling.
     uint32_t next_grid, next_k_splits, next_kb_per_split, next_kb_all, next_stages, next_ws_pitch;
+    // PRE variant: the tokens' digit rows come from matmul_q_pieces_kernel (once per launch instead of
+    // once per block): scale blocks of B as the stages want them, [k / 256][2048] bytes, and the tokens'
+    // largest magnitudes as f32 bits; the digit rows themselves arrive through their own tensor map.
+    const uint8_t* pre_sfb;
+    const uint32_t* pre_amax;
 };
 
 __host__ __device__ constexpr uint32_t matmul_q_smem_bytes(uint32_t m, uint32_t stages) {
@@ -104,10 +109,75 @@ __device__ __forceinline__ uint32_t mq_ue4m3_pow2(int q) {
     return 0u;
 }
 
-template <bool TRACE, bool XF32>
-__global__ void __launch_bounds__(MQ_THREADS, 1)
+// One lane's 8 consecutive values of K (f32 bit patterns) -> for each of the 8 pieces the 4 bytes that hold
+// this lane's 8 codes (two per byte, even K low), and the exponent field of the largest magnitude of the
+// group of 16 the lane shares with its neighbour (lanes 2g, 2g+1).  Whole warp.
+__device__ __forceinline__ void mq_digits(const uint32_t (&fb)[8], uint32_t (&w)[8], uint32_t& e8) {
+    uint32_t am = 0;
+#pragma unroll
+    for (uint32_t i = 0; i < 8; i++) am = max(am, fb[i] & 0x7FFFFFFFu);
+    am = max(am, __shfl_xor_sync(0xFFFFFFFFu, am, 1));
+    // |x| = I * 2^(E - 15), E the group's largest exponent: I = |x| * 2^(142 - e8), 16 bits.  Groups
+    // below 2^-111 count as zero (their scale factor would leave f32's range).
+    e8 = am >> 23;
+    const float to_fixed = e8 >= 16u ? __uint_as_float((269u - e8) << 23) : 0.0f;
+    uint32_t blo[4], bhi[4];
+#pragma unroll
+    for (uint32_t i = 0; i < 4; i++) {
+        const uint32_t b0 = fb[2 * i], b1 = fb[2 * i + 1];
+        const uint32_t i0 = min(__float2uint_rn(__uint_as_float(b0 & 0x7FFFFFFFu) * to_fixed), 65535u);
+        const uint32_t i1 = min(__float2uint_rn(__uint_as_float(b1 & 0x7FFFFFFFu) * to_fixed), 65535u);
+        const uint32_t sg = ((0u - (b0 >> 31)) & 0x08080808u) | ((0u - (b1 >> 31)) & 0x80808080u);
+        blo[i] = mq_spread8(i0 & 0xFFu) | (mq_spread8(i1 & 0xFFu) << 4) | sg;
+        bhi[i] = mq_spread8(i0 >> 8) | (mq_spread8(i1 >> 8) << 4) | sg;
+    }
+    // byte b of blo[i] / bhi[i] is the code pair of piece 7-b / 3-b: transpose 4x4 bytes
+    const uint32_t t0 = __byte_perm(blo[0], blo[1], 0x5140), t1 = __byte_perm(blo[2], blo[3], 0x5140);
+    const uint32_t t2 = __byte_perm(blo[0], blo[1], 0x7362), t3 = __byte_perm(blo[2], blo[3], 0x7362);
+    w[7] = __byte_perm(t0, t1, 0x5410);
+    w[6] = __byte_perm(t0, t1, 0x7632);
+    w[5] = __byte_perm(t2, t3, 0x5410);
+    w[4] = __byte_perm(t2, t3, 0x7632);
+    const uint32_t u0 = __byte_perm(bhi[0], bhi[1], 0x5140), u1 = __byte_perm(bhi[2], bhi[3], 0x5140);
+    const uint32_t u2 = __byte_perm(bhi[0], bhi[1], 0x7362), u3 = __byte_perm(bhi[2], bhi[3], 0x7362);
+    w[3] = __byte_perm(u0, u1, 0x5410);
+    w[2] = __byte_perm(u0, u1, 0x7632);
+    w[1] = __byte_perm(u2, u3, 0x5410);
+    w[0] = __byte_perm(u2, u3, 0x7632);
+}
+
+// 8 halves (one uint4) or 8 floats (two) -> f32 bit patterns
+template <bool XF32>
+__device__ __forceinline__ void mq_widen(const uint4& lo, const uint4& hi, uint32_t (&fb)[8]) {
+    if (XF32) {
+        fb[0] = lo.x; fb[1] = lo.y; fb[2] = lo.z; fb[3] = lo.w;
+        fb[4] = hi.x; fb[5] = hi.y; fb[6] = hi.z; fb[7] = hi.w;
+    } else {
+        const uint32_t hw[4] = {lo.x, lo.y, lo.z, lo.w};
+#pragma unroll
+        for (uint32_t i = 0; i < 4; i++) {
+            const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&hw[i]));
+            fb[2 * i] = __float_as_uint(f.x);
+            fb[2 * i + 1] = __float_as_uint(f.y);
+        }
+    }
+}
+
+// offset of the scale byte of (row n of B, group of 16 `grp` of the stage) inside the stage's 2048 bytes:
+// one 512-byte block per MMA (4 groups), in it 16 bytes per (n % 32), 4 per (n / 32), one per group
+__device__ __forceinline__ uint32_t mq_sfb_offset(uint32_t n, uint32_t grp) {
+    return (grp >> 2) * 512u + (n & 31u) * 16u + (n >> 5) * 4u + (grp & 3u);
+}
+
+// PRE = false: 576 threads, piece warps 10-17 derive the tokens' digit rows in every block (no second launch:
+// best for up to 4 tokens).  PRE = true: 320 threads, the digit rows were written by matmul_q_pieces_kernel
+// and the copy engine brings each stage's part of them with the weights.
+template <bool TRACE, bool XF32, bool PRE>
+__global__ void __launch_bounds__(PRE ? 32u * (2u + MQ_SCALE_WARPS) : MQ_THREADS, 1)
 matmul_q_fp4_kernel(const __grid_constant__ CUtensorMap tmap_wq, const __grid_constant__ CUtensorMap tmap_ws,
-                    const __grid_constant__ CUtensorMap next_wq, const __grid_constant__ CUtensorMap next_ws, MatmulQArgs a) {
+                    const __grid_constant__ CUtensorMap next_wq, const __grid_constant__ CUtensorMap next_ws,
+                    const __grid_constant__ CUtensorMap tmap_b, MatmulQArgs a) {
+    constexpr uint32_t NTHREADS = PRE ? 32u * (2u + MQ_SCALE_WARPS) : MQ_THREADS;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw_addr = smem_u32(smem_raw);
     const uint32_t base = (raw_addr + 1023u) & ~1023u;
@@ -148,13 +218,14 @@ matmul_q_fp4_kernel(const __grid_constant__ CUtensorMap tmap_wq, const __grid_co
         if (lane == 0) {
             prefetch_tensormap(&tmap_wq);
             prefetch_tensormap(&tmap_ws);
+            if (PRE) prefetch_tensormap(&tmap_b);
             *abort_flag = 0;
         }
         if (lane < MQ_MAX_TOKENS) tok_amax[lane] = 0;
         const uint32_t nbar = 3u * S + 1u + 2u * MQ_WS_SLOTS;
         for (uint32_t b = lane; b < nbar; b += 32u) {
             uint32_t count = 1;                                                  // raw_full, empty, acc_full, ws_full
-            if (b >= S && b < 2u * S) count = MQ_SCALE_WARPS / 2u + a.m;         // prep_full: four scale warps, one piece warp per token
+            if (b >= S && b < 2u * S) count = MQ_SCALE_WARPS / 2u + (PRE ? 0u : a.m);   // prep_full: four scale warps, one piece warp per token
             if (b >= 3u * S + 1u + MQ_WS_SLOTS) count = MQ_SCALE_WARPS;          // ws_empty: every scale warp
             mbar_init(bars + 8u * b, count);
         }
@@ -175,10 +246,10 @@ matmul_q_fp4_kernel(const __grid_constant__ CUtensorMap tmap_wq, const __grid_co
     // goes on to its loads, the other warps meet here (named barrier 2).
     uint32_t tmem_base = 0;
     if (warp == 0) {
-        asm volatile("bar.arrive 2, %0;" ::"r"(MQ_THREADS) : "memory");
+        asm volatile("bar.arrive 2, %0;" ::"r"(NTHREADS) : "memory");
     } else {
         tc_fence_before_sync();
-        asm volatile("bar.sync 2, %0;" ::"r"(MQ_THREADS) : "memory");
+        asm volatile("bar.sync 2, %0;" ::"r"(NTHREADS) : "memory");
         tc_fence_after_sync();
         tmem_base = *tmem_slot;
     }
@@ -194,6 +265,8 @@ matmul_q_fp4_kernel(const __grid_constant__ CUtensorMap tmap_wq, const __grid_co
             // come free it joins the stream's order itself: the other warps cannot free anything before
             // the launch ahead has finished, and a bounded wait must not run against that launch's time.
             bool in_order = !(a.flags & 1u);
+            const uint32_t b_bytes = PRE ? N * 128u : 0u;                  // the tokens' digit rows of a stage
+            uint32_t b_issued = 0;                                         // PRE: stages whose digit rows have been requested
             for (uint32_t kb = 0; kb < KB; kb++, ps.advance(S)) {
                 const uint32_t s = ps.s;
                 if (!in_order && (kb >= S || kb / MQ_WS_GROUP + 1u >= MQ_WS_SLOTS)) {
@@ -228,9 +301,24 @@ matmul_q_fp4_kernel(const __grid_constant__ CUtensorMap tmap_wq, const __grid_co
                         break;
                     }
                 }
-                mbar_arrive_expect_tx(raw_full(s), MQ_CODE_BYTES);
+                mbar_arrive_expect_tx(raw_full(s), MQ_CODE_BYTES + (PRE ? b_bytes + MQ_SF_BYTES : 0u));
                 tma_load_2d(codes_of(s), &tmap_wq, (int)((kb0 + kb) * (MQ_STAGE_K / 2)), (int)n0, raw_full(s));
                 if (kb + 1u == S || kb + 1u == KB) allow_dependents();       // the ring is filled (once is enough; twice is harmless)
+                if (PRE) {
+                    // The digit rows are written by the launch ahead (the pieces kernel): the first ring of
+                    // weights goes out before that launch is waited for, the digit rows of those stages after.
+                    if (!in_order && (kb + 1u == S || kb + 1u == KB)) {
+                        grid_dependency_wait();
+                        in_order = true;
+                    }
+                    if (in_order) {
+                        for (; b_issued <= kb; b_issued++) {             // stages < S sit in slot = stage
+                            const uint32_t sj = b_issued % S;
+                            tma_load_2d(b_of(sj), &tmap_b, (int)((kb0 + b_issued) * (MQ_STAGE_K / 2)), 0, raw_full(sj));
+                            tma_load_1d(sfb_of(sj), a.pre_sfb + (size_t)(kb0 + b_issued) * MQ_SF_BYTES, MQ_SF_BYTES, raw_full(sj));
+                        }
+                    }
+                }
             }
             if (*abort_flag) {
                 // copies still in flight land in this block's shared memory: give them a bounded time
@@ -315,7 +403,7 @@ matmul_q_fp4_kernel(const __grid_constant__ CUtensorMap tmap_wq, const __grid_co
             tr[4] = (unsigned long long)w_prep;      // ... for the prep warps
             tr[5] = (unsigned long long)t_issue;     // ... issuing copies and MMAs
         }
-    } else if (warp >= 2u + MQ_SCALE_WARPS) {
+    } else if (!PRE && warp >= 2u + MQ_SCALE_WARPS) {
         // ---------------------------------------------------------------- piece warps: x -> E2M1 digit rows
         const uint32_t xw = warp - (2u + MQ_SCALE_WARPS);
         const uint32_t xt = tid - 32u * (2u + MQ_SCALE_WARPS);
@@ -397,54 +485,10 @@ matmul_q_fp4_kernel(const __grid_constant__ CUtensorMap tmap_wq, const __grid_co
             const Chunk xc = xv;
             if (it + PW < items) xv = load_chunk((it + PW) / a.m, (it + PW) % a.m);
             const uint32_t te8 = tok_amax[tok] >> 23;                 // the token's largest f32 exponent field
-            // ---- 8 values of the token: K offsets 8 lane .. 8 lane + 7 of the stage, as f32 bits
-            uint32_t fb[8];
-            if (XF32) {
-                fb[0] = xc.lo.x; fb[1] = xc.lo.y; fb[2] = xc.lo.z; fb[3] = xc.lo.w;
-                fb[4] = xc.hi.x; fb[5] = xc.hi.y; fb[6] = xc.hi.z; fb[7] = xc.hi.w;
-            } else {
-                const uint32_t hw[4] = {xc.lo.x, xc.lo.y, xc.lo.z, xc.lo.w};
-#pragma unroll
-                for (uint32_t i = 0; i < 4; i++) {
-                    const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&hw[i]));
-                    fb[2 * i] = __float_as_uint(f.x);
-                    fb[2 * i + 1] = __float_as_uint(f.y);
-                }
-            }
-            uint32_t am = 0;
-#pragma unroll
-            for (uint32_t i = 0; i < 8; i++) am = max(am, fb[i] & 0x7FFFFFFFu);
-            am = max(am, __shfl_xor_sync(0xFFFFFFFFu, am, 1));        // a group of 16 is two lanes
-            // |x| = I * 2^(E - 15), E the group's largest exponent: I = |x| * 2^(142 - e8), 16 bits.  Groups
-            // below 2^-111 count as zero (their scale factor would leave f32's range).
-            const uint32_t e8 = am >> 23;
-            const float to_fixed = e8 >= 16u ? __uint_as_float((269u - e8) << 23) : 0.0f;
-            uint32_t blo[4], bhi[4];
-#pragma unroll
-            for (uint32_t i = 0; i < 4; i++) {
-                const uint32_t b0 = fb[2 * i], b1 = fb[2 * i + 1];
-                const uint32_t i0 = min(__float2uint_rn(__uint_as_float(b0 & 0x7FFFFFFFu) * to_fixed), 65535u);
-                const uint32_t i1 = min(__float2uint_rn(__uint_as_float(b1 & 0x7FFFFFFFu) * to_fixed), 65535u);
-                const uint32_t sg = ((0u - (b0 >> 31)) & 0x08080808u) | ((0u - (b1 >> 31)) & 0x80808080u);
-                blo[i] = mq_spread8(i0 & 0xFFu) | (mq_spread8(i1 & 0xFFu) << 4) | sg;
-                bhi[i] = mq_spread8(i0 >> 8) | (mq_spread8(i1 >> 8) << 4) | sg;
-            }
-            // byte b of blo[i] / bhi[i] is the code pair of piece 7-b / 3-b: transpose 4x4 bytes
-            uint32_t w[8];
-            {
-                const uint32_t t0 = __byte_perm(blo[0], blo[1], 0x5140), t1 = __byte_perm(blo[2], blo[3], 0x5140);
-                const uint32_t t2 = __byte_perm(blo[0], blo[1], 0x7362), t3 = __byte_perm(blo[2], blo[3], 0x7362);
-                w[7] = __byte_perm(t0, t1, 0x5410);
-                w[6] = __byte_perm(t0, t1, 0x7632);
-                w[5] = __byte_perm(t2, t3, 0x5410);
-                w[4] = __byte_perm(t2, t3, 0x7632);
-                const uint32_t u0 = __byte_perm(bhi[0], bhi[1], 0x5140), u1 = __byte_perm(bhi[2], bhi[3], 0x5140);
-                const uint32_t u2 = __byte_perm(bhi[0], bhi[1], 0x7362), u3 = __byte_perm(bhi[2], bhi[3], 0x7362);
-                w[3] = __byte_perm(u0, u1, 0x5410);
-                w[2] = __byte_perm(u0, u1, 0x7632);
-                w[1] = __byte_perm(u2, u3, 0x5410);
-                w[0] = __byte_perm(u2, u3, 0x7632);
-            }
+            // ---- 8 values of the token: K offsets 8 lane .. 8 lane + 7 of the stage
+            uint32_t fb[8], w[8], e8;
+            mq_widen<XF32>(xc.lo, xc.hi, fb);
+            mq_digits(fb, w, e8);
             long long q0c = 0;
             if (TRACE) q0c = clock64();
             if (!__all_sync(0xFFFFFFFFu, mbar_wait(empty(s), ph ^ 1u, abort_flag))) {
@@ -461,11 +505,11 @@ matmul_q_fp4_kernel(const __grid_constant__ CUtensorMap tmap_wq, const __grid_co
             const int q0 = 8 - (int)(te8 - e8);
             const uint32_t grp = lane >> 1;                  // group of 16 within the stage
             // row n = 8 tok + piece of the block: 16 bytes per (n % 32), 4 bytes per (n / 32), one per group
-            uint8_t* const sb = smem + (sfb_of(s) - base) + (grp >> 2) * 512u + ((tok & 3u) * MQ_PIECES) * 16u + (tok >> 2) * 4u + (grp & 3u);
+            uint8_t* const sb = smem + (sfb_of(s) - base);
 #pragma unroll
             for (uint32_t i = 0; i < 4; i++) {
                 const uint32_t pc = 4u * (lane & 1u) + i;
-                sb[pc * 16u] = (uint8_t)mq_ue4m3_pow2(q0 - 2 * (int)pc);
+                sb[mq_sfb_offset(tok * MQ_PIECES + pc, grp)] = (uint8_t)mq_ue4m3_pow2(q0 - 2 * (int)pc);
             }
             fence_proxy_async_smem();
             __syncwarp();
@@ -589,7 +633,7 @@ matmul_q_fp4_kernel(const __grid_constant__ CUtensorMap tmap_wq, const __grid_co
                     if (KB > 1u) c += __uint_as_float(d1[pc]);
                     v += c;
                 }
-                const uint32_t te = tok_amax[t] >> 23;
+                const uint32_t te = (PRE ? __ldg(a.pre_amax + t) : tok_amax[t]) >> 23;
                 const float tscale = te >= 16u ? __uint_as_float((te - 8u) << 23) : 0.0f;   // 2^G, G = E_token - 8
                 v = v * tscale * g;
                 if (row_nan || te == 255u) v = __uint_as_float(0x7FC00000u);
@@ -627,6 +671,73 @@ matmul_q_fp4_kernel(const __grid_constant__ CUtensorMap tmap_wq, const __grid_co
     if (warp == 1) {
         tc_fence_after_sync();
         tmem_dealloc(tmem_base, MQ_TMEM_COLS);
+    }
+}
+
+// The tokens' digit rows, once per launch, for the PRE variant of the kernel above: block t takes token t.
+//   pieces [8 m][k / 2] bytes: row 8 t + p holds piece p of token t, packed like wq (a tensor map with the
+//                              128-byte swizzle brings 8 m x 128 bytes of it per stage);
+//   sfb    [k / 256][2048] bytes: per stage the four scale blocks of B (rows past 8 m stay zero);
+//   amax   [m]: the token's largest magnitude as f32 bits.
+// It follows the previous launch of the same pipeline in the stream, which may still be reading these
+// buffers: nothing is written before grid_dependency_wait().
+template <bool XF32>
+__global__ void __launch_bounds__(1024, 1)
+matmul_q_pieces_kernel(const void* __restrict__ x, uint32_t k, uint8_t* __restrict__ pieces, uint8_t* __restrict__ sfb,
+                       uint32_t* __restrict__ amax) {
+    __shared__ uint32_t s_amax;
+    const uint32_t tok = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
+    if (tid == 0) s_amax = 0;
+    allow_dependents();
+    grid_dependency_wait();
+    __syncthreads();
+    const uint4* xr = XF32 ? reinterpret_cast<const uint4*>(static_cast<const float*>(x) + (size_t)tok * k)
+                           : reinterpret_cast<const uint4*>(static_cast<const __half*>(x) + (size_t)tok * k);
+    const uint32_t row_chunks = XF32 ? k / 4u : k / 8u;
+    uint32_t mx = 0;
+#pragma unroll 4
+    for (uint32_t i = tid; i < row_chunks; i += 1024u) {
+        const uint4 v = __ldg(xr + i);
+        if (XF32) {
+            mx = max(max(mx, v.x & 0x7FFFFFFFu), v.y & 0x7FFFFFFFu);
+            mx = max(max(mx, v.z & 0x7FFFFFFFu), v.w & 0x7FFFFFFFu);
+        } else {
+            mx = __vmaxu2(mx, v.x & 0x7FFF7FFFu);
+            mx = __vmaxu2(mx, v.y & 0x7FFF7FFFu);
+            mx = __vmaxu2(mx, v.z & 0x7FFF7FFFu);
+            mx = __vmaxu2(mx, v.w & 0x7FFF7FFFu);
+        }
+    }
+    if (!XF32) {
+        mx = max(mx & 0xFFFFu, mx >> 16);
+        mx = __float_as_uint(__half2float(__ushort_as_half((unsigned short)mx)));
+    }
+    mx = __reduce_max_sync(0xFFFFFFFFu, mx);
+    if (lane == 0) atomicMax(&s_amax, mx);
+    __syncthreads();
+    const uint32_t tmax = s_amax, te8 = tmax >> 23;
+    if (tid == 0) amax[tok] = tmax;
+    for (uint32_t kb = warp; kb < k / MQ_STAGE_K; kb += 32u) {
+        uint4 lo, hi = make_uint4(0, 0, 0, 0);
+        if (XF32) {
+            lo = __ldg(xr + (size_t)kb * (MQ_STAGE_K / 4u) + 2u * lane);
+            hi = __ldg(xr + (size_t)kb * (MQ_STAGE_K / 4u) + 2u * lane + 1u);
+        } else {
+            lo = __ldg(xr + (size_t)kb * (MQ_STAGE_K / 8u) + lane);
+        }
+        uint32_t fb[8], w[8], e8;
+        mq_widen<XF32>(lo, hi, fb);
+        mq_digits(fb, w, e8);
+#pragma unroll
+        for (uint32_t pc = 0; pc < MQ_PIECES; pc++)
+            *reinterpret_cast<uint32_t*>(pieces + (size_t)(tok * MQ_PIECES + pc) * (k / 2u) + kb * 128u + 4u * lane) = w[pc];
+        const int q0 = 8 - (int)(te8 - e8);
+        const uint32_t grp = lane >> 1;
+#pragma unroll
+        for (uint32_t i = 0; i < 4; i++) {
+            const uint32_t pc = 4u * (lane & 1u) + i;
+            sfb[(size_t)kb * MQ_SF_BYTES + mq_sfb_offset(tok * MQ_PIECES + pc, grp)] = (uint8_t)mq_ue4m3_pow2(q0 - 2 * (int)pc);
+        }
     }
 }
 

@@ -300,3 +300,19 @@ def test_step_list_with_the_next_steps_weights_prefetched(gpu):
     for (n, k), w, y in zip(shapes, ws_host, ys):
         check(gpu.download(y, np.float32, (m, n)), O.matmul_q_x(x_of_k[k], *w))
     assert gpu.status_word() == 0
+
+
+@pytest.mark.parametrize("m,n,k", [(1, 128, 256), (2, 256, 5120), (4, 384, 2048), (3, 128, 7168)])
+@pytest.mark.parametrize("f32", [False, True])
+def test_digit_rows_from_the_pieces_kernel_for_few_tokens_too(gpu, monkeypatch, m, n, k, f32):
+    """From 5 tokens on a small kernel ahead of the main one derives the digit rows once per launch; forced
+    here for fewer tokens, where each block derives them itself by default.  Same digits either way."""
+    x, wq, ws, wg = inputs.make_case(m, n, k, seed_base=480 + m)
+    if f32:
+        x = x.astype(np.float32) * np.float32(1.0009765)          # not representable in f16
+    want = O.matmul_q_x(x, wq, ws, wg)
+    in_block = L.matmul_fp4(gpu, x, wq, ws, wg)
+    monkeypatch.setenv("LEXB_MQ_PRE", "1")
+    ahead = L.matmul_fp4(gpu, x, wq, ws, wg)
+    check(ahead, want)
+    assert np.array_equal(ahead, in_block)
