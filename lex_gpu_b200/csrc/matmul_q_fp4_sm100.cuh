@@ -29,9 +29,14 @@
 // the hardware scale is unsigned, so the sign is moved into the 16 codes of the group in shared
 // memory.  The two NaN bytes (0x7f, 0xff) make the whole output row NaN, as in the reference.
 //
-// Block = 128 weight rows (one row tile) x one K range; 6 warps: warp 0 issues the TMA loads of codes
-// and scale bytes, warp 1 the scale copies into tensor memory and the MMAs, warps 2-5 write the
-// activations' pieces and re-lay the weight scales for each stage, then run the epilogue.
+// Block = 128 weight rows (one row tile) x one K range.  Warp 0 issues the TMA loads (codes per 256 of K
+// into a ring of stages, raw scale bytes per 1024 of K into a ring of their own, one group ahead); warp 1
+// copies each stage's scale blocks into tensor memory and issues its 4 MMAs of K = 64, alternating two
+// accumulators; warps 2-5 and 6-9 re-lay the weight scales of the even and the odd stages into the
+// 32 x 16-byte blocks the instruction reads (warps 2-5 then run the epilogue); warps 10-17 derive the
+// tokens' digit rows - unless matmul_q_pieces_kernel has done that once for the launch (PRE: from 5 tokens
+// on), in which case warp 0 loads them with the weights.  With K split over blocks, the last block of a
+// row tile to finish sums the partial products.  Every wait is bounded.
 #pragma once
 #include <cuda_fp16.h>
 #include <stdint.h>
@@ -65,7 +70,6 @@ constexpr uint32_t MQ_MAX_STAGES = 8;
 constexpr uint32_t MQ_TMEM_D1 = 64;                       // second accumulator (N = 8 columns per token, at most 64)
 constexpr uint32_t MQ_TMEM_SFA = 128;                     // ring of 16 columns per stage
 constexpr uint32_t MQ_TMEM_SFB = MQ_TMEM_SFA + 16u * MQ_MAX_STAGES;
-
 
 struct MatmulQArgs {
     const void* x;           // [m, k], f16 or f32
