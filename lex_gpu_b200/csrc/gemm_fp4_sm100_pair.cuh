@@ -444,6 +444,10 @@ struct GatherDst {
 
 __global__ void splitk_reduce_kernel(const float* __restrict__ partial, uint32_t splits, size_t elems,
                                      const float* __restrict__ r, float* __restrict__ y, const GatherDst g) {
+    // launched with programmatic stream serialization behind the GEMM that writes the partials: its
+    // blocks are in place when that launch ends
+    allow_dependents();
+    grid_dependency_wait();
     const size_t n4 = elems / 4;
     for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n4; i += (size_t)gridDim.x * blockDim.x) {
         float4 acc = reinterpret_cast<const float4*>(partial)[i];

@@ -312,7 +312,14 @@ int launch_one(lexb_gpu* g, const lexb_pipeline* p, const lexb_buffer* x, const 
                 CUDA_TRY(cudaGetLastError());
                 const size_t elems = static_cast<size_t>(p->m) * p->n;       // n % 128 == 0: a multiple of 4
                 const uint32_t blocks = static_cast<uint32_t>(std::min<size_t>((elems / 4 + 255) / 256, 148u * 8u));
-                lexb::splitk_reduce_kernel<<<blocks, 256, 0, g->stream>>>(p->partial, p->k_splits, elems, a.r, a.y, gd);
+                cudaLaunchConfig_t rc_cfg{};
+                rc_cfg.gridDim = dim3(blocks);
+                rc_cfg.blockDim = dim3(256);
+                rc_cfg.stream = g->stream;
+                rc_cfg.attrs = attr;
+                rc_cfg.numAttrs = cfg.numAttrs;
+                CUDA_TRY(cudaLaunchKernelEx(&rc_cfg, lexb::splitk_reduce_kernel, static_cast<const float*>(p->partial), p->k_splits, elems,
+                                            a.r, a.y, gd));
             }
         } else {
             lexb::gemm_fp4_tcgen05_kernel<<<p->grid, p->threads, p->smem, g->stream>>>(maps.map, a);
