@@ -391,12 +391,22 @@ int launch_one(lexb_gpu* g, const lexb_pipeline* p, const lexb_buffer* x, const 
         a.y = static_cast<float*>(y->ptr);
         a.m = p->m; a.n = p->n; a.k = p->k; a.kc = p->kc;
         const bool ragged = (p->k % lexb::MV_SLICE) != 0u;
+        cudaLaunchConfig_t cfg{};
+        cfg.gridDim = dim3(p->grid);
+        cfg.blockDim = dim3(p->threads);
+        cfg.dynamicSmemBytes = p->smem;
+        cfg.stream = g->stream;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = g->pdl ? 1 : 0;
         if (p->m > 8) {
-            if (ragged) lexb::matvec_fp4_kernel<true, true><<<p->grid, p->threads, p->smem, g->stream>>>(a);
-            else lexb::matvec_fp4_kernel<true, false><<<p->grid, p->threads, p->smem, g->stream>>>(a);
+            if (ragged) CUDA_TRY(cudaLaunchKernelEx(&cfg, lexb::matvec_fp4_kernel<true, true>, a));
+            else CUDA_TRY(cudaLaunchKernelEx(&cfg, lexb::matvec_fp4_kernel<true, false>, a));
         } else {
-            if (ragged) lexb::matvec_fp4_kernel<false, true><<<p->grid, p->threads, p->smem, g->stream>>>(a);
-            else lexb::matvec_fp4_kernel<false, false><<<p->grid, p->threads, p->smem, g->stream>>>(a);
+            if (ragged) CUDA_TRY(cudaLaunchKernelEx(&cfg, lexb::matvec_fp4_kernel<false, true>, a));
+            else CUDA_TRY(cudaLaunchKernelEx(&cfg, lexb::matvec_fp4_kernel<false, false>, a));
         }
     }
     CUDA_TRY(cudaGetLastError());

@@ -24,6 +24,7 @@
 // stored 72 bytes apart and the token pitch is 32 (mod 128) bytes, which makes the quad's
 // four 8-byte reads per token and the eight tokens of a warp hit distinct banks.
 #pragma once
+#include "sm100_ptx.cuh"
 #include "fp4_decode.cuh"
 
 namespace lexb {
@@ -76,6 +77,9 @@ __global__ void __launch_bounds__(MV_THREADS) matvec_fp4_kernel(const MatvecArgs
     uint8_t* const xs = zeros + 128u;
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
     const uint32_t g = lane >> 2, t = lane & 3u;
+    // launched with programmatic stream serialization: the blocks are in place when the launch ahead ends
+    allow_dependents();
+    grid_dependency_wait();
     const uint32_t k = a.k, kc = a.kc;
     const uint32_t pitch = matvec_x_pitch(kc);
     const uint32_t slices = (k + MV_SLICE - 1u) / MV_SLICE;             // per row block
