@@ -22,7 +22,7 @@ def _free_port() -> int:
         return s.getsockname()[1]
 
 
-def _worker(rank: int, world: int, port: int, m: int, n: int, k: int, out_dir: str):
+def _worker(rank: int, world: int, port: int, m: int, n: int, k: int, out_dir: str, op: str = "gemm_fp4"):
     sys.path.insert(0, str(ROOT))
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     dist.init_process_group("gloo", rank=rank, world_size=world)
@@ -32,7 +32,8 @@ def _worker(rank: int, world: int, port: int, m: int, n: int, k: int, out_dir: s
     x, wq, ws, wg = inputs.make_case(m, n, k, seed_base=7)
     sh = RowShard.of(n, world, rank)
     q, s, g = sh.slice_weights(wq, ws, wg)
-    y_local = torch.from_numpy(O.gemm_fp4(x, np.ascontiguousarray(q), np.ascontiguousarray(s), np.ascontiguousarray(g), threads=2))
+    fn = O.gemm_fp4 if op == "gemm_fp4" else O.matmul_q_x
+    y_local = torch.from_numpy(fn(x, np.ascontiguousarray(q), np.ascontiguousarray(s), np.ascontiguousarray(g), threads=2))
     gathered = all_gather_y(y_local, sh)
     y = assemble(gathered, sh).numpy()
     if rank == 0:
@@ -53,3 +54,15 @@ def test_two_rank_sharded_product_equals_the_unsharded_one(tmp_path, n, world):
     want = O.gemm_fp4(x, wq, ws, wg)
     got = np.load(tmp_path / "y.npy")
     assert np.array_equal(got, want)
+
+
+def test_two_rank_sharded_decode_matmul(tmp_path):
+    """The same row sharding for matmul_q_x (decode: 3 tokens), unequal shards."""
+    m, n, k, world = 3, 384, 512, 2
+    port = _free_port()
+    mp.spawn(_worker, args=(world, port, m, n, k, str(tmp_path), "matmul_q_x"), nprocs=world, join=True)
+    sys.path.insert(0, str(ROOT))
+    from lex_gpu_b200 import inputs
+    from oracle import oracle as O
+    x, wq, ws, wg = inputs.make_case(m, n, k, seed_base=7)
+    assert np.array_equal(np.load(tmp_path / "y.npy"), O.matmul_q_x(x, wq, ws, wg))
