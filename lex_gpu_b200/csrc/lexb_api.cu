@@ -362,7 +362,7 @@ int launch_one(lexb_gpu* g, const lexb_pipeline* p, const lexb_buffer* x, const 
             a.pre_sfb = p->pre_buf + pieces_bytes;
             a.pre_amax = reinterpret_cast<const uint32_t*>(p->pre_buf + pieces_bytes + sfb_bytes);
             cudaLaunchConfig_t pc{};
-            pc.gridDim = dim3(p->m);
+            pc.gridDim = dim3(p->m, (p->k / lexb::MQ_STAGE_K + 31u) / 32u);      // a warp per stage
             pc.blockDim = dim3(1024);
             pc.stream = g->stream;
             pc.attrs = attr;
@@ -667,7 +667,7 @@ int lexb_gemm_fp4_plan(lexb_gpu* g, uint32_t m, uint32_t n, uint32_t k, int resi
         if (m > lexb::MQ_MAX_TOKENS) return bail(fail(LEXB_ERR_SHAPE, "the block-scaled kernel takes at most %u tokens, not %u", lexb::MQ_MAX_TOKENS, m));
         if (n % lexb::MQ_ROWS) return bail(fail(LEXB_ERR_SHAPE, "matmul_q (nvfp4): %u rows per block do not divide n = %u", lexb::MQ_ROWS, n));
         if (k % lexb::MQ_STAGE_K) return bail(fail(LEXB_ERR_SHAPE, "matmul_q (nvfp4): blocks of %u columns do not divide k = %u", lexb::MQ_STAGE_K, k));
-        uint32_t stages = s.stages ? s.stages : (m <= 4u ? lexb::MQ_MAX_STAGES : 7u);     // what fits shared memory
+        uint32_t stages = s.stages ? s.stages : (m <= 4u ? lexb::MQ_MAX_STAGES : (m <= 8u ? 7u : 5u));     // what fits shared memory
         if (stages < 2 || stages > lexb::MQ_MAX_STAGES || lexb::matmul_q_smem_bytes(m, stages) > g->smem_optin)
             return bail(fail(LEXB_ERR_ARG, "stages = %u outside [2, %u] or over the shared-memory limit", stages, lexb::MQ_MAX_STAGES));
         const uint32_t tiles = n / lexb::MQ_ROWS, kb_all = k / lexb::MQ_STAGE_K;

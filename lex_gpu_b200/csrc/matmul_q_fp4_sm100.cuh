@@ -48,10 +48,10 @@ namespace lexb {
 constexpr uint32_t MQ_ROWS = 128;                         // weight rows per block
 constexpr uint32_t MQ_STAGE_K = 256;                      // values of K per stage: one 128-byte row of codes
 constexpr uint32_t MQ_PIECES = 8;                         // E2M1 digit rows per token
-constexpr uint32_t MQ_MAX_TOKENS = 8;
+constexpr uint32_t MQ_MAX_TOKENS = 16;
 constexpr uint32_t MQ_CODE_BYTES = MQ_ROWS * 128u;        // packed codes of a stage
-// the tokens' pieces of a stage: 128 bytes x 8 rows per token, room for 4 or for 8 tokens
-__host__ __device__ constexpr uint32_t matmul_q_b_bytes(uint32_t m) { return m <= 4u ? 4096u : 8192u; }
+// the tokens' pieces of a stage: 128 bytes x 8 rows per token, room for 4, 8 or 16 tokens
+__host__ __device__ constexpr uint32_t matmul_q_b_bytes(uint32_t m) { return m <= 4u ? 4096u : (m <= 8u ? 8192u : 16384u); }
 constexpr uint32_t MQ_SF_BYTES = 4u * 512u;               // one 512-byte scale block per MMA of the stage
 __host__ __device__ constexpr uint32_t matmul_q_stage_bytes(uint32_t m) {
     return MQ_CODE_BYTES + matmul_q_b_bytes(m) + 2u * MQ_SF_BYTES;      // a multiple of 1024: stages start on a swizzle-pattern boundary
@@ -67,8 +67,8 @@ constexpr uint32_t MQ_PIECE_WARPS = 8;                    // warps 10-17: the to
 constexpr uint32_t MQ_THREADS = 32u * (2u + MQ_SCALE_WARPS + MQ_PIECE_WARPS);
 constexpr uint32_t MQ_TMEM_COLS = 512;
 constexpr uint32_t MQ_MAX_STAGES = 8;
-constexpr uint32_t MQ_TMEM_D1 = 64;                       // second accumulator (N = 8 columns per token, at most 64)
-constexpr uint32_t MQ_TMEM_SFA = 128;                     // ring of 16 columns per stage
+constexpr uint32_t MQ_TMEM_D1 = 128;                      // second accumulator (N = 8 columns per token, at most 128)
+constexpr uint32_t MQ_TMEM_SFA = 256;                     // ring of 16 columns per stage
 constexpr uint32_t MQ_TMEM_SFB = MQ_TMEM_SFA + 16u * MQ_MAX_STAGES;
 
 struct MatmulQArgs {
@@ -97,7 +97,7 @@ struct MatmulQArgs {
 };
 
 __host__ __device__ constexpr uint32_t matmul_q_smem_bytes(uint32_t m, uint32_t stages) {
-    return stages * matmul_q_stage_bytes(m) + MQ_WS_SLOTS * MQ_WS_SLOT_BYTES + (3u * stages + 1u + 2u * MQ_WS_SLOTS) * 8u + 64u + MQ_ROWS + 1024u;
+    return stages * matmul_q_stage_bytes(m) + MQ_WS_SLOTS * MQ_WS_SLOT_BYTES + (3u * stages + 1u + 2u * MQ_WS_SLOTS) * 8u + 128u + MQ_ROWS + 1024u;
 }
 
 // bits [2i+1 : 2i] of an 8-bit value -> byte i
@@ -206,7 +206,7 @@ matmul_q_fp4_kernel(const __grid_constant__ CUtensorMap tmap_wq, const __grid_co
     volatile uint32_t* const abort_flag = misc + 1;
     uint32_t* const tok_amax = misc + 2;                                   // [MQ_MAX_TOKENS]
     volatile uint32_t* const fix_flag = misc + 2 + MQ_MAX_TOKENS;
-    volatile uint8_t* const nan_rows = reinterpret_cast<volatile uint8_t*>(misc + 16);   // [MQ_ROWS]: a NaN scale byte seen
+    volatile uint8_t* const nan_rows = reinterpret_cast<volatile uint8_t*>(misc + 32);   // [MQ_ROWS]: a NaN scale byte seen
 
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
     const uint32_t split = blockIdx.x % a.k_splits, tile = blockIdx.x / a.k_splits;
@@ -678,7 +678,8 @@ matmul_q_fp4_kernel(const __grid_constant__ CUtensorMap tmap_wq, const __grid_co
     }
 }
 
-// The tokens' digit rows, once per launch, for the PRE variant of the kernel above: block t takes token t.
+// The tokens' digit rows, once per launch, for the PRE variant of the kernel above: blocks (t, *) take token t,
+// each finds the token's largest magnitude itself and takes every gridDim.y-th set of 32 stages.
 //   pieces [8 m][k / 2] bytes: row 8 t + p holds piece p of token t, packed like wq (a tensor map with the
 //                              128-byte swizzle brings 8 m x 128 bytes of it per stage);
 //   sfb    [k / 256][2048] bytes: per stage the four scale blocks of B (rows past 8 m stay zero);
@@ -720,8 +721,8 @@ matmul_q_pieces_kernel(const void* __restrict__ x, uint32_t k, uint8_t* __restri
     if (lane == 0) atomicMax(&s_amax, mx);
     __syncthreads();
     const uint32_t tmax = s_amax, te8 = tmax >> 23;
-    if (tid == 0) amax[tok] = tmax;
-    for (uint32_t kb = warp; kb < k / MQ_STAGE_K; kb += 32u) {
+    if (tid == 0 && blockIdx.y == 0) amax[tok] = tmax;
+    for (uint32_t kb = blockIdx.y * 32u + warp; kb < k / MQ_STAGE_K; kb += 32u * gridDim.y) {
         uint4 lo, hi = make_uint4(0, 0, 0, 0);
         if (XF32) {
             lo = __ldg(xr + (size_t)kb * (MQ_STAGE_K / 4u) + 2u * lane);
