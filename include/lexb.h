@@ -58,7 +58,7 @@ typedef struct lexb_device_info {
  * (crates/lex-msl/src/gemm.rs:90-135).  Zero fields mean "choose". */
 typedef struct lexb_sched {
     uint32_t kernel;  /* 0 auto, 1 matvec (m <= 16), 2 tcgen05 GEMM, 3 two-CTA tcgen05 GEMM,
-                       * 4 block-scaled FP4 tensor-core kernel (m <= 16; matmul_q_x arithmetic, never chosen by auto) */
+                       * 4 block-scaled FP4 tensor-core kernel (m <= 32; matmul_q_x arithmetic, never chosen by auto) */
     uint32_t tm;      /* tokens per CTA tile of the GEMM: multiple of 16, <= 256 */
     uint32_t stages;  /* pipeline depth of the GEMM */
     uint32_t kc;      /* K columns of x staged per chunk in the matvec: multiple of 1024 */
@@ -235,7 +235,7 @@ LEXB_API int lexb_gemm_fp4_splitk_static(lexb_gpu* gpu, uint32_t m, uint32_t n, 
  * crates/lex-rt/src/qwen_run.rs:2605-2606), same bindings [x, wq, ws, wg, (r), y] as gemm_fp4 but with
  * the weights used as dequantised f32 values (e2m1 * e4m3 * wg, crates/lex-front/src/interp.rs:643-657),
  * not rounded to f16.  The pipeline is launched like any other (lexb_gemm_fp4_launch, lexb_step).
- * Here: t <= 16 tokens, activations f16 (x_half != 0) or f32 (x_half == 0), n_out % 128 == 0,
+ * Here: t <= 32 tokens, activations f16 (x_half != 0) or f32 (x_half == 0), n_out % 128 == 0,
  * n_in % 256 == 0.  The decode runs on the tensor cores' block-scaled FP4 path, which takes wq and ws
  * as stored; each token is split into eight rows of 2-bit E2M1 digits: 16 significant bits below the
  * largest value of every group of 16, exact for f16 values within 2^5 of that maximum, and for f32

@@ -357,7 +357,7 @@ int launch_one(lexb_gpu* g, const lexb_pipeline* p, const lexb_buffer* x, const 
         cfg.attrs = attr;
         cfg.numAttrs = g->pdl ? 1 : 0;
         a.trace = (g->d_trace && p->grid <= g->trace_ctas) ? g->d_trace : nullptr;
-        const size_t pieces_bytes = static_cast<size_t>(p->m) * 8u * (p->k / 2u), sfb_bytes = static_cast<size_t>(p->k / lexb::MQ_STAGE_K) * lexb::MQ_SF_BYTES;
+        const size_t pieces_bytes = static_cast<size_t>(p->m) * 8u * (p->k / 2u), sfb_bytes = static_cast<size_t>(p->k / lexb::MQ_STAGE_K) * lexb::matmul_q_sfb_bytes(p->m);
         if (p->mq_pre) {
             a.pre_sfb = p->pre_buf + pieces_bytes;
             a.pre_amax = reinterpret_cast<const uint32_t*>(p->pre_buf + pieces_bytes + sfb_bytes);
@@ -667,9 +667,10 @@ int lexb_gemm_fp4_plan(lexb_gpu* g, uint32_t m, uint32_t n, uint32_t k, int resi
         if (m > lexb::MQ_MAX_TOKENS) return bail(fail(LEXB_ERR_SHAPE, "the block-scaled kernel takes at most %u tokens, not %u", lexb::MQ_MAX_TOKENS, m));
         if (n % lexb::MQ_ROWS) return bail(fail(LEXB_ERR_SHAPE, "matmul_q (nvfp4): %u rows per block do not divide n = %u", lexb::MQ_ROWS, n));
         if (k % lexb::MQ_STAGE_K) return bail(fail(LEXB_ERR_SHAPE, "matmul_q (nvfp4): blocks of %u columns do not divide k = %u", lexb::MQ_STAGE_K, k));
-        uint32_t stages = s.stages ? s.stages : (m <= 4u ? lexb::MQ_MAX_STAGES : (m <= 8u ? 7u : 5u));     // what fits shared memory
-        if (stages < 2 || stages > lexb::MQ_MAX_STAGES || lexb::matmul_q_smem_bytes(m, stages) > g->smem_optin)
-            return bail(fail(LEXB_ERR_ARG, "stages = %u outside [2, %u] or over the shared-memory limit", stages, lexb::MQ_MAX_STAGES));
+        uint32_t stages = s.stages ? s.stages : (m <= 4u ? lexb::MQ_MAX_STAGES : (m <= 8u ? 7u : (m <= 16u ? 5u : 3u)));     // what fits shared memory
+        const uint32_t max_stages = m <= 16u ? lexb::MQ_MAX_STAGES : lexb::MQ_WIDE_MAX_STAGES;    // ... and, past 16 tokens, tensor memory
+        if (stages < 2 || stages > max_stages || lexb::matmul_q_smem_bytes(m, stages) > g->smem_optin)
+            return bail(fail(LEXB_ERR_ARG, "stages = %u outside [2, %u] or over the shared-memory limit", stages, max_stages));
         const uint32_t tiles = n / lexb::MQ_ROWS, kb_all = k / lexb::MQ_STAGE_K;
         const uint32_t sms = static_cast<uint32_t>(g->prop.multiProcessorCount);
         // one K range per block; split K when the row tiles alone leave most SMs idle
@@ -692,10 +693,10 @@ int lexb_gemm_fp4_plan(lexb_gpu* g, uint32_t m, uint32_t n, uint32_t k, int resi
         }
         // From 5 tokens on the digit rows are derived once per launch by a small kernel ahead of this one
         // (each block deriving them itself is what bounds the kernel there); LEXB_MQ_PRE=0/1 forces either way.
-        p->mq_pre = env_u32("LEXB_MQ_PRE", m > 4u ? 1u : 0u) != 0;
+        p->mq_pre = m > 16u || env_u32("LEXB_MQ_PRE", m > 4u ? 1u : 0u) != 0;       // past 16 tokens there is no in-block path
         if (p->mq_pre) {
-            const size_t pieces_bytes = static_cast<size_t>(m) * 8u * (k / 2u), sfb_bytes = static_cast<size_t>(kb_all) * lexb::MQ_SF_BYTES;
-            const size_t total = pieces_bytes + sfb_bytes + 64u;
+            const size_t pieces_bytes = static_cast<size_t>(m) * 8u * (k / 2u), sfb_bytes = static_cast<size_t>(kb_all) * lexb::matmul_q_sfb_bytes(m);
+            const size_t total = pieces_bytes + sfb_bytes + 4u * lexb::MQ_MAX_TOKENS;
             cudaError_t e = cudaMalloc(&p->pre_buf, total);
             if (e == cudaSuccess) e = cudaMemset(p->pre_buf, 0, total);          // scale rows nobody writes stay zero
             if (e != cudaSuccess) return bail(fail(LEXB_ERR_CUDA, "allocating the digit-row buffers: %s", cudaGetErrorString(e)));

@@ -48,13 +48,18 @@ namespace lexb {
 constexpr uint32_t MQ_ROWS = 128;                         // weight rows per block
 constexpr uint32_t MQ_STAGE_K = 256;                      // values of K per stage: one 128-byte row of codes
 constexpr uint32_t MQ_PIECES = 8;                         // E2M1 digit rows per token
-constexpr uint32_t MQ_MAX_TOKENS = 16;
+constexpr uint32_t MQ_MAX_TOKENS = 32;
 constexpr uint32_t MQ_CODE_BYTES = MQ_ROWS * 128u;        // packed codes of a stage
-// the tokens' pieces of a stage: 128 bytes x 8 rows per token, room for 4, 8 or 16 tokens
-__host__ __device__ constexpr uint32_t matmul_q_b_bytes(uint32_t m) { return m <= 4u ? 4096u : (m <= 8u ? 8192u : 16384u); }
-constexpr uint32_t MQ_SF_BYTES = 4u * 512u;               // one 512-byte scale block per MMA of the stage
+// the tokens' pieces of a stage: 128 bytes x 8 rows per token, room for 4, 8, 16 or 32 tokens
+__host__ __device__ constexpr uint32_t matmul_q_b_bytes(uint32_t m) {
+    return m <= 4u ? 4096u : (m <= 8u ? 8192u : (m <= 16u ? 16384u : 32768u));
+}
+constexpr uint32_t MQ_SF_BYTES = 4u * 512u;               // scale blocks of A for a stage: one 512-byte block per MMA
+// ... of B: one block per MMA covers 128 rows of B (16 tokens), so more than 16 tokens take two
+__host__ __device__ constexpr uint32_t matmul_q_sfb_bytes(uint32_t m) { return m <= 16u ? 2048u : 4096u; }
 __host__ __device__ constexpr uint32_t matmul_q_stage_bytes(uint32_t m) {
-    return MQ_CODE_BYTES + matmul_q_b_bytes(m) + 2u * MQ_SF_BYTES;      // a multiple of 1024: stages start on a swizzle-pattern boundary
+    // a multiple of 1024: stages start on a swizzle-pattern boundary
+    return MQ_CODE_BYTES + matmul_q_b_bytes(m) + MQ_SF_BYTES + matmul_q_sfb_bytes(m);
 }
 // The scale bytes as stored come in their own, coarser ring: one load covers MQ_WS_GROUP stages, so
 // that a row's piece of it is 64 bytes (16 bytes per stage would fetch half-used 32-byte sectors).
@@ -67,9 +72,14 @@ constexpr uint32_t MQ_PIECE_WARPS = 8;                    // warps 10-17: the to
 constexpr uint32_t MQ_THREADS = 32u * (2u + MQ_SCALE_WARPS + MQ_PIECE_WARPS);
 constexpr uint32_t MQ_TMEM_COLS = 512;
 constexpr uint32_t MQ_MAX_STAGES = 8;
-constexpr uint32_t MQ_TMEM_D1 = 128;                      // second accumulator (N = 8 columns per token, at most 128)
-constexpr uint32_t MQ_TMEM_SFA = 256;                     // ring of 16 columns per stage
+// Tensor memory.  Up to 16 tokens (N <= 128): two accumulators at columns 0 and 128 that take the even and the
+// odd stages, the scale rings of A and B at 256 and 384, 16 columns per stage.  17-32 tokens (N <= 256): one
+// accumulator, A's ring at 256 (at most 4 stages), B's at 320 with 32 columns per stage.
+constexpr uint32_t MQ_TMEM_D1 = 128;
+constexpr uint32_t MQ_TMEM_SFA = 256;
 constexpr uint32_t MQ_TMEM_SFB = MQ_TMEM_SFA + 16u * MQ_MAX_STAGES;
+constexpr uint32_t MQ_TMEM_SFB_WIDE = 320;
+constexpr uint32_t MQ_WIDE_MAX_STAGES = 4;
 
 struct MatmulQArgs {
     const void* x;           // [m, k], f16 or f32
@@ -97,7 +107,7 @@ struct MatmulQArgs {
 };
 
 __host__ __device__ constexpr uint32_t matmul_q_smem_bytes(uint32_t m, uint32_t stages) {
-    return stages * matmul_q_stage_bytes(m) + MQ_WS_SLOTS * MQ_WS_SLOT_BYTES + (3u * stages + 1u + 2u * MQ_WS_SLOTS) * 8u + 128u + MQ_ROWS + 1024u;
+    return stages * matmul_q_stage_bytes(m) + MQ_WS_SLOTS * MQ_WS_SLOT_BYTES + (3u * stages + 1u + 2u * MQ_WS_SLOTS) * 8u + 192u + MQ_ROWS + 1024u;
 }
 
 // bits [2i+1 : 2i] of an 8-bit value -> byte i
@@ -169,8 +179,9 @@ __device__ __forceinline__ void mq_widen(const uint4& lo, const uint4& hi, uint3
 
 // offset of the scale byte of (row n of B, group of 16 `grp` of the stage) inside the stage's 2048 bytes:
 // one 512-byte block per MMA (4 groups), in it 16 bytes per (n % 32), 4 per (n / 32), one per group
-__device__ __forceinline__ uint32_t mq_sfb_offset(uint32_t n, uint32_t grp) {
-    return (grp >> 2) * 512u + (n & 31u) * 16u + (n >> 5) * 4u + (grp & 3u);
+// (with more than 128 rows of B - `wide` - an MMA has two such blocks, rows 0-127 and 128-255)
+__device__ __forceinline__ uint32_t mq_sfb_offset(uint32_t n, uint32_t grp, bool wide) {
+    return (grp >> 2) * (wide ? 1024u : 512u) + (n >> 7) * 512u + (n & 31u) * 16u + ((n >> 5) & 3u) * 4u + (grp & 3u);
 }
 
 // PRE = false: 576 threads, piece warps 10-17 derive the tokens' digit rows in every block (no second launch:
@@ -206,7 +217,7 @@ matmul_q_fp4_kernel(const __grid_constant__ CUtensorMap tmap_wq, const __grid_co
     volatile uint32_t* const abort_flag = misc + 1;
     uint32_t* const tok_amax = misc + 2;                                   // [MQ_MAX_TOKENS]
     volatile uint32_t* const fix_flag = misc + 2 + MQ_MAX_TOKENS;
-    volatile uint8_t* const nan_rows = reinterpret_cast<volatile uint8_t*>(misc + 32);   // [MQ_ROWS]: a NaN scale byte seen
+    volatile uint8_t* const nan_rows = reinterpret_cast<volatile uint8_t*>(misc + 48);   // [MQ_ROWS]: a NaN scale byte seen
 
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
     const uint32_t split = blockIdx.x % a.k_splits, tile = blockIdx.x / a.k_splits;
@@ -215,6 +226,8 @@ matmul_q_fp4_kernel(const __grid_constant__ CUtensorMap tmap_wq, const __grid_co
     const uint32_t kb0 = split * a.kb_per_split;
     const uint32_t KB = (kb_all - kb0 < a.kb_per_split) ? (kb_all - kb0) : a.kb_per_split;
     const uint32_t N = a.m * MQ_PIECES;
+    const bool wide = N > 128u;                               // more than 16 tokens: one accumulator, two scale blocks of B per MMA
+    const uint32_t sfb_bytes = matmul_q_sfb_bytes(a.m);
     const long long t_start = clock64();
 
     if (warp == 0) {
@@ -305,7 +318,7 @@ matmul_q_fp4_kernel(const __grid_constant__ CUtensorMap tmap_wq, const __grid_co
                         break;
                     }
                 }
-                mbar_arrive_expect_tx(raw_full(s), MQ_CODE_BYTES + (PRE ? b_bytes + MQ_SF_BYTES : 0u));
+                mbar_arrive_expect_tx(raw_full(s), MQ_CODE_BYTES + (PRE ? b_bytes + sfb_bytes : 0u));
                 tma_load_2d(codes_of(s), &tmap_wq, (int)((kb0 + kb) * (MQ_STAGE_K / 2)), (int)n0, raw_full(s));
                 if (kb + 1u == S || kb + 1u == KB) allow_dependents();       // the ring is filled (once is enough; twice is harmless)
                 if (PRE) {
@@ -319,7 +332,7 @@ matmul_q_fp4_kernel(const __grid_constant__ CUtensorMap tmap_wq, const __grid_co
                         for (; b_issued <= kb; b_issued++) {             // stages < S sit in slot = stage
                             const uint32_t sj = b_issued % S;
                             tma_load_2d(b_of(sj), &tmap_b, (int)((kb0 + b_issued) * (MQ_STAGE_K / 2)), 0, raw_full(sj));
-                            tma_load_1d(sfb_of(sj), a.pre_sfb + (size_t)(kb0 + b_issued) * MQ_SF_BYTES, MQ_SF_BYTES, raw_full(sj));
+                            tma_load_1d(sfb_of(sj), a.pre_sfb + (size_t)(kb0 + b_issued) * sfb_bytes, sfb_bytes, raw_full(sj));
                         }
                     }
                 }
@@ -379,18 +392,23 @@ matmul_q_fp4_kernel(const __grid_constant__ CUtensorMap tmap_wq, const __grid_co
             }
             tc_fence_after_sync();
             const uint32_t a_lo = umma_desc_lo(codes_of(s)), b_lo = umma_desc_lo(b_of(s));
-            const uint32_t sfa_t = tmem_base + MQ_TMEM_SFA + 16u * s, sfb_t = tmem_base + MQ_TMEM_SFB + 16u * s;
-            const uint32_t d = tmem_base + ((kb & 1u) ? MQ_TMEM_D1 : 0u);   // two accumulators, alternating
+            const uint32_t sfa_t = tmem_base + MQ_TMEM_SFA + 16u * s;
+            const uint32_t sfb_t = tmem_base + (wide ? MQ_TMEM_SFB_WIDE + 32u * s : MQ_TMEM_SFB + 16u * s);
+            const uint32_t sfb_cols = wide ? 8u : 4u, sfb_block = wide ? 1024u : 512u;     // per MMA
+            const uint32_t d = tmem_base + ((!wide && (kb & 1u)) ? MQ_TMEM_D1 : 0u);       // two accumulators, alternating, when they fit
             if (elect_one()) {
 #pragma unroll
                 for (uint32_t j = 0; j < 4; j++) {
                     tmem_cp_32x128b_warpx4(sfa_t + 4u * j, umma_desc_scale_block(sfa_of(s) + 512u * j));
-                    tmem_cp_32x128b_warpx4(sfb_t + 4u * j, umma_desc_scale_block(sfb_of(s) + 512u * j));
+                    tmem_cp_32x128b_warpx4(sfb_t + sfb_cols * j, umma_desc_scale_block(sfb_of(s) + sfb_block * j));
+                    if (wide)          // rows 128-255 of B: the next four columns
+                        tmem_cp_32x128b_warpx4(sfb_t + sfb_cols * j + 4u, umma_desc_scale_block(sfb_of(s) + sfb_block * j + 512u));
                 }
+                const uint32_t fresh = wide ? 1u : 2u;       // stages that start an accumulator
 #pragma unroll
                 for (uint32_t j = 0; j < 4; j++)
-                    umma1_mxf4nvf4(d, a_lo + 2u * j, b_lo + 2u * j, idesc, sfa_t + 4u * j, sfb_t + 4u * j,
-                                   (kb >= 2u || j > 0u) ? 1u : 0u);
+                    umma1_mxf4nvf4(d, a_lo + 2u * j, b_lo + 2u * j, idesc, sfa_t + 4u * j, sfb_t + sfb_cols * j,
+                                   (kb >= fresh || j > 0u) ? 1u : 0u);
                 umma_commit(empty(s));
             }
             __syncwarp();
@@ -476,8 +494,8 @@ matmul_q_fp4_kernel(const __grid_constant__ CUtensorMap tmap_wq, const __grid_co
             }
         }
         // B's scale blocks start as zeros: rows nobody writes must not hold stray NaN patterns
-        for (uint32_t i = xt; i < S * (MQ_SF_BYTES / 16u); i += 32u * MQ_PIECE_WARPS) {
-            const uint32_t s = i / (MQ_SF_BYTES / 16u), o = i % (MQ_SF_BYTES / 16u);
+        for (uint32_t i = xt; i < S * (sfb_bytes / 16u); i += 32u * MQ_PIECE_WARPS) {
+            const uint32_t s = i / (sfb_bytes / 16u), o = i % (sfb_bytes / 16u);
             *reinterpret_cast<uint4*>(smem + (sfb_of(s) - base) + 16u * o) = make_uint4(0, 0, 0, 0);
         }
         asm volatile("bar.sync 1, %0;" ::"r"(32u * MQ_PIECE_WARPS) : "memory");
@@ -513,7 +531,7 @@ matmul_q_fp4_kernel(const __grid_constant__ CUtensorMap tmap_wq, const __grid_co
 #pragma unroll
             for (uint32_t i = 0; i < 4; i++) {
                 const uint32_t pc = 4u * (lane & 1u) + i;
-                sb[mq_sfb_offset(tok * MQ_PIECES + pc, grp)] = (uint8_t)mq_ue4m3_pow2(q0 - 2 * (int)pc);
+                sb[mq_sfb_offset(tok * MQ_PIECES + pc, grp, wide)] = (uint8_t)mq_ue4m3_pow2(q0 - 2 * (int)pc);
             }
             fence_proxy_async_smem();
             __syncwarp();
@@ -624,17 +642,18 @@ matmul_q_fp4_kernel(const __grid_constant__ CUtensorMap tmap_wq, const __grid_co
             const bool row_nan = nan_rows[row] != 0;
             const uint32_t lane_base = tmem_base + ((32u * (warp & 3u)) << 16);
             const bool to_partial = a.k_splits > 1u;
+            const bool two_acc = !wide && KB > 1u;
             float* const out = to_partial ? a.partial + (size_t)split * a.m * a.n : a.y;
             for (uint32_t t = 0; t < a.m; t++) {
                 uint32_t d0[8], d1[8];
                 tmem_ld_32x32b_x8(lane_base + 8u * t, d0);
-                if (KB > 1u) tmem_ld_32x32b_x8(lane_base + MQ_TMEM_D1 + 8u * t, d1);
+                if (two_acc) tmem_ld_32x32b_x8(lane_base + MQ_TMEM_D1 + 8u * t, d1);
                 tmem_ld_wait();
                 float v = 0.0f;
 #pragma unroll
                 for (int pc = 7; pc >= 0; pc--) {                // small pieces first
                     float c = __uint_as_float(d0[pc]);
-                    if (KB > 1u) c += __uint_as_float(d1[pc]);
+                    if (two_acc) c += __uint_as_float(d1[pc]);
                     v += c;
                 }
                 const uint32_t te = (PRE ? __ldg(a.pre_amax + t) : tok_amax[t]) >> 23;
@@ -682,7 +701,7 @@ matmul_q_fp4_kernel(const __grid_constant__ CUtensorMap tmap_wq, const __grid_co
 // each finds the token's largest magnitude itself and takes every gridDim.y-th set of 32 stages.
 //   pieces [8 m][k / 2] bytes: row 8 t + p holds piece p of token t, packed like wq (a tensor map with the
 //                              128-byte swizzle brings 8 m x 128 bytes of it per stage);
-//   sfb    [k / 256][2048] bytes: per stage the four scale blocks of B (rows past 8 m stay zero);
+//   sfb    [k / 256][2048 or 4096] bytes: per stage the scale blocks of B (rows past 8 m stay zero);
 //   amax   [m]: the token's largest magnitude as f32 bits.
 // It follows the previous launch of the same pipeline in the stream, which may still be reading these
 // buffers: nothing is written before grid_dependency_wait().
@@ -690,6 +709,8 @@ template <bool XF32>
 __global__ void __launch_bounds__(1024, 1)
 matmul_q_pieces_kernel(const void* __restrict__ x, uint32_t k, uint8_t* __restrict__ pieces, uint8_t* __restrict__ sfb,
                        uint32_t* __restrict__ amax) {
+    const bool wide = gridDim.x > 16u;                        // tokens = gridDim.x
+    const uint32_t sfb_stage = matmul_q_sfb_bytes(gridDim.x);
     __shared__ uint32_t s_amax;
     const uint32_t tok = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
     if (tid == 0) s_amax = 0;
@@ -741,7 +762,7 @@ matmul_q_pieces_kernel(const void* __restrict__ x, uint32_t k, uint8_t* __restri
 #pragma unroll
         for (uint32_t i = 0; i < 4; i++) {
             const uint32_t pc = 4u * (lane & 1u) + i;
-            sfb[(size_t)kb * MQ_SF_BYTES + mq_sfb_offset(tok * MQ_PIECES + pc, grp)] = (uint8_t)mq_ue4m3_pow2(q0 - 2 * (int)pc);
+            sfb[(size_t)kb * sfb_stage + mq_sfb_offset(tok * MQ_PIECES + pc, grp, wide)] = (uint8_t)mq_ue4m3_pow2(q0 - 2 * (int)pc);
         }
     }
 }

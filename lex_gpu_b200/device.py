@@ -324,7 +324,7 @@ class Gpu:
 
     def plan_matmul_fp4(self, t: int, n_out: int, n_in: int, residual: bool = False, x_half: bool = True,
                         stages: int = 0, k_splits: int = 0, weights_may_change: bool = False) -> Pipeline:
-        """matmul_q_x with the NVFP4 layout for t <= 16 tokens (llama.rs:444-499): weights as f32, not
+        """matmul_q_x with the NVFP4 layout for t <= 32 tokens (llama.rs:444-499): weights as f32, not
         rounded to f16; runs on the block-scaled FP4 tensor-core path."""
         s = Sched(0, 0, stages, 0, 0, k_splits, SCHED_WEIGHTS_MAY_CHANGE if weights_may_change else 0)
         h = c_void_p()

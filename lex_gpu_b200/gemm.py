@@ -98,7 +98,7 @@ def gemm_fp4(gpu: Gpu, x: np.ndarray, wq: np.ndarray, ws: np.ndarray, wg: np.nda
 
 def matmul_fp4(gpu: Gpu, x: np.ndarray, wq: np.ndarray, ws: np.ndarray, wg: np.ndarray,
                r: Optional[np.ndarray] = None, **sched) -> np.ndarray:
-    """matmul_q_x with the NVFP4 layout, host arrays in and out (llama.rs:444-499): t <= 16 tokens of f16 or
+    """matmul_q_x with the NVFP4 layout, host arrays in and out (llama.rs:444-499): t <= 32 tokens of f16 or
     f32 activations against weights used as f32 (not rounded to f16).  For tests and examples."""
     m, k = x.shape
     n = wq.shape[0]
