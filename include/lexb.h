@@ -169,7 +169,13 @@ LEXB_API int lexb_gemm_fp4_enqueue_host(lexb_gpu* gpu, const lexb_pipeline* p, c
                                         const lexb_buffer* wq, const lexb_buffer* ws, const lexb_buffer* wg,
                                         const lexb_buffer* r_or_null, lexb_buffer* y_dev, void* y_host);
 /* Gpu::run_launches, crates/lex-cuda/src/device.rs:650-672: all steps, one synchronise;
- * cpu_s = host time to enqueue, wall_s = host time until the device is idle. */
+ * cpu_s = host time to enqueue, wall_s = host time until the device is idle.
+ * The results are those of the steps run one after another.  Consecutive lexb_matmul_fp4_plan steps of t <= 2
+ * tokens planned with k_splits = 1 and constant weights (no LEXB_SCHED_WEIGHTS_MAY_CHANGE), with the same t, k
+ * and activation type, of which none reads or overwrites a buffer that an earlier one of them touches (x and r
+ * not written, y neither read nor written: the address ranges are compared), are run as ONE persistent kernel
+ * over all their row tiles (the gate/up pair, q/k/v); each result is bit-identical to the step launched alone.
+ * A step that depends on the run starts a new launch.  The environment variable LEXB_CHAIN=0 turns this off. */
 LEXB_API int lexb_run_launches(lexb_gpu* gpu, const lexb_step* steps, size_t nsteps, double* cpu_s, double* wall_s);
 /* Gpu::run_each_timed, crates/lex-cuda/src/device.rs:684-739: device seconds per step,
  * from events recorded between launches, no synchronise in between. */

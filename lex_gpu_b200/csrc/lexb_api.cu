@@ -14,6 +14,7 @@
 #include <mutex>
 #include <new>
 #include <string>
+#include <unordered_map>
 #include <vector>
 
 #include "../../include/lexb.h"
@@ -21,6 +22,7 @@
 #include "gemm_fp4_sm100_pair.cuh"
 #include "matvec_fp4_sm100.cuh"
 #include "matmul_q_fp4_sm100.cuh"
+#include "matmul_q_chain_sm100.cuh"
 
 // Scratch of lexb_gemm_fp4_splitk_static: split-K partial products [splits][m][n] f32.  Part of
 // the library image, so every GPU that loads the library holds these 32 MiB until the process exits.
@@ -62,6 +64,11 @@ struct lexb_gpu {
     uint32_t* d_status = nullptr;
     bool pdl = true;                         // programmatic dependent launch of the two-CTA GEMM
     float* static_scratch = nullptr;         // device address of g_splitk_static_scratch on this device, once resolved
+    // Job tables of chained runs, kept by content: a decode loop issues the same lists token after token, and a
+    // table found here needs no copy in front of its launch (a copy would put the launch behind the whole
+    // kernel before it).  A table is never written again once copied.
+    struct ChainTable { std::vector<lexb::MqChainJob> host; lexb::MqChainJob* dev; };
+    std::unordered_multimap<uint64_t, ChainTable> chain_tables;
     unsigned long long* d_trace = nullptr;   // phase timers of the last two-CTA launch, when tracing is on
     size_t trace_ctas = 0;
     cudaDeviceProp prop{};
@@ -413,6 +420,130 @@ int launch_one(lexb_gpu* g, const lexb_pipeline* p, const lexb_buffer* x, const 
     return LEXB_OK;
 }
 
+// Consecutive steps of a list that can run as one persistent kernel (matmul_q_chain_sm100.cuh): block-scaled
+// matmul_q with in-block digit rows, one K range per block, the same t, k and activation type (n may differ),
+// weights declared constant.  LEXB_CHAIN=0 turns it off.
+// (four piece warps: beyond a few tokens they would bound the kernel)
+static uint32_t chain_max_m() {
+    static const uint32_t v = env_u32("LEXB_CHAIN_MAX_M", 2);
+    return v > 4u ? 4u : v;
+}
+bool chain_member(const lexb_gpu* g, const lexb_step& s, const lexb_pipeline* first) {
+    const lexb_pipeline* p = s.pipeline;
+    if (!p || !s.buffers || p->gpu != g || p->kernel != KERNEL_MATMUL_Q || p->mq_pre || p->m > chain_max_m() || p->k_splits != 1u) return false;
+    if (!(p->flags & 1u) || s.nbuffers != (p->residual ? 6u : 5u)) return false;
+    if ((p->k / lexb::MQ_STAGE_K) % lexb::MQ_WS_GROUP == 1u) return false;          // a scale-byte group of one stage is seen by half the scale warps only
+    if (p->stages != lexb::MQ_MAX_STAGES || lexb::matmul_q_chain_smem_bytes(p->stages) > g->smem_optin) return false;
+    return !first || (p->m == first->m && p->k == first->k && p->x_f32 == first->x_f32 && p->stages == first->stages &&
+                      p->ws_pitch == first->ws_pitch);
+}
+
+size_t chain_run(const lexb_gpu* g, const lexb_step* steps, size_t nsteps, size_t i) {
+    static const bool on = env_u32("LEXB_CHAIN", 1) != 0;
+    if (!on || !chain_member(g, steps[i], nullptr)) return 0;
+    // The run's row tiles are spread over the blocks with no order between blocks, so a step joins the run only
+    // if nothing it reads (x, r) is written by a step already in it and nothing it writes (y) is read or
+    // written by one: such a step starts the next launch, and the stream orders it.
+    struct Range { const char *lo, *hi; };
+    auto range = [](const lexb_buffer* b, size_t bytes) { const char* p0 = static_cast<const char*>(b->ptr); return Range{p0, p0 + bytes}; };
+    auto meet = [](Range a, Range b) { return a.lo < b.hi && b.lo < a.hi; };
+    auto ranges = [&](size_t e, Range& x, Range& r, Range& y) {
+        const lexb_pipeline* pe = steps[e].pipeline;
+        const size_t out = static_cast<size_t>(pe->m) * pe->n * 4;
+        x = range(steps[e].buffers[0], static_cast<size_t>(pe->m) * pe->k * (pe->x_f32 ? 4 : 2));
+        r = pe->residual ? range(steps[e].buffers[4], out) : Range{nullptr, nullptr};
+        y = range(steps[e].buffers[pe->residual ? 5 : 4], out);
+    };
+    auto x_written_in_run = [&](size_t cand, size_t len) {
+        for (uint32_t b = 0; b < steps[cand].nbuffers; b++)
+            if (!steps[cand].buffers[b] || !steps[cand].buffers[b]->ptr) return true;      // (refused by the launch of its own)
+        Range cx, cr, cy;
+        ranges(cand, cx, cr, cy);
+        for (size_t e = i; e < i + len; e++) {
+            Range ex, er, ey;
+            ranges(e, ex, er, ey);
+            if (meet(cx, ey) || meet(cr, ey) || meet(cy, ex) || meet(cy, er) || meet(cy, ey)) return true;
+        }
+        return false;
+    };
+    size_t len = 1;
+    while (i + len < nsteps && len < 4096 && chain_member(g, steps[i + len], steps[i].pipeline) && !x_written_in_run(i + len, len)) len++;
+    return len >= 2 ? len : 0;
+}
+
+int launch_chain(lexb_gpu* g, const lexb_step* steps, size_t count) {
+    const lexb_pipeline* p0 = steps[0].pipeline;
+    std::vector<lexb::MqChainJob> jobs(count);
+    uint32_t tiles = 0;
+    int rc;
+    for (size_t i = 0; i < count; i++) {
+        const lexb_pipeline* p = steps[i].pipeline;
+        lexb_buffer* const* b = steps[i].buffers;
+        const lexb_buffer *x = b[0], *wq = b[1], *ws = b[2], *wg = b[3], *r = p->residual ? b[4] : nullptr;
+        const lexb_buffer* y = p->residual ? b[5] : b[4];
+        const size_t m = p->m, n = p->n, k = p->k;
+        if ((rc = check_buf(x, g, m * k * (p->x_f32 ? 4 : 2), "x"))) return rc;
+        if ((rc = check_buf(wq, g, n * k / 2, "wq"))) return rc;
+        if ((rc = check_buf(ws, g, n * k / 16, "ws"))) return rc;
+        if ((rc = check_buf(wg, g, n * 4, "wg"))) return rc;
+        if ((rc = check_buf(y, g, m * n * 4, "y"))) return rc;
+        if (r && (rc = check_buf(r, g, m * n * 4, "r"))) return rc;
+        lexb_pipeline::MapEntry maps;
+        if ((rc = get_maps(p, x->ptr, wq->ptr, ws->ptr, &maps))) return rc;
+        jobs[i].wq = maps.map_wq;
+        jobs[i].ws = maps.map_ws;
+        jobs[i].x = x->ptr;
+        jobs[i].wg = static_cast<const float*>(wg->ptr);
+        jobs[i].r = r ? static_cast<const float*>(r->ptr) : nullptr;
+        jobs[i].y = static_cast<float*>(y->ptr);
+        jobs[i].n = p->n;
+        tiles += (p->n + lexb::MQ_ROWS - 1u) / lexb::MQ_ROWS;
+        jobs[i].tile_end = tiles;
+    }
+    const size_t table_bytes = sizeof(lexb::MqChainJob) * count;
+    uint64_t h = 1469598103934665603ull;
+    {
+        const unsigned char* bytes = reinterpret_cast<const unsigned char*>(jobs.data());
+        for (size_t i = 0; i < table_bytes; i++) h = (h ^ bytes[i]) * 1099511628211ull;
+    }
+    lexb::MqChainJob* d_jobs = nullptr;
+    auto hit = g->chain_tables.equal_range(h);
+    for (auto it = hit.first; it != hit.second && !d_jobs; ++it)
+        if (it->second.host.size() == count && !memcmp(it->second.host.data(), jobs.data(), table_bytes)) d_jobs = it->second.dev;
+    if (!d_jobs) {
+        if (g->chain_tables.size() >= 4096) {
+            // (tables of launches still in flight are freed only after them)
+            CUDA_TRY(cudaStreamSynchronize(g->stream));
+            for (auto& e : g->chain_tables) cudaFree(e.second.dev);
+            g->chain_tables.clear();
+        }
+        CUDA_TRY(cudaMalloc(&d_jobs, table_bytes));
+        auto it = g->chain_tables.emplace(h, lexb_gpu::ChainTable{std::move(jobs), d_jobs});
+        // (the source is the cache's own copy: it outlives the transfer)
+        CUDA_TRY(cudaMemcpyAsync(d_jobs, it->second.host.data(), table_bytes, cudaMemcpyHostToDevice, g->stream));
+    }
+    lexb::MqChainArgs a{};
+    a.jobs = d_jobs;
+    a.n_jobs = static_cast<uint32_t>(count);
+    a.n_tiles = tiles;
+    a.m = p0->m; a.k = p0->k; a.stages = p0->stages; a.ws_pitch = p0->ws_pitch;
+    a.status = g->d_status;
+    // blocks of this kernel do not wait for one another, and there is at most one per SM
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(std::min<uint32_t>(tiles, static_cast<uint32_t>(g->prop.multiProcessorCount)));
+    cfg.blockDim = dim3(lexb::MQC_THREADS);
+    cfg.dynamicSmemBytes = lexb::matmul_q_chain_smem_bytes(p0->stages);
+    cfg.stream = g->stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = g->pdl ? 1 : 0;
+    if (p0->x_f32) CUDA_TRY(cudaLaunchKernelEx(&cfg, lexb::matmul_q_chain_kernel<true>, a));
+    else CUDA_TRY(cudaLaunchKernelEx(&cfg, lexb::matmul_q_chain_kernel<false>, a));
+    return LEXB_OK;
+}
+
 int launch_step(lexb_gpu* g, const lexb_step& s, const lexb_step* following = nullptr) {
     if (!s.pipeline || !s.buffers) return fail(LEXB_ERR_ARG, "step without pipeline or buffers");
     const bool res = s.pipeline->residual;
@@ -473,6 +604,8 @@ int lexb_open(int device, lexb_gpu** out) {
         cudaFuncSetAttribute(lexb::matvec_fp4_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem) != cudaSuccess ||
         cudaFuncSetAttribute(lexb::matvec_fp4_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem) != cudaSuccess ||
         cudaFuncSetAttribute(lexb::matvec_fp4_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem) != cudaSuccess ||
+        cudaFuncSetAttribute(lexb::matmul_q_chain_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem) != cudaSuccess ||
+        cudaFuncSetAttribute(lexb::matmul_q_chain_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem) != cudaSuccess ||
         cudaFuncSetAttribute(lexb::matmul_q_fp4_kernel<true, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem) != cudaSuccess ||
         cudaFuncSetAttribute(lexb::matmul_q_fp4_kernel<false, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem) != cudaSuccess ||
         cudaFuncSetAttribute(lexb::matmul_q_fp4_kernel<true, true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem) != cudaSuccess ||
@@ -495,6 +628,8 @@ void lexb_close(lexb_gpu* g) {
     }
     if (g->d_status) cudaFree(g->d_status);
     if (g->d_trace) cudaFree(g->d_trace);
+    for (auto& e : g->chain_tables) cudaFree(e.second.dev);
+    g->chain_tables.clear();
     delete g;
 }
 
@@ -935,8 +1070,15 @@ int lexb_run_launches(lexb_gpu* g, const lexb_step* steps, size_t nsteps, double
     if (rc) return rc;
     if (!steps && nsteps) return fail(LEXB_ERR_ARG, "lexb_run_launches: null steps");
     const auto t0 = std::chrono::steady_clock::now();
-    for (size_t i = 0; i < nsteps; i++)
+    for (size_t i = 0; i < nsteps;) {
+        if (const size_t len = chain_run(g, steps, nsteps, i)) {
+            if ((rc = launch_chain(g, steps + i, len))) return rc;
+            i += len;
+            continue;
+        }
         if ((rc = launch_step(g, steps[i], i + 1 < nsteps ? &steps[i + 1] : nullptr))) return rc;
+        i++;
+    }
     const auto t1 = std::chrono::steady_clock::now();
     CUDA_TRY(cudaStreamSynchronize(g->stream));
     const auto t2 = std::chrono::steady_clock::now();
@@ -979,10 +1121,16 @@ int lexb_time_launches(lexb_gpu* g, const lexb_step* steps, size_t nsteps, uint3
     CUDA_TRY(cudaStreamSynchronize(g->stream));
     cudaEventRecord(a, g->stream);
     for (uint32_t r = 0; r < reps; r++)
-        for (size_t i = 0; i < nsteps; i++) {
+        for (size_t i = 0; i < nsteps;) {
+            if (const size_t len = chain_run(g, steps, nsteps, i)) {
+                if ((rc = launch_chain(g, steps + i, len))) { cudaEventDestroy(a); cudaEventDestroy(b); return rc; }
+                i += len;
+                continue;
+            }
             // the list repeats: the step after the last one is the first one again
             const lexb_step* following = i + 1 < nsteps ? &steps[i + 1] : (r + 1 < reps ? &steps[0] : nullptr);
             if ((rc = launch_step(g, steps[i], following))) { cudaEventDestroy(a); cudaEventDestroy(b); return rc; }
+            i++;
         }
     cudaEventRecord(b, g->stream);
     cudaError_t e = cudaStreamSynchronize(g->stream);

@@ -325,3 +325,100 @@ def test_digit_rows_from_the_pieces_kernel_for_few_tokens_too(gpu, monkeypatch, 
     ahead = L.matmul_fp4(gpu, x, wq, ws, wg)
     check(ahead, want, rel_tol=3e-2 if f32 else 5e-3)
     assert np.array_equal(ahead, in_block)
+
+
+def test_a_step_list_whose_residuals_feed_each_other(gpu):
+    """Steps of one shape issued as a list, each adding the step before's result: no two of them may share a
+    launch, and each step's result equals the same step launched on its own, bit for bit."""
+    m, n, k = 2, 1024, 2048
+    x = inputs.make_x(m, k, seed_base=500)
+    xb = gpu.upload(x)
+    sets = [inputs.make_weights(n, k, seed_base=501, copy=c) for c in range(5)]
+    qs = [L.QBuf(gpu, *w) for w in sets]
+    pipe = gpu.plan_matmul_fp4(m, n, k, k_splits=1)                  # one K range per block: what the chain takes
+    pipe_r = gpu.plan_matmul_fp4(m, n, k, residual=True, k_splits=1)
+    ys = [gpu.alloc(4 * m * n) for _ in sets]
+    alone = []
+    for i, (q, yb) in enumerate(zip(qs, ys)):           # step i adds step i-1's result as its residual
+        if i == 0:
+            gpu.run(pipe, q.bind(xb, None, yb))
+        else:
+            gpu.run(pipe_r, q.bind(xb, ys[i - 1], yb))
+        gpu.sync()
+        alone.append(gpu.download(yb, np.float32, (m, n)))
+    for yb in ys:
+        gpu.memset(yb, 0xEE)
+    steps = [(pipe, qs[0].bind(xb, None, ys[0]))] + [(pipe_r, qs[i].bind(xb, ys[i - 1], ys[i])) for i in range(1, 5)]
+    gpu.run_launches(steps)
+    for i, yb in enumerate(ys):
+        assert np.array_equal(gpu.download(yb, np.float32, (m, n)), alone[i]), i
+    want = O.matmul_q_x(x, *sets[0])
+    for i in range(1, 5):
+        want = O.matmul_q_x(x, *sets[i], r=want)
+    check(alone[4], want)
+    assert gpu.status_word() == 0
+
+
+@pytest.mark.parametrize("m,xf32", [(1, False), (2, False), (2, True)])
+def test_independent_steps_of_a_list_run_as_one_kernel(gpu, m, xf32):
+    """Independent steps over the same K (the q/k/v or gate/up pattern: different row counts, some sharing
+    their activations, one with a residual from outside the list) run as one persistent kernel whose blocks
+    stride over all the steps' row tiles - 160 tiles here, more than the GPU has SMs.  Every result equals the
+    same step launched alone, bit for bit, and the oracle's within the operator's tolerance."""
+    k = 1024
+    ns = [4096, 1024, 1024, 4096, 2048, 8192]
+    rng = np.random.Generator(np.random.PCG64(520 + m))
+    xs = [inputs.make_x(m, k, seed_base=521), inputs.make_x(m, k, seed_base=522)]
+    if xf32:
+        xs = [x.astype(np.float32) * np.float32(1.0009765625) for x in xs]
+    xbs = [gpu.upload(x) for x in xs]
+    which_x = [0, 0, 0, 1, 1, 0]
+    sets = [inputs.make_weights(n, k, seed_base=523, copy=c) for c, n in enumerate(ns)]
+    qs = [L.QBuf(gpu, *w) for w in sets]
+    r_host = rng.standard_normal((m, ns[4])).astype(np.float32)
+    rb = gpu.upload(r_host)
+    pipes = [gpu.plan_matmul_fp4(m, n, k, residual=(i == 4), x_half=not xf32, k_splits=1) for i, n in enumerate(ns)]
+    ys = [gpu.alloc(4 * m * n) for n in ns]
+    binds = [q.bind(xbs[which_x[i]], rb if i == 4 else None, ys[i]) for i, q in enumerate(qs)]
+    alone = []
+    for i in range(len(ns)):
+        gpu.run(pipes[i], binds[i])
+        gpu.sync()
+        alone.append(gpu.download(ys[i], np.float32, (m, ns[i])))
+        check(alone[i], O.matmul_q_x(xs[which_x[i]], *sets[i], r=r_host if i == 4 else None), rel_tol=3e-2 if xf32 else 5e-3)
+    steps = L.StepList(list(zip(pipes, binds)))
+    for _ in range(2):
+        for yb in ys:
+            gpu.memset(yb, 0xEE)
+        gpu.run_launches(steps)
+        for i, yb in enumerate(ys):
+            assert np.array_equal(gpu.download(yb, np.float32, (m, ns[i])), alone[i]), i
+    assert gpu.status_word() == 0
+
+
+def test_a_chain_whose_steps_feed_each_other(gpu):
+    """n == k and f32 activations: every step reads the step before's y as its x, so every step is a launch
+    of its own and the stream orders them."""
+    m, n = 2, 1024
+    rng = np.random.Generator(np.random.PCG64(510))
+    x0 = rng.standard_normal((m, n)).astype(np.float32)
+    sets = []
+    for c in range(6):
+        wq, ws, wg = inputs.make_weights(n, n, seed_base=511, copy=c)
+        sets.append((wq, ws, (wg / np.float32(40.0)).astype(np.float32)))        # keeps the values near 1 from step to step
+    qs = [L.QBuf(gpu, *w) for w in sets]
+    pipe = gpu.plan_matmul_fp4(m, n, n, x_half=False)
+    bufs = [gpu.upload(x0)] + [gpu.alloc(4 * m * n) for _ in sets]
+    steps = L.StepList([(pipe, q.bind(bufs[i], None, bufs[i + 1])) for i, q in enumerate(qs)])
+    for _ in range(3):                                                            # repeated: counters and rings start clean each time
+        for b in bufs[1:]:
+            gpu.memset(b, 0xEE)
+        gpu.run_launches(steps)
+        want = x0
+        for i, w in enumerate(sets):
+            want = O.matmul_q_x(want, *w)
+            got = gpu.download(bufs[i + 1], np.float32, (m, n))
+            err, scale, _ = O.err_of_scale(got, want)
+            assert scale > 1e-3 and err <= 1e-4 * (i + 1), (i, err)             # each step inherits the steps before
+            want = got                                                            # compare step by step
+    assert gpu.status_word() == 0
