@@ -6,6 +6,7 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 
+#include <algorithm>
 #include <chrono>
 #include <cstdarg>
 #include <cstdio>
@@ -13,7 +14,9 @@
 #include <cstring>
 #include <mutex>
 #include <new>
+#include <map>
 #include <string>
+#include <tuple>
 #include <unordered_map>
 #include <vector>
 
@@ -69,6 +72,11 @@ struct lexb_gpu {
     // kernel before it).  A table is never written again once copied.
     struct ChainTable { std::vector<lexb::MqChainJob> host; lexb::MqChainJob* dev; };
     std::unordered_multimap<uint64_t, ChainTable> chain_tables;
+    // Digit rows of a run's activations (matmul_q_pieces_kernel's output: [8 m][k / 2] digit rows, [k / 256][2048]
+    // scale blocks, [m] magnitudes), one buffer per activation buffer, shape and stream: rewritten by every run that
+    // reads that x, in stream order.
+    struct ChainPre { uint8_t* buf; CUtensorMap map; };
+    std::map<std::tuple<const void*, uint32_t, uint32_t, bool, cudaStream_t>, ChainPre> chain_pre;
     unsigned long long* d_trace = nullptr;   // phase timers of the last two-CTA launch, when tracing is on
     size_t trace_ctas = 0;
     cudaDeviceProp prop{};
@@ -423,10 +431,15 @@ int launch_one(lexb_gpu* g, const lexb_pipeline* p, const lexb_buffer* x, const 
 // Consecutive steps of a list that can run as one persistent kernel (matmul_q_chain_sm100.cuh): block-scaled
 // matmul_q with in-block digit rows, one K range per block, the same t, k and activation type (n may differ),
 // weights declared constant.  LEXB_CHAIN=0 turns it off.
-// (four piece warps: beyond a few tokens they would bound the kernel)
+// (two accumulator sets of 2 x 32 columns: 4 tokens x 8 digit rows)
 static uint32_t chain_max_m() {
-    static const uint32_t v = env_u32("LEXB_CHAIN_MAX_M", 2);
+    static const uint32_t v = env_u32("LEXB_CHAIN_MAX_M", 4);
     return v > 4u ? 4u : v;
+}
+// From this many tokens on the digit rows of a run come from matmul_q_pieces_kernel, not from piece warps in every block.
+static uint32_t chain_pre_min_m() {
+    static const uint32_t v = env_u32("LEXB_CHAIN_PRE_MIN_M", 3);
+    return v;
 }
 bool chain_member(const lexb_gpu* g, const lexb_step& s, const lexb_pipeline* first) {
     const lexb_pipeline* p = s.pipeline;
@@ -476,6 +489,13 @@ int launch_chain(lexb_gpu* g, const lexb_step* steps, size_t count) {
     std::vector<lexb::MqChainJob> jobs(count);
     uint32_t tiles = 0;
     int rc;
+    const bool pre = p0->m >= chain_pre_min_m();
+    std::vector<const void*> pre_done;               // activation buffers whose digit rows this run has asked for
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    const size_t pieces_bytes = static_cast<size_t>(p0->m) * 8u * (p0->k / 2u);
+    const size_t sfb_bytes = static_cast<size_t>(p0->k / lexb::MQ_STAGE_K) * lexb::MQ_SF_BYTES;
     for (size_t i = 0; i < count; i++) {
         const lexb_pipeline* p = steps[i].pipeline;
         lexb_buffer* const* b = steps[i].buffers;
@@ -497,6 +517,37 @@ int launch_chain(lexb_gpu* g, const lexb_step* steps, size_t count) {
         jobs[i].r = r ? static_cast<const float*>(r->ptr) : nullptr;
         jobs[i].y = static_cast<float*>(y->ptr);
         jobs[i].n = p->n;
+        if (pre) {
+            const auto key = std::make_tuple(static_cast<const void*>(x->ptr), p0->m, p0->k, p0->x_f32 != 0, g->stream);
+            auto it = g->chain_pre.find(key);
+            if (it == g->chain_pre.end()) {
+                lexb_gpu::ChainPre cp{};
+                const size_t total = pieces_bytes + sfb_bytes + 4u * lexb::MQ_MAX_TOKENS;
+                CUDA_TRY(cudaMalloc(&cp.buf, total));
+                cudaError_t e = cudaMemsetAsync(cp.buf, 0, total, g->stream);      // scale rows nobody writes stay zero
+                int erc = e == cudaSuccess ? encode_2d(p, &cp.map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, cp.buf, p0->k / 2u, 8u * p0->m, 128u,
+                                                      8u * p0->m, CU_TENSOR_MAP_SWIZZLE_128B, "digit rows of a run")
+                                           : fail(LEXB_ERR_CUDA, "clearing the digit-row buffers: %s", cudaGetErrorString(e));
+                if (erc) { cudaFree(cp.buf); return erc; }
+                it = g->chain_pre.emplace(key, cp).first;
+            }
+            uint8_t* buf = it->second.buf;
+            jobs[i].pre = it->second.map;
+            jobs[i].pre_sfb = buf + pieces_bytes;
+            jobs[i].pre_amax = reinterpret_cast<const uint32_t*>(buf + pieces_bytes + sfb_bytes);
+            if (std::find(pre_done.begin(), pre_done.end(), x->ptr) == pre_done.end()) {
+                pre_done.push_back(x->ptr);
+                cudaLaunchConfig_t pc{};
+                pc.gridDim = dim3(p0->m, (p0->k / lexb::MQ_STAGE_K + 31u) / 32u);      // a warp per stage
+                pc.blockDim = dim3(1024);
+                pc.stream = g->stream;
+                pc.attrs = attr;
+                pc.numAttrs = g->pdl ? 1 : 0;
+                uint32_t* amax_w = reinterpret_cast<uint32_t*>(buf + pieces_bytes + sfb_bytes);
+                if (p0->x_f32) CUDA_TRY(cudaLaunchKernelEx(&pc, lexb::matmul_q_pieces_kernel<true>, static_cast<const void*>(x->ptr), p0->k, buf, buf + pieces_bytes, amax_w));
+                else CUDA_TRY(cudaLaunchKernelEx(&pc, lexb::matmul_q_pieces_kernel<false>, static_cast<const void*>(x->ptr), p0->k, buf, buf + pieces_bytes, amax_w));
+            }
+        }
         tiles += (p->n + lexb::MQ_ROWS - 1u) / lexb::MQ_ROWS;
         jobs[i].tile_end = tiles;
     }
@@ -531,16 +582,18 @@ int launch_chain(lexb_gpu* g, const lexb_step* steps, size_t count) {
     // blocks of this kernel do not wait for one another, and there is at most one per SM
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(std::min<uint32_t>(tiles, static_cast<uint32_t>(g->prop.multiProcessorCount)));
-    cfg.blockDim = dim3(lexb::MQC_THREADS);
+    cfg.blockDim = dim3(pre ? lexb::MQC_THREADS_PRE : lexb::MQC_THREADS);
     cfg.dynamicSmemBytes = lexb::matmul_q_chain_smem_bytes(p0->stages);
     cfg.stream = g->stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = g->pdl ? 1 : 0;
-    if (p0->x_f32) CUDA_TRY(cudaLaunchKernelEx(&cfg, lexb::matmul_q_chain_kernel<true>, a));
-    else CUDA_TRY(cudaLaunchKernelEx(&cfg, lexb::matmul_q_chain_kernel<false>, a));
+    if (pre) {
+        if (p0->x_f32) CUDA_TRY(cudaLaunchKernelEx(&cfg, lexb::matmul_q_chain_kernel<true, true>, a));
+        else CUDA_TRY(cudaLaunchKernelEx(&cfg, lexb::matmul_q_chain_kernel<false, true>, a));
+    } else {
+        if (p0->x_f32) CUDA_TRY(cudaLaunchKernelEx(&cfg, lexb::matmul_q_chain_kernel<true, false>, a));
+        else CUDA_TRY(cudaLaunchKernelEx(&cfg, lexb::matmul_q_chain_kernel<false, false>, a));
+    }
     return LEXB_OK;
 }
 
@@ -604,8 +657,10 @@ int lexb_open(int device, lexb_gpu** out) {
         cudaFuncSetAttribute(lexb::matvec_fp4_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem) != cudaSuccess ||
         cudaFuncSetAttribute(lexb::matvec_fp4_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem) != cudaSuccess ||
         cudaFuncSetAttribute(lexb::matvec_fp4_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem) != cudaSuccess ||
-        cudaFuncSetAttribute(lexb::matmul_q_chain_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem) != cudaSuccess ||
-        cudaFuncSetAttribute(lexb::matmul_q_chain_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem) != cudaSuccess ||
+        cudaFuncSetAttribute(lexb::matmul_q_chain_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem) != cudaSuccess ||
+        cudaFuncSetAttribute(lexb::matmul_q_chain_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem) != cudaSuccess ||
+        cudaFuncSetAttribute(lexb::matmul_q_chain_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem) != cudaSuccess ||
+        cudaFuncSetAttribute(lexb::matmul_q_chain_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem) != cudaSuccess ||
         cudaFuncSetAttribute(lexb::matmul_q_fp4_kernel<true, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem) != cudaSuccess ||
         cudaFuncSetAttribute(lexb::matmul_q_fp4_kernel<false, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem) != cudaSuccess ||
         cudaFuncSetAttribute(lexb::matmul_q_fp4_kernel<true, true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem) != cudaSuccess ||
@@ -630,6 +685,8 @@ void lexb_close(lexb_gpu* g) {
     if (g->d_trace) cudaFree(g->d_trace);
     for (auto& e : g->chain_tables) cudaFree(e.second.dev);
     g->chain_tables.clear();
+    for (auto& e : g->chain_pre) cudaFree(e.second.buf);
+    g->chain_pre.clear();
     delete g;
 }
 

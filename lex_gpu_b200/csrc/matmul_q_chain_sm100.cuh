@@ -1,4 +1,4 @@
-// A run of matmul_q steps of one step list (same t <= 2 and k; see matmul_q_fp4_sm100.cuh) as ONE persistent
+// A run of matmul_q steps of one step list (same t <= 4 and k; see matmul_q_fp4_sm100.cuh) as ONE persistent
 // kernel.  The runtime issues a layer's dispatches as a list (`Gpu::run_launches`,
 // crates/lex-cuda/src/device.rs:650-672); consecutive steps of it often read the same activations against
 // different weights (gate and up of one MLP, the q/k/v projections).
@@ -20,8 +20,11 @@
 // joins the stream's order before its first wait for a slot; every other warp joins it before touching x, r or y.
 // The job table is never rewritten once it has been copied to the device, so it may be read before that.
 //
-// Roles (576 threads): warp 0 copy engine, warp 1 scale copies + MMAs, warps 2-5 / 6-9 scale re-lay of even /
-// odd stages, warps 10-13 epilogue, warps 14-17 the tokens' digit rows.  Two sets of accumulators (by step
+// Roles: warp 0 copy engine, warp 1 scale copies + MMAs, warps 2-5 / 6-9 scale re-lay of even / odd stages,
+// warps 10-13 epilogue, and - PRE = false, 576 threads - warps 14-17 the tokens' digit rows.  Every block derives
+// the same digit rows, which bounds the kernel from 3 tokens on; PRE = true (448 threads) has them derived once
+// per run and activation buffer by matmul_q_pieces_kernel, launched ahead, and the copy engine brings each
+// stage's digit rows and scale blocks with the weights (nothing of a run writes its activations).  Two sets of accumulators (by step
 // parity of the block's tile count) let a tile's MMAs start while the tile before is being stored.
 #pragma once
 #include "matmul_q_fp4_sm100.cuh"
@@ -36,8 +39,13 @@ struct alignas(64) MqChainJob {
     float* y;                // [m, n]
     uint32_t n;              // rows of this step's weights
     uint32_t tile_end;       // the run's tile count up to and including this step
-    uint64_t pad[3];
+    // PRE: what matmul_q_pieces_kernel wrote for this step's x
+    const uint8_t* pre_sfb;  // [k / 256][2048] scale blocks of the digit rows
+    const uint32_t* pre_amax;// [m] largest magnitudes, f32 bits
+    CUtensorMap pre;         // digit rows [8 m][k / 2]
+    uint64_t pad[1];
 };
+static_assert(sizeof(MqChainJob) % 64 == 0, "tensor maps of a job table sit on 64-byte boundaries");
 
 struct MqChainArgs {
     const MqChainJob* jobs;
@@ -59,8 +67,11 @@ __host__ __device__ constexpr uint32_t matmul_q_chain_smem_bytes(uint32_t stages
            2u * MQ_ROWS + 1024u;
 }
 
-template <bool XF32>
-__global__ void __launch_bounds__(MQC_THREADS, 1) matmul_q_chain_kernel(MqChainArgs a) {
+constexpr uint32_t MQC_THREADS_PRE = 32u * MQC_WARP_PIECE;
+
+template <bool XF32, bool PRE>
+__global__ void __launch_bounds__(PRE ? MQC_THREADS_PRE : MQC_THREADS, 1) matmul_q_chain_kernel(MqChainArgs a) {
+    constexpr uint32_t NTHREADS = PRE ? MQC_THREADS_PRE : MQC_THREADS;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw_addr = smem_u32(smem_raw);
     const uint32_t base = (raw_addr + 1023u) & ~1023u;
@@ -106,7 +117,7 @@ __global__ void __launch_bounds__(MQC_THREADS, 1) matmul_q_chain_kernel(MqChainA
         if (lane < 8u) tok_amax[lane] = 0;
         for (uint32_t b = lane; b < nbar; b += 32u) {
             uint32_t count = 1;                                                       // raw_full, empty, acc_full, ws_full
-            if (b >= S && b < 2u * S) count = MQ_SCALE_WARPS / 2u + a.m;              // prep_full
+            if (b >= S && b < 2u * S) count = MQ_SCALE_WARPS / 2u + (PRE ? 0u : a.m); // prep_full
             if (b >= 3u * S + 2u && b < 3u * S + 4u) count = 4u;                      // acc_empty: the epilogue warps
             if (b >= 3u * S + 4u + MQ_WS_SLOTS) count = MQ_SCALE_WARPS;               // ws_empty
             mbar_init(bars + 8u * b, count);
@@ -114,7 +125,7 @@ __global__ void __launch_bounds__(MQC_THREADS, 1) matmul_q_chain_kernel(MqChainA
         __syncwarp();
         fence_mbar_init();
     }
-    for (uint32_t i = tid; i < 2u * MQ_ROWS; i += MQC_THREADS) nan_rows[i] = 0;
+    for (uint32_t i = tid; i < 2u * MQ_ROWS; i += NTHREADS) nan_rows[i] = 0;
     if (warp == 1) {
         tmem_alloc(smem_u32(tmem_slot), MQ_TMEM_COLS);
         tmem_relinquish();
@@ -134,7 +145,8 @@ __global__ void __launch_bounds__(MQC_THREADS, 1) matmul_q_chain_kernel(MqChainA
             RingPos ps;
             uint32_t g_issued = 0;                    // scale-byte groups requested so far (flat over the block's tiles)
             const uint32_t TG = T * GP;
-            uint32_t gj = 0;                          // the scale bytes' own cursor: they run ahead of the codes
+            uint32_t gj = 0, g_tile = ~0u, g_n0 = 0;  // the scale bytes' own cursor (they run ahead of the codes); the job
+                                                      // table is read once per tile, not per group
             // Nothing is waited for until the rings are full.  Before its first real wait this warp joins the
             // stream's order: the warps that free the slots wait for the launch ahead, and a bounded wait must
             // not run against that launch's time.
@@ -151,13 +163,25 @@ __global__ void __launch_bounds__(MQC_THREADS, 1) matmul_q_chain_kernel(MqChainA
                 if (G >= MQ_WS_SLOTS) join_order();
                 if (!mbar_wait(ws_empty(r), wph ^ 1u, abort_flag)) return false;
                 const uint32_t i = G / GP, g = G - i * GP;
-                const uint32_t gn0 = locate(i, gj);
+                if (i != g_tile) {
+                    g_tile = i;
+                    g_n0 = locate(i, gj);
+                }
+                const uint32_t gn0 = g_n0;
                 mbar_arrive_expect_tx(ws_full(r), a.ws_pitch * MQ_ROWS);
                 tma_load_2d(ws_base + r * MQ_WS_SLOT_BYTES, &a.jobs[gj].ws, (int)(g * MQ_WS_GROUP * (MQ_STAGE_K / 16)), (int)gn0, ws_full(r));
                 return true;
             };
             bool ok = true;
             uint32_t j = 0, filled = 0;
+            uint32_t b_issued = 0, bj = 0;            // PRE: stages whose digit rows have been requested, and their cursor
+            const uint32_t b_bytes = PRE ? N * 128u : 0u;
+            uint32_t b_tile = 0, b_kb = 0;
+            const uint8_t* b_sfb = nullptr;
+            if (PRE) {
+                locate(0, bj);
+                b_sfb = a.jobs[bj].pre_sfb;
+            }
             for (uint32_t ti = 0; ti < T && ok; ti++) {
                 const uint32_t n0 = locate(ti, j);
                 for (uint32_t kb = 0; kb < KB; kb++, ps.advance(S), filled++) {
@@ -173,8 +197,25 @@ __global__ void __launch_bounds__(MQC_THREADS, 1) matmul_q_chain_kernel(MqChainA
                         while (g_issued < want && g_issued < TG && ok) ok = issue_group(g_issued++);
                         if (!ok) break;
                     }
-                    mbar_arrive_expect_tx(raw_full(s), MQ_CODE_BYTES);
+                    mbar_arrive_expect_tx(raw_full(s), MQ_CODE_BYTES + (PRE ? b_bytes + MQ_SF_BYTES : 0u));
                     tma_load_2d(codes_of(s), &a.jobs[j].wq, (int)(kb * (MQ_STAGE_K / 2)), (int)n0, raw_full(s));
+                    if (PRE) {
+                        // The digit rows are written by the launch ahead: the first ring of weights goes out
+                        // before that launch is waited for, the digit rows of those stages (slot = stage) after.
+                        if (filled + 1u == S || (ti + 1u == T && kb + 1u == KB)) join_order();
+                        if (in_order) {
+                            for (; b_issued <= filled; b_issued++, b_kb++) {
+                                if (b_kb == KB) {            // the next tile of this block (the job table is not read per stage)
+                                    b_kb = 0;
+                                    locate(++b_tile, bj);
+                                    b_sfb = a.jobs[bj].pre_sfb;
+                                }
+                                const uint32_t bs = b_issued % S;
+                                tma_load_2d(b_of(bs), &a.jobs[bj].pre, (int)(b_kb * (MQ_STAGE_K / 2)), 0, raw_full(bs));
+                                tma_load_1d(sfb_of(bs), b_sfb + (size_t)b_kb * MQ_SF_BYTES, MQ_SF_BYTES, raw_full(bs));
+                            }
+                        }
+                    }
                 }
             }
             join_order();
@@ -352,7 +393,7 @@ __global__ void __launch_bounds__(MQC_THREADS, 1) matmul_q_chain_kernel(MqChainA
                     if (KB > 1u) c += __uint_as_float(d1[pc]);
                     v += c;
                 }
-                const uint32_t te = tok_amax[set * 4u + t] >> 23;
+                const uint32_t te = (PRE ? __ldg(job.pre_amax + t) : tok_amax[set * 4u + t]) >> 23;
                 const float tscale = te >= 16u ? __uint_as_float((te - 8u) << 23) : 0.0f;
                 v = v * tscale * g;
                 if (row_nan || te == 255u) v = __uint_as_float(0x7FC00000u);
@@ -369,7 +410,7 @@ __global__ void __launch_bounds__(MQC_THREADS, 1) matmul_q_chain_kernel(MqChainA
             if (lane == 0) mbar_arrive(acc_empty(set));
 
         }
-    } else {
+    } else if (!PRE) {
         // ---------------------------------------------------------------- piece warps 14-17
         const uint32_t xw = warp - MQC_WARP_PIECE;
         const uint32_t xt = tid - 32u * MQC_WARP_PIECE;

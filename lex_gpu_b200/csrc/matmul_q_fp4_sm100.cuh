@@ -754,15 +754,18 @@ matmul_q_pieces_kernel(const void* __restrict__ x, uint32_t k, uint8_t* __restri
         uint32_t fb[8], w[8], e8;
         mq_widen<XF32>(lo, hi, fb);
         mq_digits(fb, w, e8);
+        const int q0 = 8 - (int)(te8 - e8);
+        const uint32_t grp = lane >> 1;
+        uint8_t sv[4];
+#pragma unroll
+        for (uint32_t i = 0; i < 4; i++) sv[i] = (uint8_t)mq_ue4m3_pow2(q0 - 2 * (int)(4u * (lane & 1u) + i));
 #pragma unroll
         for (uint32_t pc = 0; pc < MQ_PIECES; pc++)
             *reinterpret_cast<uint32_t*>(pieces + (size_t)(tok * MQ_PIECES + pc) * (k / 2u) + kb * 128u + 4u * lane) = w[pc];
-        const int q0 = 8 - (int)(te8 - e8);
-        const uint32_t grp = lane >> 1;
 #pragma unroll
         for (uint32_t i = 0; i < 4; i++) {
             const uint32_t pc = 4u * (lane & 1u) + i;
-            sfb[(size_t)kb * sfb_stage + mq_sfb_offset(tok * MQ_PIECES + pc, grp, wide)] = (uint8_t)mq_ue4m3_pow2(q0 - 2 * (int)pc);
+            sfb[(size_t)kb * sfb_stage + mq_sfb_offset(tok * MQ_PIECES + pc, grp, wide)] = sv[i];
         }
     }
 }

@@ -359,11 +359,12 @@ def test_a_step_list_whose_residuals_feed_each_other(gpu):
     assert gpu.status_word() == 0
 
 
-@pytest.mark.parametrize("m,xf32", [(1, False), (2, False), (2, True)])
+@pytest.mark.parametrize("m,xf32", [(1, False), (2, False), (2, True), (3, False), (4, False), (4, True)])
 def test_independent_steps_of_a_list_run_as_one_kernel(gpu, m, xf32):
     """Independent steps over the same K (the q/k/v or gate/up pattern: different row counts, some sharing
     their activations, one with a residual from outside the list) run as one persistent kernel whose blocks
-    stride over all the steps' row tiles - 160 tiles here, more than the GPU has SMs.  Every result equals the
+    stride over all the steps' row tiles - 160 tiles here, more than the GPU has SMs.  With 3 and 4 tokens the
+    run's digit rows come from one launch of the pieces kernel per activation buffer.  Every result equals the
     same step launched alone, bit for bit, and the oracle's within the operator's tolerance."""
     k = 1024
     ns = [4096, 1024, 1024, 4096, 2048, 8192]
