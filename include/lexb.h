@@ -177,6 +177,10 @@ LEXB_API int lexb_gemm_fp4_enqueue_host(lexb_gpu* gpu, const lexb_pipeline* p, c
  * over all their row tiles (the gate/up pair, q/k/v); each result is bit-identical to the step launched alone.
  * A step that depends on the run starts a new launch.  The environment variable LEXB_CHAIN=0 turns this off. */
 LEXB_API int lexb_run_launches(lexb_gpu* gpu, const lexb_step* steps, size_t nsteps, double* cpu_s, double* wall_s);
+/* How lexb_run_launches would issue this list, without launching anything: run_len_out[i] = number of steps of
+ * the kernel launch that step i belongs to (1: a launch of its own).  No counterpart in the reference; for
+ * callers and tests that want to see which steps share a launch. */
+LEXB_API int lexb_list_runs(lexb_gpu* gpu, const lexb_step* steps, size_t nsteps, uint32_t* run_len_out);
 /* Gpu::run_each_timed, crates/lex-cuda/src/device.rs:684-739: device seconds per step,
  * from events recorded between launches, no synchronise in between. */
 LEXB_API int lexb_run_each_timed(lexb_gpu* gpu, const lexb_step* steps, size_t nsteps, double* seconds_out);

@@ -1168,6 +1168,19 @@ int lexb_run_each_timed(lexb_gpu* g, const lexb_step* steps, size_t nsteps, doub
     return LEXB_OK;
 }
 
+int lexb_list_runs(lexb_gpu* g, const lexb_step* steps, size_t nsteps, uint32_t* run_len_out) {
+    int rc = use(g);
+    if (rc) return rc;
+    if ((!steps || !run_len_out) && nsteps) return fail(LEXB_ERR_ARG, "lexb_list_runs: null argument");
+    for (size_t i = 0; i < nsteps;) {
+        const size_t len = chain_run(g, steps, nsteps, i);
+        const size_t take = len ? len : 1;
+        for (size_t e = i; e < i + take; e++) run_len_out[e] = static_cast<uint32_t>(take);
+        i += take;
+    }
+    return LEXB_OK;
+}
+
 int lexb_time_launches(lexb_gpu* g, const lexb_step* steps, size_t nsteps, uint32_t reps, double* seconds_out) {
     int rc = use(g);
     if (rc) return rc;

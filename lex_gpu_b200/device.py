@@ -27,7 +27,7 @@ SYMBOLS = [
     "lexb_upload", "lexb_download", "lexb_memset", "lexb_host_alloc", "lexb_host_free", "lexb_gemm_fp4_plan",
     "lexb_pipeline_free", "lexb_pipeline_describe", "lexb_gemm_fp4_launch", "lexb_gemm_fp4_run_host",
     "lexb_gemm_fp4_enqueue_host",
-    "lexb_run_launches", "lexb_run_each_timed", "lexb_time_launches", "lexb_status_word",
+    "lexb_run_launches", "lexb_list_runs", "lexb_run_each_timed", "lexb_time_launches", "lexb_status_word",
     "lexb_selftest_bounded_wait", "lexb_dequant_fp4_f16", "lexb_shard_rows", "lexb_trace_enable", "lexb_trace_read",
     "lexb_gemm_fp4_splitk_static", "lexb_gemm_fp4_launch_gather", "lexb_silu_mul", "lexb_prefill_chunks",
     "lexb_matmul_fp4_plan",
@@ -114,6 +114,7 @@ def load_library() -> ctypes.CDLL:
     L.lexb_run_launches.argtypes = [vp, POINTER(StepStruct), sz, POINTER(c_double), POINTER(c_double)]
     L.lexb_run_each_timed.argtypes = [vp, POINTER(StepStruct), sz, POINTER(c_double)]
     L.lexb_time_launches.argtypes = [vp, POINTER(StepStruct), sz, u32, POINTER(c_double)]
+    L.lexb_list_runs.argtypes = [vp, POINTER(StepStruct), sz, POINTER(c_uint32)]
     L.lexb_status_word.argtypes = [vp, POINTER(u32)]
     L.lexb_selftest_bounded_wait.argtypes = [vp, u32]
     L.lexb_dequant_fp4_f16.argtypes = [vp, u32, u32, vp, vp, vp, vp]
@@ -380,6 +381,13 @@ class Gpu:
         out = c_double()
         _check(self._L.lexb_time_launches(self.handle, s.arr, s.n, reps, byref(out)))
         return out.value
+
+    def list_runs(self, steps: Sequence[Step]) -> list:
+        """For every step the number of steps of the launch `run_launches` would put it in (1: its own)."""
+        s = steps if isinstance(steps, StepList) else StepList(steps)
+        out = (c_uint32 * max(s.n, 1))()
+        _check(self._L.lexb_list_runs(self.handle, s.arr, s.n, out))
+        return list(out[:s.n])
 
     def status_word(self) -> int:
         out = c_uint32()

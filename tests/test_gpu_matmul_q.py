@@ -349,6 +349,7 @@ def test_a_step_list_whose_residuals_feed_each_other(gpu):
     for yb in ys:
         gpu.memset(yb, 0xEE)
     steps = [(pipe, qs[0].bind(xb, None, ys[0]))] + [(pipe_r, qs[i].bind(xb, ys[i - 1], ys[i])) for i in range(1, 5)]
+    assert gpu.list_runs(steps) == [1] * 5
     gpu.run_launches(steps)
     for i, yb in enumerate(ys):
         assert np.array_equal(gpu.download(yb, np.float32, (m, n)), alone[i]), i
@@ -388,12 +389,47 @@ def test_independent_steps_of_a_list_run_as_one_kernel(gpu, m, xf32):
         alone.append(gpu.download(ys[i], np.float32, (m, ns[i])))
         check(alone[i], O.matmul_q_x(xs[which_x[i]], *sets[i], r=r_host if i == 4 else None), rel_tol=3e-2 if xf32 else 5e-3)
     steps = L.StepList(list(zip(pipes, binds)))
+    assert gpu.list_runs(steps) == [6] * 6
     for _ in range(2):
         for yb in ys:
             gpu.memset(yb, 0xEE)
         gpu.run_launches(steps)
         for i, yb in enumerate(ys):
             assert np.array_equal(gpu.download(yb, np.float32, (m, ns[i])), alone[i]), i
+    assert gpu.status_word() == 0
+
+
+def test_which_steps_share_a_launch(gpu):
+    """The rules by which consecutive steps of a list become one launch, seen through lexb_list_runs."""
+    m, n, k = 1, 2048, 2048
+    x = inputs.make_x(m, k, seed_base=530)
+    xb, x2b = gpu.upload(x), gpu.upload(x)
+    qs = [L.QBuf(gpu, *inputs.make_weights(n, k, seed_base=531, copy=c)) for c in range(4)]
+    ya, yb = gpu.alloc(4 * m * n), gpu.alloc(4 * m * n)
+    one = gpu.plan_matmul_fp4(m, n, k, k_splits=1)
+    # gate/up pairs: every second step overwrites an output of the run before it
+    pairs = [(one, q.bind(xb, None, (ya, yb)[i % 2])) for i, q in enumerate(qs)]
+    assert gpu.list_runs(pairs) == [2, 2, 2, 2]
+    # a K split over blocks (the stand-alone plan of a small n), weights that may change, more than 4 tokens,
+    # another K: launches of their own
+    split = gpu.plan_matmul_fp4(m, n, k, k_splits=2)
+    assert gpu.list_runs([(split, qs[0].bind(xb, None, ya)), (split, qs[1].bind(xb, None, yb))]) == [1, 1]
+    loose = gpu.plan_matmul_fp4(m, n, k, k_splits=1, weights_may_change=True)
+    assert gpu.list_runs([(loose, qs[0].bind(xb, None, ya)), (one, qs[1].bind(xb, None, yb))]) == [1, 1]
+    x5 = gpu.upload(inputs.make_x(5, k, seed_base=532))
+    y5a, y5b = gpu.alloc(4 * 5 * n), gpu.alloc(4 * 5 * n)
+    five = gpu.plan_matmul_fp4(5, n, k, k_splits=1)
+    assert gpu.list_runs([(five, qs[0].bind(x5, None, y5a)), (five, qs[1].bind(x5, None, y5b))]) == [1, 1]
+    # another activation buffer is fine; a step that writes the x of the step before it is not
+    assert gpu.list_runs([(one, qs[0].bind(xb, None, ya)), (one, qs[1].bind(x2b, None, yb))]) == [2, 2]
+    sq = gpu.plan_matmul_fp4(m, n, k, x_half=False, k_splits=1)          # f32 x: y can be bound as x (n == k)
+    xf = gpu.upload(x.astype(np.float32))
+    assert gpu.list_runs([(sq, qs[0].bind(ya, None, yb)), (sq, qs[1].bind(xf, None, ya))]) == [1, 1]
+    assert gpu.list_runs([(sq, qs[0].bind(xf, None, yb)), (sq, qs[1].bind(xf, None, ya))]) == [2, 2]
+    # gemm_fp4 steps between them end a run
+    gem = gpu.plan_gemm_fp4(m, n, k)
+    mixed = [(one, qs[0].bind(xb, None, ya)), (gem, qs[1].bind(xb, None, yb)), (one, qs[2].bind(xb, None, ya))]
+    assert gpu.list_runs(mixed) == [1, 1, 1]
     assert gpu.status_word() == 0
 
 
@@ -411,6 +447,7 @@ def test_a_chain_whose_steps_feed_each_other(gpu):
     pipe = gpu.plan_matmul_fp4(m, n, n, x_half=False)
     bufs = [gpu.upload(x0)] + [gpu.alloc(4 * m * n) for _ in sets]
     steps = L.StepList([(pipe, q.bind(bufs[i], None, bufs[i + 1])) for i, q in enumerate(qs)])
+    assert gpu.list_runs(steps) == [1] * 6
     for _ in range(3):                                                            # repeated: counters and rings start clean each time
         for b in bufs[1:]:
             gpu.memset(b, 0xEE)
