@@ -481,7 +481,12 @@ size_t chain_run(const lexb_gpu* g, const lexb_step* steps, size_t nsteps, size_
     };
     size_t len = 1;
     while (i + len < nsteps && len < 4096 && chain_member(g, steps[i + len], steps[i].pipeline) && !x_written_in_run(i + len, len)) len++;
-    return len >= 2 ? len : 0;
+    if (len >= 2) return len;
+    // a single step with more row tiles than SMs: the persistent kernel takes them without a second wave of
+    // block set-ups (n = 28672: 224 tiles)
+    static const bool single = env_u32("LEXB_CHAIN_SINGLE", 1) != 0;
+    const uint32_t tiles = (steps[i].pipeline->n + lexb::MQ_ROWS - 1u) / lexb::MQ_ROWS;
+    return single && tiles > static_cast<uint32_t>(g->prop.multiProcessorCount) ? 1 : 0;
 }
 
 int launch_chain(lexb_gpu* g, const lexb_step* steps, size_t count) {

@@ -399,6 +399,25 @@ def test_independent_steps_of_a_list_run_as_one_kernel(gpu, m, xf32):
     assert gpu.status_word() == 0
 
 
+@pytest.mark.parametrize("m", [1, 4])
+def test_a_step_with_more_row_tiles_than_sms(gpu, m):
+    """n = 28672 (224 row tiles): issued in a list, the step runs on the persistent kernel, whose blocks take
+    the tiles b, b + grid; the result is that of the stand-alone launch (one block per tile), bit for bit."""
+    n, k = 28672, 1024
+    x, wq, ws, wg = inputs.make_case(m, n, k, seed_base=540 + m)
+    q = L.QBuf(gpu, wq, ws, wg)
+    xb, ya, yb = gpu.upload(x), gpu.alloc(4 * m * n), gpu.alloc(4 * m * n)
+    pipe = gpu.plan_matmul_fp4(m, n, k)
+    assert pipe.describe().k_splits == 1
+    gpu.run(pipe, q.bind(xb, None, ya))
+    gpu.memset(yb, 0xEE)
+    gpu.run_launches([(pipe, q.bind(xb, None, yb))])
+    alone, listed = gpu.download(ya, np.float32, (m, n)), gpu.download(yb, np.float32, (m, n))
+    assert np.array_equal(alone, listed)
+    check(listed, O.matmul_q_x(x, wq, ws, wg))
+    assert gpu.status_word() == 0
+
+
 def test_which_steps_share_a_launch(gpu):
     """The rules by which consecutive steps of a list become one launch, seen through lexb_list_runs."""
     m, n, k = 1, 2048, 2048
