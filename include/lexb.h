@@ -106,7 +106,9 @@ LEXB_API int lexb_open(int device, lexb_gpu** out);
 LEXB_API void lexb_close(lexb_gpu* gpu);
 /* Gpu::info, crates/lex-cuda/src/device.rs:424-458 */
 LEXB_API int lexb_info(lexb_gpu* gpu, lexb_device_info* out);
-/* Launches go to the gpu's own stream unless a caller-owned CUDA stream is set (null = own). */
+/* Launches go to the gpu's own stream (non-blocking: it does not synchronise with the legacy default stream)
+ * unless a caller-owned CUDA stream is set.  null = the own stream again; a caller that works on the legacy
+ * default stream passes cudaStreamLegacy ((cudaStream_t)0x1), not null. */
 LEXB_API int lexb_set_stream(lexb_gpu* gpu, void* cuda_stream);
 LEXB_API void* lexb_get_stream(lexb_gpu* gpu);
 /* cuCtxSynchronize in Gpu::run_launches, crates/lex-cuda/src/device.rs:668-671 */

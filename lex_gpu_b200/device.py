@@ -270,7 +270,14 @@ class Gpu:
         return self.info().name.decode()
 
     def set_stream(self, cuda_stream: Optional[int]) -> None:
-        _check(self._L.lexb_set_stream(self.handle, c_void_p(cuda_stream or 0)))
+        """None: the library's own stream.  An integer is a CUDA stream handle as torch gives it
+        (`torch.cuda.current_stream().cuda_stream`); 0, torch's default stream, is passed on as
+        cudaStreamLegacy (0x1), because a null handle means the own stream to the library."""
+        if cuda_stream is None:
+            h = 0
+        else:
+            h = cuda_stream or 1
+        _check(self._L.lexb_set_stream(self.handle, c_void_p(h)))
 
     def sync(self) -> None:
         _check(self._L.lexb_sync(self.handle))

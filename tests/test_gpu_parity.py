@@ -358,6 +358,31 @@ def test_run_host_copies_in_and_out(gpu):
     check(hy.array(np.float32, (m, n)).copy(), O.gemm_fp4(x, wq, ws, wg))
 
 
+def test_torch_default_stream_is_passed_as_the_legacy_stream(gpu):
+    """torch's default stream has the handle 0, which means "the library's own stream" to lexb_set_stream: the
+    binding passes cudaStreamLegacy instead, so that launches are ordered with torch's work on that stream.
+    A torch fill, the launch and a torch read follow one another with no synchronise in between."""
+    import torch
+    m, n, k = 64, 512, 1024
+    x, wq, ws, wg = inputs.make_case(m, n, k, seed_base=14)
+    q = L.QBuf(gpu, wq, ws, wg)
+    xb = gpu.upload(x)
+    pipe = gpu.plan_gemm_fp4(m, n, k)
+    assert torch.cuda.current_stream().cuda_stream == 0
+    gpu.set_stream(torch.cuda.current_stream().cuda_stream)
+    try:
+        assert gpu._L.lexb_get_stream(gpu.handle) == 1
+        y = torch.empty((m, n), dtype=torch.float32, device="cuda")
+        for _ in range(3):
+            y.fill_(float("nan"))
+            gpu.run(pipe, q.bind(xb, None, gpu.wrap_tensor(y)))
+            got = y.clone()                    # torch's copy on the default stream, ordered after the launch
+            torch.cuda.synchronize()
+            check(got.cpu().numpy(), O.gemm_fp4(x, wq, ws, wg))
+    finally:
+        gpu.set_stream(None)
+
+
 def test_enqueue_host_on_two_streams(gpu):
     """Double-buffered chunks: two streams, two sets of staging buffers, no wait between the chunks."""
     import torch
