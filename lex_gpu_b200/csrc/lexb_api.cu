@@ -526,6 +526,13 @@ int launch_chain(lexb_gpu* g, const lexb_step* steps, size_t count) {
             const auto key = std::make_tuple(static_cast<const void*>(x->ptr), p0->m, p0->k, p0->x_f32 != 0, g->stream);
             auto it = g->chain_pre.find(key);
             if (it == g->chain_pre.end()) {
+                if (g->chain_pre.size() >= 256 && pre_done.empty()) {
+                    // activation buffers come and go: start over (buffers of launches in flight are freed after them;
+                    // not in the middle of a run, whose earlier jobs point into these buffers)
+                    CUDA_TRY(cudaDeviceSynchronize());
+                    for (auto& e : g->chain_pre) cudaFree(e.second.buf);
+                    g->chain_pre.clear();
+                }
                 lexb_gpu::ChainPre cp{};
                 const size_t total = pieces_bytes + sfb_bytes + 4u * lexb::MQ_MAX_TOKENS;
                 CUDA_TRY(cudaMalloc(&cp.buf, total));
