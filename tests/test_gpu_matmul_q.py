@@ -399,6 +399,55 @@ def test_independent_steps_of_a_list_run_as_one_kernel(gpu, m, xf32):
     assert gpu.status_word() == 0
 
 
+@pytest.mark.parametrize("m", [2, 4])
+def test_a_run_with_negative_and_nan_scale_bytes_and_bad_tokens(gpu, m):
+    """The persistent kernel keeps its own NaN flags and token maxima per accumulator set: steps whose weights
+    hold negative scales and NaN bytes (every second step, so that flagged and clean tiles alternate on a block),
+    an activation buffer with an infinite token and one of zeros, each compared bit for bit (NaNs by position)
+    with the step launched alone."""
+    n, k = 1024, 2048
+    rng = np.random.Generator(np.random.PCG64(550 + m))
+    x_ok = inputs.make_x(m, k, seed_base=551)
+    x_inf = x_ok.copy()
+    x_inf[m - 1, 77] = np.float16(-np.inf)
+    x_zero = np.zeros_like(x_ok)
+    xbs = [gpu.upload(v) for v in (x_ok, x_inf, x_zero)]
+    which_x = [0, 1, 0, 2, 0, 0, 1, 0, 0, 2, 0, 0] * 2              # 24 steps x 8 tiles: more than one tile per block
+    sets = []
+    for c in range(len(which_x)):
+        wq, ws, wg = inputs.make_weights(n, k, seed_base=552, copy=c)
+        ws = ws.copy()
+        if c % 2 == 1:
+            neg = rng.random(ws.shape) < 0.3
+            ws[neg] |= 0x80                                           # negative scales
+            ws[rng.integers(0, n, 9), rng.integers(0, ws.shape[1], 9)] = 0x7F
+            ws[rng.integers(0, n, 9), rng.integers(0, ws.shape[1], 9)] = 0xFF
+        sets.append((wq, ws, wg))
+    qs = [L.QBuf(gpu, *w) for w in sets]
+    pipe = gpu.plan_matmul_fp4(m, n, k, k_splits=1)
+    ys = [gpu.alloc(4 * m * n) for _ in sets]
+    binds = [q.bind(xbs[which_x[i]], None, ys[i]) for i, q in enumerate(qs)]
+    alone = []
+    for i in range(len(sets)):
+        gpu.run(pipe, binds[i])
+        gpu.sync()
+        alone.append(gpu.download(ys[i], np.float32, (m, n)))
+    assert np.isnan(alone[1]).any() and not np.isnan(alone[2]).any() and np.isnan(alone[1][m - 1]).all()
+    assert (alone[3] == 0).all() or np.isnan(alone[3]).any()
+    steps = L.StepList([(pipe, b) for b in binds])
+    assert gpu.list_runs(steps) == [len(sets)] * len(sets)
+    for yb in ys:
+        gpu.memset(yb, 0xEE)
+    gpu.run_launches(steps)
+    for i, yb in enumerate(ys):
+        got = gpu.download(yb, np.float32, (m, n))
+        assert np.array_equal(np.isnan(got), np.isnan(alone[i])), i
+        assert np.array_equal(np.nan_to_num(got), np.nan_to_num(alone[i])), i
+    want = O.matmul_q_x(x_ok, *sets[2])
+    check(alone[2], want)
+    assert gpu.status_word() == 0
+
+
 @pytest.mark.parametrize("m", [1, 4])
 def test_a_step_with_more_row_tiles_than_sms(gpu, m):
     """n = 28672 (224 row tiles): issued in a list, the step runs on the persistent kernel, whose blocks take
