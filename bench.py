@@ -371,10 +371,10 @@ def run_ours(args):
         #           before it - runs of two, the gate/up pair of one MLP (the same x, two weight matrices);
         #  "independent": every step has its own output - one run over the whole list (an upper bound: the
         #           q/k/v + gate/up + experts pattern with nothing in between).
-        def list_seconds(n_outputs):
+        def list_seconds(n_outputs, pipe=p_mq):
             outs_t = [torch.empty((mm, n_local), dtype=torch.float32, device=dev) for _ in range(n_outputs)]
             outs = [gpu.wrap_tensor(t) for t in outs_t]
-            lst = [(p_mq, [xs] + list(weights[i % COPIES][1]) + [outs[i % n_outputs]]) for i in range(mv_steps)]
+            lst = [(pipe, [xs] + list(weights[i % COPIES][1]) + [outs[i % n_outputs]]) for i in range(mv_steps)]
             gpu.run_launches(lst[:max(args.warmup, 8)])
             lst = L.StepList(lst)                 # marshalled outside the timed region
             gpu.run_launches(lst)                 # (job tables of the runs are kept by content from here on)
@@ -399,6 +399,14 @@ def run_ours(args):
 
         per_q = list_seconds(2)
         per_q_run = list_seconds(mv_steps)
+        # A shard with few row tiles is planned with K split over blocks, which fills the GPU for a launch on its
+        # own but keeps the step out of runs; planned with one K range per block the same lists run as runs.
+        unsplit = None
+        if p_mq.describe().k_splits > 1:
+            p_one = gpu.plan_matmul_fp4(mm, n_local, K, k_splits=1)
+            a2, ar = list_seconds(2, p_one), list_seconds(mv_steps, p_one)
+            unsplit = {"plan": "k_splits = 1", "runs_of_two": {"us_per_launch": a2 * 1e6, "gbs_weight_bytes": wbytes_local / a2 / 1e9 * world},
+                       "one_run": {"us_per_launch": ar * 1e6, "gbs_weight_bytes": wbytes_local / ar / 1e9 * world}}
         matvec[f"m{mm}"]["matmul_q_x"] = {
             "kernel": p_mq.describe().entry.decode(), "gbs_weight_bytes": wbytes_local / per_q / 1e9 * world,
             "us_per_launch": per_q * 1e6,
@@ -406,7 +414,8 @@ def run_ours(args):
             "us_per_launch_issued_one_by_one": per_q_single * 1e6, "roofline": hbm(per_q),
             "independent_steps": {"issued_as": "one step list, every step with its own output: one run",
                                   "gbs_weight_bytes": wbytes_local / per_q_run / 1e9 * world,
-                                  "us_per_launch": per_q_run * 1e6, "roofline": hbm(per_q_run)}}
+                                  "us_per_launch": per_q_run * 1e6, "roofline": hbm(per_q_run)},
+            "k_splits": p_mq.describe().k_splits, "lists_planned_unsplit": unsplit}
 
     # ---- all-gather variant (N > 1): y shards -> [N][m][n/N] on every rank
     allgather = None
