@@ -492,7 +492,7 @@ size_t chain_run(const lexb_gpu* g, const lexb_step* steps, size_t nsteps, size_
 int launch_chain(lexb_gpu* g, const lexb_step* steps, size_t count) {
     const lexb_pipeline* p0 = steps[0].pipeline;
     std::vector<lexb::MqChainJob> jobs(count);
-    uint32_t tiles = 0;
+    uint32_t tiles = 0, jobs_first_tiles = 0;        // (the latter: every step's tile count if they all agree, else 0)
     int rc;
     const bool pre = p0->m >= chain_pre_min_m();
     std::vector<const void*> pre_done;               // activation buffers whose digit rows this run has asked for
@@ -560,7 +560,10 @@ int launch_chain(lexb_gpu* g, const lexb_step* steps, size_t count) {
                 else CUDA_TRY(cudaLaunchKernelEx(&pc, lexb::matmul_q_pieces_kernel<false>, static_cast<const void*>(x->ptr), p0->k, buf, buf + pieces_bytes, amax_w));
             }
         }
-        tiles += (p->n + lexb::MQ_ROWS - 1u) / lexb::MQ_ROWS;
+        const uint32_t job_tiles = (p->n + lexb::MQ_ROWS - 1u) / lexb::MQ_ROWS;
+        if (i == 0) jobs_first_tiles = job_tiles;
+        else if (job_tiles != jobs_first_tiles) jobs_first_tiles = 0;
+        tiles += job_tiles;
         jobs[i].tile_end = tiles;
     }
     const size_t table_bytes = sizeof(lexb::MqChainJob) * count;
@@ -589,6 +592,7 @@ int launch_chain(lexb_gpu* g, const lexb_step* steps, size_t count) {
     a.jobs = d_jobs;
     a.n_jobs = static_cast<uint32_t>(count);
     a.n_tiles = tiles;
+    a.tiles_per_job = jobs_first_tiles;
     a.m = p0->m; a.k = p0->k; a.stages = p0->stages; a.ws_pitch = p0->ws_pitch;
     a.status = g->d_status;
     // blocks of this kernel do not wait for one another, and there is at most one per SM

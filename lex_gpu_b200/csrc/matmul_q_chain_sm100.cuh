@@ -50,6 +50,7 @@ static_assert(sizeof(MqChainJob) % 64 == 0, "tensor maps of a job table sit on 6
 struct MqChainArgs {
     const MqChainJob* jobs;
     uint32_t n_jobs, n_tiles;
+    uint32_t tiles_per_job;  // every step has this many row tiles, or 0: they differ and the table is walked
     uint32_t m, k, stages, ws_pitch;
     uint32_t* status;
 };
@@ -108,6 +109,10 @@ __global__ void __launch_bounds__(PRE ? MQC_THREADS_PRE : MQC_THREADS, 1) matmul
     // step and first row of the block's i-th tile; `j` is the caller's cursor into the steps (tiles ascend)
     auto locate = [&](uint32_t i, uint32_t& j) -> uint32_t {
         const uint32_t tile = blockIdx.x + i * gridDim.x;
+        if (a.tiles_per_job) {       // (a walk is one trip to L2 per step passed: with few tiles per step that is most of a tile's time)
+            j = tile / a.tiles_per_job;
+            return (tile - j * a.tiles_per_job) * MQ_ROWS;
+        }
         while (j + 1u < a.n_jobs && tile >= a.jobs[j].tile_end) j++;
         return (tile - (j ? a.jobs[j - 1u].tile_end : 0u)) * MQ_ROWS;
     };
