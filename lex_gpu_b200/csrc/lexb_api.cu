@@ -429,8 +429,8 @@ int launch_one(lexb_gpu* g, const lexb_pipeline* p, const lexb_buffer* x, const 
 }
 
 // Consecutive steps of a list that can run as one persistent kernel (matmul_q_chain_sm100.cuh): block-scaled
-// matmul_q with in-block digit rows, one K range per block, the same t, k and activation type (n may differ),
-// weights declared constant.  LEXB_CHAIN=0 turns it off.
+// matmul_q of up to 4 tokens planned for in-block digit rows and the full ring, one K range per block, the same
+// t, k and activation type (n may differ), weights declared constant.  LEXB_CHAIN=0 turns it off.
 // (two accumulator sets of 2 x 32 columns: 4 tokens x 8 digit rows)
 static uint32_t chain_max_m() {
     static const uint32_t v = env_u32("LEXB_CHAIN_MAX_M", 4);

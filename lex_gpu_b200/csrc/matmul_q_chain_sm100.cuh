@@ -9,10 +9,10 @@
 // tiles b, b + grid, b + 2 grid, ...: every SM has work whatever the steps' tile counts are (136 tiles of
 // n = 17408 leave 12 of 148 SMs idle in a launch of their own, 224 tiles of n = 28672 need two waves), and a
 // block's rings never drain: the copy engine is into the next tile's weights while this tile's last stages
-// are multiplied and stored.  The host only puts steps
-// into a run whose x is not written by an earlier step of the run (it compares the buffers), so no step waits
-// for another block's stores; a step that does read an earlier step's output starts a new launch, and the
-// stream orders it as usual.  (A version that waited inside the kernel - every block counts itself in after
+// are multiplied and stored.  Nothing orders the tiles of different blocks, so the host only puts a step into a
+// run if nothing it reads (x, r) is written, and nothing it writes (y) read or written, by a step already in the
+// run (it compares the buffers' address ranges); a step that does depend on the run starts a new launch, and
+// the stream orders it as usual.  (A version that waited inside the kernel - every block counts itself in after
 // storing a step, the next step's x is read once the count is complete - was measured: 14.3 us per step
 // against 12.2 us for separate launches, because nothing can be prefetched past the wait but one ring.)
 // Blocks never wait for one another.  The weights are declared constant by every step of a run, so the copy
@@ -24,8 +24,9 @@
 // warps 10-13 epilogue, and - PRE = false, 576 threads - warps 14-17 the tokens' digit rows.  Every block derives
 // the same digit rows, which bounds the kernel from 3 tokens on; PRE = true (448 threads) has them derived once
 // per run and activation buffer by matmul_q_pieces_kernel, launched ahead, and the copy engine brings each
-// stage's digit rows and scale blocks with the weights (nothing of a run writes its activations).  Two sets of accumulators (by step
-// parity of the block's tile count) let a tile's MMAs start while the tile before is being stored.
+// stage's digit rows and scale blocks with the weights (nothing of a run writes its activations).  Two sets of
+// accumulators (by the parity of the block's tile count) let a tile's MMAs start while the tile before is being
+// stored.
 #pragma once
 #include "matmul_q_fp4_sm100.cuh"
 
