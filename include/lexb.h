@@ -172,7 +172,7 @@ LEXB_API int lexb_gemm_fp4_enqueue_host(lexb_gpu* gpu, const lexb_pipeline* p, c
                                         const lexb_buffer* r_or_null, lexb_buffer* y_dev, void* y_host);
 /* Gpu::run_launches, crates/lex-cuda/src/device.rs:650-672: all steps, one synchronise;
  * cpu_s = host time to enqueue, wall_s = host time until the device is idle.
- * The results are those of the steps run one after another.  Consecutive lexb_matmul_fp4_plan steps of t <= 4
+ * The results are those of the steps run one after another.  Consecutive lexb_matmul_fp4_plan steps of t <= 8
  * tokens planned with k_splits = 1 and constant weights (no LEXB_SCHED_WEIGHTS_MAY_CHANGE), with the same t, k
  * and activation type, of which none reads or overwrites a buffer that an earlier one of them touches (x and r
  * not written, y neither read nor written: the address ranges are compared), are run as ONE persistent kernel

@@ -429,12 +429,12 @@ int launch_one(lexb_gpu* g, const lexb_pipeline* p, const lexb_buffer* x, const 
 }
 
 // Consecutive steps of a list that can run as one persistent kernel (matmul_q_chain_sm100.cuh): block-scaled
-// matmul_q of up to 4 tokens planned for in-block digit rows and the full ring, one K range per block, the same
+// matmul_q of up to 8 tokens with the default ring depth and digit-row source of their token count, one K range per block, the same
 // t, k and activation type (n may differ), weights declared constant.  LEXB_CHAIN=0 turns it off.
-// (two accumulator sets of 2 x 32 columns: 4 tokens x 8 digit rows)
+// (two accumulator sets of 2 x 64 columns: 8 tokens x 8 digit rows)
 static uint32_t chain_max_m() {
-    static const uint32_t v = env_u32("LEXB_CHAIN_MAX_M", 4);
-    return v > 4u ? 4u : v;
+    static const uint32_t v = env_u32("LEXB_CHAIN_MAX_M", lexb::MQC_MAX_TOKENS);
+    return v > lexb::MQC_MAX_TOKENS ? lexb::MQC_MAX_TOKENS : v;
 }
 // From this many tokens on the digit rows of a run come from matmul_q_pieces_kernel, not from piece warps in every block.
 static uint32_t chain_pre_min_m() {
@@ -443,10 +443,11 @@ static uint32_t chain_pre_min_m() {
 }
 bool chain_member(const lexb_gpu* g, const lexb_step& s, const lexb_pipeline* first) {
     const lexb_pipeline* p = s.pipeline;
-    if (!p || !s.buffers || p->gpu != g || p->kernel != KERNEL_MATMUL_Q || p->mq_pre || p->m > chain_max_m() || p->k_splits != 1u) return false;
+    if (!p || !s.buffers || p->gpu != g || p->kernel != KERNEL_MATMUL_Q || p->m > chain_max_m() || p->k_splits != 1u) return false;
+    if (p->mq_pre != (p->m > 4u)) return false;                                      // (a plan forced the other way by LEXB_MQ_PRE stays as planned)
     if (!(p->flags & 1u) || s.nbuffers != (p->residual ? 6u : 5u)) return false;
     if ((p->k / lexb::MQ_STAGE_K) % lexb::MQ_WS_GROUP == 1u) return false;          // a scale-byte group of one stage is seen by half the scale warps only
-    if (p->stages != lexb::MQ_MAX_STAGES || lexb::matmul_q_chain_smem_bytes(p->stages) > g->smem_optin) return false;
+    if (p->stages != (p->m <= 4u ? lexb::MQ_MAX_STAGES : 7u) || lexb::matmul_q_chain_smem_bytes(p->stages, p->m) > g->smem_optin) return false;
     return !first || (p->m == first->m && p->k == first->k && p->x_f32 == first->x_f32 && p->stages == first->stages &&
                       p->ws_pitch == first->ws_pitch);
 }
@@ -494,7 +495,7 @@ int launch_chain(lexb_gpu* g, const lexb_step* steps, size_t count) {
     std::vector<lexb::MqChainJob> jobs(count);
     uint32_t tiles = 0, jobs_first_tiles = 0;        // (the latter: every step's tile count if they all agree, else 0)
     int rc;
-    const bool pre = p0->m >= chain_pre_min_m();
+    const bool pre = p0->m >= chain_pre_min_m() || p0->m > 4u;       // (the piece warps of a block take up to 4 tokens)
     std::vector<const void*> pre_done;               // activation buffers whose digit rows this run has asked for
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
@@ -599,7 +600,7 @@ int launch_chain(lexb_gpu* g, const lexb_step* steps, size_t count) {
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(std::min<uint32_t>(tiles, static_cast<uint32_t>(g->prop.multiProcessorCount)));
     cfg.blockDim = dim3(pre ? lexb::MQC_THREADS_PRE : lexb::MQC_THREADS);
-    cfg.dynamicSmemBytes = lexb::matmul_q_chain_smem_bytes(p0->stages);
+    cfg.dynamicSmemBytes = lexb::matmul_q_chain_smem_bytes(p0->stages, p0->m);
     cfg.stream = g->stream;
     cfg.attrs = attr;
     cfg.numAttrs = g->pdl ? 1 : 0;

@@ -1,4 +1,4 @@
-// A run of matmul_q steps of one step list (same t <= 4 and k; see matmul_q_fp4_sm100.cuh) as ONE persistent
+// A run of matmul_q steps of one step list (same t <= 8 and k; see matmul_q_fp4_sm100.cuh) as ONE persistent
 // kernel.  The runtime issues a layer's dispatches as a list (`Gpu::run_launches`,
 // crates/lex-cuda/src/device.rs:650-672); consecutive steps of it often read the same activations against
 // different weights (gate and up of one MLP, the q/k/v projections).
@@ -60,12 +60,13 @@ constexpr uint32_t MQC_PIECE_WARPS = 4;
 constexpr uint32_t MQC_WARP_EPI = 2u + MQ_SCALE_WARPS;                 // 10
 constexpr uint32_t MQC_WARP_PIECE = MQC_WARP_EPI + 4u;                 // 14
 constexpr uint32_t MQC_THREADS = 32u * (MQC_WARP_PIECE + MQC_PIECE_WARPS);
-constexpr uint32_t MQC_TMEM_SET = 64;                                  // columns per accumulator set (two accumulators of 32)
-constexpr uint32_t MQC_TMEM_SFA = 128;
-constexpr uint32_t MQC_TMEM_SFB = MQC_TMEM_SFA + 16u * MQ_MAX_STAGES;
+// Tensor memory: two sets of two accumulators of 32 columns (up to 4 tokens) or 64 (up to 8), then the scale
+// blocks of A and of B, 16 columns per stage each: 128 + 256 or 256 + 256 of the 512 columns.
+__host__ __device__ constexpr uint32_t matmul_q_chain_acc_cols(uint32_t m) { return m <= 4u ? 32u : 64u; }
+constexpr uint32_t MQC_MAX_TOKENS = 8;
 
-__host__ __device__ constexpr uint32_t matmul_q_chain_smem_bytes(uint32_t stages) {
-    return stages * matmul_q_stage_bytes(4) + MQ_WS_SLOTS * MQ_WS_SLOT_BYTES + (3u * stages + 4u + 2u * MQ_WS_SLOTS) * 8u + 64u +
+__host__ __device__ constexpr uint32_t matmul_q_chain_smem_bytes(uint32_t stages, uint32_t m) {
+    return stages * matmul_q_stage_bytes(m <= 4u ? 4u : 8u) + MQ_WS_SLOTS * MQ_WS_SLOT_BYTES + (3u * stages + 4u + 2u * MQ_WS_SLOTS) * 8u + 64u +
            2u * MQ_ROWS + 1024u;
 }
 
@@ -80,10 +81,13 @@ __global__ void __launch_bounds__(PRE ? MQC_THREADS_PRE : MQC_THREADS, 1) matmul
     uint8_t* const smem = smem_raw + (base - raw_addr);
 
     const uint32_t S = a.stages;
-    const uint32_t STAGE_BYTES = matmul_q_stage_bytes(4);
+    const uint32_t MB = a.m <= 4u ? 4u : 8u;                               // the token count the stages are sized for
+    const uint32_t STAGE_BYTES = matmul_q_stage_bytes(MB);
+    const uint32_t ACC = matmul_q_chain_acc_cols(a.m), TMEM_SET = 2u * ACC;
+    const uint32_t TMEM_SFA = 2u * TMEM_SET, TMEM_SFB = TMEM_SFA + 16u * MQ_MAX_STAGES;
     auto codes_of = [&](uint32_t s) { return base + s * STAGE_BYTES; };
     auto b_of = [&](uint32_t s) { return codes_of(s) + MQ_CODE_BYTES; };
-    auto sfa_of = [&](uint32_t s) { return b_of(s) + matmul_q_b_bytes(4); };
+    auto sfa_of = [&](uint32_t s) { return b_of(s) + matmul_q_b_bytes(MB); };
     auto sfb_of = [&](uint32_t s) { return sfa_of(s) + MQ_SF_BYTES; };
     const uint32_t ws_base = base + S * STAGE_BYTES;
     const uint32_t bars = ws_base + MQ_WS_SLOTS * MQ_WS_SLOT_BYTES;
@@ -262,8 +266,8 @@ __global__ void __launch_bounds__(PRE ? MQC_THREADS_PRE : MQC_THREADS, 1) matmul
                 }
                 tc_fence_after_sync();
                 const uint32_t a_lo = umma_desc_lo(codes_of(s)), b_lo = umma_desc_lo(b_of(s));
-                const uint32_t sfa_t = tmem_base + MQC_TMEM_SFA + 16u * s, sfb_t = tmem_base + MQC_TMEM_SFB + 16u * s;
-                const uint32_t d = tmem_base + set * MQC_TMEM_SET + ((kb & 1u) ? 32u : 0u);
+                const uint32_t sfa_t = tmem_base + TMEM_SFA + 16u * s, sfb_t = tmem_base + TMEM_SFB + 16u * s;
+                const uint32_t d = tmem_base + set * TMEM_SET + ((kb & 1u) ? ACC : 0u);
                 if (elect_one()) {
 #pragma unroll
                     for (uint32_t q = 0; q < 4; q++) {
@@ -389,8 +393,8 @@ __global__ void __launch_bounds__(PRE ? MQC_THREADS_PRE : MQC_THREADS, 1) matmul
             const bool row_nan = nan_rows[set * MQ_ROWS + row] != 0;
             for (uint32_t t = 0; t < a.m; t++) {
                 uint32_t d0[8], d1[8];
-                tmem_ld_32x32b_x8(lane_base + set * MQC_TMEM_SET + 8u * t, d0);
-                if (KB > 1u) tmem_ld_32x32b_x8(lane_base + set * MQC_TMEM_SET + 32u + 8u * t, d1);
+                tmem_ld_32x32b_x8(lane_base + set * TMEM_SET + 8u * t, d0);
+                if (KB > 1u) tmem_ld_32x32b_x8(lane_base + set * TMEM_SET + ACC + 8u * t, d1);
                 tmem_ld_wait();
                 float v = 0.0f;
 #pragma unroll

@@ -360,11 +360,12 @@ def test_a_step_list_whose_residuals_feed_each_other(gpu):
     assert gpu.status_word() == 0
 
 
-@pytest.mark.parametrize("m,xf32", [(1, False), (2, False), (2, True), (3, False), (4, False), (4, True)])
+@pytest.mark.parametrize("m,xf32", [(1, False), (2, False), (2, True), (3, False), (4, False), (4, True),
+                                    (5, False), (7, True), (8, False)])
 def test_independent_steps_of_a_list_run_as_one_kernel(gpu, m, xf32):
     """Independent steps over the same K (the q/k/v or gate/up pattern: different row counts, some sharing
     their activations, one with a residual from outside the list) run as one persistent kernel whose blocks
-    stride over all the steps' row tiles - 160 tiles here, more than the GPU has SMs.  With 3 and 4 tokens the
+    stride over all the steps' row tiles - 160 tiles here, more than the GPU has SMs.  From 3 tokens on the
     run's digit rows come from one launch of the pieces kernel per activation buffer.  Every result equals the
     same step launched alone, bit for bit, and the oracle's within the operator's tolerance."""
     k = 1024
@@ -399,7 +400,7 @@ def test_independent_steps_of_a_list_run_as_one_kernel(gpu, m, xf32):
     assert gpu.status_word() == 0
 
 
-@pytest.mark.parametrize("m", [2, 4])
+@pytest.mark.parametrize("m", [2, 4, 8])
 def test_a_run_with_negative_and_nan_scale_bytes_and_bad_tokens(gpu, m):
     """The persistent kernel keeps its own NaN flags and token maxima per accumulator set: steps whose weights
     hold negative scales and NaN bytes (every second step, so that flagged and clean tiles alternate on a block),
@@ -478,16 +479,17 @@ def test_which_steps_share_a_launch(gpu):
     # gate/up pairs: every second step overwrites an output of the run before it
     pairs = [(one, q.bind(xb, None, (ya, yb)[i % 2])) for i, q in enumerate(qs)]
     assert gpu.list_runs(pairs) == [2, 2, 2, 2]
-    # a K split over blocks (the stand-alone plan of a small n), weights that may change, more than 4 tokens,
-    # another K: launches of their own
+    # a K split over blocks (the stand-alone plan of a small n), weights that may change, more than 8 tokens:
+    # launches of their own
     split = gpu.plan_matmul_fp4(m, n, k, k_splits=2)
     assert gpu.list_runs([(split, qs[0].bind(xb, None, ya)), (split, qs[1].bind(xb, None, yb))]) == [1, 1]
     loose = gpu.plan_matmul_fp4(m, n, k, k_splits=1, weights_may_change=True)
     assert gpu.list_runs([(loose, qs[0].bind(xb, None, ya)), (one, qs[1].bind(xb, None, yb))]) == [1, 1]
-    x5 = gpu.upload(inputs.make_x(5, k, seed_base=532))
-    y5a, y5b = gpu.alloc(4 * 5 * n), gpu.alloc(4 * 5 * n)
-    five = gpu.plan_matmul_fp4(5, n, k, k_splits=1)
-    assert gpu.list_runs([(five, qs[0].bind(x5, None, y5a)), (five, qs[1].bind(x5, None, y5b))]) == [1, 1]
+    for t, want in ((5, [2, 2]), (8, [2, 2]), (9, [1, 1])):
+        xt = gpu.upload(inputs.make_x(t, k, seed_base=532))
+        yta, ytb = gpu.alloc(4 * t * n), gpu.alloc(4 * t * n)
+        many = gpu.plan_matmul_fp4(t, n, k, k_splits=1)
+        assert gpu.list_runs([(many, qs[0].bind(xt, None, yta)), (many, qs[1].bind(xt, None, ytb))]) == want
     # another activation buffer is fine; a step that writes the x of the step before it is not
     assert gpu.list_runs([(one, qs[0].bind(xb, None, ya)), (one, qs[1].bind(x2b, None, yb))]) == [2, 2]
     sq = gpu.plan_matmul_fp4(m, n, k, x_half=False, k_splits=1)          # f32 x: y can be bound as x (n == k)
