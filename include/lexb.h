@@ -66,11 +66,19 @@ typedef struct lexb_sched {
     uint32_t k_splits; /* two-CTA GEMM: split K this many ways (partials in a workspace the pipeline owns, then summed) */
     uint32_t flags;    /* LEXB_SCHED_* bits */
 } lexb_sched;
-/* Block-scaled kernel only.  By default it treats wq and ws as constants of the stream: launched with
- * programmatic stream serialization, it starts loading them while the kernel ahead of it in the stream
- * is still running (x, r and y wait for that kernel as usual).  Set this bit when a kernel launched
- * just before on the same stream writes the weights; copies and other streams' work are ordered anyway. */
+/* Block-scaled kernel only.  Launches are in order on their stream, as the reference's are
+ * (crates/lex-cuda/src/device.rs:629-672): every read waits for the kernel ahead.  The kernel can do
+ * better when it knows that nothing in flight writes wq and ws - launched with programmatic stream
+ * serialization, it then starts loading them while the kernel ahead of it is still running (x, r and y
+ * wait as usual).  It knows in two ways:
+ *   - inside one lexb_run_launches / lexb_time_launches call the library proves it from the step list (the
+ *     call's first launch waits for all earlier work of the stream; a later step whose wq/ws meet no y of an
+ *     earlier step of the call loads them early).  LEXB_SCHED_WEIGHTS_MAY_CHANGE turns that off for a pipeline
+ *     whose weights something outside the list (another stream) rewrites;
+ *   - LEXB_SCHED_WEIGHTS_CONSTANT is the caller's promise that nothing writes wq/ws while launches of
+ *     this pipeline are in flight, for launches made one at a time (lexb_gemm_fp4_launch). */
 #define LEXB_SCHED_WEIGHTS_MAY_CHANGE 1u
+#define LEXB_SCHED_WEIGHTS_CONSTANT 2u
 
 /* lex_msl::program::Lowered, crates/lex-msl/src/program.rs:44-63: the launch descriptor.
  * `writes` is per binding in the order [x, wq, ws, wg, (r), y] (crates/lex-msl/src/gemm.rs:78-82). */
@@ -173,9 +181,10 @@ LEXB_API int lexb_gemm_fp4_enqueue_host(lexb_gpu* gpu, const lexb_pipeline* p, c
 /* Gpu::run_launches, crates/lex-cuda/src/device.rs:650-672: all steps, one synchronise;
  * cpu_s = host time to enqueue, wall_s = host time until the device is idle.
  * The results are those of the steps run one after another.  Consecutive lexb_matmul_fp4_plan steps of t <= 8
- * tokens planned with k_splits = 1 and constant weights (no LEXB_SCHED_WEIGHTS_MAY_CHANGE), with the same t, k
- * and activation type, of which none reads or overwrites a buffer that an earlier one of them touches (x and r
- * not written, y neither read nor written: the address ranges are compared), are run as ONE persistent kernel
+ * tokens planned with k_splits = 1 (and without LEXB_SCHED_WEIGHTS_MAY_CHANGE), with the same t, k
+ * and activation type, of which none reads or overwrites a buffer that an earlier one of them touches (x, r,
+ * wq and ws not written, y neither read nor written: the address ranges are compared; wq and ws must also be
+ * untouched by every earlier step of the call, or declared constant), are run as ONE persistent kernel
  * over all their row tiles (the gate/up pair, q/k/v); each result is bit-identical to the step launched alone.
  * A step that depends on the run starts a new launch.  The environment variable LEXB_CHAIN=0 turns this off. */
 LEXB_API int lexb_run_launches(lexb_gpu* gpu, const lexb_step* steps, size_t nsteps, double* cpu_s, double* wall_s);
@@ -275,6 +284,18 @@ LEXB_API int lexb_silu_mul(lexb_gpu* gpu, uint32_t rows, uint32_t cols, const le
  * matvec.  gemm_ok = 0 reproduces the no-GEMM fallback (chunks of 8).  chunks may be null to count. */
 LEXB_API int lexb_prefill_chunks(uint32_t tokens, uint32_t limit, int gemm_ok, uint32_t* chunks, uint32_t max_chunks,
                                  uint32_t* count);
+
+/* Host-side failure injection, for tests of the error paths: the nth call from now (1 = the next) that
+ * reaches `site` is not made and reports `cuda_error` (a cudaError_t value; 0 = cudaErrorUnknown) instead, so
+ * that the entry point around it returns LEXB_ERR_CUDA, releases what it had taken and leaves its handles
+ * usable.  Sites: 1 device allocation, 2 host<->device copy, 3 kernel launch, 4 tensor-map encoding;
+ * site 0 disarms everything.  Nothing on the device is made to fail.  It stands in for the injectable
+ * driver table of the reference (the `api!` table, crates/lex-cuda/src/device.rs:88-132). */
+#define LEXB_SITE_ALLOC 1
+#define LEXB_SITE_COPY 2
+#define LEXB_SITE_LAUNCH 3
+#define LEXB_SITE_ENCODE 4
+LEXB_API int lexb_debug_fail_next(int site, int nth, int cuda_error);
 
 /* Column-parallel sharding over `world` devices (new: the reference is single-GPU,
  * crates/lex-cuda/src/device.rs:358-359).  Rank `rank` owns weight rows [*n0, *n1) - whole

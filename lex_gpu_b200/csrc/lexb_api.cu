@@ -52,6 +52,45 @@ int fail(int code, const char* fmt, ...) {
             return fail(LEXB_ERR_CUDA, "%s: %s (%s)", #expr, cudaGetErrorString(e_), cudaGetErrorName(e_)); \
     } while (0)
 
+// Host-side failure injection (tests only): lexb_debug_fail_next arms one site; the n-th call that reaches it
+// from then on fails with the given CUDA error instead of being made.  It stands where the reference's
+// injectable driver table would (the `api!` table, crates/lex-cuda/src/device.rs:88-132); nothing on the
+// device is made to fail.
+enum { SITE_ALLOC = 1, SITE_COPY = 2, SITE_LAUNCH = 3, SITE_ENCODE = 4, SITE_COUNT = 5 };
+struct Injection { int countdown = 0; int error = 0; };
+Injection g_inject[SITE_COUNT];
+std::mutex g_inject_lock;
+
+cudaError_t take_injected(int site) {
+    std::lock_guard<std::mutex> lk(g_inject_lock);
+    Injection& in = g_inject[site];
+    if (in.countdown > 0 && --in.countdown == 0) return static_cast<cudaError_t>(in.error);
+    return cudaSuccess;
+}
+
+#define CUDA_TRY_AT(site, expr)                                                                 \
+    do {                                                                                        \
+        cudaError_t e_ = take_injected(site);                                                   \
+        const bool injected_ = e_ != cudaSuccess;                                               \
+        if (!injected_) e_ = (expr);                                                            \
+        if (e_ != cudaSuccess)                                                                  \
+            return fail(LEXB_ERR_CUDA, "%s: %s (%s)%s", #expr, cudaGetErrorString(e_), cudaGetErrorName(e_), \
+                        injected_ ? " [injected]" : "");                                       \
+    } while (0)
+#define LAUNCH_TRY(expr) CUDA_TRY_AT(SITE_LAUNCH, expr)
+// in front of a <<<...>>> launch
+#define INJECT_LAUNCH()                                                                         \
+    do {                                                                                        \
+        if (cudaError_t e_ = take_injected(SITE_LAUNCH))                                        \
+            return fail(LEXB_ERR_CUDA, "kernel launch: %s (%s) [injected]", cudaGetErrorString(e_), cudaGetErrorName(e_)); \
+    } while (0)
+
+cudaError_t x_malloc(void** p, size_t bytes) {
+    if (cudaError_t e = take_injected(SITE_ALLOC)) { *p = nullptr; return e; }
+    return cudaMalloc(p, bytes);
+}
+template <typename T> cudaError_t x_malloc(T** p, size_t bytes) { return x_malloc(reinterpret_cast<void**>(p), bytes); }
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -101,6 +140,8 @@ struct lexb_pipeline {
     uint32_t k_splits = 1, kb_per_split = 0, tok_blocks = 2;
     uint32_t ws_pitch = 0;      // block-scaled kernel: bytes per row of one scale load
     bool x_f32 = false;         // ... with f32 activations
+    bool w_const = false;       // ... whose caller declared wq/ws constant (LEXB_SCHED_WEIGHTS_CONSTANT): loaded ahead of the stream's order
+    bool w_volatile = false;    // ... or said they may change (LEXB_SCHED_WEIGHTS_MAY_CHANGE): never loaded early, not even in a list
     bool mq_pre = false;        // ... with the tokens' digit rows from the pieces kernel: buffers and their tensor map
     uint8_t* pre_buf = nullptr; // [8 m][k / 2] digit rows, then [k / 256][2048] scale blocks, then [m] magnitudes
     CUtensorMap pre_map{};
@@ -214,6 +255,8 @@ int encode_2d(const lexb_pipeline* p, CUtensorMap* map, CUtensorMapDataType dt, 
     const cuuint64_t strides[1] = {inner * esize};
     const cuuint32_t box[2] = {box_inner, box_outer};
     const cuuint32_t estr[2] = {1, 1};
+    if (cudaError_t ie = take_injected(SITE_ENCODE))
+        return fail(LEXB_ERR_CUDA, "cuTensorMapEncodeTiled(%s) failed with CUresult %d [injected]", what, (int)ie);
     CUresult r = p->gpu->encode_tiled(map, dt, 2, const_cast<void*>(ptr), dims, strides, box, estr,
                                       CU_TENSOR_MAP_INTERLEAVE_NONE, swz, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                                       CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
@@ -263,9 +306,19 @@ struct NextWeights {
     const lexb_buffer *x, *wq, *ws;
 };
 
+// How a launch sits in its stream.  `early_weights`: the block-scaled kernel may load wq/ws before the launch ahead of
+// it has finished (the caller declared them constant, or the step list shows that nothing in flight writes them).
+// `fence`: launched without programmatic stream serialization, so that it starts only when everything ahead of it
+// in the stream is done - the first launch of a step list, behind which the list's own launches overlap one another only.
+struct Order {
+    bool early_weights = false;
+    bool fence = false;
+};
+
 int launch_one(lexb_gpu* g, const lexb_pipeline* p, const lexb_buffer* x, const lexb_buffer* wq, const lexb_buffer* ws,
                const lexb_buffer* wg, const lexb_buffer* r, lexb_buffer* y, const lexb::GatherDst* gather = nullptr,
-               const NextWeights* next = nullptr) {
+               const NextWeights* next = nullptr, Order order = Order{}) {
+    const bool pdl = g->pdl && !order.fence;
     if (!p) return fail(LEXB_ERR_ARG, "null pipeline");
     if (p->gpu != g) return fail(LEXB_ERR_ARG, "pipeline was planned on another gpu handle");
     const size_t m = p->m, n = p->n, k = p->k;
@@ -318,25 +371,26 @@ int launch_one(lexb_gpu* g, const lexb_pipeline* p, const lexb_buffer* x, const 
             attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
             attr[0].val.programmaticStreamSerializationAllowed = 1;
             cfg.attrs = attr;
-            cfg.numAttrs = g->pdl ? 1 : 0;
+            cfg.numAttrs = pdl ? 1 : 0;
             if (a.trace)
-                CUDA_TRY(cudaLaunchKernelEx(&cfg, lexb::gemm_fp4_tcgen05_pair_kernel<true>, maps.map, maps.map_wq, maps.map_ws, a));
+                LAUNCH_TRY(cudaLaunchKernelEx(&cfg, lexb::gemm_fp4_tcgen05_pair_kernel<true>, maps.map, maps.map_wq, maps.map_ws, a));
             else
-                CUDA_TRY(cudaLaunchKernelEx(&cfg, lexb::gemm_fp4_tcgen05_pair_kernel<false>, maps.map, maps.map_wq, maps.map_ws, a));
+                LAUNCH_TRY(cudaLaunchKernelEx(&cfg, lexb::gemm_fp4_tcgen05_pair_kernel<false>, maps.map, maps.map_wq, maps.map_ws, a));
             if (p->k_splits > 1) {
                 CUDA_TRY(cudaGetLastError());
                 const size_t elems = static_cast<size_t>(p->m) * p->n;       // n % 128 == 0: a multiple of 4
-                const uint32_t blocks = static_cast<uint32_t>(std::min<size_t>((elems / 4 + 255) / 256, 148u * 8u));
+                const uint32_t blocks = static_cast<uint32_t>(std::min<size_t>((elems / 4 + 255) / 256, static_cast<size_t>(g->prop.multiProcessorCount) * 8u));
                 cudaLaunchConfig_t rc_cfg{};
                 rc_cfg.gridDim = dim3(blocks);
                 rc_cfg.blockDim = dim3(256);
                 rc_cfg.stream = g->stream;
                 rc_cfg.attrs = attr;
-                rc_cfg.numAttrs = cfg.numAttrs;
-                CUDA_TRY(cudaLaunchKernelEx(&rc_cfg, lexb::splitk_reduce_kernel, static_cast<const float*>(p->partial), p->k_splits, elems,
+                rc_cfg.numAttrs = g->pdl ? 1 : 0;
+                LAUNCH_TRY(cudaLaunchKernelEx(&rc_cfg, lexb::splitk_reduce_kernel, static_cast<const float*>(p->partial), p->k_splits, elems,
                                             a.r, a.y, gd));
             }
         } else {
+            INJECT_LAUNCH();
             lexb::gemm_fp4_tcgen05_kernel<<<p->grid, p->threads, p->smem, g->stream>>>(maps.map, a);
         }
     } else if (p->kernel == KERNEL_MATMUL_Q) {
@@ -353,10 +407,11 @@ int launch_one(lexb_gpu* g, const lexb_pipeline* p, const lexb_buffer* x, const 
         a.status = g->d_status;
         a.m = p->m; a.n = p->n; a.k = p->k; a.stages = p->stages;
         a.k_splits = p->k_splits; a.kb_per_split = p->kb_per_split;
-        a.ws_pitch = p->ws_pitch; a.flags = p->flags;
+        a.ws_pitch = p->ws_pitch;
+        a.flags = (p->w_const || (order.early_weights && !p->w_volatile)) ? 1u : 0u;
         lexb_pipeline::MapEntry nmaps = maps;         // placeholders when there is no hint (next_grid = 0)
         if (next && next->pipe && next->pipe->kernel == KERNEL_MATMUL_Q && next->pipe->gpu == g && next->wq && next->ws &&
-            next->x && (p->flags & 1u) && get_maps(next->pipe, next->x->ptr, next->wq->ptr, next->ws->ptr, &nmaps) == LEXB_OK) {
+            next->x && (a.flags & 1u) && get_maps(next->pipe, next->x->ptr, next->wq->ptr, next->ws->ptr, &nmaps) == LEXB_OK) {
             const lexb_pipeline* q = next->pipe;
             a.next_grid = q->grid; a.next_k_splits = q->k_splits; a.next_kb_per_split = q->kb_per_split;
             a.next_kb_all = q->k / lexb::MQ_STAGE_K; a.next_stages = q->stages; a.next_ws_pitch = q->ws_pitch;
@@ -370,7 +425,7 @@ int launch_one(lexb_gpu* g, const lexb_pipeline* p, const lexb_buffer* x, const 
         attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
         attr[0].val.programmaticStreamSerializationAllowed = 1;
         cfg.attrs = attr;
-        cfg.numAttrs = g->pdl ? 1 : 0;
+        cfg.numAttrs = (g->pdl && (!order.fence || p->mq_pre)) ? 1 : 0;      // (behind the pieces kernel, that one is the fence)
         a.trace = (g->d_trace && p->grid <= g->trace_ctas) ? g->d_trace : nullptr;
         const size_t pieces_bytes = static_cast<size_t>(p->m) * 8u * (p->k / 2u), sfb_bytes = static_cast<size_t>(p->k / lexb::MQ_STAGE_K) * lexb::matmul_q_sfb_bytes(p->m);
         if (p->mq_pre) {
@@ -381,13 +436,13 @@ int launch_one(lexb_gpu* g, const lexb_pipeline* p, const lexb_buffer* x, const 
             pc.blockDim = dim3(1024);
             pc.stream = g->stream;
             pc.attrs = attr;
-            pc.numAttrs = cfg.numAttrs;
+            pc.numAttrs = pdl ? 1 : 0;
             uint32_t* amax_w = reinterpret_cast<uint32_t*>(p->pre_buf + pieces_bytes + sfb_bytes);
-            if (p->x_f32) CUDA_TRY(cudaLaunchKernelEx(&pc, lexb::matmul_q_pieces_kernel<true>, static_cast<const void*>(x->ptr), p->k, p->pre_buf, p->pre_buf + pieces_bytes, amax_w));
-            else CUDA_TRY(cudaLaunchKernelEx(&pc, lexb::matmul_q_pieces_kernel<false>, static_cast<const void*>(x->ptr), p->k, p->pre_buf, p->pre_buf + pieces_bytes, amax_w));
+            if (p->x_f32) LAUNCH_TRY(cudaLaunchKernelEx(&pc, lexb::matmul_q_pieces_kernel<true>, static_cast<const void*>(x->ptr), p->k, p->pre_buf, p->pre_buf + pieces_bytes, amax_w));
+            else LAUNCH_TRY(cudaLaunchKernelEx(&pc, lexb::matmul_q_pieces_kernel<false>, static_cast<const void*>(x->ptr), p->k, p->pre_buf, p->pre_buf + pieces_bytes, amax_w));
         }
         const CUtensorMap& bmap = p->mq_pre ? p->pre_map : maps.map_wq;      // a placeholder without the pieces kernel
-#define LEXB_MQ_LAUNCH(TR, XF, PR) CUDA_TRY(cudaLaunchKernelEx(&cfg, lexb::matmul_q_fp4_kernel<TR, XF, PR>, maps.map_wq, maps.map_ws, nmaps.map_wq, nmaps.map_ws, bmap, a))
+#define LEXB_MQ_LAUNCH(TR, XF, PR) LAUNCH_TRY(cudaLaunchKernelEx(&cfg, lexb::matmul_q_fp4_kernel<TR, XF, PR>, maps.map_wq, maps.map_ws, nmaps.map_wq, nmaps.map_ws, bmap, a))
         if (p->mq_pre) {
             if (p->x_f32) { if (a.trace) LEXB_MQ_LAUNCH(true, true, true); else LEXB_MQ_LAUNCH(false, true, true); }
             else { if (a.trace) LEXB_MQ_LAUNCH(true, false, true); else LEXB_MQ_LAUNCH(false, false, true); }
@@ -415,13 +470,13 @@ int launch_one(lexb_gpu* g, const lexb_pipeline* p, const lexb_buffer* x, const 
         attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
         attr[0].val.programmaticStreamSerializationAllowed = 1;
         cfg.attrs = attr;
-        cfg.numAttrs = g->pdl ? 1 : 0;
+        cfg.numAttrs = pdl ? 1 : 0;
         if (p->m > 8) {
-            if (ragged) CUDA_TRY(cudaLaunchKernelEx(&cfg, lexb::matvec_fp4_kernel<true, true>, a));
-            else CUDA_TRY(cudaLaunchKernelEx(&cfg, lexb::matvec_fp4_kernel<true, false>, a));
+            if (ragged) LAUNCH_TRY(cudaLaunchKernelEx(&cfg, lexb::matvec_fp4_kernel<true, true>, a));
+            else LAUNCH_TRY(cudaLaunchKernelEx(&cfg, lexb::matvec_fp4_kernel<true, false>, a));
         } else {
-            if (ragged) CUDA_TRY(cudaLaunchKernelEx(&cfg, lexb::matvec_fp4_kernel<false, true>, a));
-            else CUDA_TRY(cudaLaunchKernelEx(&cfg, lexb::matvec_fp4_kernel<false, false>, a));
+            if (ragged) LAUNCH_TRY(cudaLaunchKernelEx(&cfg, lexb::matvec_fp4_kernel<false, true>, a));
+            else LAUNCH_TRY(cudaLaunchKernelEx(&cfg, lexb::matvec_fp4_kernel<false, false>, a));
         }
     }
     CUDA_TRY(cudaGetLastError());
@@ -441,47 +496,89 @@ static uint32_t chain_pre_min_m() {
     static const uint32_t v = env_u32("LEXB_CHAIN_PRE_MIN_M", 3);
     return v;
 }
+// Address ranges a step reads and writes, for the dependence checks of a step list.
+struct Range { const char *lo, *hi; };
+inline bool meet(Range a, Range b) { return a.lo < b.hi && b.lo < a.hi; }
+struct StepRanges {
+    Range x{}, wq{}, ws{}, r{}, y{};
+    bool valid = false;          // false: a null pipeline, buffer list or buffer (the step's own launch reports it)
+};
+
+StepRanges step_ranges(const lexb_step& s) {
+    StepRanges out;
+    const lexb_pipeline* p = s.pipeline;
+    if (!p || !s.buffers || s.nbuffers != (p->residual ? 6u : 5u)) return out;
+    for (uint32_t b = 0; b < s.nbuffers; b++)
+        if (!s.buffers[b] || !s.buffers[b]->ptr) return out;
+    auto range = [](const lexb_buffer* b, size_t bytes) { const char* p0 = static_cast<const char*>(b->ptr); return Range{p0, p0 + bytes}; };
+    const size_t m = p->m, n = p->n, k = p->k, out_bytes = m * n * 4;
+    out.x = range(s.buffers[0], m * k * (p->x_f32 ? 4 : 2));
+    out.wq = range(s.buffers[1], n * k / 2);
+    out.ws = range(s.buffers[2], n * k / 16);
+    out.r = p->residual ? range(s.buffers[4], out_bytes) : Range{nullptr, nullptr};
+    out.y = range(s.buffers[p->residual ? 5 : 4], out_bytes);
+    out.valid = true;
+    return out;
+}
+
+// What the steps of one lexb_run_launches / lexb_time_launches call have written so far.  The call's first launch
+// is a fence (it starts when all earlier work of the stream is done), so a later step whose packed weights meet
+// none of these ranges reads weights that nothing in flight writes: its kernel may load them ahead of the
+// stream's order.  That is proven here from the list, as the reference's in-order contract
+// (crates/lex-cuda/src/device.rs:629-672) leaves no other way to know it.
+struct ListProof {
+    std::vector<Range> written;      // distinct y ranges
+    bool weights_untouched(const StepRanges& s) const {
+        for (const Range& w : written)
+            if (meet(s.wq, w) || meet(s.ws, w)) return false;
+        return true;
+    }
+    void add(const StepRanges& s) {
+        for (const Range& w : written)
+            if (w.lo == s.y.lo && w.hi == s.y.hi) return;
+        written.push_back(s.y);
+    }
+};
+
 bool chain_member(const lexb_gpu* g, const lexb_step& s, const lexb_pipeline* first) {
     const lexb_pipeline* p = s.pipeline;
     if (!p || !s.buffers || p->gpu != g || p->kernel != KERNEL_MATMUL_Q || p->m > chain_max_m() || p->k_splits != 1u) return false;
     if (p->mq_pre != (p->m > 4u)) return false;                                      // (a plan forced the other way by LEXB_MQ_PRE stays as planned)
-    if (!(p->flags & 1u) || s.nbuffers != (p->residual ? 6u : 5u)) return false;
+    if (p->w_volatile || s.nbuffers != (p->residual ? 6u : 5u)) return false;
     if ((p->k / lexb::MQ_STAGE_K) % lexb::MQ_WS_GROUP == 1u) return false;          // a scale-byte group of one stage is seen by half the scale warps only
     if (p->stages != (p->m <= 4u ? lexb::MQ_MAX_STAGES : 7u) || lexb::matmul_q_chain_smem_bytes(p->stages, p->m) > g->smem_optin) return false;
     return !first || (p->m == first->m && p->k == first->k && p->x_f32 == first->x_f32 && p->stages == first->stages &&
                       p->ws_pitch == first->ws_pitch);
 }
 
-size_t chain_run(const lexb_gpu* g, const lexb_step* steps, size_t nsteps, size_t i) {
+// Length of the run of steps starting at i that one persistent kernel can take (0: step i is launched on its own).
+// The run's copy warp starts on the weights at once, so every member's weights must be declared constant or be
+// untouched by the steps of this call so far (`proof`) and by the run's own members.
+size_t chain_run(const lexb_gpu* g, const lexb_step* steps, size_t nsteps, size_t i, const ListProof& proof) {
     static const bool on = env_u32("LEXB_CHAIN", 1) != 0;
     if (!on || !chain_member(g, steps[i], nullptr)) return 0;
+    const StepRanges first = step_ranges(steps[i]);
+    if (!first.valid) return 0;                                  // a null buffer entry: the step's own launch reports it
+    if (!steps[i].pipeline->w_const && !proof.weights_untouched(first)) return 0;
     // The run's row tiles are spread over the blocks with no order between blocks, so a step joins the run only
-    // if nothing it reads (x, r) is written by a step already in it and nothing it writes (y) is read or
-    // written by one: such a step starts the next launch, and the stream orders it.
-    struct Range { const char *lo, *hi; };
-    auto range = [](const lexb_buffer* b, size_t bytes) { const char* p0 = static_cast<const char*>(b->ptr); return Range{p0, p0 + bytes}; };
-    auto meet = [](Range a, Range b) { return a.lo < b.hi && b.lo < a.hi; };
-    auto ranges = [&](size_t e, Range& x, Range& r, Range& y) {
-        const lexb_pipeline* pe = steps[e].pipeline;
-        const size_t out = static_cast<size_t>(pe->m) * pe->n * 4;
-        x = range(steps[e].buffers[0], static_cast<size_t>(pe->m) * pe->k * (pe->x_f32 ? 4 : 2));
-        r = pe->residual ? range(steps[e].buffers[4], out) : Range{nullptr, nullptr};
-        y = range(steps[e].buffers[pe->residual ? 5 : 4], out);
-    };
-    auto x_written_in_run = [&](size_t cand, size_t len) {
-        for (uint32_t b = 0; b < steps[cand].nbuffers; b++)
-            if (!steps[cand].buffers[b] || !steps[cand].buffers[b]->ptr) return true;      // (refused by the launch of its own)
-        Range cx, cr, cy;
-        ranges(cand, cx, cr, cy);
-        for (size_t e = i; e < i + len; e++) {
-            Range ex, er, ey;
-            ranges(e, ex, er, ey);
-            if (meet(cx, ey) || meet(cr, ey) || meet(cy, ex) || meet(cy, er) || meet(cy, ey)) return true;
+    // if nothing it reads (x, r, the weights) is written by a step already in it and nothing it writes (y) is
+    // read or written by one: such a step starts the next launch, and the stream orders it.
+    std::vector<StepRanges> in_run{first};
+    auto conflicts = [&](const StepRanges& c, bool declared_const) {
+        if (!declared_const && !proof.weights_untouched(c)) return true;
+        for (const StepRanges& e : in_run) {
+            if (meet(c.x, e.y) || meet(c.r, e.y) || meet(c.y, e.x) || meet(c.y, e.r) || meet(c.y, e.y)) return true;
+            if (meet(c.wq, e.y) || meet(c.ws, e.y) || meet(c.y, e.wq) || meet(c.y, e.ws)) return true;
         }
         return false;
     };
     size_t len = 1;
-    while (i + len < nsteps && len < 4096 && chain_member(g, steps[i + len], steps[i].pipeline) && !x_written_in_run(i + len, len)) len++;
+    while (i + len < nsteps && len < 4096 && chain_member(g, steps[i + len], steps[i].pipeline)) {
+        const StepRanges c = step_ranges(steps[i + len]);
+        if (!c.valid || conflicts(c, steps[i + len].pipeline->w_const)) break;
+        in_run.push_back(c);
+        len++;
+    }
     if (len >= 2) return len;
     // a single step with more row tiles than SMs: the persistent kernel takes them without a second wave of
     // block set-ups (n = 28672: 224 tiles)
@@ -490,7 +587,8 @@ size_t chain_run(const lexb_gpu* g, const lexb_step* steps, size_t nsteps, size_
     return single && tiles > static_cast<uint32_t>(g->prop.multiProcessorCount) ? 1 : 0;
 }
 
-int launch_chain(lexb_gpu* g, const lexb_step* steps, size_t count) {
+int launch_chain(lexb_gpu* g, const lexb_step* steps, size_t count, bool fence) {
+    bool pdl_next = g->pdl && !fence;            // the run's first kernel launch is the fence, when one is asked for
     const lexb_pipeline* p0 = steps[0].pipeline;
     std::vector<lexb::MqChainJob> jobs(count);
     uint32_t tiles = 0, jobs_first_tiles = 0;        // (the latter: every step's tile count if they all agree, else 0)
@@ -536,7 +634,7 @@ int launch_chain(lexb_gpu* g, const lexb_step* steps, size_t count) {
                 }
                 lexb_gpu::ChainPre cp{};
                 const size_t total = pieces_bytes + sfb_bytes + 4u * lexb::MQ_MAX_TOKENS;
-                CUDA_TRY(cudaMalloc(&cp.buf, total));
+                CUDA_TRY(x_malloc(&cp.buf, total));
                 cudaError_t e = cudaMemsetAsync(cp.buf, 0, total, g->stream);      // scale rows nobody writes stay zero
                 int erc = e == cudaSuccess ? encode_2d(p, &cp.map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, cp.buf, p0->k / 2u, 8u * p0->m, 128u,
                                                       8u * p0->m, CU_TENSOR_MAP_SWIZZLE_128B, "digit rows of a run")
@@ -555,10 +653,11 @@ int launch_chain(lexb_gpu* g, const lexb_step* steps, size_t count) {
                 pc.blockDim = dim3(1024);
                 pc.stream = g->stream;
                 pc.attrs = attr;
-                pc.numAttrs = g->pdl ? 1 : 0;
+                pc.numAttrs = pdl_next ? 1 : 0;
+                pdl_next = g->pdl;
                 uint32_t* amax_w = reinterpret_cast<uint32_t*>(buf + pieces_bytes + sfb_bytes);
-                if (p0->x_f32) CUDA_TRY(cudaLaunchKernelEx(&pc, lexb::matmul_q_pieces_kernel<true>, static_cast<const void*>(x->ptr), p0->k, buf, buf + pieces_bytes, amax_w));
-                else CUDA_TRY(cudaLaunchKernelEx(&pc, lexb::matmul_q_pieces_kernel<false>, static_cast<const void*>(x->ptr), p0->k, buf, buf + pieces_bytes, amax_w));
+                if (p0->x_f32) LAUNCH_TRY(cudaLaunchKernelEx(&pc, lexb::matmul_q_pieces_kernel<true>, static_cast<const void*>(x->ptr), p0->k, buf, buf + pieces_bytes, amax_w));
+                else LAUNCH_TRY(cudaLaunchKernelEx(&pc, lexb::matmul_q_pieces_kernel<false>, static_cast<const void*>(x->ptr), p0->k, buf, buf + pieces_bytes, amax_w));
             }
         }
         const uint32_t job_tiles = (p->n + lexb::MQ_ROWS - 1u) / lexb::MQ_ROWS;
@@ -584,10 +683,10 @@ int launch_chain(lexb_gpu* g, const lexb_step* steps, size_t count) {
             for (auto& e : g->chain_tables) cudaFree(e.second.dev);
             g->chain_tables.clear();
         }
-        CUDA_TRY(cudaMalloc(&d_jobs, table_bytes));
+        CUDA_TRY(x_malloc(&d_jobs, table_bytes));
         auto it = g->chain_tables.emplace(h, lexb_gpu::ChainTable{std::move(jobs), d_jobs});
         // (the source is the cache's own copy: it outlives the transfer)
-        CUDA_TRY(cudaMemcpyAsync(d_jobs, it->second.host.data(), table_bytes, cudaMemcpyHostToDevice, g->stream));
+        CUDA_TRY_AT(SITE_COPY, cudaMemcpyAsync(d_jobs, it->second.host.data(), table_bytes, cudaMemcpyHostToDevice, g->stream));
     }
     lexb::MqChainArgs a{};
     a.jobs = d_jobs;
@@ -603,18 +702,18 @@ int launch_chain(lexb_gpu* g, const lexb_step* steps, size_t count) {
     cfg.dynamicSmemBytes = lexb::matmul_q_chain_smem_bytes(p0->stages, p0->m);
     cfg.stream = g->stream;
     cfg.attrs = attr;
-    cfg.numAttrs = g->pdl ? 1 : 0;
+    cfg.numAttrs = pdl_next ? 1 : 0;
     if (pre) {
-        if (p0->x_f32) CUDA_TRY(cudaLaunchKernelEx(&cfg, lexb::matmul_q_chain_kernel<true, true>, a));
-        else CUDA_TRY(cudaLaunchKernelEx(&cfg, lexb::matmul_q_chain_kernel<false, true>, a));
+        if (p0->x_f32) LAUNCH_TRY(cudaLaunchKernelEx(&cfg, lexb::matmul_q_chain_kernel<true, true>, a));
+        else LAUNCH_TRY(cudaLaunchKernelEx(&cfg, lexb::matmul_q_chain_kernel<false, true>, a));
     } else {
-        if (p0->x_f32) CUDA_TRY(cudaLaunchKernelEx(&cfg, lexb::matmul_q_chain_kernel<true, false>, a));
-        else CUDA_TRY(cudaLaunchKernelEx(&cfg, lexb::matmul_q_chain_kernel<false, false>, a));
+        if (p0->x_f32) LAUNCH_TRY(cudaLaunchKernelEx(&cfg, lexb::matmul_q_chain_kernel<true, false>, a));
+        else LAUNCH_TRY(cudaLaunchKernelEx(&cfg, lexb::matmul_q_chain_kernel<false, false>, a));
     }
     return LEXB_OK;
 }
 
-int launch_step(lexb_gpu* g, const lexb_step& s, const lexb_step* following = nullptr) {
+int launch_step(lexb_gpu* g, const lexb_step& s, const lexb_step* following = nullptr, Order order = Order{}) {
     if (!s.pipeline || !s.buffers) return fail(LEXB_ERR_ARG, "step without pipeline or buffers");
     const bool res = s.pipeline->residual;
     if (s.nbuffers != (res ? 6u : 5u))
@@ -626,7 +725,32 @@ int launch_step(lexb_gpu* g, const lexb_step& s, const lexb_step* following = nu
     if (hints && following && following->pipeline && following->buffers && following->nbuffers >= 5u)
         nw = NextWeights{following->pipeline, following->buffers[0], following->buffers[1], following->buffers[2]};
     return launch_one(g, s.pipeline, b[0], b[1], b[2], b[3], res ? b[4] : nullptr, res ? b[5] : b[4], nullptr,
-                      nw.pipe ? &nw : nullptr);
+                      nw.pipe ? &nw : nullptr, order);
+}
+
+// Issues the steps of a list once, in order, forming runs; `proof` and `first` carry over between the passes of
+// lexb_time_launches.  `first`: nothing of this call has been launched yet - that launch is the call's fence.
+int issue_list(lexb_gpu* g, const lexb_step* steps, size_t nsteps, ListProof& proof, bool& first, const lexb_step* after_last) {
+    int rc;
+    for (size_t i = 0; i < nsteps;) {
+        if (const size_t len = chain_run(g, steps, nsteps, i, proof)) {
+            if ((rc = launch_chain(g, steps + i, len, first))) return rc;
+            for (size_t e = i; e < i + len; e++) proof.add(step_ranges(steps[e]));
+            first = false;
+            i += len;
+            continue;
+        }
+        const StepRanges sr = step_ranges(steps[i]);
+        Order order;
+        order.fence = first;
+        order.early_weights = sr.valid && proof.weights_untouched(sr);
+        const lexb_step* following = i + 1 < nsteps ? &steps[i + 1] : after_last;
+        if ((rc = launch_step(g, steps[i], following, order))) return rc;
+        if (sr.valid) proof.add(sr);
+        first = false;
+        i++;
+    }
+    return LEXB_OK;
 }
 
 }  // namespace
@@ -658,7 +782,8 @@ int lexb_open(int device, lexb_gpu** out) {
     if (cudaStreamCreateWithFlags(&g->own_stream, cudaStreamNonBlocking) != cudaSuccess)
         return bail(fail(LEXB_ERR_CUDA, "cudaStreamCreate failed"));
     g->stream = g->own_stream;
-    if (cudaMalloc(&g->d_status, sizeof(uint32_t)) != cudaSuccess || cudaMemset(g->d_status, 0, sizeof(uint32_t)) != cudaSuccess)
+    if (cudaMalloc(&g->d_status, sizeof(uint32_t)) != cudaSuccess || cudaMemsetAsync(g->d_status, 0, sizeof(uint32_t), g->stream) != cudaSuccess ||
+        cudaStreamSynchronize(g->stream) != cudaSuccess)
         return bail(fail(LEXB_ERR_CUDA, "allocating the status word failed"));
     void* fn = nullptr;
     cudaDriverEntryPointQueryResult qres;
@@ -744,7 +869,7 @@ int lexb_alloc(lexb_gpu* g, size_t bytes, lexb_buffer** out) {
     if (!out) return fail(LEXB_ERR_ARG, "lexb_alloc: null out");
     *out = nullptr;
     void* p = nullptr;
-    CUDA_TRY(cudaMalloc(&p, bytes ? bytes : 1));
+    CUDA_TRY(x_malloc(&p, bytes ? bytes : 1));
     lexb_buffer* b = new (std::nothrow) lexb_buffer{g, p, bytes, true};
     if (!b) {
         cudaFree(p);
@@ -799,7 +924,7 @@ int lexb_upload(lexb_gpu* g, lexb_buffer* dst, size_t off, const void* src, size
     if (!dst || (!src && bytes)) return fail(LEXB_ERR_ARG, "lexb_upload: null argument");
     if (off > dst->bytes || bytes > dst->bytes - off)
         return fail(LEXB_ERR_ARG, "lexb_upload: %zu bytes at offset %zu overrun a buffer of %zu", bytes, off, dst->bytes);
-    CUDA_TRY(cudaMemcpyAsync(static_cast<char*>(dst->ptr) + off, src, bytes, cudaMemcpyHostToDevice, g->stream));
+    CUDA_TRY_AT(SITE_COPY, cudaMemcpyAsync(static_cast<char*>(dst->ptr) + off, src, bytes, cudaMemcpyHostToDevice, g->stream));
     CUDA_TRY(cudaStreamSynchronize(g->stream));
     return LEXB_OK;
 }
@@ -810,7 +935,7 @@ int lexb_download(lexb_gpu* g, const lexb_buffer* src, size_t off, void* dst, si
     if (!src || (!dst && bytes)) return fail(LEXB_ERR_ARG, "lexb_download: null argument");
     if (off > src->bytes || bytes > src->bytes - off)
         return fail(LEXB_ERR_ARG, "lexb_download: %zu bytes at offset %zu overrun a buffer of %zu", bytes, off, src->bytes);
-    CUDA_TRY(cudaMemcpyAsync(dst, static_cast<const char*>(src->ptr) + off, bytes, cudaMemcpyDeviceToHost, g->stream));
+    CUDA_TRY_AT(SITE_COPY, cudaMemcpyAsync(dst, static_cast<const char*>(src->ptr) + off, bytes, cudaMemcpyDeviceToHost, g->stream));
     CUDA_TRY(cudaStreamSynchronize(g->stream));
     return LEXB_OK;
 }
@@ -891,13 +1016,21 @@ int lexb_gemm_fp4_plan(lexb_gpu* g, uint32_t m, uint32_t n, uint32_t k, int resi
         splits = (kb_all + per - 1u) / per;
         p->k_splits = splits; p->kb_per_split = per; p->stages = stages;
         p->ws_pitch = k / 16u < 16u * lexb::MQ_WS_GROUP ? k / 16u : 16u * lexb::MQ_WS_GROUP;
-        // the weights are taken as constant (loaded ahead of the stream's order) unless the caller says otherwise
-        p->flags = (s.flags & LEXB_SCHED_WEIGHTS_MAY_CHANGE) ? 0u : 1u;
+        // In order by default, as the reference's launches are (crates/lex-cuda/src/device.rs:629-672): wq/ws are
+        // loaded ahead of the stream's order only when the caller declares them constant or a step list shows
+        // that nothing in flight writes them (ListProof); never when the caller says they may change.
+        p->w_const = (s.flags & LEXB_SCHED_WEIGHTS_CONSTANT) != 0u;
+        p->w_volatile = (s.flags & LEXB_SCHED_WEIGHTS_MAY_CHANGE) != 0u;
+        if (p->w_const && p->w_volatile)
+            return bail(fail(LEXB_ERR_ARG, "LEXB_SCHED_WEIGHTS_CONSTANT and LEXB_SCHED_WEIGHTS_MAY_CHANGE exclude one another"));
+        p->flags = 0u;
         if (splits > 1u) {
             // partial products [splits][m][n], then one arrival counter per row tile (zero between launches)
             const size_t pbytes = sizeof(float) * splits * static_cast<size_t>(m) * n;
-            cudaError_t e = cudaMalloc(&p->partial, pbytes + sizeof(uint32_t) * tiles);
-            if (e == cudaSuccess) e = cudaMemset(reinterpret_cast<char*>(p->partial) + pbytes, 0, sizeof(uint32_t) * tiles);
+            cudaError_t e = x_malloc(&p->partial, pbytes + sizeof(uint32_t) * tiles);
+            // cleared on the launch stream and waited for: a launch on any stream may follow at once
+            if (e == cudaSuccess) e = cudaMemsetAsync(reinterpret_cast<char*>(p->partial) + pbytes, 0, sizeof(uint32_t) * tiles, g->stream);
+            if (e == cudaSuccess) e = cudaStreamSynchronize(g->stream);
             if (e != cudaSuccess) return bail(fail(LEXB_ERR_CUDA, "allocating the split-K workspace: %s", cudaGetErrorString(e)));
         }
         // From 5 tokens on the digit rows are derived once per launch by a small kernel ahead of this one
@@ -906,8 +1039,9 @@ int lexb_gemm_fp4_plan(lexb_gpu* g, uint32_t m, uint32_t n, uint32_t k, int resi
         if (p->mq_pre) {
             const size_t pieces_bytes = static_cast<size_t>(m) * 8u * (k / 2u), sfb_bytes = static_cast<size_t>(kb_all) * lexb::matmul_q_sfb_bytes(m);
             const size_t total = pieces_bytes + sfb_bytes + 4u * lexb::MQ_MAX_TOKENS;
-            cudaError_t e = cudaMalloc(&p->pre_buf, total);
-            if (e == cudaSuccess) e = cudaMemset(p->pre_buf, 0, total);          // scale rows nobody writes stay zero
+            cudaError_t e = x_malloc(&p->pre_buf, total);
+            if (e == cudaSuccess) e = cudaMemsetAsync(p->pre_buf, 0, total, g->stream);          // scale rows nobody writes stay zero
+            if (e == cudaSuccess) e = cudaStreamSynchronize(g->stream);
             if (e != cudaSuccess) return bail(fail(LEXB_ERR_CUDA, "allocating the digit-row buffers: %s", cudaGetErrorString(e)));
             int erc = encode_2d(p, &p->pre_map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, p->pre_buf, k / 2u, 8u * m, 128u, 8u * m,
                                 CU_TENSOR_MAP_SWIZZLE_128B, "digit rows");
@@ -986,7 +1120,7 @@ int lexb_gemm_fp4_plan(lexb_gpu* g, uint32_t m, uint32_t n, uint32_t k, int resi
         p->k_splits = splits;
         p->kb_per_split = rb_per_split * (lexb::PAIR_RAW_K / lexb::GEMM_BK);
         if (splits > 1u) {
-            cudaError_t e = cudaMalloc(&p->partial, sizeof(float) * splits * static_cast<size_t>(m) * n);
+            cudaError_t e = x_malloc(&p->partial, sizeof(float) * splits * static_cast<size_t>(m) * n);
             if (e != cudaSuccess) return bail(fail(LEXB_ERR_CUDA, "allocating the split-K workspace: %s", cudaGetErrorString(e)));
         }
         p->grid = 2u * tiles * splits;
@@ -1118,9 +1252,9 @@ int lexb_gemm_fp4_enqueue_host(lexb_gpu* g, const lexb_pipeline* p, const void* 
     if (!p || !x_host || !y_host || !x_dev || !y_dev) return fail(LEXB_ERR_ARG, "lexb_gemm_fp4_enqueue_host: null argument");
     const size_t xb = static_cast<size_t>(p->m) * p->k * (p->x_f32 ? 4 : 2), yb = static_cast<size_t>(p->m) * p->n * 4;
     if (x_dev->bytes < xb || y_dev->bytes < yb) return fail(LEXB_ERR_ARG, "lexb_gemm_fp4_enqueue_host: staging buffers too small");
-    CUDA_TRY(cudaMemcpyAsync(x_dev->ptr, x_host, xb, cudaMemcpyHostToDevice, g->stream));
+    CUDA_TRY_AT(SITE_COPY, cudaMemcpyAsync(x_dev->ptr, x_host, xb, cudaMemcpyHostToDevice, g->stream));
     if ((rc = launch_one(g, p, x_dev, wq, ws, wg, r, y_dev))) return rc;
-    CUDA_TRY(cudaMemcpyAsync(y_host, y_dev->ptr, yb, cudaMemcpyDeviceToHost, g->stream));
+    CUDA_TRY_AT(SITE_COPY, cudaMemcpyAsync(y_host, y_dev->ptr, yb, cudaMemcpyDeviceToHost, g->stream));
     return LEXB_OK;
 }
 
@@ -1132,9 +1266,9 @@ int lexb_gemm_fp4_run_host(lexb_gpu* g, const lexb_pipeline* p, const void* x_ho
     if (!p || !x_host || !y_host || !x_dev || !y_dev) return fail(LEXB_ERR_ARG, "lexb_gemm_fp4_run_host: null argument");
     const size_t xb = static_cast<size_t>(p->m) * p->k * (p->x_f32 ? 4 : 2), yb = static_cast<size_t>(p->m) * p->n * 4;
     if (x_dev->bytes < xb || y_dev->bytes < yb) return fail(LEXB_ERR_ARG, "lexb_gemm_fp4_run_host: staging buffers too small");
-    CUDA_TRY(cudaMemcpyAsync(x_dev->ptr, x_host, xb, cudaMemcpyHostToDevice, g->stream));
+    CUDA_TRY_AT(SITE_COPY, cudaMemcpyAsync(x_dev->ptr, x_host, xb, cudaMemcpyHostToDevice, g->stream));
     if ((rc = launch_one(g, p, x_dev, wq, ws, wg, r, y_dev))) return rc;
-    CUDA_TRY(cudaMemcpyAsync(y_host, y_dev->ptr, yb, cudaMemcpyDeviceToHost, g->stream));
+    CUDA_TRY_AT(SITE_COPY, cudaMemcpyAsync(y_host, y_dev->ptr, yb, cudaMemcpyDeviceToHost, g->stream));
     CUDA_TRY(cudaStreamSynchronize(g->stream));
     return LEXB_OK;
 }
@@ -1144,15 +1278,9 @@ int lexb_run_launches(lexb_gpu* g, const lexb_step* steps, size_t nsteps, double
     if (rc) return rc;
     if (!steps && nsteps) return fail(LEXB_ERR_ARG, "lexb_run_launches: null steps");
     const auto t0 = std::chrono::steady_clock::now();
-    for (size_t i = 0; i < nsteps;) {
-        if (const size_t len = chain_run(g, steps, nsteps, i)) {
-            if ((rc = launch_chain(g, steps + i, len))) return rc;
-            i += len;
-            continue;
-        }
-        if ((rc = launch_step(g, steps[i], i + 1 < nsteps ? &steps[i + 1] : nullptr))) return rc;
-        i++;
-    }
+    ListProof proof;
+    bool first = true;
+    if ((rc = issue_list(g, steps, nsteps, proof, first, nullptr))) return rc;
     const auto t1 = std::chrono::steady_clock::now();
     CUDA_TRY(cudaStreamSynchronize(g->stream));
     const auto t2 = std::chrono::steady_clock::now();
@@ -1170,8 +1298,14 @@ int lexb_run_each_timed(lexb_gpu* g, const lexb_step* steps, size_t nsteps, doub
     for (auto& e : ev)
         if (cudaEventCreate(&e) != cudaSuccess) { cleanup(); return fail(LEXB_ERR_CUDA, "cudaEventCreate failed"); }
     cudaEventRecord(ev[0], g->stream);
+    ListProof proof;
     for (size_t i = 0; i < nsteps; i++) {
-        if ((rc = launch_step(g, steps[i], i + 1 < nsteps ? &steps[i + 1] : nullptr))) { cleanup(); return rc; }
+        const StepRanges sr = step_ranges(steps[i]);
+        Order order;
+        order.fence = i == 0;
+        order.early_weights = sr.valid && proof.weights_untouched(sr);
+        if ((rc = launch_step(g, steps[i], i + 1 < nsteps ? &steps[i + 1] : nullptr, order))) { cleanup(); return rc; }
+        if (sr.valid) proof.add(sr);
         cudaEventRecord(ev[i + 1], g->stream);
     }
     cudaError_t e = cudaStreamSynchronize(g->stream);
@@ -1189,10 +1323,15 @@ int lexb_list_runs(lexb_gpu* g, const lexb_step* steps, size_t nsteps, uint32_t*
     int rc = use(g);
     if (rc) return rc;
     if ((!steps || !run_len_out) && nsteps) return fail(LEXB_ERR_ARG, "lexb_list_runs: null argument");
+    ListProof proof;
     for (size_t i = 0; i < nsteps;) {
-        const size_t len = chain_run(g, steps, nsteps, i);
+        const size_t len = chain_run(g, steps, nsteps, i, proof);
         const size_t take = len ? len : 1;
-        for (size_t e = i; e < i + take; e++) run_len_out[e] = static_cast<uint32_t>(take);
+        for (size_t e = i; e < i + take; e++) {
+            run_len_out[e] = static_cast<uint32_t>(take);
+            const StepRanges sr = step_ranges(steps[e]);
+            if (sr.valid) proof.add(sr);
+        }
         i += take;
     }
     return LEXB_OK;
@@ -1207,18 +1346,13 @@ int lexb_time_launches(lexb_gpu* g, const lexb_step* steps, size_t nsteps, uint3
     CUDA_TRY(cudaEventCreate(&b));
     CUDA_TRY(cudaStreamSynchronize(g->stream));
     cudaEventRecord(a, g->stream);
-    for (uint32_t r = 0; r < reps; r++)
-        for (size_t i = 0; i < nsteps;) {
-            if (const size_t len = chain_run(g, steps, nsteps, i)) {
-                if ((rc = launch_chain(g, steps + i, len))) { cudaEventDestroy(a); cudaEventDestroy(b); return rc; }
-                i += len;
-                continue;
-            }
-            // the list repeats: the step after the last one is the first one again
-            const lexb_step* following = i + 1 < nsteps ? &steps[i + 1] : (r + 1 < reps ? &steps[0] : nullptr);
-            if ((rc = launch_step(g, steps[i], following))) { cudaEventDestroy(a); cudaEventDestroy(b); return rc; }
-            i++;
-        }
+    ListProof proof;
+    bool first = true;
+    for (uint32_t r = 0; r < reps; r++) {
+        // the list repeats: the step after the last one is the first one again
+        const lexb_step* after_last = (r + 1 < reps && nsteps) ? &steps[0] : nullptr;
+        if ((rc = issue_list(g, steps, nsteps, proof, first, after_last))) { cudaEventDestroy(a); cudaEventDestroy(b); return rc; }
+    }
     cudaEventRecord(b, g->stream);
     cudaError_t e = cudaStreamSynchronize(g->stream);
     float ms = 0.f;
@@ -1234,9 +1368,11 @@ int lexb_status_word(lexb_gpu* g, uint32_t* out) {
     int rc = use(g);
     if (rc) return rc;
     if (!out) return fail(LEXB_ERR_ARG, "lexb_status_word: null out");
+    // read and cleared in the launch stream's order, then waited for: the legacy default stream would not be
+    // ordered with the library's non-blocking stream
+    CUDA_TRY(cudaMemcpyAsync(out, g->d_status, sizeof(uint32_t), cudaMemcpyDeviceToHost, g->stream));
+    CUDA_TRY(cudaMemsetAsync(g->d_status, 0, sizeof(uint32_t), g->stream));
     CUDA_TRY(cudaStreamSynchronize(g->stream));
-    CUDA_TRY(cudaMemcpy(out, g->d_status, sizeof(uint32_t), cudaMemcpyDeviceToHost));
-    CUDA_TRY(cudaMemset(g->d_status, 0, sizeof(uint32_t)));
     return LEXB_OK;
 }
 
@@ -1249,8 +1385,9 @@ int lexb_trace_enable(lexb_gpu* g, uint32_t max_ctas) {
         g->trace_ctas = 0;
     }
     if (max_ctas) {
-        CUDA_TRY(cudaMalloc(&g->d_trace, sizeof(unsigned long long) * 16u * max_ctas));
-        CUDA_TRY(cudaMemset(g->d_trace, 0, sizeof(unsigned long long) * 16u * max_ctas));
+        CUDA_TRY(x_malloc(&g->d_trace, sizeof(unsigned long long) * 16u * max_ctas));
+        CUDA_TRY(cudaMemsetAsync(g->d_trace, 0, sizeof(unsigned long long) * 16u * max_ctas, g->stream));
+        CUDA_TRY(cudaStreamSynchronize(g->stream));
         g->trace_ctas = max_ctas;
     }
     return LEXB_OK;
@@ -1260,8 +1397,8 @@ int lexb_trace_read(lexb_gpu* g, uint64_t* out, uint32_t ctas) {
     int rc = use(g);
     if (rc) return rc;
     if (!out || !g->d_trace || ctas > g->trace_ctas) return fail(LEXB_ERR_ARG, "lexb_trace_read: tracing is off or the request is too large");
+    CUDA_TRY(cudaMemcpyAsync(out, g->d_trace, sizeof(uint64_t) * 16u * ctas, cudaMemcpyDeviceToHost, g->stream));
     CUDA_TRY(cudaStreamSynchronize(g->stream));
-    CUDA_TRY(cudaMemcpy(out, g->d_trace, sizeof(uint64_t) * 16u * ctas, cudaMemcpyDeviceToHost));
     return LEXB_OK;
 }
 
@@ -1270,6 +1407,7 @@ int lexb_selftest_bounded_wait(lexb_gpu* g, uint32_t limit_us) {
     if (rc) return rc;
     if (limit_us == 0 || limit_us > 1000000u) return fail(LEXB_ERR_ARG, "limit_us must be in [1, 1000000]");
     const long long cycles = static_cast<long long>(limit_us) * (g->prop.clockRate / 1000);   // clockRate is kHz
+    INJECT_LAUNCH();
     bounded_wait_selftest_kernel<<<1, 32, 0, g->stream>>>(g->d_status, cycles);
     CUDA_TRY(cudaGetLastError());
     CUDA_TRY(cudaStreamSynchronize(g->stream));
@@ -1288,7 +1426,8 @@ int lexb_dequant_fp4_f16(lexb_gpu* g, uint32_t n, uint32_t k, const lexb_buffer*
     if ((rc = check_buf(w_f16, g, nn * kk * 2, "w_f16"))) return rc;
     const size_t groups = nn * kk / 16;
     const uint32_t threads = 256;
-    const uint32_t blocks = static_cast<uint32_t>(std::min<size_t>((groups + threads - 1) / threads, 148u * 32u));
+    const uint32_t blocks = static_cast<uint32_t>(std::min<size_t>((groups + threads - 1) / threads, static_cast<size_t>(g->prop.multiProcessorCount) * 32u));
+    INJECT_LAUNCH();
     dequant_fp4_f16_kernel<<<blocks, threads, 0, g->stream>>>(n, k, static_cast<const uint8_t*>(wq->ptr),
                                                               static_cast<const uint8_t*>(ws->ptr),
                                                               static_cast<const float*>(wg->ptr),
@@ -1329,9 +1468,11 @@ int lexb_gemm_fp4_splitk_static(lexb_gpu* g, uint32_t m, uint32_t n, uint32_t k,
     p.kernel = KERNEL_TCGEN05_PAIR;
     p.m = m; p.n = n; p.k = k;
     p.residual = r != nullptr;
-    p.tok_blocks = 2; p.tm = lexb::PAIR_TOKENS; p.stages = 4; p.w_stages = 3; p.tmem_cols = lexb::PAIR_TMEM_COLS; p.n_acc = 1; p.flags = 0;
+    // one block of 256 tokens per tile up to m = 256, two beyond: the shape lexb_gemm_fp4_plan gives the same m
+    p.tok_blocks = m > 256u ? 2u : 1u;
+    p.tm = p.tok_blocks * 256u; p.stages = 4; p.w_stages = 3; p.tmem_cols = lexb::PAIR_TMEM_COLS; p.n_acc = 1; p.flags = 0;
     p.kc = 0;
-    p.m_tiles = (m + lexb::PAIR_TOKENS - 1) / lexb::PAIR_TOKENS;
+    p.m_tiles = (m + p.tm - 1) / p.tm;
     p.k_splits = splits;
     p.kb_per_split = rb_per_split * (lexb::PAIR_RAW_K / lexb::GEMM_BK);
     p.grid = 2u * p.m_tiles * ((n + 2u * lexb::GEMM_TN - 1) / (2u * lexb::GEMM_TN)) * splits;
@@ -1365,14 +1506,16 @@ int lexb_gemm_fp4_splitk_static(lexb_gpu* g, uint32_t m, uint32_t n, uint32_t k,
     a.trace = nullptr;
     a.m = m; a.n = n; a.k = k;
     a.tm = p.tm; a.stages = p.stages; a.w_stages = p.w_stages; a.flags = 0;
-    a.k_splits = splits; a.kb_per_split = p.kb_per_split; a.tok_blocks = 2;
+    a.k_splits = splits; a.kb_per_split = p.kb_per_split; a.tok_blocks = p.tok_blocks;
     a.partial = g->static_scratch;          // every element of the partials is written before it is read: nothing to clear
     a.tmem_cols = p.tmem_cols; a.m_tiles = p.m_tiles; a.n_acc = 1;
     a.x_tx_bytes = lexb::PAIR_XBLK_BYTES;
+    INJECT_LAUNCH();
     lexb::gemm_fp4_tcgen05_pair_kernel<false><<<p.grid, p.threads, p.smem, g->stream>>>(map_x, map_wq, map_ws, a);
     CUDA_TRY(cudaGetLastError());
     const size_t elems = mm * nn;
-    const uint32_t blocks = static_cast<uint32_t>(std::min<size_t>((elems / 4 + 255) / 256, 148u * 8u));
+    const uint32_t blocks = static_cast<uint32_t>(std::min<size_t>((elems / 4 + 255) / 256, static_cast<size_t>(g->prop.multiProcessorCount) * 8u));
+    INJECT_LAUNCH();
     lexb::splitk_reduce_kernel<<<blocks, 256, 0, g->stream>>>(g->static_scratch, splits, elems, a.r, a.y, lexb::GatherDst{});
     CUDA_TRY(cudaGetLastError());
     return LEXB_OK;
@@ -1392,9 +1535,10 @@ int lexb_silu_mul(lexb_gpu* g, uint32_t rows, uint32_t cols, const lexb_buffer* 
     if ((rc = check_buf(up, g, need_u, "up"))) return rc;
     if ((rc = check_buf(out, g, static_cast<size_t>(rows) * cols * (out_f16 ? 2 : 4), "out"))) return rc;
     const size_t total = static_cast<size_t>(rows) * (cols / 4u);
-    const uint32_t blocks = static_cast<uint32_t>(std::min<size_t>((total + 255) / 256, 148u * 16u));
+    const uint32_t blocks = static_cast<uint32_t>(std::min<size_t>((total + 255) / 256, static_cast<size_t>(g->prop.multiProcessorCount) * 16u));
     const float* gp = static_cast<const float*>(gate->ptr) + gate_offset;
     const float* up_ = static_cast<const float*>(up->ptr) + up_offset;
+    INJECT_LAUNCH();
     if (out_f16)
         silu_mul_kernel<uint16_t><<<blocks, 256, 0, g->stream>>>(rows, cols, gp, gate_pitch, up_, up_pitch, static_cast<uint16_t*>(out->ptr));
     else
@@ -1428,6 +1572,19 @@ int lexb_prefill_chunks(uint32_t tokens, uint32_t limit, int gemm_ok, uint32_t* 
         left -= take;
     }
     *count = n;
+    return LEXB_OK;
+}
+
+int lexb_debug_fail_next(int site, int nth, int cuda_error) {
+    if (site < 0 || site >= SITE_COUNT) return fail(LEXB_ERR_ARG, "lexb_debug_fail_next: site %d outside [0, %d]", site, SITE_COUNT - 1);
+    if (nth < 0 || cuda_error < 0) return fail(LEXB_ERR_ARG, "lexb_debug_fail_next: negative argument");
+    std::lock_guard<std::mutex> lk(g_inject_lock);
+    if (site == 0) {
+        for (auto& in : g_inject) in = Injection{};
+        return LEXB_OK;
+    }
+    g_inject[site].countdown = nth;
+    g_inject[site].error = cuda_error ? cuda_error : static_cast<int>(cudaErrorUnknown);
     return LEXB_OK;
 }
 

@@ -30,7 +30,7 @@ SYMBOLS = [
     "lexb_run_launches", "lexb_list_runs", "lexb_run_each_timed", "lexb_time_launches", "lexb_status_word",
     "lexb_selftest_bounded_wait", "lexb_dequant_fp4_f16", "lexb_shard_rows", "lexb_trace_enable", "lexb_trace_read",
     "lexb_gemm_fp4_splitk_static", "lexb_gemm_fp4_launch_gather", "lexb_silu_mul", "lexb_prefill_chunks",
-    "lexb_matmul_fp4_plan",
+    "lexb_matmul_fp4_plan", "lexb_debug_fail_next",
 ]
 
 
@@ -53,6 +53,8 @@ class Sched(ctypes.Structure):
 
 
 SCHED_WEIGHTS_MAY_CHANGE = 1
+SCHED_WEIGHTS_CONSTANT = 2
+SITE_ALLOC, SITE_COPY, SITE_LAUNCH, SITE_ENCODE = 1, 2, 3, 4
 
 
 class Lowered(ctypes.Structure):
@@ -125,6 +127,7 @@ def load_library() -> ctypes.CDLL:
     L.lexb_gemm_fp4_launch_gather.argtypes = [vp, vp, vp, vp, vp, vp, vp, POINTER(vp), u32, u32, u32]
     L.lexb_gemm_fp4_splitk_static.argtypes = [vp, u32, u32, u32, u32, vp, vp, vp, vp, vp, vp]
     L.lexb_trace_read.argtypes = [vp, vp, u32]
+    L.lexb_debug_fail_next.argtypes = [c_int, c_int, c_int]
     _lib = L
     return L
 
@@ -132,6 +135,12 @@ def load_library() -> ctypes.CDLL:
 def _check(rc: int) -> None:
     if rc != 0:
         raise LexbError(rc, load_library().lexb_last_error().decode(errors="replace"))
+
+
+def debug_fail_next(site: int, nth: int = 1, cuda_error: int = 0) -> None:
+    """Tests of the error paths: the nth call from now that reaches `site` (SITE_ALLOC, SITE_COPY, SITE_LAUNCH,
+    SITE_ENCODE) reports a CUDA error instead of being made; site 0 disarms everything."""
+    _check(load_library().lexb_debug_fail_next(site, nth, cuda_error))
 
 
 def prefill_chunks(tokens: int, limit: int = 0, gemm_ok: bool = True) -> list[int]:
@@ -331,10 +340,15 @@ class Gpu:
         return Pipeline(self, h.value)
 
     def plan_matmul_fp4(self, t: int, n_out: int, n_in: int, residual: bool = False, x_half: bool = True,
-                        stages: int = 0, k_splits: int = 0, weights_may_change: bool = False) -> Pipeline:
+                        stages: int = 0, k_splits: int = 0, weights_may_change: bool = False,
+                        weights_constant: bool = False) -> Pipeline:
         """matmul_q_x with the NVFP4 layout for t <= 32 tokens (llama.rs:444-499): weights as f32, not
-        rounded to f16; runs on the block-scaled FP4 tensor-core path."""
-        s = Sched(0, 0, stages, 0, 0, k_splits, SCHED_WEIGHTS_MAY_CHANGE if weights_may_change else 0)
+        rounded to f16; runs on the block-scaled FP4 tensor-core path.  Launches are in order on their stream;
+        `weights_constant` promises that nothing writes wq/ws while launches are in flight, so that a launch
+        made on its own may load them ahead of the stream's order (inside a step list the library works that
+        out itself unless `weights_may_change`)."""
+        flags = (SCHED_WEIGHTS_MAY_CHANGE if weights_may_change else 0) | (SCHED_WEIGHTS_CONSTANT if weights_constant else 0)
+        s = Sched(0, 0, stages, 0, 0, k_splits, flags)
         h = c_void_p()
         _check(self._L.lexb_matmul_fp4_plan(self.handle, t, n_out, n_in, int(residual), int(x_half), byref(s), byref(h)))
         return Pipeline(self, h.value)

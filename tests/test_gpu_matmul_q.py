@@ -530,3 +530,66 @@ def test_a_chain_whose_steps_feed_each_other(gpu):
             assert scale > 1e-3 and err <= 1e-4 * (i + 1), (i, err)             # each step inherits the steps before
             want = got                                                            # compare step by step
     assert gpu.status_word() == 0
+
+
+def test_launches_one_at_a_time_with_weights_declared_constant(gpu):
+    """The caller's promise (LEXB_SCHED_WEIGHTS_CONSTANT) lets a launch made on its own load its weights while
+    the launch ahead still runs; the results are those of the in-order default, bit for bit."""
+    m, n, k = 2, 1024, 2048
+    x = inputs.make_x(m, k, seed_base=440)
+    sets = [inputs.make_weights(n, k, seed_base=441, copy=c) for c in range(4)]
+    qs = [L.QBuf(gpu, *w) for w in sets]
+    xb = gpu.upload(x)
+    outs = {}
+    for const in (False, True):
+        pipe = gpu.plan_matmul_fp4(m, n, k, weights_constant=const)
+        ys = [gpu.alloc(4 * m * n) for _ in sets]
+        for rep in range(3):
+            for q, yb in zip(qs, ys):
+                gpu.run(pipe, q.bind(xb, None, yb))
+        gpu.sync()
+        outs[const] = [gpu.download(yb, np.float32, (m, n)) for yb in ys]
+    for a, b, w in zip(outs[False], outs[True], sets):
+        assert np.array_equal(a, b)
+        check(a, O.matmul_q_x(x, *w))
+    with pytest.raises(L.LexbError):
+        gpu.plan_matmul_fp4(m, n, k, weights_constant=True, weights_may_change=True)
+    assert gpu.status_word() == 0
+
+
+def test_a_step_whose_weights_an_earlier_step_of_the_list_writes(gpu):
+    """The in-order contract of the reference's launches (crates/lex-cuda/src/device.rs:629-672): step B's packed
+    codes are the bytes step A writes as its y.  The list must not start B's weight loads before A is done:
+    B is a launch of its own, and its result equals B launched after a synchronise, bit for bit."""
+    t = 8
+    n_a, k_a = 16384, 1024                      # y_A: 8 x 16384 f32 = 512 KiB
+    n_b, k_b = 1024, 1024                       # wq_B: 1024 x 512 bytes = 512 KiB
+    xa = inputs.make_x(t, k_a, seed_base=450)
+    wa = inputs.make_weights(n_a, k_a, seed_base=451)
+    _, ws_b, wg_b = inputs.make_weights(n_b, k_b, seed_base=452)
+    qa = L.QBuf(gpu, *wa)
+    xab = gpu.upload(xa)
+    ya = gpu.alloc(4 * t * n_a)
+    xbb = gpu.upload(inputs.make_x(t, k_b, seed_base=453))
+    wsb, wgb = gpu.upload(ws_b), gpu.upload(wg_b)
+    pa = gpu.plan_matmul_fp4(t, n_a, k_a, k_splits=1)
+    pb = gpu.plan_matmul_fp4(t, n_b, k_b, k_splits=1)
+    y_list, y_alone = gpu.alloc(4 * t * n_b), gpu.alloc(4 * t * n_b)
+    step_a = (pa, qa.bind(xab, None, ya))
+    bind_b = lambda y: [xbb, ya, wsb, wgb, y]
+    assert gpu.list_runs([step_a, (pb, bind_b(y_list))]) == [1, 1]
+    # reference order: A, wait, B
+    gpu.memset(ya, 0)
+    gpu.run(pa, step_a[1])
+    gpu.sync()
+    gpu.run(pb, bind_b(y_alone))
+    gpu.sync()
+    want = gpu.download(y_alone, np.float32, (t, n_b))
+    for _ in range(3):
+        gpu.memset(ya, 0)                       # codes of zeros: a B that ran early would give zeros
+        gpu.memset(y_list, 0xEE)
+        gpu.run_launches([step_a, (pb, bind_b(y_list))])
+        got = gpu.download(y_list, np.float32, (t, n_b))
+        assert np.array_equal(np.isnan(got), np.isnan(want)) and np.array_equal(np.nan_to_num(got), np.nan_to_num(want))
+    assert np.abs(np.nan_to_num(want)).max() > 0
+    assert gpu.status_word() == 0

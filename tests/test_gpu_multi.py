@@ -59,13 +59,18 @@ def _worker(rank, world, port, m, n, k, out_dir):
     dist.destroy_process_group()
 
 
-def test_fused_gather_equals_nccl_all_gather(tmp_path):
+@pytest.mark.parametrize("shape", ["whole tiles", "27B gate/up shard"])
+def test_fused_gather_equals_nccl_all_gather(tmp_path, shape):
+    """Every rank's gathered y, written by the other ranks' peer stores, equals the NCCL all-gather of the same
+    shards bit for bit and the oracle to tolerance.  The second shape is what each rank of an n-sharded 27B
+    gate/up call computes (2176 rows, k = 5120: the planner splits K, so the stores come from the reduction
+    launch)."""
     import torch
     import torch.multiprocessing as mp
-    world = min(torch.cuda.device_count(), 4)
+    world = min(torch.cuda.device_count(), 8)        # every GPU of the box: the gather takes up to 8 ranks
     if world < 2:
         pytest.skip("needs at least two GPUs")
-    m, n, k = 512, 256 * world * 2, 1024
+    m, n, k = (512, 256 * world * 2, 1024) if shape == "whole tiles" else (512, 2176 * world, 5120)
     mp.spawn(_worker, args=(world, _free_port(), m, n, k, str(tmp_path)), nprocs=world, join=True)
     sys.path.insert(0, str(ROOT))
     from lex_gpu_b200 import inputs
@@ -73,7 +78,7 @@ def test_fused_gather_equals_nccl_all_gather(tmp_path):
     assert int(np.load(tmp_path / "same.npy")[0]) == 1
     x, wq, ws, wg = inputs.make_case(m, n, k, seed_base=9)
     err, scale, rel = O.err_of_scale(np.load(tmp_path / "y.npy"), O.gemm_fp4(x, wq, ws, wg))
-    assert scale > 1e-3 and err <= 2e-3 and rel <= 2e-3
+    assert scale > 1e-3 and err <= 2e-3 and rel <= (2e-3 if k < 4096 else 1e-2)
 
 
 def _decode_worker(rank, world, port, m, n, k, out_dir):
@@ -108,7 +113,7 @@ def test_row_sharded_decode_matmul(tmp_path):
     """matmul_q_x with the rows of W split over the GPUs and the shards gathered by NCCL."""
     import torch
     import torch.multiprocessing as mp
-    world = min(torch.cuda.device_count(), 4)
+    world = min(torch.cuda.device_count(), 8)        # every GPU of the box: the gather takes up to 8 ranks
     if world < 2:
         pytest.skip("needs at least two GPUs")
     m, n, k = 3, 128 * world * 3, 2048

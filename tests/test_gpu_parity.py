@@ -463,3 +463,97 @@ def test_gather_epilogue_writes_every_ranks_y(gpu, m, n, k, splits):
         assert np.isnan(full[:, :n0]).all() and np.isnan(full[:, n0 + n:]).all()      # nothing else touched
     with pytest.raises(L.LexbError):
         gpu.run_gather(pipe, xb, q.wq, q.ws, q.wg, rb, [y.ptr for y in ys], n_total, n_total - 128)
+
+
+# ---------------------------------------------------------------- accuracy against exact arithmetic
+
+def _exact_slice(x, wq, ws, wg, lo, hi):
+    """y[:, lo:hi] in f64 from the oracle's own f16 weights: what both implementations approximate."""
+    w16 = O.dequant_fp4_f16(wq[lo:hi], ws[lo:hi], wg[lo:hi]).view(np.float16).astype(np.float64)
+    return x.astype(np.float64) @ w16.T
+
+
+def _against_exact(tag, got, oracle, exact):
+    """Errors of the GPU result and of the oracle against f64 arithmetic on the same slice; returns the ratio."""
+    scale = np.abs(exact).max()
+    assert scale > 1e-3
+    d_gpu, d_or = got.astype(np.float64) - exact, oracle.astype(np.float64) - exact
+    e_gpu, e_or = np.abs(d_gpu).max() / scale, np.abs(d_or).max() / scale
+    floor = np.maximum(np.abs(exact), 1e-3 * scale)
+    r_gpu, r_or = (np.abs(d_gpu) / floor).max(), (np.abs(d_or) / floor).max()
+    # a truncating accumulator loses magnitude: the error is then correlated with the sign of the result
+    bias_gpu = float((d_gpu * np.sign(exact)).mean()) / scale
+    bias_or = float((d_or * np.sign(exact)).mean()) / scale
+    print(f"  {tag}: of scale GPU {e_gpu:.2e} / oracle {e_or:.2e} (x{e_gpu / e_or:.1f}); per element GPU {r_gpu:.2e} / oracle {r_or:.2e}; "
+          f"mean signed error toward zero GPU {bias_gpu:+.2e} / oracle {bias_or:+.2e} of scale; rms GPU "
+          f"{np.sqrt((d_gpu ** 2).mean()) / scale:.2e} / oracle {np.sqrt((d_or ** 2).mean()) / scale:.2e}")
+    return e_gpu, e_or, r_gpu, r_or
+
+
+# Each tcgen05.mma adds its 16 products into the f32 accumulator with the low bits cut off, not rounded to
+# nearest, so an accumulator that takes all k/16 additions of a long contraction ends up a few units of the
+# oracle's own rounding error away from exact arithmetic, biased toward zero.  Where tensor memory has room for
+# two accumulators per tile (m <= 256) or K is split, the runs are shorter.  The bound asked of the kernels is
+# the reference's own (2e-3 of scale, crates/lex-cuda/tests/device_gpu.rs:294-303) with three decades to
+# spare, and a multiple of the oracle's own distance from exact arithmetic.
+EXACT_OF_SCALE = 5e-5
+EXACT_RATIO = {"short": 2.0, "long": 8.0}
+
+
+@pytest.mark.parametrize("m,n,k,run", [(512, 17408, 5120, "long"), (512, 5120, 17408, "long"), (2048, 5120, 17408, "long"),
+                                       (256, 17408, 5120, "long"), (512, 2176, 5120, "short"), (512, 1024, 2048, "short")])
+def test_gpu_error_against_exact_arithmetic(gpu, m, n, k, run):
+    """Distance of the GPU result from f64 arithmetic on the oracle's f16 weights, beside the oracle's own, on a
+    slice of 256 weight rows: of scale, per element, and the mean signed error toward zero."""
+    x, wq, ws, wg = inputs.make_case(m, n, k, seed_base=17)
+    got = L.gemm_fp4(gpu, x, wq, ws, wg)
+    lo, hi = n // 2 - 128, n // 2 + 128
+    want = O.gemm_fp4(x, wq, ws, wg, rows=(lo, hi))[:, lo:hi]
+    exact = _exact_slice(x, wq, ws, wg, lo, hi)
+    e_gpu, e_or, r_gpu, r_or = _against_exact(f"m={m} n={n} k={k}", got[:, lo:hi], want, exact)
+    assert e_gpu <= EXACT_OF_SCALE
+    assert e_gpu <= EXACT_RATIO[run] * e_or, f"GPU {e_gpu:e} vs oracle {e_or:e} of scale against exact arithmetic"
+
+
+# ---------------------------------------------------------------- the larger configurations and the shard shapes
+
+def _check_row_slices(got, x, wq, ws, wg, slices, rel_tol, r=None):
+    for lo, hi in slices:
+        want = O.gemm_fp4(x, wq, ws, wg, r=r, rows=(lo, hi))
+        check(got[:, lo:hi], want[:, lo:hi], rel_tol=rel_tol)
+
+
+def test_gemm_m2048_gate_up_shape(gpu):
+    """Configuration 3 at m = 2048 on the gate/up shape (n = 17408, k = 5120): oracle on three slices of rows."""
+    n, k = 17408, 5120
+    x, wq, ws, wg = inputs.make_case(2048, n, k, seed_base=4)
+    got = L.gemm_fp4(gpu, x, wq, ws, wg)
+    _check_row_slices(got, x, wq, ws, wg, [(0, 128), (n // 2, n // 2 + 128), (n - 128, n)], LONG_K_REL)
+
+
+@pytest.mark.parametrize("n,k", [(17408, 5120), (5120, 17408)])
+def test_gemm_m4096_stack_layer_shapes(gpu, n, k):
+    """Configuration 4's calls (m = 4096) on one GPU: oracle on two slices of rows, and the last m tile
+    against the same tokens run as a batch of their own."""
+    m = 4096
+    x, wq, ws, wg = inputs.make_case(m, n, k, seed_base=6)
+    got = L.gemm_fp4(gpu, x, wq, ws, wg, k_splits=1)
+    _check_row_slices(got, x, wq, ws, wg, [(256, 384), (n - 128, n)], LONG_K_REL)
+    sub = L.gemm_fp4(gpu, x[m - 512:].copy(), wq, ws, wg, k_splits=1)
+    assert np.array_equal(sub, got[m - 512:])
+
+
+@pytest.mark.parametrize("m", [512, 2048, 4096])
+@pytest.mark.parametrize("n,k", [(2176, 5120), (640, 17408), (4352, 5120), (1280, 17408), (8704, 5120), (2560, 17408)])
+def test_gemm_shard_shapes_with_the_planned_split(gpu, m, n, k):
+    """What one rank of 8, 4 or 2 computes (n/8, n/4, n/2 rows of the 27B MLP matrices) with the K split the
+    planner picks for it, against the oracle: the full product for m = 512, slices of rows beyond."""
+    x, wq, ws, wg = inputs.make_case(m, n, k, seed_base=n + m)
+    pipe = gpu.plan_gemm_fp4(m, n, k)
+    d = pipe.describe()
+    print(f"  m={m} n={n} k={k}: kernel {d.kernel}, k_splits {d.k_splits}, grid {d.grid}")
+    got = L.gemm_fp4(gpu, x, wq, ws, wg)
+    if m == 512:
+        check(got, O.gemm_fp4(x, wq, ws, wg), rel_tol=LONG_K_REL)
+    else:
+        _check_row_slices(got, x, wq, ws, wg, [(0, 128), (n - 128, n)], LONG_K_REL)

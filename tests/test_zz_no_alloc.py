@@ -42,7 +42,8 @@ def _static(gpu, x, wq, ws, wg, r, splits):
 
 
 def test_static_scratch_matches_the_planned_pipeline_on_two_calls_in_a_row(gpu):
-    cases = [(512, 384, 2048, 4, True, 11), (300, 256, 1024, 2, False, 12)]
+    # (192 tokens: one block of 256 tokens per tile, as the planner shapes m <= 256)
+    cases = [(512, 384, 2048, 4, True, 11), (300, 256, 1024, 2, False, 12), (192, 256, 1024, 2, True, 13)]
     for m, n, k, splits, with_r, seed in cases:
         x, wq, ws, wg = inputs.make_case(m, n, k, seed_base=seed)
         r = inputs.make_residual(m, n, seed_base=seed) if with_r else None
@@ -52,6 +53,27 @@ def test_static_scratch_matches_the_planned_pipeline_on_two_calls_in_a_row(gpu):
         assert np.array_equal(got, planned)
         err, scale, rel = O.err_of_scale(got, O.gemm_fp4(x, wq, ws, wg, r=r))
         assert scale > 1e-3 and err <= 2e-3 and rel <= 2e-3
+
+
+def test_static_scratch_calls_take_no_device_memory(gpu):
+    """What the entry point is for: once the first call on the device has resolved the array's address, further
+    calls leave the amount of free device memory where it was."""
+    import torch
+    m, n, k, splits = 512, 256, 1024, 2
+    x, wq, ws, wg = inputs.make_case(m, n, k, seed_base=14)
+    q = L.QBuf(gpu, wq, ws, wg)
+    xb, yb = gpu.upload(x), gpu.alloc(4 * m * n)
+    gpu.gemm_fp4_splitk_static(m, n, k, splits, q.bind(xb, None, yb))        # first call: set-up
+    gpu.sync()
+    torch.cuda.synchronize()
+    before = torch.cuda.mem_get_info()[0]
+    for _ in range(5):
+        gpu.gemm_fp4_splitk_static(m, n, k, splits, q.bind(xb, None, yb))
+    gpu.sync()
+    torch.cuda.synchronize()
+    assert torch.cuda.mem_get_info()[0] == before
+    err, scale, rel = O.err_of_scale(gpu.download(yb, np.float32, (m, n)), O.gemm_fp4(x, wq, ws, wg))
+    assert scale > 1e-3 and err <= 2e-3 and rel <= 2e-3
 
 
 def test_static_scratch_refuses_what_does_not_fit(gpu):
