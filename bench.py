@@ -34,8 +34,8 @@ ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
 
 M, N_ROWS, K = 512, 17408, 5120
-# DRAM bytes per launch of the block-scaled matmul_q_x kernel at (17408, 5120), from the ncu capture under
-# profiles/: 50.26 MB read, 9 KB written
+# DRAM bytes per launch of the block-scaled matmul_q_x kernel at (17408, 5120), from an ncu capture
+# (dram__bytes_read.sum + dram__bytes_write.sum): 50.26 MB read, 9 KB written
 MQ_TRAFFIC = 50.27e6
 METRIC = "gemm_fp4 TFLOP/s at m=512 (27B MLP gate/up: n=17408 k=5120)"
 
@@ -92,9 +92,22 @@ class ClockSampler:
         mhz = [float(p[0]) for p in inside if p[0].replace(".", "").isdigit()]
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         reasons = [n for i, n in enumerate(names) if any(p[3 + i].lower().startswith("active") for p in inside)]
+        bins = {}
+        for v in mhz:
+            key = str(int(v // 100 * 100))
+            bins[key] = bins.get(key, 0) + 1
         return {"sm_mhz": statistics.median(mhz) if mhz else None,
                 "sm_max_mhz": float(inside[0][1]) if inside[0][1].replace(".", "").isdigit() else None,
-                "samples": len(inside), "reasons": reasons}
+                "samples": len(inside), "reasons": reasons, "samples_by_100mhz": bins}
+
+
+def host_cores() -> int:
+    """Cores this process may run on.  The launcher of multi-rank runs exports OMP_NUM_THREADS=1, so the count is
+    passed to the oracle explicitly rather than left to OpenMP's default."""
+    try:
+        return len(os.sched_getaffinity(0))
+    except AttributeError:
+        return os.cpu_count() or 1
 
 
 def _cpu_time_rows(x, rows: int):
@@ -102,7 +115,7 @@ def _cpu_time_rows(x, rows: int):
     from oracle import oracle as O
     wq, ws, wg = inputs.make_weights(rows, K)
     t = time.perf_counter()
-    O.gemm_fp4(x, wq, ws, wg)
+    O.gemm_fp4(x, wq, ws, wg, threads=host_cores())
     return time.perf_counter() - t
 
 
@@ -117,7 +130,7 @@ def cpu_leg(target_seconds: float = 12.0):
     rows = int(min(N_ROWS, max(probe, probe * target_seconds / max(dt, 1e-6))) // 128 * 128)
     dt = _cpu_time_rows(x, rows)
     tflops = 2.0 * M * rows * K / dt / 1e12
-    return {"value": tflops, "unit": "TFLOP/s", "cores": O.max_threads(), "kind": "port",
+    return {"value": tflops, "unit": "TFLOP/s", "cores": host_cores(), "kind": "port",
             "sample": f"{rows} of {N_ROWS} weight rows, all {M} tokens, k={K}: {dt:.2f} s"}
 
 
@@ -142,7 +155,7 @@ def run_reference(args):
     for _ in range(args.steps):
         secs += _cpu_time_rows(x, rows)
     val = 2.0 * M * rows * K * args.steps / secs / 1e12
-    info = {"value": val, "unit": "TFLOP/s", "cores": O.max_threads(), "kind": "port",
+    info = {"value": val, "unit": "TFLOP/s", "cores": host_cores(), "kind": "port",
             "sample": f"{rows} of {N_ROWS} weight rows per step, all {M} tokens, k={K}"}
     line = {"impl": "reference", "metric": METRIC, "value": val, "unit": "TFLOP/s", "n_gpus": args.gpus,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * secs / args.steps,
@@ -193,6 +206,7 @@ def run_ours(args):
     x_t = torch.from_numpy(x_np.view(np.int16)).to(dev)
     xb = gpu.wrap_tensor(x_t)
     weights = []
+    w0_host = None
     # enough copies of this rank's slab to exceed the L2 (126 MB) several times over
     wbytes_one = n_local * K // 2 + n_local * K // 16 + 4 * n_local
     COPIES = max(8, -(-400_000_000 // wbytes_one))
@@ -203,6 +217,8 @@ def run_ours(args):
             # a rank generates only its own slab (same distributions, its own seed): generating and
             # slicing the whole matrix on every rank would cost minutes of host time
             wq, ws, wg = inputs.make_weights(n_local, K, seed_base=10_000 * (rank + 1), copy=c)
+        if c == 0:
+            w0_host = (wq, ws, wg)
         t = [torch.from_numpy(np.ascontiguousarray(a)).to(dev) for a in (wq, ws, wg)]
         weights.append((t, [gpu.wrap_tensor(v) for v in t]))
     y_t = torch.empty((M, n_local), dtype=torch.float32, device=dev)
@@ -244,6 +260,40 @@ def run_ours(args):
         _, bufs = weights[i % COPIES]
         gpu.run(pipe, [xb, bufs[0], bufs[1], bufs[2], yb])
 
+    # ---- parity gate: before anything is timed, 128-row slices of this rank's y against the oracle (the checker);
+    # a run that fails it prints no value
+    from oracle import oracle as O
+
+    def slice_errors(y_np, w_host, col0, slices, x_host=x_np):
+        worst = (0.0, 0.0)
+        for lo, hi in slices:
+            want = O.gemm_fp4(x_host, *w_host, rows=(lo, hi), threads=host_cores())[:, lo:hi]
+            err, scale, rel = O.err_of_scale(y_np[:, col0 + lo:col0 + hi], want)
+            if not (scale > 1e-3 and np.isfinite(y_np[:, col0 + lo:col0 + hi]).all()):
+                return (float("inf"), float("inf"))
+            worst = (max(worst[0], err), max(worst[1], rel))
+        return worst
+
+    def all_ranks_max(v):
+        if dist is None:
+            return v
+        tt = torch.tensor(list(v), device=dev, dtype=torch.float64)
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        return tuple(float(t) for t in tt)
+
+    GATE = 2e-3
+    y_t.fill_(float("nan"))
+    with torch.cuda.stream(stream):
+        gemm_step(0)
+    barrier()
+    row_slices = [(0, 128), (n_local // 2 // 128 * 128, n_local // 2 // 128 * 128 + 128), (n_local - 128, n_local)]
+    p_err, p_rel = all_ranks_max(slice_errors(y_t.cpu().numpy(), w0_host, 0, row_slices))
+    parity = {"gate_of_scale": GATE, "of_scale": p_err, "per_element_floor_1e-3_of_scale": p_rel,
+              "checked": f"{len(row_slices)} slices of 128 weight rows x all {M} tokens of every rank's y against the CPU oracle",
+              "ok": bool(p_err <= GATE)}
+    if not parity["ok"]:
+        raise SystemExit(f"parity gate failed before timing: {p_err:e} of scale (gate {GATE:e}); no value is reported")
+
     # long enough for the clock sampler to see the load: repeat the measured block
     full = args.only == "all"
     if args.only == "matvec":
@@ -262,13 +312,26 @@ def run_ours(args):
     tflops = flops_step * args.steps / secs / 1e12
     per_launch = secs / args.steps
     local_flops = 2.0 * M * n_local * K
-    # DRAM bytes per launch (read + write) from the ncu capture summarised under profiles/
+    # DRAM bytes per launch (read + write) from an ncu capture of this kernel
     # (m=512 n=17408 k=5120 on one GPU: 55.5 MB read, 3.2 MB written, y still in L2); only for that shape
     gemm_traffic = 58.7e6 if world == 1 else None
     roofline = {"bound": "tensor", "achieved": local_flops / per_launch / 1e12, "peak": peaks["tflops"],
                 "unit": "TFLOP/s", "frac": local_flops / per_launch / 1e12 / peaks["tflops"], "traffic": gemm_traffic,
                 "peak_source": f"{peaks['source']} bf16 burst (cuBLAS 8192^3)", "kernel": desc.entry.decode(),
                 "frac_of_nominal_2250": local_flops / per_launch / 1e12 / 2250.0}
+
+    # ---- the same steps for seconds, not milliseconds: what the kernel holds under the power cap, with the clocks
+    # sampled over this very region and the fraction taken against the sustained cuBLAS figure
+    sustained = None
+    if full:
+        n_sus = int(min(200_000, max(args.steps, 2.5 / per_launch)))
+        s_sus, c_sus = timed(pipe, gemm_step, n_sus, 3, sample_clocks=True)
+        tf_sus = flops_step * n_sus / s_sus / 1e12
+        peak_sus = peaks.get("tflops_sustained") or peaks["tflops"]
+        sustained = {"value": tf_sus, "unit": "TFLOP/s", "steps": n_sus, "seconds": s_sus, "ms_per_step": 1e3 * s_sus / n_sus,
+                     "frac_of_sustained_peak": (local_flops * n_sus / s_sus / 1e12) / peak_sus, "sustained_peak": peak_sus,
+                     "frac_of_nominal_2250": (local_flops * n_sus / s_sus / 1e12) / 2250.0, "clocks": c_sus,
+                     "us_x_median_mhz": (1e6 * s_sus / n_sus) * c_sus["sm_mhz"] if c_sus and c_sus.get("sm_mhz") else None}
 
     # ---- e2e: host x -> device, launch, y -> host, every step, through the C ABI call
     e2e, checksum = None, None
@@ -297,19 +360,21 @@ def run_ours(args):
         # The same steps double-buffered: two streams, two sets of staging buffers, lexb_gemm_fp4_enqueue_host.
         # Every step still copies its x in and its y out inside the timed region; step i's copy back overlaps
         # step i+1's copy in and launch.
+        # Each lane has its own pipeline: a pipeline planned with a K split owns one split-K workspace, and two
+        # launches of it must not overlap on two streams.
         stream2 = torch.cuda.Stream(device=dev)
-        lanes = [(stream, hx, hy, xd, yd)]
+        lanes = [(stream, hx, hy, xd, yd, pipe)]
         hx2 = L.HostBuffer(x_np.nbytes)
         hx2.array(np.float16, (M, K))[:] = x_np
         hy2 = L.HostBuffer(M * n_local * 4)
-        lanes.append((stream2, hx2, hy2, gpu.alloc(x_np.nbytes), gpu.alloc(M * n_local * 4)))
+        lanes.append((stream2, hx2, hy2, gpu.alloc(x_np.nbytes), gpu.alloc(M * n_local * 4), gpu.plan_gemm_fp4(M, n_local, K)))
 
         def piped(nsteps, first):
             for i in range(nsteps):
-                st, h_x, h_y, d_x, d_y = lanes[i % 2]
+                st, h_x, h_y, d_x, d_y, lane_pipe = lanes[i % 2]
                 gpu.set_stream(st.cuda_stream)
                 b = weights[(first + i) % COPIES][1]
-                gpu.enqueue_host(pipe, h_x.ptr, d_x, b[0], b[1], b[2], None, d_y, h_y.ptr)
+                gpu.enqueue_host(lane_pipe, h_x.ptr, d_x, b[0], b[1], b[2], None, d_y, h_y.ptr)
             torch.cuda.synchronize(dev)
 
         piped(4, 0)
@@ -322,7 +387,15 @@ def run_ours(args):
             tt = torch.tensor([e2e_secs], device=dev, dtype=torch.float64)
             dist.all_reduce(tt, op=dist.ReduceOp.MAX)
             e2e_secs = float(tt.item())
-        checksum2 = float(hy2.array(np.float32, (M, n_local))[0, :8].sum())
+        # what each lane brought back last, against the same weight sets run one step at a time on one stream
+        lanes_ok = True
+        for lane, i_last in ((0, e2e_steps - 2 + (e2e_steps % 2)), (1, e2e_steps - 1 - (e2e_steps % 2))):
+            got_lane = lanes[lane][2].array(np.float32, (M, n_local)).copy()
+            b = weights[(4 + i_last) % COPIES][1]
+            gpu.run_host(pipe, hx.ptr, xd, b[0], b[1], b[2], None, yd, hy.ptr)
+            lanes_ok = lanes_ok and np.array_equal(got_lane, hy.array(np.float32, (M, n_local)))
+        if all_ranks_max((0.0 if lanes_ok else 1.0,))[0] != 0.0:
+            raise SystemExit("the double-buffered end-to-end leg returned a y that differs from the single-stream result")
         e2e = {"value": flops_step * e2e_steps / e2e_secs / 1e12, "unit": "TFLOP/s",
                "h2d_bytes_per_step": int(x_np.nbytes), "d2h_bytes_per_step": int(M * n_local * 4), "steps": e2e_steps,
                "ms_per_step": 1e3 * e2e_secs / e2e_steps,
@@ -330,7 +403,7 @@ def run_ours(args):
                        "resident; one step's copy back overlaps the next step's copy in and launch",
                "one_stream": {"value": flops_step * e2e_steps / serial_secs / 1e12, "ms_per_step": 1e3 * serial_secs / e2e_steps,
                               "note": "lexb_gemm_fp4_run_host, one step at a time"},
-               "checksum_second_lane": checksum2}
+               "lanes_equal_single_stream": True}
 
     # ---- matvec (m = 1, 4): GB/s of weight bytes
     matvec = {}
@@ -363,6 +436,12 @@ def run_ours(args):
 
         s_mq, _ = timed(p_mq, mq_step, mv_steps, max(args.warmup, 20) if full else args.warmup)
         per_q_single = s_mq / mv_steps
+        # launched one at a time the kernel reads in order; with the caller's promise that nothing writes the
+        # weights (LEXB_SCHED_WEIGHTS_CONSTANT) it loads them while the launch ahead still runs
+        p_mq_c = gpu.plan_matmul_fp4(mm, n_local, K, weights_constant=True)
+        s_mqc, _ = timed(p_mq_c, lambda i, p_mq_c=p_mq_c, xs=xs, ys=ys: gpu.run(p_mq_c, [xs] + list(weights[i % COPIES][1]) + [ys]),
+                         mv_steps, max(args.warmup, 20) if full else args.warmup)
+        per_q_single_const = s_mqc / mv_steps
         # The same launches as step lists through lexb_run_launches (Gpu::run_launches, how the runtime issues a
         # layer's dispatches).  The library runs consecutive steps that do not depend on one another as one
         # persistent kernel whose blocks stride over all their row tiles; a step that reads or overwrites what
@@ -411,7 +490,8 @@ def run_ours(args):
             "kernel": p_mq.describe().entry.decode(), "gbs_weight_bytes": wbytes_local / per_q / 1e9 * world,
             "us_per_launch": per_q * 1e6,
             "issued_as": "one step list (lexb_run_launches), outputs alternating between two buffers: runs of two steps",
-            "us_per_launch_issued_one_by_one": per_q_single * 1e6, "roofline": hbm(per_q),
+            "us_per_launch_issued_one_by_one": per_q_single * 1e6,
+            "us_per_launch_issued_one_by_one_weights_declared_constant": per_q_single_const * 1e6, "roofline": hbm(per_q),
             "independent_steps": {"issued_as": "one step list, every step with its own output: one run",
                                   "gbs_weight_bytes": wbytes_local / per_q_run / 1e9 * world,
                                   "us_per_launch": per_q_run * 1e6, "roofline": hbm(per_q_run)},
@@ -428,9 +508,12 @@ def run_ours(args):
             all_gather_y(y_t, shard)        # NCCL, ordered after the launch on the same stream
 
         s_ag, _ = timed(pipe, ag_step, args.steps, args.warmup)
+        # the floor of any gather: the NCCL all-gather of the same bytes with nothing else in the step
+        s_only, _ = timed(pipe, lambda i: all_gather_y(y_t, shard), args.steps, args.warmup)
         allgather = {"value": flops_step * args.steps / s_ag / 1e12, "unit": "TFLOP/s",
                      "ms_per_step": 1e3 * s_ag / args.steps, "bytes_per_rank": int(M * shard.max_rows() * 4),
-                     "layout": "[N][m][max rows per rank]"}
+                     "layout": "[N][m][max rows per rank]", "gather_only_us": 1e6 * s_only / args.steps,
+                     "gemm_only_us": 1e6 * per_launch}
         # the same gather fused into the kernel: peer stores into every rank's y[m, n] (symmetric memory),
         # one cross-rank barrier per step
         try:
@@ -444,13 +527,29 @@ def run_ours(args):
                     sy.barrier()
 
                 s_fu, _ = timed(pipe, fused_step, args.steps, args.warmup)
+                # parity of the gathered y: the columns another rank stored here, against the oracle on that
+                # rank's weights (regenerated on the host from its seed)
+                sy.tensor.fill_(float("nan"))
+                sy.barrier()
+                fused_step(0)
+                torch.cuda.synchronize(dev)
+                other = (rank + 1) % world
+                o0, o1 = L.shard_rows(N_ROWS, world, other)
+                w_other = inputs.make_weights(o1 - o0, K, seed_base=10_000 * (other + 1), copy=0)
+                g_err, g_rel = all_ranks_max(slice_errors(sy.tensor.cpu().numpy(), w_other, o0, [(0, 128), (o1 - o0 - 128, o1 - o0)]))
+                sy.barrier()
+            if not g_err <= GATE:
+                raise SystemExit(f"parity gate failed on the gathered y: {g_err:e} of scale")
             allgather["fused_peer_stores"] = {"value": flops_step * args.steps / s_fu / 1e12, "unit": "TFLOP/s",
                                               "ms_per_step": 1e3 * s_fu / args.steps, "layout": "[m][n] on every rank",
-                                              "note": "epilogue stores to all ranks over NVLink + one barrier per step"}
+                                              "note": "epilogue stores to all ranks over NVLink + one barrier per step",
+                                              "parity_of_scale": g_err}
+        except SystemExit:
+            raise
         except Exception as e:      # symmetric memory unavailable on this machine
             allgather["fused_peer_stores"] = {"unavailable": repr(e)[:200]}
 
-    # ---- one layer of the 27B MLP stack at m = 4096 (benchmark configuration 4 of BASELINE.json), n-sharded: gate, up (n=17408,
+    # ---- one layer of the 27B MLP stack at m = 4096 (the 64-layer stack configuration), n-sharded: gate, up (n=17408,
     # k=5120) and down (n=5120, k=17408), independent calls, y not chained.  Reported, not the headline.
     stack = None
     if full and args.stack:
@@ -486,6 +585,46 @@ def run_ours(args):
                  "layers_timed": n_layers}
         del keep
 
+    # ---- the reference's own CUDA kernels, compiled for sm_100a from its tree (oracle/_ref): the bar on this box.
+    # Same shapes, same rotation of weight copies, same event timing; f32 x for its matvec, as it is emitted.
+    ref_box = None
+    if world == 1 and full:
+        from oracle import refkernels as R
+        ref_box = {}
+        try:
+            entry = R.gemm_entry(M, N_ROWS, K)
+            yr = torch.empty((M, N_ROWS), dtype=torch.float32, device=dev)
+
+            def ref_gemm_step(i):
+                t = weights[i % COPIES][0]
+                R.run_torch(entry, [x_t, t[0], t[1], t[2], yr], stream.cuda_stream)
+
+            n_ref = max(8, min(args.steps, 24))
+            s_ref, _ = timed(None, ref_gemm_step, n_ref, 3)
+            err, scale, _ = O.err_of_scale(yr[:, :128].cpu().numpy(),
+                                           O.gemm_fp4(x_np, *inputs.make_weights(N_ROWS, K, copy=(3 + n_ref - 1) % COPIES), rows=(0, 128),
+                                                      threads=host_cores())[:, :128])
+            ref_box["gemm"] = {"kernel": R.info(entry), "tflops": flops_step * n_ref / s_ref / 1e12, "us_per_launch": 1e6 * s_ref / n_ref,
+                               "source": "crates/lex-msl/src/gemm.rs:89-320 instantiated for this shape, nvcc sm_100a",
+                               "of_scale_vs_oracle": err, "ours_over_reference": (s_ref / n_ref) / per_launch}
+        except Exception as e:
+            ref_box["gemm"] = {"unavailable": repr(e)[:200]}
+        try:
+            x32 = x_t[:1].view(torch.float16).float().contiguous()
+            yv = torch.empty((1, N_ROWS), dtype=torch.float32, device=dev)
+
+            def ref_mv_step(i):
+                t = weights[i % COPIES][0]
+                R.run_torch(R.MATVEC_ENTRY, [x32, t[0], t[1], t[2], yv], stream.cuda_stream)
+
+            s_rv, _ = timed(None, ref_mv_step, 200, 20)
+            per_rv = s_rv / 200
+            ref_box["matvec"] = {"kernel": R.info(R.MATVEC_ENTRY), "us_per_launch": 1e6 * per_rv,
+                                 "gbs_weight_bytes": wbytes_local / per_rv / 1e9, "frac_of_hbm_peak": wbytes_local / per_rv / 1e9 / peaks["hbm_gbs"],
+                                 "source": "crates/lex-msl/tests/golden/matvec_nvfp4_17408x5120_cuda.cu unchanged, nvcc sm_100a"}
+        except Exception as e:
+            ref_box["matvec"] = {"unavailable": repr(e)[:200]}
+
     if rank == 0:
         info = cpu_leg() if (world == 1 and full) else None
         line = {"metric": METRIC, "value": tflops, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
@@ -499,7 +638,8 @@ def run_ours(args):
                                         "grid": desc.grid, "threads": desc.threads, "smem": desc.threadgroup_bytes}},
                 "roofline": roofline, "cpu_baseline": info, "e2e": e2e, "gpu_launches": args.steps,
                 "clocks": clocks, "matvec": matvec, "allgather": allgather, "device_status": status,
-                "checksum": checksum, "only": args.only, "stack_m4096": stack}
+                "checksum": checksum, "only": args.only, "stack_m4096": stack, "parity": parity, "sustained": sustained,
+                "reference_kernels_on_this_box": ref_box}
         print(json.dumps(line))
     if dist is not None:
         dist.barrier()

@@ -7,7 +7,7 @@ decode_tables.npz comes from the reference's own Python statement of the two for
 dequantised f32 weights of a small seeded matrix formed with those tables in that script's order
 (`E2M1[nib] * scale`, then `* gs`, scripts/qwen_nvfp4.py:88-92).  The oracle is checked against them.
 
-config0.npz holds this repository's oracle outputs for benchmark configuration 0 of BASELINE.json (m = n = 128, k = 64, seeded
+config0.npz holds this repository's oracle outputs for the README's CPU-interpreter example (m = n = 128, k = 64, seeded
 inputs of lex_gpu_b200/inputs.py): y and the f16 bit patterns of the staged weights.  The reference keeps
 no stored outputs for gemm_fp4, so this one is a regression pin of the oracle, not a reference vector.
 """

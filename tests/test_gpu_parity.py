@@ -104,7 +104,7 @@ def test_matvec_residual(gpu):
 @pytest.mark.parametrize("m", [1, 4])
 @pytest.mark.parametrize("n,k", [(17408, 5120), (5120, 17408)])
 def test_matvec_benchmark_shapes(gpu, m, n, k):
-    """Benchmark configuration 1 of BASELINE.json at full size, against the full oracle."""
+    """The decode / spec-verify matvec configuration (m in {1, 4} at the 27B MLP shapes) at full size, against the full oracle."""
     x, wq, ws, wg = inputs.make_case(m, n, k)
     got = L.gemm_fp4(gpu, x, wq, ws, wg)
     check(got, O.gemm_fp4(x, wq, ws, wg))
@@ -123,7 +123,7 @@ def test_a_token_does_not_depend_on_its_batch(gpu):
 # ---------------------------------------------------------------- tcgen05 path (m > 16)
 
 def test_gemm_config0_readme_example(gpu):
-    """m = n = 128, k = 64: one tile, one K step (configuration 0 of BASELINE.json); also against the committed fixture."""
+    """m = n = 128, k = 64: one tile, one K step (the README's CPU-interpreter example); also against the committed fixture."""
     from pathlib import Path
     x, wq, ws, wg = inputs.make_case(128, 128, 64)
     got = L.gemm_fp4(gpu, x, wq, ws, wg)
@@ -255,14 +255,14 @@ def test_gemm_wide_scale_range(gpu):
 
 @pytest.mark.parametrize("n,k", [(17408, 5120), (5120, 17408)])
 def test_gemm_27b_mlp_prefill_m512(gpu, n, k):
-    """Configuration 3 of BASELINE.json (m = 512) at full size against the full oracle."""
+    """The 27B MLP prefill configuration (m = 512) at full size against the full oracle."""
     x, wq, ws, wg = inputs.make_case(512, n, k)
     check(L.gemm_fp4(gpu, x, wq, ws, wg), O.gemm_fp4(x, wq, ws, wg), rel_tol=LONG_K_REL)
 
 
 @pytest.mark.parametrize("n,k", [(6144, 4096), (28672, 4096), (4096, 14336)])
 def test_gemm_llama8b_prefill_projections(gpu, n, k):
-    """Configuration 2 of BASELINE.json: oracle on a slice of rows (full n on the GPU)."""
+    """The Llama-3.1-8B-shaped prefill projections at m = 512: oracle on a slice of rows (full n on the GPU)."""
     x, wq, ws, wg = inputs.make_case(512, n, k, seed_base=2)
     got = L.gemm_fp4(gpu, x, wq, ws, wg)
     lo, hi = n // 2 - 256, n // 2 + 256
@@ -276,7 +276,7 @@ def test_gemm_llama8b_prefill_projections(gpu, n, k):
 
 
 def test_gemm_m2048_linearity_and_slices(gpu):
-    """m = 2048 (config 3's larger batch): oracle on row slices, and the size-independent
+    """m = 2048 (the larger prefill batch): oracle on row slices, and the size-independent
     property that the result for a sub-batch equals the same rows of the full batch."""
     n, k = 5120, 17408
     x, wq, ws, wg = inputs.make_case(2048, n, k, seed_base=3)
@@ -524,7 +524,7 @@ def _check_row_slices(got, x, wq, ws, wg, slices, rel_tol, r=None):
 
 
 def test_gemm_m2048_gate_up_shape(gpu):
-    """Configuration 3 at m = 2048 on the gate/up shape (n = 17408, k = 5120): oracle on three slices of rows."""
+    """The 27B MLP prefill at m = 2048 on the gate/up shape (n = 17408, k = 5120): oracle on three slices of rows."""
     n, k = 17408, 5120
     x, wq, ws, wg = inputs.make_case(2048, n, k, seed_base=4)
     got = L.gemm_fp4(gpu, x, wq, ws, wg)
@@ -533,7 +533,7 @@ def test_gemm_m2048_gate_up_shape(gpu):
 
 @pytest.mark.parametrize("n,k", [(17408, 5120), (5120, 17408)])
 def test_gemm_m4096_stack_layer_shapes(gpu, n, k):
-    """Configuration 4's calls (m = 4096) on one GPU: oracle on two slices of rows, and the last m tile
+    """The calls of the 64-layer stack configuration (m = 4096) on one GPU: oracle on two slices of rows, and the last m tile
     against the same tokens run as a batch of their own."""
     m = 4096
     x, wq, ws, wg = inputs.make_case(m, n, k, seed_base=6)
