@@ -34,6 +34,7 @@ static __device__ __align__(256) float g_splitk_static_scratch[LEXB_STATIC_SCRAT
 namespace {
 
 thread_local std::string g_last_error;
+thread_local bool t_injected = false;     // the failure being reported was made by lexb_debug_fail_next
 
 int fail(int code, const char* fmt, ...) {
     char buf[512];
@@ -42,6 +43,8 @@ int fail(int code, const char* fmt, ...) {
     vsnprintf(buf, sizeof buf, fmt, ap);
     va_end(ap);
     g_last_error = buf;
+    if (t_injected) g_last_error += " [injected]";
+    t_injected = false;
     return code;
 }
 
@@ -64,25 +67,26 @@ std::mutex g_inject_lock;
 cudaError_t take_injected(int site) {
     std::lock_guard<std::mutex> lk(g_inject_lock);
     Injection& in = g_inject[site];
-    if (in.countdown > 0 && --in.countdown == 0) return static_cast<cudaError_t>(in.error);
+    if (in.countdown > 0 && --in.countdown == 0) {
+        t_injected = true;
+        return static_cast<cudaError_t>(in.error);
+    }
     return cudaSuccess;
 }
 
 #define CUDA_TRY_AT(site, expr)                                                                 \
     do {                                                                                        \
         cudaError_t e_ = take_injected(site);                                                   \
-        const bool injected_ = e_ != cudaSuccess;                                               \
-        if (!injected_) e_ = (expr);                                                            \
+        if (e_ == cudaSuccess) e_ = (expr);                                                     \
         if (e_ != cudaSuccess)                                                                  \
-            return fail(LEXB_ERR_CUDA, "%s: %s (%s)%s", #expr, cudaGetErrorString(e_), cudaGetErrorName(e_), \
-                        injected_ ? " [injected]" : "");                                       \
+            return fail(LEXB_ERR_CUDA, "%s: %s (%s)", #expr, cudaGetErrorString(e_), cudaGetErrorName(e_)); \
     } while (0)
 #define LAUNCH_TRY(expr) CUDA_TRY_AT(SITE_LAUNCH, expr)
 // in front of a <<<...>>> launch
 #define INJECT_LAUNCH()                                                                         \
     do {                                                                                        \
         if (cudaError_t e_ = take_injected(SITE_LAUNCH))                                        \
-            return fail(LEXB_ERR_CUDA, "kernel launch: %s (%s) [injected]", cudaGetErrorString(e_), cudaGetErrorName(e_)); \
+            return fail(LEXB_ERR_CUDA, "kernel launch: %s (%s)", cudaGetErrorString(e_), cudaGetErrorName(e_)); \
     } while (0)
 
 cudaError_t x_malloc(void** p, size_t bytes) {
@@ -256,7 +260,7 @@ int encode_2d(const lexb_pipeline* p, CUtensorMap* map, CUtensorMapDataType dt, 
     const cuuint32_t box[2] = {box_inner, box_outer};
     const cuuint32_t estr[2] = {1, 1};
     if (cudaError_t ie = take_injected(SITE_ENCODE))
-        return fail(LEXB_ERR_CUDA, "cuTensorMapEncodeTiled(%s) failed with CUresult %d [injected]", what, (int)ie);
+        return fail(LEXB_ERR_CUDA, "cuTensorMapEncodeTiled(%s) failed with CUresult %d", what, (int)ie);
     CUresult r = p->gpu->encode_tiled(map, dt, 2, const_cast<void*>(ptr), dims, strides, box, estr,
                                       CU_TENSOR_MAP_INTERLEAVE_NONE, swz, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                                       CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
