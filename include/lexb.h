@@ -164,6 +164,29 @@ LEXB_API int lexb_gemm_fp4_launch_gather(lexb_gpu* gpu, const lexb_pipeline* p, 
                                          const lexb_buffer* wq, const lexb_buffer* ws, const lexb_buffer* wg,
                                          const lexb_buffer* r_or_null, void* const* y_of_rank, uint32_t world,
                                          uint32_t n_total, uint32_t n0);
+/* gate and up of one MLP in ONE launch with the step after them fused in: the caller interleaves the rows of
+ * the two weight matrices once at load (row 2j = gate row j, row 2j + 1 = up row j: lexb_interleave_rows on
+ * wq, ws and wg), plans lexb_gemm_fp4_plan(m, 2 * ffn, k) and launches here; the epilogue forms
+ * act[m, ffn] = silu(gate) * up as f16 - what `down` reads (X_DTYPE, crates/lex-rt/src/qwen_run.rs:317-327) -
+ * and the f32 [m, 2 * ffn] is never written.  It replaces the three dispatches "matvec gate/up" (twice) and
+ * silu_mul of crates/lex-rt/src/qwen_run.rs:3165-3183 (crates/lex-front/lx/silu_mul.lx).  Values: the GEMM's
+ * own f32 results, then g * (1 / (1 + exp(-g))) * u in f32 with one rounding per operation, then one
+ * rounding to f16.  Two-CTA GEMM shapes only (m > 8, 2 * ffn % 128 == 0, k % 256 == 0), no residual; with a
+ * K split the reduction launch applies it. */
+LEXB_API int lexb_gemm_fp4_silu_launch(lexb_gpu* gpu, const lexb_pipeline* p, const lexb_buffer* x, const lexb_buffer* wq,
+                                       const lexb_buffer* ws, const lexb_buffer* wg, lexb_buffer* act);
+/* The same, n-sharded, with the all-gather of the activation fused in (no reference counterpart): this rank owns
+ * interleaved rows [n0, n0 + n) of n_total (so columns [n0/2, (n0 + n)/2) of act[m, n_total/2]) and stores them
+ * into every rank's act buffer with plain peer stores; 2 bytes per output element cross NVLink where the f32
+ * gate and up would be 8. */
+LEXB_API int lexb_gemm_fp4_silu_launch_gather(lexb_gpu* gpu, const lexb_pipeline* p, const lexb_buffer* x, const lexb_buffer* wq,
+                                              const lexb_buffer* ws, const lexb_buffer* wg, void* const* act_of_rank,
+                                              uint32_t world, uint32_t n_total, uint32_t n0);
+/* out row 2j = a row j, out row 2j + 1 = b row j (device to device, asynchronous on the gpu's stream): the
+ * load-time step that puts gate and up rows side by side.  No reference counterpart. */
+LEXB_API int lexb_interleave_rows(lexb_gpu* gpu, const lexb_buffer* a, const lexb_buffer* b, size_t rows, size_t row_bytes,
+                                  lexb_buffer* out);
+
 /* The call a runtime makes per prefill chunk with host activations: copy x from host memory
  * into x_dev, launch, copy y_dev back into y_host, wait.  The weights stay resident, as
  * lex-rt keeps them (Runner::forward_with writes only per-step inputs,

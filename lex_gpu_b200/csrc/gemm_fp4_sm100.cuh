@@ -61,7 +61,25 @@ struct GemmArgs {
     uint32_t tok_blocks;  // two-CTA kernel: 256-token blocks per tile, 2 (m > 256) or 1; with 1, TMEM holds two
                           // accumulators that take even and odd K steps
     float* partial;
+    // Two-CTA kernel, gate/up fused (crates/lex-rt/src/qwen_run.rs:3165-3183): the weight rows are gate and up
+    // interleaved (row 2j = gate j, row 2j + 1 = up j) and, with `act` set (or `silu_gather` with the gather
+    // pointers), the epilogue writes silu(gate) * up as f16 [m, n/2] - the activation `down` reads - instead of
+    // the f32 y [m, n].
+    uint16_t* act;
+    uint32_t silu_gather;
 };
+
+// silu(g) * u = g * (1 / (1 + exp(-g))) * u in f32, one rounding per operation, as the interpreter evaluates
+// lex_front::llama::silu_mul (crates/lex-front/src/llama.rs:879-888; sigmoid: crates/lex-front/src/ir.rs:244)
+__device__ __forceinline__ float silu_mul_f32(float g, float u) {
+    const float sg = __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-g)));
+    return __fmul_rn(__fmul_rn(g, sg), u);
+}
+__device__ __forceinline__ uint16_t f32_to_f16_bits(float v) {
+    uint16_t h;
+    asm("cvt.rn.f16.f32 %0, %1;" : "=h"(h) : "f"(v));
+    return h;
+}
 
 __host__ __device__ constexpr uint32_t gemm_stage_bytes(uint32_t tm) { return tm * 128u + GEMM_W_TILE_BYTES; }
 // stages, then 3 barriers per stage + 1, the TMEM slot and the abort flag; 1 KiB alignment slack

@@ -396,7 +396,32 @@ gemm_fp4_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const _
                 } else {
                     tmem_ld_wait();
                 }
-                if (a.gather_world == 0u || to_partial) {
+                if (!to_partial && (a.act != nullptr || a.silu_gather != 0u)) {
+                    // gate/up fused: this lane's row is a gate row (even) or the up row of the same output
+                    // column (odd).  The gate lane finishes tokens 0-7 of the chunk, the up lane tokens 8-15;
+                    // each sends the other the eight values it needs.
+                    const bool is_up = (lane & 1u) != 0u;
+                    const uint32_t col = out_row >> 1;
+#pragma unroll
+                    for (uint32_t j = 0; j < 8; j++) {
+                        const float send = __uint_as_float(is_up ? v[j] : v[8u + j]);
+                        const float recv = __shfl_xor_sync(0xFFFFFFFFu, send, 1);
+                        const float g = is_up ? recv : __uint_as_float(v[j]);
+                        const float u = is_up ? __uint_as_float(v[8u + j]) : recv;
+                        const uint32_t t = t0 + (is_up ? 8u + j : j);
+                        if (t < a.m) {
+                            const uint16_t h = f32_to_f16_bits(silu_mul_f32(g, u));
+                            if (a.silu_gather == 0u) {
+                                a.act[(size_t)t * (a.n >> 1) + col] = h;
+                            } else {
+                                const size_t o = (size_t)t * (a.gather_n >> 1) + (a.gather_n0 >> 1) + col;
+#pragma unroll
+                                for (uint32_t d = 0; d < GATHER_MAX; d++)
+                                    if (d < a.gather_world) reinterpret_cast<uint16_t*>(a.gather_y[d])[o] = h;
+                            }
+                        }
+                    }
+                } else if (a.gather_world == 0u || to_partial) {
 #pragma unroll
                     for (uint32_t j = 0; j < 16; j++) {
                         const uint32_t t = t0 + j;
@@ -440,10 +465,13 @@ gemm_fp4_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const _
 struct GatherDst {
     float* y[GATHER_MAX];
     uint32_t world, n_total, n0, n_local;   // world = 0: plain y
+    uint32_t silu;                          // the gathered buffers are f16 [m, n_total/2] of silu(gate) * up
 };
 
+// With `act` (or g.silu) set, columns are gate/up interleaved and the kernel writes silu(gate) * up as f16 [m, n/2].
 __global__ void splitk_reduce_kernel(const float* __restrict__ partial, uint32_t splits, size_t elems,
-                                     const float* __restrict__ r, float* __restrict__ y, const GatherDst g) {
+                                     const float* __restrict__ r, float* __restrict__ y, const GatherDst g,
+                                     uint16_t* __restrict__ act, uint32_t n_local) {
     // launched with programmatic stream serialization behind the GEMM that writes the partials: its
     // blocks are in place when that launch ends
     allow_dependents();
@@ -459,7 +487,20 @@ __global__ void splitk_reduce_kernel(const float* __restrict__ partial, uint32_t
             const float4 q = reinterpret_cast<const float4*>(r)[i];
             acc.x += q.x; acc.y += q.y; acc.z += q.z; acc.w += q.w;
         }
-        if (g.world == 0u) {
+        if (act != nullptr || g.silu != 0u) {
+            // four columns = two (gate, up) pairs -> two f16 values of row t, columns c/2 and c/2 + 1
+            const uint32_t two = (uint32_t)f32_to_f16_bits(silu_mul_f32(acc.x, acc.y)) |
+                                 ((uint32_t)f32_to_f16_bits(silu_mul_f32(acc.z, acc.w)) << 16);
+            const size_t e = i * 4, t = e / n_local, c = e - t * n_local;
+            if (g.world == 0u) {
+                reinterpret_cast<uint32_t*>(act)[(t * (n_local >> 1) + (c >> 1)) >> 1] = two;
+            } else {
+                const size_t o = (t * (g.n_total >> 1) + ((g.n0 + c) >> 1)) >> 1;
+#pragma unroll
+                for (uint32_t d = 0; d < GATHER_MAX; d++)
+                    if (d < g.world) reinterpret_cast<uint32_t*>(g.y[d])[o] = two;
+            }
+        } else if (g.world == 0u) {
             reinterpret_cast<float4*>(y)[i] = acc;
         } else {
             // fused all-gather: element (t, c) of the local [m, n_local] goes to column n0 + c of every y

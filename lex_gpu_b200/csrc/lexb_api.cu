@@ -321,8 +321,10 @@ struct Order {
 
 int launch_one(lexb_gpu* g, const lexb_pipeline* p, const lexb_buffer* x, const lexb_buffer* wq, const lexb_buffer* ws,
                const lexb_buffer* wg, const lexb_buffer* r, lexb_buffer* y, const lexb::GatherDst* gather = nullptr,
-               const NextWeights* next = nullptr, Order order = Order{}) {
+               const NextWeights* next = nullptr, Order order = Order{}, lexb_buffer* act = nullptr) {
     const bool pdl = g->pdl && !order.fence;
+    // gate/up fused: `act` (or a gather whose destination buffers are f16 activations) replaces y
+    const bool silu = act != nullptr || (gather && gather->silu);
     if (!p) return fail(LEXB_ERR_ARG, "null pipeline");
     if (p->gpu != g) return fail(LEXB_ERR_ARG, "pipeline was planned on another gpu handle");
     const size_t m = p->m, n = p->n, k = p->k;
@@ -331,7 +333,11 @@ int launch_one(lexb_gpu* g, const lexb_pipeline* p, const lexb_buffer* x, const 
     if ((rc = check_buf(wq, g, n * k / 2, "wq"))) return rc;
     if ((rc = check_buf(ws, g, n * k / 16, "ws"))) return rc;
     if ((rc = check_buf(wg, g, n * 4, "wg"))) return rc;
-    if (!gather && (rc = check_buf(y, g, m * n * 4, "y"))) return rc;
+    if (silu) {
+        if (p->kernel != KERNEL_TCGEN05_PAIR || p->residual)
+            return fail(LEXB_ERR_UNSUPPORTED, "silu(gate) * up is fused into the two-CTA GEMM only (m > 8, n %% 128 == 0, k %% 256 == 0, no residual)");
+        if (act && (rc = check_buf(act, g, m * (n / 2) * 2, "act"))) return rc;
+    } else if (!gather && (rc = check_buf(y, g, m * n * 4, "y"))) return rc;
     if (gather && p->kernel != KERNEL_TCGEN05_PAIR)
         return fail(LEXB_ERR_UNSUPPORTED, "the fused all-gather exists in the two-CTA GEMM only (m > 16, n %% 128 == 0, k %% 256 == 0)");
     if (p->residual) {
@@ -348,6 +354,8 @@ int launch_one(lexb_gpu* g, const lexb_pipeline* p, const lexb_buffer* x, const 
         a.wg = static_cast<const float*>(wg->ptr);
         a.r = r ? static_cast<const float*>(r->ptr) : nullptr;
         a.y = y ? static_cast<float*>(y->ptr) : nullptr;
+        a.act = act ? static_cast<uint16_t*>(act->ptr) : nullptr;
+        a.silu_gather = (gather && gather->silu) ? 1u : 0u;
         lexb::GatherDst gd{};
         if (gather) {
             gd = *gather;
@@ -391,7 +399,7 @@ int launch_one(lexb_gpu* g, const lexb_pipeline* p, const lexb_buffer* x, const 
                 rc_cfg.attrs = attr;
                 rc_cfg.numAttrs = g->pdl ? 1 : 0;
                 LAUNCH_TRY(cudaLaunchKernelEx(&rc_cfg, lexb::splitk_reduce_kernel, static_cast<const float*>(p->partial), p->k_splits, elems,
-                                            a.r, a.y, gd));
+                                            a.r, a.y, gd, a.act, p->n));
             }
         } else {
             INJECT_LAUNCH();
@@ -1248,6 +1256,46 @@ int lexb_gemm_fp4_launch_gather(lexb_gpu* g, const lexb_pipeline* p, const lexb_
     return launch_one(g, p, x, wq, ws, wg, r, nullptr, &gd);
 }
 
+int lexb_gemm_fp4_silu_launch(lexb_gpu* g, const lexb_pipeline* p, const lexb_buffer* x, const lexb_buffer* wq,
+                              const lexb_buffer* ws, const lexb_buffer* wg, lexb_buffer* act) {
+    int rc = use(g);
+    if (rc) return rc;
+    if (!act) return fail(LEXB_ERR_ARG, "lexb_gemm_fp4_silu_launch: null act");
+    return launch_one(g, p, x, wq, ws, wg, nullptr, nullptr, nullptr, nullptr, Order{}, act);
+}
+
+int lexb_gemm_fp4_silu_launch_gather(lexb_gpu* g, const lexb_pipeline* p, const lexb_buffer* x, const lexb_buffer* wq,
+                                     const lexb_buffer* ws, const lexb_buffer* wg, void* const* act_of_rank, uint32_t world,
+                                     uint32_t n_total, uint32_t n0) {
+    int rc = use(g);
+    if (rc) return rc;
+    if (!p || !act_of_rank) return fail(LEXB_ERR_ARG, "lexb_gemm_fp4_silu_launch_gather: null argument");
+    if (world == 0 || world > lexb::GATHER_MAX) return fail(LEXB_ERR_ARG, "world = %u outside [1, %u]", world, lexb::GATHER_MAX);
+    if (n_total % 8u || n0 % 8u || static_cast<uint64_t>(n0) + p->n > n_total)
+        return fail(LEXB_ERR_ARG, "interleaved rows [%u, %u) do not fit %u rows in all", n0, n0 + p->n, n_total);
+    lexb::GatherDst gd{};
+    gd.world = world; gd.n_total = n_total; gd.n0 = n0; gd.n_local = p->n; gd.silu = 1u;
+    for (uint32_t d = 0; d < world; d++) {
+        if (!act_of_rank[d] || (reinterpret_cast<uintptr_t>(act_of_rank[d]) & 15u))
+            return fail(LEXB_ERR_ARG, "act of rank %u is null or not 16-byte aligned", d);
+        gd.y[d] = static_cast<float*>(act_of_rank[d]);
+    }
+    return launch_one(g, p, x, wq, ws, wg, nullptr, nullptr, &gd);
+}
+
+int lexb_interleave_rows(lexb_gpu* g, const lexb_buffer* a, const lexb_buffer* b, size_t rows, size_t row_bytes, lexb_buffer* out) {
+    int rc = use(g);
+    if (rc) return rc;
+    if (!a || !b || !out) return fail(LEXB_ERR_ARG, "lexb_interleave_rows: null buffer");
+    if (rows == 0 || row_bytes == 0) return fail(LEXB_ERR_SHAPE, "lexb_interleave_rows: empty extent");
+    if (a->bytes < rows * row_bytes || b->bytes < rows * row_bytes || out->bytes < 2 * rows * row_bytes)
+        return fail(LEXB_ERR_ARG, "lexb_interleave_rows: %zu rows of %zu bytes do not fit the buffers", rows, row_bytes);
+    char* o = static_cast<char*>(out->ptr);
+    CUDA_TRY_AT(SITE_COPY, cudaMemcpy2DAsync(o, 2 * row_bytes, a->ptr, row_bytes, row_bytes, rows, cudaMemcpyDeviceToDevice, g->stream));
+    CUDA_TRY_AT(SITE_COPY, cudaMemcpy2DAsync(o + row_bytes, 2 * row_bytes, b->ptr, row_bytes, row_bytes, rows, cudaMemcpyDeviceToDevice, g->stream));
+    return LEXB_OK;
+}
+
 int lexb_gemm_fp4_enqueue_host(lexb_gpu* g, const lexb_pipeline* p, const void* x_host, lexb_buffer* x_dev,
                                const lexb_buffer* wq, const lexb_buffer* ws, const lexb_buffer* wg, const lexb_buffer* r,
                                lexb_buffer* y_dev, void* y_host) {
@@ -1520,7 +1568,8 @@ int lexb_gemm_fp4_splitk_static(lexb_gpu* g, uint32_t m, uint32_t n, uint32_t k,
     const size_t elems = mm * nn;
     const uint32_t blocks = static_cast<uint32_t>(std::min<size_t>((elems / 4 + 255) / 256, static_cast<size_t>(g->prop.multiProcessorCount) * 8u));
     INJECT_LAUNCH();
-    lexb::splitk_reduce_kernel<<<blocks, 256, 0, g->stream>>>(g->static_scratch, splits, elems, a.r, a.y, lexb::GatherDst{});
+    lexb::splitk_reduce_kernel<<<blocks, 256, 0, g->stream>>>(g->static_scratch, splits, elems, a.r, a.y, lexb::GatherDst{},
+                                                              static_cast<uint16_t*>(nullptr), n);
     CUDA_TRY(cudaGetLastError());
     return LEXB_OK;
 }

@@ -30,7 +30,8 @@ SYMBOLS = [
     "lexb_run_launches", "lexb_list_runs", "lexb_run_each_timed", "lexb_time_launches", "lexb_status_word",
     "lexb_selftest_bounded_wait", "lexb_dequant_fp4_f16", "lexb_shard_rows", "lexb_trace_enable", "lexb_trace_read",
     "lexb_gemm_fp4_splitk_static", "lexb_gemm_fp4_launch_gather", "lexb_silu_mul", "lexb_prefill_chunks",
-    "lexb_matmul_fp4_plan", "lexb_debug_fail_next",
+    "lexb_matmul_fp4_plan", "lexb_debug_fail_next", "lexb_gemm_fp4_silu_launch", "lexb_gemm_fp4_silu_launch_gather",
+    "lexb_interleave_rows",
 ]
 
 
@@ -128,6 +129,9 @@ def load_library() -> ctypes.CDLL:
     L.lexb_gemm_fp4_splitk_static.argtypes = [vp, u32, u32, u32, u32, vp, vp, vp, vp, vp, vp]
     L.lexb_trace_read.argtypes = [vp, vp, u32]
     L.lexb_debug_fail_next.argtypes = [c_int, c_int, c_int]
+    L.lexb_gemm_fp4_silu_launch.argtypes = [vp, vp, vp, vp, vp, vp, vp]
+    L.lexb_gemm_fp4_silu_launch_gather.argtypes = [vp, vp, vp, vp, vp, vp, POINTER(vp), u32, u32, u32]
+    L.lexb_interleave_rows.argtypes = [vp, vp, vp, sz, sz, vp]
     _lib = L
     return L
 
@@ -371,6 +375,22 @@ class Gpu:
         _check(self._L.lexb_gemm_fp4_launch_gather(self.handle, pipe.handle, x.handle, wq.handle, ws.handle, wg.handle,
                                                    r.handle if r is not None else None, arr, len(y_ptr_of_rank),
                                                    n_total, n0))
+
+    def run_silu(self, pipe: Pipeline, x: Buffer, wq: Buffer, ws: Buffer, wg: Buffer, act: Buffer) -> None:
+        """gate/up in one launch with silu(gate) * up fused in: wq/ws/wg hold gate and up rows interleaved, act is
+        f16 [m, n/2] (lexb_gemm_fp4_silu_launch)."""
+        _check(self._L.lexb_gemm_fp4_silu_launch(self.handle, pipe.handle, x.handle, wq.handle, ws.handle, wg.handle, act.handle))
+
+    def run_silu_gather(self, pipe: Pipeline, x: Buffer, wq: Buffer, ws: Buffer, wg: Buffer, act_ptrs: Sequence[int],
+                        n_total: int, n0: int) -> None:
+        """The n-sharded form with the all-gather of the f16 activation fused in (peer stores)."""
+        arr = (c_void_p * len(act_ptrs))(*act_ptrs)
+        _check(self._L.lexb_gemm_fp4_silu_launch_gather(self.handle, pipe.handle, x.handle, wq.handle, ws.handle, wg.handle,
+                                                        arr, len(act_ptrs), n_total, n0))
+
+    def interleave_rows(self, a: Buffer, b: Buffer, rows: int, row_bytes: int, out: Buffer) -> None:
+        """out row 2j = a row j, out row 2j + 1 = b row j, on the device (lexb_interleave_rows)."""
+        _check(self._L.lexb_interleave_rows(self.handle, a.handle, b.handle, rows, row_bytes, out.handle))
 
     def enqueue_host(self, pipe: Pipeline, x_host_ptr: int, x_dev: Buffer, wq: Buffer, ws: Buffer, wg: Buffer,
                      r: Optional[Buffer], y_dev: Buffer, y_host_ptr: int) -> None:

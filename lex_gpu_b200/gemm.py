@@ -48,6 +48,21 @@ class QBuf:
         """[x, wq, ws, wg, (r), y]"""
         return [x, self.wq, self.ws, self.wg] + ([r] if r is not None else []) + [y]
 
+    @classmethod
+    def gate_up(cls, gpu: Gpu, gate: "QBuf", up: "QBuf") -> "QBuf":
+        """The weights of gate and up with their rows interleaved on the device (row 2j = gate j, 2j + 1 = up j):
+        what the fused launch Gpu.run_silu multiplies by.  A load-time step."""
+        if (gate.n, gate.k) != (up.n, up.k):
+            raise ValueError("gate and up differ in shape")
+        q = cls.__new__(cls)
+        q.n, q.k = 2 * gate.n, gate.k
+        q.wq, q.ws, q.wg = gpu.alloc(q.n * q.k // 2), gpu.alloc(q.n * q.k // 16), gpu.alloc(q.n * 4)
+        gpu.interleave_rows(gate.wq, up.wq, gate.n, gate.k // 2, q.wq)
+        gpu.interleave_rows(gate.ws, up.ws, gate.n, gate.k // 16, q.ws)
+        gpu.interleave_rows(gate.wg, up.wg, gate.n, 4, q.wg)
+        gpu.sync()
+        return q
+
     def close(self) -> None:
         for b in (self.wq, self.ws, self.wg):
             b.close()

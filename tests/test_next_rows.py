@@ -133,3 +133,73 @@ def test_mlp_block_gate_up_fused_silu_down(gpu, tmp_path):
     # and the whole block against the oracle's chain, of scale (inputs of the last stage differ by f16 steps)
     e3, s3, _ = O.err_of_scale(got, want)
     assert s3 > 1e-3 and e3 <= 2e-3
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("m,ffn,hidden,splits", [(96, 1024, 512, 0), (512, 768, 1024, 0), (700, 512, 2048, 2), (300, 640, 1280, 5)])
+def test_gate_up_in_one_launch_with_silu_mul_in_the_epilogue(gpu, m, ffn, hidden, splits):
+    """The three dispatches of crates/lex-rt/src/qwen_run.rs:3165-3183 (gate, up, silu_mul) as one launch: rows of
+    gate and up interleaved at load, silu(gate) * up formed in the GEMM's epilogue (in the reduction launch when K
+    is split) and written as the f16 activation.  Against (1) the same launch's f32 gate/up run through the
+    interpreter's formula: equal up to one f16 step; (2) the oracle's whole chain, of scale."""
+    x = inputs.make_x(m, hidden, seed_base=40)
+    wg_, wu_ = inputs.make_weights(ffn, hidden, seed_base=41), inputs.make_weights(ffn, hidden, seed_base=42)
+    # row scales that keep gate near the knee of the sigmoid
+    wg_ = (wg_[0], wg_[1], (wg_[2] * np.float32(0.02)).astype(np.float32))
+    wu_ = (wu_[0], wu_[1], (wu_[2] * np.float32(0.03)).astype(np.float32))
+    qg, qu = L.QBuf(gpu, *wg_), L.QBuf(gpu, *wu_)
+    qgu = L.QBuf.gate_up(gpu, qg, qu)
+    # the interleave itself: row 2j = gate j, 2j + 1 = up j, for all three arrays
+    for dev, a, b, dt in ((qgu.wq, wg_[0], wu_[0], np.uint8), (qgu.ws, wg_[1], wu_[1], np.uint8), (qgu.wg, wg_[2], wu_[2], np.float32)):
+        got = gpu.download(dev, dt, (2 * ffn,) + a.shape[1:])
+        assert np.array_equal(got[0::2], a) and np.array_equal(got[1::2], b)
+    xb = gpu.upload(x)
+    pipe = gpu.plan_gemm_fp4(m, 2 * ffn, hidden, kernel=3, k_splits=splits)
+    act, ygu = gpu.alloc(m * ffn * 2), gpu.alloc(m * 2 * ffn * 4)
+    gpu.memset(act, 0xFF)
+    gpu.run_silu(pipe, xb, qgu.wq, qgu.ws, qgu.wg, act)
+    gpu.run(pipe, qgu.bind(xb, None, ygu))
+    got_act = gpu.download(act, np.float16, (m, ffn))
+    got_gu = gpu.download(ygu, np.float32, (m, 2 * ffn))
+    assert gpu.status_word() == 0
+    assert np.isfinite(got_act.astype(np.float32)).all()
+    same_inputs = O.np_silu_mul(got_gu[:, 0::2], got_gu[:, 1::2], out_f16=True).astype(np.float32)
+    assert np.all(np.abs(got_act.astype(np.float32) - same_inputs) <= np.abs(same_inputs) * 2.0 ** -10 + 1e-7)
+    want = O.np_silu_mul(O.gemm_fp4(x, *wg_), O.gemm_fp4(x, *wu_), out_f16=True).astype(np.float32)
+    err, scale, rel = O.err_of_scale(got_act.astype(np.float32), want)
+    print(f"  fused activation vs the oracle's chain: {err:.2e} of scale, {rel:.2e} per element")
+    assert scale > 1e-3 and err <= 2e-3 and rel <= 2e-3
+    with pytest.raises(L.LexbError):                      # a residual pipeline has no fused form
+        gpu.run_silu(gpu.plan_gemm_fp4(m, 2 * ffn, hidden, residual=True, kernel=3), xb, qgu.wq, qgu.ws, qgu.wg, act)
+    with pytest.raises(L.LexbError):                      # nor has the one-CTA kernel
+        gpu.run_silu(gpu.plan_gemm_fp4(m, 2 * ffn, hidden, kernel=2), xb, qgu.wq, qgu.ws, qgu.wg, act)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("splits", [1, 3])
+def test_fused_activation_gathered_into_every_ranks_buffer(gpu, splits):
+    """The n-sharded form: this 'rank' owns interleaved rows [n0, n0 + n) and stores its columns of the f16
+    activation into every rank's buffer (three buffers on one GPU stand for the ranks)."""
+    m, ffn_local, hidden, ffn_total, col0 = 300, 256, 1536, 1024, 384
+    x = inputs.make_x(m, hidden, seed_base=50)
+    wg_, wu_ = inputs.make_weights(ffn_local, hidden, seed_base=51), inputs.make_weights(ffn_local, hidden, seed_base=52)
+    wg_ = (wg_[0], wg_[1], (wg_[2] * np.float32(0.02)).astype(np.float32))
+    wu_ = (wu_[0], wu_[1], (wu_[2] * np.float32(0.03)).astype(np.float32))
+    qgu = L.QBuf.gate_up(gpu, L.QBuf(gpu, *wg_), L.QBuf(gpu, *wu_))
+    xb = gpu.upload(x)
+    pipe = gpu.plan_gemm_fp4(m, 2 * ffn_local, hidden, kernel=3, k_splits=splits)
+    local = gpu.alloc(m * ffn_local * 2)
+    gpu.run_silu(pipe, xb, qgu.wq, qgu.ws, qgu.wg, local)
+    want = gpu.download(local, np.float16, (m, ffn_local))
+    bufs = [gpu.alloc(m * ffn_total * 2) for _ in range(3)]
+    for b in bufs:
+        gpu.memset(b, 0xFF)
+    gpu.run_silu_gather(pipe, xb, qgu.wq, qgu.ws, qgu.wg, [b.ptr for b in bufs], 2 * ffn_total, 2 * col0)
+    assert gpu.status_word() == 0
+    for b in bufs:
+        full = gpu.download(b, np.uint16, (m, ffn_total))
+        assert np.array_equal(full[:, col0:col0 + ffn_local], want.view(np.uint16))
+        assert (full[:, :col0] == 0xFFFF).all() and (full[:, col0 + ffn_local:] == 0xFFFF).all()
+    ref = O.np_silu_mul(O.gemm_fp4(x, *wg_), O.gemm_fp4(x, *wu_), out_f16=True).astype(np.float32)
+    err, scale, rel = O.err_of_scale(want.astype(np.float32), ref)
+    assert scale > 1e-3 and err <= 2e-3 and rel <= 2e-3
