@@ -66,7 +66,7 @@ typedef struct lexb_sched {
     uint32_t k_splits; /* two-CTA GEMM: split K this many ways (partials in a workspace the pipeline owns, then summed) */
     uint32_t flags;    /* LEXB_SCHED_* bits */
 } lexb_sched;
-/* Block-scaled kernel only.  Launches are in order on their stream, as the reference's are
+/* Block-scaled kernel and two-CTA GEMM.  Launches are in order on their stream, as the reference's are
  * (crates/lex-cuda/src/device.rs:629-672): every read waits for the kernel ahead.  The kernel can do
  * better when it knows that nothing in flight writes wq and ws - launched with programmatic stream
  * serialization, it then starts loading them while the kernel ahead of it is still running (x, r and y
@@ -88,7 +88,7 @@ typedef struct lexb_lowered {
     uint32_t threads;
     uint32_t threadgroup_bytes;  /* dynamic shared memory */
     uint32_t nbind;
-    uint8_t writes[6];
+    uint8_t writes[8];           /* (7 bindings for lexb_matmul_int8_plan with a residual) */
     uint32_t kernel;             /* 1 matvec, 2 tcgen05, 3 two-CTA tcgen05, 4 block-scaled FP4 */
     uint32_t m, n, k, residual;
     uint32_t bm, bn, bk, stages;
@@ -101,7 +101,7 @@ typedef struct lexb_lowered {
 typedef struct lexb_step {
     const lexb_pipeline* pipeline;
     lexb_buffer* const* buffers;
-    uint32_t nbuffers;           /* 5 without residual, 6 with */
+    uint32_t nbuffers;           /* 5 without residual, 6 with; one more ([xq, xs, ...]) for lexb_matmul_int8_plan */
 } lexb_step;
 
 LEXB_API const char* lexb_last_error(void);   /* message of this thread's last failing call */
@@ -290,6 +290,22 @@ LEXB_API int lexb_gemm_fp4_splitk_static(lexb_gpu* gpu, uint32_t m, uint32_t n, 
  * NaN gives NaN for the whole token; magnitudes below 2^-111 count as zero. */
 LEXB_API int lexb_matmul_fp4_plan(lexb_gpu* gpu, uint32_t t, uint32_t n_out, uint32_t n_in, int residual, int x_half,
                                   const lexb_sched* sched_or_null, lexb_pipeline** out);
+
+/* lex_msl::int8 (crates/lex-msl/src/int8.rs): the integer-activation path the reference decodes and verifies with
+ * on CUDA for t <= 4 tokens (crates/lex-rt/src/qwen_run.rs:2876-2924).
+ * lexb_quant16 = int8::quant16 (:47-114), operation for operation: each group of 16 values of x[m, k] (f32, or f16
+ * when x_half) becomes 16 int16 in xq[m, k] and one f32 scale in xs[m, k/16] (largest magnitude / 32767); k % 32 == 0.
+ * lexb_matmul_int8_plan = int8::matmul_int8 (:121-223): y[t, n] = sum_p (xq * xs)[t, p] * W[n, p] (+ r) with the NVFP4
+ * W as matmul_q_x takes it; the pipeline is launched as a lexb_step with the reference's bindings
+ * [xq, xs, wq, ws, wg, (r), y] (7 with the residual).  Here the products run on the block-scaled FP4 tensor-core
+ * kernel (t <= 32, n % 128 == 0, k % 256 == 0): the activation is widened to xq * xs in f32 and split into digit
+ * rows like any f32 activation, which keeps 16 bits below each group's largest value - the precision int16
+ * carries.  Within the reference's bar for this path against the interpreter's matmul_q_x (2e-3 of scale,
+ * crates/lex-cuda/tests/device_gpu.rs:314-380), and a token's result does not depend on its batch. */
+LEXB_API int lexb_quant16(lexb_gpu* gpu, uint32_t m, uint32_t k, int x_half, const lexb_buffer* x, lexb_buffer* xq,
+                          lexb_buffer* xs);
+LEXB_API int lexb_matmul_int8_plan(lexb_gpu* gpu, uint32_t t, uint32_t n_out, uint32_t n_in, int residual,
+                                   const lexb_sched* sched_or_null, lexb_pipeline** out);
 
 /* The step after gate/up in the MLP: out = silu(gate) * up, elementwise in f32, written as f16 (what
  * `down` reads, X_DTYPE in crates/lex-rt/src/qwen_run.rs:317-327) or f32.  The operator is

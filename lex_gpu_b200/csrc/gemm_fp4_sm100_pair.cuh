@@ -123,7 +123,14 @@ gemm_fp4_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const _
     const uint32_t tmem_base = *tmem_slot;
     // Everything above touched only this block's shared memory and TMEM.  From here on the kernel
     // reads x, the weights and r and writes y: wait for the launch ahead of this one in the stream.
-    grid_dependency_wait();
+    // With flag bit 1 (the packed weights are known to be constant: declared by the caller or proven from
+    // the step list) the two roles that touch only wq, ws and wg - the copy of the packed weights and the
+    // decode into shared memory - start at once and fill their rings while the launch ahead still runs;
+    // each joins the stream's order before its first wait on a ring slot (a bounded wait must not run
+    // against another launch's time) and, for the decode warps, before the epilogue.
+    const bool early_w = (a.flags & 2u) != 0u;
+    const bool weight_role = warp == PAIR_WARP_RAW || warp < PAIR_DEQ_THREADS / 32u;
+    if (!(early_w && weight_role)) grid_dependency_wait();
 
     if (warp == PAIR_WARP_TMA) {
         // ---------------------------------------------------------------- TMA producer (both CTAs)
@@ -161,6 +168,7 @@ gemm_fp4_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const _
             RingPos pr;
             for (uint32_t rb = 0; rb < RB; rb++, pr.advance(PAIR_RAW_STAGES)) {
                 const uint32_t rs = pr.s, ph = pr.ph;
+                if (early_w && rb == PAIR_RAW_STAGES) grid_dependency_wait();     // the ring is full: join the stream's order
                 if (!mbar_wait(raw_empty(rs), ph ^ 1u, abort_flag)) {
                     atomicOr(a.status, ST_WAIT_EMPTY_TMA);
                     *abort_flag = 1;
@@ -336,6 +344,7 @@ gemm_fp4_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const _
             decode_group16(q, sb, g, o0, o1);
             long long tq1 = 0;
             if (TRACE) tq1 = clock64();
+            if (early_w && kb == SW) grid_dependency_wait();                      // the W ring is full
             if (!__all_sync(0xFFFFFFFFu, mbar_wait(w_empty(s), ph ^ 1u, abort_flag))) {
                 atomicOr(a.status, ST_WAIT_EMPTY_DEQ);
                 *abort_flag = 1;
@@ -360,6 +369,7 @@ gemm_fp4_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const _
         }
         __syncwarp();
         // ---------------------------------------------------------------- epilogue (both CTAs)
+        if (early_w) grid_dependency_wait();        // r, y and the partials belong to the stream's order
         uint32_t go = 0;
         if (lane == 0) {
             go = ok && mbar_wait(acc_full, 0, abort_flag);

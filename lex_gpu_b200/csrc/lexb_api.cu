@@ -100,6 +100,7 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
 enum { KERNEL_MATVEC = 1, KERNEL_TCGEN05 = 2, KERNEL_TCGEN05_PAIR = 3, KERNEL_MATMUL_Q = 4 };
+constexpr uint32_t SCHED_INTERNAL_Q16 = 1u << 30;      // set by lexb_matmul_int8_plan on its way through lexb_gemm_fp4_plan
 
 }  // namespace
 
@@ -144,7 +145,9 @@ struct lexb_pipeline {
     uint32_t k_splits = 1, kb_per_split = 0, tok_blocks = 2;
     uint32_t ws_pitch = 0;      // block-scaled kernel: bytes per row of one scale load
     bool x_f32 = false;         // ... with f32 activations
-    bool w_const = false;       // ... whose caller declared wq/ws constant (LEXB_SCHED_WEIGHTS_CONSTANT): loaded ahead of the stream's order
+    bool x_q16 = false;         // ... with int16 activations and one f32 scale per 16 (lexb_matmul_int8_plan): bindings [xq, xs, wq, ...]
+    bool w_const = false;       // the caller declared wq/ws constant (LEXB_SCHED_WEIGHTS_CONSTANT): loaded ahead of the stream's order
+                                // by the kernels that can (block-scaled kernel, two-CTA GEMM)
     bool w_volatile = false;    // ... or said they may change (LEXB_SCHED_WEIGHTS_MAY_CHANGE): never loaded early, not even in a list
     bool mq_pre = false;        // ... with the tokens' digit rows from the pieces kernel: buffers and their tensor map
     uint8_t* pre_buf = nullptr; // [8 m][k / 2] digit rows, then [k / 256][2048] scale blocks, then [m] magnitudes
@@ -252,6 +255,46 @@ __global__ void silu_mul_kernel(uint32_t rows, uint32_t cols, const float* __res
     }
 }
 
+// lex_msl::int8::quant16 (crates/lex-msl/src/int8.rs:47-114), operation for operation: per group of 16 the largest
+// magnitude mx, inv = 32767 / mx (0 for a group of zeros), q = round-to-nearest-even(v * inv) as int16, scale mx / 32767.
+template <bool XH>
+__global__ void quant16_kernel(const void* __restrict__ x, short* __restrict__ xq, float* __restrict__ xs, size_t groups) {
+    const size_t g = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x;
+    if (g >= groups) return;
+    float v[16];
+    if (XH) {
+        const uint4* xp = reinterpret_cast<const uint4*>(x) + g * 2u;
+        const uint4 raw[2] = {xp[0], xp[1]};
+        const __half2* hp = reinterpret_cast<const __half2*>(raw);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const float2 f = __half22float2(hp[i]);
+            v[2 * i] = f.x;
+            v[2 * i + 1] = f.y;
+        }
+    } else {
+        const float4* xp = reinterpret_cast<const float4*>(x) + g * 4u;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float4 f = xp[i];
+            v[4 * i] = f.x; v[4 * i + 1] = f.y; v[4 * i + 2] = f.z; v[4 * i + 3] = f.w;
+        }
+    }
+    float mx = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) mx = fmaxf(mx, fabsf(v[i]));
+    const float inv = mx > 0.0f ? __fdiv_rn(32767.0f, mx) : 0.0f;
+    uint32_t w[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+        w[i] = (static_cast<uint32_t>(__float2int_rn(__fmul_rn(v[2 * i], inv))) & 0xFFFFu) |
+               ((static_cast<uint32_t>(__float2int_rn(__fmul_rn(v[2 * i + 1], inv))) & 0xFFFFu) << 16);
+    uint4* out = reinterpret_cast<uint4*>(xq) + g * 2u;
+    out[0] = make_uint4(w[0], w[1], w[2], w[3]);
+    out[1] = make_uint4(w[4], w[5], w[6], w[7]);
+    xs[g] = __fdiv_rn(mx, 32767.0f);
+}
+
 int encode_2d(const lexb_pipeline* p, CUtensorMap* map, CUtensorMapDataType dt, uint32_t esize, const void* ptr,
               uint64_t inner, uint64_t outer, uint32_t box_inner, uint32_t box_outer, CUtensorMapSwizzle swz,
               const char* what) {
@@ -321,7 +364,8 @@ struct Order {
 
 int launch_one(lexb_gpu* g, const lexb_pipeline* p, const lexb_buffer* x, const lexb_buffer* wq, const lexb_buffer* ws,
                const lexb_buffer* wg, const lexb_buffer* r, lexb_buffer* y, const lexb::GatherDst* gather = nullptr,
-               const NextWeights* next = nullptr, Order order = Order{}, lexb_buffer* act = nullptr) {
+               const NextWeights* next = nullptr, Order order = Order{}, lexb_buffer* act = nullptr,
+               const lexb_buffer* xs_q16 = nullptr) {
     const bool pdl = g->pdl && !order.fence;
     // gate/up fused: `act` (or a gather whose destination buffers are f16 activations) replaces y
     const bool silu = act != nullptr || (gather && gather->silu);
@@ -329,7 +373,12 @@ int launch_one(lexb_gpu* g, const lexb_pipeline* p, const lexb_buffer* x, const 
     if (p->gpu != g) return fail(LEXB_ERR_ARG, "pipeline was planned on another gpu handle");
     const size_t m = p->m, n = p->n, k = p->k;
     int rc;
-    if ((rc = check_buf(x, g, m * k * (p->x_f32 ? 4 : 2), "x"))) return rc;
+    if ((rc = check_buf(x, g, m * k * (p->x_f32 ? 4 : 2), p->x_q16 ? "xq" : "x"))) return rc;
+    if (p->x_q16) {
+        if ((rc = check_buf(xs_q16, g, m * (k / 16) * 4, "xs"))) return rc;
+    } else if (xs_q16) {
+        return fail(LEXB_ERR_ARG, "an activation-scale buffer was bound to a pipeline that takes f16 or f32 activations");
+    }
     if ((rc = check_buf(wq, g, n * k / 2, "wq"))) return rc;
     if ((rc = check_buf(ws, g, n * k / 16, "ws"))) return rc;
     if ((rc = check_buf(wg, g, n * 4, "wg"))) return rc;
@@ -365,7 +414,10 @@ int launch_one(lexb_gpu* g, const lexb_pipeline* p, const lexb_buffer* x, const 
         a.status = g->d_status;
         a.trace = (g->d_trace && p->kernel == KERNEL_TCGEN05_PAIR && p->grid <= g->trace_ctas) ? g->d_trace : nullptr;
         a.m = p->m; a.n = p->n; a.k = p->k;
-        a.tm = p->tm; a.stages = p->stages; a.w_stages = p->w_stages; a.flags = p->flags;
+        a.tm = p->tm; a.stages = p->stages; a.w_stages = p->w_stages;
+        // bit 0: operand-collector hint; bit 1 (two-CTA kernel): the packed weights are constant - declared, or
+        // proven from the step list - so their copy and decode may run ahead of the stream's order
+        a.flags = p->flags | ((p->w_const || (order.early_weights && !p->w_volatile)) ? 2u : 0u);
         a.k_splits = p->k_splits; a.kb_per_split = p->kb_per_split; a.partial = p->partial; a.tok_blocks = p->tok_blocks;
         a.tmem_cols = p->tmem_cols; a.m_tiles = p->m_tiles; a.n_acc = p->n_acc;
         a.x_tx_bytes = p->kernel == KERNEL_TCGEN05_PAIR ? (p->m < lexb::PAIR_XBLK_ROWS ? p->m : lexb::PAIR_XBLK_ROWS) * 128u
@@ -450,8 +502,10 @@ int launch_one(lexb_gpu* g, const lexb_pipeline* p, const lexb_buffer* x, const 
             pc.attrs = attr;
             pc.numAttrs = pdl ? 1 : 0;
             uint32_t* amax_w = reinterpret_cast<uint32_t*>(p->pre_buf + pieces_bytes + sfb_bytes);
-            if (p->x_f32) LAUNCH_TRY(cudaLaunchKernelEx(&pc, lexb::matmul_q_pieces_kernel<true>, static_cast<const void*>(x->ptr), p->k, p->pre_buf, p->pre_buf + pieces_bytes, amax_w));
-            else LAUNCH_TRY(cudaLaunchKernelEx(&pc, lexb::matmul_q_pieces_kernel<false>, static_cast<const void*>(x->ptr), p->k, p->pre_buf, p->pre_buf + pieces_bytes, amax_w));
+            const float* no_xs = nullptr;
+            if (p->x_q16) LAUNCH_TRY(cudaLaunchKernelEx(&pc, lexb::matmul_q_pieces_kernel<2>, static_cast<const void*>(x->ptr), p->k, p->pre_buf, p->pre_buf + pieces_bytes, amax_w, static_cast<const float*>(xs_q16->ptr)));
+            else if (p->x_f32) LAUNCH_TRY(cudaLaunchKernelEx(&pc, lexb::matmul_q_pieces_kernel<1>, static_cast<const void*>(x->ptr), p->k, p->pre_buf, p->pre_buf + pieces_bytes, amax_w, no_xs));
+            else LAUNCH_TRY(cudaLaunchKernelEx(&pc, lexb::matmul_q_pieces_kernel<0>, static_cast<const void*>(x->ptr), p->k, p->pre_buf, p->pre_buf + pieces_bytes, amax_w, no_xs));
         }
         const CUtensorMap& bmap = p->mq_pre ? p->pre_map : maps.map_wq;      // a placeholder without the pieces kernel
 #define LEXB_MQ_LAUNCH(TR, XF, PR) LAUNCH_TRY(cudaLaunchKernelEx(&cfg, lexb::matmul_q_fp4_kernel<TR, XF, PR>, maps.map_wq, maps.map_ws, nmaps.map_wq, nmaps.map_ws, bmap, a))
@@ -519,16 +573,17 @@ struct StepRanges {
 StepRanges step_ranges(const lexb_step& s) {
     StepRanges out;
     const lexb_pipeline* p = s.pipeline;
-    if (!p || !s.buffers || s.nbuffers != (p->residual ? 6u : 5u)) return out;
+    const uint32_t q = p && p->x_q16 ? 1u : 0u;       // int16 activations bring their scales as a second binding
+    if (!p || !s.buffers || s.nbuffers != (p->residual ? 6u : 5u) + q) return out;
     for (uint32_t b = 0; b < s.nbuffers; b++)
         if (!s.buffers[b] || !s.buffers[b]->ptr) return out;
     auto range = [](const lexb_buffer* b, size_t bytes) { const char* p0 = static_cast<const char*>(b->ptr); return Range{p0, p0 + bytes}; };
     const size_t m = p->m, n = p->n, k = p->k, out_bytes = m * n * 4;
     out.x = range(s.buffers[0], m * k * (p->x_f32 ? 4 : 2));
-    out.wq = range(s.buffers[1], n * k / 2);
-    out.ws = range(s.buffers[2], n * k / 16);
-    out.r = p->residual ? range(s.buffers[4], out_bytes) : Range{nullptr, nullptr};
-    out.y = range(s.buffers[p->residual ? 5 : 4], out_bytes);
+    out.wq = range(s.buffers[1 + q], n * k / 2);
+    out.ws = range(s.buffers[2 + q], n * k / 16);
+    out.r = p->residual ? range(s.buffers[4 + q], out_bytes) : Range{nullptr, nullptr};
+    out.y = range(s.buffers[(p->residual ? 5 : 4) + q], out_bytes);
     out.valid = true;
     return out;
 }
@@ -554,7 +609,7 @@ struct ListProof {
 
 bool chain_member(const lexb_gpu* g, const lexb_step& s, const lexb_pipeline* first) {
     const lexb_pipeline* p = s.pipeline;
-    if (!p || !s.buffers || p->gpu != g || p->kernel != KERNEL_MATMUL_Q || p->m > chain_max_m() || p->k_splits != 1u) return false;
+    if (!p || !s.buffers || p->gpu != g || p->kernel != KERNEL_MATMUL_Q || p->x_q16 || p->m > chain_max_m() || p->k_splits != 1u) return false;
     if (p->mq_pre != (p->m > 4u)) return false;                                      // (a plan forced the other way by LEXB_MQ_PRE stays as planned)
     if (p->w_volatile || s.nbuffers != (p->residual ? 6u : 5u)) return false;
     if ((p->k / lexb::MQ_STAGE_K) % lexb::MQ_WS_GROUP == 1u) return false;          // a scale-byte group of one stage is seen by half the scale warps only
@@ -668,8 +723,9 @@ int launch_chain(lexb_gpu* g, const lexb_step* steps, size_t count, bool fence) 
                 pc.numAttrs = pdl_next ? 1 : 0;
                 pdl_next = g->pdl;
                 uint32_t* amax_w = reinterpret_cast<uint32_t*>(buf + pieces_bytes + sfb_bytes);
-                if (p0->x_f32) LAUNCH_TRY(cudaLaunchKernelEx(&pc, lexb::matmul_q_pieces_kernel<true>, static_cast<const void*>(x->ptr), p0->k, buf, buf + pieces_bytes, amax_w));
-                else LAUNCH_TRY(cudaLaunchKernelEx(&pc, lexb::matmul_q_pieces_kernel<false>, static_cast<const void*>(x->ptr), p0->k, buf, buf + pieces_bytes, amax_w));
+                const float* no_xs = nullptr;
+                if (p0->x_f32) LAUNCH_TRY(cudaLaunchKernelEx(&pc, lexb::matmul_q_pieces_kernel<1>, static_cast<const void*>(x->ptr), p0->k, buf, buf + pieces_bytes, amax_w, no_xs));
+                else LAUNCH_TRY(cudaLaunchKernelEx(&pc, lexb::matmul_q_pieces_kernel<0>, static_cast<const void*>(x->ptr), p0->k, buf, buf + pieces_bytes, amax_w, no_xs));
             }
         }
         const uint32_t job_tiles = (p->n + lexb::MQ_ROWS - 1u) / lexb::MQ_ROWS;
@@ -728,13 +784,20 @@ int launch_chain(lexb_gpu* g, const lexb_step* steps, size_t count, bool fence) 
 int launch_step(lexb_gpu* g, const lexb_step& s, const lexb_step* following = nullptr, Order order = Order{}) {
     if (!s.pipeline || !s.buffers) return fail(LEXB_ERR_ARG, "step without pipeline or buffers");
     const bool res = s.pipeline->residual;
-    if (s.nbuffers != (res ? 6u : 5u))
-        return fail(LEXB_ERR_ARG, "step binds %u buffers, the pipeline takes %u: [x, wq, ws, wg, %sy]", s.nbuffers,
-                    res ? 6u : 5u, res ? "r, " : "");
+    const uint32_t q = s.pipeline->x_q16 ? 1u : 0u;
+    if (s.nbuffers != (res ? 6u : 5u) + q)
+        return fail(LEXB_ERR_ARG, "step binds %u buffers, the pipeline takes %u: [%s, wq, ws, wg, %sy]", s.nbuffers,
+                    (res ? 6u : 5u) + q, q ? "xq, xs" : "x", res ? "r, " : "");
+    if (q) {
+        // matmul_int8's bindings (crates/lex-msl/src/int8.rs:121-125): [xq, xs, wq, ws, wg, (r), y]
+        lexb_buffer* const* c = s.buffers;
+        return launch_one(g, s.pipeline, c[0], c[2], c[3], c[4], res ? c[5] : nullptr, res ? c[6] : c[5], nullptr, nullptr, order,
+                          nullptr, c[1]);
+    }
     lexb_buffer* const* b = s.buffers;
     NextWeights nw{};
     static const bool hints = env_u32("LEXB_NEXT_HINT", 1) != 0;     // LEXB_NEXT_HINT=0: no prefetch of the next step's weights
-    if (hints && following && following->pipeline && following->buffers && following->nbuffers >= 5u)
+    if (hints && following && following->pipeline && following->buffers && following->nbuffers >= 5u && !following->pipeline->x_q16)
         nw = NextWeights{following->pipeline, following->buffers[0], following->buffers[1], following->buffers[2]};
     return launch_one(g, s.pipeline, b[0], b[1], b[2], b[3], res ? b[4] : nullptr, res ? b[5] : b[4], nullptr,
                       nw.pipe ? &nw : nullptr, order);
@@ -980,6 +1043,7 @@ int lexb_gemm_fp4_plan(lexb_gpu* g, uint32_t m, uint32_t n, uint32_t k, int resi
     if (m == 0 || n == 0 || k == 0) return fail(LEXB_ERR_SHAPE, "gemm_fp4: empty extent (m=%u n=%u k=%u)", m, n, k);
     lexb_sched s{};
     if (sched) s = *sched;
+    if (s.kernel != KERNEL_MATMUL_Q) s.flags &= ~SCHED_INTERNAL_Q16;
     if (!s.kernel) s.kernel = env_u32("LEXB_KERNEL", 0);
     if (!s.tm) s.tm = env_u32("LEXB_TM", 0);
     if (!s.stages) s.stages = env_u32("LEXB_STAGES", 0);
@@ -1006,6 +1070,10 @@ int lexb_gemm_fp4_plan(lexb_gpu* g, uint32_t m, uint32_t n, uint32_t k, int resi
     p->residual = residual != 0;
     auto bail = [&](int code) { lexb_pipeline_free(p); return code; };
     const char* stem = residual ? "gemm_fp4_res" : "gemm_fp4";
+    p->w_const = (s.flags & LEXB_SCHED_WEIGHTS_CONSTANT) != 0u;
+    p->w_volatile = (s.flags & LEXB_SCHED_WEIGHTS_MAY_CHANGE) != 0u;
+    if (p->w_const && p->w_volatile)
+        return bail(fail(LEXB_ERR_ARG, "LEXB_SCHED_WEIGHTS_CONSTANT and LEXB_SCHED_WEIGHTS_MAY_CHANGE exclude one another"));
 
     if (kernel == KERNEL_MATMUL_Q) {
         // Only through lexb_matmul_fp4_plan or an explicit selector: its arithmetic is matmul_q_x's
@@ -1031,10 +1099,6 @@ int lexb_gemm_fp4_plan(lexb_gpu* g, uint32_t m, uint32_t n, uint32_t k, int resi
         // In order by default, as the reference's launches are (crates/lex-cuda/src/device.rs:629-672): wq/ws are
         // loaded ahead of the stream's order only when the caller declares them constant or a step list shows
         // that nothing in flight writes them (ListProof); never when the caller says they may change.
-        p->w_const = (s.flags & LEXB_SCHED_WEIGHTS_CONSTANT) != 0u;
-        p->w_volatile = (s.flags & LEXB_SCHED_WEIGHTS_MAY_CHANGE) != 0u;
-        if (p->w_const && p->w_volatile)
-            return bail(fail(LEXB_ERR_ARG, "LEXB_SCHED_WEIGHTS_CONSTANT and LEXB_SCHED_WEIGHTS_MAY_CHANGE exclude one another"));
         p->flags = 0u;
         if (splits > 1u) {
             // partial products [splits][m][n], then one arrival counter per row tile (zero between launches)
@@ -1047,7 +1111,9 @@ int lexb_gemm_fp4_plan(lexb_gpu* g, uint32_t m, uint32_t n, uint32_t k, int resi
         }
         // From 5 tokens on the digit rows are derived once per launch by a small kernel ahead of this one
         // (each block deriving them itself is what bounds the kernel there); LEXB_MQ_PRE=0/1 forces either way.
-        p->mq_pre = m > 16u || env_u32("LEXB_MQ_PRE", m > 4u ? 1u : 0u) != 0;       // past 16 tokens there is no in-block path
+        // (past 16 tokens there is no in-block path; int16 activations are widened by the pieces kernel only)
+        p->x_q16 = (s.flags & SCHED_INTERNAL_Q16) != 0u;
+        p->mq_pre = m > 16u || p->x_q16 || env_u32("LEXB_MQ_PRE", m > 4u ? 1u : 0u) != 0;
         if (p->mq_pre) {
             const size_t pieces_bytes = static_cast<size_t>(m) * 8u * (k / 2u), sfb_bytes = static_cast<size_t>(kb_all) * lexb::matmul_q_sfb_bytes(m);
             const size_t total = pieces_bytes + sfb_bytes + 4u * lexb::MQ_MAX_TOKENS;
@@ -1098,7 +1164,11 @@ int lexb_gemm_fp4_plan(lexb_gpu* g, uint32_t m, uint32_t n, uint32_t k, int resi
         if (stages < 2 || w_stages < 2 || lexb::pair_smem_bytes(stages, w_stages) > g->smem_optin)
             return bail(fail(LEXB_ERR_ARG, "stages = %u with w_stages = %u need %u bytes of shared memory (limit %zu)", stages,
                              w_stages, lexb::pair_smem_bytes(stages, w_stages), g->smem_optin));
-        p->tok_blocks = m > 256u ? 2u : 1u;
+        // 512 tokens per tile (each weight decoded once for 512 tokens) when there are that many; tm = 256 asks for
+        // tiles of 256 tokens at any m: twice the tiles and two accumulators per tile, each weight decoded twice
+        if (s.tm && s.tm != 256u && s.tm != 512u)
+            return bail(fail(LEXB_ERR_ARG, "tm = %u: the two-CTA kernel's tiles hold 256 or 512 tokens", s.tm));
+        p->tok_blocks = (m > 256u && s.tm != 256u) ? 2u : 1u;
         p->tm = p->tok_blocks * 256u; p->stages = stages; p->w_stages = w_stages;
         p->flags = env_u32("LEXB_COLLECTOR", 0) ? 1u : 0u; p->tmem_cols = lexb::PAIR_TMEM_COLS; p->n_acc = 1;
         p->m_tiles = (m + p->tm - 1) / p->tm;
@@ -1126,7 +1196,37 @@ int lexb_gemm_fp4_plan(lexb_gpu* g, uint32_t m, uint32_t n, uint32_t k, int resi
                 }
             }
         }
+        // A second way to fill the SM pairs when m > 256 leaves them short of tiles: tiles of 256 tokens (twice the
+        // tiles; every weight is decoded twice, but a tile's partial product is half as large and fewer splits
+        // are needed).  Figures fitted to launches timed on a B200 (us): 3.6 until a block's first MMA, 0.50 / 0.42
+        // per K step with 512 / 256 tokens, 7.5 / 3.8 for a block to store its tile, 3 between launches, and for
+        // the reduction launch its bytes at 4 TB/s plus 2.  The smaller tile is taken when it wins by a tenth.
+        if (!s.k_splits && !s.tm && m > 256u) {
+            auto model = [&](uint32_t tb, uint32_t c, uint32_t* eff_out) {
+                const uint32_t mt = (m + tb * 256u - 1u) / (tb * 256u);
+                const uint32_t rbs = (raw_blocks + c - 1u) / c, eff = (raw_blocks + rbs - 1u) / rbs;
+                const double waves = static_cast<double>((mt * n_pairs * eff + sm_pairs - 1u) / sm_pairs);
+                double us = waves * (3.6 + rbs * 4.0 * (tb == 2u ? 0.50 : 0.42) + (tb == 2u ? 7.5 : 3.8)) + 3.0;
+                if (eff > 1u) us += static_cast<double>(eff) * m * n * 4.0 / 4e6 + 2.0;
+                *eff_out = eff;
+                return us;
+            };
+            uint32_t eff = 0, best_c = 0;
+            const double wide = model(2u, splits, &eff);
+            double best = 1e30;
+            for (uint32_t c = 1; c <= 8u && raw_blocks / c >= 4u; c++) {
+                const double us = model(1u, c, &eff);
+                if (us < best && eff == c) { best = us; best_c = c; }
+            }
+            if (best_c && best < 0.9 * wide) {
+                splits = best_c;
+                p->tok_blocks = 1u;
+                p->tm = 256u;
+                p->m_tiles = (m + 255u) / 256u;
+            }
+        }
         if (splits < 1u || splits > raw_blocks) return bail(fail(LEXB_ERR_ARG, "k_splits = %u outside [1, %u]", splits, raw_blocks));
+        const uint32_t tiles_final = p->m_tiles * n_pairs;
         const uint32_t rb_per_split = (raw_blocks + splits - 1u) / splits;
         splits = (raw_blocks + rb_per_split - 1u) / rb_per_split;          // no empty split
         p->k_splits = splits;
@@ -1135,7 +1235,7 @@ int lexb_gemm_fp4_plan(lexb_gpu* g, uint32_t m, uint32_t n, uint32_t k, int resi
             cudaError_t e = x_malloc(&p->partial, sizeof(float) * splits * static_cast<size_t>(m) * n);
             if (e != cudaSuccess) return bail(fail(LEXB_ERR_CUDA, "allocating the split-K workspace: %s", cudaGetErrorString(e)));
         }
-        p->grid = 2u * tiles * splits;
+        p->grid = 2u * tiles_final * splits;
         p->threads = lexb::PAIR_THREADS;
         p->smem = lexb::pair_smem_bytes(stages, w_stages);
         snprintf(p->entry, sizeof p->entry, "%s_%u_%u_%u_%u_%u_%u", stem, m, n, k, p->tm, 2u * lexb::GEMM_TN, lexb::GEMM_BK);
@@ -1193,6 +1293,38 @@ int lexb_matmul_fp4_plan(lexb_gpu* g, uint32_t t, uint32_t n_out, uint32_t n_in,
     return LEXB_OK;
 }
 
+int lexb_matmul_int8_plan(lexb_gpu* g, uint32_t t, uint32_t n_out, uint32_t n_in, int residual, const lexb_sched* sched,
+                          lexb_pipeline** out) {
+    if (!out) return fail(LEXB_ERR_ARG, "lexb_matmul_int8_plan: null out");
+    *out = nullptr;
+    lexb_sched s{};
+    if (sched) s = *sched;
+    s.kernel = KERNEL_MATMUL_Q;
+    s.flags |= SCHED_INTERNAL_Q16;
+    int rc = lexb_gemm_fp4_plan(g, t, n_out, n_in, residual, &s, out);
+    if (rc) return rc;
+    // the reference's name for the kernel (crates/lex-msl/src/int8.rs:129-132)
+    snprintf((*out)->entry, sizeof (*out)->entry, "matmul_int8_%ux%ux%u%s", t, n_out, n_in, residual ? "_res" : "");
+    return LEXB_OK;
+}
+
+int lexb_quant16(lexb_gpu* g, uint32_t m, uint32_t k, int x_half, const lexb_buffer* x, lexb_buffer* xq, lexb_buffer* xs) {
+    int rc = use(g);
+    if (rc) return rc;
+    if (m == 0 || k == 0 || k % 32u) return fail(LEXB_ERR_SHAPE, "quant16: %u inputs are not whole groups of 32", k);
+    const size_t mm = m, kk = k;
+    if ((rc = check_buf(x, g, mm * kk * (x_half ? 2 : 4), "x"))) return rc;
+    if ((rc = check_buf(xq, g, mm * kk * 2, "xq"))) return rc;
+    if ((rc = check_buf(xs, g, mm * (kk / 16) * 4, "xs"))) return rc;
+    const size_t groups = mm * kk / 16;
+    const uint32_t blocks = static_cast<uint32_t>((groups + 255) / 256);
+    INJECT_LAUNCH();
+    if (x_half) quant16_kernel<true><<<blocks, 256, 0, g->stream>>>(x->ptr, static_cast<short*>(xq->ptr), static_cast<float*>(xs->ptr), groups);
+    else quant16_kernel<false><<<blocks, 256, 0, g->stream>>>(x->ptr, static_cast<short*>(xq->ptr), static_cast<float*>(xs->ptr), groups);
+    CUDA_TRY(cudaGetLastError());
+    return LEXB_OK;
+}
+
 void lexb_pipeline_free(lexb_pipeline* p) {
     if (!p) return;
     if (p->partial || p->pre_buf) {
@@ -1211,7 +1343,7 @@ int lexb_pipeline_describe(const lexb_pipeline* p, lexb_lowered* out) {
     out->grid2 = 1;
     out->threads = p->threads;
     out->threadgroup_bytes = p->smem;
-    out->nbind = p->residual ? 6 : 5;
+    out->nbind = (p->residual ? 6 : 5) + (p->x_q16 ? 1 : 0);
     out->writes[out->nbind - 1] = 1;
     out->kernel = p->kernel;
     out->m = p->m; out->n = p->n; out->k = p->k; out->residual = p->residual;
@@ -1302,6 +1434,7 @@ int lexb_gemm_fp4_enqueue_host(lexb_gpu* g, const lexb_pipeline* p, const void* 
     int rc = use(g);
     if (rc) return rc;
     if (!p || !x_host || !y_host || !x_dev || !y_dev) return fail(LEXB_ERR_ARG, "lexb_gemm_fp4_enqueue_host: null argument");
+    if (p->x_q16) return fail(LEXB_ERR_UNSUPPORTED, "lexb_gemm_fp4_enqueue_host takes f16 or f32 activations; quantise on the device (lexb_quant16) and launch a step");
     const size_t xb = static_cast<size_t>(p->m) * p->k * (p->x_f32 ? 4 : 2), yb = static_cast<size_t>(p->m) * p->n * 4;
     if (x_dev->bytes < xb || y_dev->bytes < yb) return fail(LEXB_ERR_ARG, "lexb_gemm_fp4_enqueue_host: staging buffers too small");
     CUDA_TRY_AT(SITE_COPY, cudaMemcpyAsync(x_dev->ptr, x_host, xb, cudaMemcpyHostToDevice, g->stream));
@@ -1316,6 +1449,7 @@ int lexb_gemm_fp4_run_host(lexb_gpu* g, const lexb_pipeline* p, const void* x_ho
     int rc = use(g);
     if (rc) return rc;
     if (!p || !x_host || !y_host || !x_dev || !y_dev) return fail(LEXB_ERR_ARG, "lexb_gemm_fp4_run_host: null argument");
+    if (p->x_q16) return fail(LEXB_ERR_UNSUPPORTED, "lexb_gemm_fp4_run_host takes f16 or f32 activations; quantise on the device (lexb_quant16) and launch a step");
     const size_t xb = static_cast<size_t>(p->m) * p->k * (p->x_f32 ? 4 : 2), yb = static_cast<size_t>(p->m) * p->n * 4;
     if (x_dev->bytes < xb || y_dev->bytes < yb) return fail(LEXB_ERR_ARG, "lexb_gemm_fp4_run_host: staging buffers too small");
     CUDA_TRY_AT(SITE_COPY, cudaMemcpyAsync(x_dev->ptr, x_host, xb, cudaMemcpyHostToDevice, g->stream));

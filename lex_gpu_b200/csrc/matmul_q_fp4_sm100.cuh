@@ -705,10 +705,13 @@ matmul_q_fp4_kernel(const __grid_constant__ CUtensorMap tmap_wq, const __grid_co
 //   amax   [m]: the token's largest magnitude as f32 bits.
 // It follows the previous launch of the same pipeline in the stream, which may still be reading these
 // buffers: nothing is written before grid_dependency_wait().
-template <bool XF32>
+// XMODE: 0 = f16 activations, 1 = f32, 2 = int16 activations with one f32 scale per 16 values (`xs`), as
+// lex_msl::int8::quant16 leaves them (crates/lex-msl/src/int8.rs:47-114): the value is q * xs in f32.
+template <int XMODE>
 __global__ void __launch_bounds__(1024, 1)
 matmul_q_pieces_kernel(const void* __restrict__ x, uint32_t k, uint8_t* __restrict__ pieces, uint8_t* __restrict__ sfb,
-                       uint32_t* __restrict__ amax) {
+                       uint32_t* __restrict__ amax, const float* __restrict__ xs) {
+    constexpr bool XF32 = XMODE == 1, Q16 = XMODE == 2;
     const bool wide = gridDim.x > 16u;                        // tokens = gridDim.x
     const uint32_t sfb_stage = matmul_q_sfb_bytes(gridDim.x);
     __shared__ uint32_t s_amax;
@@ -718,7 +721,17 @@ matmul_q_pieces_kernel(const void* __restrict__ x, uint32_t k, uint8_t* __restri
     grid_dependency_wait();
     __syncthreads();
     const uint4* xr = XF32 ? reinterpret_cast<const uint4*>(static_cast<const float*>(x) + (size_t)tok * k)
-                           : reinterpret_cast<const uint4*>(static_cast<const __half*>(x) + (size_t)tok * k);
+                           : reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(x) + (size_t)tok * k);
+    const float* xsr = Q16 ? xs + (size_t)tok * (k / 16u) : nullptr;
+    // eight int16 (one 16-byte load) times their group's scale, as f32 bit patterns
+    auto q16_widen = [](const uint4& v, float sc, uint32_t (&fb)[8]) {
+        const uint32_t hw[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (uint32_t i = 0; i < 4; i++) {
+            fb[2 * i] = __float_as_uint(__fmul_rn((float)(short)(hw[i] & 0xFFFFu), sc));
+            fb[2 * i + 1] = __float_as_uint(__fmul_rn((float)(short)(hw[i] >> 16), sc));
+        }
+    };
     const uint32_t row_chunks = XF32 ? k / 4u : k / 8u;
     uint32_t mx = 0;
 #pragma unroll 4
@@ -727,6 +740,11 @@ matmul_q_pieces_kernel(const void* __restrict__ x, uint32_t k, uint8_t* __restri
         if (XF32) {
             mx = max(max(mx, v.x & 0x7FFFFFFFu), v.y & 0x7FFFFFFFu);
             mx = max(max(mx, v.z & 0x7FFFFFFFu), v.w & 0x7FFFFFFFu);
+        } else if (Q16) {
+            uint32_t fb[8];
+            q16_widen(v, __ldg(xsr + (i >> 1)), fb);
+#pragma unroll
+            for (uint32_t j = 0; j < 8; j++) mx = max(mx, fb[j] & 0x7FFFFFFFu);
         } else {
             mx = __vmaxu2(mx, v.x & 0x7FFF7FFFu);
             mx = __vmaxu2(mx, v.y & 0x7FFF7FFFu);
@@ -734,7 +752,7 @@ matmul_q_pieces_kernel(const void* __restrict__ x, uint32_t k, uint8_t* __restri
             mx = __vmaxu2(mx, v.w & 0x7FFF7FFFu);
         }
     }
-    if (!XF32) {
+    if (!XF32 && !Q16) {
         mx = max(mx & 0xFFFFu, mx >> 16);
         mx = __float_as_uint(__half2float(__ushort_as_half((unsigned short)mx)));
     }
@@ -752,7 +770,8 @@ matmul_q_pieces_kernel(const void* __restrict__ x, uint32_t k, uint8_t* __restri
             lo = __ldg(xr + (size_t)kb * (MQ_STAGE_K / 8u) + lane);
         }
         uint32_t fb[8], w[8], e8;
-        mq_widen<XF32>(lo, hi, fb);
+        if (Q16) q16_widen(lo, __ldg(xsr + (size_t)kb * (MQ_STAGE_K / 16u) + (lane >> 1)), fb);
+        else mq_widen<XF32>(lo, hi, fb);
         mq_digits(fb, w, e8);
         const int q0 = 8 - (int)(te8 - e8);
         const uint32_t grp = lane >> 1;

@@ -31,7 +31,7 @@ SYMBOLS = [
     "lexb_selftest_bounded_wait", "lexb_dequant_fp4_f16", "lexb_shard_rows", "lexb_trace_enable", "lexb_trace_read",
     "lexb_gemm_fp4_splitk_static", "lexb_gemm_fp4_launch_gather", "lexb_silu_mul", "lexb_prefill_chunks",
     "lexb_matmul_fp4_plan", "lexb_debug_fail_next", "lexb_gemm_fp4_silu_launch", "lexb_gemm_fp4_silu_launch_gather",
-    "lexb_interleave_rows",
+    "lexb_interleave_rows", "lexb_quant16", "lexb_matmul_int8_plan",
 ]
 
 
@@ -60,7 +60,7 @@ SITE_ALLOC, SITE_COPY, SITE_LAUNCH, SITE_ENCODE = 1, 2, 3, 4
 
 class Lowered(ctypes.Structure):
     _fields_ = [("entry", c_char * 96), ("grid", c_uint32), ("grid2", c_uint32), ("threads", c_uint32),
-                ("threadgroup_bytes", c_uint32), ("nbind", c_uint32), ("writes", c_uint8 * 6), ("kernel", c_uint32),
+                ("threadgroup_bytes", c_uint32), ("nbind", c_uint32), ("writes", c_uint8 * 8), ("kernel", c_uint32),
                 ("m", c_uint32), ("n", c_uint32), ("k", c_uint32), ("residual", c_uint32),
                 ("bm", c_uint32), ("bn", c_uint32), ("bk", c_uint32), ("stages", c_uint32),
                 ("k_splits", c_uint32), ("scratch_bytes", c_uint64)]
@@ -132,6 +132,8 @@ def load_library() -> ctypes.CDLL:
     L.lexb_gemm_fp4_silu_launch.argtypes = [vp, vp, vp, vp, vp, vp, vp]
     L.lexb_gemm_fp4_silu_launch_gather.argtypes = [vp, vp, vp, vp, vp, vp, POINTER(vp), u32, u32, u32]
     L.lexb_interleave_rows.argtypes = [vp, vp, vp, sz, sz, vp]
+    L.lexb_quant16.argtypes = [vp, u32, u32, c_int, vp, vp, vp]
+    L.lexb_matmul_int8_plan.argtypes = [vp, u32, u32, u32, c_int, POINTER(Sched), POINTER(vp)]
     _lib = L
     return L
 
@@ -337,8 +339,10 @@ class Gpu:
 
     # ---- the operator
     def plan_gemm_fp4(self, m: int, n: int, k: int, residual: bool = False, kernel: int = 0, tm: int = 0,
-                      stages: int = 0, kc: int = 0, w_stages: int = 0, k_splits: int = 0) -> Pipeline:
-        s = Sched(kernel, tm, stages, kc, w_stages, k_splits)
+                      stages: int = 0, kc: int = 0, w_stages: int = 0, k_splits: int = 0, weights_constant: bool = False,
+                      weights_may_change: bool = False) -> Pipeline:
+        flags = (SCHED_WEIGHTS_MAY_CHANGE if weights_may_change else 0) | (SCHED_WEIGHTS_CONSTANT if weights_constant else 0)
+        s = Sched(kernel, tm, stages, kc, w_stages, k_splits, flags)
         h = c_void_p()
         _check(self._L.lexb_gemm_fp4_plan(self.handle, m, n, k, int(residual), byref(s), byref(h)))
         return Pipeline(self, h.value)
@@ -356,6 +360,18 @@ class Gpu:
         h = c_void_p()
         _check(self._L.lexb_matmul_fp4_plan(self.handle, t, n_out, n_in, int(residual), int(x_half), byref(s), byref(h)))
         return Pipeline(self, h.value)
+
+    def plan_matmul_int8(self, t: int, n_out: int, n_in: int, residual: bool = False, stages: int = 0, k_splits: int = 0) -> Pipeline:
+        """matmul_int8 (crates/lex-msl/src/int8.rs:121-223): int16 activations with one f32 scale per 16, as quant16
+        leaves them; launched as a step with the bindings [xq, xs, wq, ws, wg, (r), y]."""
+        s = Sched(0, 0, stages, 0, 0, k_splits, 0)
+        h = c_void_p()
+        _check(self._L.lexb_matmul_int8_plan(self.handle, t, n_out, n_in, int(residual), byref(s), byref(h)))
+        return Pipeline(self, h.value)
+
+    def quant16(self, m: int, k: int, x: Buffer, xq: Buffer, xs: Buffer, x_half: bool) -> None:
+        """quant16 (crates/lex-msl/src/int8.rs:47-114): x[m, k] -> int16 xq[m, k] and f32 xs[m, k/16]."""
+        _check(self._L.lexb_quant16(self.handle, m, k, int(x_half), x.handle, xq.handle, xs.handle))
 
     def run(self, pipe: Pipeline, bufs: Sequence[Buffer]) -> None:
         """One launch, asynchronous; bufs = [x, wq, ws, wg, (r), y] (Gpu::run, device.rs:629-648)."""

@@ -307,3 +307,39 @@ def ensure_built() -> None:
     build()
     if not os.path.exists(HERE / "liblexoracle.so"):
         raise RuntimeError("oracle library missing after build")
+
+
+# ------------------------------------------- the integer-activation path (crates/lex-msl/src/int8.rs)
+
+def np_quant16(x: np.ndarray):
+    """quant16 (crates/lex-msl/src/int8.rs:47-114) restated in numpy float32, operation for operation: per group
+    of 16 values the largest magnitude mx, inv = 32767 / mx (0 for a group of zeros), q = rint(v * inv) as int16
+    (round half to even, as __float2int_rn), scale mx / 32767.  Returns (xq int16 [m, k], xs float32 [m, k/16])."""
+    x = np.asarray(x)
+    m, k = x.shape
+    if k % 32:
+        raise ValueError("quant16: inputs are not whole groups of 32")
+    v = x.astype(np.float32).reshape(m, k // 16, 16)
+    mx = np.abs(v).max(axis=2)
+    with np.errstate(divide="ignore", invalid="ignore"):
+        inv = np.where(mx > 0, np.float32(32767.0) / mx, np.float32(0.0)).astype(np.float32)
+    q = np.rint((v * inv[:, :, None]).astype(np.float32)).astype(np.int32)
+    xq = (q & 0xFFFF).astype(np.uint16).view(np.int16).reshape(m, k)
+    xs = (mx / np.float32(32767.0)).astype(np.float32)
+    return xq, xs
+
+
+def np_matmul_int8_f64(xq, xs, wq, ws, wg, r=None) -> np.ndarray:
+    """What matmul_int8 computes (crates/lex-msl/src/int8.rs:121-223) in f64: per group of 16 the integer dot product
+    of the int16 activations with twice the E2M1 values, times the group's weight scale and activation scale, summed
+    over the row, times the row scale and one half, plus the residual.  (The kernel adds the groups in f32 in a
+    lane-strided order; this is its value without those roundings.)"""
+    m, k = xq.shape
+    c = np_codes(wq)
+    e = E2M1[c].astype(np.float64)                                    # [n, k]
+    s = np.repeat(E4M3[ws.view(np.uint8)].astype(np.float64), 16, axis=1)
+    xv = xq.astype(np.float64) * np.repeat(xs.astype(np.float64), 16, axis=1)
+    y = (xv @ (e * s).T) * wg.astype(np.float64)[None, :]
+    if r is not None:
+        y = y + r.astype(np.float64)
+    return y

@@ -227,3 +227,19 @@ def test_matmul_q_x_on_the_reference_gpu_test_recipes():
     ref = x.astype(np.float64) @ w.T
     assert np.abs(y - ref).max() / np.abs(ref).max() < 1e-6
     assert np.abs(ref).max() > 1.0
+
+
+def test_quant16_restatement_properties():
+    """crates/lex-msl/src/int8.rs:47-114: int16 codes within +-32767, the group's largest value on the end of the
+    range, a group of zeros gives scale 0 and codes 0, and xq * xs is within half a step of x."""
+    rng = np.random.Generator(np.random.PCG64(9))
+    x = (rng.standard_normal((4, 256)) * np.exp2(rng.integers(-10, 6, (4, 256)))).astype(np.float32)
+    x[0, :16] = 0
+    xq, xs = O.np_quant16(x)
+    assert xq.dtype == np.int16 and xs.dtype == np.float32 and xs.shape == (4, 16)
+    assert np.abs(xq.astype(np.int32)).max() == 32767 and not xq[0, :16].any() and xs[0, 0] == 0
+    back = xq.astype(np.float64) * np.repeat(xs.astype(np.float64), 16, axis=1)
+    assert np.all(np.abs(back - x) <= 0.5000001 * np.repeat(xs, 16, axis=1) + 1e-30)
+    assert np.array_equal(np.abs(xq).reshape(4, 16, 16).max(axis=2)[xs > 0], np.full((xs > 0).sum(), 32767))
+    with pytest.raises(ValueError):
+        O.np_quant16(np.zeros((1, 48), dtype=np.float32))
