@@ -203,3 +203,51 @@ def test_fused_activation_gathered_into_every_ranks_buffer(gpu, splits):
     ref = O.np_silu_mul(O.gemm_fp4(x, *wg_), O.gemm_fp4(x, *wu_), out_f16=True).astype(np.float32)
     err, scale, rel = O.err_of_scale(want.astype(np.float32), ref)
     assert scale > 1e-3 and err <= 2e-3 and rel <= 2e-3
+
+
+def test_ollama_store_manifest_and_sharded_reads(tmp_path, monkeypatch):
+    """The store around the blobs (crates/lex-rt/src/qwen.rs:86-145): a manifest maps tensor names to blob files;
+    a rank of an n-sharded run reads its own 128-row tiles only, and the slabs of all ranks tile the matrix."""
+    mats = {}
+    for i, (name, n, k) in enumerate([("blk.0.ffn_gate.weight", 1152, 256), ("blk.0.ffn_up.weight", 1152, 256), ("blk.0.ffn_down.weight", 256, 1152)]):
+        wq, ws, _ = inputs.make_weights(n, k, seed_base=70 + i)
+        mats[name] = (wq, ws, [0.02, 0.03, 0.5][i])
+    checkpoint.write_store(tmp_path, "synthetic:27b", mats)
+    st = checkpoint.Store.open("synthetic:27b", root=tmp_path)
+    assert st.names() == sorted(mats) and st.has("blk.0.ffn_up.weight") and not st.has("nope")
+    monkeypatch.setenv("OLLAMA_MODELS", str(tmp_path))             # the default root comes from the environment
+    assert checkpoint.Store.open("synthetic:27b").names() == st.names()
+    for name, (wq, ws, gs) in mats.items():
+        full = st.nvfp4(name)
+        assert np.array_equal(full[0], wq) and np.array_equal(full[1], ws) and np.all(full[2] == np.float32(gs))
+    # 1152 rows = 9 tiles over 4 ranks: 3, 2, 2, 2 tiles; the spans are lexb_shard_rows' own
+    name = "blk.0.ffn_gate.weight"
+    spans = []
+    for rank in range(4):
+        wq, ws, wg, n0, n1 = st.nvfp4_shard(name, 4, rank)
+        assert (n0, n1) == L.shard_rows(1152, 4, rank) == checkpoint.shard_span(1152, 4, rank)
+        assert np.array_equal(wq, mats[name][0][n0:n1]) and np.array_equal(ws, mats[name][1][n0:n1]) and wg.shape == (n1 - n0,)
+        spans.append((n0, n1))
+    assert spans[0][0] == 0 and spans[-1][1] == 1152 and all(a[1] == b[0] for a, b in zip(spans, spans[1:]))
+    # gate and up of a rank, interleaved for the fused launch
+    cols = []
+    for rank in range(2):
+        wq, ws, wg, j0, j1 = st.gate_up_shard("blk.0.ffn_gate.weight", "blk.0.ffn_up.weight", 2, rank)
+        g, u = mats["blk.0.ffn_gate.weight"], mats["blk.0.ffn_up.weight"]
+        assert np.array_equal(wq[0::2], g[0][j0:j1]) and np.array_equal(wq[1::2], u[0][j0:j1])
+        assert np.array_equal(ws[0::2], g[1][j0:j1]) and np.array_equal(ws[1::2], u[1][j0:j1])
+        assert np.all(wg[0::2] == np.float32(g[2])) and np.all(wg[1::2] == np.float32(u[2])) and (2 * (j1 - j0)) % 128 == 0
+        cols.append((j0, j1))
+    assert cols[0][0] == 0 and cols[0][1] == cols[1][0] and cols[1][1] == 1152
+    # errors: a model that is not there, a manifest without named layers, rows outside the matrix
+    with pytest.raises(FileNotFoundError):
+        checkpoint.Store.open("missing", root=tmp_path)
+    mdir = tmp_path / "manifests" / "registry.ollama.ai" / "library" / "empty"
+    mdir.mkdir(parents=True)
+    (mdir / "latest").write_text('{"layers": [{"digest": "sha256:1"}]}')
+    with pytest.raises(ValueError):
+        checkpoint.Store.open("empty", root=tmp_path)
+    with pytest.raises(ValueError):
+        st.nvfp4(name, (1024, 2048))
+    with pytest.raises(KeyError):
+        st.nvfp4("blk.9.missing")
