@@ -79,9 +79,6 @@ typedef struct lexb_sched {
  *     this pipeline are in flight, for launches made one at a time (lexb_gemm_fp4_launch). */
 #define LEXB_SCHED_WEIGHTS_MAY_CHANGE 1u
 #define LEXB_SCHED_WEIGHTS_CONSTANT 2u
-/* Two-CTA GEMM with a K split: sum the partial products in a second launch even where the kernel could sum them
- * itself (it does when all of its blocks can be resident at once).  The results are the same bit for bit. */
-#define LEXB_SCHED_REDUCE_LAUNCH 4u
 
 /* lex_msl::program::Lowered, crates/lex-msl/src/program.rs:44-63: the launch descriptor.
  * `writes` is per binding in the order [x, wq, ws, wg, (r), y] (crates/lex-msl/src/gemm.rs:78-82). */
@@ -95,9 +92,8 @@ typedef struct lexb_lowered {
     uint32_t kernel;             /* 1 matvec, 2 tcgen05, 3 two-CTA tcgen05, 4 block-scaled FP4 */
     uint32_t m, n, k, residual;
     uint32_t bm, bn, bk, stages;
-    uint32_t k_splits;           /* > 1: K is split over blocks and the partial products are summed */
+    uint32_t k_splits;           /* > 1: a second launch sums the partial products */
     uint64_t scratch_bytes;      /* Lowered::scratch_bytes: the split-K workspace */
-    uint32_t splits_summed_in_kernel;   /* 1: by the kernel itself; 0 with k_splits > 1: by a second launch */
 } lexb_lowered;
 
 /* lex_cuda::Step, crates/lex-cuda/src/device.rs:314: a pipeline and its buffers in binding

@@ -67,11 +67,6 @@ struct GemmArgs {
     // the f32 y [m, n].
     uint16_t* act;
     uint32_t silu_gather;
-    // Two-CTA kernel with a K split summed inside the launch: after storing its partial tile, a block counts itself
-    // in on `counters[4 * tile + 2 * cta rank]`, waits (bounded) until all k_splits blocks of the tile have, and
-    // sums every k_splits-th token of the tile over the splits in split order; the last block to finish puts the
-    // counters back to zero.  All blocks of the grid must be able to be resident at once (the host checks).
-    uint32_t* counters;
 };
 
 // silu(g) * u = g * (1 / (1 + exp(-g))) * u in f32, one rounding per operation, as the interpreter evaluates

@@ -50,45 +50,6 @@ __host__ __device__ constexpr uint32_t pair_smem_bytes(uint32_t sx, uint32_t sw)
            (2u * sx + 3u * sw + 1u + 2u * PAIR_RAW_STAGES) * 8u + 16u + 1024u;
 }
 
-// Where a summed split-K result goes: y, the f16 activation silu(gate) * up, or - the fused all-gather - every
-// rank's copy of either.
-struct GatherDst {
-    float* y[GATHER_MAX];
-    uint32_t world, n_total, n0, n_local;   // world = 0: plain y
-    uint32_t silu;                          // the gathered buffers are f16 [m, n_total/2] of silu(gate) * up
-};
-
-// Four consecutive columns c..c+3 of token t, summed over the splits (acc): add r, then store as the
-// destination asks.  Shared by the reduction launch and the in-kernel sum, so that both give the same bits.
-__device__ __forceinline__ void splitk_store4(float4 acc, size_t t, size_t c, uint32_t n_local, const float* __restrict__ r,
-                                              float* __restrict__ y, uint16_t* __restrict__ act, const GatherDst& g) {
-    if (r) {
-        const float4 q = *reinterpret_cast<const float4*>(r + t * n_local + c);
-        acc.x += q.x; acc.y += q.y; acc.z += q.z; acc.w += q.w;
-    }
-    if (act != nullptr || g.silu != 0u) {
-        // four columns = two (gate, up) pairs -> two f16 values of row t, columns c/2 and c/2 + 1
-        const uint32_t two = (uint32_t)f32_to_f16_bits(silu_mul_f32(acc.x, acc.y)) |
-                             ((uint32_t)f32_to_f16_bits(silu_mul_f32(acc.z, acc.w)) << 16);
-        if (g.world == 0u) {
-            reinterpret_cast<uint32_t*>(act)[(t * (n_local >> 1) + (c >> 1)) >> 1] = two;
-        } else {
-            const size_t o = (t * (g.n_total >> 1) + ((g.n0 + c) >> 1)) >> 1;
-#pragma unroll
-            for (uint32_t d = 0; d < GATHER_MAX; d++)
-                if (d < g.world) reinterpret_cast<uint32_t*>(g.y[d])[o] = two;
-        }
-    } else if (g.world == 0u) {
-        *reinterpret_cast<float4*>(y + t * n_local + c) = acc;
-    } else {
-        // fused all-gather: element (t, c) of the local [m, n_local] goes to column n0 + c of every y
-        const size_t o = t * g.n_total + g.n0 + c;
-#pragma unroll
-        for (uint32_t d = 0; d < GATHER_MAX; d++)
-            if (d < g.world) *reinterpret_cast<float4*>(g.y[d] + o) = acc;
-    }
-}
-
 template <bool TRACE>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1)
 gemm_fp4_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_wq,
@@ -498,61 +459,6 @@ gemm_fp4_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const _
                 }
             }
         }
-        if (a.counters != nullptr && a.k_splits > 1u) {
-            // ------------------------------------------------------------ the K splits summed inside the launch
-            // Every block of the tile has stored its partial [tile tokens x 128 rows]; count in, wait for the
-            // others, then take every k_splits-th token of the tile.  (Blocks that gave up above still count
-            // in, so that the others are not kept waiting; the status word tells.)
-            uint32_t* const cnt = a.counters + 4u * tile + 2u * rank;
-            __threadfence();                                              // this thread's partial stores, device-wide
-            asm volatile("bar.sync 1, %0;" ::"r"(PAIR_DEQ_THREADS) : "memory");
-            uint32_t all_in = 1;
-            if (tid == 0) {
-                __threadfence();                                          // (after the barrier: all threads' stores)
-                atomicAdd(cnt, 1u);
-                const long long t0 = clock64();
-                uint32_t seen = 0;
-                for (;;) {
-                    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(cnt) : "memory");
-                    if (seen >= a.k_splits) break;
-                    if (*abort_flag || clock64() - t0 > WAIT_LIMIT_CYCLES) {
-                        atomicOr(a.status, ST_WAIT_SPLITS);
-                        all_in = 0;
-                        break;
-                    }
-                    __nanosleep(64);
-                }
-                *reinterpret_cast<volatile uint32_t*>(tmem_slot + 2) = all_in;
-            }
-            asm volatile("bar.sync 1, %0;" ::"r"(PAIR_DEQ_THREADS) : "memory");
-            all_in = *reinterpret_cast<volatile uint32_t*>(tmem_slot + 2);
-            if (go && all_in && n0 < a.n) {
-                __threadfence();
-                GatherDst gd;
-#pragma unroll
-                for (uint32_t d = 0; d < GATHER_MAX; d++) gd.y[d] = a.gather_y[d];
-                gd.world = a.gather_world; gd.n_total = a.gather_n; gd.n0 = a.gather_n0; gd.n_local = a.n; gd.silu = a.silu_gather;
-                const uint32_t t_end = (m0 + TB * 256u < a.m) ? m0 + TB * 256u : a.m;
-                const size_t plane = (size_t)a.m * a.n;
-                // a warp per token: 32 lanes x 4 columns = this block's 128 rows
-                for (uint32_t t = m0 + split + a.k_splits * warp; t < t_end; t += a.k_splits * (PAIR_DEQ_THREADS / 32u)) {
-                    const size_t e = (size_t)t * a.n + n0 + 4u * lane;
-                    float4 acc = __ldcg(reinterpret_cast<const float4*>(a.partial + e));
-                    for (uint32_t s2 = 1; s2 < a.k_splits; s2++) {
-                        const float4 p2 = __ldcg(reinterpret_cast<const float4*>(a.partial + (size_t)s2 * plane + e));
-                        acc.x += p2.x; acc.y += p2.y; acc.z += p2.z; acc.w += p2.w;
-                    }
-                    splitk_store4(acc, t, n0 + 4u * lane, a.n, a.r, a.y, a.act, gd);
-                }
-            }
-            // the last block of the tile to be done puts both counters back for the next launch
-            asm volatile("bar.sync 1, %0;" ::"r"(PAIR_DEQ_THREADS) : "memory");
-            if (tid == 0 && atomicAdd(cnt + 1, 1u) + 1u == a.k_splits) {
-                cnt[0] = 0;
-                cnt[1] = 0;
-                __threadfence();
-            }
-        }
     }
 
     tc_fence_before_sync();
@@ -566,6 +472,12 @@ gemm_fp4_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const _
 }
 
 // y = sum over splits of partial[s] (+ r), four floats per thread step; the order of the sum is fixed.
+struct GatherDst {
+    float* y[GATHER_MAX];
+    uint32_t world, n_total, n0, n_local;   // world = 0: plain y
+    uint32_t silu;                          // the gathered buffers are f16 [m, n_total/2] of silu(gate) * up
+};
+
 // With `act` (or g.silu) set, columns are gate/up interleaved and the kernel writes silu(gate) * up as f16 [m, n/2].
 __global__ void splitk_reduce_kernel(const float* __restrict__ partial, uint32_t splits, size_t elems,
                                      const float* __restrict__ r, float* __restrict__ y, const GatherDst g,
@@ -581,8 +493,33 @@ __global__ void splitk_reduce_kernel(const float* __restrict__ partial, uint32_t
             const float4 p = reinterpret_cast<const float4*>(partial + (size_t)s * elems)[i];
             acc.x += p.x; acc.y += p.y; acc.z += p.z; acc.w += p.w;
         }
-        const size_t e = i * 4, t = e / n_local, c = e - t * n_local;
-        splitk_store4(acc, t, c, n_local, r, y, act, g);
+        if (r) {
+            const float4 q = reinterpret_cast<const float4*>(r)[i];
+            acc.x += q.x; acc.y += q.y; acc.z += q.z; acc.w += q.w;
+        }
+        if (act != nullptr || g.silu != 0u) {
+            // four columns = two (gate, up) pairs -> two f16 values of row t, columns c/2 and c/2 + 1
+            const uint32_t two = (uint32_t)f32_to_f16_bits(silu_mul_f32(acc.x, acc.y)) |
+                                 ((uint32_t)f32_to_f16_bits(silu_mul_f32(acc.z, acc.w)) << 16);
+            const size_t e = i * 4, t = e / n_local, c = e - t * n_local;
+            if (g.world == 0u) {
+                reinterpret_cast<uint32_t*>(act)[(t * (n_local >> 1) + (c >> 1)) >> 1] = two;
+            } else {
+                const size_t o = (t * (g.n_total >> 1) + ((g.n0 + c) >> 1)) >> 1;
+#pragma unroll
+                for (uint32_t d = 0; d < GATHER_MAX; d++)
+                    if (d < g.world) reinterpret_cast<uint32_t*>(g.y[d])[o] = two;
+            }
+        } else if (g.world == 0u) {
+            reinterpret_cast<float4*>(y)[i] = acc;
+        } else {
+            // fused all-gather: element (t, c) of the local [m, n_local] goes to column n0 + c of every y
+            const size_t e = i * 4, t = e / g.n_local, c = e - t * g.n_local;
+            const size_t o = t * g.n_total + g.n0 + c;
+#pragma unroll
+            for (uint32_t d = 0; d < GATHER_MAX; d++)
+                if (d < g.world) *reinterpret_cast<float4*>(g.y[d] + o) = acc;
+        }
     }
 }
 

@@ -153,7 +153,6 @@ struct lexb_pipeline {
     uint8_t* pre_buf = nullptr; // [8 m][k / 2] digit rows, then [k / 256][2048] scale blocks, then [m] magnitudes
     CUtensorMap pre_map{};
     float* partial = nullptr;   // split-K workspace [k_splits][m][n], owned by the pipeline
-    uint32_t* counters = nullptr;   // two-CTA GEMM summing its K splits inside the launch: arrival counters behind the partials
     // matvec
     uint32_t kc;
     uint32_t grid, threads, smem;
@@ -420,7 +419,6 @@ int launch_one(lexb_gpu* g, const lexb_pipeline* p, const lexb_buffer* x, const 
         // proven from the step list - so their copy and decode may run ahead of the stream's order
         a.flags = p->flags | ((p->w_const || (order.early_weights && !p->w_volatile)) ? 2u : 0u);
         a.k_splits = p->k_splits; a.kb_per_split = p->kb_per_split; a.partial = p->partial; a.tok_blocks = p->tok_blocks;
-        a.counters = p->counters;
         a.tmem_cols = p->tmem_cols; a.m_tiles = p->m_tiles; a.n_acc = p->n_acc;
         a.x_tx_bytes = p->kernel == KERNEL_TCGEN05_PAIR ? (p->m < lexb::PAIR_XBLK_ROWS ? p->m : lexb::PAIR_XBLK_ROWS) * 128u
                                                         : (p->tm < p->m ? p->tm : p->m) * 128u;
@@ -442,7 +440,7 @@ int launch_one(lexb_gpu* g, const lexb_pipeline* p, const lexb_buffer* x, const 
                 LAUNCH_TRY(cudaLaunchKernelEx(&cfg, lexb::gemm_fp4_tcgen05_pair_kernel<true>, maps.map, maps.map_wq, maps.map_ws, a));
             else
                 LAUNCH_TRY(cudaLaunchKernelEx(&cfg, lexb::gemm_fp4_tcgen05_pair_kernel<false>, maps.map, maps.map_wq, maps.map_ws, a));
-            if (p->k_splits > 1 && !p->counters) {
+            if (p->k_splits > 1) {
                 CUDA_TRY(cudaGetLastError());
                 const size_t elems = static_cast<size_t>(p->m) * p->n;       // n % 128 == 0: a multiple of 4
                 const uint32_t blocks = static_cast<uint32_t>(std::min<size_t>((elems / 4 + 255) / 256, static_cast<size_t>(g->prop.multiProcessorCount) * 8u));
@@ -1233,43 +1231,13 @@ int lexb_gemm_fp4_plan(lexb_gpu* g, uint32_t m, uint32_t n, uint32_t k, int resi
         splits = (raw_blocks + rb_per_split - 1u) / rb_per_split;          // no empty split
         p->k_splits = splits;
         p->kb_per_split = rb_per_split * (lexb::PAIR_RAW_K / lexb::GEMM_BK);
+        if (splits > 1u) {
+            cudaError_t e = x_malloc(&p->partial, sizeof(float) * splits * static_cast<size_t>(m) * n);
+            if (e != cudaSuccess) return bail(fail(LEXB_ERR_CUDA, "allocating the split-K workspace: %s", cudaGetErrorString(e)));
+        }
         p->grid = 2u * tiles_final * splits;
         p->threads = lexb::PAIR_THREADS;
         p->smem = lexb::pair_smem_bytes(stages, w_stages);
-        if (splits > 1u) {
-            // The splits are summed inside the launch when every block of the grid can be resident at once (blocks
-            // of a tile wait for one another): no second launch, and each block sums its share of the tile while
-            // the partials are in L2.  Otherwise, or with LEXB_SCHED_REDUCE_LAUNCH / LEXB_FUSED_REDUCE=0, a
-            // reduction launch follows.  Both add the splits in the same order: the same bits.
-            bool in_kernel = !(s.flags & LEXB_SCHED_REDUCE_LAUNCH) && env_u32("LEXB_FUSED_REDUCE", 1) != 0;
-            if (in_kernel) {
-                cudaLaunchConfig_t occ{};
-                occ.gridDim = dim3(p->grid);
-                occ.blockDim = dim3(p->threads);
-                occ.dynamicSmemBytes = p->smem;
-                cudaLaunchAttribute cl[1];
-                cl[0].id = cudaLaunchAttributeClusterDimension;
-                cl[0].val.clusterDim.x = 2; cl[0].val.clusterDim.y = 1; cl[0].val.clusterDim.z = 1;
-                occ.attrs = cl;
-                occ.numAttrs = 1;
-                int resident = 0;
-                if (cudaOccupancyMaxActiveClusters(&resident, lexb::gemm_fp4_tcgen05_pair_kernel<false>, &occ) != cudaSuccess) {
-                    cudaGetLastError();
-                    resident = 0;
-                }
-                in_kernel = static_cast<uint32_t>(resident) >= p->grid / 2u;
-            }
-            const size_t pbytes = sizeof(float) * splits * static_cast<size_t>(m) * n;
-            const size_t cbytes = in_kernel ? sizeof(uint32_t) * 4u * tiles_final : 0u;
-            cudaError_t e = x_malloc(&p->partial, pbytes + cbytes);
-            if (e != cudaSuccess) return bail(fail(LEXB_ERR_CUDA, "allocating the split-K workspace: %s", cudaGetErrorString(e)));
-            if (in_kernel) {
-                p->counters = reinterpret_cast<uint32_t*>(reinterpret_cast<char*>(p->partial) + pbytes);
-                e = cudaMemsetAsync(p->counters, 0, cbytes, g->stream);
-                if (e == cudaSuccess) e = cudaStreamSynchronize(g->stream);
-                if (e != cudaSuccess) return bail(fail(LEXB_ERR_CUDA, "clearing the split-K counters: %s", cudaGetErrorString(e)));
-            }
-        }
         snprintf(p->entry, sizeof p->entry, "%s_%u_%u_%u_%u_%u_%u", stem, m, n, k, p->tm, 2u * lexb::GEMM_TN, lexb::GEMM_BK);
     } else {
         if (n % lexb::MV_ROWS) return bail(fail(LEXB_ERR_SHAPE, "gemm_fp4 (matvec): %u rows per block do not divide n = %u", lexb::MV_ROWS, n));
@@ -1375,7 +1343,6 @@ int lexb_pipeline_describe(const lexb_pipeline* p, lexb_lowered* out) {
     out->grid2 = 1;
     out->threads = p->threads;
     out->threadgroup_bytes = p->smem;
-    out->splits_summed_in_kernel = (p->kernel == KERNEL_TCGEN05_PAIR && p->counters) || (p->kernel == KERNEL_MATMUL_Q && p->k_splits > 1u);
     out->nbind = (p->residual ? 6 : 5) + (p->x_q16 ? 1 : 0);
     out->writes[out->nbind - 1] = 1;
     out->kernel = p->kernel;

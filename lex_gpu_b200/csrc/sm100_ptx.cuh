@@ -28,7 +28,6 @@ enum : uint32_t {
     ST_WAIT_EMPTY_DEQ = 1u << 3,   // dequant thread gave up waiting for a free stage
     ST_WAIT_ACC = 1u << 4,         // epilogue gave up waiting for the accumulator
     ST_WAIT_DRAIN = 1u << 5,       // producer gave up waiting for its own copies in flight
-    ST_WAIT_SPLITS = 1u << 6,      // a split-K block gave up waiting for the other splits of its tile
     ST_BAD_ARGS = 1u << 8,         // a device-side argument check failed
     ST_WAIT_NEVER = 1u << 16,      // the self-test wait ran out, as it is meant to
 };

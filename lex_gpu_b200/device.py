@@ -55,7 +55,6 @@ class Sched(ctypes.Structure):
 
 SCHED_WEIGHTS_MAY_CHANGE = 1
 SCHED_WEIGHTS_CONSTANT = 2
-SCHED_REDUCE_LAUNCH = 4
 SITE_ALLOC, SITE_COPY, SITE_LAUNCH, SITE_ENCODE = 1, 2, 3, 4
 
 
@@ -64,7 +63,7 @@ class Lowered(ctypes.Structure):
                 ("threadgroup_bytes", c_uint32), ("nbind", c_uint32), ("writes", c_uint8 * 8), ("kernel", c_uint32),
                 ("m", c_uint32), ("n", c_uint32), ("k", c_uint32), ("residual", c_uint32),
                 ("bm", c_uint32), ("bn", c_uint32), ("bk", c_uint32), ("stages", c_uint32),
-                ("k_splits", c_uint32), ("scratch_bytes", c_uint64), ("splits_summed_in_kernel", c_uint32)]
+                ("k_splits", c_uint32), ("scratch_bytes", c_uint64)]
 
 
 class StepStruct(ctypes.Structure):
@@ -341,9 +340,8 @@ class Gpu:
     # ---- the operator
     def plan_gemm_fp4(self, m: int, n: int, k: int, residual: bool = False, kernel: int = 0, tm: int = 0,
                       stages: int = 0, kc: int = 0, w_stages: int = 0, k_splits: int = 0, weights_constant: bool = False,
-                      weights_may_change: bool = False, reduce_launch: bool = False) -> Pipeline:
-        flags = ((SCHED_WEIGHTS_MAY_CHANGE if weights_may_change else 0) | (SCHED_WEIGHTS_CONSTANT if weights_constant else 0) |
-                 (SCHED_REDUCE_LAUNCH if reduce_launch else 0))
+                      weights_may_change: bool = False) -> Pipeline:
+        flags = (SCHED_WEIGHTS_MAY_CHANGE if weights_may_change else 0) | (SCHED_WEIGHTS_CONSTANT if weights_constant else 0)
         s = Sched(kernel, tm, stages, kc, w_stages, k_splits, flags)
         h = c_void_p()
         _check(self._L.lexb_gemm_fp4_plan(self.handle, m, n, k, int(residual), byref(s), byref(h)))

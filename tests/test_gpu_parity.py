@@ -569,42 +569,3 @@ def test_gemm_shard_shapes_with_the_planned_split(gpu, m, n, k):
         check(got, O.gemm_fp4(x, wq, ws, wg), rel_tol=LONG_K_REL)
     else:
         _check_row_slices(got, x, wq, ws, wg, [(0, 128), (n - 128, n)], LONG_K_REL)
-
-
-# ---------------------------------------------------------------- K splits summed inside the launch
-
-@pytest.mark.parametrize("m,n,k,splits,tm", [(512, 256, 2048, 2, 0), (600, 384, 4096, 4, 0), (300, 128, 1024, 3, 0), (512, 640, 2304, 5, 0),
-                                             (1000, 2176, 5120, 0, 0), (512, 2176, 5120, 4, 256), (700, 384, 2048, 8, 256)])
-def test_splits_summed_in_the_kernel_equal_the_reduction_launch(gpu, m, n, k, splits, tm):
-    """With a K split the two-CTA kernel sums the partial products itself when all its blocks fit the GPU at once:
-    each block of a tile waits for the others and sums its share.  Same order of addition as the reduction launch,
-    so the same bits - with and without the residual, for ragged m and an odd last pair, and launch after launch
-    (the arrival counters must be back at zero each time)."""
-    x, wq, ws, wg = inputs.make_case(m, n, k, seed_base=n + k + 1)
-    r = inputs.make_residual(m, n, seed_base=6)
-    q = L.QBuf(gpu, wq, ws, wg)
-    xb, rb = gpu.upload(x), gpu.upload(r)
-    for res in (False, True):
-        inside = gpu.plan_gemm_fp4(m, n, k, residual=res, kernel=3, k_splits=splits, tm=tm)
-        second = gpu.plan_gemm_fp4(m, n, k, residual=res, kernel=3, k_splits=splits, tm=tm, reduce_launch=True)
-        di, ds = inside.describe(), second.describe()
-        assert di.k_splits == ds.k_splits > 1 and di.splits_summed_in_kernel == 1 and ds.splits_summed_in_kernel == 0
-        ya, yb = gpu.alloc(4 * m * n), gpu.alloc(4 * m * n)
-        gpu.memset(ya, 0xFF)
-        gpu.memset(yb, 0xFF)
-        for _ in range(4):                                  # back to back, no synchronise in between
-            gpu.run(inside, q.bind(xb, rb if res else None, ya))
-        gpu.run(second, q.bind(xb, rb if res else None, yb))
-        got, want = gpu.download(ya, np.float32, (m, n)), gpu.download(yb, np.float32, (m, n))
-        assert gpu.status_word() == 0
-        assert np.array_equal(got, want)
-        check(got, O.gemm_fp4(x, wq, ws, wg, r=r if res else None), rel_tol=TOL if k < 4096 else LONG_K_REL)
-
-
-def test_too_many_blocks_for_the_in_kernel_sum_fall_back_to_the_reduction_launch(gpu):
-    """Blocks of a tile wait for one another, so the kernel sums its splits only when the whole grid is resident
-    at once; a larger grid keeps the second launch."""
-    d = gpu.plan_gemm_fp4(2048, 5120, 17408, kernel=3, k_splits=4).describe()        # 4 m tiles x 20 pairs x 4 splits
-    assert d.grid > 148 and d.k_splits == 4 and d.splits_summed_in_kernel == 0
-    d = gpu.plan_gemm_fp4(512, 5120, 17408).describe()
-    assert d.grid == 120 and d.splits_summed_in_kernel == 1
