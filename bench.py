@@ -549,6 +549,125 @@ def run_ours(args):
         except Exception as e:      # symmetric memory unavailable on this machine
             allgather["fused_peer_stores"] = {"unavailable": repr(e)[:200]}
 
+    # ---- the MLP around the headline GEMM (crates/lex-rt/src/qwen_run.rs:3165-3189) at m = 512: gate and up in ONE
+    # launch over their interleaved rows with silu(gate) * up formed in the epilogue (f16 activation out), then down
+    # with the residual.  N = 1: against the same layer as three GEMM launches and an elementwise launch.  N > 1: rows
+    # sharded, the f16 activation gathered by the epilogue's peer stores (2 bytes per element cross NVLink).
+    mlp = None
+    if full:
+        def rolled_sets(rows, cols_k, seed, copies):
+            """`copies` weight sets of one seeded slab, each the slab rolled by whole 128-row tiles (same bytes
+            and distributions, distinct memory), on the device."""
+            wq, ws, wg = inputs.make_weights(rows, cols_k, seed_base=seed)
+            base = [torch.from_numpy(np.ascontiguousarray(a)).to(dev) for a in (wq, ws, wg)]
+            out = []
+            for c in range(copies):
+                t = [torch.roll(b, shifts=128 * c, dims=0).contiguous() for b in base]
+                out.append((t, [gpu.wrap_tensor(v) for v in t]))
+            return out
+
+        gu_rows = 2 * n_local                                   # this rank's gate and up rows, interleaved
+        gu_bytes = gu_rows * K // 2 + gu_rows * K // 16 + 4 * gu_rows
+        gu_sets = rolled_sets(gu_rows, K, 30_000 * (rank + 1), max(3, -(-300_000_000 // gu_bytes)))
+        pipe_gu = gpu.plan_gemm_fp4(M, gu_rows, K)
+        act_t = torch.empty((M, n_local), dtype=torch.float16, device=dev)
+        act_b = gpu.wrap_tensor(act_t)
+        flops_gu = 2.0 * M * (2 * N_ROWS) * K
+
+        def gu_fused(i):
+            b = gu_sets[i % len(gu_sets)][1]
+            gpu.run_silu(pipe_gu, xb, b[0], b[1], b[2], act_b)
+
+        s_gu, _ = timed(None, gu_fused, args.steps, args.warmup)
+        d_gu = pipe_gu.describe()
+        mlp = {"gate_up_fused": {"us_per_launch": 1e6 * s_gu / args.steps, "value": flops_gu * args.steps / s_gu / 1e12, "unit": "TFLOP/s",
+                                 "kernel": d_gu.entry.decode(), "k_splits": d_gu.k_splits, "out": "f16 [m, ffn/N] activation",
+                                 "bytes_written_per_launch": int(M * n_local * 2)}}
+        if world == 1:
+            ygu_t = torch.empty((M, gu_rows), dtype=torch.float32, device=dev)
+            ygu_b = gpu.wrap_tensor(ygu_t)
+
+            def gu_unfused(i):
+                b = gu_sets[i % len(gu_sets)][1]
+                gpu.run(pipe_gu, [xb, b[0], b[1], b[2], ygu_b])
+                gpu.silu_mul(M, n_local, ygu_b, ygu_b, act_b, out_f16=True, gate_pitch=gu_rows, up_offset=n_local, up_pitch=gu_rows)
+
+            s_un, _ = timed(None, gu_unfused, args.steps, args.warmup)
+            mlp["gate_up_then_silu_mul_launch"] = {"us_per_step": 1e6 * s_un / args.steps,
+                                                   "note": "one GEMM launch over [m, 2 ffn] f32, then the elementwise launch"}
+            # the whole layer: fused gate/up, then down (n = 5120, k = 17408) with the residual
+            dn_sets = rolled_sets(K, N_ROWS, 31_000, 4)
+            pipe_dn = gpu.plan_gemm_fp4(M, K, N_ROWS, residual=True)
+            res_t = torch.zeros((M, K), dtype=torch.float32, device=dev)
+            out_t = torch.empty((M, K), dtype=torch.float32, device=dev)
+            res_b, out_b = gpu.wrap_tensor(res_t), gpu.wrap_tensor(out_t)
+
+            def layer(i):
+                gu_fused(i)
+                b = dn_sets[i % len(dn_sets)][1]
+                gpu.run(pipe_dn, [act_b, b[0], b[1], b[2], res_b, out_b])
+
+            s_ly, _ = timed(None, layer, args.steps, args.warmup)
+            flops_layer = flops_gu + 2.0 * M * K * N_ROWS
+            mlp["layer"] = {"us_per_layer": 1e6 * s_ly / args.steps, "value": flops_layer * args.steps / s_ly / 1e12, "unit": "TFLOP/s",
+                            "config": "m=512: gate+up fused with silu_mul (ffn 17408, k 5120), down (n 5120, k 17408) + residual"}
+            # end to end through host buffers: x in (f16), the layer, y [m, 5120] f32 out - what a prefill chunk's
+            # MLP moves across PCIe when the activation stays on the device
+            hx_l, hy_l = L.HostBuffer(x_np.nbytes), L.HostBuffer(M * K * 4)
+            hx_l.array(np.float16, (M, K))[:] = x_np
+            x_dev_l = torch.empty((M, K), dtype=torch.float16, device=dev)
+
+            def layer_host(i):
+                with torch.cuda.stream(stream):
+                    x_dev_l.copy_(torch.from_numpy(hx_l.array(np.float16, (M, K))), non_blocking=True)
+                    b = gu_sets[i % len(gu_sets)][1]
+                    gpu.run_silu(pipe_gu, gpu.wrap_tensor(x_dev_l), b[0], b[1], b[2], act_b)
+                    b = dn_sets[i % len(dn_sets)][1]
+                    gpu.run(pipe_dn, [act_b, b[0], b[1], b[2], res_b, out_b])
+                    torch.from_numpy(hy_l.array(np.float32, (M, K))).copy_(out_t, non_blocking=True)
+
+            for i in range(3):
+                layer_host(i)
+            torch.cuda.synchronize(dev)
+            t_h = time.perf_counter()
+            n_h = max(5, min(args.steps, 50))
+            for i in range(n_h):
+                layer_host(i)
+            torch.cuda.synchronize(dev)
+            t_h = time.perf_counter() - t_h
+            mlp["layer_e2e_host_buffers"] = {"us_per_layer": 1e6 * t_h / n_h, "value": flops_layer * n_h / t_h / 1e12, "unit": "TFLOP/s",
+                                             "h2d_bytes_per_step": int(x_np.nbytes), "d2h_bytes_per_step": int(M * K * 4)}
+        else:
+            try:
+                from lex_gpu_b200.shard import SymmetricY
+                with torch.cuda.stream(stream):
+                    sa = SymmetricY(M, N_ROWS, dist.group.WORLD, dtype=torch.float16)
+
+                    def gu_gather(i):
+                        b = gu_sets[i % len(gu_sets)][1]
+                        gpu.run_silu_gather(pipe_gu, xb, b[0], b[1], b[2], sa.ptrs, 2 * N_ROWS, 2 * n0)
+                        sa.barrier()
+
+                    s_gg, _ = timed(None, gu_gather, args.steps, args.warmup)
+                    # parity of the gathered activation: this rank's own columns against its unfused result
+                    sa.tensor.fill_(0)
+                    sa.barrier()
+                    gu_gather(0)
+                    gu_fused(0)
+                    torch.cuda.synchronize(dev)
+                    same = bool(torch.equal(sa.tensor[:, n0:n1], act_t))
+                    sa.barrier()
+                if all_ranks_max((0.0 if same else 1.0,))[0] != 0.0:
+                    raise SystemExit("the gathered f16 activation differs from the rank's own fused result")
+                mlp["gate_up_fused_gathered"] = {"us_per_step": 1e6 * s_gg / args.steps, "value": flops_gu * args.steps / s_gg / 1e12,
+                                                 "unit": "TFLOP/s", "bytes_into_every_gpu": int(M * (N_ROWS - n_local) * 2),
+                                                 "note": "f16 activation [m, ffn] on every rank by peer stores + one barrier per step"}
+            except SystemExit:
+                raise
+            except Exception as e:
+                mlp["gate_up_fused_gathered"] = {"unavailable": repr(e)[:200]}
+        del gu_sets
+
     # ---- one layer of the 27B MLP stack at m = 4096 (the 64-layer stack configuration), n-sharded: gate, up (n=17408,
     # k=5120) and down (n=5120, k=17408), independent calls, y not chained.  Reported, not the headline.
     stack = None
@@ -639,7 +758,7 @@ def run_ours(args):
                 "roofline": roofline, "cpu_baseline": info, "e2e": e2e, "gpu_launches": args.steps,
                 "clocks": clocks, "matvec": matvec, "allgather": allgather, "device_status": status,
                 "checksum": checksum, "only": args.only, "stack_m4096": stack, "parity": parity, "sustained": sustained,
-                "reference_kernels_on_this_box": ref_box}
+                "reference_kernels_on_this_box": ref_box, "mlp_m512": mlp}
         print(json.dumps(line))
     if dist is not None:
         dist.barrier()

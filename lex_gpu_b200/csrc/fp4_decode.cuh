@@ -78,22 +78,32 @@ __device__ __forceinline__ GroupTable make_group_table(uint32_t scale_byte, floa
     return make_group_table_f32(e4m3_to_f32(scale_byte), wg);
 }
 
+// d = a ^ (b & c) in one logic instruction
+__device__ __forceinline__ uint32_t xor_and(uint32_t a, uint32_t b, uint32_t c) {
+    uint32_t r;
+    asm("lop3.b32 %0, %1, %2, %3, 0x78;" : "=r"(r) : "r"(a), "r"(b), "r"(c));
+    return r;
+}
+
 // Eight codes (one 32-bit word of wq: code j in bits 4j..4j+3, i.e. column order) ->
 // eight f16 in column order, packed as four f16x2 words.
+// The decode is bound by the integer pipe (64 lanes a clock against the FP32 pipe's 128), so the two shifts are
+// written as multiplies, which the FP32 pipe's integer multiply-add takes, and each sign is folded into its
+// lookup with one three-input logic instruction.
 __device__ __forceinline__ void decode8(const GroupTable& t, uint32_t w, uint32_t& o0, uint32_t& o1,
                                         uint32_t& o2, uint32_t& o3) {
     const uint32_t mag = w & 0x77777777u;     // selector nibbles: bit 3 must be clear for prmt
-    const uint32_t mag_hi = mag >> 16;
-    const uint32_t w4 = w << 4;
+    const uint32_t mag_hi = __umulhi(mag, 0x10000u);      // mag >> 16
+    const uint32_t w4 = w * 16u;                          // w << 4
     // sign bytes: prmt's replicate-msb mode (selector bit 3) turns the sign bit of a code
     // into 0x00 / 0xff.  Codes 0..3 live in bytes 0,1 of w (odd codes: bit 7 of the byte)
     // and of w4 (even codes: bit 3 of w's byte moved up to bit 7).
-    const uint32_t sgn_a = prmt(w4, w, 0xD9C8u) & 0x80808080u;   // codes 0,1,2,3
-    const uint32_t sgn_b = prmt(w4, w, 0xFBEAu) & 0x80808080u;   // codes 4,5,6,7
+    const uint32_t sgn_a = prmt(w4, w, 0xD9C8u);          // codes 0,1,2,3
+    const uint32_t sgn_b = prmt(w4, w, 0xFBEAu);          // codes 4,5,6,7
     const uint32_t lo_a = prmt(t.lo0, t.lo1, mag);
-    const uint32_t hi_a = prmt(t.hi0, t.hi1, mag) ^ sgn_a;
+    const uint32_t hi_a = xor_and(prmt(t.hi0, t.hi1, mag), sgn_a, 0x80808080u);
     const uint32_t lo_b = prmt(t.lo0, t.lo1, mag_hi);
-    const uint32_t hi_b = prmt(t.hi0, t.hi1, mag_hi) ^ sgn_b;
+    const uint32_t hi_b = xor_and(prmt(t.hi0, t.hi1, mag_hi), sgn_b, 0x80808080u);
     o0 = prmt(lo_a, hi_a, 0x5140u);
     o1 = prmt(lo_a, hi_a, 0x7362u);
     o2 = prmt(lo_b, hi_b, 0x5140u);

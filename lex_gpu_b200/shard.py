@@ -70,13 +70,14 @@ def assemble(gathered, shard: RowShard):
 
 
 class SymmetricY:
-    """A gathered y[m, n] f32 on every rank, allocated as symmetric memory so that each rank holds the
-    device addresses of all ranks' buffers (`ptrs`), which is what lexb_gemm_fp4_launch_gather stores to."""
+    """A gathered y[m, n] on every rank (f32 by default; f16 for the gathered activation silu(gate) * up), allocated
+    as symmetric memory so that each rank holds the device addresses of all ranks' buffers (`ptrs`), which is what
+    lexb_gemm_fp4_launch_gather and lexb_gemm_fp4_silu_launch_gather store to."""
 
-    def __init__(self, m: int, n: int, group):
+    def __init__(self, m: int, n: int, group, dtype=None):
         import torch
         import torch.distributed._symmetric_memory as symm
-        self.tensor = symm.empty((m, n), dtype=torch.float32, device=torch.device("cuda", torch.cuda.current_device()))
+        self.tensor = symm.empty((m, n), dtype=dtype or torch.float32, device=torch.device("cuda", torch.cuda.current_device()))
         self.handle = symm.rendezvous(self.tensor, group)
         self.ptrs = [int(p) for p in self.handle.buffer_ptrs]
 
