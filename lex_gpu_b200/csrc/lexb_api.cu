@@ -538,11 +538,14 @@ int launch_one(lexb_gpu* g, const lexb_pipeline* p, const lexb_buffer* x, const 
         cfg.attrs = attr;
         cfg.numAttrs = pdl ? 1 : 0;
         if (p->m > 8) {
-            if (ragged) LAUNCH_TRY(cudaLaunchKernelEx(&cfg, lexb::matvec_fp4_kernel<true, true>, a));
-            else LAUNCH_TRY(cudaLaunchKernelEx(&cfg, lexb::matvec_fp4_kernel<true, false>, a));
+            if (ragged) LAUNCH_TRY(cudaLaunchKernelEx(&cfg, lexb::matvec_fp4_kernel<true, true, false>, a));
+            else LAUNCH_TRY(cudaLaunchKernelEx(&cfg, lexb::matvec_fp4_kernel<true, false, false>, a));
+        } else if (lexb::matvec_uses_ring(p->m)) {
+            if (ragged) LAUNCH_TRY(cudaLaunchKernelEx(&cfg, lexb::matvec_fp4_kernel<false, true, true>, a));
+            else LAUNCH_TRY(cudaLaunchKernelEx(&cfg, lexb::matvec_fp4_kernel<false, false, true>, a));
         } else {
-            if (ragged) LAUNCH_TRY(cudaLaunchKernelEx(&cfg, lexb::matvec_fp4_kernel<false, true>, a));
-            else LAUNCH_TRY(cudaLaunchKernelEx(&cfg, lexb::matvec_fp4_kernel<false, false>, a));
+            if (ragged) LAUNCH_TRY(cudaLaunchKernelEx(&cfg, lexb::matvec_fp4_kernel<false, true, false>, a));
+            else LAUNCH_TRY(cudaLaunchKernelEx(&cfg, lexb::matvec_fp4_kernel<false, false, false>, a));
         }
     }
     CUDA_TRY(cudaGetLastError());
@@ -870,10 +873,12 @@ int lexb_open(int device, lexb_gpu** out) {
     if (cudaFuncSetAttribute(lexb::gemm_fp4_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem) != cudaSuccess ||
         cudaFuncSetAttribute(lexb::gemm_fp4_tcgen05_pair_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem) != cudaSuccess ||
         cudaFuncSetAttribute(lexb::gemm_fp4_tcgen05_pair_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem) != cudaSuccess ||
-        cudaFuncSetAttribute(lexb::matvec_fp4_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem) != cudaSuccess ||
-        cudaFuncSetAttribute(lexb::matvec_fp4_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem) != cudaSuccess ||
-        cudaFuncSetAttribute(lexb::matvec_fp4_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem) != cudaSuccess ||
-        cudaFuncSetAttribute(lexb::matvec_fp4_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem) != cudaSuccess ||
+        cudaFuncSetAttribute(lexb::matvec_fp4_kernel<true, true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem) != cudaSuccess ||
+        cudaFuncSetAttribute(lexb::matvec_fp4_kernel<true, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem) != cudaSuccess ||
+        cudaFuncSetAttribute(lexb::matvec_fp4_kernel<false, true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem) != cudaSuccess ||
+        cudaFuncSetAttribute(lexb::matvec_fp4_kernel<false, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem) != cudaSuccess ||
+        cudaFuncSetAttribute(lexb::matvec_fp4_kernel<false, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem) != cudaSuccess ||
+        cudaFuncSetAttribute(lexb::matvec_fp4_kernel<false, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem) != cudaSuccess ||
         cudaFuncSetAttribute(lexb::matmul_q_chain_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem) != cudaSuccess ||
         cudaFuncSetAttribute(lexb::matmul_q_chain_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem) != cudaSuccess ||
         cudaFuncSetAttribute(lexb::matmul_q_chain_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem) != cudaSuccess ||
@@ -1253,7 +1258,7 @@ int lexb_gemm_fp4_plan(lexb_gpu* g, uint32_t m, uint32_t n, uint32_t k, int resi
         if (kc % lexb::MV_ROUND || kc == 0) return bail(fail(LEXB_ERR_ARG, "kc = %u is not a multiple of %u", kc, lexb::MV_ROUND));
         p->kc = kc;
         p->threads = lexb::MV_THREADS;
-        p->smem = lexb::matvec_smem_bytes(m, kc);
+        p->smem = lexb::matvec_smem_bytes(m, kc, lexb::matvec_uses_ring(m));
         if (p->smem > g->smem_optin) return bail(fail(LEXB_ERR_UNSUPPORTED, "kc = %u needs %u bytes of shared memory", kc, p->smem));
         const uint32_t row_blocks = n / lexb::MV_ROWS;
         if (kc >= k) {

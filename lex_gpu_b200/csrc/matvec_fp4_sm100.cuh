@@ -35,6 +35,13 @@ constexpr uint32_t MV_THREADS = MV_WARPS * 32;
 constexpr uint32_t MV_SLICE = 128;                   // K columns per warp iteration
 constexpr uint32_t MV_ROUND = MV_SLICE * MV_WARPS;   // K columns per block round
 constexpr uint32_t MV_RED_BYTES = MV_WARPS * MV_ROWS * 16u * 4u;   // one reduction buffer
+// The packed weights come through a ring in shared memory filled by asynchronous copies (cp.async): a warp keeps
+// MV_DEPTH slices in flight, each lane copying exactly the 2 x 16 bytes of codes it will decode itself (so the ring
+// is a per-lane FIFO and its reads are conflict-free) and one lane of each quad the quad's 2 x 8 scale bytes.
+// With the loads in registers one slice ahead, the warps spent most of their time waiting for memory.
+constexpr uint32_t MV_DEPTH = 3;
+constexpr uint32_t MV_STAGE_BYTES = 2u * 512u + 128u;              // codes of row g, codes of row g + 8, scale bytes
+constexpr uint32_t MV_RING_BYTES = MV_WARPS * MV_DEPTH * MV_STAGE_BYTES;
 
 struct MatvecArgs {
     const __half* x;      // [m, k]
@@ -51,10 +58,13 @@ struct MatvecArgs {
 __host__ __device__ constexpr uint32_t matvec_x_pitch(uint32_t kc) {
     return (kc / 32u) * 72u + ((32u + 128u - ((kc / 32u) * 72u) % 128u) % 128u);
 }
-// two reduction buffers (alternating per row block), then the x chunk
-__host__ __device__ constexpr uint32_t matvec_smem_bytes(uint32_t m, uint32_t kc) {
-    return 2u * MV_RED_BYTES + 128u + m * matvec_x_pitch(kc) + 16u;   // 128 bytes of zeros before x
+// two reduction buffers (alternating per row block), the ring (when used), then the x chunk
+__host__ __device__ constexpr uint32_t matvec_smem_bytes(uint32_t m, uint32_t kc, bool ring) {
+    return 2u * MV_RED_BYTES + (ring ? MV_RING_BYTES : 0u) + 128u + m * matvec_x_pitch(kc) + 16u;   // 128 bytes of zeros before x
 }
+// The ring pays while x leaves room for several blocks per SM: up to 4 tokens.  Beyond, the staged x fills shared
+// memory and the ring would cost a resident block; the weights then come through registers, one slice ahead.
+__host__ __device__ constexpr bool matvec_uses_ring(uint32_t m) { return m <= 4u; }
 
 __device__ __forceinline__ void mma_m16n8k16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                              uint32_t b0, uint32_t b1) {
@@ -69,11 +79,24 @@ struct MvLoad {
     uint32_t sa, sb;     // their two scale bytes (low 16 bits)
 };
 
-template <bool HI, bool RAGGED>   // HI: m > 8, a second group of 8 tokens; RAGGED: k % 128 != 0
+// 16, 8 or 0 bytes from global to shared memory without passing through registers; src_bytes = 0 fills with zeros
+__device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src, uint32_t src_bytes) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_8(uint32_t dst, const void* src, uint32_t src_bytes) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 8, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <uint32_t N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+// HI: m > 8, a second group of 8 tokens; RAGGED: k % 128 != 0; RING: packed weights through the cp.async ring
+template <bool HI, bool RAGGED, bool RING>
 __global__ void __launch_bounds__(MV_THREADS) matvec_fp4_kernel(const MatvecArgs a) {
     extern __shared__ __align__(16) uint8_t mv_smem[];
     float* const red = reinterpret_cast<float*>(mv_smem);               // [2][warp][row 16][token 16]
-    uint8_t* const zeros = mv_smem + 2u * MV_RED_BYTES;                 // 128 bytes: x of a token that does not exist
+    uint8_t* const ring = mv_smem + 2u * MV_RED_BYTES;                  // [warp][MV_DEPTH] stages of packed weights
+    uint8_t* const zeros = ring + (RING ? MV_RING_BYTES : 0u);          // 128 bytes: x of a token that does not exist
     uint8_t* const xs = zeros + 128u;
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
     const uint32_t g = lane >> 2, t = lane & 3u;
@@ -101,26 +124,95 @@ __global__ void __launch_bounds__(MV_THREADS) matvec_fp4_kernel(const MatvecArgs
         if (tid < 16u) *reinterpret_cast<uint2*>(zeros + tid * 8u) = make_uint2(0u, 0u);
     };
 
-    // this lane's loads for slice `it` of row block `rb`
+    // This warp's ring.  Stage layout: [codes of row g: 32 lanes x 16 B][codes of row g + 8][scales: 16 rows x 8 B].
+    uint8_t* const my_ring = ring + warp * (MV_DEPTH * MV_STAGE_BYTES);
+    const uint32_t my_ring_u32 = smem_u32(my_ring);
     const size_t q_pitch8 = (size_t)8u * (k / 2), s_pitch8 = (size_t)8u * (k / 16);
+    // asynchronous copies of slice `it` of row block `rb` into stage `st` (one commit group, also when the slice
+    // does not exist: the groups are counted)
+    auto issue = [&](uint32_t rb, uint32_t it, uint32_t st, bool exists) {
+        if (exists) {
+            const uint32_t col = it * MV_SLICE + 32u * t;               // first of this lane's 32 columns
+            const uint32_t in_k = (lane_in_k_always || col < k) ? 1u : 0u;   // k % 32 == 0: all 32 or none (then zeros)
+            const uint32_t colc = in_k ? col : 0u;
+            const uint8_t* qa_p = a.wq + (size_t)(rb * MV_ROWS + g) * (k / 2) + colc / 2u;
+            const uint32_t dst = my_ring_u32 + st * MV_STAGE_BYTES + lane * 16u;
+            cp_async_16(dst, qa_p, 16u * in_k);
+            cp_async_16(dst + 512u, qa_p + q_pitch8, 16u * in_k);
+            if (RAGGED) {
+                // k % 128 != 0: a row's scale bytes are not 8-byte aligned, so each lane fetches its own two
+                // (plain loads; these shapes are small)
+                const uint8_t* sa_p = a.ws + (size_t)(rb * MV_ROWS + g) * (k / 16) + colc / 16u;
+                uint8_t* sdst = my_ring + st * MV_STAGE_BYTES + 1024u + g * 8u + 2u * t;
+                *reinterpret_cast<unsigned short*>(sdst) = in_k ? __ldg(reinterpret_cast<const unsigned short*>(sa_p)) : (unsigned short)0;
+                *reinterpret_cast<unsigned short*>(sdst + 64u) =
+                    in_k ? __ldg(reinterpret_cast<const unsigned short*>(sa_p + s_pitch8)) : (unsigned short)0;
+            } else if (t == 0u) {
+                // the quad's scale bytes: columns it * 128 .. +127 of rows g and g + 8, 8 bytes each
+                const uint8_t* sa_p = a.ws + (size_t)(rb * MV_ROWS + g) * (k / 16) + it * (MV_SLICE / 16u);
+                const uint32_t sdst = my_ring_u32 + st * MV_STAGE_BYTES + 1024u + g * 8u;
+                cp_async_8(sdst, sa_p, 8u);
+                cp_async_8(sdst + 64u, sa_p + s_pitch8, 8u);
+            }
+        }
+        cp_async_commit();
+    };
+    // the register path (RING = false): this lane's loads for slice `it` of row block `rb`
     auto load = [&](uint32_t rb, uint32_t it) {
         MvLoad L;
-        const uint32_t col = it * MV_SLICE + 32u * t;                   // first of this lane's 32 columns
-        if (lane_in_k_always || col < k) {                              // k % 32 == 0: all 32 or none
+        const uint32_t col = it * MV_SLICE + 32u * t;
+        if (lane_in_k_always || col < k) {
             const uint8_t* qa_p = a.wq + (size_t)(rb * MV_ROWS + g) * (k / 2) + col / 2u;
             const uint8_t* sa_p = a.ws + (size_t)(rb * MV_ROWS + g) * (k / 16) + col / 16u;
             L.qa = __ldg(reinterpret_cast<const uint4*>(qa_p));
             L.qb = __ldg(reinterpret_cast<const uint4*>(qa_p + q_pitch8));
             L.sa = __ldg(reinterpret_cast<const unsigned short*>(sa_p));
             L.sb = __ldg(reinterpret_cast<const unsigned short*>(sa_p + s_pitch8));
-        } else {                                                        // past the end: zero codes, unit scale
+        } else {                                                        // past the end: zero codes (their lane multiplies by 1.0)
             L.qa = make_uint4(0, 0, 0, 0);
             L.qb = make_uint4(0, 0, 0, 0);
-            L.sa = 0x3838u;
-            L.sb = 0x3838u;
+            L.sa = 0u;
+            L.sb = 0u;
         }
         return L;
     };
+    auto take = [&](uint32_t st) {
+        MvLoad L;
+        const uint8_t* sp = my_ring + st * MV_STAGE_BYTES;
+        L.qa = *reinterpret_cast<const uint4*>(sp + lane * 16u);
+        L.qb = *reinterpret_cast<const uint4*>(sp + 512u + lane * 16u);
+        L.sa = *reinterpret_cast<const unsigned short*>(sp + 1024u + g * 8u + 2u * t);
+        L.sb = *reinterpret_cast<const unsigned short*>(sp + 1024u + 64u + g * 8u + 2u * t);
+        return L;
+    };
+
+    // (started before x is staged: the first slices land meanwhile)
+    // the copy cursor runs MV_DEPTH slices ahead of the decode, in the same order: this warp's slices of a row
+    // block, then those of the block's next row block
+    uint32_t rb_c = blockIdx.x, it_c = warp, st_c = 0;
+    auto issue_next = [&]() {
+        while (rb_c < row_blocks && it_c >= slices) {                   // (a warp with no slice in this row block)
+            it_c = warp;
+            rb_c += gridDim.x;
+        }
+        const bool exists = rb_c < row_blocks && it_c < slices;
+        issue(rb_c, it_c, st_c, exists);
+        st_c = st_c + 1u == MV_DEPTH ? 0u : st_c + 1u;
+        if (exists) {
+            it_c += MV_WARPS;
+            if (it_c >= slices) {
+                it_c = warp;
+                rb_c += gridDim.x;
+            }
+        }
+    };
+    MvLoad nxt{};
+    if constexpr (RING) {
+#pragma unroll
+        for (uint32_t d = 0; d < MV_DEPTH; d++) issue_next();
+    } else {
+        nxt = load(blockIdx.x < row_blocks ? blockIdx.x : 0u, warp < slices ? warp : 0u);
+    }
 
     if (resident) {
         stage_x(0, k);
@@ -129,7 +221,7 @@ __global__ void __launch_bounds__(MV_THREADS) matvec_fp4_kernel(const MatvecArgs
 
     uint32_t rb = blockIdx.x;
     uint32_t it = warp;
-    MvLoad nxt = load(rb < row_blocks ? rb : 0u, it < slices ? it : 0u);
+    uint32_t st = 0;
     uint32_t parity = 0;
 
     for (; rb < row_blocks; rb += gridDim.x, parity ^= 1u) {
@@ -146,8 +238,17 @@ __global__ void __launch_bounds__(MV_THREADS) matvec_fp4_kernel(const MatvecArgs
                 __syncthreads();
             }
             while (it < slices && it * MV_SLICE < k1) {
-                const MvLoad cur = nxt;
-                {   // next slice of this row block, or the first slice of the block's next row block
+                MvLoad cur;
+                if constexpr (RING) {
+                    cp_async_wait<MV_DEPTH - 1>();                      // the oldest slice in flight has landed
+                    __syncwarp();                                       // (the scale bytes were copied by lane 0 of the quad)
+                    cur = take(st);
+                    __syncwarp();                                       // every lane has read the stage: refill it
+                    issue_next();
+                    st = st + 1u == MV_DEPTH ? 0u : st + 1u;
+                } else {
+                    cur = nxt;
+                    // next slice of this row block, or the first slice of the block's next row block
                     uint32_t it_n = it + MV_WARPS, rb_n = rb;
                     if (it_n >= slices) {
                         it_n = warp;
