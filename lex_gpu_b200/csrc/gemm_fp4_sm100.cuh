@@ -72,7 +72,7 @@ struct GemmArgs {
 // silu(g) * u = g * (1 / (1 + exp(-g))) * u in f32, one rounding per operation, as the interpreter evaluates
 // lex_front::llama::silu_mul (crates/lex-front/src/llama.rs:879-888; sigmoid: crates/lex-front/src/ir.rs:244)
 __device__ __forceinline__ float silu_mul_f32(float g, float u) {
-    const float sg = __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-g)));
+    const float sg = __frcp_rn(__fadd_rn(1.0f, expf(-g)));      // 1 / x rounded to nearest: the same bits as the division
     return __fmul_rn(__fmul_rn(g, sg), u);
 }
 __device__ __forceinline__ uint16_t f32_to_f16_bits(float v) {

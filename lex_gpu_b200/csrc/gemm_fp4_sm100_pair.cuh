@@ -409,51 +409,66 @@ gemm_fp4_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const _
                 if (!to_partial && (a.act != nullptr || a.silu_gather != 0u)) {
                     // gate/up fused: this lane's row is a gate row (even) or the up row of the same output
                     // column (odd).  The gate lane finishes tokens 0-7 of the chunk, the up lane tokens 8-15;
-                    // each sends the other the eight values it needs.
+                    // each sends the other the eight values it needs.  The f16 results of the chunk - 16 tokens
+                    // x this block's 64 activation columns, from the four warps that share the chunk - meet in
+                    // shared memory (the x ring is idle by now) and leave as 16-byte stores, 128 contiguous
+                    // bytes per token: full lines for local memory and for the NVLink stores of the gather.
                     const bool is_up = (lane & 1u) != 0u;
-                    const uint32_t col = out_row >> 1;
+                    uint8_t* const tile = smem + slice * 4096u + ((cc >> 2) & 1u) * 2048u;     // two buffers per slice
 #pragma unroll
                     for (uint32_t j = 0; j < 8; j++) {
                         const float send = __uint_as_float(is_up ? v[j] : v[8u + j]);
                         const float recv = __shfl_xor_sync(0xFFFFFFFFu, send, 1);
                         const float g = is_up ? recv : __uint_as_float(v[j]);
                         const float u = is_up ? __uint_as_float(v[8u + j]) : recv;
-                        const uint32_t t = t0 + (is_up ? 8u + j : j);
-                        if (t < a.m) {
-                            const uint16_t h = f32_to_f16_bits(silu_mul_f32(g, u));
-                            if (a.silu_gather == 0u) {
-                                a.act[(size_t)t * (a.n >> 1) + col] = h;
-                            } else {
-                                const size_t o = (size_t)t * (a.gather_n >> 1) + (a.gather_n0 >> 1) + col;
-#pragma unroll
-                                for (uint32_t d = 0; d < GATHER_MAX; d++)
-                                    if (d < a.gather_world) reinterpret_cast<uint16_t*>(a.gather_y[d])[o] = h;
-                            }
-                        }
+                        const uint32_t tl = is_up ? 8u + j : j;
+                        *reinterpret_cast<uint16_t*>(tile + tl * 128u + (16u * quarter + (lane >> 1)) * 2u) =
+                            f32_to_f16_bits(silu_mul_f32(g, u));
                     }
-                } else if (a.gather_world == 0u || to_partial) {
+                    asm volatile("bar.sync %0, 128;" ::"r"(2u + slice) : "memory");
+                    const uint32_t i = 32u * quarter + lane, tok = i >> 3, part = i & 7u;
+                    const uint32_t t = t0 + tok;
+                    if (t < a.m) {
+                        const uint4 val = *reinterpret_cast<const uint4*>(tile + tok * 128u + part * 16u);
+                        if (a.silu_gather == 0u) {
+                            *reinterpret_cast<uint4*>(a.act + (size_t)t * (a.n >> 1) + (n0 >> 1) + part * 8u) = val;
+                        } else {
+                            const size_t o = (size_t)t * (a.gather_n >> 1) + ((a.gather_n0 + n0) >> 1) + part * 8u;
 #pragma unroll
-                    for (uint32_t j = 0; j < 16; j++) {
-                        const uint32_t t = t0 + j;
-                        if (t < a.m) {
-                            const size_t o = (size_t)t * a.n + out_row;
-                            float val = __uint_as_float(v[j]);
-                            if (res) val = val + __ldg(res + o);
-                            out[o] = val;
+                            for (uint32_t d = 0; d < GATHER_MAX; d++)
+                                if (d < a.gather_world) *reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(a.gather_y[d]) + o) = val;
                         }
                     }
                 } else {
-                    // fused all-gather: the same 128-byte row segment goes to every GPU's y
+                    // The chunk - 16 tokens x this block's 128 rows, from the four warps that share it - meets in
+                    // shared memory (the x ring is idle by now) and leaves as 16-byte stores: a warp writes 512
+                    // contiguous bytes of one token where a lane-per-row store would write 128, and the gather's
+                    // NVLink stores are full lines.  Two buffers per slice, so one barrier per chunk is enough.
+                    float* const tile = reinterpret_cast<float*>(smem + slice * 16384u + ((cc >> 2) & 1u) * 8192u);
 #pragma unroll
-                    for (uint32_t j = 0; j < 16; j++) {
-                        const uint32_t t = t0 + j;
+                    for (uint32_t j = 0; j < 16; j++) tile[j * 128u + 32u * quarter + lane] = __uint_as_float(v[j]);
+                    asm volatile("bar.sync %0, 128;" ::"r"(2u + slice) : "memory");
+                    const uint32_t i = 32u * quarter + lane;
+#pragma unroll
+                    for (uint32_t q = 0; q < 4; q++) {
+                        const uint32_t p = i + 128u * q, tok = p >> 5, part = p & 31u;
+                        const uint32_t t = t0 + tok;
                         if (t < a.m) {
-                            float val = __uint_as_float(v[j]);
-                            if (res) val = val + __ldg(res + (size_t)t * a.n + out_row);
-                            const size_t o = (size_t)t * a.gather_n + a.gather_n0 + out_row;
+                            float4 val = *reinterpret_cast<const float4*>(tile + tok * 128u + part * 4u);
+                            const size_t o = (size_t)t * a.n + n0 + part * 4u;
+                            if (res) {
+                                const float4 rr = __ldg(reinterpret_cast<const float4*>(res + o));
+                                val.x += rr.x; val.y += rr.y; val.z += rr.z; val.w += rr.w;
+                            }
+                            if (a.gather_world == 0u || to_partial) {
+                                *reinterpret_cast<float4*>(out + o) = val;
+                            } else {
+                                // fused all-gather: the same row segment goes to every GPU's y
+                                const size_t og = (size_t)t * a.gather_n + a.gather_n0 + n0 + part * 4u;
 #pragma unroll
-                            for (uint32_t d = 0; d < GATHER_MAX; d++)
-                                if (d < a.gather_world) a.gather_y[d][o] = val;
+                                for (uint32_t d = 0; d < GATHER_MAX; d++)
+                                    if (d < a.gather_world) *reinterpret_cast<float4*>(a.gather_y[d] + og) = val;
+                            }
                         }
                     }
                 }

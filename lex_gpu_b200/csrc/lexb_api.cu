@@ -241,8 +241,7 @@ __global__ void silu_mul_kernel(uint32_t rows, uint32_t cols, const float* __res
         float y[4];
 #pragma unroll
         for (int j = 0; j < 4; j++) {
-            const float sg = __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-gg[j])));
-            y[j] = __fmul_rn(__fmul_rn(gg[j], sg), uu[j]);
+            y[j] = lexb::silu_mul_f32(gg[j], uu[j]);
         }
         if constexpr (sizeof(OutT) == 4) {
             *reinterpret_cast<float4*>(reinterpret_cast<float*>(out) + r * cols + c) = make_float4(y[0], y[1], y[2], y[3]);
