@@ -300,13 +300,6 @@ def run_ours(args):
         secs, clocks = timed(pipe, gemm_step, 1, 3)
     else:
         secs, clocks = timed(pipe, gemm_step, args.steps, args.warmup, sample_clocks=full)
-    if full and (clocks or {}).get("samples", 0) < 3:
-        # the timed region is shorter than the sampler's period: sample clocks over a longer
-        # run of the same steps (not the reported time)
-        _, clocks2 = timed(pipe, gemm_step, max(args.steps, 3000), 0, sample_clocks=True)
-        if clocks2 and clocks2.get("sm_mhz"):
-            clocks = clocks2
-            clocks["note"] = "sampled over a longer run of the same steps"
     status = gpu.status_word()
     flops_step = 2.0 * M * N_ROWS * K
     tflops = flops_step * args.steps / secs / 1e12
@@ -323,7 +316,7 @@ def run_ours(args):
     # ---- the same steps for seconds, not milliseconds: what the kernel holds under the power cap, with the clocks
     # sampled over this very region and the fraction taken against the sustained cuBLAS figure
     sustained = None
-    if full:
+    if full and args.sustained:
         n_sus = int(min(200_000, max(args.steps, 2.5 / per_launch)))
         s_sus, c_sus = timed(pipe, gemm_step, n_sus, 3, sample_clocks=True)
         tf_sus = flops_step * n_sus / s_sus / 1e12
@@ -332,6 +325,11 @@ def run_ours(args):
                      "frac_of_sustained_peak": (local_flops * n_sus / s_sus / 1e12) / peak_sus, "sustained_peak": peak_sus,
                      "frac_of_nominal_2250": (local_flops * n_sus / s_sus / 1e12) / 2250.0, "clocks": c_sus,
                      "us_x_median_mhz": (1e6 * s_sus / n_sus) * c_sus["sm_mhz"] if c_sus and c_sus.get("sm_mhz") else None}
+        if (clocks or {}).get("samples", 0) < 3 and c_sus and c_sus.get("sm_mhz"):
+            # the headline's timed region is shorter than the sampler's period: the record of the same steps held
+            # for seconds stands in (its own figure is under "sustained")
+            clocks = dict(c_sus)
+            clocks["note"] = "the timed region is shorter than the sampler's period; sampled over the sustained run of the same steps"
 
     # ---- e2e: host x -> device, launch, y -> host, every step, through the C ABI call
     e2e, checksum = None, None
@@ -773,6 +771,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-stack", dest="stack", action="store_false",
                     help="skip the m=4096 stack-layer leg (reported under stack_m4096)")
+    ap.add_argument("--no-sustained", dest="sustained", action="store_false",
+                    help="skip the seconds-long run of the headline steps (short runs for profilers)")
     ap.add_argument("--only", default="all", choices=["all", "gemm", "matvec"],
                     help="time one kernel only (short runs for profilers); the JSON line then omits the other legs")
     args = ap.parse_args()

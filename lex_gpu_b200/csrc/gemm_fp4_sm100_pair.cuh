@@ -316,9 +316,16 @@ gemm_fp4_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const _
         long long dq_wait_raw = 0, dq_wait_empty = 0, dq_t0 = 0;
         if (TRACE) dq_t0 = clock64();
         RingPos pw, pr;
-        for (uint32_t kb = 0; kb < KB; kb++, pw.advance(SW)) {
-            const uint32_t s = pw.s, ph = pw.ph;
-            const uint32_t jj = kb & 3u;
+        bool joined = !early_w;
+        // Two K steps per iteration (KB is a multiple of 4: K comes in blocks of 256 columns): the two groups'
+        // decodes are independent instruction streams the scheduler can interleave, and the block's waits and
+        // barrier traffic are paid once per pair.  The tiles still go to the MMA one K step at a time.
+        for (uint32_t kb = 0; kb < KB; kb += 2u) {
+            const uint32_t s0 = pw.s, ph0 = pw.ph;
+            pw.advance(SW);
+            const uint32_t s1 = pw.s, ph1 = pw.ph;
+            pw.advance(SW);
+            const uint32_t jj = kb & 3u;                                   // 0 or 2
             if (jj == 0u && kb != 0u) pr.advance(PAIR_RAW_STAGES);
             const uint32_t rs = pr.s, rph = pr.ph;
             long long tq0 = 0;
@@ -331,35 +338,53 @@ gemm_fp4_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const _
                 break;
             }
             if (TRACE) dq_wait_raw += clock64() - tq0;
-            // codes of K step jj of this block: bytes 32 jj + 8 qtr of row r, in the swizzled tile
+            // codes of K steps jj, jj + 1 of this block: bytes 32 jj + 8 qtr of row r, in the swizzled tile
             const uint8_t* raw = raw0 + rs * PAIR_RAW_BYTES;
-            const uint32_t ch = 2u * jj + (qtr >> 1);
-            const uint2 q = *reinterpret_cast<const uint2*>(raw + r * 128u + ((ch ^ sw_xor) << 4) + 8u * (qtr & 1u));
-            const uint32_t sb = raw[PAIR_RAW_WQ_BYTES + r * 16u + 4u * jj + qtr];
-            if (jj == 3u || kb + 1 == KB) {                              // this warp is done with the block
+            const uint32_t cha = 2u * jj + (qtr >> 1), chb = cha + 2u;
+            const uint2 qa = *reinterpret_cast<const uint2*>(raw + r * 128u + ((cha ^ sw_xor) << 4) + 8u * (qtr & 1u));
+            const uint2 qb = *reinterpret_cast<const uint2*>(raw + r * 128u + ((chb ^ sw_xor) << 4) + 8u * (qtr & 1u));
+            const uint32_t sba = raw[PAIR_RAW_WQ_BYTES + r * 16u + 4u * jj + qtr];
+            const uint32_t sbb = raw[PAIR_RAW_WQ_BYTES + r * 16u + 4u * jj + 4u + qtr];
+            if (jj == 2u || kb + 2u >= KB) {                             // this warp is done with the block
                 __syncwarp();
                 if (lane == 0) mbar_arrive(raw_empty(rs));
             }
-            uint4 o0, o1;
-            decode_group16(q, sb, g, o0, o1);
+            uint4 a0, a1, b0, b1;
+            decode_group16(qa, sba, g, a0, a1);
+            decode_group16(qb, sbb, g, b0, b1);
             long long tq1 = 0;
             if (TRACE) tq1 = clock64();
-            if (early_w && kb == SW) grid_dependency_wait();                      // the W ring is full
-            if (!__all_sync(0xFFFFFFFFu, mbar_wait(w_empty(s), ph ^ 1u, abort_flag))) {
+            if (!joined && kb + 1u >= SW) {                              // the W ring is full: join the stream's order
+                grid_dependency_wait();
+                joined = true;
+            }
+            if (!__all_sync(0xFFFFFFFFu, mbar_wait(w_empty(s0), ph0 ^ 1u, abort_flag))) {
+                atomicOr(a.status, ST_WAIT_EMPTY_DEQ);
+                *abort_flag = 1;
+                ok = false;
+                break;
+            }
+            uint8_t* wt = smem + s0 * GEMM_W_TILE_BYTES + w_off;
+            *reinterpret_cast<uint4*>(wt + (((c + 0u) ^ sw_xor) << 4)) = a0;
+            *reinterpret_cast<uint4*>(wt + (((c + 1u) ^ sw_xor) << 4)) = a1;
+            fence_proxy_async_smem();       // generic-proxy stores -> visible to the MMA's reads
+            // One arrival per warp: hundreds of arrivals on one barrier serialise in shared memory
+            // and were the longest item of a K step.
+            __syncwarp();
+            if (lane == 0) mbar_arrive(w_full(s0));
+            if (!__all_sync(0xFFFFFFFFu, mbar_wait(w_empty(s1), ph1 ^ 1u, abort_flag))) {
                 atomicOr(a.status, ST_WAIT_EMPTY_DEQ);
                 *abort_flag = 1;
                 ok = false;
                 break;
             }
             if (TRACE) dq_wait_empty += clock64() - tq1;
-            uint8_t* wt = smem + s * GEMM_W_TILE_BYTES + w_off;
-            *reinterpret_cast<uint4*>(wt + (((c + 0u) ^ sw_xor) << 4)) = o0;
-            *reinterpret_cast<uint4*>(wt + (((c + 1u) ^ sw_xor) << 4)) = o1;
-            fence_proxy_async_smem();       // generic-proxy stores -> visible to the MMA's reads
-            // One arrival per warp: hundreds of arrivals on one barrier serialise in shared memory
-            // and were the longest item of a K step.
+            wt = smem + s1 * GEMM_W_TILE_BYTES + w_off;
+            *reinterpret_cast<uint4*>(wt + (((c + 0u) ^ sw_xor) << 4)) = b0;
+            *reinterpret_cast<uint4*>(wt + (((c + 1u) ^ sw_xor) << 4)) = b1;
+            fence_proxy_async_smem();
             __syncwarp();
-            if (lane == 0) mbar_arrive(w_full(s));
+            if (lane == 0) mbar_arrive(w_full(s1));
         }
         if (TRACE && a.trace && (tid == 0 || tid == 511)) {
             unsigned long long* tr = a.trace + 16ull * blockIdx.x + (tid == 0 ? 8 : 12);
