@@ -237,7 +237,10 @@ LEXB_API int lexb_selftest_bounded_wait(lexb_gpu* gpu, uint32_t limit_us);
  * x tiles, [4] for its own W tile, [5] for the partner's W tile, [6] accumulator complete,
  * [7] epilogue done ([1]-[5] only in the leader block of a pair); [8..10] and [12..14]: for the
  * first and the last dequant thread, cycles in the decode loop, of which waiting for packed
- * weights, of which waiting for a free W stage.  max_ctas = 0 turns it off.
+ * weights, of which waiting for a free W stage; [15] the block's end and, in the partner block of a
+ * pair, [11] its start, both in nanoseconds of the GPU's global timer.  With max_ctas >= twice the
+ * grid, consecutive launches record into alternating halves of the buffer, so that two launches in a
+ * row can be read side by side.  max_ctas = 0 turns it off.
  * The block-scaled kernel records, per block: [0] start, [1] first stage ready to multiply, [2] all
  * MMAs issued, [3] cycles its MMA warp waited for codes, [4] for scale blocks and pieces, [5] spent
  * issuing; [6..8] the first scale warp's loop, of which waiting for a free stage, for scale bytes;

@@ -87,6 +87,8 @@ gemm_fp4_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const _
     const uint32_t kb_all = a.k / GEMM_BK;
     const uint32_t KB = (kb_all - kb0 < a.kb_per_split) ? (kb_all - kb0) : a.kb_per_split;
     const long long t_start = clock64();
+    unsigned long long gt_start = 0;
+    if (TRACE) asm volatile("mov.u64 %0, %globaltimer;" : "=l"(gt_start));
 
     if (tid == 0) {
         *abort_flag = 0;
@@ -296,7 +298,7 @@ gemm_fp4_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const _
                 tr[4] = (unsigned long long)wait_w;
                 tr[5] = (unsigned long long)wait_p;
                 tr[11] = (unsigned long long)t_issue;     // cycles spent issuing MMAs (queue back-pressure included)
-                tr[15] = (unsigned long long)t_commit;    // cycles spent issuing the two commits
+                (void)t_commit;
             }
         }
         __syncwarp();
@@ -406,6 +408,8 @@ gemm_fp4_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const _
         go = __shfl_sync(0xFFFFFFFFu, go, 0);
         if (TRACE && a.trace && tid == 0) {
             a.trace[16ull * blockIdx.x + 0] = (unsigned long long)t_start;
+            // block start on the global timer (ns): in the partner's record (the leader's slot 11 holds its MMA issue cycles)
+            if (rank != 0u) a.trace[16ull * blockIdx.x + 11] = gt_start;
             a.trace[16ull * blockIdx.x + 6] = (unsigned long long)clock64();   // accumulator complete
         }
         if (go && n0 < a.n) {
@@ -503,7 +507,12 @@ gemm_fp4_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const _
 
     tc_fence_before_sync();
     __syncthreads();
-    if (TRACE && a.trace && tid == 0) a.trace[16ull * blockIdx.x + 7] = (unsigned long long)clock64();   // epilogue done
+    if (TRACE && a.trace && tid == 0) {
+        a.trace[16ull * blockIdx.x + 7] = (unsigned long long)clock64();   // epilogue done
+        unsigned long long gt;
+        asm volatile("mov.u64 %0, %globaltimer;" : "=l"(gt));
+        a.trace[16ull * blockIdx.x + 15] = gt;                             // ... in nanoseconds of the GPU's global timer
+    }
     cluster_sync_all();          // the partner's shared memory and barriers stay alive until both are done
     if (warp == PAIR_WARP_MMA) {
         tc_fence_after_sync();

@@ -100,7 +100,7 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
 enum { KERNEL_MATVEC = 1, KERNEL_TCGEN05 = 2, KERNEL_TCGEN05_PAIR = 3, KERNEL_MATMUL_Q = 4 };
-constexpr uint32_t SCHED_INTERNAL_Q16 = 1u << 30;      // set by lexb_matmul_int8_plan on its way through lexb_gemm_fp4_plan
+thread_local bool t_plan_q16 = false;      // set by lexb_matmul_int8_plan around its call of lexb_gemm_fp4_plan
 
 }  // namespace
 
@@ -123,6 +123,7 @@ struct lexb_gpu {
     std::map<std::tuple<const void*, uint32_t, uint32_t, bool, cudaStream_t>, ChainPre> chain_pre;
     unsigned long long* d_trace = nullptr;   // phase timers of the last two-CTA launch, when tracing is on
     size_t trace_ctas = 0;
+    uint32_t trace_toggle = 0;
     cudaDeviceProp prop{};
     EncodeTiledFn encode_tiled = nullptr;
     size_t smem_optin = 0;
@@ -412,6 +413,9 @@ int launch_one(lexb_gpu* g, const lexb_pipeline* p, const lexb_buffer* x, const 
         }
         a.status = g->d_status;
         a.trace = (g->d_trace && p->kernel == KERNEL_TCGEN05_PAIR && p->grid <= g->trace_ctas) ? g->d_trace : nullptr;
+        // with room for two launches the records alternate between the two halves, so that two launches in a row
+        // can be read side by side (the gap between them on the GPU's global timer)
+        if (a.trace && 2u * p->grid <= g->trace_ctas) a.trace += 16ull * p->grid * (g->trace_toggle++ & 1u);
         a.m = p->m; a.n = p->n; a.k = p->k;
         a.tm = p->tm; a.stages = p->stages; a.w_stages = p->w_stages;
         // bit 0: operand-collector hint; bit 1 (two-CTA kernel): the packed weights are constant - declared, or
@@ -1047,7 +1051,6 @@ int lexb_gemm_fp4_plan(lexb_gpu* g, uint32_t m, uint32_t n, uint32_t k, int resi
     if (m == 0 || n == 0 || k == 0) return fail(LEXB_ERR_SHAPE, "gemm_fp4: empty extent (m=%u n=%u k=%u)", m, n, k);
     lexb_sched s{};
     if (sched) s = *sched;
-    if (s.kernel != KERNEL_MATMUL_Q) s.flags &= ~SCHED_INTERNAL_Q16;
     if (!s.kernel) s.kernel = env_u32("LEXB_KERNEL", 0);
     if (!s.tm) s.tm = env_u32("LEXB_TM", 0);
     if (!s.stages) s.stages = env_u32("LEXB_STAGES", 0);
@@ -1116,7 +1119,7 @@ int lexb_gemm_fp4_plan(lexb_gpu* g, uint32_t m, uint32_t n, uint32_t k, int resi
         // From 5 tokens on the digit rows are derived once per launch by a small kernel ahead of this one
         // (each block deriving them itself is what bounds the kernel there); LEXB_MQ_PRE=0/1 forces either way.
         // (past 16 tokens there is no in-block path; int16 activations are widened by the pieces kernel only)
-        p->x_q16 = (s.flags & SCHED_INTERNAL_Q16) != 0u;
+        p->x_q16 = t_plan_q16;
         p->mq_pre = m > 16u || p->x_q16 || env_u32("LEXB_MQ_PRE", m > 4u ? 1u : 0u) != 0;
         if (p->mq_pre) {
             const size_t pieces_bytes = static_cast<size_t>(m) * 8u * (k / 2u), sfb_bytes = static_cast<size_t>(kb_all) * lexb::matmul_q_sfb_bytes(m);
@@ -1304,8 +1307,9 @@ int lexb_matmul_int8_plan(lexb_gpu* g, uint32_t t, uint32_t n_out, uint32_t n_in
     lexb_sched s{};
     if (sched) s = *sched;
     s.kernel = KERNEL_MATMUL_Q;
-    s.flags |= SCHED_INTERNAL_Q16;
+    t_plan_q16 = true;
     int rc = lexb_gemm_fp4_plan(g, t, n_out, n_in, residual, &s, out);
+    t_plan_q16 = false;
     if (rc) return rc;
     // the reference's name for the kernel (crates/lex-msl/src/int8.rs:129-132)
     snprintf((*out)->entry, sizeof (*out)->entry, "matmul_int8_%ux%ux%u%s", t, n_out, n_in, residual ? "_res" : "");
