@@ -45,6 +45,7 @@ struct GemmArgs {
     uint32_t tm;          // tokens per CTA tile: multiple of 16, 16..256
     uint32_t stages;      // pipeline depth (of the x ring in the two-CTA kernel)
     uint32_t w_stages;    // two-CTA kernel: depth of the ring of decoded W tiles
+    uint32_t raw_stages;  // two-CTA kernel: depth of the ring of packed-weight blocks (256 K columns each)
     uint32_t tmem_cols;   // power of two >= max(32, n_acc * tm)
     uint32_t n_acc;       // 1 or 2 accumulators; with 2, even and odd K steps alternate
     uint32_t m_tiles;     // ceil(m / tm)

@@ -30,7 +30,8 @@ namespace lexb {
 constexpr uint32_t PAIR_TOKENS = 512;                 // tokens per pair tile
 constexpr uint32_t PAIR_XBLK_ROWS = 128;              // tokens per TMA box (one CTA's half of a block)
 constexpr uint32_t PAIR_XBLK_BYTES = PAIR_XBLK_ROWS * 128u;                  // 16 KiB
-constexpr uint32_t PAIR_X_STAGE_BYTES = 2u * PAIR_XBLK_BYTES;                // 32 KiB: two token blocks
+// a stage of the x ring holds this CTA's half of one token block (tiles of 256 tokens) or of two (512): 16 or 32 KiB
+__host__ __device__ constexpr uint32_t pair_x_stage_bytes(uint32_t tok_blocks) { return tok_blocks * PAIR_XBLK_BYTES; }
 constexpr uint32_t PAIR_TMEM_COLS = 512;
 constexpr uint32_t PAIR_DEQ_THREADS = 512;            // 16 warps: one group of 16 weights per thread and K step
 constexpr uint32_t PAIR_WARP_TMA = 16;
@@ -41,13 +42,13 @@ constexpr uint32_t PAIR_RAW_K = 256;                  // K columns per block of 
 constexpr uint32_t PAIR_RAW_WQ_BYTES = GEMM_TN * (PAIR_RAW_K / 2);          // 16 KiB
 constexpr uint32_t PAIR_RAW_WS_BYTES = GEMM_TN * (PAIR_RAW_K / 16);         // 2 KiB
 constexpr uint32_t PAIR_RAW_BYTES = PAIR_RAW_WQ_BYTES + PAIR_RAW_WS_BYTES;
-constexpr uint32_t PAIR_RAW_STAGES = 2;
+constexpr uint32_t PAIR_RAW_STAGES = 2;                // default depth of the ring of packed-weight blocks
 
 // x ring, W ring (their depths are independent: the decoded W tiles may run further ahead of the
 // MMA than the x tiles), packed-weight blocks, barriers, TMEM slot + abort flag, alignment slack
-__host__ __device__ constexpr uint32_t pair_smem_bytes(uint32_t sx, uint32_t sw) {
-    return sx * PAIR_X_STAGE_BYTES + sw * GEMM_W_TILE_BYTES + PAIR_RAW_STAGES * PAIR_RAW_BYTES +
-           (2u * sx + 3u * sw + 1u + 2u * PAIR_RAW_STAGES) * 8u + 16u + 1024u;
+__host__ __device__ constexpr uint32_t pair_smem_bytes(uint32_t tok_blocks, uint32_t sx, uint32_t sw, uint32_t sr = PAIR_RAW_STAGES) {
+    return sx * pair_x_stage_bytes(tok_blocks) + sw * GEMM_W_TILE_BYTES + sr * PAIR_RAW_BYTES +
+           (2u * sx + 3u * sw + 1u + 2u * sr) * 8u + 16u + 1024u;
 }
 
 template <bool TRACE>
@@ -59,10 +60,11 @@ gemm_fp4_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const _
     const uint32_t base = (raw_addr + 1023u) & ~1023u;
     uint8_t* const smem = smem_raw + (base - raw_addr);
 
-    const uint32_t SX = a.stages, SW = a.w_stages;
-    const uint32_t w_base = base + SX * PAIR_X_STAGE_BYTES;                // decoded W tiles
+    const uint32_t SX = a.stages, SW = a.w_stages, SR = a.raw_stages;
+    const uint32_t XSB = pair_x_stage_bytes(a.tok_blocks);
+    const uint32_t w_base = base + SX * XSB;                               // decoded W tiles
     const uint32_t raw_base = w_base + SW * GEMM_W_TILE_BYTES;             // packed weight blocks
-    const uint32_t bars = raw_base + PAIR_RAW_STAGES * PAIR_RAW_BYTES;
+    const uint32_t bars = raw_base + SR * PAIR_RAW_BYTES;
     auto x_full = [&](uint32_t s) { return bars + 8u * s; };                      // leader only: bytes of both CTAs
     auto x_empty = [&](uint32_t s) { return bars + 8u * (SX + s); };              // both CTAs, signalled together
     auto w_full = [&](uint32_t s) { return bars + 8u * (2u * SX + s); };          // each CTA: its own dequant threads
@@ -71,8 +73,8 @@ gemm_fp4_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const _
     const uint32_t nb = 2u * SX + 3u * SW;
     const uint32_t acc_full = bars + 8u * nb;                                     // both CTAs
     auto raw_full = [&](uint32_t rs) { return bars + 8u * (nb + 1u + rs); };
-    auto raw_empty = [&](uint32_t rs) { return bars + 8u * (nb + 1u + PAIR_RAW_STAGES + rs); };
-    uint32_t* const tmem_slot = reinterpret_cast<uint32_t*>(smem + (bars - base) + (nb + 1u + 2u * PAIR_RAW_STAGES) * 8u);
+    auto raw_empty = [&](uint32_t rs) { return bars + 8u * (nb + 1u + SR + rs); };
+    uint32_t* const tmem_slot = reinterpret_cast<uint32_t*>(smem + (bars - base) + (nb + 1u + 2u * SR) * 8u);
     volatile uint32_t* const abort_flag = tmem_slot + 1;
 
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
@@ -101,7 +103,7 @@ gemm_fp4_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const _
             mbar_init(w_peer(s), 1);                         // the partner's relay thread
             mbar_init(w_empty(s), 1);
         }
-        for (uint32_t rs = 0; rs < PAIR_RAW_STAGES; rs++) {
+        for (uint32_t rs = 0; rs < SR; rs++) {
             mbar_init(raw_full(rs), 1);
             mbar_init(raw_empty(rs), PAIR_DEQ_THREADS / 32u);
         }
@@ -147,7 +149,7 @@ gemm_fp4_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const _
                 }
                 const uint32_t lead_bar = map_to_cta(x_full(s), 0);
                 mbar_arrive_expect_tx_cluster(lead_bar, TB * a.x_tx_bytes);
-                const uint32_t dst = base + s * PAIR_X_STAGE_BYTES;
+                const uint32_t dst = base + s * XSB;
                 // token block tb covers tokens m0 + 256 tb .. +255; this CTA holds 128 of them
                 tma_load_2d_pair(dst, &tmap_x, (int)((kb0 + kb) * GEMM_BK), (int)(m0 + rank * PAIR_XBLK_ROWS), lead_bar);
                 if (TB > 1u)
@@ -168,9 +170,9 @@ gemm_fp4_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const _
         if (lane == 0) {
             const uint32_t RB = (KB + 3u) / 4u, rb0 = kb0 / 4u;
             RingPos pr;
-            for (uint32_t rb = 0; rb < RB; rb++, pr.advance(PAIR_RAW_STAGES)) {
+            for (uint32_t rb = 0; rb < RB; rb++, pr.advance(SR)) {
                 const uint32_t rs = pr.s, ph = pr.ph;
-                if (early_w && rb == PAIR_RAW_STAGES) grid_dependency_wait();     // the ring is full: join the stream's order
+                if (early_w && rb == SR) grid_dependency_wait();     // the ring is full: join the stream's order
                 if (!mbar_wait(raw_empty(rs), ph ^ 1u, abort_flag)) {
                     atomicOr(a.status, ST_WAIT_EMPTY_TMA);
                     *abort_flag = 1;
@@ -250,7 +252,7 @@ gemm_fp4_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const _
                 long long ti0 = 0;
                 if (TRACE) ti0 = clock64();
                 // low descriptor halves of this K step's tiles; +2 per 16 columns of K
-                const uint32_t b0 = x_lo0 + s * (PAIR_X_STAGE_BYTES >> 4);
+                const uint32_t b0 = x_lo0 + s * (XSB >> 4);
                 const uint32_t b1 = b0 + (PAIR_XBLK_BYTES >> 4);
                 const uint32_t aw = w_lo0 + sw * (GEMM_W_TILE_BYTES >> 4);
                 if (elect_one()) {
@@ -328,7 +330,7 @@ gemm_fp4_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const _
             const uint32_t s1 = pw.s, ph1 = pw.ph;
             pw.advance(SW);
             const uint32_t jj = kb & 3u;                                   // 0 or 2
-            if (jj == 0u && kb != 0u) pr.advance(PAIR_RAW_STAGES);
+            if (jj == 0u && kb != 0u) pr.advance(SR);
             const uint32_t rs = pr.s, rph = pr.ph;
             long long tq0 = 0;
             if (TRACE) tq0 = clock64();

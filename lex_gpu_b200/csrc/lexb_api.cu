@@ -143,6 +143,7 @@ struct lexb_pipeline {
     bool residual;
     // tcgen05 GEMM
     uint32_t tm, stages, w_stages, tmem_cols, m_tiles, n_acc, flags;
+    uint32_t raw_stages = lexb::PAIR_RAW_STAGES;
     uint32_t k_splits = 1, kb_per_split = 0, tok_blocks = 2;
     uint32_t ws_pitch = 0;      // block-scaled kernel: bytes per row of one scale load
     bool x_f32 = false;         // ... with f32 activations
@@ -417,7 +418,7 @@ int launch_one(lexb_gpu* g, const lexb_pipeline* p, const lexb_buffer* x, const 
         // can be read side by side (the gap between them on the GPU's global timer)
         if (a.trace && 2u * p->grid <= g->trace_ctas) a.trace += 16ull * p->grid * (g->trace_toggle++ & 1u);
         a.m = p->m; a.n = p->n; a.k = p->k;
-        a.tm = p->tm; a.stages = p->stages; a.w_stages = p->w_stages;
+        a.tm = p->tm; a.stages = p->stages; a.w_stages = p->w_stages; a.raw_stages = p->raw_stages;
         // bit 0: operand-collector hint; bit 1 (two-CTA kernel): the packed weights are constant - declared, or
         // proven from the step list - so their copy and decode may run ahead of the stream's order
         a.flags = p->flags | ((p->w_const || (order.early_weights && !p->w_volatile)) ? 2u : 0u);
@@ -1165,18 +1166,14 @@ int lexb_gemm_fp4_plan(lexb_gpu* g, uint32_t m, uint32_t n, uint32_t k, int resi
     } else if (kernel == KERNEL_TCGEN05_PAIR) {
         if (n % lexb::GEMM_TN) return bail(fail(LEXB_ERR_SHAPE, "gemm_fp4 (pair): %u rows per CTA do not divide n = %u", lexb::GEMM_TN, n));
         if (k % lexb::PAIR_RAW_K) return bail(fail(LEXB_ERR_SHAPE, "gemm_fp4 (pair): the packed-weight block of %u columns does not divide k = %u", lexb::PAIR_RAW_K, k));
-        // x ring of 4 stages and W ring of 3 by default (212 KiB with the packed-weight blocks)
-        uint32_t stages = s.stages ? s.stages : 4u;
-        uint32_t w_stages = s.w_stages ? s.w_stages : 3u;
-        if (stages < 2 || w_stages < 2 || lexb::pair_smem_bytes(stages, w_stages) > g->smem_optin)
-            return bail(fail(LEXB_ERR_ARG, "stages = %u with w_stages = %u need %u bytes of shared memory (limit %zu)", stages,
-                             w_stages, lexb::pair_smem_bytes(stages, w_stages), g->smem_optin));
+        const uint32_t raw_stages = env_u32("LEXB_RAWSTAGES", lexb::PAIR_RAW_STAGES);
+        p->raw_stages = raw_stages;
         // 512 tokens per tile (each weight decoded once for 512 tokens) when there are that many; tm = 256 asks for
         // tiles of 256 tokens at any m: twice the tiles and two accumulators per tile, each weight decoded twice
         if (s.tm && s.tm != 256u && s.tm != 512u)
             return bail(fail(LEXB_ERR_ARG, "tm = %u: the two-CTA kernel's tiles hold 256 or 512 tokens", s.tm));
         p->tok_blocks = (m > 256u && s.tm != 256u) ? 2u : 1u;
-        p->tm = p->tok_blocks * 256u; p->stages = stages; p->w_stages = w_stages;
+        p->tm = p->tok_blocks * 256u;
         p->flags = env_u32("LEXB_COLLECTOR", 0) ? 1u : 0u; p->tmem_cols = lexb::PAIR_TMEM_COLS; p->n_acc = 1;
         p->m_tiles = (m + p->tm - 1) / p->tm;
         const uint32_t n_pairs = (n + 2u * lexb::GEMM_TN - 1) / (2u * lexb::GEMM_TN);
@@ -1233,6 +1230,16 @@ int lexb_gemm_fp4_plan(lexb_gpu* g, uint32_t m, uint32_t n, uint32_t k, int resi
             }
         }
         if (splits < 1u || splits > raw_blocks) return bail(fail(LEXB_ERR_ARG, "k_splits = %u outside [1, %u]", splits, raw_blocks));
+        // Ring depths (212 KiB with the two packed-weight blocks either way).  Tiles of 512 tokens: x ring of 4
+        // stages of 32 KiB, W ring of 3; their K step is bound by the MMAs.  Tiles of 256 tokens: a K step's MMAs
+        // take half as long and the hand-offs around a ring slot (commit -> free -> refill -> full, through the
+        // partner CTA) set the pace, so the x stages, half the size, and the W stages are both made deeper: 6 and 5.
+        const uint32_t stages = s.stages ? s.stages : (p->tok_blocks == 2u ? 4u : 6u);
+        const uint32_t w_stages = s.w_stages ? s.w_stages : (p->tok_blocks == 2u ? 3u : 5u);
+        if (stages < 2 || w_stages < 2 || raw_stages < 2 || lexb::pair_smem_bytes(p->tok_blocks, stages, w_stages, raw_stages) > g->smem_optin)
+            return bail(fail(LEXB_ERR_ARG, "stages = %u with w_stages = %u and %u packed-weight blocks need %u bytes of shared memory (limit %zu)",
+                             stages, w_stages, raw_stages, lexb::pair_smem_bytes(p->tok_blocks, stages, w_stages, raw_stages), g->smem_optin));
+        p->stages = stages; p->w_stages = w_stages;
         const uint32_t tiles_final = p->m_tiles * n_pairs;
         const uint32_t rb_per_split = (raw_blocks + splits - 1u) / splits;
         splits = (raw_blocks + rb_per_split - 1u) / rb_per_split;          // no empty split
@@ -1244,7 +1251,7 @@ int lexb_gemm_fp4_plan(lexb_gpu* g, uint32_t m, uint32_t n, uint32_t k, int resi
         }
         p->grid = 2u * tiles_final * splits;
         p->threads = lexb::PAIR_THREADS;
-        p->smem = lexb::pair_smem_bytes(stages, w_stages);
+        p->smem = lexb::pair_smem_bytes(p->tok_blocks, stages, w_stages, raw_stages);
         snprintf(p->entry, sizeof p->entry, "%s_%u_%u_%u_%u_%u_%u", stem, m, n, k, p->tm, 2u * lexb::GEMM_TN, lexb::GEMM_BK);
     } else {
         if (n % lexb::MV_ROWS) return bail(fail(LEXB_ERR_SHAPE, "gemm_fp4 (matvec): %u rows per block do not divide n = %u", lexb::MV_ROWS, n));
@@ -1671,7 +1678,7 @@ int lexb_gemm_fp4_splitk_static(lexb_gpu* g, uint32_t m, uint32_t n, uint32_t k,
     p.kb_per_split = rb_per_split * (lexb::PAIR_RAW_K / lexb::GEMM_BK);
     p.grid = 2u * p.m_tiles * ((n + 2u * lexb::GEMM_TN - 1) / (2u * lexb::GEMM_TN)) * splits;
     p.threads = lexb::PAIR_THREADS;
-    p.smem = lexb::pair_smem_bytes(p.stages, p.w_stages);
+    p.smem = lexb::pair_smem_bytes(2u, p.stages, p.w_stages);
     if (p.smem > g->smem_optin) return fail(LEXB_ERR_UNSUPPORTED, "the device offers %zu bytes of shared memory, the kernel needs %u", g->smem_optin, p.smem);
     const size_t mm = m, nn = n, kk = k;
     if ((rc = check_buf(x, g, mm * kk * 2, "x"))) return rc;
@@ -1699,7 +1706,7 @@ int lexb_gemm_fp4_splitk_static(lexb_gpu* g, uint32_t m, uint32_t n, uint32_t k,
     a.status = g->d_status;
     a.trace = nullptr;
     a.m = m; a.n = n; a.k = k;
-    a.tm = p.tm; a.stages = p.stages; a.w_stages = p.w_stages; a.flags = 0;
+    a.tm = p.tm; a.stages = p.stages; a.w_stages = p.w_stages; a.raw_stages = p.raw_stages; a.flags = 0;
     a.k_splits = splits; a.kb_per_split = p.kb_per_split; a.tok_blocks = p.tok_blocks;
     a.partial = g->static_scratch;          // every element of the partials is written before it is read: nothing to clear
     a.tmem_cols = p.tmem_cols; a.m_tiles = p.m_tiles; a.n_acc = 1;
