@@ -16,9 +16,14 @@
 // 128-byte swizzled, and a [128 x 16 bytes] tile of scales), two such blocks in flight, and the
 // dequant threads read their 8 bytes of codes and 1 scale byte per K step from shared memory.
 //
-// Barriers: the leader CTA's `x_full` and `w_full` collect arrivals from both CTAs (the partner
-// arrives through shared::cluster addresses; its TMA reports bytes to the leader's barrier);
-// `empty` and `acc_full` exist in both CTAs and are signalled together by tcgen05.commit.
+// Barriers: the MMA warp's own loop sets the pace of a K step when the MMAs are short (every wait it makes
+// costs about a hundred cycles even when the barrier is ready, every commit more), so a K step has ONE barrier
+// the MMA warp waits on and ONE it signals.  `full[j]` (leader CTA) collects everything K step j needs: the two
+// x producers' arrive.expect_tx (the partner's through a shared::cluster address; its TMA reports bytes to the
+// leader's barrier), the four warps of the leader's decode group that owns the K step, and one arrival from the
+// partner's relay thread, which waits on the partner's own `w_part` barrier for its four warps.  `done[j]` exists in both CTAs and is signalled
+// in both by one tcgen05.commit: it frees the x stage and the W stage of K step j at once.  Both rings of
+// barriers are indexed by K step modulo max(x stages, W stages, 4); the data rings keep their own depths.
 // No TMA multicast is used.
 #pragma once
 #include "fp4_decode.cuh"
@@ -33,7 +38,7 @@ constexpr uint32_t PAIR_XBLK_BYTES = PAIR_XBLK_ROWS * 128u;                  // 
 // a stage of the x ring holds this CTA's half of one token block (tiles of 256 tokens) or of two (512): 16 or 32 KiB
 __host__ __device__ constexpr uint32_t pair_x_stage_bytes(uint32_t tok_blocks) { return tok_blocks * PAIR_XBLK_BYTES; }
 constexpr uint32_t PAIR_TMEM_COLS = 512;
-constexpr uint32_t PAIR_DEQ_THREADS = 512;            // 16 warps: one group of 16 weights per thread and K step
+constexpr uint32_t PAIR_DEQ_THREADS = 512;            // 16 warps in 4 groups: a group decodes one K step in four, a row per thread
 constexpr uint32_t PAIR_WARP_TMA = 16;
 constexpr uint32_t PAIR_WARP_MMA = 17;                // leader: issues the MMAs; partner: relays its w_full
 constexpr uint32_t PAIR_WARP_RAW = 18;                // TMA of the packed codes and scales
@@ -65,12 +70,14 @@ gemm_fp4_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const _
     const uint32_t w_base = base + SX * XSB;                               // decoded W tiles
     const uint32_t raw_base = w_base + SW * GEMM_W_TILE_BYTES;             // packed weight blocks
     const uint32_t bars = raw_base + SR * PAIR_RAW_BYTES;
-    auto x_full = [&](uint32_t s) { return bars + 8u * s; };                      // leader only: bytes of both CTAs
-    auto x_empty = [&](uint32_t s) { return bars + 8u * (SX + s); };              // both CTAs, signalled together
-    auto w_full = [&](uint32_t s) { return bars + 8u * (2u * SX + s); };          // each CTA: its own dequant threads
-    auto w_peer = [&](uint32_t s) { return bars + 8u * (2u * SX + SW + s); };     // leader only: the partner's W tile
-    auto w_empty = [&](uint32_t s) { return bars + 8u * (2u * SX + 2u * SW + s); };   // both CTAs
-    const uint32_t nb = 2u * SX + 3u * SW;
+    // Depth of the barrier rings: no data ring may be deeper, and at least 4 - a decode group visits the `done`
+    // ring every fourth K step, and a parity wait is only right if the barrier cannot be two phases behind the
+    // one awaited: the group's previous wait (K step j - 4) guarantees phase (j - DN) only if DN >= 4.
+    const uint32_t DN = (SX > SW ? SX : SW) > 4u ? (SX > SW ? SX : SW) : 4u;
+    auto full = [&](uint32_t j) { return bars + 8u * j; };                        // leader only: all inputs of K step j
+    auto done = [&](uint32_t j) { return bars + 8u * (DN + j); };                 // both CTAs: K step j's MMAs complete
+    auto w_part = [&](uint32_t s) { return bars + 8u * (2u * DN + s); };          // partner only: its own decode warps
+    const uint32_t nb = 2u * DN + SW;
     const uint32_t acc_full = bars + 8u * nb;                                     // both CTAs
     auto raw_full = [&](uint32_t rs) { return bars + 8u * (nb + 1u + rs); };
     auto raw_empty = [&](uint32_t rs) { return bars + 8u * (nb + 1u + SR + rs); };
@@ -94,15 +101,12 @@ gemm_fp4_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const _
 
     if (tid == 0) {
         *abort_flag = 0;
-        for (uint32_t s = 0; s < SX; s++) {
-            mbar_init(x_full(s), 2);                         // one arrive.expect_tx per CTA
-            mbar_init(x_empty(s), 1);
+        for (uint32_t j = 0; j < DN; j++) {
+            // one arrive.expect_tx per CTA, one arrival per warp of the leader's decode group, one from the partner's relay
+            mbar_init(full(j), 2u + PAIR_DEQ_THREADS / 128u + 1u);
+            mbar_init(done(j), 1);
         }
-        for (uint32_t s = 0; s < SW; s++) {
-            mbar_init(w_full(s), PAIR_DEQ_THREADS / 32u);    // one arrival per dequant warp of this CTA
-            mbar_init(w_peer(s), 1);                         // the partner's relay thread
-            mbar_init(w_empty(s), 1);
-        }
+        for (uint32_t s = 0; s < SW; s++) mbar_init(w_part(s), PAIR_DEQ_THREADS / 128u);
         for (uint32_t rs = 0; rs < SR; rs++) {
             mbar_init(raw_full(rs), 1);
             mbar_init(raw_empty(rs), PAIR_DEQ_THREADS / 32u);
@@ -139,15 +143,18 @@ gemm_fp4_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const _
     if (warp == PAIR_WARP_TMA) {
         // ---------------------------------------------------------------- TMA producer (both CTAs)
         if (lane == 0) {
-            RingPos px;
-            for (uint32_t kb = 0; kb < KB; kb++, px.advance(SX)) {
-                const uint32_t s = px.s, ph = px.ph;
-                if (!mbar_wait(x_empty(s), ph ^ 1u, abort_flag)) {
-                    atomicOr(a.status, ST_WAIT_EMPTY_TMA);
-                    *abort_flag = 1;
-                    break;
+            RingPos px, pf, pe;              // x stage, barrier of this K step, barrier of the K step that held the stage
+            for (uint32_t kb = 0; kb < KB; kb++, px.advance(SX), pf.advance(DN)) {
+                const uint32_t s = px.s;
+                if (kb >= SX) {
+                    if (!mbar_wait(done(pe.s), pe.ph, abort_flag)) {
+                        atomicOr(a.status, ST_WAIT_EMPTY_TMA);
+                        *abort_flag = 1;
+                        break;
+                    }
+                    pe.advance(DN);
                 }
-                const uint32_t lead_bar = map_to_cta(x_full(s), 0);
+                const uint32_t lead_bar = map_to_cta(full(pf.s), 0);
                 mbar_arrive_expect_tx_cluster(lead_bar, TB * a.x_tx_bytes);
                 const uint32_t dst = base + s * XSB;
                 // token block tb covers tokens m0 + 256 tb .. +255; this CTA holds 128 of them
@@ -192,18 +199,17 @@ gemm_fp4_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const _
         __syncwarp();
     } else if (warp == PAIR_WARP_MMA) {
         if (rank != 0 && lane == 0) {
-            // ------------------------------------------------------------ partner: relay of w_full
+            // ------------------------------------------------------------ partner: relay of its W tiles
             // One cluster-scope arrive per K step from this otherwise idle thread, so that the
             // dequant threads only ever touch barriers of their own CTA.
-            RingPos pw;
-            for (uint32_t kb = 0; kb < KB; kb++, pw.advance(SW)) {
-                const uint32_t s = pw.s, ph = pw.ph;
-                if (!mbar_wait(w_full(s), ph, abort_flag)) {
+            RingPos pw, pf;
+            for (uint32_t kb = 0; kb < KB; kb++, pw.advance(SW), pf.advance(DN)) {
+                if (!mbar_wait(w_part(pw.s), pw.ph, abort_flag)) {
                     atomicOr(a.status, ST_WAIT_W_FULL);
                     *abort_flag = 1;
                     break;
                 }
-                mbar_arrive_cluster(map_to_cta(w_peer(s), 0));
+                mbar_arrive_cluster(map_to_cta(full(pf.s), 0));
             }
         }
         // ---------------------------------------------------------------- MMA issuer (leader only)
@@ -214,38 +220,21 @@ gemm_fp4_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const _
             const uint32_t d0 = tmem_base, d1 = tmem_base + 256u;
             const bool reuse_a = (a.flags & 1u) != 0u;
             bool ok = true;
-            long long wait_x = 0, wait_w = 0, wait_p = 0, t_first = 0, t_issue = 0, t_commit = 0;
-            RingPos px, pw;
-            for (uint32_t kb = 0; kb < KB; kb++, px.advance(SX), pw.advance(SW)) {
-                const uint32_t s = px.s, ph = px.ph;
-                const uint32_t sw = pw.s, phw = pw.ph;
-                long long tw0 = 0, tw1 = 0, tw2 = 0;
+            long long wait_full = 0, t_first = 0, t_issue = 0;
+            RingPos px, pw, pf;
+            for (uint32_t kb = 0; kb < KB; kb++, px.advance(SX), pw.advance(SW), pf.advance(DN)) {
+                const uint32_t s = px.s, sw = pw.s;
+                long long tw0 = 0;
                 if (TRACE) tw0 = clock64();
-                if (!__all_sync(0xFFFFFFFFu, mbar_wait_cluster(x_full(s), ph, abort_flag))) {
-                    atomicOr(a.status, ST_WAIT_X_FULL);
-                    *abort_flag = 1;
-                    ok = false;
-                    break;
-                }
-                if (TRACE) tw1 = clock64();
-                if (!__all_sync(0xFFFFFFFFu, mbar_wait(w_full(sw), phw, abort_flag))) {
-                    atomicOr(a.status, ST_WAIT_W_FULL);
-                    *abort_flag = 1;
-                    ok = false;
-                    break;
-                }
-                if (TRACE) tw2 = clock64();
-                if (!__all_sync(0xFFFFFFFFu, mbar_wait_cluster(w_peer(sw), phw, abort_flag))) {
-                    atomicOr(a.status, ST_WAIT_W_FULL);
+                if (!__all_sync(0xFFFFFFFFu, mbar_wait(full(pf.s), pf.ph, abort_flag))) {
+                    atomicOr(a.status, ST_WAIT_X_FULL | ST_WAIT_W_FULL);
                     *abort_flag = 1;
                     ok = false;
                     break;
                 }
                 if (TRACE) {
                     const long long tw3 = clock64();
-                    wait_x += tw1 - tw0;
-                    wait_w += tw2 - tw1;
-                    wait_p += tw3 - tw2;
+                    wait_full += tw3 - tw0;
                     if (kb == 0) t_first = tw3;
                 }
                 tc_fence_after_sync();
@@ -284,8 +273,7 @@ gemm_fp4_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const _
 #pragma unroll
                     for (uint32_t kk = 1; kk < GEMM_BK / 16; kk++) umma2_acc(d, aw + 2u * kk, b0 + 2u * kk, idesc);
                 }
-                umma_commit_pair(x_empty(s), 3);             // frees the x stage in both CTAs
-                umma_commit_pair(w_empty(sw), 3);            // and the W stage
+                umma_commit_pair(done(pf.s), 3);             // frees this K step's x stage and W stage in both CTAs
                 }
                 __syncwarp();
                 if (TRACE) t_issue += clock64() - ti0;
@@ -296,99 +284,89 @@ gemm_fp4_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const _
                 unsigned long long* tr = a.trace + 16ull * blockIdx.x;
                 tr[1] = (unsigned long long)t_first;      // first stage ready
                 tr[2] = (unsigned long long)clock64();    // all MMAs issued
-                tr[3] = (unsigned long long)wait_x;
-                tr[4] = (unsigned long long)wait_w;
-                tr[5] = (unsigned long long)wait_p;
+                tr[3] = (unsigned long long)wait_full;    // cycles the MMA warp waited for a K step's inputs
+                tr[4] = 0;
+                tr[5] = 0;
                 tr[11] = (unsigned long long)t_issue;     // cycles spent issuing MMAs (queue back-pressure included)
-                (void)t_commit;
             }
         }
         __syncwarp();
     } else {
         // ---------------------------------------------------------------- dequant warps 0-15 (both CTAs)
-        // Thread (row r, group q): a warp covers 32 consecutive rows and one group of 16 columns,
-        // so the 16-byte chunks any 8 consecutive lanes store fall into different bank groups.
-        const uint32_t r = tid & 127u, qtr = tid >> 7;
+        // Four groups of four warps.  A group decodes WHOLE K steps: of every block of 256 K columns, group q takes
+        // K step q - its 128 threads one row each, 64 weights per thread - so a warp meets the barriers once per four
+        // K steps (one wait for the packed block, one for a free W stage, one proxy fence, one arrival) where a
+        // split of every K step over all 16 warps met them every K step; those waits, not the decode arithmetic,
+        // were the longer part of a warp's loop.  The four groups work on four consecutive K steps at once, and
+        // each scheduler holds one warp of every group.
+        // Thread (row r, K step q of the block): a warp covers 32 consecutive rows, so the 16-byte chunks any 8
+        // consecutive lanes load or store fall into different bank groups.
+        const uint32_t r = tid & 127u, q = tid >> 7;
         const uint32_t row = n0 + r;
         // rows past n (second half of an odd last pair): the copy engine fills their codes with zeros
         const float g = row < a.n ? __ldg(a.wg + row) : 0.0f;
         const uint32_t w_off = (w_base - base) + r * 128u;
         const uint32_t sw_xor = r & 7u;
-        const uint32_t c = 2u * qtr;
         const uint8_t* raw0 = smem + (raw_base - base);
         bool ok = true;
         long long dq_wait_raw = 0, dq_wait_empty = 0, dq_t0 = 0;
         if (TRACE) dq_t0 = clock64();
-        RingPos pw, pr;
-        bool joined = !early_w;
-        // Two K steps per iteration (KB is a multiple of 4: K comes in blocks of 256 columns): the two groups'
-        // decodes are independent instruction streams the scheduler can interleave, and the block's waits and
-        // barrier traffic are paid once per pair.  The tiles still go to the MMA one K step at a time.
-        for (uint32_t kb = 0; kb < KB; kb += 2u) {
-            const uint32_t s0 = pw.s, ph0 = pw.ph;
-            pw.advance(SW);
-            const uint32_t s1 = pw.s, ph1 = pw.ph;
-            pw.advance(SW);
-            const uint32_t jj = kb & 3u;                                   // 0 or 2
-            if (jj == 0u && kb != 0u) pr.advance(SR);
+        RingPos pr, pw, pf, pe;          // packed block; W stage and barrier of this K step; barrier of the stage's last user
+        pw.seek(q, SW);
+        pf.seek(q, DN);
+        bool joined = !early_w, pe_set = false;
+        for (uint32_t kb = q; kb < KB; kb += 4u, pr.advance(SR), pw.advance_by(4u, SW), pf.advance_by(4u, DN)) {
             const uint32_t rs = pr.s, rph = pr.ph;
             long long tq0 = 0;
             if (TRACE) tq0 = clock64();
             // waits are made warp-uniform (a vote) so that a give-up leaves no lane behind at a __syncwarp
-            if (jj == 0 && !__all_sync(0xFFFFFFFFu, mbar_wait(raw_full(rs), rph, abort_flag))) {
+            if (!__all_sync(0xFFFFFFFFu, mbar_wait(raw_full(rs), rph, abort_flag))) {
                 atomicOr(a.status, ST_WAIT_X_FULL);
                 *abort_flag = 1;
                 ok = false;
                 break;
             }
             if (TRACE) dq_wait_raw += clock64() - tq0;
-            // codes of K steps jj, jj + 1 of this block: bytes 32 jj + 8 qtr of row r, in the swizzled tile
+            // this K step's 32 bytes of codes (chunks 2q, 2q + 1 of the row, in the swizzled tile) and 4 scale bytes
             const uint8_t* raw = raw0 + rs * PAIR_RAW_BYTES;
-            const uint32_t cha = 2u * jj + (qtr >> 1), chb = cha + 2u;
-            const uint2 qa = *reinterpret_cast<const uint2*>(raw + r * 128u + ((cha ^ sw_xor) << 4) + 8u * (qtr & 1u));
-            const uint2 qb = *reinterpret_cast<const uint2*>(raw + r * 128u + ((chb ^ sw_xor) << 4) + 8u * (qtr & 1u));
-            const uint32_t sba = raw[PAIR_RAW_WQ_BYTES + r * 16u + 4u * jj + qtr];
-            const uint32_t sbb = raw[PAIR_RAW_WQ_BYTES + r * 16u + 4u * jj + 4u + qtr];
-            if (jj == 2u || kb + 2u >= KB) {                             // this warp is done with the block
-                __syncwarp();
-                if (lane == 0) mbar_arrive(raw_empty(rs));
-            }
-            uint4 a0, a1, b0, b1;
-            decode_group16(qa, sba, g, a0, a1);
-            decode_group16(qb, sbb, g, b0, b1);
+            const uint4 c0 = *reinterpret_cast<const uint4*>(raw + r * 128u + (((2u * q) ^ sw_xor) << 4));
+            const uint4 c1 = *reinterpret_cast<const uint4*>(raw + r * 128u + (((2u * q + 1u) ^ sw_xor) << 4));
+            const uint32_t sc = *reinterpret_cast<const uint32_t*>(raw + PAIR_RAW_WQ_BYTES + r * 16u + 4u * q);
+            __syncwarp();
+            if (lane == 0) mbar_arrive(raw_empty(rs));                   // this warp is done with the block
+            uint4 o[8];
+            decode_group16(make_uint2(c0.x, c0.y), sc & 0xFFu, g, o[0], o[1]);
+            decode_group16(make_uint2(c0.z, c0.w), (sc >> 8) & 0xFFu, g, o[2], o[3]);
+            decode_group16(make_uint2(c1.x, c1.y), (sc >> 16) & 0xFFu, g, o[4], o[5]);
+            decode_group16(make_uint2(c1.z, c1.w), sc >> 24, g, o[6], o[7]);
             long long tq1 = 0;
             if (TRACE) tq1 = clock64();
-            if (!joined && kb + 1u >= SW) {                              // the W ring is full: join the stream's order
-                grid_dependency_wait();
-                joined = true;
-            }
-            if (!__all_sync(0xFFFFFFFFu, mbar_wait(w_empty(s0), ph0 ^ 1u, abort_flag))) {
-                atomicOr(a.status, ST_WAIT_EMPTY_DEQ);
-                *abort_flag = 1;
-                ok = false;
-                break;
-            }
-            uint8_t* wt = smem + s0 * GEMM_W_TILE_BYTES + w_off;
-            *reinterpret_cast<uint4*>(wt + (((c + 0u) ^ sw_xor) << 4)) = a0;
-            *reinterpret_cast<uint4*>(wt + (((c + 1u) ^ sw_xor) << 4)) = a1;
-            fence_proxy_async_smem();       // generic-proxy stores -> visible to the MMA's reads
-            // One arrival per warp: hundreds of arrivals on one barrier serialise in shared memory
-            // and were the longest item of a K step.
-            __syncwarp();
-            if (lane == 0) mbar_arrive(w_full(s0));
-            if (!__all_sync(0xFFFFFFFFu, mbar_wait(w_empty(s1), ph1 ^ 1u, abort_flag))) {
-                atomicOr(a.status, ST_WAIT_EMPTY_DEQ);
-                *abort_flag = 1;
-                ok = false;
-                break;
+            if (kb >= SW) {
+                if (!joined) {                                           // first wait on a W stage: join the stream's order
+                    grid_dependency_wait();
+                    joined = true;
+                }
+                if (!pe_set) {
+                    pe.seek(kb - SW, DN);
+                    pe_set = true;
+                }
+                if (!__all_sync(0xFFFFFFFFu, mbar_wait(done(pe.s), pe.ph, abort_flag))) {
+                    atomicOr(a.status, ST_WAIT_EMPTY_DEQ);
+                    *abort_flag = 1;
+                    ok = false;
+                    break;
+                }
+                pe.advance_by(4u, DN);
             }
             if (TRACE) dq_wait_empty += clock64() - tq1;
-            wt = smem + s1 * GEMM_W_TILE_BYTES + w_off;
-            *reinterpret_cast<uint4*>(wt + (((c + 0u) ^ sw_xor) << 4)) = b0;
-            *reinterpret_cast<uint4*>(wt + (((c + 1u) ^ sw_xor) << 4)) = b1;
-            fence_proxy_async_smem();
+            uint8_t* const wt = smem + pw.s * GEMM_W_TILE_BYTES + w_off;
+#pragma unroll
+            for (uint32_t c = 0; c < 8; c++) *reinterpret_cast<uint4*>(wt + ((c ^ sw_xor) << 4)) = o[c];
+            fence_proxy_async_smem();       // generic-proxy stores -> visible to the MMA's reads
+            // One arrival per warp: hundreds of arrivals on one barrier serialise in shared memory.  The tile is
+            // reported to the K step's barrier (leader) or to the relay's (partner).
             __syncwarp();
-            if (lane == 0) mbar_arrive(w_full(s1));
+            if (lane == 0) mbar_arrive(rank == 0u ? full(pf.s) : w_part(pw.s));
         }
         if (TRACE && a.trace && (tid == 0 || tid == 511)) {
             unsigned long long* tr = a.trace + 16ull * blockIdx.x + (tid == 0 ? 8 : 12);

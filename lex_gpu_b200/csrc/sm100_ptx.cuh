@@ -18,6 +18,19 @@ struct RingPos {
             ph ^= 1u;
         }
     }
+    // n steps at once (n small: a few turns of the loop at most)
+    __device__ __forceinline__ void advance_by(uint32_t n, uint32_t depth) {
+        s += n;
+        while (s >= depth) {
+            s -= depth;
+            ph ^= 1u;
+        }
+    }
+    // position of item `index` (divides: for the start of a loop, not for its body)
+    __device__ __forceinline__ void seek(uint32_t index, uint32_t depth) {
+        s = index % depth;
+        ph = (index / depth) & 1u;
+    }
 };
 
 // Status codes a kernel may OR into the status word (0 = clean run).
