@@ -1178,55 +1178,48 @@ int lexb_gemm_fp4_plan(lexb_gpu* g, uint32_t m, uint32_t n, uint32_t k, int resi
         p->m_tiles = (m + p->tm - 1) / p->tm;
         const uint32_t n_pairs = (n + 2u * lexb::GEMM_TN - 1) / (2u * lexb::GEMM_TN);
         const uint32_t tiles = p->m_tiles * n_pairs;
-        // Split K when whole tiles fill the SM pairs badly (few tiles, or a short last wave).  Each
-        // split takes whole blocks of 256 columns (at least 4) and writes a partial product that a
-        // second launch sums.  Model: a K step costs about 0.9 us on a pair with 512 tokens and 0.55 us
-        // with 256 (the decode is the same, the MMAs half); the partials cost their write and read, at
-        // about 8 TB/s while they fit in L2 and 4 TB/s when they do not.
+        // Two ways to fill the SM pairs when whole tiles fill them badly (few tiles, or a short last wave).  Split K:
+        // each split takes whole blocks of 256 columns (at least 4) and writes a partial product that a second
+        // launch sums.  Tiles of 256 tokens when m > 256: twice the tiles; every weight is decoded twice, but a K
+        // step's MMAs take half as long, a tile's partial product is half as large and fewer splits are needed.
+        // Every (tile, splits) pair is priced with figures fitted to launches timed on a B200 (us; rms error 6 %):
+        // per wave of tiles 12.3 / 8.0 for a block's start and its store of a 512 / 256-token tile and 0.595 / 0.385
+        // per K step; for the reduction launch 0.9 plus its bytes at 3.76 TB/s; minus 3.4 overall.  The cheapest
+        // wins; a smaller tile or a further split must win by 2 %.
         const uint32_t sm_pairs = static_cast<uint32_t>(g->prop.multiProcessorCount) / 2u;
         const uint32_t raw_blocks = k / lexb::PAIR_RAW_K;
         uint32_t splits = s.k_splits ? s.k_splits : 1u;
-        if (!s.k_splits) {
-            double best = 1e30;
-            for (uint32_t c = 1; c <= 8u && raw_blocks / c >= 4u; c++) {
-                const uint32_t rbs = (raw_blocks + c - 1u) / c, eff = (raw_blocks + rbs - 1u) / rbs;
-                const double waves = static_cast<double>((tiles * eff + sm_pairs - 1u) / sm_pairs);
-                double us = waves * rbs * 4.0 * (p->tok_blocks == 2u ? 0.9 : 0.55) + 12.0;
-                const double pbytes = static_cast<double>(eff) * m * n * 4.0;
-                if (eff > 1u) us += 2.0 * pbytes / (pbytes <= 64e6 ? 8e6 : 4e6) + 4.0;
-                if (us < best * 0.97) {      // a larger split must win clearly
-                    best = us;
-                    splits = eff;
-                }
-            }
-        }
-        // A second way to fill the SM pairs when m > 256 leaves them short of tiles: tiles of 256 tokens (twice the
-        // tiles; every weight is decoded twice, but a tile's partial product is half as large and fewer splits
-        // are needed).  Figures fitted to launches timed on a B200 (us): 3.6 until a block's first MMA, 0.50 / 0.42
-        // per K step with 512 / 256 tokens, 7.5 / 3.8 for a block to store its tile, 3 between launches, and for
-        // the reduction launch its bytes at 4 TB/s plus 2.  The smaller tile is taken when it wins by a tenth.
-        if (!s.k_splits && !s.tm && m > 256u) {
+        {
             auto model = [&](uint32_t tb, uint32_t c, uint32_t* eff_out) {
                 const uint32_t mt = (m + tb * 256u - 1u) / (tb * 256u);
                 const uint32_t rbs = (raw_blocks + c - 1u) / c, eff = (raw_blocks + rbs - 1u) / rbs;
                 const double waves = static_cast<double>((mt * n_pairs * eff + sm_pairs - 1u) / sm_pairs);
-                double us = waves * (3.6 + rbs * 4.0 * (tb == 2u ? 0.50 : 0.42) + (tb == 2u ? 7.5 : 3.8)) + 3.0;
-                if (eff > 1u) us += static_cast<double>(eff) * m * n * 4.0 / 4e6 + 2.0;
+                double us = -3.4 + waves * (rbs * 4.0 * (tb == 2u ? 0.595 : 0.385) + (tb == 2u ? 12.3 : 8.0));
+                if (eff > 1u) us += 0.9 + static_cast<double>(eff) * m * n * 4.0 / 3.76e6;
                 *eff_out = eff;
                 return us;
             };
-            uint32_t eff = 0, best_c = 0;
-            const double wide = model(2u, splits, &eff);
             double best = 1e30;
-            for (uint32_t c = 1; c <= 8u && raw_blocks / c >= 4u; c++) {
-                const double us = model(1u, c, &eff);
-                if (us < best && eff == c) { best = us; best_c = c; }
+            uint32_t best_tb = p->tok_blocks, best_c = splits;
+            for (uint32_t tb = 2u; tb >= 1u; tb--) {
+                if (tb != p->tok_blocks && (s.tm || m <= 256u)) continue;           // the caller fixed the tile
+                for (uint32_t c = 1; c <= 8u && (c == 1u || raw_blocks / c >= 4u); c++) {
+                    if (s.k_splits && c != s.k_splits) continue;                    // the caller fixed the splits
+                    uint32_t eff = 0;
+                    const double us = model(tb, c, &eff);
+                    if (eff != c && !s.k_splits) continue;                          // the same plan as a smaller c
+                    if (us < best * 0.98) {
+                        best = us;
+                        best_tb = tb;
+                        best_c = c;
+                    }
+                }
             }
-            if (best_c && best < 0.9 * wide) {
-                splits = best_c;
-                p->tok_blocks = 1u;
-                p->tm = 256u;
-                p->m_tiles = (m + 255u) / 256u;
+            splits = best_c;
+            if (best_tb != p->tok_blocks) {
+                p->tok_blocks = best_tb;
+                p->tm = best_tb * 256u;
+                p->m_tiles = (m + p->tm - 1u) / p->tm;
             }
         }
         if (splits < 1u || splits > raw_blocks) return bail(fail(LEXB_ERR_ARG, "k_splits = %u outside [1, %u]", splits, raw_blocks));

@@ -546,12 +546,14 @@ def test_gemm_m2048_gate_up_shape(gpu):
 @pytest.mark.parametrize("n,k", [(17408, 5120), (5120, 17408)])
 def test_gemm_m4096_stack_layer_shapes(gpu, n, k):
     """The calls of the 64-layer stack configuration (m = 4096) on one GPU: oracle on two slices of rows, and the last m tile
-    against the same tokens run as a batch of their own."""
+    against the same tokens run as a batch of their own with the same tile and no K split (the order of the f32
+    additions, and so the bits, belong to the tile shape: the planner may pick another one for 512 tokens alone)."""
     m = 4096
     x, wq, ws, wg = inputs.make_case(m, n, k, seed_base=6)
-    got = L.gemm_fp4(gpu, x, wq, ws, wg, k_splits=1)
+    assert gpu.plan_gemm_fp4(m, n, k).describe().entry.decode() == f"gemm_fp4_{m}_{n}_{k}_512_256_64"
+    got = L.gemm_fp4(gpu, x, wq, ws, wg, k_splits=1, tm=512)
     _check_row_slices(got, x, wq, ws, wg, [(256, 384), (n - 128, n)], LONG_K_REL)
-    sub = L.gemm_fp4(gpu, x[m - 512:].copy(), wq, ws, wg, k_splits=1)
+    sub = L.gemm_fp4(gpu, x[m - 512:].copy(), wq, ws, wg, k_splits=1, tm=512)
     assert np.array_equal(sub, got[m - 512:])
 
 
