@@ -395,7 +395,6 @@ gemm_fp4_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const _
         if (go && n0 < a.n) {
             tc_fence_after_sync();
             const uint32_t quarter = warp & 3u, slice = warp >> 2;      // 4 lane quarters x 4 column slices
-            const uint32_t out_row = n0 + 32u * quarter + lane;
             const bool to_partial = a.k_splits > 1u;
             float* const out = to_partial ? a.partial + (size_t)split * a.m * a.n : a.y;
             const float* const res = to_partial ? nullptr : a.r;

@@ -1177,7 +1177,6 @@ int lexb_gemm_fp4_plan(lexb_gpu* g, uint32_t m, uint32_t n, uint32_t k, int resi
         p->flags = env_u32("LEXB_COLLECTOR", 0) ? 1u : 0u; p->tmem_cols = lexb::PAIR_TMEM_COLS; p->n_acc = 1;
         p->m_tiles = (m + p->tm - 1) / p->tm;
         const uint32_t n_pairs = (n + 2u * lexb::GEMM_TN - 1) / (2u * lexb::GEMM_TN);
-        const uint32_t tiles = p->m_tiles * n_pairs;
         // Two ways to fill the SM pairs when whole tiles fill them badly (few tiles, or a short last wave).  Split K:
         // each split takes whole blocks of 256 columns (at least 4) and writes a partial product that a second
         // launch sums.  Tiles of 256 tokens when m > 256: twice the tiles; every weight is decoded twice, but a K
