@@ -307,7 +307,7 @@ def run_ours(args):
     local_flops = 2.0 * M * n_local * K
     # DRAM bytes per launch (read + write) from an ncu capture of this kernel
     # (m=512 n=17408 k=5120 on one GPU: 55.5 MB read, 3.2 MB written, y still in L2); only for that shape
-    gemm_traffic = 58.7e6 if world == 1 else None
+    gemm_traffic = 58.7e6 if world == 1 and M == 512 else None
     roofline = {"bound": "tensor", "achieved": local_flops / per_launch / 1e12, "peak": peaks["tflops"],
                 "unit": "TFLOP/s", "frac": local_flops / per_launch / 1e12 / peaks["tflops"], "traffic": gemm_traffic,
                 "peak_source": f"{peaks['source']} bf16 burst (cuBLAS 8192^3)", "kernel": desc.entry.decode(),
@@ -775,7 +775,15 @@ def main():
                     help="skip the seconds-long run of the headline steps (short runs for profilers)")
     ap.add_argument("--only", default="all", choices=["all", "gemm", "matvec"],
                     help="time one kernel only (short runs for profilers); the JSON line then omits the other legs")
+    ap.add_argument("--tokens", type=int, default=M,
+                    help="with --only gemm: another token count m for the same matrices (profiler runs of other tile shapes); "
+                         "the metric's own m is the default")
     args = ap.parse_args()
+    if args.tokens != M:
+        if args.only != "gemm" or args.impl != "ours":
+            ap.error("--tokens is for --only gemm runs of this implementation")
+        globals()["M"] = args.tokens
+        globals()["METRIC"] = METRIC.replace("m=512", f"m={args.tokens}")
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.impl == "reference":
         run_reference(args)

@@ -233,9 +233,10 @@ LEXB_API int lexb_selftest_bounded_wait(lexb_gpu* gpu, uint32_t limit_us);
 /* In-kernel phase timers of the two-CTA GEMM (the counterpart of LEX_SYNC's per-call-site
  * attribution, crates/lex-rt/src/qwen_run.rs:2926-2960, one level down): with tracing enabled
  * for up to max_ctas blocks, each block of the next launch records 16 SM-clock values:
- * [0] start, [1] first K step ready, [2] all MMAs issued, [3] cycles the MMA thread waited for
- * x tiles, [4] for its own W tile, [5] for the partner's W tile, [6] accumulator complete,
- * [7] epilogue done ([1]-[5] only in the leader block of a pair); [8..10] and [12..14]: for the
+ * [0] start, [1] first K step ready, [2] all MMAs issued, [3] cycles the MMA warp waited for the
+ * inputs of a K step (x tiles and both CTAs' W tiles report to one barrier), [4] and [5] zero,
+ * [6] accumulator complete, [7] epilogue done ([1]-[5] and, as [11], the cycles spent issuing MMAs
+ * only in the leader block of a pair); [8..10] and [12..14]: for the
  * first and the last dequant thread, cycles in the decode loop, of which waiting for packed
  * weights, of which waiting for a free W stage; [15] the block's end and, in the partner block of a
  * pair, [11] its start, both in nanoseconds of the GPU's global timer.  With max_ctas >= twice the

@@ -74,16 +74,28 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
+// The same test with a suspend-time hint: the hardware may park the thread until the phase completes or
+// `hint_ns` nanoseconds pass, instead of returning at once.  A warp that waits this way does not poll: it
+// takes no issue slots and no shared-memory cycles from the warps that are working.
+__device__ __forceinline__ bool mbar_try_wait_parked(uint32_t bar, uint32_t parity, uint32_t hint_ns) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity), "r"(hint_ns)
+        : "memory");
+    return ok != 0;
+}
+constexpr uint32_t WAIT_PARK_NS = 4000;      // one parked attempt; the loop around it keeps the overall bound
 // Bounded wait.  `abort_flag` (shared memory) lets one role's failure end the others' waits early.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag) {
     if (mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
-    uint32_t spins = 0;
-    while (!mbar_try_wait(bar, parity)) {
-        if ((++spins & 0x3Fu) == 0) {
-            if (*abort_flag) return false;
-            if (clock64() - t0 > WAIT_LIMIT_CYCLES) return false;
-        }
+    while (!mbar_try_wait_parked(bar, parity, WAIT_PARK_NS)) {
+        if (*abort_flag) return false;
+        if (clock64() - t0 > WAIT_LIMIT_CYCLES) return false;
     }
     return true;
 }
@@ -328,29 +340,6 @@ __device__ __forceinline__ void mbar_arrive_expect_tx_cluster(uint32_t cluster_a
     asm volatile("mbarrier.arrive.expect_tx.shared::cluster.b64 _, [%0], %1;" ::"r"(cluster_addr),
                  "r"(bytes)
                  : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok)
-        : "r"(bar), "r"(parity)
-        : "memory");
-    return ok != 0;
-}
-__device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag) {
-    if (mbar_try_wait_cluster(bar, parity)) return true;
-    const long long t0 = clock64();
-    uint32_t spins = 0;
-    while (!mbar_try_wait_cluster(bar, parity)) {
-        if ((++spins & 0x3Fu) == 0) {
-            if (*abort_flag) return false;
-            if (clock64() - t0 > WAIT_LIMIT_CYCLES) return false;
-        }
-    }
-    return true;
 }
 // TMA tile load of a CTA pair: the data lands in this CTA's shared memory, the byte count is
 // reported to the barrier at `bar_cluster_addr`, which may live in the partner CTA.  No multicast.
