@@ -36,7 +36,10 @@ constexpr uint32_t PAIR_TOKENS = 512;                 // tokens per pair tile
 constexpr uint32_t PAIR_XBLK_ROWS = 128;              // tokens per TMA box (one CTA's half of a block)
 constexpr uint32_t PAIR_XBLK_BYTES = PAIR_XBLK_ROWS * 128u;                  // 16 KiB
 // a stage of the x ring holds this CTA's half of one token block (tiles of 256 tokens) or of two (512): 16 or 32 KiB
-__host__ __device__ constexpr uint32_t pair_x_stage_bytes(uint32_t tok_blocks) { return tok_blocks * PAIR_XBLK_BYTES; }
+// (`k_sub` K steps of 64 columns per stage: 1, or 2 with the W tiles in tensor memory)
+__host__ __device__ constexpr uint32_t pair_x_stage_bytes(uint32_t tok_blocks, uint32_t k_sub = 1) {
+    return tok_blocks * k_sub * PAIR_XBLK_BYTES;
+}
 constexpr uint32_t PAIR_TMEM_COLS = 512;
 constexpr uint32_t PAIR_DEQ_THREADS = 512;            // 16 warps in 4 groups: a group decodes one K step in four, a row per thread
 constexpr uint32_t PAIR_WARP_TMA = 16;
@@ -51,8 +54,10 @@ constexpr uint32_t PAIR_RAW_STAGES = 2;                // default depth of the r
 
 // x ring, W ring (their depths are independent: the decoded W tiles may run further ahead of the
 // MMA than the x tiles), packed-weight blocks, barriers, TMEM slot + abort flag, alignment slack
-__host__ __device__ constexpr uint32_t pair_smem_bytes(uint32_t tok_blocks, uint32_t sx, uint32_t sw, uint32_t sr = PAIR_RAW_STAGES) {
-    return sx * pair_x_stage_bytes(tok_blocks) + sw * GEMM_W_TILE_BYTES + sr * PAIR_RAW_BYTES +
+// (`w_in_tmem`: the decoded W tiles live in tensor memory and take no shared memory)
+__host__ __device__ constexpr uint32_t pair_smem_bytes(uint32_t tok_blocks, uint32_t sx, uint32_t sw, uint32_t sr = PAIR_RAW_STAGES,
+                                                      bool w_in_tmem = false, uint32_t k_sub = 1) {
+    return sx * pair_x_stage_bytes(tok_blocks, k_sub) + (w_in_tmem ? 0u : sw * GEMM_W_TILE_BYTES) + sr * PAIR_RAW_BYTES +
            (2u * sx + 3u * sw + 1u + 2u * sr) * 8u + 16u + 1024u;
 }
 
@@ -66,13 +71,24 @@ gemm_fp4_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const _
     uint8_t* const smem = smem_raw + (base - raw_addr);
 
     const uint32_t SX = a.stages, SW = a.w_stages, SR = a.raw_stages;
-    const uint32_t XSB = pair_x_stage_bytes(a.tok_blocks);
+    const uint32_t KS = a.k_sub;                                           // K steps per ring stage: 1, or 2 (W in TMEM only)
+    const uint32_t XSB = pair_x_stage_bytes(a.tok_blocks, KS);
     const uint32_t w_base = base + SX * XSB;                               // decoded W tiles
-    const uint32_t raw_base = w_base + SW * GEMM_W_TILE_BYTES;             // packed weight blocks
+    // Flag bit 2 (tiles of 256 tokens only): the decoded W tiles go to tensor memory - columns 256.. of this CTA's
+    // TMEM, 32 columns per K step (so at most 8 K steps in flight), the accumulator keeps columns 0-255 - and the
+    // MMAs take their A operand from there.  With 256 tokens a K step is bound by the shared-memory pipe; this takes the W
+    // tile's 16 KiB of stores and 16 KiB of operand reads per K step off it, and the W ring out of shared memory.
+    // One accumulator instead of two.  What then sets the pace is the MMA warp's own loop (a wait, a fence, a commit:
+    // ~600 cycles next to four decode warps on its scheduler, against 512 for the four MMAs of a K step), so in this
+    // mode a ring stage may hold two K steps (k_sub = 2): two decode groups fill one stage and that loop runs half as
+    // often.
+    const bool w_tmem = (a.flags & 4u) != 0u && a.tok_blocks == 1u;
+    const uint32_t raw_base = w_base + (w_tmem ? 0u : SW * GEMM_W_TILE_BYTES);     // packed weight blocks
     const uint32_t bars = raw_base + SR * PAIR_RAW_BYTES;
     // Depth of the barrier rings: no data ring may be deeper, and at least 4 - a decode group visits the `done`
-    // ring every fourth K step, and a parity wait is only right if the barrier cannot be two phases behind the
-    // one awaited: the group's previous wait (K step j - 4) guarantees phase (j - DN) only if DN >= 4.
+    // ring every fourth K step (every 4 / KS stage steps), and a parity wait is only right if the barrier cannot be
+    // two phases behind the one awaited: the group's previous wait (step j - 4 / KS) guarantees phase (j - DN) only
+    // if DN >= 4 / KS.
     const uint32_t DN = (SX > SW ? SX : SW) > 4u ? (SX > SW ? SX : SW) : 4u;
     auto full = [&](uint32_t j) { return bars + 8u * j; };                        // leader only: all inputs of K step j
     auto done = [&](uint32_t j) { return bars + 8u * (DN + j); };                 // both CTAs: K step j's MMAs complete
@@ -103,10 +119,10 @@ gemm_fp4_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const _
         *abort_flag = 0;
         for (uint32_t j = 0; j < DN; j++) {
             // one arrive.expect_tx per CTA, one arrival per warp of the leader's decode group, one from the partner's relay
-            mbar_init(full(j), 2u + PAIR_DEQ_THREADS / 128u + 1u);
+            mbar_init(full(j), 2u + KS * (PAIR_DEQ_THREADS / 128u) + 1u);
             mbar_init(done(j), 1);
         }
-        for (uint32_t s = 0; s < SW; s++) mbar_init(w_part(s), PAIR_DEQ_THREADS / 128u);
+        for (uint32_t s = 0; s < SW; s++) mbar_init(w_part(s), KS * (PAIR_DEQ_THREADS / 128u));
         for (uint32_t rs = 0; rs < SR; rs++) {
             mbar_init(raw_full(rs), 1);
             mbar_init(raw_empty(rs), PAIR_DEQ_THREADS / 32u);
@@ -137,6 +153,7 @@ gemm_fp4_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const _
     // each joins the stream's order before its first wait on a ring slot (a bounded wait must not run
     // against another launch's time) and, for the decode warps, before the epilogue.
     const bool early_w = (a.flags & 2u) != 0u;
+
     const bool weight_role = warp == PAIR_WARP_RAW || warp < PAIR_DEQ_THREADS / 32u;
     if (!(early_w && weight_role)) grid_dependency_wait();
 
@@ -144,9 +161,9 @@ gemm_fp4_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const _
         // ---------------------------------------------------------------- TMA producer (both CTAs)
         if (lane == 0) {
             RingPos px, pf, pe;              // x stage, barrier of this K step, barrier of the K step that held the stage
-            for (uint32_t kb = 0; kb < KB; kb++, px.advance(SX), pf.advance(DN)) {
+            for (uint32_t st = 0; st < KB / KS; st++, px.advance(SX), pf.advance(DN)) {
                 const uint32_t s = px.s;
-                if (kb >= SX) {
+                if (st >= SX) {
                     if (!mbar_wait(done(pe.s), pe.ph, abort_flag)) {
                         atomicOr(a.status, ST_WAIT_EMPTY_TMA);
                         *abort_flag = 1;
@@ -155,13 +172,17 @@ gemm_fp4_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const _
                     pe.advance(DN);
                 }
                 const uint32_t lead_bar = map_to_cta(full(pf.s), 0);
-                mbar_arrive_expect_tx_cluster(lead_bar, TB * a.x_tx_bytes);
+                mbar_arrive_expect_tx_cluster(lead_bar, KS * TB * a.x_tx_bytes);
                 const uint32_t dst = base + s * XSB;
+                const uint32_t kb = kb0 + st * KS;
                 // token block tb covers tokens m0 + 256 tb .. +255; this CTA holds 128 of them
-                tma_load_2d_pair(dst, &tmap_x, (int)((kb0 + kb) * GEMM_BK), (int)(m0 + rank * PAIR_XBLK_ROWS), lead_bar);
+                tma_load_2d_pair(dst, &tmap_x, (int)(kb * GEMM_BK), (int)(m0 + rank * PAIR_XBLK_ROWS), lead_bar);
                 if (TB > 1u)
-                    tma_load_2d_pair(dst + PAIR_XBLK_BYTES, &tmap_x, (int)((kb0 + kb) * GEMM_BK),
+                    tma_load_2d_pair(dst + PAIR_XBLK_BYTES, &tmap_x, (int)(kb * GEMM_BK),
                                      (int)(m0 + 256u + rank * PAIR_XBLK_ROWS), lead_bar);
+                if (KS > 1u)      // the stage's second K step (one token block)
+                    tma_load_2d_pair(dst + PAIR_XBLK_BYTES, &tmap_x, (int)((kb + 1u) * GEMM_BK),
+                                     (int)(m0 + rank * PAIR_XBLK_ROWS), lead_bar);
             }
             if (*abort_flag) {
                 // The byte counts of this CTA's copies are kept by the leader's barriers, which
@@ -203,7 +224,7 @@ gemm_fp4_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const _
             // One cluster-scope arrive per K step from this otherwise idle thread, so that the
             // dequant threads only ever touch barriers of their own CTA.
             RingPos pw, pf;
-            for (uint32_t kb = 0; kb < KB; kb++, pw.advance(SW), pf.advance(DN)) {
+            for (uint32_t st = 0; st < KB / KS; st++, pw.advance(SW), pf.advance(DN)) {
                 if (!mbar_wait(w_part(pw.s), pw.ph, abort_flag)) {
                     atomicOr(a.status, ST_WAIT_W_FULL);
                     *abort_flag = 1;
@@ -222,7 +243,7 @@ gemm_fp4_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const _
             bool ok = true;
             long long wait_full = 0, t_first = 0, t_issue = 0;
             RingPos px, pw, pf;
-            for (uint32_t kb = 0; kb < KB; kb++, px.advance(SX), pw.advance(SW), pf.advance(DN)) {
+            for (uint32_t kb = 0; kb < KB; kb += KS, px.advance(SX), pw.advance(SW), pf.advance(DN)) {
                 const uint32_t s = px.s, sw = pw.s;
                 long long tw0 = 0;
                 if (TRACE) tw0 = clock64();
@@ -264,6 +285,16 @@ gemm_fp4_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const _
                             umma2_acc(d0, aw + 2u * kk, b0 + 2u * kk, idesc);
                             umma2_acc(d1, aw + 2u * kk, b1 + 2u * kk, idesc);
                         }
+                    }
+                } else if (w_tmem) {
+                    const uint32_t at = tmem_base + 256u + sw * (32u * KS);
+                    umma2_ts_flag(d0, at, b0, idesc, kb != 0u);
+#pragma unroll
+                    for (uint32_t kk = 1; kk < GEMM_BK / 16; kk++) umma2_ts_flag(d0, at + 8u * kk, b0 + 2u * kk, idesc, 1u);
+                    if (KS > 1u) {            // the stage's second K step: the next 32 columns, the next x block
+#pragma unroll
+                        for (uint32_t kk = 0; kk < GEMM_BK / 16; kk++)
+                            umma2_ts_flag(d0, at + 32u + 8u * kk, b1 + 2u * kk, idesc, 1u);
                     }
                 } else {
                     // one token block: even and odd K steps go to two accumulators, which halves the
@@ -312,10 +343,12 @@ gemm_fp4_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const _
         long long dq_wait_raw = 0, dq_wait_empty = 0, dq_t0 = 0;
         if (TRACE) dq_t0 = clock64();
         RingPos pr, pw, pf, pe;          // packed block; W stage and barrier of this K step; barrier of the stage's last user
-        pw.seek(q, SW);
-        pf.seek(q, DN);
+        pw.seek(q / KS, SW);
+        pf.seek(q / KS, DN);
+        const uint32_t hop = 4u / KS;                                // stage steps between this group's K steps
+        const uint32_t sub_col = (q % KS) * 32u;                     // this group's K step within a two-step stage
         bool joined = !early_w, pe_set = false;
-        for (uint32_t kb = q; kb < KB; kb += 4u, pr.advance(SR), pw.advance_by(4u, SW), pf.advance_by(4u, DN)) {
+        for (uint32_t kb = q; kb < KB; kb += 4u, pr.advance(SR), pw.advance_by(hop, SW), pf.advance_by(hop, DN)) {
             const uint32_t rs = pr.s, rph = pr.ph;
             long long tq0 = 0;
             if (TRACE) tq0 = clock64();
@@ -341,13 +374,14 @@ gemm_fp4_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const _
             decode_group16(make_uint2(c1.z, c1.w), sc >> 24, g, o[6], o[7]);
             long long tq1 = 0;
             if (TRACE) tq1 = clock64();
-            if (kb >= SW) {
+            const uint32_t st = kb / KS;                                 // KS is 1 or 2
+            if (st >= SW) {
                 if (!joined) {                                           // first wait on a W stage: join the stream's order
                     grid_dependency_wait();
                     joined = true;
                 }
                 if (!pe_set) {
-                    pe.seek(kb - SW, DN);
+                    pe.seek(st - SW, DN);
                     pe_set = true;
                 }
                 if (!__all_sync(0xFFFFFFFFu, mbar_wait(done(pe.s), pe.ph, abort_flag))) {
@@ -356,13 +390,28 @@ gemm_fp4_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const _
                     ok = false;
                     break;
                 }
-                pe.advance_by(4u, DN);
+                pe.advance_by(hop, DN);
             }
             if (TRACE) dq_wait_empty += clock64() - tq1;
-            uint8_t* const wt = smem + pw.s * GEMM_W_TILE_BYTES + w_off;
+            if (w_tmem) {
+                // this lane's row of the tile: 64 f16 in K order = 32 columns of its TMEM lane
+                uint32_t v[32];
 #pragma unroll
-            for (uint32_t c = 0; c < 8; c++) *reinterpret_cast<uint4*>(wt + ((c ^ sw_xor) << 4)) = o[c];
-            fence_proxy_async_smem();       // generic-proxy stores -> visible to the MMA's reads
+                for (uint32_t c = 0; c < 8; c++) {
+                    v[4u * c + 0u] = o[c].x;
+                    v[4u * c + 1u] = o[c].y;
+                    v[4u * c + 2u] = o[c].z;
+                    v[4u * c + 3u] = o[c].w;
+                }
+                tmem_st_32x32b_x32(tmem_base + ((32u * (warp & 3u)) << 16) + 256u + pw.s * (32u * KS) + sub_col, v);
+                tmem_st_wait();
+                tc_fence_before_sync();
+            } else {
+                uint8_t* const wt = smem + pw.s * GEMM_W_TILE_BYTES + w_off;
+#pragma unroll
+                for (uint32_t c = 0; c < 8; c++) *reinterpret_cast<uint4*>(wt + ((c ^ sw_xor) << 4)) = o[c];
+                fence_proxy_async_smem();       // generic-proxy stores -> visible to the MMA's reads
+            }
             // One arrival per warp: hundreds of arrivals on one barrier serialise in shared memory.  The tile is
             // reported to the K step's barrier (leader) or to the relay's (partner).
             __syncwarp();
@@ -398,7 +447,7 @@ gemm_fp4_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const _
             const bool to_partial = a.k_splits > 1u;
             float* const out = to_partial ? a.partial + (size_t)split * a.m * a.n : a.y;
             const float* const res = to_partial ? nullptr : a.r;
-            const bool two_acc = TB == 1u && KB > 1u;
+            const bool two_acc = TB == 1u && KB > 1u && !w_tmem;
             for (uint32_t cc = slice; cc < TB * 16u; cc += 4u) {
                 const uint32_t t0 = m0 + cc * 16u;
                 if (t0 >= a.m) break;                        // warp-uniform

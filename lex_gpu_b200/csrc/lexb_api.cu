@@ -144,6 +144,7 @@ struct lexb_pipeline {
     // tcgen05 GEMM
     uint32_t tm, stages, w_stages, tmem_cols, m_tiles, n_acc, flags;
     uint32_t raw_stages = lexb::PAIR_RAW_STAGES;
+    uint32_t k_sub = 1;         // two-CTA kernel: K steps per ring stage
     uint32_t k_splits = 1, kb_per_split = 0, tok_blocks = 2;
     uint32_t ws_pitch = 0;      // block-scaled kernel: bytes per row of one scale load
     bool x_f32 = false;         // ... with f32 activations
@@ -418,7 +419,7 @@ int launch_one(lexb_gpu* g, const lexb_pipeline* p, const lexb_buffer* x, const 
         // can be read side by side (the gap between them on the GPU's global timer)
         if (a.trace && 2u * p->grid <= g->trace_ctas) a.trace += 16ull * p->grid * (g->trace_toggle++ & 1u);
         a.m = p->m; a.n = p->n; a.k = p->k;
-        a.tm = p->tm; a.stages = p->stages; a.w_stages = p->w_stages; a.raw_stages = p->raw_stages;
+        a.tm = p->tm; a.stages = p->stages; a.w_stages = p->w_stages; a.raw_stages = p->raw_stages; a.k_sub = p->k_sub;
         // bit 0: operand-collector hint; bit 1 (two-CTA kernel): the packed weights are constant - declared, or
         // proven from the step list - so their copy and decode may run ahead of the stream's order
         a.flags = p->flags | ((p->w_const || (order.early_weights && !p->w_volatile)) ? 2u : 0u);
@@ -1182,8 +1183,8 @@ int lexb_gemm_fp4_plan(lexb_gpu* g, uint32_t m, uint32_t n, uint32_t k, int resi
         // launch sums.  Tiles of 256 tokens when m > 256: twice the tiles; every weight is decoded twice, but a K
         // step's MMAs take half as long, a tile's partial product is half as large and fewer splits are needed.
         // Every (tile, splits) pair is priced with figures fitted to launches timed on a B200 (us; rms error 6 %):
-        // per wave of tiles 12.3 / 8.0 for a block's start and its store of a 512 / 256-token tile and 0.595 / 0.385
-        // per K step; for the reduction launch 0.9 plus its bytes at 3.76 TB/s; minus 3.4 overall.  The cheapest
+        // per wave of tiles 13.0 / 7.6 for a block's start and its store of a 512 / 256-token tile and 0.593 / 0.367
+        // per K step; for the reduction launch 1.05 plus its bytes at 3.93 TB/s; minus 3.85 overall.  The cheapest
         // wins; a smaller tile or a further split must win by 2 %.
         const uint32_t sm_pairs = static_cast<uint32_t>(g->prop.multiProcessorCount) / 2u;
         const uint32_t raw_blocks = k / lexb::PAIR_RAW_K;
@@ -1193,8 +1194,8 @@ int lexb_gemm_fp4_plan(lexb_gpu* g, uint32_t m, uint32_t n, uint32_t k, int resi
                 const uint32_t mt = (m + tb * 256u - 1u) / (tb * 256u);
                 const uint32_t rbs = (raw_blocks + c - 1u) / c, eff = (raw_blocks + rbs - 1u) / rbs;
                 const double waves = static_cast<double>((mt * n_pairs * eff + sm_pairs - 1u) / sm_pairs);
-                double us = -3.4 + waves * (rbs * 4.0 * (tb == 2u ? 0.595 : 0.385) + (tb == 2u ? 12.3 : 8.0));
-                if (eff > 1u) us += 0.9 + static_cast<double>(eff) * m * n * 4.0 / 3.76e6;
+                double us = -3.85 + waves * (rbs * 4.0 * (tb == 2u ? 0.593 : 0.367) + (tb == 2u ? 13.0 : 7.6));
+                if (eff > 1u) us += 1.05 + static_cast<double>(eff) * m * n * 4.0 / 3.93e6;
                 *eff_out = eff;
                 return us;
             };
@@ -1222,16 +1223,29 @@ int lexb_gemm_fp4_plan(lexb_gpu* g, uint32_t m, uint32_t n, uint32_t k, int resi
             }
         }
         if (splits < 1u || splits > raw_blocks) return bail(fail(LEXB_ERR_ARG, "k_splits = %u outside [1, %u]", splits, raw_blocks));
-        // Ring depths (212 KiB with the two packed-weight blocks either way).  Tiles of 512 tokens: x ring of 4
-        // stages of 32 KiB, W ring of 3; their K step is bound by the MMAs.  Tiles of 256 tokens: a K step's MMAs
-        // take half as long and the hand-offs around a ring slot (commit -> free -> refill -> full, through the
-        // partner CTA) set the pace, so the x stages, half the size, and the W stages are both made deeper: 6 and 5.
-        const uint32_t stages = s.stages ? s.stages : (p->tok_blocks == 2u ? 4u : 6u);
-        const uint32_t w_stages = s.w_stages ? s.w_stages : (p->tok_blocks == 2u ? 3u : 5u);
-        if (stages < 2 || w_stages < 2 || raw_stages < 2 || lexb::pair_smem_bytes(p->tok_blocks, stages, w_stages, raw_stages) > g->smem_optin)
+        // Ring depths.  Tiles of 512 tokens: x ring of 4 stages of 32 KiB, W ring of 3 of 16 KiB, two packed-weight
+        // blocks: 212 KiB; their K step is bound by the MMAs.  Tiles of 256 tokens: a K step's MMAs take half as
+        // long and the shared-memory pipe sets the pace, so the decoded W tiles go to tensor memory (256 of its 512
+        // columns are free with one accumulator: 8 stages of 32 columns) and the MMAs read them from there; the x
+        // ring, 16 KiB a stage, gets 8 stages: 164 KiB.  A caller who asks for more than 8 W stages, or
+        // LEXB_WTMEM=0, gets the W ring in shared memory (x 6, W 5 by default).
+        // In that mode a ring stage holds two K steps (x 32 KiB, W 64 columns of TMEM, so at most 4 W stages) and
+        // the MMA warp waits and commits once per two K steps; depths the caller gives that do not fit that way are
+        // taken as stages of one K step.
+        const bool w_tmem = p->tok_blocks == 1u && s.w_stages <= 8u && env_u32("LEXB_WTMEM", 1u) != 0u;
+        uint32_t k_sub = (w_tmem && env_u32("LEXB_KSUB", 2u) == 2u) ? 2u : 1u;
+        if (k_sub == 2u && (s.w_stages > 4u ||
+                            lexb::pair_smem_bytes(1u, s.stages ? s.stages : 4u, s.w_stages ? s.w_stages : 4u, raw_stages, true, 2u) > g->smem_optin))
+            k_sub = 1u;
+        const uint32_t stages = s.stages ? s.stages : (p->tok_blocks == 2u ? 4u : k_sub == 2u ? 4u : w_tmem ? 8u : 6u);
+        const uint32_t w_stages = s.w_stages ? s.w_stages : (p->tok_blocks == 2u ? 3u : k_sub == 2u ? 4u : w_tmem ? 8u : 5u);
+        const uint32_t need = lexb::pair_smem_bytes(p->tok_blocks, stages, w_stages, raw_stages, w_tmem, k_sub);
+        if (stages < 2 || w_stages < 2 || raw_stages < 2 || need > g->smem_optin)
             return bail(fail(LEXB_ERR_ARG, "stages = %u with w_stages = %u and %u packed-weight blocks need %u bytes of shared memory (limit %zu)",
-                             stages, w_stages, raw_stages, lexb::pair_smem_bytes(p->tok_blocks, stages, w_stages, raw_stages), g->smem_optin));
+                             stages, w_stages, raw_stages, need, g->smem_optin));
+        p->k_sub = k_sub;
         p->stages = stages; p->w_stages = w_stages;
+        if (w_tmem) p->flags |= 4u;
         const uint32_t tiles_final = p->m_tiles * n_pairs;
         const uint32_t rb_per_split = (raw_blocks + splits - 1u) / splits;
         splits = (raw_blocks + rb_per_split - 1u) / rb_per_split;          // no empty split
@@ -1243,7 +1257,7 @@ int lexb_gemm_fp4_plan(lexb_gpu* g, uint32_t m, uint32_t n, uint32_t k, int resi
         }
         p->grid = 2u * tiles_final * splits;
         p->threads = lexb::PAIR_THREADS;
-        p->smem = lexb::pair_smem_bytes(p->tok_blocks, stages, w_stages, raw_stages);
+        p->smem = need;
         snprintf(p->entry, sizeof p->entry, "%s_%u_%u_%u_%u_%u_%u", stem, m, n, k, p->tm, 2u * lexb::GEMM_TN, lexb::GEMM_BK);
     } else {
         if (n % lexb::MV_ROWS) return bail(fail(LEXB_ERR_SHAPE, "gemm_fp4 (matvec): %u rows per block do not divide n = %u", lexb::MV_ROWS, n));
@@ -1698,7 +1712,8 @@ int lexb_gemm_fp4_splitk_static(lexb_gpu* g, uint32_t m, uint32_t n, uint32_t k,
     a.status = g->d_status;
     a.trace = nullptr;
     a.m = m; a.n = n; a.k = k;
-    a.tm = p.tm; a.stages = p.stages; a.w_stages = p.w_stages; a.raw_stages = p.raw_stages; a.flags = 0;
+    a.tm = p.tm; a.stages = p.stages; a.w_stages = p.w_stages; a.raw_stages = p.raw_stages; a.k_sub = 1;
+    a.flags = p.tok_blocks == 1u ? 4u : 0u;      // tiles of 256 tokens: W tiles in tensor memory, as the planned pipeline has them
     a.k_splits = splits; a.kb_per_split = p.kb_per_split; a.tok_blocks = p.tok_blocks;
     a.partial = g->static_scratch;          // every element of the partials is written before it is read: nothing to clear
     a.tmem_cols = p.tmem_cols; a.m_tiles = p.m_tiles; a.n_acc = 1;

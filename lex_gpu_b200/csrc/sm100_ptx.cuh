@@ -250,6 +250,26 @@ __device__ __forceinline__ void umma2_acc_lastuse(uint32_t d_tmem, uint32_t a_lo
     LEXB_UMMA_ASM("2", ".collector::a::lastuse", "setp.eq.b32 p, 0, 0;\n\t");
 }
 
+// A operand from tensor memory (rows = lanes, two f16 of K per 32-bit column; written by tcgen05.st), B from shared
+// memory: nothing of the A tile crosses the shared-memory pipe.  `a_tmem` is the tile's address at lane 0; stepping
+// K by 16 elements is +8 columns.
+__device__ __forceinline__ void umma2_ts_flag(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\t.reg .b64 db;\n\tsetp.ne.b32 p, %5, 0;\n\t"
+                 "mov.b64 db, {%2, %4};\n\t"
+                 "tcgen05.mma.cta_group::2.kind::f16 [%0], [%1], db, %3, p;\n\t}"
+                 ::"r"(d_tmem), "r"(a_tmem), "r"(b_lo), "r"(idesc), "r"(UMMA_DESC_HI_SW128), "r"(accumulate)
+                 : "memory");
+}
+// Each lane of the warp writes 32 consecutive 32-bit columns of its own TMEM lane (the warp's lane quarter).
+__device__ __forceinline__ void tmem_st_32x32b_x32(uint32_t taddr, const uint32_t (&v)[32]) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+                 ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]), "r"(v[16]), "r"(v[17]), "r"(v[18]), "r"(v[19]), "r"(v[20]), "r"(v[21]), "r"(v[22]), "r"(v[23]), "r"(v[24]), "r"(v[25]), "r"(v[26]), "r"(v[27]), "r"(v[28]), "r"(v[29]), "r"(v[30]), "r"(v[31])
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() {
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+
 // Instruction descriptor, kind::f16: f16 x f16 -> f32, both operands K-major, M x N tile.
 __host__ __device__ constexpr uint32_t umma_idesc_f16_f32(uint32_t M, uint32_t N) {
     return (1u << 4)              // D format f32

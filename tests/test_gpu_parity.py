@@ -174,13 +174,17 @@ def test_gemm_two_cta_kernel(gpu, m, n, k):
     check(L.gemm_fp4(gpu, x, wq, ws, wg, kernel=2), want)
 
 
-def test_gemm_two_cta_kernel_residual_and_stages(gpu):
+@pytest.mark.parametrize("tm", [256, 512])
+def test_gemm_two_cta_kernel_residual_and_stages(gpu, tm):
+    """Ring depths around the defaults, for both tile sizes: (2, 2) makes the barrier rings (at least 4 deep) deeper
+    than both data rings, (3, 5) and (6, 5) make the W ring deeper than the four decode groups, (4, 2) has fewer W
+    stages than groups.  28 K steps: every ring wraps several times."""
     m, n, k = 640, 512, 1792
     x, wq, ws, wg = inputs.make_case(m, n, k, seed_base=77)
     r = inputs.make_residual(m, n, seed_base=77)
     want = O.gemm_fp4(x, wq, ws, wg, r=r)
-    for stages, w_stages in ((2, 2), (3, 5), (4, 2), (0, 0)):
-        check(L.gemm_fp4(gpu, x, wq, ws, wg, r=r, kernel=3, stages=stages, w_stages=w_stages), want)
+    for stages, w_stages in ((2, 2), (3, 5), (4, 2), (2, 6), (6, 5) if tm == 256 else (3, 4), (0, 0)):
+        check(L.gemm_fp4(gpu, x, wq, ws, wg, r=r, kernel=3, tm=tm, stages=stages, w_stages=w_stages), want)
 
 
 @pytest.mark.parametrize("m,n,k,splits", [(512, 256, 2048, 2), (600, 384, 4096, 4), (512, 384, 512, 1),

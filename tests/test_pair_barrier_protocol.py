@@ -2,7 +2,7 @@
 
 One cluster: two x producers, two packed-weight producers, 2 x 16 decode warps in four groups (a group owns every
 fourth K step), the partner's relay and the MMA warp, with parity waits on barriers that count arrivals exactly as
-the kernel's do.  The model checks what the kernel relies on: no parity wait passes before the phase it stands for
+the kernel's do (`KS` K steps of 64 columns per ring stage: 1, or 2 when the W tiles live in tensor memory).  The model checks what the kernel relies on: no parity wait passes before the phase it stands for
 has completed, no W stage is overwritten while its K step is still to be multiplied, and the MMA warp only starts a
 K step whose tiles are complete.  It also shows why the barrier rings are at least 4 deep: with a shallower ring a
 decode group, which visits the `done` ring every fourth K step, can find the barrier two phases behind the one it
@@ -13,7 +13,7 @@ import pytest
 import random
 
 
-def run(SX, SW, SR, KB, seed, DNmin):
+def run(SX, SW, SR, KB, seed, DNmin, KS=1):
     rnd = random.Random(seed)
     DN = max(SX, SW, DNmin)
     class Bar:
@@ -23,9 +23,10 @@ def run(SX, SW, SR, KB, seed, DNmin):
             assert s.pending >= 0
             if s.pending == 0: s.pending = s.count; s.done += 1
         def test(s, parity): return (s.done & 1) != parity
-    full=[Bar(2+4+1,f"full{j}") for j in range(DN)]
+    NST = KB // KS                       # stage steps: KS K steps of 64 columns each
+    full=[Bar(2+4*KS+1,f"full{j}") for j in range(DN)]
     done=[[Bar(1,f"done{c}_{j}") for j in range(DN)] for c in range(2)]
-    wpart=[Bar(4,f"wpart{j}") for j in range(SW)]
+    wpart=[Bar(4*KS,f"wpart{j}") for j in range(SW)]
     rawf=[[Bar(1,"rawf") for _ in range(SR)] for c in range(2)]
     rawe=[[Bar(16,"rawe") for _ in range(SR)] for c in range(2)]
     mma_done=[-1]      # highest K step whose MMAs completed
@@ -37,7 +38,7 @@ def run(SX, SW, SR, KB, seed, DNmin):
         while not bar.test(parity): yield
         if not truth(): errors.append(f"false pass: {what}")
     def xprod(c):
-        for kb in range(KB):
+        for kb in range(NST):
             if kb >= SX:
                 j=kb-SX
                 yield from wait(done[c][j%DN], (j//DN)&1, lambda j=j: mma_done[0]>=j, f"xprod{c} done({j})")
@@ -60,28 +61,29 @@ def run(SX, SW, SR, KB, seed, DNmin):
             yield
             rawe[c][rb%SR].arrive()
             for _ in range(rnd.randint(0,6)): yield
-            if kb >= SW:
-                j=kb-SW
-                yield from wait(done[c][j%DN], (j//DN)&1, lambda j=j: mma_done[0]>=j, f"dec{c}.{w} done({j}) for kb={kb}")
+            st = kb // KS
+            if st >= SW:
+                j=st-SW
+                yield from wait(done[c][j%DN], (j//DN)&1, lambda j=j: mma_done[0]>=j, f"dec{c}.{w} done({j}) for step={st}")
             yield
             # store
-            if wslot[c][kb%SW] is not None and wslot[c][kb%SW][0] > mma_done[0] and wslot[c][kb%SW][0] != kb:
-                errors.append(f"overwrite of live W slot by kb={kb} (holds {wslot[c][kb%SW]})")
-            cur = wslot[c][kb%SW]
-            wslot[c][kb%SW] = (kb, (cur[1]+1 if cur and cur[0]==kb else 1))
+            if wslot[c][st%SW] is not None and wslot[c][st%SW][0] > mma_done[0] and wslot[c][st%SW][0] != st:
+                errors.append(f"overwrite of live W slot by step={st} (holds {wslot[c][st%SW]})")
+            cur = wslot[c][st%SW]
+            wslot[c][st%SW] = (st, (cur[1]+1 if cur and cur[0]==st else 1))
             yield
             if c == 0:
-                full[kb%DN].arrive()
+                full[st%DN].arrive()
             else:
-                wpart[kb%SW].arrive()
+                wpart[st%SW].arrive()
     def relay():
-        for kb in range(KB):
-            yield from wait(wpart[kb%SW], (kb//SW)&1, lambda kb=kb: wslot[1][kb%SW]==(kb,4), f"relay kb={kb}")
+        for kb in range(NST):
+            yield from wait(wpart[kb%SW], (kb//SW)&1, lambda kb=kb: wslot[1][kb%SW]==(kb,4*KS), f"relay kb={kb}")
             yield
             full[kb%DN].arrive()
     def mma():
-        for kb in range(KB):
-            yield from wait(full[kb%DN], (kb//DN)&1, lambda kb=kb: wslot[0][kb%SW]==(kb,4) and wslot[1][kb%SW]==(kb,4) and xslot[0][kb%SX]==kb and xslot[1][kb%SX]==kb, f"mma kb={kb}")
+        for kb in range(NST):
+            yield from wait(full[kb%DN], (kb//DN)&1, lambda kb=kb: wslot[0][kb%SW]==(kb,4*KS) and wslot[1][kb%SW]==(kb,4*KS) and xslot[0][kb%SX]==kb and xslot[1][kb%SX]==kb, f"mma kb={kb}")
             for _ in range(rnd.randint(0,3)): yield
             mma_done[0]=kb
             done[0][kb%DN].arrive(); done[1][kb%DN].arrive()
@@ -99,10 +101,17 @@ def run(SX, SW, SR, KB, seed, DNmin):
     return errors
 
 
-@pytest.mark.parametrize("sx,sw", [(2, 2), (4, 2), (3, 5), (4, 3), (6, 5), (2, 7), (3, 3), (2, 3)])
+@pytest.mark.parametrize("sx,sw", [(2, 2), (4, 2), (3, 5), (4, 3), (6, 5), (2, 7), (3, 3), (2, 3), (8, 8)])
 def test_protocol_is_safe_with_barrier_rings_of_at_least_four(sx, sw):
     for seed in range(6):
         assert run(sx, sw, 2, 24, seed, 4) == []
+
+
+@pytest.mark.parametrize("sx,sw", [(4, 4), (2, 2), (4, 2), (2, 3), (3, 3)])
+def test_protocol_is_safe_with_two_k_steps_per_stage(sx, sw):
+    """W tiles in tensor memory: a ring stage holds two K steps, two decode groups fill one stage."""
+    for seed in range(6):
+        assert run(sx, sw, 2, 24, seed, 4, KS=2) == []
 
 
 def test_a_shallower_barrier_ring_lets_a_parity_wait_pass_early():
