@@ -565,8 +565,17 @@ __global__ void splitk_reduce_kernel(const float* __restrict__ partial, uint32_t
     grid_dependency_wait();
     const size_t n4 = elems / 4;
     for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n4; i += (size_t)gridDim.x * blockDim.x) {
-        float4 acc = reinterpret_cast<const float4*>(partial)[i];
-        for (uint32_t s = 1; s < splits; s++) {
+        // the first eight splits' loads are issued together (one trip to L2 instead of one per split); the sum
+        // keeps the order of the splits
+        float4 v[8];
+#pragma unroll
+        for (uint32_t s = 0; s < 8u; s++)
+            if (s < splits) v[s] = reinterpret_cast<const float4*>(partial + (size_t)s * elems)[i];
+        float4 acc = v[0];
+#pragma unroll
+        for (uint32_t s = 1; s < 8u; s++)
+            if (s < splits) { acc.x += v[s].x; acc.y += v[s].y; acc.z += v[s].z; acc.w += v[s].w; }
+        for (uint32_t s = 8u; s < splits; s++) {
             const float4 p = reinterpret_cast<const float4*>(partial + (size_t)s * elems)[i];
             acc.x += p.x; acc.y += p.y; acc.z += p.z; acc.w += p.w;
         }
