@@ -47,6 +47,7 @@ struct GemmArgs {
     uint32_t w_stages;    // two-CTA kernel: depth of the ring of decoded W tiles
     uint32_t raw_stages;  // two-CTA kernel: depth of the ring of packed-weight blocks (256 K columns each)
     uint32_t k_sub;       // two-CTA kernel: K steps of 64 columns per ring stage (1; 2 only with the W tiles in TMEM)
+    uint32_t x_rows;      // two-CTA kernel: tokens each CTA holds of a token block (128; 64 / 32 with tiles of 128 / 64 tokens)
     uint32_t tmem_cols;   // power of two >= max(32, n_acc * tm)
     uint32_t n_acc;       // 1 or 2 accumulators; with 2, even and odd K steps alternate
     uint32_t m_tiles;     // ceil(m / tm)

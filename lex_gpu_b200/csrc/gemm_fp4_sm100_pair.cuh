@@ -37,9 +37,12 @@ constexpr uint32_t PAIR_XBLK_ROWS = 128;              // tokens per TMA box (one
 constexpr uint32_t PAIR_XBLK_BYTES = PAIR_XBLK_ROWS * 128u;                  // 16 KiB
 // a stage of the x ring holds this CTA's half of one token block (tiles of 256 tokens) or of two (512): 16 or 32 KiB
 // (`k_sub` K steps of 64 columns per stage: 1, or 2 with the W tiles in tensor memory)
-__host__ __device__ constexpr uint32_t pair_x_stage_bytes(uint32_t tok_blocks, uint32_t k_sub = 1) {
-    return tok_blocks * k_sub * PAIR_XBLK_BYTES;
+// (`x_rows`: tokens each CTA holds of a token block - 128, or 64 / 32 with tiles of 128 / 64 tokens)
+__host__ __device__ constexpr uint32_t pair_x_stage_bytes(uint32_t tok_blocks, uint32_t k_sub = 1, uint32_t x_rows = PAIR_XBLK_ROWS) {
+    return tok_blocks * k_sub * x_rows * 128u;
 }
+// The epilogue stages its chunks in the first 64 KiB of the rings (idle by then); the barriers sit behind.
+constexpr uint32_t PAIR_STAGING_BYTES = 65536;
 constexpr uint32_t PAIR_TMEM_COLS = 512;
 constexpr uint32_t PAIR_DEQ_THREADS = 512;            // 16 warps in 4 groups: a group decodes one K step in four, a row per thread
 constexpr uint32_t PAIR_WARP_TMA = 16;
@@ -56,8 +59,9 @@ constexpr uint32_t PAIR_RAW_STAGES = 2;                // default depth of the r
 // MMA than the x tiles), packed-weight blocks, barriers, TMEM slot + abort flag, alignment slack
 // (`w_in_tmem`: the decoded W tiles live in tensor memory and take no shared memory)
 __host__ __device__ constexpr uint32_t pair_smem_bytes(uint32_t tok_blocks, uint32_t sx, uint32_t sw, uint32_t sr = PAIR_RAW_STAGES,
-                                                      bool w_in_tmem = false, uint32_t k_sub = 1) {
-    return sx * pair_x_stage_bytes(tok_blocks, k_sub) + (w_in_tmem ? 0u : sw * GEMM_W_TILE_BYTES) + sr * PAIR_RAW_BYTES +
+                                                      bool w_in_tmem = false, uint32_t k_sub = 1, uint32_t x_rows = PAIR_XBLK_ROWS) {
+    const uint32_t rings = sx * pair_x_stage_bytes(tok_blocks, k_sub, x_rows) + (w_in_tmem ? 0u : sw * GEMM_W_TILE_BYTES) + sr * PAIR_RAW_BYTES;
+    return (rings > PAIR_STAGING_BYTES ? rings : PAIR_STAGING_BYTES) +
            (2u * sx + 3u * sw + 1u + 2u * sr) * 8u + 16u + 1024u;
 }
 
@@ -72,7 +76,9 @@ gemm_fp4_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const _
 
     const uint32_t SX = a.stages, SW = a.w_stages, SR = a.raw_stages;
     const uint32_t KS = a.k_sub;                                           // K steps per ring stage: 1, or 2 (W in TMEM only)
-    const uint32_t XSB = pair_x_stage_bytes(a.tok_blocks, KS);
+    const uint32_t XR = a.x_rows;                                          // tokens this CTA holds of a token block
+    const uint32_t XB = XR * 128u;                                         // bytes of one x box: XR tokens x 64 K columns
+    const uint32_t XSB = pair_x_stage_bytes(a.tok_blocks, KS, XR);
     const uint32_t w_base = base + SX * XSB;                               // decoded W tiles
     // Flag bit 2 (tiles of 256 tokens only): the decoded W tiles go to tensor memory - columns 256.. of this CTA's
     // TMEM, 32 columns per K step (so at most 8 K steps in flight), the accumulator keeps columns 0-255 - and the
@@ -84,7 +90,8 @@ gemm_fp4_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const _
     // often.
     const bool w_tmem = (a.flags & 4u) != 0u && a.tok_blocks == 1u;
     const uint32_t raw_base = w_base + (w_tmem ? 0u : SW * GEMM_W_TILE_BYTES);     // packed weight blocks
-    const uint32_t bars = raw_base + SR * PAIR_RAW_BYTES;
+    const uint32_t rings_end = raw_base + SR * PAIR_RAW_BYTES;
+    const uint32_t bars = rings_end > base + PAIR_STAGING_BYTES ? rings_end : base + PAIR_STAGING_BYTES;
     // Depth of the barrier rings: no data ring may be deeper, and at least 4 - a decode group visits the `done`
     // ring every fourth K step (every 4 / KS stage steps), and a parity wait is only right if the barrier cannot be
     // two phases behind the one awaited: the group's previous wait (step j - 4 / KS) guarantees phase (j - DN) only
@@ -106,7 +113,7 @@ gemm_fp4_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const _
     const uint32_t split = pair % a.k_splits, tile = pair / a.k_splits;
     const uint32_t m_tile = tile % a.m_tiles, n_pair = tile / a.m_tiles;
     const uint32_t TB = a.tok_blocks;                              // 1 or 2 blocks of 256 tokens per tile
-    const uint32_t m0 = m_tile * TB * 256u;
+    const uint32_t m0 = m_tile * TB * 2u * XR;                     // TB = 2 only with XR = 128
     const uint32_t n0 = n_pair * 2u * GEMM_TN + rank * GEMM_TN;     // may be == n in the last pair: nothing to store
     const uint32_t kb0 = split * a.kb_per_split;                    // first K step of this split (a multiple of 4)
     const uint32_t kb_all = a.k / GEMM_BK;
@@ -176,13 +183,11 @@ gemm_fp4_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const _
                 const uint32_t dst = base + s * XSB;
                 const uint32_t kb = kb0 + st * KS;
                 // token block tb covers tokens m0 + 256 tb .. +255; this CTA holds 128 of them
-                tma_load_2d_pair(dst, &tmap_x, (int)(kb * GEMM_BK), (int)(m0 + rank * PAIR_XBLK_ROWS), lead_bar);
+                tma_load_2d_pair(dst, &tmap_x, (int)(kb * GEMM_BK), (int)(m0 + rank * XR), lead_bar);
                 if (TB > 1u)
-                    tma_load_2d_pair(dst + PAIR_XBLK_BYTES, &tmap_x, (int)(kb * GEMM_BK),
-                                     (int)(m0 + 256u + rank * PAIR_XBLK_ROWS), lead_bar);
+                    tma_load_2d_pair(dst + XB, &tmap_x, (int)(kb * GEMM_BK), (int)(m0 + 2u * XR + rank * XR), lead_bar);
                 if (KS > 1u)      // the stage's second K step (one token block)
-                    tma_load_2d_pair(dst + PAIR_XBLK_BYTES, &tmap_x, (int)((kb + 1u) * GEMM_BK),
-                                     (int)(m0 + rank * PAIR_XBLK_ROWS), lead_bar);
+                    tma_load_2d_pair(dst + XB, &tmap_x, (int)((kb + 1u) * GEMM_BK), (int)(m0 + rank * XR), lead_bar);
             }
             if (*abort_flag) {
                 // The byte counts of this CTA's copies are kept by the leader's barriers, which
@@ -236,7 +241,7 @@ gemm_fp4_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const _
         // ---------------------------------------------------------------- MMA issuer (leader only)
         // The whole warp runs the loop with warp-uniform values; one elected lane issues.
         if (rank == 0) {
-            const uint32_t idesc = umma_idesc_f16_f32(256u, 256u);
+            const uint32_t idesc = umma_idesc_f16_f32(256u, 2u * XR);       // N = the tokens of one block, both CTAs' halves
             const uint32_t x_lo0 = umma_desc_lo(base), w_lo0 = umma_desc_lo(w_base);
             const uint32_t d0 = tmem_base, d1 = tmem_base + 256u;
             const bool reuse_a = (a.flags & 1u) != 0u;
@@ -263,7 +268,7 @@ gemm_fp4_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const _
                 if (TRACE) ti0 = clock64();
                 // low descriptor halves of this K step's tiles; +2 per 16 columns of K
                 const uint32_t b0 = x_lo0 + s * (XSB >> 4);
-                const uint32_t b1 = b0 + (PAIR_XBLK_BYTES >> 4);
+                const uint32_t b1 = b0 + (XB >> 4);
                 const uint32_t aw = w_lo0 + sw * (GEMM_W_TILE_BYTES >> 4);
                 if (elect_one()) {
                 if (TB > 1u) {
@@ -448,7 +453,7 @@ gemm_fp4_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const _
             float* const out = to_partial ? a.partial + (size_t)split * a.m * a.n : a.y;
             const float* const res = to_partial ? nullptr : a.r;
             const bool two_acc = TB == 1u && KB > 1u && !w_tmem;
-            for (uint32_t cc = slice; cc < TB * 16u; cc += 4u) {
+            for (uint32_t cc = slice; cc < TB * XR / 8u; cc += 4u) {     // chunks of 16 tokens: 2 XR tokens per block
                 const uint32_t t0 = m0 + cc * 16u;
                 if (t0 >= a.m) break;                        // warp-uniform
                 uint32_t v[16];

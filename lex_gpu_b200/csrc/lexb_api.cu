@@ -145,6 +145,7 @@ struct lexb_pipeline {
     uint32_t tm, stages, w_stages, tmem_cols, m_tiles, n_acc, flags;
     uint32_t raw_stages = lexb::PAIR_RAW_STAGES;
     uint32_t k_sub = 1;         // two-CTA kernel: K steps per ring stage
+    uint32_t x_rows = lexb::PAIR_XBLK_ROWS;     // two-CTA kernel: tokens per CTA and token block (tm / 2 for tiles below 512 tokens)
     uint32_t k_splits = 1, kb_per_split = 0, tok_blocks = 2;
     uint32_t ws_pitch = 0;      // block-scaled kernel: bytes per row of one scale load
     bool x_f32 = false;         // ... with f32 activations
@@ -327,7 +328,7 @@ int get_maps(const lexb_pipeline* p, const void* x, const void* wq, const void* 
     int rc;
     // x f16[m, k] row-major; box = 64 columns (128 bytes, the swizzle span) x the tile's tokens, never
     // taller than the tensor.  Rows past m are filled with zeros by the copy engine.
-    const uint32_t box_rows = pair ? (p->m < lexb::PAIR_XBLK_ROWS ? p->m : lexb::PAIR_XBLK_ROWS) : (p->tm < p->m ? p->tm : p->m);
+    const uint32_t box_rows = pair ? (p->m < p->x_rows ? p->m : p->x_rows) : (p->tm < p->m ? p->tm : p->m);
     if (p->kernel != KERNEL_MATMUL_Q &&      // that kernel reads x with plain loads
         (rc = encode_2d(p, &e.map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, x, p->k, p->m, lexb::GEMM_BK, box_rows,
                         CU_TENSOR_MAP_SWIZZLE_128B, "x")))
@@ -419,13 +420,13 @@ int launch_one(lexb_gpu* g, const lexb_pipeline* p, const lexb_buffer* x, const 
         // can be read side by side (the gap between them on the GPU's global timer)
         if (a.trace && 2u * p->grid <= g->trace_ctas) a.trace += 16ull * p->grid * (g->trace_toggle++ & 1u);
         a.m = p->m; a.n = p->n; a.k = p->k;
-        a.tm = p->tm; a.stages = p->stages; a.w_stages = p->w_stages; a.raw_stages = p->raw_stages; a.k_sub = p->k_sub;
+        a.tm = p->tm; a.stages = p->stages; a.w_stages = p->w_stages; a.raw_stages = p->raw_stages; a.k_sub = p->k_sub; a.x_rows = p->x_rows;
         // bit 0: operand-collector hint; bit 1 (two-CTA kernel): the packed weights are constant - declared, or
         // proven from the step list - so their copy and decode may run ahead of the stream's order
         a.flags = p->flags | ((p->w_const || (order.early_weights && !p->w_volatile)) ? 2u : 0u);
         a.k_splits = p->k_splits; a.kb_per_split = p->kb_per_split; a.partial = p->partial; a.tok_blocks = p->tok_blocks;
         a.tmem_cols = p->tmem_cols; a.m_tiles = p->m_tiles; a.n_acc = p->n_acc;
-        a.x_tx_bytes = p->kernel == KERNEL_TCGEN05_PAIR ? (p->m < lexb::PAIR_XBLK_ROWS ? p->m : lexb::PAIR_XBLK_ROWS) * 128u
+        a.x_tx_bytes = p->kernel == KERNEL_TCGEN05_PAIR ? (p->m < p->x_rows ? p->m : p->x_rows) * 128u
                                                         : (p->tm < p->m ? p->tm : p->m) * 128u;
         if (p->kernel == KERNEL_TCGEN05_PAIR) {
             // Programmatic dependent launch: this kernel's blocks may be scheduled while the previous
@@ -1167,61 +1168,67 @@ int lexb_gemm_fp4_plan(lexb_gpu* g, uint32_t m, uint32_t n, uint32_t k, int resi
     } else if (kernel == KERNEL_TCGEN05_PAIR) {
         if (n % lexb::GEMM_TN) return bail(fail(LEXB_ERR_SHAPE, "gemm_fp4 (pair): %u rows per CTA do not divide n = %u", lexb::GEMM_TN, n));
         if (k % lexb::PAIR_RAW_K) return bail(fail(LEXB_ERR_SHAPE, "gemm_fp4 (pair): the packed-weight block of %u columns does not divide k = %u", lexb::PAIR_RAW_K, k));
-        const uint32_t raw_stages = env_u32("LEXB_RAWSTAGES", lexb::PAIR_RAW_STAGES);
-        p->raw_stages = raw_stages;
-        // 512 tokens per tile (each weight decoded once for 512 tokens) when there are that many; tm = 256 asks for
-        // tiles of 256 tokens at any m: twice the tiles and two accumulators per tile, each weight decoded twice
-        if (s.tm && s.tm != 256u && s.tm != 512u)
-            return bail(fail(LEXB_ERR_ARG, "tm = %u: the two-CTA kernel's tiles hold 256 or 512 tokens", s.tm));
-        p->tok_blocks = (m > 256u && s.tm != 256u) ? 2u : 1u;
-        p->tm = p->tok_blocks * 256u;
+        // Tiles of 512 tokens (two blocks of 256: each weight decoded once for 512 tokens), 256, 128 or 64 (one block;
+        // the MMAs' N shrinks with it, the decode per tile does not); tm asks for one of them at any m
+        if (s.tm && s.tm != 64u && s.tm != 128u && s.tm != 256u && s.tm != 512u)
+            return bail(fail(LEXB_ERR_ARG, "tm = %u: the two-CTA kernel's tiles hold 64, 128, 256 or 512 tokens", s.tm));
+        p->tm = s.tm ? s.tm : (m > 256u ? 512u : m > 128u ? 256u : m > 64u ? 128u : 64u);
+        p->tok_blocks = p->tm == 512u ? 2u : 1u;
         p->flags = env_u32("LEXB_COLLECTOR", 0) ? 1u : 0u; p->tmem_cols = lexb::PAIR_TMEM_COLS; p->n_acc = 1;
         p->m_tiles = (m + p->tm - 1) / p->tm;
         const uint32_t n_pairs = (n + 2u * lexb::GEMM_TN - 1) / (2u * lexb::GEMM_TN);
         // Two ways to fill the SM pairs when whole tiles fill them badly (few tiles, or a short last wave).  Split K:
         // each split takes whole blocks of 256 columns (at least 4) and writes a partial product that a second
-        // launch sums.  Tiles of 256 tokens when m > 256: twice the tiles; every weight is decoded twice, but a K
-        // step's MMAs take half as long, a tile's partial product is half as large and fewer splits are needed.
-        // Every (tile, splits) pair is priced with figures fitted to launches timed on a B200 (us; rms error 6 %):
-        // per wave of tiles 13.0 / 7.6 for a block's start and its store of a 512 / 256-token tile and 0.593 / 0.367
-        // per K step; for the reduction launch 1.05 plus its bytes at 3.93 TB/s; minus 3.85 overall.  The cheapest
-        // wins; a smaller tile or a further split must win by 2 %.
+        // launch sums.  Smaller tiles: more of them; every weight is decoded once per tile of tokens, but a tile's
+        // partial product and its store shrink with it and fewer splits are needed.  (Below 256 tokens a K step
+        // costs the same: it is the decode that bounds it, not the MMAs.)
+        // Every (tile, splits) pair is priced with figures fitted to 159 launches timed on a B200 (us; rms error
+        // 4 %): 4.5 overall; per wave of tiles 8.05 / 5.3 / 4.0 / 4.1 for a block's start and its store of a
+        // 512 / 256 / 128 / 64-token tile and 0.559 / 0.311 / 0.310 / 0.304 per K step; for the reduction launch its
+        // bytes at 3.33 TB/s minus 1.1.  The cheapest wins; a smaller tile or a further split must win by 2 %.
         const uint32_t sm_pairs = static_cast<uint32_t>(g->prop.multiProcessorCount) / 2u;
         const uint32_t raw_blocks = k / lexb::PAIR_RAW_K;
         uint32_t splits = s.k_splits ? s.k_splits : 1u;
         {
-            auto model = [&](uint32_t tb, uint32_t c, uint32_t* eff_out) {
-                const uint32_t mt = (m + tb * 256u - 1u) / (tb * 256u);
+            // per tile size 512 / 256 / 128 / 64: us per K step, us per wave for a block's start and store
+            static const double kstep_us[4] = {0.559, 0.311, 0.310, 0.304}, wave_us[4] = {8.05, 5.32, 4.02, 4.14};
+            auto model = [&](uint32_t ti, uint32_t c, uint32_t* eff_out) {
+                const uint32_t tt = 512u >> ti;
+                const uint32_t mt = (m + tt - 1u) / tt;
                 const uint32_t rbs = (raw_blocks + c - 1u) / c, eff = (raw_blocks + rbs - 1u) / rbs;
                 const double waves = static_cast<double>((mt * n_pairs * eff + sm_pairs - 1u) / sm_pairs);
-                double us = -3.85 + waves * (rbs * 4.0 * (tb == 2u ? 0.593 : 0.367) + (tb == 2u ? 13.0 : 7.6));
-                if (eff > 1u) us += 1.05 + static_cast<double>(eff) * m * n * 4.0 / 3.93e6;
+                double us = 4.51 + waves * (rbs * 4.0 * kstep_us[ti] + wave_us[ti]);
+                if (eff > 1u) us += -1.12 + static_cast<double>(eff) * m * n * 4.0 / 3.33e6;
                 *eff_out = eff;
                 return us;
             };
             double best = 1e30;
-            uint32_t best_tb = p->tok_blocks, best_c = splits;
-            for (uint32_t tb = 2u; tb >= 1u; tb--) {
-                if (tb != p->tok_blocks && (s.tm || m <= 256u)) continue;           // the caller fixed the tile
+            uint32_t best_tt = p->tm, best_c = splits;
+            for (uint32_t ti = 0; ti < 4u; ti++) {
+                const uint32_t tt = 512u >> ti;
+                if (s.tm ? tt != s.tm : (tt != 64u && tt / 2u >= m)) continue;      // the caller's tile; or no tile more than half empty
                 for (uint32_t c = 1; c <= 8u && (c == 1u || raw_blocks / c >= 4u); c++) {
                     if (s.k_splits && c != s.k_splits) continue;                    // the caller fixed the splits
                     uint32_t eff = 0;
-                    const double us = model(tb, c, &eff);
+                    const double us = model(ti, c, &eff);
                     if (eff != c && !s.k_splits) continue;                          // the same plan as a smaller c
                     if (us < best * 0.98) {
                         best = us;
-                        best_tb = tb;
+                        best_tt = tt;
                         best_c = c;
                     }
                 }
             }
             splits = best_c;
-            if (best_tb != p->tok_blocks) {
-                p->tok_blocks = best_tb;
-                p->tm = best_tb * 256u;
-                p->m_tiles = (m + p->tm - 1u) / p->tm;
-            }
+            p->tm = best_tt;
+            p->tok_blocks = best_tt == 512u ? 2u : 1u;
+            p->m_tiles = (m + p->tm - 1u) / p->tm;
         }
+        p->x_rows = p->tm == 512u ? lexb::PAIR_XBLK_ROWS : p->tm / 2u;
+        // packed-weight blocks in flight: 2; 3 with tiles of 128 tokens or fewer, whose K step is short enough for the
+        // third block's trip to HBM to show (2-3 % per launch)
+        const uint32_t raw_stages = env_u32("LEXB_RAWSTAGES", p->tm <= 128u ? 3u : lexb::PAIR_RAW_STAGES);
+        p->raw_stages = raw_stages;
         if (splits < 1u || splits > raw_blocks) return bail(fail(LEXB_ERR_ARG, "k_splits = %u outside [1, %u]", splits, raw_blocks));
         // Ring depths.  Tiles of 512 tokens: x ring of 4 stages of 32 KiB, W ring of 3 of 16 KiB, two packed-weight
         // blocks: 212 KiB; their K step is bound by the MMAs.  Tiles of 256 tokens: a K step's MMAs take half as
@@ -1235,11 +1242,11 @@ int lexb_gemm_fp4_plan(lexb_gpu* g, uint32_t m, uint32_t n, uint32_t k, int resi
         const bool w_tmem = p->tok_blocks == 1u && s.w_stages <= 8u && env_u32("LEXB_WTMEM", 1u) != 0u;
         uint32_t k_sub = (w_tmem && env_u32("LEXB_KSUB", 2u) == 2u) ? 2u : 1u;
         if (k_sub == 2u && (s.w_stages > 4u ||
-                            lexb::pair_smem_bytes(1u, s.stages ? s.stages : 4u, s.w_stages ? s.w_stages : 4u, raw_stages, true, 2u) > g->smem_optin))
+                            lexb::pair_smem_bytes(1u, s.stages ? s.stages : 4u, s.w_stages ? s.w_stages : 4u, raw_stages, true, 2u, p->x_rows) > g->smem_optin))
             k_sub = 1u;
         const uint32_t stages = s.stages ? s.stages : (p->tok_blocks == 2u ? 4u : k_sub == 2u ? 4u : w_tmem ? 8u : 6u);
         const uint32_t w_stages = s.w_stages ? s.w_stages : (p->tok_blocks == 2u ? 3u : k_sub == 2u ? 4u : w_tmem ? 8u : 5u);
-        const uint32_t need = lexb::pair_smem_bytes(p->tok_blocks, stages, w_stages, raw_stages, w_tmem, k_sub);
+        const uint32_t need = lexb::pair_smem_bytes(p->tok_blocks, stages, w_stages, raw_stages, w_tmem, k_sub, p->x_rows);
         if (stages < 2 || w_stages < 2 || raw_stages < 2 || need > g->smem_optin)
             return bail(fail(LEXB_ERR_ARG, "stages = %u with w_stages = %u and %u packed-weight blocks need %u bytes of shared memory (limit %zu)",
                              stages, w_stages, raw_stages, need, g->smem_optin));
@@ -1712,7 +1719,7 @@ int lexb_gemm_fp4_splitk_static(lexb_gpu* g, uint32_t m, uint32_t n, uint32_t k,
     a.status = g->d_status;
     a.trace = nullptr;
     a.m = m; a.n = n; a.k = k;
-    a.tm = p.tm; a.stages = p.stages; a.w_stages = p.w_stages; a.raw_stages = p.raw_stages; a.k_sub = 1;
+    a.tm = p.tm; a.stages = p.stages; a.w_stages = p.w_stages; a.raw_stages = p.raw_stages; a.k_sub = 1; a.x_rows = lexb::PAIR_XBLK_ROWS;
     a.flags = p.tok_blocks == 1u ? 4u : 0u;      // tiles of 256 tokens: W tiles in tensor memory, as the planned pipeline has them
     a.k_splits = splits; a.kb_per_split = p.kb_per_split; a.tok_blocks = p.tok_blocks;
     a.partial = g->static_scratch;          // every element of the partials is written before it is read: nothing to clear

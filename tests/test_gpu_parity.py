@@ -174,6 +174,21 @@ def test_gemm_two_cta_kernel(gpu, m, n, k):
     check(L.gemm_fp4(gpu, x, wq, ws, wg, kernel=2), want)
 
 
+@pytest.mark.parametrize("m,n,k,tm,splits", [(64, 256, 512, 64, 0), (128, 256, 1024, 128, 0), (100, 384, 768, 64, 0),
+                                             (100, 384, 768, 128, 0), (512, 512, 2048, 128, 2), (512, 256, 1024, 64, 0),
+                                             (300, 256, 1024, 128, 3), (17, 256, 512, 0, 0), (48, 128, 256, 0, 0),
+                                             (129, 256, 768, 0, 0)])
+def test_gemm_two_cta_kernel_tiles_of_128_and_64_tokens(gpu, m, n, k, tm, splits):
+    """The narrower tiles (MMAs of N = 128 / 64, x boxes of 64 / 32 tokens per CTA), forced and as the planner picks them
+    for small m: partial last tiles, several tiles of tokens, split K, residual."""
+    x, wq, ws, wg = inputs.make_case(m, n, k, seed_base=m + k + tm)
+    r = inputs.make_residual(m, n, seed_base=3)
+    d = gpu.plan_gemm_fp4(m, n, k, kernel=3, tm=tm, k_splits=splits).describe()
+    assert int(d.entry.decode().split("_")[-3]) in ((tm,) if tm else (64, 128, 256))
+    check(L.gemm_fp4(gpu, x, wq, ws, wg, r=r, kernel=3, tm=tm, k_splits=splits), O.gemm_fp4(x, wq, ws, wg, r=r))
+    check(L.gemm_fp4(gpu, x, wq, ws, wg, kernel=3, tm=tm, k_splits=splits), O.gemm_fp4(x, wq, ws, wg))
+
+
 @pytest.mark.parametrize("tm", [256, 512])
 def test_gemm_two_cta_kernel_residual_and_stages(gpu, tm):
     """Ring depths around the defaults, for both tile sizes: (2, 2) makes the barrier rings (at least 4 deep) deeper
@@ -327,7 +342,9 @@ def test_describe_mirrors_the_lowered_descriptor(gpu):
     d = gpu.plan_gemm_fp4(256, 17408, 5120).describe()
     assert d.entry.decode() == "gemm_fp4_256_17408_5120_256_256_64" and d.kernel == 3 and d.grid == 136
     d = gpu.plan_gemm_fp4(64, 17408, 5120).describe()
-    assert d.entry.decode() == "gemm_fp4_64_17408_5120_256_256_64" and d.kernel == 3 and d.grid == 136
+    assert d.entry.decode() == "gemm_fp4_64_17408_5120_64_256_64" and d.kernel == 3 and d.grid == 136      # 64-token tiles
+    d = gpu.plan_gemm_fp4(128, 17408, 5120).describe()
+    assert d.entry.decode() == "gemm_fp4_128_17408_5120_128_256_64" and d.grid == 136
     assert gpu.plan_gemm_fp4(64, 2176, 5120).describe().kernel == 3         # few tiles: split K on CTA pairs
     assert gpu.plan_gemm_fp4(64, 256, 320).describe().kernel == 2           # k not in blocks of 256
     d = gpu.plan_gemm_fp4(4, 17408, 5120, residual=True).describe()
@@ -554,7 +571,6 @@ def test_gemm_m4096_stack_layer_shapes(gpu, n, k):
     additions, and so the bits, belong to the tile shape: the planner may pick another one for 512 tokens alone)."""
     m = 4096
     x, wq, ws, wg = inputs.make_case(m, n, k, seed_base=6)
-    assert gpu.plan_gemm_fp4(m, n, k).describe().entry.decode() == f"gemm_fp4_{m}_{n}_{k}_512_256_64"
     got = L.gemm_fp4(gpu, x, wq, ws, wg, k_splits=1, tm=512)
     _check_row_slices(got, x, wq, ws, wg, [(256, 384), (n - 128, n)], LONG_K_REL)
     sub = L.gemm_fp4(gpu, x[m - 512:].copy(), wq, ws, wg, k_splits=1, tm=512)

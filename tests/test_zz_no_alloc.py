@@ -42,7 +42,8 @@ def _static(gpu, x, wq, ws, wg, r, splits):
 
 
 def test_static_scratch_matches_the_planned_pipeline_on_two_calls_in_a_row(gpu):
-    # (192 tokens: one block of 256 tokens per tile, as the planner shapes m <= 256)
+    # (192 tokens: a tile of one token block; the static entry point and the planner may cut the tokens into
+    # different tiles - the sums per element, and so the bits, are the same)
     cases = [(512, 384, 2048, 4, True, 11), (300, 256, 1024, 2, False, 12), (192, 256, 1024, 2, True, 13)]
     for m, n, k, splits, with_r, seed in cases:
         x, wq, ws, wg = inputs.make_case(m, n, k, seed_base=seed)
