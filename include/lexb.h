@@ -59,10 +59,12 @@ typedef struct lexb_device_info {
 typedef struct lexb_sched {
     uint32_t kernel;  /* 0 auto, 1 matvec (m <= 16), 2 tcgen05 GEMM, 3 two-CTA tcgen05 GEMM,
                        * 4 block-scaled FP4 tensor-core kernel (m <= 32; matmul_q_x arithmetic, never chosen by auto) */
-    uint32_t tm;      /* tokens per CTA tile of the GEMM: multiple of 16, <= 256 */
+    uint32_t tm;      /* tokens per tile of the GEMM: one-CTA kernel a multiple of 16, <= 256; two-CTA kernel 64, 128,
+                       * 256 or 512 (0: the planner prices every size with every K split and takes the cheapest) */
     uint32_t stages;  /* pipeline depth of the GEMM */
     uint32_t kc;      /* K columns of x staged per chunk in the matvec: multiple of 1024 */
-    uint32_t w_stages; /* two-CTA GEMM: depth of the ring of decoded W tiles (stages = depth of the x ring) */
+    uint32_t w_stages; /* two-CTA GEMM: depth of the ring of decoded W tiles (stages = depth of the x ring); tiles below
+                        * 512 tokens keep that ring in tensor memory: at most 8 stages there, more puts it in shared memory */
     uint32_t k_splits; /* two-CTA GEMM: split K this many ways (partials in a workspace the pipeline owns, then summed) */
     uint32_t flags;    /* LEXB_SCHED_* bits */
 } lexb_sched;
