@@ -1,30 +1,36 @@
-// gemm_fp4 for m > 256 on sm_100a: the two-CTA form of gemm_fp4_sm100.cuh.
+// gemm_fp4 for m > 8 on sm_100a: the two-CTA form of gemm_fp4_sm100.cuh.
 //
 // The cost of a tile is the FP4 decode, not the multiply (the reference found the same on Ada,
 // crates/lex-msl/src/gemm.rs:107-110), so every weight should be decoded once for as many
-// tokens as possible.  A pair of CTAs (one cluster, two SMs) owns 256 rows of W and 512
+// tokens as possible.  A pair of CTAs (one cluster, two SMs) owns 256 rows of W and up to 512
 // tokens: each CTA decodes its own 128 rows once per K step, each loads half of the x tile
 // (two blocks of 128 tokens), and the leader CTA issues tcgen05.mma.cta_group::2 - M = 256
-// rows of W (128 from each CTA's shared memory), N = 256 tokens (128 from each) - twice per
-// 16 columns of K, once per token block.  Each CTA's TMEM then holds its 128 weight rows x 512
-// tokens (all 512 columns).  Per CTA and K step of 64 that is 1024 tensor-core clocks for 8192
-// decoded weights: twice the decode budget of the one-CTA kernel, and half its shared-memory
-// traffic for x.
+// rows of W (128 from each CTA), N = 256 tokens (128 from each) - twice per 16 columns of K,
+// once per token block.  Each CTA's TMEM then holds its 128 weight rows x 512 tokens (all 512
+// columns).  Per CTA and K step of 64 that is 1024 tensor-core clocks for 8192 decoded weights:
+// twice the decode budget of the one-CTA kernel, and half its shared-memory traffic for x.
+//
+// Smaller tiles have one token block of 256, 128 or 64 tokens (N of the MMAs; each CTA holds
+// half).  Their decoded W tiles go to tensor memory instead of shared memory - the accumulator
+// leaves at least 256 of the 512 columns free - and the MMAs take their A operand from there;
+// a ring stage then holds two K steps.
 //
 // The packed weights never pass through a dequant thread's global loads: a third single-thread
 // role brings them in by TMA, 256 columns of K at a time (a [128 rows x 128 bytes] tile of codes,
-// 128-byte swizzled, and a [128 x 16 bytes] tile of scales), two such blocks in flight, and the
-// dequant threads read their 8 bytes of codes and 1 scale byte per K step from shared memory.
+// 128-byte swizzled, and a [128 x 16 bytes] tile of scales), two or three such blocks in flight,
+// and a dequant thread reads its row's 32 bytes of codes and 4 scale bytes of a K step from
+// shared memory.
 //
-// Barriers: the MMA warp's own loop sets the pace of a K step when the MMAs are short (every wait it makes
-// costs about a hundred cycles even when the barrier is ready, every commit more), so a K step has ONE barrier
-// the MMA warp waits on and ONE it signals.  `full[j]` (leader CTA) collects everything K step j needs: the two
-// x producers' arrive.expect_tx (the partner's through a shared::cluster address; its TMA reports bytes to the
-// leader's barrier), the four warps of the leader's decode group that owns the K step, and one arrival from the
-// partner's relay thread, which waits on the partner's own `w_part` barrier for its four warps.  `done[j]` exists in both CTAs and is signalled
-// in both by one tcgen05.commit: it frees the x stage and the W stage of K step j at once.  Both rings of
-// barriers are indexed by K step modulo max(x stages, W stages, 4); the data rings keep their own depths.
-// No TMA multicast is used.
+// Barriers: the MMA warp's own loop sets the pace of a K step when the MMAs are short (every wait it
+// makes costs about a hundred cycles even when the barrier is ready, every commit more), so a ring
+// stage has ONE barrier the MMA warp waits on and ONE it signals.  `full[j]` (leader CTA) collects
+// everything stage step j needs: the two x producers' arrive.expect_tx (the partner's through a
+// shared::cluster address; its TMA reports bytes to the leader's barrier), the four warps of each
+// decode group of the leader that owns a K step of it, and one arrival from the partner's relay
+// thread, which waits on the partner's own `w_part` barrier for its warps.  `done[j]` exists in both
+// CTAs and is signalled in both by one tcgen05.commit: it frees the x stage and the W stage of step j
+// at once.  Both rings of barriers are indexed by step modulo max(x stages, W stages, 4); the data
+// rings keep their own depths.  No TMA multicast is used.
 #pragma once
 #include "fp4_decode.cuh"
 #include "gemm_fp4_sm100.cuh"
@@ -32,7 +38,7 @@
 
 namespace lexb {
 
-constexpr uint32_t PAIR_TOKENS = 512;                 // tokens per pair tile
+constexpr uint32_t PAIR_TOKENS = 512;                 // tokens of the largest pair tile
 constexpr uint32_t PAIR_XBLK_ROWS = 128;              // tokens per TMA box (one CTA's half of a block)
 constexpr uint32_t PAIR_XBLK_BYTES = PAIR_XBLK_ROWS * 128u;                  // 16 KiB
 // a stage of the x ring holds this CTA's half of one token block (tiles of 256 tokens) or of two (512): 16 or 32 KiB
