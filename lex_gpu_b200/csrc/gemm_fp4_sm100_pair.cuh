@@ -95,6 +95,7 @@ gemm_fp4_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const _
     // mode a ring stage may hold two K steps (k_sub = 2): two decode groups fill one stage and that loop runs half as
     // often.
     const bool w_tmem = (a.flags & 4u) != 0u && a.tok_blocks == 1u;
+    const uint32_t a_col0 = XR <= 64u ? 128u : 256u;                       // first TMEM column of the W ring: behind the accumulator
     const uint32_t raw_base = w_base + (w_tmem ? 0u : SW * GEMM_W_TILE_BYTES);     // packed weight blocks
     const uint32_t rings_end = raw_base + SR * PAIR_RAW_BYTES;
     const uint32_t bars = rings_end > base + PAIR_STAGING_BYTES ? rings_end : base + PAIR_STAGING_BYTES;
@@ -192,8 +193,8 @@ gemm_fp4_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const _
                 tma_load_2d_pair(dst, &tmap_x, (int)(kb * GEMM_BK), (int)(m0 + rank * XR), lead_bar);
                 if (TB > 1u)
                     tma_load_2d_pair(dst + XB, &tmap_x, (int)(kb * GEMM_BK), (int)(m0 + 2u * XR + rank * XR), lead_bar);
-                if (KS > 1u)      // the stage's second K step (one token block)
-                    tma_load_2d_pair(dst + XB, &tmap_x, (int)((kb + 1u) * GEMM_BK), (int)(m0 + rank * XR), lead_bar);
+                for (uint32_t sub = 1; sub < KS; sub++)      // the stage's further K steps (one token block)
+                    tma_load_2d_pair(dst + sub * XB, &tmap_x, (int)((kb + sub) * GEMM_BK), (int)(m0 + rank * XR), lead_bar);
             }
             if (*abort_flag) {
                 // The byte counts of this CTA's copies are kept by the leader's barriers, which
@@ -298,14 +299,14 @@ gemm_fp4_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const _
                         }
                     }
                 } else if (w_tmem) {
-                    const uint32_t at = tmem_base + 256u + sw * (32u * KS);
+                    const uint32_t at = tmem_base + a_col0 + sw * (32u * KS);
                     umma2_ts_flag(d0, at, b0, idesc, kb != 0u);
 #pragma unroll
                     for (uint32_t kk = 1; kk < GEMM_BK / 16; kk++) umma2_ts_flag(d0, at + 8u * kk, b0 + 2u * kk, idesc, 1u);
-                    if (KS > 1u) {            // the stage's second K step: the next 32 columns, the next x block
+                    for (uint32_t sub = 1; sub < KS; sub++) {      // the stage's further K steps: the next 32 columns, the next x block
+                        const uint32_t as = at + 32u * sub, bs = b0 + sub * (XB >> 4);
 #pragma unroll
-                        for (uint32_t kk = 0; kk < GEMM_BK / 16; kk++)
-                            umma2_ts_flag(d0, at + 32u + 8u * kk, b1 + 2u * kk, idesc, 1u);
+                        for (uint32_t kk = 0; kk < GEMM_BK / 16; kk++) umma2_ts_flag(d0, as + 8u * kk, bs + 2u * kk, idesc, 1u);
                     }
                 } else {
                     // one token block: even and odd K steps go to two accumulators, which halves the
@@ -414,7 +415,7 @@ gemm_fp4_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const _
                     v[4u * c + 2u] = o[c].z;
                     v[4u * c + 3u] = o[c].w;
                 }
-                tmem_st_32x32b_x32(tmem_base + ((32u * (warp & 3u)) << 16) + 256u + pw.s * (32u * KS) + sub_col, v);
+                tmem_st_32x32b_x32(tmem_base + ((32u * (warp & 3u)) << 16) + a_col0 + pw.s * (32u * KS) + sub_col, v);
                 tmem_st_wait();
                 tc_fence_before_sync();
             } else {

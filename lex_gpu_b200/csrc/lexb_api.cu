@@ -1231,21 +1231,24 @@ int lexb_gemm_fp4_plan(lexb_gpu* g, uint32_t m, uint32_t n, uint32_t k, int resi
         p->raw_stages = raw_stages;
         if (splits < 1u || splits > raw_blocks) return bail(fail(LEXB_ERR_ARG, "k_splits = %u outside [1, %u]", splits, raw_blocks));
         // Ring depths.  Tiles of 512 tokens: x ring of 4 stages of 32 KiB, W ring of 3 of 16 KiB, two packed-weight
-        // blocks: 212 KiB; their K step is bound by the MMAs.  Tiles of 256 tokens: a K step's MMAs take half as
-        // long and the shared-memory pipe sets the pace, so the decoded W tiles go to tensor memory (256 of its 512
-        // columns are free with one accumulator: 8 stages of 32 columns) and the MMAs read them from there; the x
-        // ring, 16 KiB a stage, gets 8 stages: 164 KiB.  A caller who asks for more than 8 W stages, or
-        // LEXB_WTMEM=0, gets the W ring in shared memory (x 6, W 5 by default).
-        // In that mode a ring stage holds two K steps (x 32 KiB, W 64 columns of TMEM, so at most 4 W stages) and
-        // the MMA warp waits and commits once per two K steps; depths the caller gives that do not fit that way are
-        // taken as stages of one K step.
+        // blocks: 212 KiB; their K step is bound by the MMAs.  Smaller tiles: a K step's MMAs take half as long or
+        // less and the shared-memory pipe would set the pace, so the decoded W tiles go to tensor memory (the columns
+        // behind the accumulator: 256 with tiles of 256 tokens, 384 below; 32 columns per K step) and the MMAs read
+        // them from there.  A ring stage then holds two K steps (x 2 x 16 KiB with 256 tokens, W 64 columns; x ring of
+        // 4, W ring of 4 or 6) or, with tiles of 128 tokens or fewer, a whole block of four (x ring of 3, W ring of 3),
+        // and the MMA warp waits and commits once per stage.  Depths the caller gives that do not fit that way are
+        // taken as stages of one K step (at most 8 W stages in tensor memory); more than 8 W stages, or
+        // LEXB_WTMEM=0, put the W ring in shared memory (x 6, W 5 by default).
         const bool w_tmem = p->tok_blocks == 1u && s.w_stages <= 8u && env_u32("LEXB_WTMEM", 1u) != 0u;
-        uint32_t k_sub = (w_tmem && env_u32("LEXB_KSUB", 2u) == 2u) ? 2u : 1u;
-        if (k_sub == 2u && (s.w_stages > 4u ||
-                            lexb::pair_smem_bytes(1u, s.stages ? s.stages : 4u, s.w_stages ? s.w_stages : 4u, raw_stages, true, 2u, p->x_rows) > g->smem_optin))
+        uint32_t k_sub = w_tmem ? env_u32("LEXB_KSUB", p->x_rows <= 64u ? 4u : 2u) : 1u;
+        if (k_sub != 1u && k_sub != 2u && k_sub != 4u) k_sub = 1u;
+        const uint32_t w_cols = p->x_rows <= 64u ? 384u : 256u;             // TMEM columns behind the accumulator
+        const uint32_t w_max = k_sub ? w_cols / (32u * k_sub) : 0u;
+        if (k_sub > 1u && (s.w_stages > w_max ||
+                            lexb::pair_smem_bytes(1u, s.stages ? s.stages : (k_sub == 4u ? 2u : 4u), 2u, raw_stages, true, k_sub, p->x_rows) > g->smem_optin))
             k_sub = 1u;
-        const uint32_t stages = s.stages ? s.stages : (p->tok_blocks == 2u ? 4u : k_sub == 2u ? 4u : w_tmem ? 8u : 6u);
-        const uint32_t w_stages = s.w_stages ? s.w_stages : (p->tok_blocks == 2u ? 3u : k_sub == 2u ? 4u : w_tmem ? 8u : 5u);
+        const uint32_t stages = s.stages ? s.stages : (p->tok_blocks == 2u ? 4u : k_sub == 4u ? (p->x_rows == 128u ? 2u : 3u) : k_sub == 2u ? 4u : w_tmem ? 8u : 6u);
+        const uint32_t w_stages = s.w_stages ? s.w_stages : (p->tok_blocks == 2u ? 3u : k_sub >= 2u ? w_cols / (32u * k_sub) : w_tmem ? 8u : 5u);
         const uint32_t need = lexb::pair_smem_bytes(p->tok_blocks, stages, w_stages, raw_stages, w_tmem, k_sub, p->x_rows);
         if (stages < 2 || w_stages < 2 || raw_stages < 2 || need > g->smem_optin)
             return bail(fail(LEXB_ERR_ARG, "stages = %u with w_stages = %u and %u packed-weight blocks need %u bytes of shared memory (limit %zu)",

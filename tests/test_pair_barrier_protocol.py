@@ -114,6 +114,13 @@ def test_protocol_is_safe_with_two_k_steps_per_stage(sx, sw):
         assert run(sx, sw, 2, 24, seed, 4, KS=2) == []
 
 
+@pytest.mark.parametrize("sx,sw", [(2, 2), (3, 3), (3, 2), (2, 3)])
+def test_protocol_is_safe_with_four_k_steps_per_stage(sx, sw):
+    """A ring stage holds a whole block of four K steps: all four decode groups fill one stage."""
+    for seed in range(6):
+        assert run(sx, sw, 2, 24, seed, 4, KS=4) == []
+
+
 def test_a_shallower_barrier_ring_lets_a_parity_wait_pass_early():
     found = [e for seed in range(12) for e in run(2, 2, 2, 24, seed, 1)]
     assert any(e.startswith("false pass") for e in found)
