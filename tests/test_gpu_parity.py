@@ -189,6 +189,34 @@ def test_gemm_two_cta_kernel_tiles_of_128_and_64_tokens(gpu, m, n, k, tm, splits
     check(L.gemm_fp4(gpu, x, wq, ws, wg, kernel=3, tm=tm, k_splits=splits), O.gemm_fp4(x, wq, ws, wg))
 
 
+def test_gemm_two_cta_kernel_seeded_random_plans(gpu):
+    """Forty seeded draws of (m, n, k, tile, K split, ring depths, residual) for the two-CTA kernel against the oracle:
+    every tile size with every stage layout it can take, odd last pairs, partial token tiles."""
+    rng = np.random.Generator(np.random.PCG64(20240611))
+    done = 0
+    for draw in range(200):
+        if done == 40:
+            break
+        m = int(rng.integers(9, 700))
+        n = 128 * int(rng.integers(1, 9))
+        k = 256 * int(rng.integers(1, 13))
+        tm = int(rng.choice([0, 64, 128, 256, 512]))
+        splits = int(rng.choice([0, 0, 1, 2, 3]))
+        stages, w_stages = (int(rng.integers(2, 7)), int(rng.integers(2, 9))) if rng.random() < 0.5 else (0, 0)
+        with_r = bool(rng.random() < 0.5)
+        try:
+            gpu.plan_gemm_fp4(m, n, k, with_r, kernel=3, tm=tm, k_splits=splits, stages=stages, w_stages=w_stages)
+        except L.LexbError:
+            continue                                  # a combination the planner refuses (shared memory, splits > blocks)
+        x, wq, ws, wg = inputs.make_case(m, n, k, seed_base=1000 + draw)
+        r = inputs.make_residual(m, n, seed_base=draw) if with_r else None
+        got = L.gemm_fp4(gpu, x, wq, ws, wg, r=r, kernel=3, tm=tm, k_splits=splits, stages=stages, w_stages=w_stages)
+        print(f"  draw {draw}: m={m} n={n} k={k} tm={tm} splits={splits} stages={stages}/{w_stages} r={with_r}")
+        check(got, O.gemm_fp4(x, wq, ws, wg, r=r), rel_tol=TOL if k < 2048 else LONG_K_REL)
+        done += 1
+    assert done == 40
+
+
 @pytest.mark.parametrize("tm", [256, 512])
 def test_gemm_two_cta_kernel_residual_and_stages(gpu, tm):
     """Ring depths around the defaults, for both tile sizes: (2, 2) makes the barrier rings (at least 4 deep) deeper
