@@ -15,6 +15,10 @@ the variant that all-gathers y over NCCL is timed separately and reported under 
 
 `--impl reference` times the CPU restatement of the reference interpreter (the reference is
 Rust and cannot be built here) on the host cores, on a bounded sample of the same workload.
+
+`--only gemm|matvec` times one kernel alone (short runs for profilers), `--no-sustained` leaves out
+the seconds-long run of the headline steps, and `--only gemm --tokens M` runs the headline matrices
+at another token count (other tile shapes of the same kernel); the full run is always m = 512.
 """
 from __future__ import annotations
 
